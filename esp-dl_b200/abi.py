@@ -1,0 +1,133 @@
+"""ctypes mirror of include/espdl_b200.h and loader of the CUDA backend library.
+
+This is plumbing for tests and the benchmark: the descriptors are the C structs
+of the C ABI, field for field.  The library is built in-tree by build.py; loading
+fails loudly (RuntimeError) when it is missing - there is no CPU fallback.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libespdl_b200.so")
+
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_NO_DEVICE, ERR_NO_MEM, ERR_TIMEOUT, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6, -7
+DTYPE_FLOAT, DTYPE_INT8, DTYPE_INT16, DTYPE_INT32, DTYPE_INT64 = 1, 3, 5, 6, 7
+ACT_LINEAR, ACT_RELU = 0, 1
+ROUND_HALF_UP, ROUND_HALF_EVEN = 0, 1
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
+ELT_ADD, ELT_MUL, ELT_REQUANTIZE, ELT_LUT, ELT_CLIP, ELT_RELU, ELT_PRELU, ELT_SUB = range(8)
+POOL_MAX, POOL_AVG, POOL_GLOBAL_AVG = 0, 1, 2
+
+i32 = C.c_int32
+
+
+class ConvDesc(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("filter", C.c_void_p), ("bias", C.c_void_p), ("output", C.c_void_p),
+        ("filter_exponents", C.c_void_p), ("lut", C.c_void_p),
+        ("dtype", i32), ("n", i32), ("in_h", i32), ("in_w", i32), ("in_c", i32),
+        ("out_h", i32), ("out_w", i32), ("out_c", i32), ("kh", i32), ("kw", i32),
+        ("stride_h", i32), ("stride_w", i32), ("dilation_h", i32), ("dilation_w", i32),
+        ("pad_top", i32), ("pad_bottom", i32), ("pad_left", i32), ("pad_right", i32),
+        ("group", i32), ("in_pixel_stride", i32), ("out_pixel_stride", i32),
+        ("in_exponent", i32), ("out_exponent", i32), ("filter_exponent", i32), ("per_channel", i32),
+        ("activation", i32), ("round_mode", i32), ("kernel", i32), ("reserved", i32),
+    ]
+
+
+class EltwiseDesc(C.Structure):
+    _fields_ = [
+        ("input0", C.c_void_p), ("input1", C.c_void_p), ("output", C.c_void_p),
+        ("op", i32), ("in_dtype", i32), ("out_dtype", i32), ("ndim", i32),
+        ("out_shape", i32 * 4), ("in0_shape", i32 * 4), ("in1_shape", i32 * 4),
+        ("in0_exponent", i32), ("in1_exponent", i32), ("out_exponent", i32),
+        ("clip_lo", i32), ("clip_hi", i32), ("round_mode", i32), ("reserved", i32),
+    ]
+
+
+class PoolDesc(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("output", C.c_void_p), ("op", i32), ("dtype", i32),
+        ("n", i32), ("in_h", i32), ("in_w", i32), ("c", i32), ("out_h", i32), ("out_w", i32),
+        ("kh", i32), ("kw", i32), ("stride_h", i32), ("stride_w", i32),
+        ("pad_top", i32), ("pad_bottom", i32), ("pad_left", i32), ("pad_right", i32),
+        ("in_exponent", i32), ("out_exponent", i32),
+    ]
+
+
+class ResizeDesc(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("output", C.c_void_p), ("dtype", i32),
+        ("n", i32), ("in_h", i32), ("in_w", i32), ("c", i32), ("out_h", i32), ("out_w", i32),
+        ("scale_h", C.c_float), ("scale_w", C.c_float),
+        ("in_exponent", i32), ("out_exponent", i32), ("out_pixel_stride", i32), ("reserved", i32),
+    ]
+
+
+class CopyDesc(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p), ("dst", C.c_void_p), ("elem_size", i32), ("ndim", i32),
+        ("shape", i32 * 6), ("src_stride", C.c_int64 * 6), ("dst_stride", C.c_int64 * 6),
+    ]
+
+
+class SoftmaxDesc(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("output", C.c_void_p), ("exp_table", C.c_void_p),
+        ("rows", i32), ("len", i32), ("out_dtype", i32), ("out_exponent", i32),
+    ]
+
+
+# every symbol include/espdl_b200.h declares: name -> (restype, argtypes)
+SYMBOLS = {
+    "espdl_b200_init": (C.c_int, [C.c_int]),
+    "espdl_b200_shutdown": (None, []),
+    "espdl_b200_strerror": (C.c_char_p, [C.c_int]),
+    "espdl_b200_last_error": (C.c_char_p, []),
+    "espdl_b200_arena_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "espdl_b200_arena_free": (C.c_int, [C.c_void_p]),
+    "espdl_b200_upload": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "espdl_b200_download": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "espdl_b200_memset": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
+    "espdl_b200_stream_sync": (C.c_int, [C.c_void_p]),
+    "espdl_b200_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "espdl_b200_host_free": (C.c_int, [C.c_void_p]),
+    "espdl_b200_launch_count": (C.c_uint64, []),
+    "espdl_b200_conv2d": (C.c_int, [C.POINTER(ConvDesc), C.c_void_p]),
+    "espdl_b200_conv2d_workspace_bytes": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]),
+    "espdl_b200_conv2d_ws": (C.c_int, [C.POINTER(ConvDesc), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "espdl_b200_eltwise": (C.c_int, [C.POINTER(EltwiseDesc), C.c_void_p]),
+    "espdl_b200_pool": (C.c_int, [C.POINTER(PoolDesc), C.c_void_p]),
+    "espdl_b200_resize": (C.c_int, [C.POINTER(ResizeDesc), C.c_void_p]),
+    "espdl_b200_copy": (C.c_int, [C.POINTER(CopyDesc), C.c_void_p]),
+    "espdl_b200_softmax": (C.c_int, [C.POINTER(SoftmaxDesc), C.c_void_p]),
+}
+
+_lib = None
+
+
+def bind(lib, symbols=SYMBOLS):
+    for name, (res, args) in symbols.items():
+        fn = getattr(lib, name)  # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+def load():
+    """Load libespdl_b200.so (built by build.py).  Raises if it is absent: no fallback exists."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'`; "
+                "the backend has no CPU or PyTorch fallback")
+        _lib = bind(C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL))
+    return _lib
+
+
+def check(status, what=""):
+    if status != OK:
+        lib = load()
+        raise RuntimeError(
+            f"{what}: {lib.espdl_b200_strerror(status).decode()} ({status}) {lib.espdl_b200_last_error().decode()}")

@@ -1,0 +1,250 @@
+/*
+ * espdl_b200.h - C ABI of the B200 (sm_100a) backend for ESP-DL's quantized
+ * operator forward path.
+ *
+ * ESP-DL itself has no C ABI: its operator layer is a set of C++ free
+ * functions that take a pointer to a POD argument block, e.g.
+ *   void dl::base::conv2d<int8_t,int32_t,int32_t>(void *args)   esp-dl/dl/base/dl_base_conv2d.hpp:15
+ * with args -> dl::base::ArgsType<T>                            esp-dl/dl/base/dl_base.hpp:12-98
+ * Each entry point below replaces one family of those functions.  The
+ * descriptor structs carry the same information as the reference argument
+ * blocks (pointers, NHWC extents, strides/dilations/pads, exponents,
+ * activation), but with DEVICE pointers and an explicit batch extent.
+ *
+ * Conventions
+ *  - every function returns ESPDL_OK (0) or a negative ESPDL_ERR_* code and
+ *    never throws or aborts;
+ *  - kernels are enqueued on the caller's CUDA stream (a cudaStream_t passed
+ *    as void*; NULL = the legacy default stream) and are asynchronous;
+ *  - all buffers are caller-owned device memory unless stated otherwise;
+ *  - activations are NHWC, value = q * 2^exponent (dl::TensorBase,
+ *    esp-dl/dl/tensor/include/dl_tensor_base.hpp:297-344);
+ *  - convolution filters use the reference's "c" target memory order
+ *    [Cout][KH][KW][Cin] (esp-dl/dl/base/dl_base_conv2d.cpp:140-162) and
+ *    depthwise filters [KH][KW][C] (esp-dl/dl/base/dl_base_depthwise_conv2d.cpp:47-66).
+ */
+#ifndef ESPDL_B200_H
+#define ESPDL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ status */
+#define ESPDL_OK 0
+#define ESPDL_ERR_INVALID_ARG (-1) /* NULL pointer, bad extent, bad enum            */
+#define ESPDL_ERR_UNSUPPORTED (-2) /* a combination the backend does not implement  */
+#define ESPDL_ERR_CUDA (-3)        /* a CUDA runtime/driver call failed             */
+#define ESPDL_ERR_NO_DEVICE (-4)   /* no usable sm_100 device / not initialised     */
+#define ESPDL_ERR_NO_MEM (-5)      /* device allocation failed                      */
+#define ESPDL_ERR_TIMEOUT (-6)     /* a bounded device-side wait expired            */
+#define ESPDL_ERR_TOO_LARGE (-7)   /* size beyond a documented fixed maximum        */
+
+/* Same numeric values as dl::dtype_t (esp-dl/dl/tensor/include/dl_tensor_base.hpp:216-233). */
+typedef enum {
+    ESPDL_DTYPE_FLOAT = 1,
+    ESPDL_DTYPE_INT8 = 3,
+    ESPDL_DTYPE_INT16 = 5,
+    ESPDL_DTYPE_INT32 = 6,
+    ESPDL_DTYPE_INT64 = 7
+} espdl_dtype_t;
+
+/* Same numeric values as dl::activation_type_t (esp-dl/dl/dl_define.hpp:108-114). */
+typedef enum { ESPDL_ACT_LINEAR = 0, ESPDL_ACT_RELU = 1, ESPDL_ACT_LEAKYRELU = 2, ESPDL_ACT_PRELU = 3 } espdl_act_t;
+
+/* Rounding of the requantisation shift: HALF_UP is what the reference's generic
+ * C build does, HALF_EVEN what ESP32-P4 silicon does
+ * (esp-dl/dl/dl_define_private.hpp:44-48, esp-dl/dl/tool/src/dl_tool.cpp:95-146). */
+typedef enum { ESPDL_ROUND_HALF_UP = 0, ESPDL_ROUND_HALF_EVEN = 1 } espdl_round_t;
+
+/* Kernel selection.  AUTO picks the tensor-core (tcgen05) tile kernel when the
+ * shape allows it and the CUDA-core kernel otherwise; the other two values
+ * force one path (UNSUPPORTED is returned if it cannot run the shape). */
+typedef enum { ESPDL_KERNEL_AUTO = 0, ESPDL_KERNEL_SIMT = 1, ESPDL_KERNEL_TCGEN05 = 2 } espdl_kernel_t;
+
+/* -------------------------------------------------------------- life cycle */
+/* Select `device`, check that it is an sm_100 part, create internal state. */
+int espdl_b200_init(int device);
+void espdl_b200_shutdown(void);
+const char *espdl_b200_strerror(int status);
+/* Human-readable text of the last failing CUDA call on this thread ("" if none). */
+const char *espdl_b200_last_error(void);
+
+/* Device memory for tensors (the arena of dl::ModelContext lives in one such block). */
+int espdl_b200_arena_alloc(size_t bytes, void **dptr);
+int espdl_b200_arena_free(void *dptr);
+int espdl_b200_upload(void *dst_dev, const void *src_host, size_t bytes, void *stream);
+int espdl_b200_download(void *dst_host, const void *src_dev, size_t bytes, void *stream);
+int espdl_b200_memset(void *dst_dev, int value, size_t bytes, void *stream);
+int espdl_b200_stream_sync(void *stream);
+/* Pinned host staging memory (for the end-to-end path with host buffers). */
+int espdl_b200_host_alloc(size_t bytes, void **hptr);
+int espdl_b200_host_free(void *hptr);
+/* Number of kernels this library has launched since init (all entry points). */
+uint64_t espdl_b200_launch_count(void);
+
+/* ------------------------------------------------------------ convolution */
+/*
+ * Conv2D / pointwise conv / Gemm / MatMul / DepthwiseConv2D, int8 or int16.
+ * Replaces dl::base::conv2d<> and dl::base::depthwise_conv2d<>
+ * (esp-dl/dl/base/dl_base_conv2d.cpp:1383-1411,912-939;
+ *  esp-dl/dl/base/dl_base_depthwise_conv2d.cpp:495,854) including the argument
+ * derivation of dl::base::ConvOpArgs (esp-dl/dl/base/dl_base.hpp:132-380).
+ *
+ *   out[n,y,x,o] = sat( act( rnd( (sum_{ky,kx,c} in[n, y*sh+ky*dh-pt, x*sw+kx*dw-pl, c] * w[o,ky,kx,c]
+ *                                  + bias[o]) , shift[o] ) ) )
+ *   shift[o] = out_exponent - filter_exponent[o] - in_exponent
+ *
+ * Taps outside the image are skipped (== zero padding).  A Gemm of A[M,K] by
+ * W[N][K] is the call n=1,in_h=1,in_w=M,in_c=K,out_c=N,kh=kw=1
+ * (esp-dl/dl/module/include/dl_module_gemm.hpp:85-123).
+ * group is 1 (dense) or in_c (depthwise, out_c == in_c).
+ */
+typedef struct espdl_conv_desc {
+    const void *input;                /* NHWC, dtype                                                   */
+    const void *filter;               /* [out_c][kh][kw][in_c] (group 1) or [kh][kw][in_c] (depthwise) */
+    const void *bias;                 /* int32[out_c] (int8 op) / int64[out_c] (int16 op), or NULL     */
+    void *output;                     /* NHWC, dtype                                                   */
+    const int32_t *filter_exponents;  /* device int32[out_c] if per_channel, else ignored              */
+    const int8_t *lut;                /* optional device int8[256]: out = lut[(uint8)q ^ 0x80] after
+                                         the epilogue (a fused dl::module::LUT node); int8 only        */
+    int32_t dtype;                    /* ESPDL_DTYPE_INT8 or ESPDL_DTYPE_INT16                         */
+    int32_t n, in_h, in_w, in_c;
+    int32_t out_h, out_w, out_c;
+    int32_t kh, kw;
+    int32_t stride_h, stride_w;
+    int32_t dilation_h, dilation_w;
+    int32_t pad_top, pad_bottom, pad_left, pad_right;
+    int32_t group;
+    int32_t in_pixel_stride;          /* elements between consecutive input pixels; 0 = in_c (dense)   */
+    int32_t out_pixel_stride;         /* elements between consecutive output pixels; 0 = out_c (dense);
+                                         lets a producer write straight into a Concat slice            */
+    int32_t in_exponent, out_exponent;
+    int32_t filter_exponent;          /* used when per_channel == 0                                    */
+    int32_t per_channel;              /* 0 = per-tensor filter exponent, 1 = filter_exponents[out_c]   */
+    int32_t activation;               /* espdl_act_t: LINEAR or RELU                                   */
+    int32_t round_mode;               /* espdl_round_t                                                 */
+    int32_t kernel;                   /* espdl_kernel_t                                                */
+    int32_t reserved;
+} espdl_conv_desc;
+
+int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream);
+
+/*
+ * Scratch the int16 tensor-core path needs (the 8-bit limb planes of both
+ * operands).  Returns 0 bytes for shapes that need none.  Pass the buffer with
+ * espdl_b200_conv2d_ws; espdl_b200_conv2d allocates and caches one internally.
+ */
+int espdl_b200_conv2d_workspace_bytes(const espdl_conv_desc *desc, size_t *bytes);
+int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------ elementwise */
+typedef enum {
+    ESPDL_ELT_ADD = 0,        /* sat(a + b), numpy broadcasting       esp-dl/dl/base/dl_base_add.cpp:8-44          */
+    ESPDL_ELT_MUL = 1,        /* sat(round((a*b) * 2^(ea+eb-eo)))     esp-dl/dl/base/dl_base_mul.cpp:9-46          */
+    ESPDL_ELT_REQUANTIZE = 2, /* TensorBase::assign: int<->int, float->int, int->float
+                                                                      esp-dl/dl/tensor/src/dl_tensor_base.cpp:223-404 */
+    ESPDL_ELT_LUT = 3,        /* out = table[(uint8)in ^ 0x80]        esp-dl/dl/base/dl_base_lut.cpp:10-15         */
+    ESPDL_ELT_CLIP = 4,       /* sat(round(clamp(q,lo,hi) * 2^(ei-eo))) esp-dl/dl/module/include/dl_module_clip.hpp:78-90 */
+    ESPDL_ELT_RELU = 5,       /* max(q,0) then requantise if exponents differ
+                                                                      esp-dl/dl/module/include/dl_module_relu.hpp  */
+    ESPDL_ELT_PRELU = 6,      /* q<0 ? sat((q*alpha[c]) >> shift) : q esp-dl/dl/base/dl_base_prelu.cpp:5-19        */
+    ESPDL_ELT_SUB = 7         /* sat(a - b)                           esp-dl/dl/base/dl_base_sub.cpp               */
+} espdl_eltwise_op_t;
+
+typedef struct espdl_eltwise_desc {
+    const void *input0;
+    const void *input1;       /* ADD/MUL/SUB: second operand; LUT: int8[256] table; PRELU: alpha[c]; else NULL */
+    void *output;             /* may alias input0 or input1 (the planner runs these ops in place)              */
+    int32_t op;               /* espdl_eltwise_op_t                                                            */
+    int32_t in_dtype;         /* dtype of input0 (and input1 for ADD/MUL/SUB)                                  */
+    int32_t out_dtype;
+    int32_t ndim;             /* 1..4; shapes are right-aligned, every input extent is 1 or the output extent  */
+    int32_t out_shape[4];
+    int32_t in0_shape[4];
+    int32_t in1_shape[4];
+    int32_t in0_exponent, in1_exponent, out_exponent;
+    int32_t clip_lo, clip_hi; /* CLIP: bounds in the input's quantised scale                                   */
+    int32_t round_mode;
+    int32_t reserved;
+} espdl_eltwise_desc;
+
+int espdl_b200_eltwise(const espdl_eltwise_desc *desc, void *stream);
+
+/* ---------------------------------------------------------------- pooling */
+typedef enum { ESPDL_POOL_MAX = 0, ESPDL_POOL_AVG = 1, ESPDL_POOL_GLOBAL_AVG = 2 } espdl_pool_op_t;
+
+/* Replaces dl::base::max_pool2d<> / avg_pool2d<> (esp-dl/dl/base/dl_base_max_pool2d.cpp:9-27,
+ * esp-dl/dl/base/dl_base_avg_pool2d.cpp:10-55).  Max ignores padded taps; average is
+ * sat(round(sum * ((2^e_in * (1/area)) * 2^-e_out))) in fp32, area = kh*kw. */
+typedef struct espdl_pool_desc {
+    const void *input;
+    void *output;
+    int32_t op;
+    int32_t dtype;
+    int32_t n, in_h, in_w, c;
+    int32_t out_h, out_w;
+    int32_t kh, kw;
+    int32_t stride_h, stride_w;
+    int32_t pad_top, pad_bottom, pad_left, pad_right;
+    int32_t in_exponent, out_exponent;
+} espdl_pool_desc;
+
+int espdl_b200_pool(const espdl_pool_desc *desc, void *stream);
+
+/* ----------------------------------------------------------------- resize */
+/* Nearest-neighbour resize (asymmetric / floor), dl::base::resize<>
+ * (esp-dl/dl/base/dl_base_resize.cpp:7-35,239-279). */
+typedef struct espdl_resize_desc {
+    const void *input;
+    void *output;
+    int32_t dtype;
+    int32_t n, in_h, in_w, c;
+    int32_t out_h, out_w;
+    float scale_h, scale_w;
+    int32_t in_exponent, out_exponent;
+    int32_t out_pixel_stride; /* 0 = c */
+    int32_t reserved;
+} espdl_resize_desc;
+
+int espdl_b200_resize(const espdl_resize_desc *desc, void *stream);
+
+/* ------------------------------------------------------------------- copy */
+/* Strided gather/scatter copy used for Concat / Split / Transpose / Slice
+ * (esp-dl/dl/module/include/dl_module_concat.hpp:38-107 and friends):
+ * dst[sum i_k*dst_stride[k]] = src[sum i_k*src_stride[k]] for i in shape. */
+typedef struct espdl_copy_desc {
+    const void *src;
+    void *dst;
+    int32_t elem_size; /* bytes: 1, 2, 4 or 8 */
+    int32_t ndim;      /* 1..6 */
+    int32_t shape[6];
+    int64_t src_stride[6]; /* in elements */
+    int64_t dst_stride[6];
+} espdl_copy_desc;
+
+int espdl_b200_copy(const espdl_copy_desc *desc, void *stream);
+
+/* ---------------------------------------------------------------- softmax */
+/* int8 Softmax along the last axis with the reference's 256-entry exp table
+ * (esp-dl/dl/module/include/dl_module_softmax.hpp:148-187): the row sum is a
+ * sequential fp32 sum.  out_dtype FLOAT writes y; INT8/INT16 additionally apply
+ * the following QuantizeLinear, sat(round(y * 2^-out_exponent)). */
+typedef struct espdl_softmax_desc {
+    const int8_t *input;
+    void *output;
+    const float *exp_table; /* device float[256], entry k = expf(2^in_exponent * (k - 128)) */
+    int32_t rows, len;
+    int32_t out_dtype;
+    int32_t out_exponent;
+} espdl_softmax_desc;
+
+int espdl_b200_softmax(const espdl_softmax_desc *desc, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ESPDL_B200_H */

@@ -1,0 +1,477 @@
+/*
+ * espdl_oracle.c - TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * A plain-C, single-threaded restatement of the arithmetic of ESP-DL's
+ * generic ("ANSI C") quantized operators, written as straightforward loops
+ * over the same descriptor structs the CUDA backend's C ABI takes (with HOST
+ * pointers here).  It exists only so that tests, the smoke check and the
+ * benchmark's cpu_baseline leg can compare the CUDA kernels against an
+ * independent implementation; the shipped library never links or calls it.
+ *
+ * Pinning: every function here is cross-checked (tests/test_oracle_vs_reference.py)
+ * against the reference's own C++ operators compiled unmodified from its
+ * source tree (oracle/ref_harness.cpp -> oracle/_ref/libespdl_ref.so) and
+ * against the reference's shipped golden Gemm / MLP vectors (tests/golden/).
+ * The only semantics with no compiled reference counterpart are the
+ * per-channel filter exponents (the reference's C epilogue has no working
+ * per-channel branch; the rule restated here is the ESP32-P4 assembly one,
+ * see oracle_requant below) and the batch extent n > 1 (the reference reads
+ * one image; here image i is an independent repetition of the same op).
+ *
+ * Each function cites the reference file:line (paths relative to the
+ * reference project root) whose behaviour it restates.
+ */
+#include "../include/espdl_b200.h"
+
+#include <limits.h>
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#if defined(_OPENMP)
+#include <omp.h>
+#endif
+
+/* ------------------------------------------------------------ primitives */
+
+/* dl::tool::truncate  esp-dl/dl/tool/include/dl_tool.hpp:225-254 */
+static inline int64_t clamp64(int64_t v, int64_t lo, int64_t hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+/* dl::tool::round(float): (int)floorf(value + 0.5) with a double literal, i.e. the
+ * sum is formed in double, narrowed to float, then floored.
+ * esp-dl/dl/tool/src/dl_tool.cpp:72-90.  Half-even variant: :33-70. */
+static inline int fround_half_up(float v) { return (int)floorf((float)((double)v + 0.5)); }
+
+/* Half-even: what ESP32-P4 does (fcvt.w.s with rne, esp-dl/dl/tool/src/dl_tool.cpp:24-31). */
+static inline int fround_half_even(float v) { return (int)rintf(v); }
+
+static inline int fround(float v, int mode) { return mode == ESPDL_ROUND_HALF_EVEN ? fround_half_even(v) : fround_half_up(v); }
+
+/* dl::tool::shift_and_round  esp-dl/dl/tool/src/dl_tool.cpp:95-146.
+ * shift > 0: arithmetic right shift with half-up or half-even rounding;
+ * shift <= 0: left shift in 64 bits, then saturate to the accumulator type
+ * (acc_bits = 32 for int8 ops, 64 for int16 ops). */
+static inline int64_t shift_and_round(int64_t v, int shift, int mode, int acc_bits)
+{
+    if (shift <= 0) {
+        int64_t s = (int64_t)((uint64_t)v << (-shift));
+        if (acc_bits == 32)
+            s = clamp64(s, INT32_MIN, INT32_MAX);
+        return s;
+    }
+    if (mode == ESPDL_ROUND_HALF_EVEN) {
+        int64_t q = v >> shift;
+        int64_t rem = v & (((int64_t)1 << shift) - 1);
+        int64_t half = (int64_t)1 << (shift - 1);
+        if (rem > half || (rem == half && (q & 1)))
+            q += 1;
+        return q;
+    }
+    return (v + ((int64_t)1 << (shift - 1))) >> shift;
+}
+
+/* DL_SCALE / DL_RESCALE  esp-dl/dl/dl_define.hpp:84-90 (float power of two) */
+static inline float dl_scale(int e) { return e > 0 ? (float)(1 << e) : (float)1.0 / (float)(1 << -e); }
+static inline float dl_rescale(int e) { return e > 0 ? (float)1.0 / (float)(1 << e) : (float)(1 << -e); }
+
+/*
+ * Conv / depthwise epilogue.
+ * per-tensor: esp-dl/dl/base/dl_base_activate_buffer.hpp:27-37,60-73
+ *   acc += bias; acc = shift_and_round(acc, mac_shift); relu; truncate.
+ * per-channel (no working C branch in the reference; this is the ESP32-P4 rule:
+ *   bias pre-loaded into the accumulator esp-dl/dl/base/isa/esp32p4/dl_esp32p4_s8.S:6-11,
+ *   shift[c] = e_out - e_w[c] - e_in esp-dl/dl/base/dl_base.hpp:249-252,
+ *   shift/round/saturate :57-65, then ReLU dl_esp32p4_s8_conv2d.S:1261-1266).
+ * Saturate-then-ReLU equals ReLU-then-saturate, so one code path serves both.
+ */
+static inline int64_t oracle_requant(int64_t acc, int64_t bias, int shift, int act, int mode, int is16)
+{
+    if (!is16)
+        acc = (int32_t)((uint32_t)(int32_t)acc + (uint32_t)(int32_t)bias); /* 32-bit accumulator wraps */
+    else
+        acc += bias;
+    int64_t v = shift_and_round(acc, shift, mode, is16 ? 64 : 32);
+    if (act == ESPDL_ACT_RELU && v < 0)
+        v = 0;
+    return is16 ? clamp64(v, INT16_MIN, INT16_MAX) : clamp64(v, INT8_MIN, INT8_MAX);
+}
+
+static int conv_check(const espdl_conv_desc *d)
+{
+    if (!d || !d->input || !d->filter || !d->output)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->dtype != ESPDL_DTYPE_INT8 && d->dtype != ESPDL_DTYPE_INT16)
+        return ESPDL_ERR_UNSUPPORTED;
+    if (d->n < 0 || d->in_h <= 0 || d->in_w <= 0 || d->in_c <= 0 || d->out_c <= 0 || d->kh <= 0 || d->kw <= 0)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->group != 1 && !(d->group == d->in_c && d->out_c == d->in_c))
+        return ESPDL_ERR_UNSUPPORTED;
+    if (d->per_channel && !d->filter_exponents)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->activation != ESPDL_ACT_LINEAR && d->activation != ESPDL_ACT_RELU)
+        return ESPDL_ERR_UNSUPPORTED;
+    return ESPDL_OK;
+}
+
+/*
+ * Conv2D / Gemm / depthwise.
+ * MAC loops: esp-dl/dl/base/dl_base_conv2d.cpp:141-162 (conv2d_hwcn, filter [N][H][W][C]),
+ *            esp-dl/dl/base/dl_base_depthwise_conv2d.cpp:47-66 (filter [H][W][C]);
+ * border handling (skip taps outside the image): esp-dl/dl/base/dl_base.hpp:951-1022;
+ * output extents: esp-dl/dl/module/include/dl_module_conv.hpp:81-102.
+ */
+int oracle_conv2d(const espdl_conv_desc *d)
+{
+    int st = conv_check(d);
+    if (st)
+        return st;
+    const int is16 = d->dtype == ESPDL_DTYPE_INT16;
+    const int ips = d->in_pixel_stride ? d->in_pixel_stride : d->in_c;
+    const int ops = d->out_pixel_stride ? d->out_pixel_stride : d->out_c;
+    const int dw = d->group != 1;
+    const int8_t *in8 = (const int8_t *)d->input;
+    const int16_t *in16 = (const int16_t *)d->input;
+    const int8_t *w8 = (const int8_t *)d->filter;
+    const int16_t *w16 = (const int16_t *)d->filter;
+    const int32_t *b32 = (const int32_t *)d->bias;
+    const int64_t *b64 = (const int64_t *)d->bias;
+    int8_t *o8 = (int8_t *)d->output;
+    int16_t *o16 = (int16_t *)d->output;
+    const int64_t total_rows = (int64_t)d->n * d->out_h;
+
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static)
+#endif
+    for (int64_t row = 0; row < total_rows; row++) {
+        const int n = (int)(row / d->out_h), oy = (int)(row % d->out_h);
+        for (int ox = 0; ox < d->out_w; ox++) {
+            for (int oc = 0; oc < d->out_c; oc++) {
+                int64_t acc = 0;
+                for (int ky = 0; ky < d->kh; ky++) {
+                    const int iy = oy * d->stride_h + ky * d->dilation_h - d->pad_top;
+                    if (iy < 0 || iy >= d->in_h)
+                        continue;
+                    for (int kx = 0; kx < d->kw; kx++) {
+                        const int ix = ox * d->stride_w + kx * d->dilation_w - d->pad_left;
+                        if (ix < 0 || ix >= d->in_w)
+                            continue;
+                        const int64_t ibase = (((int64_t)n * d->in_h + iy) * d->in_w + ix) * ips;
+                        if (dw) {
+                            const int64_t wi = ((int64_t)ky * d->kw + kx) * d->in_c + oc;
+                            acc += is16 ? (int64_t)in16[ibase + oc] * w16[wi] : (int64_t)in8[ibase + oc] * w8[wi];
+                        } else {
+                            const int64_t wbase = (((int64_t)oc * d->kh + ky) * d->kw + kx) * d->in_c;
+                            if (is16) {
+                                for (int c = 0; c < d->in_c; c++) acc += (int64_t)in16[ibase + c] * w16[wbase + c];
+                            } else {
+                                int32_t a = 0;
+                                for (int c = 0; c < d->in_c; c++) a += (int32_t)in8[ibase + c] * w8[wbase + c];
+                                acc += a;
+                            }
+                        }
+                    }
+                }
+                if (!is16)
+                    acc = (int32_t)acc;
+                const int ew = d->per_channel ? d->filter_exponents[oc] : d->filter_exponent;
+                const int shift = d->out_exponent - ew - d->in_exponent;
+                const int64_t bias = d->bias ? (is16 ? b64[oc] : (int64_t)b32[oc]) : 0;
+                int64_t q = oracle_requant(acc, bias, shift, d->activation, d->round_mode, is16);
+                const int64_t oi = (((int64_t)n * d->out_h + oy) * d->out_w + ox) * ops + oc;
+                if (is16) {
+                    o16[oi] = (int16_t)q;
+                } else {
+                    /* fused dl::module::LUT node: esp-dl/dl/base/dl_base_lut.cpp:10-15 */
+                    o8[oi] = d->lut ? d->lut[(uint8_t)(int8_t)q ^ 0x80u] : (int8_t)q;
+                }
+            }
+        }
+    }
+    return ESPDL_OK;
+}
+
+/* --------------------------------------------------------- elementwise */
+
+static inline int64_t load_int(const void *p, int dtype, int64_t i)
+{
+    return dtype == ESPDL_DTYPE_INT8 ? ((const int8_t *)p)[i] : ((const int16_t *)p)[i];
+}
+
+static inline void store_sat(void *p, int dtype, int64_t i, int64_t v)
+{
+    if (dtype == ESPDL_DTYPE_INT8)
+        ((int8_t *)p)[i] = (int8_t)clamp64(v, INT8_MIN, INT8_MAX);
+    else
+        ((int16_t *)p)[i] = (int16_t)clamp64(v, INT16_MIN, INT16_MAX);
+}
+
+/* quantize<RT>(float, inv_scale): esp-dl/dl/tensor/src/dl_tensor_base.cpp:18-30 */
+static inline int64_t quantize_f(float x, float inv_scale, int mode) { return fround(x * inv_scale, mode); }
+
+int oracle_eltwise(const espdl_eltwise_desc *d)
+{
+    if (!d || !d->input0 || !d->output || d->ndim < 1 || d->ndim > 4)
+        return ESPDL_ERR_INVALID_ARG;
+    int os[4] = {1, 1, 1, 1}, s0[4] = {1, 1, 1, 1}, s1[4] = {1, 1, 1, 1};
+    for (int i = 0; i < d->ndim; i++) {
+        os[4 - d->ndim + i] = d->out_shape[i];
+        s0[4 - d->ndim + i] = d->in0_shape[i];
+        s1[4 - d->ndim + i] = d->in1_shape[i];
+    }
+    const int binary = d->op == ESPDL_ELT_ADD || d->op == ESPDL_ELT_MUL || d->op == ESPDL_ELT_SUB;
+    if ((binary || d->op == ESPDL_ELT_LUT || d->op == ESPDL_ELT_PRELU) && !d->input1)
+        return ESPDL_ERR_INVALID_ARG;
+    int64_t st0[4], st1[4];
+    {
+        int64_t a = 1, b = 1;
+        for (int i = 3; i >= 0; i--) {
+            if (s0[i] != os[i] && s0[i] != 1)
+                return ESPDL_ERR_INVALID_ARG;
+            if (binary && s1[i] != os[i] && s1[i] != 1)
+                return ESPDL_ERR_INVALID_ARG;
+            st0[i] = s0[i] == 1 ? 0 : a;
+            st1[i] = s1[i] == 1 ? 0 : b;
+            a *= s0[i];
+            b *= s1[i];
+        }
+    }
+    const int mode = d->round_mode;
+    const int idt = d->in_dtype, odt = d->out_dtype;
+    /* Mul: esp-dl/dl/base/dl_base_mul.cpp:128 - scale = (2^e0 * 2^e1) * 2^-eo, in that float order */
+    const float mul_scale = dl_scale(d->in0_exponent) * dl_scale(d->in1_exponent) * dl_rescale(d->out_exponent);
+    /* Clip: esp-dl/dl/module/include/dl_module_clip.hpp:85 */
+    const float clip_rescale = dl_scale(d->in0_exponent) * dl_rescale(d->out_exponent);
+    const int C = os[3];
+    int64_t oi = 0;
+    for (int i3 = 0; i3 < os[0]; i3++)
+        for (int i2 = 0; i2 < os[1]; i2++)
+            for (int i1 = 0; i1 < os[2]; i1++)
+                for (int i0 = 0; i0 < os[3]; i0++, oi++) {
+                    const int64_t a_i = i3 * st0[0] + i2 * st0[1] + i1 * st0[2] + i0 * st0[3];
+                    const int64_t b_i = i3 * st1[0] + i2 * st1[1] + i1 * st1[2] + i0 * st1[3];
+                    switch (d->op) {
+                    case ESPDL_ELT_ADD: /* esp-dl/dl/base/dl_base_add.cpp:8-44: exponents already equal */
+                        store_sat(d->output, odt, oi, load_int(d->input0, idt, a_i) + load_int(d->input1, idt, b_i));
+                        break;
+                    case ESPDL_ELT_SUB: /* esp-dl/dl/base/dl_base_sub.cpp, same shape as add */
+                        store_sat(d->output, odt, oi, load_int(d->input0, idt, a_i) - load_int(d->input1, idt, b_i));
+                        break;
+                    case ESPDL_ELT_MUL: { /* esp-dl/dl/base/dl_base_mul.cpp:9-46 */
+                        int32_t t = (int32_t)(load_int(d->input0, idt, a_i) * load_int(d->input1, idt, b_i));
+                        float out = (float)t * mul_scale;
+                        store_sat(d->output, odt, oi, fround(out, mode));
+                        break;
+                    }
+                    case ESPDL_ELT_REQUANTIZE: { /* esp-dl/dl/tensor/src/dl_tensor_base.cpp:223-404 */
+                        if (idt == ESPDL_DTYPE_FLOAT) { /* :251-264 QuantizeLinear */
+                            float x = ((const float *)d->input0)[a_i];
+                            store_sat(d->output, odt, oi, quantize_f(x, dl_rescale(d->out_exponent), mode));
+                        } else if (odt == ESPDL_DTYPE_FLOAT) { /* :283-298 DequantizeLinear */
+                            ((float *)d->output)[oi] = (float)load_int(d->input0, idt, a_i) * dl_scale(d->in0_exponent);
+                        } else if (d->in0_exponent == d->out_exponent) { /* :311-328 */
+                            store_sat(d->output, odt, oi, load_int(d->input0, idt, a_i));
+                        } else { /* :362-395 quantize(dequantize()) */
+                            float src_scale = dl_scale(d->in0_exponent);
+                            float inv_scale = (float)(1.0 / (double)dl_scale(d->out_exponent));
+                            float tmp = (float)load_int(d->input0, idt, a_i) * src_scale;
+                            store_sat(d->output, odt, oi, quantize_f(tmp, inv_scale, mode));
+                        }
+                        break;
+                    }
+                    case ESPDL_ELT_LUT: /* esp-dl/dl/base/dl_base_lut.cpp:10-15 */
+                        ((int8_t *)d->output)[oi] =
+                            ((const int8_t *)d->input1)[(uint8_t)((const int8_t *)d->input0)[a_i] ^ 0x80u];
+                        break;
+                    case ESPDL_ELT_CLIP: { /* esp-dl/dl/module/include/dl_module_clip.hpp:78-90 */
+                        int64_t v = clamp64(load_int(d->input0, idt, a_i), d->clip_lo, d->clip_hi);
+                        store_sat(d->output, odt, oi, fround((float)v * clip_rescale, mode));
+                        break;
+                    }
+                    case ESPDL_ELT_RELU: { /* esp-dl/dl/module/include/dl_module_relu.hpp:66-91 */
+                        int64_t v = load_int(d->input0, idt, a_i);
+                        if (d->in0_exponent == d->out_exponent) {
+                            store_sat(d->output, odt, oi, v >= 0 ? v : 0);
+                        } else {
+                            float temp = (float)v * dl_scale(d->in0_exponent);
+                            if (temp >= 0)
+                                store_sat(d->output, odt, oi, fround(temp * dl_rescale(d->out_exponent), mode));
+                            else
+                                store_sat(d->output, odt, oi, 0);
+                        }
+                        break;
+                    }
+                    case ESPDL_ELT_PRELU: { /* esp-dl/dl/base/dl_base_prelu.cpp:5-19, shift esp-dl/dl/base/dl_base.hpp:2165-2168 */
+                        int64_t v = load_int(d->input0, idt, a_i);
+                        if (v < 0) {
+                            int shift = d->out_exponent - d->in0_exponent - d->in1_exponent;
+                            int64_t prod = v * load_int(d->input1, idt, i0 % C);
+                            if (idt == ESPDL_DTYPE_INT8)
+                                prod = (int32_t)prod;
+                            /* DL_RIGHT_SHIFT: plain arithmetic shift, no rounding */
+                            v = shift > 0 ? (prod >> shift) : (int64_t)((uint64_t)prod << (-shift));
+                            if (idt == ESPDL_DTYPE_INT8)
+                                v = (int32_t)v;
+                        }
+                        store_sat(d->output, odt, oi, v);
+                        break;
+                    }
+                    default:
+                        return ESPDL_ERR_UNSUPPORTED;
+                    }
+                }
+    return ESPDL_OK;
+}
+
+/* ------------------------------------------------------------- pooling */
+/* Max: esp-dl/dl/base/dl_base_max_pool2d.cpp:9-27 over in-bounds taps only (shell
+ * esp-dl/dl/base/dl_base_pool2d.hpp shrinks the window at borders).
+ * Avg / global avg: esp-dl/dl/base/dl_base_avg_pool2d.cpp:10-55: integer sum of the in-bounds
+ * taps, then sat(round((float)sum * scale)), scale = (2^e_in * (1.f/area)) * 2^-e_out with
+ * area = kh*kw of the full window (esp-dl/dl/base/dl_base_pool2d.hpp:132). */
+int oracle_pool(const espdl_pool_desc *d)
+{
+    if (!d || !d->input || !d->output)
+        return ESPDL_ERR_INVALID_ARG;
+    const int is16 = d->dtype == ESPDL_DTYPE_INT16;
+    int kh = d->kh, kw = d->kw, sh = d->stride_h, sw = d->stride_w, oh = d->out_h, ow = d->out_w;
+    int pt = d->pad_top, pl = d->pad_left;
+    if (d->op == ESPDL_POOL_GLOBAL_AVG) {
+        kh = d->in_h, kw = d->in_w, sh = sw = 1, oh = ow = 1, pt = pl = 0;
+    }
+    const float inv_area = 1.f / (float)(kh * kw);
+    const float scale = dl_scale(d->in_exponent) * inv_area * dl_rescale(d->out_exponent);
+    for (int n = 0; n < d->n; n++)
+        for (int oy = 0; oy < oh; oy++)
+            for (int ox = 0; ox < ow; ox++)
+                for (int c = 0; c < d->c; c++) {
+                    int64_t sum = 0, mx = INT64_MIN;
+                    for (int ky = 0; ky < kh; ky++) {
+                        int iy = oy * sh + ky - pt;
+                        if (iy < 0 || iy >= d->in_h)
+                            continue;
+                        for (int kx = 0; kx < kw; kx++) {
+                            int ix = ox * sw + kx - pl;
+                            if (ix < 0 || ix >= d->in_w)
+                                continue;
+                            int64_t v = load_int(d->input, d->dtype, (((int64_t)n * d->in_h + iy) * d->in_w + ix) * d->c + c);
+                            sum += v;
+                            if (v > mx)
+                                mx = v;
+                        }
+                    }
+                    int64_t oi = (((int64_t)n * oh + oy) * ow + ox) * d->c + c;
+                    if (d->op == ESPDL_POOL_MAX)
+                        store_sat(d->output, d->dtype, oi, mx);
+                    else
+                        store_sat(d->output, d->dtype, oi, fround_half_up((float)(is16 ? sum : (int32_t)sum) * scale));
+                }
+    return ESPDL_OK;
+}
+
+/* -------------------------------------------------------------- resize */
+/* esp-dl/dl/base/dl_base_resize.cpp:7-35 (value), :239-268 (coordinates),
+ * esp-dl/dl/base/dl_base_resize.hpp:80-85 (scale/shift).  The value is a plain cast
+ * of round(), without saturation. */
+int oracle_resize(const espdl_resize_desc *d)
+{
+    if (!d || !d->input || !d->output)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->dtype != ESPDL_DTYPE_INT8) /* resize<int16_t> is an empty function: esp-dl/dl/base/dl_base_resize.cpp:298-309 */
+        return ESPDL_ERR_UNSUPPORTED;
+    int shift = d->out_exponent - d->in_exponent, oscale = 1;
+    if (shift < 0) {
+        oscale = 1 << (-shift);
+        shift = 0;
+    }
+    const float sh_inv = 1 / d->scale_h, sw_inv = 1 / d->scale_w;
+    const int ops = d->out_pixel_stride ? d->out_pixel_stride : d->c;
+    const int two = d->scale_h == 2 && d->scale_w == 2;
+    for (int n = 0; n < d->n; n++)
+        for (int y = 0; y < d->out_h; y++) {
+            int iy = two ? y / 2 : (int)(y * sh_inv);
+            if (iy > d->in_h - 1)
+                iy = d->in_h - 1;
+            for (int x = 0; x < d->out_w; x++) {
+                int ix = two ? x / 2 : (int)(x * sw_inv);
+                if (ix > d->in_w - 1)
+                    ix = d->in_w - 1;
+                for (int c = 0; c < d->c; c++) {
+                    int64_t ii = (((int64_t)n * d->in_h + iy) * d->in_w + ix) * d->c + c;
+                    int64_t oi = (((int64_t)n * d->out_h + y) * d->out_w + x) * ops + c;
+                    int v = fround_half_up((float)load_int(d->input, d->dtype, ii) * (float)oscale / (float)(1 << shift));
+                    if (d->dtype == ESPDL_DTYPE_INT8)
+                        ((int8_t *)d->output)[oi] = (int8_t)v;
+                    else
+                        ((int16_t *)d->output)[oi] = (int16_t)v;
+                }
+            }
+        }
+    return ESPDL_OK;
+}
+
+/* ---------------------------------------------------------------- copy */
+int oracle_copy(const espdl_copy_desc *d)
+{
+    if (!d || !d->src || !d->dst || d->ndim < 1 || d->ndim > 6)
+        return ESPDL_ERR_INVALID_ARG;
+    int shp[6] = {1, 1, 1, 1, 1, 1};
+    int64_t ss[6] = {0}, ds[6] = {0};
+    for (int i = 0; i < d->ndim; i++) {
+        shp[6 - d->ndim + i] = d->shape[i];
+        ss[6 - d->ndim + i] = d->src_stride[i];
+        ds[6 - d->ndim + i] = d->dst_stride[i];
+    }
+    const int es = d->elem_size;
+    for (int a = 0; a < shp[0]; a++)
+        for (int b = 0; b < shp[1]; b++)
+            for (int c = 0; c < shp[2]; c++)
+                for (int e = 0; e < shp[3]; e++)
+                    for (int f = 0; f < shp[4]; f++)
+                        for (int g = 0; g < shp[5]; g++) {
+                            int64_t si = a * ss[0] + b * ss[1] + c * ss[2] + e * ss[3] + f * ss[4] + g * ss[5];
+                            int64_t di = a * ds[0] + b * ds[1] + c * ds[2] + e * ds[3] + f * ds[4] + g * ds[5];
+                            memcpy((char *)d->dst + di * es, (const char *)d->src + si * es, (size_t)es);
+                        }
+    return ESPDL_OK;
+}
+
+/* ------------------------------------------------------------- softmax */
+/* esp-dl/dl/module/include/dl_module_softmax.hpp:148-187: y_i = T[x_i+128] / sum_j T[x_j+128],
+ * sequential fp32 sum in index order; T from dl::tool::gen_lut_8bit
+ * (esp-dl/dl/tool/src/dl_tool.cpp:258-268).  A following QuantizeLinear
+ * (esp-dl/dl/tensor/src/dl_tensor_base.cpp:251-264) is folded in when out_dtype is an integer type. */
+void oracle_softmax_table(float *table, int in_exponent)
+{
+    float scale = dl_scale(in_exponent);
+    for (int i = 0; i < 256; i++) table[i] = expf(scale * (float)(i - 128));
+}
+
+int oracle_softmax(const espdl_softmax_desc *d)
+{
+    if (!d || !d->input || !d->output || !d->exp_table)
+        return ESPDL_ERR_INVALID_ARG;
+    const float inv_scale = dl_rescale(d->out_exponent);
+    for (int r = 0; r < d->rows; r++) {
+        const int8_t *x = d->input + (int64_t)r * d->len;
+        float sum = 0.f;
+        for (int i = 0; i < d->len; i++) sum += d->exp_table[x[i] + 128];
+        for (int i = 0; i < d->len; i++) {
+            float y = d->exp_table[x[i] + 128] / sum;
+            int64_t oi = (int64_t)r * d->len + i;
+            if (d->out_dtype == ESPDL_DTYPE_FLOAT)
+                ((float *)d->output)[oi] = y;
+            else
+                store_sat(d->output, d->out_dtype, oi, fround_half_up(y * inv_scale));
+        }
+    }
+    return ESPDL_OK;
+}
+
+int oracle_num_threads(void)
+{
+#if defined(_OPENMP)
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

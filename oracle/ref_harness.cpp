@@ -1,0 +1,257 @@
+/*
+ * ref_harness.cpp - TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+ *
+ * C entry points around the UNMODIFIED reference operators.  The reference's own
+ * sources are compiled where they lie in the reference checkout (see the
+ * Makefile beside this file) for the host CPU with no CONFIG_IDF_TARGET_*
+ * defined, i.e. its generic C kernels with round-half-up; this file only builds
+ * dl::TensorBase views over the caller's host buffers, instantiates the
+ * reference's dl::module::* classes through their public constructors and calls
+ * Module::run().  Descriptors are the same structs the CUDA backend's C ABI
+ * takes, with HOST pointers.
+ *
+ * What the reference cannot do and this harness therefore rejects:
+ *  - per-channel filter exponents (no working branch in the generic C epilogue);
+ *  - HALF_EVEN rounding (a compile-time switch tied to the ESP32-P4 target);
+ *  - a fused LUT in the conv epilogue, pixel strides other than dense.
+ * A batch extent n > 1 is executed as n independent single-image calls, which
+ * is how a caller of the reference has to run a batch (its conv / pool / resize
+ * kernels read one image).
+ */
+#include "../include/espdl_b200.h"
+
+#include "dl_module_add.hpp"
+#include "dl_module_average_pool.hpp"
+#include "dl_module_clip.hpp"
+#include "dl_module_concat.hpp"
+#include "dl_module_conv.hpp"
+#include "dl_module_gemm.hpp"
+#include "dl_module_global_average_pool.hpp"
+#include "dl_module_lut.hpp"
+#include "dl_module_max_pool.hpp"
+#include "dl_module_mul.hpp"
+#include "dl_module_prelu.hpp"
+#include "dl_module_relu.hpp"
+#include "dl_module_requantize_linear.hpp"
+#include "dl_module_resize.hpp"
+#include "dl_module_softmax.hpp"
+#include "dl_module_sub.hpp"
+
+#include <memory>
+#include <vector>
+
+#if defined(_OPENMP)
+#include <omp.h>
+#endif
+
+using namespace dl;
+
+static dtype_t to_dtype(int d) { return (dtype_t)d; }
+static quant_type_t to_quant(int d)
+{
+    return d == ESPDL_DTYPE_INT8 ? QUANT_TYPE_SYMM_8BIT : d == ESPDL_DTYPE_INT16 ? QUANT_TYPE_SYMM_16BIT : QUANT_TYPE_FLOAT32;
+}
+static size_t esize(int d) { return d == ESPDL_DTYPE_INT8 ? 1 : d == ESPDL_DTYPE_INT16 ? 2 : d == ESPDL_DTYPE_INT64 ? 8 : 4; }
+
+static TensorBase *view(std::vector<int> shape, const void *p, int exponent, int dtype)
+{
+    return new TensorBase(shape, p, exponent, to_dtype(dtype), false);
+}
+
+extern "C" {
+
+int ref_num_threads(void)
+{
+#if defined(_OPENMP)
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* dl::module::Conv (group 1 or depthwise).  gemm != 0 routes through dl::module::Gemm with
+ * input [in_w, in_c] instead (requires n = in_h = kh = kw = 1). */
+int ref_conv2d(const espdl_conv_desc *d, int gemm)
+{
+    if (!d || d->per_channel || d->lut || d->round_mode != ESPDL_ROUND_HALF_UP)
+        return ESPDL_ERR_UNSUPPORTED;
+    if ((d->in_pixel_stride && d->in_pixel_stride != d->in_c) || (d->out_pixel_stride && d->out_pixel_stride != d->out_c))
+        return ESPDL_ERR_UNSUPPORTED;
+    const size_t es = esize(d->dtype);
+    const quant_type_t qt = to_quant(d->dtype);
+    const int bias_dtype = d->dtype == ESPDL_DTYPE_INT8 ? ESPDL_DTYPE_INT32 : ESPDL_DTYPE_INT64;
+    const int dw = d->group != 1;
+    std::vector<int> fshape = dw ? std::vector<int>{d->kh, d->kw, d->in_c, 1} : std::vector<int>{d->kh, d->kw, d->in_c, d->out_c};
+    const size_t in_img = (size_t)d->in_h * d->in_w * d->in_c * es, out_img = (size_t)d->out_h * d->out_w * d->out_c * es;
+    int status = ESPDL_OK;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static)
+#endif
+    for (int n = 0; n < d->n; n++) {
+        std::unique_ptr<TensorBase> filter(view(fshape, d->filter, d->filter_exponent, d->dtype));
+        std::unique_ptr<TensorBase> bias(d->bias ? view({d->out_c}, d->bias, d->in_exponent + d->filter_exponent, bias_dtype) : nullptr);
+        const char *ip = (const char *)d->input + (size_t)n * in_img;
+        char *op = (char *)d->output + (size_t)n * out_img;
+        if (gemm) {
+            std::unique_ptr<TensorBase> in(view({d->in_w, d->in_c}, ip, d->in_exponent, d->dtype));
+            std::unique_ptr<TensorBase> out(view({d->out_w, d->out_c}, op, d->out_exponent, d->dtype));
+            module::Gemm m((activation_type_t)d->activation, nullptr, qt);
+            std::vector<TensorBase *> ins = {in.get(), filter.get()};
+            if (bias)
+                ins.push_back(bias.get());
+            m.run(ins, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
+        } else {
+            std::unique_ptr<TensorBase> in(view({1, d->in_h, d->in_w, d->in_c}, ip, d->in_exponent, d->dtype));
+            std::unique_ptr<TensorBase> out(view({1, d->out_h, d->out_w, d->out_c}, op, d->out_exponent, d->dtype));
+            module::Conv m((activation_type_t)d->activation,
+                           {d->pad_top, d->pad_bottom, d->pad_left, d->pad_right},
+                           {d->dilation_h, d->dilation_w},
+                           {d->stride_h, d->stride_w},
+                           nullptr,
+                           d->group,
+                           qt);
+            std::vector<TensorBase *> ins = {in.get(), filter.get()};
+            if (bias)
+                ins.push_back(bias.get());
+            m.run(ins, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
+        }
+    }
+    return status;
+}
+
+int ref_eltwise(const espdl_eltwise_desc *d)
+{
+    if (!d || d->round_mode != ESPDL_ROUND_HALF_UP)
+        return ESPDL_ERR_UNSUPPORTED;
+    std::vector<int> os(d->out_shape, d->out_shape + d->ndim), s0(d->in0_shape, d->in0_shape + d->ndim),
+        s1(d->in1_shape, d->in1_shape + d->ndim);
+    const quant_type_t qt = to_quant(d->in_dtype == ESPDL_DTYPE_FLOAT ? d->out_dtype : d->in_dtype);
+    std::unique_ptr<TensorBase> in0(view(s0, d->input0, d->in0_exponent, d->in_dtype));
+    std::unique_ptr<TensorBase> out(view(os, d->output, d->out_exponent, d->out_dtype));
+    switch (d->op) {
+    case ESPDL_ELT_ADD:
+    case ESPDL_ELT_SUB:
+    case ESPDL_ELT_MUL: {
+        std::unique_ptr<TensorBase> in1(view(s1, d->input1, d->in1_exponent, d->in_dtype));
+        std::unique_ptr<module::Module> m;
+        if (d->op == ESPDL_ELT_ADD)
+            m.reset(new module::Add(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_SUB)
+            m.reset(new module::Sub(nullptr, MODULE_NON_INPLACE, qt));
+        else
+            m.reset(new module::Mul(nullptr, MODULE_NON_INPLACE, qt));
+        m->run({in0.get(), in1.get()}, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
+        return ESPDL_OK;
+    }
+    case ESPDL_ELT_REQUANTIZE: {
+        module::RequantizeLinear m(nullptr, MODULE_NON_INPLACE, qt);
+        m.run(in0.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        return ESPDL_OK;
+    }
+    case ESPDL_ELT_LUT: {
+        TensorBase *table = new TensorBase({256}, d->input1, d->out_exponent, DATA_TYPE_INT8, true); /* owned by LUT */
+        module::LUT m(nullptr, table, MODULE_NON_INPLACE, qt);
+        m.run(in0.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        return ESPDL_OK;
+    }
+    case ESPDL_ELT_CLIP: {
+        /* min / max arrive as one-element tensors in the input's quantised scale */
+        int16_t lo16 = (int16_t)d->clip_lo, hi16 = (int16_t)d->clip_hi;
+        int8_t lo8 = (int8_t)d->clip_lo, hi8 = (int8_t)d->clip_hi;
+        const void *lo = d->in_dtype == ESPDL_DTYPE_INT8 ? (const void *)&lo8 : (const void *)&lo16;
+        const void *hi = d->in_dtype == ESPDL_DTYPE_INT8 ? (const void *)&hi8 : (const void *)&hi16;
+        std::unique_ptr<TensorBase> tmin(new TensorBase({1}, lo, d->in0_exponent, to_dtype(d->in_dtype), true));
+        std::unique_ptr<TensorBase> tmax(new TensorBase({1}, hi, d->in0_exponent, to_dtype(d->in_dtype), true));
+        module::Clip m(nullptr, MODULE_NON_INPLACE, qt);
+        m.run({in0.get(), tmin.get(), tmax.get()}, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
+        return ESPDL_OK;
+    }
+    case ESPDL_ELT_RELU: {
+        module::Relu m(nullptr, MODULE_NON_INPLACE, qt);
+        m.run(in0.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        return ESPDL_OK;
+    }
+    case ESPDL_ELT_PRELU: {
+        if (d->ndim != 4)
+            return ESPDL_ERR_UNSUPPORTED;
+        int c = d->out_shape[3];
+        TensorBase *alpha = new TensorBase({c, 1, 1}, d->input1, d->in1_exponent, to_dtype(d->in_dtype), true); /* owned by PRelu */
+        module::PRelu m(nullptr, alpha, MODULE_NON_INPLACE, qt);
+        m.run(in0.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        return ESPDL_OK;
+    }
+    default:
+        return ESPDL_ERR_UNSUPPORTED;
+    }
+}
+
+int ref_pool(const espdl_pool_desc *d)
+{
+    if (!d)
+        return ESPDL_ERR_INVALID_ARG;
+    const size_t es = esize(d->dtype);
+    const quant_type_t qt = to_quant(d->dtype);
+    const int oh = d->op == ESPDL_POOL_GLOBAL_AVG ? 1 : d->out_h, ow = d->op == ESPDL_POOL_GLOBAL_AVG ? 1 : d->out_w;
+    for (int n = 0; n < d->n; n++) {
+        const char *ip = (const char *)d->input + (size_t)n * d->in_h * d->in_w * d->c * es;
+        char *op = (char *)d->output + (size_t)n * oh * ow * d->c * es;
+        std::unique_ptr<TensorBase> in(view({1, d->in_h, d->in_w, d->c}, ip, d->in_exponent, d->dtype));
+        std::unique_ptr<TensorBase> out(view({1, oh, ow, d->c}, op, d->out_exponent, d->dtype));
+        std::vector<int> pads = {d->pad_top, d->pad_bottom, d->pad_left, d->pad_right};
+        if (d->op == ESPDL_POOL_MAX) {
+            module::MaxPool m(nullptr, {d->kh, d->kw}, pads, {d->stride_h, d->stride_w}, qt);
+            m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        } else if (d->op == ESPDL_POOL_AVG) {
+            module::AveragePool m(nullptr, {d->kh, d->kw}, pads, {d->stride_h, d->stride_w}, qt);
+            m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        } else {
+            module::GlobalAveragePool m(nullptr, qt);
+            m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        }
+    }
+    return ESPDL_OK;
+}
+
+int ref_resize(const espdl_resize_desc *d)
+{
+    if (!d || (d->out_pixel_stride && d->out_pixel_stride != d->c))
+        return ESPDL_ERR_UNSUPPORTED;
+    const size_t es = esize(d->dtype);
+    for (int n = 0; n < d->n; n++) {
+        const char *ip = (const char *)d->input + (size_t)n * d->in_h * d->in_w * d->c * es;
+        char *op = (char *)d->output + (size_t)n * d->out_h * d->out_w * d->c * es;
+        std::unique_ptr<TensorBase> in(view({1, d->in_h, d->in_w, d->c}, ip, d->in_exponent, d->dtype));
+        std::unique_ptr<TensorBase> out(view({1, d->out_h, d->out_w, d->c}, op, d->out_exponent, d->dtype));
+        module::Resize m(nullptr, RESIZE_NEAREST, {1.f, 1.f, d->scale_h, d->scale_w}, {}, false, to_quant(d->dtype));
+        m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+    }
+    return ESPDL_OK;
+}
+
+/* Softmax over the last axis of an int8 [rows, len] tensor into float32. */
+int ref_softmax(const espdl_softmax_desc *d, int in_exponent)
+{
+    if (!d || d->out_dtype != ESPDL_DTYPE_FLOAT)
+        return ESPDL_ERR_UNSUPPORTED;
+    std::unique_ptr<TensorBase> in(view({d->rows, d->len}, d->input, in_exponent, ESPDL_DTYPE_INT8));
+    std::unique_ptr<TensorBase> out(view({d->rows, d->len}, d->output, 0, ESPDL_DTYPE_FLOAT));
+    module::Softmax m(nullptr, -1, MODULE_NON_INPLACE, QUANT_TYPE_SYMM_8BIT);
+    m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+    return ESPDL_OK;
+}
+
+/* Concat of two int8 tensors along `axis` (checks the copy descriptors the backend derives). */
+int ref_concat2(const int8_t *a, const int8_t *b, int8_t *out, const int *shape_a, const int *shape_b, int ndim, int axis)
+{
+    std::vector<int> sa(shape_a, shape_a + ndim), sb(shape_b, shape_b + ndim), so(sa);
+    so[axis] += sb[axis];
+    std::unique_ptr<TensorBase> ta(view(sa, a, 0, ESPDL_DTYPE_INT8)), tb(view(sb, b, 0, ESPDL_DTYPE_INT8)),
+        to(view(so, out, 0, ESPDL_DTYPE_INT8));
+    module::Concat m(nullptr, axis, QUANT_TYPE_SYMM_8BIT);
+    std::vector<std::vector<int>> shapes = {sa, sb};
+    m.get_output_shape(shapes);
+    m.run({ta.get(), tb.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return ESPDL_OK;
+}
+
+} /* extern "C" */

@@ -1,0 +1,2 @@
+#pragma once
+#include "esp_err.h"

@@ -1,0 +1,33 @@
+"""Collects the golden-vector models the reference ships for the quantized operator path.
+
+Run in a container that has the reference checkout:  python tests/golden/make_golden.py [/path/to/reference]
+It copies the small `.espdl` test models that embed `test_inputs_value` / `test_outputs_value`
+(the data the reference's own `Model::test()` checks, test_apps/esp-dl/main/test_dl_model.cpp:14-52)
+into tests/golden/espdl/<target>__<name>.espdl, byte for byte.  They are data files, a few KB each.
+"""
+import os
+import shutil
+import sys
+
+REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+HERE = os.path.dirname(os.path.abspath(__file__))
+OUT = os.path.join(HERE, "espdl")
+
+SOURCES = []
+for target in ("c", "esp32p4", "esp32s3"):
+    d = os.path.join(REF, "test_apps/esp-dl/models", target, "Gemm")
+    for f in sorted(os.listdir(d)):
+        if f.endswith(".espdl"):
+            SOURCES.append((os.path.join(d, f), f"{target}__{f}"))
+for chip, target in (("p4", "esp32p4"), ("s3", "esp32s3")):
+    SOURCES.append((os.path.join(REF, "examples/tutorial/how_to_run_model/main/models", chip, "model.espdl"),
+                    f"{target}__sin_mlp.espdl"))
+for target in ("esp32p4", "esp32s3"):
+    SOURCES.append((os.path.join(REF, "examples/tutorial/how_to_deploy_streaming_model/test_streaming_model/main/models",
+                                 target, "model.espdl"), f"{target}__streaming_tcn.espdl"))
+
+if __name__ == "__main__":
+    os.makedirs(OUT, exist_ok=True)
+    for src, name in SOURCES:
+        shutil.copyfile(src, os.path.join(OUT, name))
+        print(f"{name}: {os.path.getsize(src)} bytes")
