@@ -1,0 +1,274 @@
+// C ABI: life cycle, memory and the conv2d dispatcher (include/espdl_b200.h).
+#include "common.cuh"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace espdl {
+
+static thread_local char g_last_error[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+static int g_device = -1;
+static int g_num_sms = 0;
+static std::mutex g_ws_mutex;
+static void *g_ws = nullptr; // cached scratch of espdl_b200_conv2d (int16 limb planes)
+static size_t g_ws_bytes = 0;
+
+int set_cuda_error(cudaError_t e, const char *what)
+{
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    return ESPDL_ERR_CUDA;
+}
+
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+int num_sms() { return g_num_sms > 0 ? g_num_sms : 148; }
+
+int check_launch(const char *what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess)
+        return set_cuda_error(e, what);
+    return ESPDL_OK;
+}
+
+} // namespace espdl
+
+using namespace espdl;
+
+extern "C" {
+
+int espdl_b200_init(int device)
+{
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        snprintf(g_last_error, sizeof(g_last_error), "no CUDA device: %s", cudaGetErrorString(e));
+        return ESPDL_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= count)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    ESPDL_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        snprintf(g_last_error, sizeof(g_last_error), "device %d is sm_%d%d; this library holds sm_100a code only", device,
+                 prop.major, prop.minor);
+        return ESPDL_ERR_NO_DEVICE;
+    }
+    g_device = device;
+    g_num_sms = prop.multiProcessorCount;
+    return ESPDL_OK;
+}
+
+void espdl_b200_shutdown(void)
+{
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    if (g_ws) {
+        cudaFree(g_ws);
+        g_ws = nullptr;
+        g_ws_bytes = 0;
+    }
+    g_device = -1;
+}
+
+const char *espdl_b200_strerror(int status)
+{
+    switch (status) {
+    case ESPDL_OK: return "ok";
+    case ESPDL_ERR_INVALID_ARG: return "invalid argument";
+    case ESPDL_ERR_UNSUPPORTED: return "unsupported combination";
+    case ESPDL_ERR_CUDA: return "CUDA call failed";
+    case ESPDL_ERR_NO_DEVICE: return "no usable sm_100 device";
+    case ESPDL_ERR_NO_MEM: return "out of device memory";
+    case ESPDL_ERR_TIMEOUT: return "device-side wait timed out";
+    case ESPDL_ERR_TOO_LARGE: return "size beyond the fixed maximum";
+    default: return "unknown status";
+    }
+}
+
+const char *espdl_b200_last_error(void) { return g_last_error; }
+
+int espdl_b200_arena_alloc(size_t bytes, void **dptr)
+{
+    if (!dptr)
+        return ESPDL_ERR_INVALID_ARG;
+    *dptr = nullptr;
+    cudaError_t e = cudaMalloc(dptr, bytes ? bytes : 16);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        return ESPDL_ERR_NO_MEM;
+    }
+    if (e != cudaSuccess)
+        return set_cuda_error(e, "cudaMalloc");
+    return ESPDL_OK;
+}
+
+int espdl_b200_arena_free(void *dptr)
+{
+    if (dptr)
+        ESPDL_CUDA_TRY(cudaFree(dptr));
+    return ESPDL_OK;
+}
+
+int espdl_b200_upload(void *dst_dev, const void *src_host, size_t bytes, void *stream)
+{
+    if ((!dst_dev || !src_host) && bytes)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
+int espdl_b200_download(void *dst_host, const void *src_dev, size_t bytes, void *stream)
+{
+    if ((!dst_host || !src_dev) && bytes)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
+int espdl_b200_memset(void *dst_dev, int value, size_t bytes, void *stream)
+{
+    ESPDL_CUDA_TRY(cudaMemsetAsync(dst_dev, value, bytes, (cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
+int espdl_b200_stream_sync(void *stream)
+{
+    ESPDL_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    // a tile kernel whose bounded wait expired leaves its status in a device word
+    const int dev = read_and_clear_device_error();
+    if (dev) {
+        snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
+        return dev;
+    }
+    return ESPDL_OK;
+}
+
+int espdl_b200_host_alloc(size_t bytes, void **hptr)
+{
+    if (!hptr)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaMallocHost(hptr, bytes ? bytes : 16));
+    return ESPDL_OK;
+}
+
+int espdl_b200_host_free(void *hptr)
+{
+    if (hptr)
+        ESPDL_CUDA_TRY(cudaFreeHost(hptr));
+    return ESPDL_OK;
+}
+
+uint64_t espdl_b200_launch_count(void) { return g_launches.load(); }
+
+// ------------------------------------------------------------------ conv2d
+static int conv_validate(const espdl_conv_desc *d)
+{
+    if (!d || !d->input || !d->filter || !d->output)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->dtype != ESPDL_DTYPE_INT8 && d->dtype != ESPDL_DTYPE_INT16)
+        return ESPDL_ERR_UNSUPPORTED;
+    if (d->n < 0 || d->in_h <= 0 || d->in_w <= 0 || d->in_c <= 0 || d->out_c <= 0 || d->out_h <= 0 || d->out_w <= 0)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->kh <= 0 || d->kw <= 0 || d->stride_h <= 0 || d->stride_w <= 0 || d->dilation_h <= 0 || d->dilation_w <= 0)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->pad_top < 0 || d->pad_bottom < 0 || d->pad_left < 0 || d->pad_right < 0)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->group != 1 && !(d->group == d->in_c && d->out_c == d->in_c))
+        return ESPDL_ERR_UNSUPPORTED;
+    if (d->per_channel && !d->filter_exponents)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->activation != ESPDL_ACT_LINEAR && d->activation != ESPDL_ACT_RELU)
+        return ESPDL_ERR_UNSUPPORTED;
+    if (d->round_mode != ESPDL_ROUND_HALF_UP && d->round_mode != ESPDL_ROUND_HALF_EVEN)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->lut && d->dtype != ESPDL_DTYPE_INT8)
+        return ESPDL_ERR_UNSUPPORTED;
+    if ((d->in_pixel_stride && d->in_pixel_stride < d->in_c) || (d->out_pixel_stride && d->out_pixel_stride < d->out_c))
+        return ESPDL_ERR_INVALID_ARG;
+    // output extents must be the ones the reference derives (dl_module_conv.hpp:81-102)
+    const int oh = (d->in_h + d->pad_top + d->pad_bottom - d->dilation_h * (d->kh - 1) - 1) / d->stride_h + 1;
+    const int ow = (d->in_w + d->pad_left + d->pad_right - d->dilation_w * (d->kw - 1) - 1) / d->stride_w + 1;
+    if (oh != d->out_h || ow != d->out_w)
+        return ESPDL_ERR_INVALID_ARG;
+    if (!d->per_channel) {
+        const int shift = d->out_exponent - d->filter_exponent - d->in_exponent;
+        const int lim = d->dtype == ESPDL_DTYPE_INT8 ? 31 : 62;
+        if (shift > lim || shift < -lim)
+            return ESPDL_ERR_INVALID_ARG;
+    }
+    return ESPDL_OK;
+}
+
+int espdl_b200_conv2d_workspace_bytes(const espdl_conv_desc *desc, size_t *bytes)
+{
+    if (!bytes)
+        return ESPDL_ERR_INVALID_ARG;
+    *bytes = 0;
+    int st = conv_validate(desc);
+    if (st)
+        return st;
+    if (desc->kernel != ESPDL_KERNEL_SIMT && desc->group == 1 && conv2d_tc_supported(*desc))
+        *bytes = conv2d_tc_workspace_bytes(*desc);
+    return ESPDL_OK;
+}
+
+int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t workspace_bytes, void *stream)
+{
+    int st = conv_validate(desc);
+    if (st)
+        return st;
+    if (g_device < 0)
+        return ESPDL_ERR_NO_DEVICE;
+    if (desc->n == 0)
+        return ESPDL_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (desc->group != 1) {
+        if (desc->kernel == ESPDL_KERNEL_TCGEN05)
+            return ESPDL_ERR_UNSUPPORTED;
+        return conv2d_depthwise(*desc, s);
+    }
+    const bool tc_ok = conv2d_tc_supported(*desc);
+    if (desc->kernel == ESPDL_KERNEL_TCGEN05 && !tc_ok)
+        return ESPDL_ERR_UNSUPPORTED;
+    if (tc_ok && desc->kernel != ESPDL_KERNEL_SIMT) {
+        const size_t need = conv2d_tc_workspace_bytes(*desc);
+        if (need > workspace_bytes || (need && !workspace))
+            return ESPDL_ERR_INVALID_ARG;
+        return conv2d_tc(*desc, workspace, workspace_bytes, s);
+    }
+    return conv2d_simt(*desc, s);
+}
+
+int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream)
+{
+    size_t need = 0;
+    int st = espdl_b200_conv2d_workspace_bytes(desc, &need);
+    if (st)
+        return st;
+    if (need == 0)
+        return espdl_b200_conv2d_ws(desc, nullptr, 0, stream);
+    // The cached scratch is shared by all calls of this entry point: calls that need it are
+    // serialised on the host here and must be ordered on the device by the caller's streams.
+    std::lock_guard<std::mutex> lock(g_ws_mutex);
+    if (need > g_ws_bytes) {
+        if (g_ws) {
+            ESPDL_CUDA_TRY(cudaDeviceSynchronize());
+            ESPDL_CUDA_TRY(cudaFree(g_ws));
+            g_ws = nullptr;
+            g_ws_bytes = 0;
+        }
+        cudaError_t e = cudaMalloc(&g_ws, need);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return ESPDL_ERR_NO_MEM;
+        }
+        g_ws_bytes = need;
+    }
+    return espdl_b200_conv2d_ws(desc, g_ws, g_ws_bytes, stream);
+}
+
+} // extern "C"

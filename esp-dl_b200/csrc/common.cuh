@@ -1,0 +1,108 @@
+// Shared device/host helpers of the B200 backend: ESP-DL's exact rounding and
+// saturation rules as device functions, status plumbing and launch accounting.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/espdl_b200.h"
+
+namespace espdl {
+
+// ---------------------------------------------------------------- host state
+int set_cuda_error(cudaError_t e, const char *what); // records text, returns ESPDL_ERR_CUDA
+void count_launch(int n = 1);
+int num_sms();
+// Records the most recent failed launch (cudaGetLastError) if any.
+int check_launch(const char *what);
+
+#define ESPDL_CUDA_TRY(call)                                \
+    do {                                                    \
+        cudaError_t e__ = (call);                           \
+        if (e__ != cudaSuccess)                             \
+            return ::espdl::set_cuda_error(e__, #call);     \
+    } while (0)
+
+// kernels behind the C ABI (one translation unit each)
+int conv2d_simt(const espdl_conv_desc &d, cudaStream_t s);
+int conv2d_depthwise(const espdl_conv_desc &d, cudaStream_t s);
+bool conv2d_tc_supported(const espdl_conv_desc &d);
+size_t conv2d_tc_workspace_bytes(const espdl_conv_desc &d);
+int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes, cudaStream_t s);
+int read_and_clear_device_error(); // status word written by device-side bounded waits (0 = none)
+
+// ------------------------------------------------------------- device math
+// dl::tool::shift_and_round on a 32-bit accumulator (int8 operators).
+//   shift > 0 : HALF_UP   floor((v + 2^(s-1)) / 2^s)  ==  (v >> s) + bit (s-1) of v
+//               HALF_EVEN floor, +1 if remainder > half or (== half and quotient odd)
+//   shift <= 0: (int64)v << -shift, saturated to int32
+// Callers guarantee |shift| <= 31.
+__device__ __forceinline__ int32_t shift_round32(int32_t v, int shift, int half_even)
+{
+    if (shift > 0) {
+        int32_t q = v >> shift;
+        if (!half_even) {
+            q += (v >> (shift - 1)) & 1;
+        } else {
+            const int32_t rem = v & ((1 << shift) - 1);
+            const int32_t half = 1 << (shift - 1);
+            q += (rem > half || (rem == half && (q & 1))) ? 1 : 0;
+        }
+        return q;
+    }
+    const long long s = (long long)v << (-shift);
+    return (int32_t)max(min(s, (long long)INT32_MAX), (long long)INT32_MIN);
+}
+
+// Same on a 64-bit accumulator (int16 operators); |shift| <= 62.
+__device__ __forceinline__ long long shift_round64(long long v, int shift, int half_even)
+{
+    if (shift > 0) {
+        long long q = v >> shift;
+        if (!half_even) {
+            q += (v >> (shift - 1)) & 1;
+        } else {
+            const long long rem = v & ((1ll << shift) - 1);
+            const long long half = 1ll << (shift - 1);
+            q += (rem > half || (rem == half && (q & 1))) ? 1 : 0;
+        }
+        return q;
+    }
+    return (long long)((unsigned long long)v << (-shift));
+}
+
+__device__ __forceinline__ int32_t sat8(int32_t v) { return max(-128, min(127, v)); }
+__device__ __forceinline__ int32_t sat16(int32_t v) { return max(-32768, min(32767, v)); }
+__device__ __forceinline__ long long sat16_64(long long v) { return max(-32768ll, min(32767ll, v)); }
+
+// int8 conv epilogue: bias (wrapping 32-bit add), shift/round, ReLU, saturate.
+__device__ __forceinline__ int32_t requant8(int32_t acc, int32_t bias, int shift, int relu, int half_even)
+{
+    int32_t v = shift_round32((int32_t)((uint32_t)acc + (uint32_t)bias), shift, half_even);
+    if (relu)
+        v = max(v, 0);
+    return sat8(v);
+}
+
+__device__ __forceinline__ int32_t requant16(long long acc, long long bias, int shift, int relu, int half_even)
+{
+    long long v = shift_round64(acc + bias, shift, half_even);
+    if (relu)
+        v = max(v, 0ll);
+    return (int32_t)sat16_64(v);
+}
+
+// dl::tool::round(float) on generic targets: (int)floorf((float)((double)v + 0.5)).
+// A single correctly rounded fp32 add gives the same float as the double sum
+// narrowed to float (the double sum of two floats whose exponents differ by less
+// than 29 is exact), so one __fadd_rn reproduces it without fp64.
+__device__ __forceinline__ int fround_half_up(float v) { return (int)floorf(__fadd_rn(v, 0.5f)); }
+// ESP32-P4: fcvt.w.s with round-to-nearest-even.
+__device__ __forceinline__ int fround_half_even(float v) { return __float2int_rn(v); }
+__device__ __forceinline__ int fround(float v, int half_even) { return half_even ? fround_half_even(v) : fround_half_up(v); }
+
+// DL_SCALE / DL_RESCALE: exact powers of two as floats.
+__host__ __device__ __forceinline__ float dl_scale(int e) { return e > 0 ? (float)(1 << e) : 1.0f / (float)(1 << -e); }
+__host__ __device__ __forceinline__ float dl_rescale(int e) { return e > 0 ? 1.0f / (float)(1 << e) : (float)(1 << -e); }
+
+} // namespace espdl

@@ -1,0 +1,248 @@
+// Elementwise operators of the quantized path: Add / Sub / Mul with numpy broadcasting,
+// RequantizeLinear (TensorBase::assign), 8-bit LUT activations, Clip, ReLU, PReLU.
+// All are bandwidth bound.  The int8 same-shape case (what a network's residual Adds, LUT
+// activations and requantize nodes are) runs a 128-bit vectorised kernel; everything else
+// (broadcast operands, int16, float endpoints) runs a strided scalar kernel.
+//
+// Arithmetic follows the reference exactly, including its fp32 sequences:
+//   Add/Sub  esp-dl/dl/base/dl_base_add.cpp:8-44      Mul   esp-dl/dl/base/dl_base_mul.cpp:9-46
+//   assign   esp-dl/dl/tensor/src/dl_tensor_base.cpp:223-404
+//   LUT      esp-dl/dl/base/dl_base_lut.cpp:10-15     Clip  esp-dl/dl/module/include/dl_module_clip.hpp:78-90
+//   ReLU     esp-dl/dl/module/include/dl_module_relu.hpp:66-91   PReLU esp-dl/dl/base/dl_base_prelu.cpp:5-19
+#include "common.cuh"
+
+namespace espdl {
+
+struct EltParams {
+    const void *a, *b;
+    void *out;
+    int op, idt, odt;
+    int os[4];
+    long long sa[4], sb[4]; // element strides (0 on broadcast axes)
+    int e0, e1, eo, lo, hi, half_even;
+    float mul_scale, clip_rescale, in_scale, out_rescale, inv_scale;
+    int prelu_shift;
+    long long total;
+};
+
+__device__ __forceinline__ long long ld_int(const void *p, int dt, long long i)
+{
+    return dt == ESPDL_DTYPE_INT8 ? (long long)((const int8_t *)p)[i] : (long long)((const int16_t *)p)[i];
+}
+
+__device__ __forceinline__ void st_sat(void *p, int dt, long long i, long long v)
+{
+    if (dt == ESPDL_DTYPE_INT8)
+        ((int8_t *)p)[i] = (int8_t)max(-128ll, min(127ll, v));
+    else
+        ((int16_t *)p)[i] = (int16_t)max(-32768ll, min(32767ll, v));
+}
+
+// One integer-in / integer-out element.  a, b are the widened operands.
+__device__ __forceinline__ long long elt_int(const EltParams &p, long long a, long long b)
+{
+    switch (p.op) {
+    case ESPDL_ELT_ADD: return a + b;
+    case ESPDL_ELT_SUB: return a - b;
+    case ESPDL_ELT_MUL: {
+        const int t = (int)(a * b);
+        return fround(__fmul_rn(__int2float_rn(t), p.mul_scale), p.half_even);
+    }
+    case ESPDL_ELT_REQUANTIZE: {
+        if (p.e0 == p.eo)
+            return a;
+        const float tmp = __fmul_rn(__int2float_rn((int)a), p.in_scale);
+        return fround(__fmul_rn(tmp, p.inv_scale), p.half_even);
+    }
+    case ESPDL_ELT_CLIP: {
+        const long long v = max((long long)p.lo, min((long long)p.hi, a));
+        return fround(__fmul_rn(__int2float_rn((int)v), p.clip_rescale), p.half_even);
+    }
+    case ESPDL_ELT_RELU: {
+        if (p.e0 == p.eo)
+            return a >= 0 ? a : 0;
+        const float temp = __fmul_rn(__int2float_rn((int)a), p.in_scale);
+        return temp >= 0 ? (long long)fround(__fmul_rn(temp, p.out_rescale), p.half_even) : 0ll;
+    }
+    case ESPDL_ELT_PRELU: {
+        if (a >= 0)
+            return a;
+        long long prod = a * b;
+        if (p.idt == ESPDL_DTYPE_INT8)
+            prod = (int)prod;
+        long long v = p.prelu_shift > 0 ? (prod >> p.prelu_shift) : (long long)((unsigned long long)prod << (-p.prelu_shift));
+        if (p.idt == ESPDL_DTYPE_INT8)
+            v = (int)v;
+        return v;
+    }
+    default: return 0;
+    }
+}
+
+__global__ void __launch_bounds__(256) elt_generic_kernel(EltParams p)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
+        long long r = i;
+        const int i0 = (int)(r % p.os[3]);
+        r /= p.os[3];
+        const int i1 = (int)(r % p.os[2]);
+        r /= p.os[2];
+        const int i2 = (int)(r % p.os[1]);
+        const int i3 = (int)(r / p.os[1]);
+        const long long ai = i3 * p.sa[0] + i2 * p.sa[1] + i1 * p.sa[2] + i0 * p.sa[3];
+        const long long bi = i3 * p.sb[0] + i2 * p.sb[1] + i1 * p.sb[2] + i0 * p.sb[3];
+        if (p.op == ESPDL_ELT_LUT) {
+            ((int8_t *)p.out)[i] = ((const int8_t *)p.b)[(uint8_t)((const int8_t *)p.a)[ai] ^ 0x80u];
+        } else if (p.op == ESPDL_ELT_REQUANTIZE && p.idt == ESPDL_DTYPE_FLOAT) {
+            st_sat(p.out, p.odt, i, fround(__fmul_rn(((const float *)p.a)[ai], p.out_rescale), p.half_even));
+        } else if (p.op == ESPDL_ELT_REQUANTIZE && p.odt == ESPDL_DTYPE_FLOAT) {
+            ((float *)p.out)[i] = __fmul_rn(__int2float_rn((int)ld_int(p.a, p.idt, ai)), p.in_scale);
+        } else {
+            const long long a = ld_int(p.a, p.idt, ai);
+            long long b = 0;
+            if (p.op == ESPDL_ELT_ADD || p.op == ESPDL_ELT_SUB || p.op == ESPDL_ELT_MUL)
+                b = ld_int(p.b, p.idt, bi);
+            else if (p.op == ESPDL_ELT_PRELU)
+                b = ld_int(p.b, p.idt, i0);
+            st_sat(p.out, p.odt, i, elt_int(p, a, b));
+        }
+    }
+}
+
+// int8 -> int8, operands of identical shape, 16 elements per thread.
+template <int OP>
+__global__ void __launch_bounds__(256) elt_s8_vec16_kernel(EltParams p, long long nvec)
+{
+    __shared__ int8_t table[256];
+    if (OP == ESPDL_ELT_LUT) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) table[i] = ((const int8_t *)p.b)[i];
+        __syncthreads();
+    }
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+        const uint4 a4 = ((const uint4 *)p.a)[v];
+        uint4 b4 = make_uint4(0, 0, 0, 0);
+        if (OP == ESPDL_ELT_ADD || OP == ESPDL_ELT_SUB || OP == ESPDL_ELT_MUL)
+            b4 = ((const uint4 *)p.b)[v];
+        const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
+        const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            uint32_t wd = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int a = (int)(int8_t)(aw[q] >> (8 * j));
+                const int b = (int)(int8_t)(bw[q] >> (8 * j));
+                int r;
+                if (OP == ESPDL_ELT_LUT) {
+                    r = table[(uint8_t)a ^ 0x80u];
+                } else if (OP == ESPDL_ELT_ADD) {
+                    r = sat8(a + b);
+                } else if (OP == ESPDL_ELT_SUB) {
+                    r = sat8(a - b);
+                } else {
+                    EltParams q2 = p;
+                    q2.op = OP;
+                    r = sat8((int)max(-1000000ll, min(1000000ll, elt_int(q2, a, b))));
+                }
+                wd |= ((uint32_t)r & 0xffu) << (8 * j);
+            }
+            ow[q] = wd;
+        }
+        ((uint4 *)p.out)[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
+template <int OP>
+static void launch_vec(const EltParams &p, long long nvec, cudaStream_t s)
+{
+    const int threads = 256;
+    long long blocks = min((nvec + threads - 1) / threads, (long long)num_sms() * 16);
+    elt_s8_vec16_kernel<OP><<<(unsigned)max(blocks, 1ll), threads, 0, s>>>(p, nvec);
+}
+
+} // namespace espdl
+
+using namespace espdl;
+
+extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
+{
+    if (!d || !d->input0 || !d->output || d->ndim < 1 || d->ndim > 4)
+        return ESPDL_ERR_INVALID_ARG;
+    const bool binary = d->op == ESPDL_ELT_ADD || d->op == ESPDL_ELT_SUB || d->op == ESPDL_ELT_MUL;
+    if ((binary || d->op == ESPDL_ELT_LUT || d->op == ESPDL_ELT_PRELU) && !d->input1)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->op < ESPDL_ELT_ADD || d->op > ESPDL_ELT_SUB)
+        return ESPDL_ERR_INVALID_ARG;
+    auto is_int = [](int t) { return t == ESPDL_DTYPE_INT8 || t == ESPDL_DTYPE_INT16; };
+    if (d->op == ESPDL_ELT_REQUANTIZE) {
+        const bool ok = (is_int(d->in_dtype) || d->in_dtype == ESPDL_DTYPE_FLOAT) && (is_int(d->out_dtype) || d->out_dtype == ESPDL_DTYPE_FLOAT) &&
+            !(d->in_dtype == ESPDL_DTYPE_FLOAT && d->out_dtype == ESPDL_DTYPE_FLOAT);
+        if (!ok)
+            return ESPDL_ERR_UNSUPPORTED;
+    } else if (d->op == ESPDL_ELT_LUT) {
+        if (d->in_dtype != ESPDL_DTYPE_INT8 || d->out_dtype != ESPDL_DTYPE_INT8)
+            return ESPDL_ERR_UNSUPPORTED;
+    } else if (!is_int(d->in_dtype) || d->in_dtype != d->out_dtype) {
+        return ESPDL_ERR_UNSUPPORTED;
+    }
+    EltParams p;
+    memset(&p, 0, sizeof(p));
+    int os[4] = {1, 1, 1, 1}, s0[4] = {1, 1, 1, 1}, s1[4] = {1, 1, 1, 1};
+    for (int i = 0; i < d->ndim; i++) {
+        os[4 - d->ndim + i] = d->out_shape[i];
+        s0[4 - d->ndim + i] = d->in0_shape[i];
+        s1[4 - d->ndim + i] = binary ? d->in1_shape[i] : 1;
+    }
+    long long a = 1, b = 1, total = 1;
+    bool same = true;
+    for (int i = 3; i >= 0; i--) {
+        if (os[i] < 0 || (s0[i] != os[i] && s0[i] != 1) || (s1[i] != os[i] && s1[i] != 1))
+            return ESPDL_ERR_INVALID_ARG;
+        p.os[i] = os[i];
+        p.sa[i] = s0[i] == 1 ? 0 : a;
+        p.sb[i] = s1[i] == 1 ? 0 : b;
+        a *= s0[i], b *= s1[i], total *= os[i];
+        if (s0[i] != os[i] || (binary && s1[i] != os[i]))
+            same = false;
+    }
+    if (total == 0)
+        return ESPDL_OK;
+    p.a = d->input0, p.b = d->input1, p.out = d->output;
+    p.op = d->op, p.idt = d->in_dtype, p.odt = d->out_dtype;
+    p.e0 = d->in0_exponent, p.e1 = d->in1_exponent, p.eo = d->out_exponent;
+    p.lo = d->clip_lo, p.hi = d->clip_hi, p.half_even = d->round_mode == ESPDL_ROUND_HALF_EVEN;
+    for (int e : {p.e0, p.e1, p.eo})
+        if (e > 30 || e < -30)
+            return ESPDL_ERR_INVALID_ARG;
+    p.mul_scale = dl_scale(p.e0) * dl_scale(p.e1) * dl_rescale(p.eo);
+    p.clip_rescale = dl_scale(p.e0) * dl_rescale(p.eo);
+    p.in_scale = dl_scale(p.e0);
+    p.out_rescale = dl_rescale(p.eo);
+    p.inv_scale = (float)(1.0 / (double)dl_scale(p.eo));
+    p.prelu_shift = p.eo - p.e0 - p.e1;
+    p.total = total;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool vec = same && d->in_dtype == ESPDL_DTYPE_INT8 && d->out_dtype == ESPDL_DTYPE_INT8 && total % 16 == 0 &&
+        ((uintptr_t)d->input0 % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && (!binary || ((uintptr_t)d->input1 % 16) == 0) &&
+        d->op != ESPDL_ELT_PRELU;
+    if (vec) {
+        const long long nvec = total / 16;
+        switch (d->op) {
+        case ESPDL_ELT_ADD: launch_vec<ESPDL_ELT_ADD>(p, nvec, s); break;
+        case ESPDL_ELT_SUB: launch_vec<ESPDL_ELT_SUB>(p, nvec, s); break;
+        case ESPDL_ELT_MUL: launch_vec<ESPDL_ELT_MUL>(p, nvec, s); break;
+        case ESPDL_ELT_REQUANTIZE: launch_vec<ESPDL_ELT_REQUANTIZE>(p, nvec, s); break;
+        case ESPDL_ELT_LUT: launch_vec<ESPDL_ELT_LUT>(p, nvec, s); break;
+        case ESPDL_ELT_CLIP: launch_vec<ESPDL_ELT_CLIP>(p, nvec, s); break;
+        case ESPDL_ELT_RELU: launch_vec<ESPDL_ELT_RELU>(p, nvec, s); break;
+        default: return ESPDL_ERR_UNSUPPORTED;
+        }
+    } else {
+        const int threads = 256;
+        long long blocks = min((total + threads - 1) / threads, (long long)num_sms() * 32);
+        elt_generic_kernel<<<(unsigned)blocks, threads, 0, s>>>(p);
+    }
+    count_launch();
+    return check_launch("eltwise");
+}

@@ -1,0 +1,224 @@
+// Pooling, nearest-neighbour resize and strided copy (Concat / Split / Transpose / Slice).
+// All bandwidth bound; threads run along the channel axis so every warp access is contiguous.
+//   MaxPool            esp-dl/dl/base/dl_base_max_pool2d.cpp:9-27 (in-bounds taps only)
+//   (Global)AveragePool esp-dl/dl/base/dl_base_avg_pool2d.cpp:10-55 (int sum, fp32 scale, area = kh*kw)
+//   Resize nearest     esp-dl/dl/base/dl_base_resize.cpp:7-35,239-279
+//   Concat             esp-dl/dl/module/include/dl_module_concat.hpp:87-107
+#include "common.cuh"
+
+namespace espdl {
+
+struct PoolParams {
+    const void *in;
+    void *out;
+    int op, is16, n, ih, iw, c, oh, ow, kh, kw, sh, sw, pt, pl;
+    float scale;
+    long long total;
+};
+
+__global__ void __launch_bounds__(256) pool_kernel(PoolParams p)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % p.c);
+        const long long pix = i / p.c;
+        const int ox = (int)(pix % p.ow);
+        const int oy = (int)((pix / p.ow) % p.oh);
+        const int n = (int)(pix / ((long long)p.ow * p.oh));
+        long long sum = 0;
+        int mx = INT32_MIN;
+        for (int ky = 0; ky < p.kh; ky++) {
+            const int iy = oy * p.sh + ky - p.pt;
+            if (iy < 0 || iy >= p.ih)
+                continue;
+            for (int kx = 0; kx < p.kw; kx++) {
+                const int ix = ox * p.sw + kx - p.pl;
+                if (ix < 0 || ix >= p.iw)
+                    continue;
+                const long long ii = (((long long)n * p.ih + iy) * p.iw + ix) * p.c + c;
+                const int v = p.is16 ? (int)((const int16_t *)p.in)[ii] : (int)((const int8_t *)p.in)[ii];
+                sum += v;
+                mx = max(mx, v);
+            }
+        }
+        int r;
+        if (p.op == ESPDL_POOL_MAX) {
+            r = mx;
+        } else {
+            // int8: the reference accumulates in int32, int16: in int64; both convert the sum to fp32
+            const float f = p.is16 ? __ll2float_rn(sum) : __int2float_rn((int)sum);
+            r = fround_half_up(__fmul_rn(f, p.scale));
+        }
+        if (p.is16)
+            ((int16_t *)p.out)[i] = (int16_t)sat16(r);
+        else
+            ((int8_t *)p.out)[i] = (int8_t)sat8(r);
+    }
+}
+
+struct ResizeParams {
+    const int8_t *in;
+    int8_t *out;
+    int n, ih, iw, c, oh, ow, ops, two;
+    float sh_inv, sw_inv, oscale, odiv;
+    long long total;
+};
+
+__global__ void __launch_bounds__(256) resize_nearest_kernel(ResizeParams p)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % p.c);
+        const long long pix = i / p.c;
+        const int x = (int)(pix % p.ow);
+        const int y = (int)((pix / p.ow) % p.oh);
+        const int n = (int)(pix / ((long long)p.ow * p.oh));
+        int iy = p.two ? y / 2 : (int)__fmul_rn((float)y, p.sh_inv);
+        int ix = p.two ? x / 2 : (int)__fmul_rn((float)x, p.sw_inv);
+        iy = min(iy, p.ih - 1);
+        ix = min(ix, p.iw - 1);
+        const int v = p.in[(((long long)n * p.ih + iy) * p.iw + ix) * p.c + c];
+        // (float)x * scale / (1 << shift), then round; the reference stores the result with a plain cast
+        const float f = __fdiv_rn(__fmul_rn((float)v, p.oscale), p.odiv);
+        p.out[pix * p.ops + c] = (int8_t)fround_half_up(f);
+    }
+}
+
+struct CopyParams {
+    const char *src;
+    char *dst;
+    int es;
+    int shape[6];
+    long long ss[6], ds[6];
+    long long total;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) copy_kernel(CopyParams p)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
+        long long r = i, si = 0, di = 0;
+#pragma unroll
+        for (int k = 5; k >= 0; k--) {
+            const int idx = (int)(r % p.shape[k]);
+            r /= p.shape[k];
+            si += idx * p.ss[k];
+            di += idx * p.ds[k];
+        }
+        ((T *)p.dst)[di] = ((const T *)p.src)[si];
+    }
+}
+
+} // namespace espdl
+
+using namespace espdl;
+
+extern "C" int espdl_b200_pool(const espdl_pool_desc *d, void *stream)
+{
+    if (!d || !d->input || !d->output)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->dtype != ESPDL_DTYPE_INT8 && d->dtype != ESPDL_DTYPE_INT16)
+        return ESPDL_ERR_UNSUPPORTED;
+    if (d->op < ESPDL_POOL_MAX || d->op > ESPDL_POOL_GLOBAL_AVG || d->n < 0 || d->in_h <= 0 || d->in_w <= 0 || d->c <= 0)
+        return ESPDL_ERR_INVALID_ARG;
+    PoolParams p;
+    p.in = d->input, p.out = d->output, p.op = d->op, p.is16 = d->dtype == ESPDL_DTYPE_INT16;
+    p.n = d->n, p.ih = d->in_h, p.iw = d->in_w, p.c = d->c;
+    if (d->op == ESPDL_POOL_GLOBAL_AVG) {
+        p.oh = p.ow = 1, p.kh = d->in_h, p.kw = d->in_w, p.sh = p.sw = 1, p.pt = p.pl = 0;
+    } else {
+        if (d->kh <= 0 || d->kw <= 0 || d->stride_h <= 0 || d->stride_w <= 0 || d->out_h <= 0 || d->out_w <= 0)
+            return ESPDL_ERR_INVALID_ARG;
+        if (d->out_h != (d->in_h + d->pad_top + d->pad_bottom - d->kh) / d->stride_h + 1 ||
+            d->out_w != (d->in_w + d->pad_left + d->pad_right - d->kw) / d->stride_w + 1)
+            return ESPDL_ERR_INVALID_ARG;
+        p.oh = d->out_h, p.ow = d->out_w, p.kh = d->kh, p.kw = d->kw, p.sh = d->stride_h, p.sw = d->stride_w;
+        p.pt = d->pad_top, p.pl = d->pad_left;
+    }
+    if (d->in_exponent > 30 || d->in_exponent < -30 || d->out_exponent > 30 || d->out_exponent < -30)
+        return ESPDL_ERR_INVALID_ARG;
+    const float inv_area = 1.f / (float)(p.kh * p.kw);
+    p.scale = dl_scale(d->in_exponent) * inv_area * dl_rescale(d->out_exponent);
+    p.total = (long long)p.n * p.oh * p.ow * p.c;
+    if (p.total == 0)
+        return ESPDL_OK;
+    long long blocks = min((p.total + 255) / 256, (long long)num_sms() * 32);
+    pool_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+    count_launch();
+    return check_launch("pool");
+}
+
+extern "C" int espdl_b200_resize(const espdl_resize_desc *d, void *stream)
+{
+    if (!d || !d->input || !d->output)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->dtype != ESPDL_DTYPE_INT8) // the reference's int16 resize is an empty function (dl_base_resize.cpp:298-309)
+        return ESPDL_ERR_UNSUPPORTED;
+    if (d->n < 0 || d->in_h <= 0 || d->in_w <= 0 || d->c <= 0 || d->out_h <= 0 || d->out_w <= 0 || d->scale_h <= 0 || d->scale_w <= 0)
+        return ESPDL_ERR_INVALID_ARG;
+    ResizeParams p;
+    p.in = (const int8_t *)d->input, p.out = (int8_t *)d->output;
+    p.n = d->n, p.ih = d->in_h, p.iw = d->in_w, p.c = d->c, p.oh = d->out_h, p.ow = d->out_w;
+    p.ops = d->out_pixel_stride ? d->out_pixel_stride : d->c;
+    p.two = d->scale_h == 2 && d->scale_w == 2;
+    p.sh_inv = 1 / d->scale_h, p.sw_inv = 1 / d->scale_w;
+    int shift = d->out_exponent - d->in_exponent, oscale = 1;
+    if (shift < 0) {
+        oscale = 1 << (-shift);
+        shift = 0;
+    }
+    if (shift > 30 || oscale > (1 << 30))
+        return ESPDL_ERR_INVALID_ARG;
+    p.oscale = (float)oscale, p.odiv = (float)(1 << shift);
+    p.total = (long long)p.n * p.oh * p.ow * p.c;
+    if (p.total == 0)
+        return ESPDL_OK;
+    long long blocks = min((p.total + 255) / 256, (long long)num_sms() * 32);
+    resize_nearest_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+    count_launch();
+    return check_launch("resize");
+}
+
+extern "C" int espdl_b200_copy(const espdl_copy_desc *d, void *stream)
+{
+    if (!d || !d->src || !d->dst || d->ndim < 1 || d->ndim > 6)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->elem_size != 1 && d->elem_size != 2 && d->elem_size != 4 && d->elem_size != 8)
+        return ESPDL_ERR_INVALID_ARG;
+    CopyParams p;
+    p.src = (const char *)d->src, p.dst = (char *)d->dst, p.es = d->elem_size;
+    p.total = 1;
+    for (int i = 0; i < 6; i++) p.shape[i] = 1, p.ss[i] = 0, p.ds[i] = 0;
+    for (int i = 0; i < d->ndim; i++) {
+        if (d->shape[i] < 0)
+            return ESPDL_ERR_INVALID_ARG;
+        p.shape[6 - d->ndim + i] = d->shape[i];
+        p.ss[6 - d->ndim + i] = d->src_stride[i];
+        p.ds[6 - d->ndim + i] = d->dst_stride[i];
+        p.total *= d->shape[i];
+    }
+    if (p.total == 0)
+        return ESPDL_OK;
+    // widen the element when the innermost run is contiguous and everything is aligned
+    int es = d->elem_size;
+    while (es < 16) {
+        const int f = 2;
+        bool ok = p.ss[5] == 1 && p.ds[5] == 1 && p.shape[5] % f == 0 && ((uintptr_t)p.src % (es * f)) == 0 && ((uintptr_t)p.dst % (es * f)) == 0;
+        for (int k = 0; k < 5 && ok; k++) ok = p.ss[k] % f == 0 && p.ds[k] % f == 0;
+        if (!ok)
+            break;
+        p.shape[5] /= f;
+        for (int k = 0; k < 5; k++) p.ss[k] /= f, p.ds[k] /= f;
+        p.total /= f;
+        es *= f;
+    }
+    long long blocks = min((p.total + 255) / 256, (long long)num_sms() * 32);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (es) {
+    case 1: copy_kernel<uint8_t><<<(unsigned)blocks, 256, 0, s>>>(p); break;
+    case 2: copy_kernel<uint16_t><<<(unsigned)blocks, 256, 0, s>>>(p); break;
+    case 4: copy_kernel<uint32_t><<<(unsigned)blocks, 256, 0, s>>>(p); break;
+    case 8: copy_kernel<uint2><<<(unsigned)blocks, 256, 0, s>>>(p); break;
+    default: copy_kernel<uint4><<<(unsigned)blocks, 256, 0, s>>>(p); break;
+    }
+    count_launch();
+    return check_launch("copy");
+}

@@ -1,0 +1,78 @@
+"""Helpers for the GPU parity tests: device buffers through the C ABI itself (no torch on this path)."""
+import ctypes as C
+
+import numpy as np
+
+from espdl_b200 import abi
+
+_initialised = False
+
+
+def lib():
+    global _initialised
+    L = abi.load()
+    if not _initialised:
+        abi.check(L.espdl_b200_init(0), "espdl_b200_init")
+        _initialised = True
+    return L
+
+
+class DeviceBuffers:
+    """Uploads numpy arrays, hands out device addresses, frees everything on exit."""
+
+    def __init__(self):
+        self.lib = lib()
+        self.ptrs = []
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        for p in self.ptrs:
+            self.lib.espdl_b200_arena_free(p)
+        self.ptrs = []
+
+    def alloc(self, nbytes):
+        p = C.c_void_p()
+        abi.check(self.lib.espdl_b200_arena_alloc(max(int(nbytes), 16), C.byref(p)), "arena_alloc")
+        self.ptrs.append(p)
+        return p.value
+
+    def upload(self, arr):
+        if arr is None:
+            return None
+        arr = np.ascontiguousarray(arr)
+        p = self.alloc(arr.nbytes)
+        abi.check(self.lib.espdl_b200_upload(p, arr.ctypes.data, arr.nbytes, None), "upload")
+        abi.check(self.lib.espdl_b200_stream_sync(None), "sync")
+        return p
+
+    def download(self, ptr, like):
+        out = np.empty_like(like)
+        abi.check(self.lib.espdl_b200_stream_sync(None), "sync")
+        abi.check(self.lib.espdl_b200_download(out.ctypes.data, ptr, out.nbytes, None), "download")
+        abi.check(self.lib.espdl_b200_stream_sync(None), "sync")
+        return out
+
+
+def run_conv_gpu(case, kernel=abi.KERNEL_AUTO, expect=abi.OK):
+    import cases
+    with DeviceBuffers() as dev:
+        ptrs = dict(input=dev.upload(case["x"]), filter=dev.upload(case["w"]), bias=dev.upload(case["b"]),
+                    filter_exponents=dev.upload(case["ew"]), lut=dev.upload(case["lut"]),
+                    output=dev.upload(np.full_like(case["out"], 0x55)))
+        d = cases.conv_desc(dict(case, kernel=kernel), ptrs)
+        st = dev.lib.espdl_b200_conv2d(C.byref(d), None)
+        if expect != abi.OK:
+            assert st == expect
+            return None
+        abi.check(st, "espdl_b200_conv2d")
+        return dev.download(ptrs["output"], case["out"])
+
+
+def run_conv_oracle(case):
+    import cases
+    import checkers
+    out = np.full_like(case["out"], 0x55)
+    assert checkers.oracle().oracle_conv2d(cases.conv_desc(dict(case, out=out))) == 0
+    return out

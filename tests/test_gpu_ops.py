@@ -1,0 +1,254 @@
+"""GPU parity: every CUDA-core kernel behind the C ABI against the plain-C oracle, bit for bit, on seeded
+inputs (sizes the oracle finishes in well under a second)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+import checkers
+import gpu_util
+from espdl_b200 import abi
+from test_oracle_vs_reference import CONV_CASES
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("round_mode", [abi.ROUND_HALF_UP, abi.ROUND_HALF_EVEN])
+@pytest.mark.parametrize("per_channel", [False, True])
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("idx", range(len(CONV_CASES)))
+def test_conv_simt(idx, dtype, per_channel, round_mode):
+    kw = dict(CONV_CASES[idx])
+    if dtype == abi.DTYPE_INT16:
+        kw.setdefault("e_in", -14)
+        kw.setdefault("e_w", (-15, -13))
+        kw.setdefault("e_out", -12)
+    case = cases.conv_case(seed=200 + idx, dtype=dtype, per_channel=per_channel, round_mode=round_mode, **kw)
+    got = gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT)
+    np.testing.assert_array_equal(got, gpu_util.run_conv_oracle(case))
+
+
+def test_conv_simt_config1_exact_shape():
+    """The single-image 3x3 conv configuration: 1x56x56x64 -> 64, per-channel exponents in {-9..-6}, ReLU."""
+    case = cases.conv_case(seed=1, n=1, h=56, w=56, cin=64, cout=64, kh=3, kw=3, per_channel=True, e_in=-7, e_out=-6, e_w=(-9, -6))
+    got = gpu_util.run_conv_gpu(case)
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(got, want)
+    assert 0.05 < (want == 0).mean() < 0.95 and (want == 127).mean() < 0.5
+
+
+def test_conv_lut_and_pixel_strides():
+    case = cases.conv_case(seed=31, n=2, h=7, w=6, cin=8, cout=12, kh=3, kw=3, lut=True, in_stride=24, out_stride=40, per_channel=True)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT), gpu_util.run_conv_oracle(case))
+
+
+def test_conv_first_layer_shape():
+    """3-channel 3x3 stride-2 stem (224x224x3 -> 112x112x32), two images."""
+    case = cases.conv_case(seed=33, n=2, h=224, w=224, cin=3, cout=32, kh=3, kw=3, stride=2, pad=(0, 1, 0, 1), per_channel=True,
+                           e_in=-7, e_out=-5, e_w=(-8, -6))
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), gpu_util.run_conv_oracle(case))
+
+
+@pytest.mark.parametrize("round_mode", [abi.ROUND_HALF_UP, abi.ROUND_HALF_EVEN])
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("kw", [
+    dict(h=8, w=8, cin=16, kh=3, kw=3),
+    dict(n=3, h=14, w=14, cin=96, kh=3, kw=3, stride=2, pad=(0, 1, 0, 1)),       # vector path, stride 2
+    dict(n=2, h=9, w=11, cin=24, kh=3, kw=3, stride=2),                          # 24 channels: scalar path
+    dict(h=10, w=10, cin=25, kh=7, kw=7, stride=(1, 2), pad=(2, 2, 2, 2)),
+    dict(h=8, w=8, cin=32, kh=3, kw=3, dil=2, pad=(2, 2, 2, 2)),
+    dict(n=2, h=6, w=7, cin=32, kh=3, kw=3, act=abi.ACT_LINEAR, bias=False),
+    dict(n=2, h=6, w=7, cin=32, kh=3, kw=3, in_stride=48, out_stride=64, lut=True),
+])
+def test_depthwise(kw, dtype, round_mode):
+    kw = dict(kw)
+    if dtype == abi.DTYPE_INT16:
+        kw.update(e_in=-13, e_w=(-14, -12), e_out=-11)
+        kw.pop("lut", None)
+    case = cases.conv_case(seed=41, dtype=dtype, depthwise=True, per_channel=True, round_mode=round_mode, **kw)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), gpu_util.run_conv_oracle(case))
+
+
+def test_depthwise_block_shape():
+    """The inverted-residual block's depthwise layer shape: 112x112x192, 3x3 stride 1 (two images)."""
+    case = cases.conv_case(seed=43, n=2, h=112, w=112, cin=192, kh=3, kw=3, depthwise=True, per_channel=True, e_in=-5, e_out=-5, e_w=(-9, -5))
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), gpu_util.run_conv_oracle(case))
+
+
+def run_eltwise(case, inplace=None):
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input0=dev.upload(case["a"]), input1=dev.upload(case["b"]), output=dev.upload(case["out"]))
+        if inplace:
+            ptrs["output"] = ptrs[inplace]
+        d = cases.eltwise_desc(case, ptrs)
+        abi.check(dev.lib.espdl_b200_eltwise(C.byref(d), None), "eltwise")
+        got = dev.download(ptrs["output"], case["out"])
+    want = case["out"].copy()
+    assert checkers.oracle().oracle_eltwise(cases.eltwise_desc(dict(case, out=want))) == 0
+    return got, want
+
+
+@pytest.mark.parametrize("round_mode", [abi.ROUND_HALF_UP, abi.ROUND_HALF_EVEN])
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("op", [abi.ELT_ADD, abi.ELT_SUB, abi.ELT_MUL])
+@pytest.mark.parametrize("shapes", [
+    ((2, 5, 7, 16), None, None), ((2, 5, 7, 16), (2, 5, 7, 16), (1, 1, 1, 16)), ((2, 5, 7, 16), (2, 5, 7, 16), (1, 1, 1, 1)),
+    ((2, 5, 7, 16), (1, 1, 1, 1), (2, 5, 7, 16)), ((2, 5, 7, 16), (2, 1, 7, 1), (1, 5, 1, 16)), ((3, 20), (3, 1), (1, 20)), ((37,), None, None),
+])
+def test_binary(op, dtype, shapes, round_mode):
+    e = dict(e0=-5, e1=-6, eo=-8) if op == abi.ELT_MUL else dict(e0=-5, e1=-5, eo=-5)
+    if dtype == abi.DTYPE_INT16 and op == abi.ELT_MUL:
+        e = dict(e0=-12, e1=-13, eo=-11)
+    case = cases.eltwise_case(op, seed=3, dtype=dtype, out_shape=shapes[0], in0_shape=shapes[1], in1_shape=shapes[2],
+                              round_mode=round_mode, **e)
+    got, want = run_eltwise(case)
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("inplace", ["input0", "input1"])
+def test_add_in_place(inplace):
+    """The planner runs Add in place: the output may alias either input."""
+    case = cases.eltwise_case(abi.ELT_ADD, seed=5, out_shape=(4, 14, 14, 32), e0=-5, e1=-5, eo=-5)
+    got, want = run_eltwise(case, inplace=inplace)
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("idt,odt,e0,eo", [
+    (abi.DTYPE_INT8, abi.DTYPE_INT8, -4, -2), (abi.DTYPE_INT8, abi.DTYPE_INT8, -4, -6), (abi.DTYPE_INT8, abi.DTYPE_INT8, -4, -4),
+    (abi.DTYPE_INT16, abi.DTYPE_INT16, -10, -7), (abi.DTYPE_INT16, abi.DTYPE_INT8, -10, -5), (abi.DTYPE_INT8, abi.DTYPE_INT16, -5, -10),
+    (abi.DTYPE_INT16, abi.DTYPE_INT8, -7, -7), (abi.DTYPE_INT8, abi.DTYPE_INT16, -7, -7),
+    (abi.DTYPE_FLOAT, abi.DTYPE_INT8, 0, -4), (abi.DTYPE_FLOAT, abi.DTYPE_INT16, 0, -11),
+    (abi.DTYPE_INT8, abi.DTYPE_FLOAT, -4, 0), (abi.DTYPE_INT16, abi.DTYPE_FLOAT, -9, 0),
+])
+def test_requantize(idt, odt, e0, eo):
+    case = cases.eltwise_case(abi.ELT_REQUANTIZE, seed=5, in_dtype=idt, out_dtype=odt, out_shape=(3, 4, 5, 16), e0=e0, eo=eo)
+    got, want = run_eltwise(case)
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("shape", [(1, 4, 6, 24), (2, 8, 8, 32)])  # scalar and 128-bit paths
+@pytest.mark.parametrize("op,dtype,kw", [
+    (abi.ELT_LUT, abi.DTYPE_INT8, {}),
+    (abi.ELT_CLIP, abi.DTYPE_INT8, dict(e0=-4, eo=-4, clip=(0, 96))),
+    (abi.ELT_CLIP, abi.DTYPE_INT8, dict(e0=-4, eo=-5, clip=(0, 96))),
+    (abi.ELT_CLIP, abi.DTYPE_INT16, dict(e0=-10, eo=-9, clip=(-3000, 6000))),
+    (abi.ELT_RELU, abi.DTYPE_INT8, dict(e0=-4, eo=-4)),
+    (abi.ELT_RELU, abi.DTYPE_INT8, dict(e0=-4, eo=-6)),
+    (abi.ELT_RELU, abi.DTYPE_INT16, dict(e0=-9, eo=-7)),
+    (abi.ELT_PRELU, abi.DTYPE_INT8, dict(e0=-4, e1=-7, eo=-4)),
+    (abi.ELT_PRELU, abi.DTYPE_INT16, dict(e0=-10, e1=-15, eo=-10)),
+])
+def test_unary(op, dtype, kw, shape):
+    case = cases.eltwise_case(op, seed=9, dtype=dtype, out_shape=shape, **kw)
+    got, want = run_eltwise(case)
+    np.testing.assert_array_equal(got, want)
+
+
+def test_lut_all_codes():
+    """All 256 input codes through a LUT (the reference's own primitive test pattern, test_apps/dl_pie_func test_lut.cpp)."""
+    case = cases.eltwise_case(abi.ELT_LUT, seed=11, out_shape=(256,))
+    case["a"] = np.arange(-128, 128, dtype=np.int8)
+    got, want = run_eltwise(case)
+    np.testing.assert_array_equal(got, want)
+    np.testing.assert_array_equal(got, case["b"][(case["a"].astype(np.int32) + 128)])
+
+
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("op,kw", [
+    (abi.POOL_MAX, dict(kh=3, kw=3, stride=2, pad=(1, 1, 1, 1))),
+    (abi.POOL_MAX, dict(h=20, w=20, c=128, kh=5, kw=5, stride=1, pad=(2, 2, 2, 2))),
+    (abi.POOL_MAX, dict(kh=2, kw=2, stride=2, pad=(0, 0, 0, 0))),
+    (abi.POOL_AVG, dict(kh=2, kw=2, stride=2, pad=(0, 0, 0, 0))),
+    (abi.POOL_AVG, dict(kh=3, kw=3, stride=2, pad=(1, 1, 1, 1), e_out=-4)),
+    (abi.POOL_GLOBAL_AVG, dict(h=7, w=7, c=40, e_in=-4, e_out=-5)),
+    (abi.POOL_GLOBAL_AVG, dict(n=4, h=7, w=7, c=1280, e_in=-5, e_out=-5)),
+])
+def test_pool(op, kw, dtype):
+    case = cases.pool_case(op, seed=13, dtype=dtype, **kw)
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input=dev.upload(case["x"]), output=dev.upload(case["out"]))
+        d = cases.pool_desc(case, ptrs)
+        abi.check(dev.lib.espdl_b200_pool(C.byref(d), None), "pool")
+        got = dev.download(ptrs["output"], case["out"])
+    want = case["out"].copy()
+    assert checkers.oracle().oracle_pool(cases.pool_desc(dict(case, out=want))) == 0
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("kw", [dict(scale=(2.0, 2.0)), dict(scale=(2.0, 2.0), e_in=-5, e_out=-4), dict(scale=(2.0, 2.0), e_in=-5, e_out=-6),
+                                dict(scale=(3.0, 2.0)), dict(scale=(1.5, 2.5), h=8, w=8), dict(scale=(0.5, 0.5), h=8, w=10),
+                                dict(scale=(2.0, 2.0), n=2, h=20, w=20, c=64, out_stride=192)])
+def test_resize(kw):
+    case = cases.resize_case(seed=17, **kw)
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input=dev.upload(case["x"]), output=dev.upload(case["out"]))
+        d = cases.resize_desc(case, ptrs)
+        abi.check(dev.lib.espdl_b200_resize(C.byref(d), None), "resize")
+        got = dev.download(ptrs["output"], case["out"])
+    want = case["out"].copy()
+    assert checkers.oracle().oracle_resize(cases.resize_desc(dict(case, out=want))) == 0
+    np.testing.assert_array_equal(got, want)
+
+
+def test_resize_int16_is_rejected():
+    case = cases.resize_case(seed=17, dtype=abi.DTYPE_INT16)
+    with gpu_util.DeviceBuffers() as dev:
+        d = cases.resize_desc(case, dict(input=dev.upload(case["x"]), output=dev.upload(case["out"])))
+        assert dev.lib.espdl_b200_resize(C.byref(d), None) == abi.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("es,dtype", [(1, np.int8), (2, np.int16), (4, np.float32)])
+def test_copy_concat_and_transpose(es, dtype):
+    rng = np.random.default_rng(23)
+    a = rng.integers(-100, 100, size=(2, 3, 4, 8)).astype(dtype)
+    b = rng.integers(-100, 100, size=(2, 3, 4, 24)).astype(dtype)
+    with gpu_util.DeviceBuffers() as dev:
+        pa, pb = dev.upload(a), dev.upload(b)
+        out = np.zeros((2, 3, 4, 32), dtype=dtype)
+        po = dev.upload(out)
+        for src, off, c in ((pa, 0, 8), (pb, 8, 24)):       # channel Concat = one strided copy per input
+            d = cases.copy_desc(src, po + off * es, es, (24, c), (c, 1), (32, 1))
+            abi.check(dev.lib.espdl_b200_copy(C.byref(d), None), "copy")
+        np.testing.assert_array_equal(dev.download(po, out), np.concatenate([a, b], axis=3))
+        # Transpose NHWC -> NCHW: permuted source strides
+        t = np.zeros((2, 8, 3, 4), dtype=dtype)
+        pt = dev.upload(t)
+        d = cases.copy_desc(pa, pt, es, (2, 8, 3, 4), (96, 1, 32, 8), (96, 12, 4, 1))
+        abi.check(dev.lib.espdl_b200_copy(C.byref(d), None), "copy")
+        np.testing.assert_array_equal(dev.download(pt, t), a.transpose(0, 3, 1, 2))
+
+
+@pytest.mark.parametrize("odt,eo", [(abi.DTYPE_FLOAT, 0), (abi.DTYPE_INT8, -7), (abi.DTYPE_INT16, -15)])
+@pytest.mark.parametrize("e_in,rows,length", [(-4, 64, 400), (-3, 3, 37), (-6, 5, 64)])
+def test_softmax(e_in, rows, length, odt, eo):
+    rng = np.random.default_rng(19)
+    x = rng.integers(-128, 128, size=(rows, length), dtype=np.int8)
+    table = np.zeros(256, dtype=np.float32)
+    checkers.oracle().oracle_softmax_table(table.ctypes.data, e_in)
+    want = np.zeros((rows, length), dtype=cases.NP[odt])
+    assert checkers.oracle().oracle_softmax(cases.softmax_desc(x.ctypes.data, want.ctypes.data, table.ctypes.data, rows, length, odt, eo)) == 0
+    with gpu_util.DeviceBuffers() as dev:
+        px, pt, po = dev.upload(x), dev.upload(table), dev.upload(np.zeros_like(want))
+        d = cases.softmax_desc(px, po, pt, rows, length, odt, eo)
+        abi.check(dev.lib.espdl_b200_softmax(C.byref(d), None), "softmax")
+        got = dev.download(po, want)
+    np.testing.assert_array_equal(got.view(np.uint8), want.view(np.uint8))
+
+
+def test_invalid_arguments_are_rejected():
+    L = gpu_util.lib()
+    assert L.espdl_b200_conv2d(None, None) == abi.ERR_INVALID_ARG
+    case = cases.conv_case(seed=1)
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input=dev.upload(case["x"]), filter=dev.upload(case["w"]), bias=dev.upload(case["b"]), filter_exponents=None,
+                    lut=None, output=dev.upload(case["out"]))
+        bad = cases.conv_desc(dict(case, out_h=case["out_h"] + 1), ptrs)
+        assert L.espdl_b200_conv2d(C.byref(bad), None) == abi.ERR_INVALID_ARG
+        bad = cases.conv_desc(dict(case, activation=3), ptrs)
+        assert L.espdl_b200_conv2d(C.byref(bad), None) == abi.ERR_UNSUPPORTED
+        bad = cases.conv_desc(dict(case, per_channel=1), ptrs)
+        assert L.espdl_b200_conv2d(C.byref(bad), None) == abi.ERR_INVALID_ARG
+        empty = cases.conv_desc(dict(case, n=0), ptrs)
+        assert L.espdl_b200_conv2d(C.byref(empty), None) == abi.OK  # empty batch: nothing to do
+    assert b"invalid" in L.espdl_b200_strerror(abi.ERR_INVALID_ARG)

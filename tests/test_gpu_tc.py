@@ -1,0 +1,112 @@
+"""GPU parity of the tcgen05 tile kernel (pointwise conv / Gemm, int8 and int16) against the plain-C oracle,
+and replay of the reference's golden Gemm models through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+
+import cases
+import gpu_util
+from espdl_b200 import abi
+from test_golden_vectors import GEMM_FILES, replay_gemm_chain
+
+pytestmark = pytest.mark.gpu
+
+# (M, K, N): ragged M, every K swizzle width (32 / 64 / 128 byte rows, partial last K block),
+# N below / not a multiple of 16, N split over several tiles.
+TC_SHAPES = [
+    (128, 128, 128), (256, 64, 64), (100, 32, 32), (1, 16, 16), (300, 16, 96), (777, 96, 24), (130, 144, 32),
+    (257, 192, 32), (384, 32, 192), (50, 384, 64), (64, 576, 96), (33, 960, 160), (200, 320, 1280), (129, 1280, 1000),
+    (512, 160, 960), (90, 48, 17), (128, 256, 256), (1000, 64, 40),
+]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_gemm_s8_tc(shape):
+    m, k, n = shape
+    case = cases.gemm_case(seed=sum(shape), m=m, k=k, n_out=n, per_channel=True, e_in=-7, e_out=-5 + (k > 256), e_w=(-9, -6))
+    want = gpu_util.run_conv_oracle(case)
+    got = gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05)
+    np.testing.assert_array_equal(got, want)
+    assert want.std() > 0
+
+
+@pytest.mark.parametrize("round_mode", [abi.ROUND_HALF_UP, abi.ROUND_HALF_EVEN])
+@pytest.mark.parametrize("act", [abi.ACT_LINEAR, abi.ACT_RELU])
+def test_gemm_s8_tc_epilogue_variants(act, round_mode):
+    for per_channel, bias, lut in [(False, True, False), (True, False, False), (True, True, True)]:
+        case = cases.gemm_case(seed=5, m=300, k=64, n_out=48, per_channel=per_channel, bias=bias, lut=lut, act=act, round_mode=round_mode)
+        np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), gpu_util.run_conv_oracle(case))
+
+
+def test_pointwise_conv_tc_nhwc_and_strides():
+    """A 1x1 conv over an NHWC batch, reading a channel slice of a wider tensor and writing into a Concat slice."""
+    case = cases.conv_case(seed=7, n=3, h=14, w=14, cin=32, cout=64, kh=1, kw=1, pad=(0, 0, 0, 0), per_channel=True,
+                           in_stride=48, out_stride=96)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), gpu_util.run_conv_oracle(case))
+
+
+def test_tc_and_simt_agree_and_auto_picks_tc():
+    case = cases.gemm_case(seed=9, m=500, k=96, n_out=144, per_channel=True)
+    a = gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05)
+    b = gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT)
+    c = gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_AUTO)
+    np.testing.assert_array_equal(a, b)
+    np.testing.assert_array_equal(a, c)
+
+
+def test_tc_rejects_shapes_it_cannot_run():
+    case = cases.gemm_case(seed=9, m=64, k=24, n_out=16)  # K not a multiple of 16
+    gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05, expect=abi.ERR_UNSUPPORTED)
+    case = cases.conv_case(seed=9, cin=16, cout=16, kh=3, kw=3)
+    gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05, expect=abi.ERR_UNSUPPORTED)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(cases.gemm_case(seed=9, m=64, k=24, n_out=16)),
+                                  gpu_util.run_conv_oracle(cases.gemm_case(seed=9, m=64, k=24, n_out=16)))
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 128), (100, 64, 48), (300, 1024, 200), (64, 16, 16), (257, 144, 130)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_gemm_s16_tc(shape):
+    """int16 through 8-bit limbs: full-range operands, int64 bias, shift 17 (the int16 Gemm configuration's exponents)."""
+    m, k, n = shape
+    case = cases.gemm_case(seed=sum(shape), dtype=abi.DTYPE_INT16, m=m, k=k, n_out=n, e_in=-14, e_w=(-15, -15), e_out=-12, wide=True,
+                           bias_mag=1 << 20)
+    want = gpu_util.run_conv_oracle(case)
+    got = gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05)
+    np.testing.assert_array_equal(got, want)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT), want)
+    assert want.std() > 0
+
+
+def test_gemm_s16_tc_extreme_values():
+    """All operands at -32768 / 32767: the limb partial sums reach their largest magnitude."""
+    case = cases.gemm_case(seed=1, dtype=abi.DTYPE_INT16, m=130, k=2048, n_out=32, e_in=-14, e_w=(-15, -15), e_out=-2, wide=True)
+    case["x"][:] = -32768
+    case["w"][:] = -32768
+    case["x"][0, 0, 1::2] = 32767
+    case["w"][1::2] = 32767
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), gpu_util.run_conv_oracle(case))
+
+
+def test_config2_int8_gemm_full_size():
+    """int8 Gemm 4096x1024x1024, per-channel exponents in {-9..-6}, int32 bias, output exponent -5, no activation."""
+    case = cases.gemm_case(seed=2, m=4096, k=1024, n_out=1024, per_channel=True, e_in=-7, e_out=-5, e_w=(-9, -6))
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), want)
+    assert (np.abs(want.astype(np.int32)) < 127).mean() > 0.3
+
+
+def test_config2_int16_gemm_full_size():
+    """int16 variant: A/B over the full int16 range, exponents -14/-15, output exponent -12 (shift 17)."""
+    case = cases.gemm_case(seed=3, dtype=abi.DTYPE_INT16, m=4096, k=1024, n_out=1024, e_in=-14, e_w=(-15, -15), e_out=-12, wide=True,
+                           bias_mag=1 << 20)
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), want)
+
+
+@pytest.mark.parametrize("path", GEMM_FILES, ids=os.path.basename)
+def test_gpu_reproduces_golden_gemm(path):
+    mode = abi.ROUND_HALF_EVEN if "esp32p4" in os.path.basename(path) else abi.ROUND_HALF_UP
+    m, tensors = replay_gemm_chain(path, lambda case: gpu_util.run_conv_gpu(case), mode)
+    for name, t in m["test_outputs"].items():
+        np.testing.assert_array_equal(tensors[name].reshape(-1), t["data"].reshape(-1))
