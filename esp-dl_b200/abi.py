@@ -93,6 +93,16 @@ SYMBOLS = {
     "espdl_b200_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "espdl_b200_host_free": (C.c_int, [C.c_void_p]),
     "espdl_b200_launch_count": (C.c_uint64, []),
+    "espdl_b200_stream_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "espdl_b200_stream_destroy": (C.c_int, [C.c_void_p]),
+    "espdl_b200_event_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "espdl_b200_event_destroy": (C.c_int, [C.c_void_p]),
+    "espdl_b200_event_record": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "espdl_b200_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
+    "espdl_b200_graph_begin": (C.c_int, [C.c_void_p]),
+    "espdl_b200_graph_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "espdl_b200_graph_launch": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "espdl_b200_graph_destroy": (C.c_int, [C.c_void_p]),
     "espdl_b200_conv2d": (C.c_int, [C.POINTER(ConvDesc), C.c_void_p]),
     "espdl_b200_conv2d_workspace_bytes": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]),
     "espdl_b200_conv2d_ws": (C.c_int, [C.POINTER(ConvDesc), C.c_void_p, C.c_size_t, C.c_void_p]),

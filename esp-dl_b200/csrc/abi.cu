@@ -164,6 +164,95 @@ int espdl_b200_host_free(void *hptr)
 
 uint64_t espdl_b200_launch_count(void) { return g_launches.load(); }
 
+int espdl_b200_stream_create(void **stream)
+{
+    if (!stream)
+        return ESPDL_ERR_INVALID_ARG;
+    cudaStream_t s;
+    ESPDL_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream = (void *)s;
+    return ESPDL_OK;
+}
+
+int espdl_b200_stream_destroy(void *stream)
+{
+    if (stream)
+        ESPDL_CUDA_TRY(cudaStreamDestroy((cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
+int espdl_b200_event_create(void **event)
+{
+    if (!event)
+        return ESPDL_ERR_INVALID_ARG;
+    cudaEvent_t e;
+    ESPDL_CUDA_TRY(cudaEventCreate(&e));
+    *event = (void *)e;
+    return ESPDL_OK;
+}
+
+int espdl_b200_event_destroy(void *event)
+{
+    if (event)
+        ESPDL_CUDA_TRY(cudaEventDestroy((cudaEvent_t)event));
+    return ESPDL_OK;
+}
+
+int espdl_b200_event_record(void *event, void *stream)
+{
+    if (!event)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaEventRecord((cudaEvent_t)event, (cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
+int espdl_b200_event_elapsed_ms(void *start, void *stop, float *ms)
+{
+    if (!start || !stop || !ms)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaEventSynchronize((cudaEvent_t)stop));
+    ESPDL_CUDA_TRY(cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+    return ESPDL_OK;
+}
+
+int espdl_b200_graph_begin(void *stream)
+{
+    if (!stream)
+        return ESPDL_ERR_INVALID_ARG; // the legacy default stream cannot be captured
+    ESPDL_CUDA_TRY(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    return ESPDL_OK;
+}
+
+int espdl_b200_graph_end(void *stream, void **graph)
+{
+    if (!stream || !graph)
+        return ESPDL_ERR_INVALID_ARG;
+    cudaGraph_t g = nullptr;
+    ESPDL_CUDA_TRY(cudaStreamEndCapture((cudaStream_t)stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess)
+        return set_cuda_error(e, "cudaGraphInstantiate");
+    *graph = (void *)exec;
+    return ESPDL_OK;
+}
+
+int espdl_b200_graph_launch(void *graph, void *stream)
+{
+    if (!graph)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaGraphLaunch((cudaGraphExec_t)graph, (cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
+int espdl_b200_graph_destroy(void *graph)
+{
+    if (graph)
+        ESPDL_CUDA_TRY(cudaGraphExecDestroy((cudaGraphExec_t)graph));
+    return ESPDL_OK;
+}
+
 // ------------------------------------------------------------------ conv2d
 static int conv_validate(const espdl_conv_desc *d)
 {

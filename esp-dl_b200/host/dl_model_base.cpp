@@ -1,0 +1,632 @@
+#include "dl_model_base.hpp"
+#include "espdl_b200.h"
+
+#include <algorithm>
+#include <climits>
+#include <cstring>
+
+namespace dl {
+
+// ----------------------------------------------------------------------------- arena planner
+size_t MemoryManagerGreedy::plan(std::vector<TensorInfo> &tensors, bool reuse)
+{
+    constexpr size_t ALIGN = 256;
+    auto round_up = [](size_t v) { return (v + ALIGN - 1) / ALIGN * ALIGN; };
+    // a buffer lives as long as any tensor that aliases it
+    std::vector<int> root(tensors.size());
+    for (size_t i = 0; i < tensors.size(); i++) {
+        int r = (int)i;
+        while (tensors[r].alias_of >= 0) r = tensors[r].alias_of;
+        root[i] = r;
+    }
+    std::vector<int> last(tensors.size());
+    std::vector<size_t> bytes(tensors.size());
+    for (size_t i = 0; i < tensors.size(); i++) last[i] = tensors[i].last, bytes[i] = round_up(tensors[i].bytes);
+    for (size_t i = 0; i < tensors.size(); i++) {
+        last[root[i]] = std::max(last[root[i]], tensors[i].last);
+        bytes[root[i]] = std::max(bytes[root[i]], round_up(tensors[i].bytes));
+    }
+    struct Chunk {
+        size_t offset, size;
+    };
+    std::vector<Chunk> free_list;
+    size_t arena = 0;
+    // roots in order of first use; release buffers whose last reader is before the current step
+    std::vector<int> order;
+    for (size_t i = 0; i < tensors.size(); i++)
+        if (root[i] == (int)i)
+            order.push_back((int)i);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return tensors[a].first < tensors[b].first; });
+    std::vector<int> live;
+    for (int t : order) {
+        if (reuse) {
+            for (size_t k = 0; k < live.size();) {
+                if (last[live[k]] < tensors[t].first) {
+                    Chunk c{tensors[live[k]].offset, bytes[live[k]]};
+                    // coalesce with neighbours
+                    for (size_t f = 0; f < free_list.size();) {
+                        if (free_list[f].offset + free_list[f].size == c.offset) {
+                            c.offset = free_list[f].offset, c.size += free_list[f].size;
+                            free_list.erase(free_list.begin() + f);
+                        } else if (c.offset + c.size == free_list[f].offset) {
+                            c.size += free_list[f].size;
+                            free_list.erase(free_list.begin() + f);
+                        } else {
+                            f++;
+                        }
+                    }
+                    free_list.push_back(c);
+                    live.erase(live.begin() + k);
+                } else {
+                    k++;
+                }
+            }
+        }
+        // best fit
+        int best = -1;
+        for (size_t f = 0; f < free_list.size(); f++)
+            if (free_list[f].size >= bytes[t] && (best < 0 || free_list[f].size < free_list[best].size))
+                best = (int)f;
+        if (best >= 0) {
+            tensors[t].offset = free_list[best].offset;
+            if (free_list[best].size == bytes[t]) {
+                free_list.erase(free_list.begin() + best);
+            } else {
+                free_list[best].offset += bytes[t];
+                free_list[best].size -= bytes[t];
+            }
+        } else {
+            // grow: extend a free chunk that ends at the arena's end, else append
+            int tail = -1;
+            for (size_t f = 0; f < free_list.size(); f++)
+                if (free_list[f].offset + free_list[f].size == arena)
+                    tail = (int)f;
+            if (tail >= 0) {
+                tensors[t].offset = free_list[tail].offset;
+                arena = free_list[tail].offset + bytes[t];
+                free_list.erase(free_list.begin() + tail);
+            } else {
+                tensors[t].offset = arena;
+                arena += bytes[t];
+            }
+        }
+        live.push_back(t);
+    }
+    for (size_t i = 0; i < tensors.size(); i++)
+        if (root[i] != (int)i)
+            tensors[i].offset = tensors[root[i]].offset;
+    return arena;
+}
+
+// ----------------------------------------------------------------------------- model
+static bool env_flag(const char *name, bool def)
+{
+    const char *v = getenv(name);
+    return v ? (*v != '0') : def;
+}
+
+Model::Model(const char *path, fbs::model_location_type_t location, int max_internal_size, memory_manager_t mm_type, const uint8_t *key,
+             bool param_copy, const std::map<std::string, std::vector<int>> &input_shapes)
+{
+    m_use_graph = env_flag("ESPDL_B200_GRAPH", true);
+    if (load(path, location, 0, key, param_copy) == ESP_OK)
+        build(max_internal_size, mm_type, false, input_shapes);
+}
+
+Model::Model(const char *path, int model_index, fbs::model_location_type_t location, int max_internal_size, memory_manager_t mm_type,
+             const uint8_t *key, bool param_copy, const std::map<std::string, std::vector<int>> &input_shapes)
+{
+    m_use_graph = env_flag("ESPDL_B200_GRAPH", true);
+    if (load(path, location, model_index, key, param_copy) == ESP_OK)
+        build(max_internal_size, mm_type, false, input_shapes);
+}
+
+Model::Model(fbs::FbsModel *fbs_model, int internal_size, memory_manager_t mm_type, const std::map<std::string, std::vector<int>> &input_shapes)
+{
+    m_use_graph = env_flag("ESPDL_B200_GRAPH", true);
+    if (load(fbs_model) == ESP_OK)
+        build(internal_size, mm_type, false, input_shapes);
+}
+
+void Model::release()
+{
+    if (m_graph)
+        espdl_b200_graph_destroy(m_graph);
+    m_graph = nullptr;
+    for (auto *m : m_execution_plan) delete m;
+    m_execution_plan.clear();
+    if (m_model_context) {
+        for (auto &kv : m_inputs)
+            if (kv.second->data && !kv.second->auto_free) {
+                espdl_b200_host_free(kv.second->data);
+                kv.second->data = nullptr;
+            }
+        for (auto &kv : m_outputs)
+            if (kv.second->data && !kv.second->auto_free) {
+                espdl_b200_host_free(kv.second->data);
+                kv.second->data = nullptr;
+            }
+        if (m_model_context->workspace)
+            espdl_b200_arena_free(m_model_context->workspace);
+        if (m_model_context->stream)
+            espdl_b200_stream_destroy(m_model_context->stream);
+        delete m_model_context;
+        m_model_context = nullptr;
+    }
+    if (m_arena)
+        espdl_b200_arena_free(m_arena);
+    m_arena = nullptr;
+    m_inputs.clear();
+    m_outputs.clear();
+}
+
+Model::~Model()
+{
+    release();
+    if (m_own_fbs_model)
+        delete m_fbs_model;
+    delete m_fbs_loader;
+}
+
+esp_err_t Model::load(const char *path, fbs::model_location_type_t location, int model_index, const uint8_t *key, bool param_copy)
+{
+    m_fbs_loader = new fbs::FbsLoader(path, location);
+    fbs::FbsModel *m = m_fbs_loader->load(model_index, key, param_copy);
+    if (!m) {
+        ESP_LOGE("dl::Model", "Failed to load model.");
+        m_status = ESPDL_ERR_INVALID_ARG;
+        return ESP_FAIL;
+    }
+    m_own_fbs_model = true;
+    return load(m);
+}
+
+esp_err_t Model::load(fbs::FbsModel *fbs_model)
+{
+    m_fbs_model = fbs_model;
+    if (!fbs_model)
+        return ESP_FAIL;
+    m_name = fbs_model->get_model_name();
+    m_version = fbs_model->get_model_version();
+    m_doc_string = fbs_model->get_model_doc_string();
+    m_model_context = new ModelContext();
+    m_model_context->own_tensors = true;
+    // rounding follows the chip the model was exported for (esp-dl/dl/dl_define_private.hpp:44-48)
+    std::string target = fbs_model->get_model_metadata_prop("target");
+    if (const char *env = getenv("ESPDL_B200_TARGET"))
+        if (target.empty())
+            target = env;
+    m_model_context->round_mode = (target == "esp32p4" || target == "esp32s31") ? ROUND_HALF_EVEN : ROUND_HALF_UP;
+    if (const char *env = getenv("ESPDL_B200_ROUND"))
+        m_model_context->round_mode = strcmp(env, "half_even") == 0 ? ROUND_HALF_EVEN : ROUND_HALF_UP;
+
+    module::ModuleCreator *creator = module::ModuleCreator::get_instance();
+    for (const std::string &node : fbs_model->topological_sort()) {
+        const std::string op_type = fbs_model->get_operation_type(node);
+        module::Module *mod = creator->create(fbs_model, op_type, node);
+        if (!mod) {
+            ESP_LOGE("dl::Model", "Do not support operation %s (node %s)", op_type.c_str(), node.c_str());
+            m_status = ESPDL_ERR_UNSUPPORTED;
+            return ESP_FAIL;
+        }
+        std::vector<std::string> ins, outs;
+        fbs_model->get_operation_inputs_and_outputs(node, ins, outs);
+        // initializer inputs become parameter tensors of the context, created once per name
+        for (size_t i = 0; i < ins.size(); i++) {
+            if (fbs_model->is_parameter(ins[i]) && m_model_context->get_tensor_index(ins[i]) < 0) {
+                TensorBase *t = fbs_model->get_operation_parameter(node, (int)i);
+                if (t)
+                    m_model_context->push_back_tensor(t, ins[i]);
+            }
+        }
+        m_execution_plan.push_back(mod);
+        m_module_types.push_back(op_type);
+        m_module_inputs.push_back(ins);
+        m_module_outputs.push_back(outs);
+    }
+    return ESP_OK;
+}
+
+void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool preload, const std::map<std::string, std::vector<int>> &input_shapes)
+{
+    (void)max_internal_size;
+    (void)mm_type;
+    (void)preload;
+    if (!m_fbs_model || !m_model_context || m_built)
+        return;
+    ModelContext *ctx = m_model_context;
+    std::vector<TensorInfo> &infos = m_tensor_infos;
+    std::map<std::string, int> info_index;
+    auto add_info = [&](const std::string &name, const std::vector<int> &shape, int first) {
+        TensorInfo ti;
+        ti.name = name, ti.shape = shape, ti.first = first, ti.last = first;
+        ti.dtype = m_fbs_model->get_value_info_dtype(name);
+        if (ti.dtype == DATA_TYPE_UNDEFINED)
+            ti.dtype = DATA_TYPE_INT8;
+        ti.exponent = m_fbs_model->get_value_info_exponent(name);
+        size_t n = 1;
+        for (int d : shape) n *= (size_t)d;
+        ti.bytes = n * dtype_sizeof(ti.dtype);
+        infos.push_back(ti);
+        info_index[name] = (int)infos.size() - 1;
+        return (int)infos.size() - 1;
+    };
+    for (const std::string &name : m_fbs_model->get_graph_inputs()) {
+        std::vector<int> shape = m_fbs_model->get_value_info_shape(name);
+        auto it = input_shapes.find(name);
+        if (it != input_shapes.end())
+            shape = it->second;
+        infos[add_info(name, shape, -1)].is_graph_io = true;
+    }
+    // shape inference, lifetimes and in-place links along the plan
+    for (size_t step = 0; step < m_execution_plan.size(); step++) {
+        module::Module *mod = m_execution_plan[step];
+        std::vector<std::vector<int>> in_shapes;
+        for (const std::string &in : m_module_inputs[step]) {
+            auto it = info_index.find(in);
+            if (it != info_index.end()) {
+                in_shapes.push_back(infos[it->second].shape);
+                infos[it->second].last = std::max(infos[it->second].last, (int)step);
+            } else if (TensorBase *p = ctx->get_tensor(in)) {
+                in_shapes.push_back(p->shape);
+            } else {
+                in_shapes.push_back({});
+            }
+        }
+        std::vector<std::vector<int>> out_shapes = mod->get_output_shape(in_shapes);
+        for (size_t o = 0; o < m_module_outputs[step].size() && o < out_shapes.size(); o++)
+            add_info(m_module_outputs[step][o], out_shapes[o], (int)step);
+    }
+    for (const std::string &name : m_fbs_model->get_graph_outputs()) {
+        auto it = info_index.find(name);
+        if (it != info_index.end()) {
+            infos[it->second].last = INT_MAX;
+            infos[it->second].is_graph_io = true;
+        }
+    }
+    // In-place: a view (Reshape / Flatten / ...) always shares its input's buffer; a module that may overwrite an
+    // input (Add, LUT, RequantizeLinear, ...) takes the buffer of an input that dies at this step, is no graph
+    // input/output, is not shared through a view, and is large enough (dl_memory_manager_greedy.cpp:147-212).
+    if (m_reuse_memory) {
+        std::vector<bool> has_view(infos.size(), false);
+        for (size_t step = 0; step < m_execution_plan.size(); step++) {
+            module::Module *mod = m_execution_plan[step];
+            if (mod->inplace == MODULE_NON_INPLACE || m_module_outputs[step].size() != 1)
+                continue;
+            const int out = info_index[m_module_outputs[step][0]];
+            for (const std::string &in_name : m_module_inputs[step]) {
+                auto it = info_index.find(in_name);
+                if (it == info_index.end())
+                    continue;
+                TensorInfo &in = infos[it->second];
+                if (mod->inplace == MODULE_INPLACE_UNCHANGED_BUFFER) {
+                    if (!in.is_graph_io || infos[out].last != INT_MAX) {
+                        infos[out].alias_of = it->second;
+                        has_view[it->second] = true;
+                        int r = it->second;
+                        while (infos[r].alias_of >= 0) r = infos[r].alias_of;
+                        has_view[r] = true;
+                    }
+                    break;
+                }
+                int r = it->second;
+                while (infos[r].alias_of >= 0) r = infos[r].alias_of;
+                bool root_dies = true; // every tensor on this buffer must be dead after this step
+                for (size_t k = 0; k < infos.size(); k++) {
+                    int rk = (int)k;
+                    while (infos[rk].alias_of >= 0) rk = infos[rk].alias_of;
+                    if (rk == r && (int)k != out && infos[k].last > (int)step)
+                        root_dies = false;
+                }
+                if (root_dies && !in.is_graph_io && !infos[r].is_graph_io && !has_view[r] && infos[out].last != INT_MAX &&
+                    in.bytes >= infos[out].bytes) {
+                    infos[out].alias_of = it->second;
+                    break;
+                }
+            }
+        }
+    }
+    m_arena_bytes = MemoryManagerGreedy::plan(infos, m_reuse_memory);
+    if (espdl_b200_arena_alloc(m_arena_bytes + 256, &m_arena) != ESPDL_OK) {
+        ESP_LOGE("dl::Model", "Failed to allocate a %.1f MB device arena", m_arena_bytes / 1048576.0);
+        m_status = ESPDL_ERR_NO_MEM;
+        return;
+    }
+    espdl_b200_memset(m_arena, 0, m_arena_bytes, nullptr);
+    espdl_b200_stream_create(&ctx->stream);
+    for (TensorInfo &ti : infos) {
+        TensorBase *t = new TensorBase(ti.shape, nullptr, ti.exponent, ti.dtype, false);
+        t->device = (char *)m_arena + ti.offset;
+        if (ti.is_graph_io) { // pinned host buffer the user reads / writes
+            void *h = nullptr;
+            if (espdl_b200_host_alloc(t->get_aligned_bytes(), &h) == ESPDL_OK) {
+                memset(h, 0, t->get_aligned_bytes());
+                t->data = h;
+            }
+        }
+        ctx->push_back_tensor(t, ti.name);
+        if (ti.first < 0)
+            m_inputs[ti.name] = t;
+        else if (ti.last == INT_MAX)
+            m_outputs[ti.name] = t;
+    }
+    size_t ws = 0;
+    for (size_t step = 0; step < m_execution_plan.size(); step++) {
+        module::Module *mod = m_execution_plan[step];
+        mod->m_inputs_index.clear();
+        mod->m_outputs_index.clear();
+        for (const std::string &in : m_module_inputs[step]) mod->m_inputs_index.push_back(ctx->get_tensor_index(in));
+        for (const std::string &out : m_module_outputs[step]) mod->m_outputs_index.push_back(ctx->get_tensor_index(out));
+        if (mod->prepare(ctx) != ESP_OK) {
+            ESP_LOGE("dl::Model", "prepare failed for node %s", mod->name ? mod->name : "?");
+            m_status = ESPDL_ERR_CUDA;
+            return;
+        }
+        ws = std::max(ws, mod->workspace_bytes(ctx));
+    }
+    if (ws) {
+        if (espdl_b200_arena_alloc(ws, &ctx->workspace) != ESPDL_OK) {
+            m_status = ESPDL_ERR_NO_MEM;
+            return;
+        }
+        ctx->workspace_bytes = ws;
+    }
+    espdl_b200_stream_sync(nullptr);
+    m_built = true;
+}
+
+esp_err_t Model::execute(int first, int last)
+{
+    ModelContext *ctx = m_model_context;
+    for (int i = first; i < last; i++) {
+        m_execution_plan[i]->forward(ctx, RUNTIME_MODE_SINGLE_CORE);
+        if (ctx->status) {
+            m_status = ctx->status;
+            return ESP_FAIL;
+        }
+    }
+    return ESP_OK;
+}
+
+esp_err_t Model::run_device(bool sync)
+{
+    if (!m_built)
+        return ESP_FAIL;
+    ModelContext *ctx = m_model_context;
+    int st = ESPDL_OK;
+    if (m_use_graph) {
+        if (!m_graph) {
+            // one plain pass first (it also settles lazily created state), then capture the same launches
+            if (execute(0, (int)m_execution_plan.size()) != ESP_OK || espdl_b200_stream_sync(ctx->stream) != ESPDL_OK)
+                return ESP_FAIL;
+            st = espdl_b200_graph_begin(ctx->stream);
+            if (!st) {
+                esp_err_t e = execute(0, (int)m_execution_plan.size());
+                st = espdl_b200_graph_end(ctx->stream, &m_graph);
+                if (e != ESP_OK)
+                    st = m_status;
+            }
+            if (st) {
+                m_status = st;
+                return ESP_FAIL;
+            }
+        }
+        st = espdl_b200_graph_launch(m_graph, ctx->stream);
+    } else if (execute(0, (int)m_execution_plan.size()) != ESP_OK) {
+        return ESP_FAIL;
+    }
+    if (!st && sync)
+        st = espdl_b200_stream_sync(ctx->stream);
+    if (st)
+        m_status = st;
+    return st ? ESP_FAIL : ESP_OK;
+}
+
+void Model::run(runtime_mode_t mode)
+{
+    (void)mode;
+    if (!m_built)
+        return;
+    ModelContext *ctx = m_model_context;
+    for (auto &kv : m_inputs)
+        if (kv.second->data)
+            espdl_b200_upload(kv.second->device, kv.second->data, kv.second->get_bytes(), ctx->stream);
+    if (run_device(false) != ESP_OK)
+        return;
+    for (auto &kv : m_outputs)
+        if (kv.second->data)
+            espdl_b200_download(kv.second->data, kv.second->device, kv.second->get_bytes(), ctx->stream);
+    int st = espdl_b200_stream_sync(ctx->stream);
+    if (st)
+        m_status = st;
+}
+
+void Model::run(TensorBase *input, runtime_mode_t mode)
+{
+    if (m_inputs.size() != 1 || !input)
+        return;
+    m_inputs.begin()->second->assign(input); // copy / quantise into the graph input, as the reference does
+    run(mode);
+}
+
+void Model::run(std::map<std::string, TensorBase *> &user_inputs, runtime_mode_t mode, std::map<std::string, TensorBase *> user_outputs)
+{
+    for (auto &kv : user_inputs) {
+        TensorBase *t = get_input(kv.first);
+        if (t)
+            t->assign(kv.second);
+    }
+    run(mode);
+    for (auto &kv : user_outputs) {
+        TensorBase *t = get_intermediate(kv.first);
+        if (t && kv.second && kv.second->data && t->device) {
+            espdl_b200_download(kv.second->data, t->device, std::min(kv.second->get_bytes(), t->get_bytes()), m_model_context->stream);
+            espdl_b200_stream_sync(m_model_context->stream);
+        }
+    }
+}
+
+void Model::run(int stage_num, int stage_index, runtime_mode_t mode)
+{
+    (void)mode;
+    if (!m_built || stage_num <= 0 || stage_index < 0 || stage_index >= stage_num)
+        return;
+    ModelContext *ctx = m_model_context;
+    const int n = (int)m_execution_plan.size();
+    const int per = (n + stage_num - 1) / stage_num;
+    const int first = stage_index * per, last = std::min(n, first + per);
+    if (stage_index == 0)
+        for (auto &kv : m_inputs)
+            if (kv.second->data)
+                espdl_b200_upload(kv.second->device, kv.second->data, kv.second->get_bytes(), ctx->stream);
+    execute(first, last);
+    if (stage_index == stage_num - 1)
+        for (auto &kv : m_outputs)
+            if (kv.second->data)
+                espdl_b200_download(kv.second->data, kv.second->device, kv.second->get_bytes(), ctx->stream);
+    espdl_b200_stream_sync(ctx->stream);
+}
+
+// The model's own golden check (esp-dl/dl/model/src/dl_model_base.cpp:442-519): feed the embedded test inputs,
+// run module by module, compare every output that has an embedded expected value.
+esp_err_t Model::test()
+{
+    if (!m_built)
+        return ESP_FAIL;
+    ModelContext *ctx = m_model_context;
+    for (auto &kv : m_inputs) {
+        TensorBase *t = m_fbs_model->get_test_input_tensor(kv.first);
+        if (!t) {
+            ESP_LOGE("dl::Model", "Model input %s doesn't have a corresponding test input.", kv.first.c_str());
+            return ESP_FAIL;
+        }
+        const bool ok = t->get_bytes() == kv.second->get_bytes();
+        if (ok) {
+            memcpy(kv.second->data, t->data, t->get_bytes());
+            espdl_b200_upload(kv.second->device, kv.second->data, kv.second->get_bytes(), ctx->stream);
+        }
+        delete t;
+        if (!ok) {
+            ESP_LOGE("dl::Model", "test input %s does not match the (batch-overridden?) input shape", kv.first.c_str());
+            return ESP_FAIL;
+        }
+    }
+    esp_err_t result = ESP_OK;
+    for (size_t step = 0; step < m_execution_plan.size(); step++) {
+        if (execute((int)step, (int)step + 1) != ESP_OK)
+            return ESP_FAIL;
+        for (const std::string &out_name : m_module_outputs[step]) {
+            TensorBase *expect = m_fbs_model->get_test_output_tensor(out_name);
+            if (!expect)
+                continue;
+            TensorBase *got_dev = ctx->get_tensor(out_name);
+            TensorBase got(got_dev->shape, nullptr, (int)got_dev->exponent, got_dev->dtype, true);
+            espdl_b200_download(got.data, got_dev->device, got.get_bytes(), ctx->stream);
+            espdl_b200_stream_sync(ctx->stream);
+            if (!got.equal(expect, 2e-5f, true)) {
+                ESP_LOGE("dl::Model", "Test failed for output %s of %s", out_name.c_str(), m_module_types[step].c_str());
+                result = ESP_FAIL;
+            }
+            delete expect;
+        }
+    }
+    if (espdl_b200_stream_sync(ctx->stream) != ESPDL_OK)
+        return ESP_FAIL;
+    return result;
+}
+
+std::map<std::string, module_info> Model::get_module_info()
+{
+    std::map<std::string, module_info> info;
+    if (!m_built)
+        return info;
+    ModelContext *ctx = m_model_context;
+    void *e0 = nullptr, *e1 = nullptr;
+    espdl_b200_event_create(&e0);
+    espdl_b200_event_create(&e1);
+    execute(0, (int)m_execution_plan.size()); // warm up
+    espdl_b200_stream_sync(ctx->stream);
+    for (size_t step = 0; step < m_execution_plan.size(); step++) {
+        float best = 1e30f;
+        for (int rep = 0; rep < 3; rep++) {
+            espdl_b200_event_record(e0, ctx->stream);
+            execute((int)step, (int)step + 1);
+            espdl_b200_event_record(e1, ctx->stream);
+            float ms = 0;
+            espdl_b200_event_elapsed_ms(e0, e1, &ms);
+            best = std::min(best, ms);
+        }
+        char key[32];
+        snprintf(key, sizeof(key), "%04d:", (int)step);
+        module_info mi;
+        mi.type = m_module_types[step];
+        mi.latency_us = best * 1000.f;
+        info[std::string(key) + (m_execution_plan[step]->name ? m_execution_plan[step]->name : "")] = mi;
+    }
+    espdl_b200_event_destroy(e0);
+    espdl_b200_event_destroy(e1);
+    return info;
+}
+
+void Model::profile_module(bool sort_module_by_latency)
+{
+    auto info = get_module_info();
+    std::vector<std::pair<std::string, module_info>> rows(info.begin(), info.end());
+    if (sort_module_by_latency)
+        std::sort(rows.begin(), rows.end(), [](auto &a, auto &b) { return a.second.latency_us > b.second.latency_us; });
+    float total = 0;
+    printf("%-72s %-20s %12s\n", "name", "type", "latency(us)");
+    for (auto &r : rows) {
+        printf("%-72s %-20s %12.1f\n", r.first.c_str(), r.second.type.c_str(), r.second.latency_us);
+        total += r.second.latency_us;
+    }
+    printf("%-72s %-20s %12.1f\n", "total", "", total);
+}
+
+void Model::profile_memory()
+{
+    size_t params = 0;
+    for (auto *t : m_model_context->m_variables)
+        if (t && t->device_owned)
+            params += t->get_aligned_bytes();
+    printf("device arena (activations): %.2f MB\nparameters on device: %.2f MB\nflatbuffers model: %.2f MB\nscratch: %.2f MB\n",
+           m_arena_bytes / 1048576.0, params / 1048576.0, m_fbs_model ? m_fbs_model->get_size() / 1048576.0 : 0.0,
+           m_model_context->workspace_bytes / 1048576.0);
+}
+
+void Model::profile(bool sort_module_by_latency)
+{
+    profile_memory();
+    profile_module(sort_module_by_latency);
+}
+
+TensorBase *Model::get_input(const std::string &name)
+{
+    auto it = m_inputs.find(name);
+    return it == m_inputs.end() ? nullptr : it->second;
+}
+
+TensorBase *Model::get_output(const std::string &name)
+{
+    auto it = m_outputs.find(name);
+    return it == m_outputs.end() ? nullptr : it->second;
+}
+
+TensorBase *Model::get_intermediate(const std::string &name) { return m_model_context ? m_model_context->get_tensor(name) : nullptr; }
+
+std::string Model::get_metadata_prop(const std::string &key) { return m_fbs_model ? m_fbs_model->get_model_metadata_prop(key) : ""; }
+
+void Model::print()
+{
+    for (size_t i = 0; i < m_execution_plan.size(); i++) {
+        fprintf(stderr, "%3d %-18s %s\n", (int)i, m_module_types[i].c_str(), m_execution_plan[i]->name ? m_execution_plan[i]->name : "");
+        m_execution_plan[i]->print();
+    }
+}
+
+void Model::reset()
+{
+    for (auto *m : m_execution_plan) m->reset();
+}
+
+} // namespace dl

@@ -1,0 +1,1085 @@
+#include "dl_module_ops.hpp"
+#include "espdl_b200.h"
+
+#include <cassert>
+#include <cmath>
+#include <cstring>
+
+namespace dl {
+
+ModelContext::~ModelContext()
+{
+    if (own_tensors)
+        for (auto *t : m_variables) delete t;
+}
+
+int ModelContext::push_back_tensor(TensorBase *t, const std::string &name)
+{
+    m_variables.push_back(t);
+    if (!name.empty())
+        m_name2index[name] = (int)m_variables.size() - 1;
+    return (int)m_variables.size() - 1;
+}
+
+TensorBase *ModelContext::get_tensor(const std::string &name)
+{
+    auto it = m_name2index.find(name);
+    return it == m_name2index.end() ? nullptr : m_variables[it->second];
+}
+
+int ModelContext::get_tensor_index(const std::string &name)
+{
+    auto it = m_name2index.find(name);
+    return it == m_name2index.end() ? -1 : it->second;
+}
+
+namespace module {
+
+Module::Module(const char *n, module_inplace_t inplace, quant_type_t quant_type) : inplace(inplace), quant_type(quant_type)
+{
+    name = n ? strdup(n) : nullptr;
+}
+
+Module::~Module() { free(name); }
+
+void Module::run(TensorBase *input, TensorBase *output, runtime_mode_t mode) { run(std::vector<TensorBase *>{input}, {output}, mode); }
+
+void Module::run(std::vector<TensorBase *> inputs, std::vector<TensorBase *> outputs, runtime_mode_t mode)
+{
+    ModelContext context;
+    m_inputs_index.clear();
+    m_outputs_index.clear();
+    for (auto *t : inputs) m_inputs_index.push_back(context.push_back_tensor(t));
+    for (auto *t : outputs) m_outputs_index.push_back(context.push_back_tensor(t));
+    prepare(&context);
+    size_t ws = workspace_bytes(&context);
+    if (ws && espdl_b200_arena_alloc(ws, &context.workspace) == ESPDL_OK)
+        context.workspace_bytes = ws;
+    forward(&context, mode);
+    espdl_b200_stream_sync(nullptr);
+    if (context.workspace)
+        espdl_b200_arena_free(context.workspace);
+}
+
+static int espdl_dtype(TensorBase *t) { return (int)t->dtype; }
+static int quant_dtype(quant_type_t q) { return q == QUANT_TYPE_SYMM_16BIT ? ESPDL_DTYPE_INT16 : ESPDL_DTYPE_INT8; }
+
+// --------------------------------------------------------------------------------- Conv / Gemm
+Conv::Conv(activation_type_t activation, std::vector<int> pads, std::vector<int> dilations, std::vector<int> strides, const char *name,
+           const int group, quant_type_t quant_type, const std::string &target) :
+    Module(name, MODULE_NON_INPLACE, quant_type), m_dilations(dilations), m_strides(strides), m_group(group), activation(activation),
+    m_pads(pads), m_target(target)
+{
+    if (m_pads.empty())
+        m_pads = {0, 0, 0, 0};
+    if (m_strides.empty())
+        m_strides = {1, 1};
+    if (m_dilations.empty())
+        m_dilations = {1, 1};
+}
+
+Conv::~Conv()
+{
+    if (m_dev_exponents)
+        espdl_b200_arena_free(m_dev_exponents);
+}
+
+std::vector<std::vector<int>> Conv::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    // esp-dl/dl/module/include/dl_module_conv.hpp:81-102
+    std::vector<int> in = input_shapes[0], f = input_shapes[1], out = in;
+    if (in.size() == 3) { // conv1d: [N, W, C], filter [K, Cin, Cout]
+        out[1] = (in[1] + m_pads[0] + m_pads[1] - m_dilations[0] * (f[0] - 1) - 1) / m_strides[0] + 1;
+        out[2] = m_group == 1 ? f[2] : in[2];
+    } else {
+        out[1] = (in[1] + m_pads[0] + m_pads[1] - m_dilations[0] * (f[0] - 1) - 1) / m_strides[0] + 1;
+        out[2] = (in[2] + m_pads[2] + m_pads[3] - m_dilations[1] * (f[1] - 1) - 1) / m_strides[1] + 1;
+        out[3] = m_group == 1 ? f[3] : in[3];
+    }
+    return {out};
+}
+
+// Filter payloads are stored per export target although the declared shape is always [KH,KW,Cin,Cout]
+// (esp-dl/dl/base/dl_base_conv2d.cpp:23-32,140-162; esp-dl/dl/base/dl_base.hpp:305-310,1255-1262):
+//   "c"       dense [Cout][KH][KW][Cin], depthwise [KH][KW][C]
+//   p4 / s3   dense [Cout/u][KH][KW][Cin][u] + tail [Cout%u][KH][KW][Cin]; depthwise [C/u][KH][KW][u] + tail [KH][KW][C%u]
+// with u = 16 bytes / element size.  The kernels take the "c" order.
+template <typename T> static void relayout_filter(T *data, int kh, int kw, int cin, int cout, bool depthwise)
+{
+    const int u = 16 / (int)sizeof(T);
+    std::vector<T> src(data, data + (size_t)kh * kw * cin * (depthwise ? 1 : cout));
+    if (!depthwise) {
+        const int nb = cout / u;
+        const size_t per = (size_t)kh * kw * cin;
+        for (int o = 0; o < cout; o++)
+            for (size_t r = 0; r < per; r++) {
+                size_t s = o < nb * u ? ((size_t)(o / u) * per + r) * u + (o % u) : (size_t)nb * u * per + (size_t)(o - nb * u) * per + r;
+                data[(size_t)o * per + r] = src[s];
+            }
+    } else {
+        const int c = cin, nb = c / u, hw = kh * kw;
+        for (int p = 0; p < hw; p++)
+            for (int ch = 0; ch < c; ch++) {
+                size_t s = ch < nb * u ? ((size_t)(ch / u) * hw + p) * u + (ch % u) : (size_t)nb * u * hw + (size_t)p * (c % u) + (ch - nb * u);
+                data[(size_t)p * c + ch] = src[s];
+            }
+    }
+}
+
+esp_err_t Conv::prepare(ModelContext *context)
+{
+    if (m_prepared)
+        return ESP_OK;
+    m_prepared = true;
+    TensorBase *filter = context->get_tensor(m_inputs_index[1]);
+    if (!filter)
+        return ESP_FAIL;
+    std::vector<int> fs = filter->shape;
+    if (fs.size() == 3)
+        fs.insert(fs.begin(), 1); // conv1d filter [K, Cin, Cout] -> [1, K, Cin, Cout]
+    if (fs.size() != 4)
+        return ESP_FAIL;
+    const bool dw = m_group != 1;
+    if (m_target != "c" && !m_target.empty() && filter->data && !filter->device) {
+        if (!filter->auto_free) {
+            ESP_LOGE("Conv", "filter of %s aliases the model bytes; load with param_copy=true to re-order it", name ? name : "?");
+            return ESP_FAIL;
+        }
+        if (filter->dtype == DATA_TYPE_INT8)
+            relayout_filter((int8_t *)filter->data, fs[0], fs[1], fs[2], fs[3], dw);
+        else if (filter->dtype == DATA_TYPE_INT16)
+            relayout_filter((int16_t *)filter->data, fs[0], fs[1], fs[2], fs[3], dw);
+    }
+    if (filter->exponent.is_per_channel() && !m_dev_exponents) {
+        std::vector<int32_t> e(filter->exponent.values().begin(), filter->exponent.values().end());
+        if (espdl_b200_arena_alloc(e.size() * 4, &m_dev_exponents) != ESPDL_OK)
+            return ESP_FAIL;
+        if (espdl_b200_upload(m_dev_exponents, e.data(), e.size() * 4, nullptr) != ESPDL_OK || espdl_b200_stream_sync(nullptr) != ESPDL_OK)
+            return ESP_FAIL;
+    }
+    for (size_t i = 1; i < m_inputs_index.size(); i++) {
+        TensorBase *t = context->get_tensor(m_inputs_index[i]);
+        if (t && !t->device && t->to_device() != ESP_OK)
+            return ESP_FAIL;
+    }
+    if (m_lut && !m_lut->device && m_lut->to_device() != ESP_OK)
+        return ESP_FAIL;
+    return espdl_b200_stream_sync(nullptr) == ESPDL_OK ? ESP_OK : ESP_FAIL;
+}
+
+int Conv::fill_desc(ModelContext *context, void *desc)
+{
+    espdl_conv_desc &d = *(espdl_conv_desc *)desc;
+    memset(&d, 0, sizeof(d));
+    TensorBase *input = context->get_tensor(m_inputs_index[0]);
+    TensorBase *filter = context->get_tensor(m_inputs_index[1]);
+    TensorBase *bias = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
+    TensorBase *output = context->get_tensor(m_outputs_index[0]);
+    if (!input || !filter || !output || !input->device || !filter->device || !output->device)
+        return ESPDL_ERR_INVALID_ARG;
+    d.input = input->device, d.filter = filter->device, d.bias = bias ? bias->device : nullptr, d.output = output->device;
+    d.filter_exponents = (const int32_t *)m_dev_exponents;
+    d.lut = m_lut ? (const int8_t *)m_lut->device : nullptr;
+    d.dtype = quant_dtype(quant_type);
+    std::vector<int> fs = filter->shape;
+    if (m_gemm) {
+        // esp-dl/dl/module/include/dl_module_gemm.hpp:96-99: every leading dim folds into rows
+        const int k = input->shape.back();
+        d.n = 1, d.in_h = 1, d.in_w = input->get_size() / k, d.in_c = k;
+        d.out_h = 1, d.out_w = d.in_w, d.out_c = fs[3];
+        d.kh = d.kw = 1, d.stride_h = d.stride_w = d.dilation_h = d.dilation_w = 1;
+        d.group = 1;
+    } else if (input->shape.size() == 4) {
+        d.n = input->shape[0], d.in_h = input->shape[1], d.in_w = input->shape[2], d.in_c = input->shape[3];
+        d.out_h = output->shape[1], d.out_w = output->shape[2], d.out_c = output->shape[3];
+        d.kh = fs[0], d.kw = fs[1];
+        d.stride_h = m_strides[0], d.stride_w = m_strides[1], d.dilation_h = m_dilations[0], d.dilation_w = m_dilations[1];
+        d.pad_top = m_pads[0], d.pad_bottom = m_pads[1], d.pad_left = m_pads[2], d.pad_right = m_pads[3];
+        d.group = m_group == 1 ? 1 : d.in_c;
+    } else if (input->shape.size() == 3) { // conv1d: esp-dl/dl/base/dl_base.hpp:150-182
+        d.n = input->shape[0], d.in_h = 1, d.in_w = input->shape[1], d.in_c = input->shape[2];
+        d.out_h = 1, d.out_w = output->shape[1], d.out_c = output->shape[2];
+        d.kh = 1, d.kw = fs[0];
+        d.stride_h = 1, d.stride_w = m_strides[0], d.dilation_h = 1, d.dilation_w = m_dilations[0];
+        d.pad_left = m_pads[0], d.pad_right = m_pads[1];
+        d.group = m_group == 1 ? 1 : d.in_c;
+    } else {
+        return ESPDL_ERR_UNSUPPORTED;
+    }
+    d.in_exponent = input->exponent, d.out_exponent = output->exponent;
+    d.per_channel = filter->exponent.is_per_channel();
+    d.filter_exponent = filter->exponent;
+    d.activation = activation == ReLU ? ESPDL_ACT_RELU : ESPDL_ACT_LINEAR;
+    d.round_mode = context->round_mode;
+    d.kernel = ESPDL_KERNEL_AUTO;
+    if (activation != Linear && activation != ReLU)
+        return ESPDL_ERR_UNSUPPORTED;
+    return ESPDL_OK;
+}
+
+size_t Conv::workspace_bytes(ModelContext *context)
+{
+    espdl_conv_desc d;
+    size_t bytes = 0;
+    if (fill_desc(context, &d) == ESPDL_OK)
+        espdl_b200_conv2d_workspace_bytes(&d, &bytes);
+    return bytes;
+}
+
+void Conv::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    espdl_conv_desc d;
+    int st = fill_desc(context, &d);
+    if (st == ESPDL_OK)
+        st = espdl_b200_conv2d_ws(&d, context->workspace, context->workspace_bytes, context->stream);
+    if (st)
+        ESP_LOGE("Conv", "%s failed: %s %s", name ? name : "?", espdl_b200_strerror(st), espdl_b200_last_error());
+    context->note(st);
+}
+
+static std::string model_target(fbs::FbsModel *m)
+{
+    std::string t = m->get_model_metadata_prop("target");
+    if (t.empty()) {
+        const char *env = getenv("ESPDL_B200_TARGET"); // exports without a target tag (the model zoo) are SIMD-layout files
+        t = env ? env : "esp32p4";
+    }
+    return t;
+}
+
+Module *Conv::deserialize(fbs::FbsModel *fbs_model, std::string node_name)
+{
+    std::vector<int> pads, strides, dilations;
+    int group = 1;
+    activation_type_t activation_type = Linear;
+    quant_type_t quant_type = QUANT_TYPE_NONE;
+    fbs_model->get_operation_attribute(node_name, "pads", pads);
+    fbs_model->get_operation_attribute(node_name, "strides", strides);
+    fbs_model->get_operation_attribute(node_name, "dilations", dilations);
+    fbs_model->get_operation_attribute(node_name, "group", group);
+    fbs_model->get_operation_attribute(node_name, "activation", activation_type);
+    fbs_model->get_operation_attribute(node_name, "quant_type", quant_type);
+    if (quant_type != QUANT_TYPE_SYMM_8BIT && quant_type != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    if (pads.size() == 4)
+        pads = {pads[0], pads[2], pads[1], pads[3]}; // ONNX [t,l,b,r] -> [t,b,l,r] (dl_module_conv.hpp:186-187)
+    else if (pads.empty())
+        pads = {0, 0, 0, 0};
+    return new Conv(activation_type, pads, dilations, strides, node_name.c_str(), group, quant_type, model_target(fbs_model));
+}
+
+void Conv::print()
+{
+    ESP_LOGI("Conv", "pads %s strides %s dilations %s group %d activation %s quant %s", vector_to_string(m_pads).c_str(),
+             vector_to_string(m_strides).c_str(), vector_to_string(m_dilations).c_str(), m_group, activation_type_to_string(activation),
+             quant_type_to_string(quant_type));
+}
+
+Gemm::Gemm(activation_type_t activation, const char *name, quant_type_t quant_type, const std::string &target) :
+    Conv(activation, {0, 0, 0, 0}, {1, 1}, {1, 1}, name, 1, quant_type, target)
+{
+    m_gemm = true;
+}
+
+std::vector<std::vector<int>> Gemm::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> f = input_shapes[1];
+    assert(f.size() == 4 && f[0] == 1 && f[1] == 1);
+    assert(input_shapes[0].back() == f[2]);
+    std::vector<int> out = input_shapes[0];
+    out.back() = f[3];
+    return {out};
+}
+
+Module *Gemm::deserialize(fbs::FbsModel *fbs_model, std::string node_name)
+{
+    activation_type_t activation_type = Linear;
+    quant_type_t quant_type = QUANT_TYPE_NONE;
+    int transA = -1, transB = -1;
+    fbs_model->get_operation_attribute(node_name, "activation", activation_type);
+    fbs_model->get_operation_attribute(node_name, "quant_type", quant_type);
+    fbs_model->get_operation_attribute(node_name, "transA", transA);
+    fbs_model->get_operation_attribute(node_name, "transB", transB);
+    if ((transA != -1 && transA != 0) || (transB != -1 && transB != 0))
+        return nullptr;
+    if (quant_type != QUANT_TYPE_SYMM_8BIT && quant_type != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    return new Gemm(activation_type, node_name.c_str(), quant_type, model_target(fbs_model));
+}
+
+// --------------------------------------------------------------------------------- elementwise
+static std::vector<int> broadcast_shape(const std::vector<int> &a, const std::vector<int> &b)
+{
+    const size_t n = std::max(a.size(), b.size());
+    std::vector<int> out(n);
+    for (size_t i = 0; i < n; i++) {
+        const int da = i < n - a.size() ? 1 : a[i - (n - a.size())];
+        const int db = i < n - b.size() ? 1 : b[i - (n - b.size())];
+        out[i] = std::max(da, db);
+    }
+    return out;
+}
+
+std::vector<std::vector<int>> Elementwise::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    return {broadcast_shape(input_shapes[0], input_shapes[1])};
+}
+
+// Shapes with more than four axes are merged from the right where both operands are dense.
+static bool pack_shapes(const std::vector<int> &out, const std::vector<int> &a, const std::vector<int> &b, espdl_eltwise_desc &d)
+{
+    const size_t n = out.size();
+    std::vector<int> o(out), x(n, 1), y(n, 1);
+    for (size_t i = 0; i < a.size(); i++) x[n - a.size() + i] = a[i];
+    for (size_t i = 0; i < b.size(); i++) y[n - b.size() + i] = b[i];
+    // drop unit axes, then merge neighbours on which both operands broadcast the same way
+    std::vector<int> mo, mx, my;
+    for (size_t i = 0; i < n; i++) {
+        if (o[i] == 1)
+            continue;
+        const bool fx = x[i] == o[i], fy = y[i] == o[i];
+        if (!mo.empty() && (mx.back() == mo.back()) == fx && (my.back() == mo.back()) == fy) {
+            mo.back() *= o[i], mx.back() *= x[i], my.back() *= y[i];
+        } else {
+            mo.push_back(o[i]), mx.push_back(x[i]), my.push_back(y[i]);
+        }
+    }
+    if (mo.empty())
+        mo = {1}, mx = {1}, my = {1};
+    if (mo.size() > 4)
+        return false;
+    d.ndim = (int)mo.size();
+    for (size_t i = 0; i < mo.size(); i++) d.out_shape[i] = mo[i], d.in0_shape[i] = mx[i], d.in1_shape[i] = my[i];
+    return true;
+}
+
+void Elementwise::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *a = context->get_tensor(m_inputs_index[0]), *b = context->get_tensor(m_inputs_index[1]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    espdl_eltwise_desc d;
+    memset(&d, 0, sizeof(d));
+    int st = ESPDL_OK;
+    if (!a || !b || !out || !a->device || !b->device || !out->device)
+        st = ESPDL_ERR_INVALID_ARG;
+    if (!st && !pack_shapes(out->shape, a->shape, b->shape, d))
+        st = ESPDL_ERR_UNSUPPORTED;
+    if (!st) {
+        d.input0 = a->device, d.input1 = b->device, d.output = out->device;
+        d.op = m_op, d.in_dtype = espdl_dtype(a), d.out_dtype = espdl_dtype(out);
+        d.in0_exponent = a->exponent, d.in1_exponent = b->exponent, d.out_exponent = out->exponent;
+        d.round_mode = context->round_mode;
+        st = espdl_b200_eltwise(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Elementwise", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Add::Add(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Elementwise(ESPDL_ELT_ADD, name, inplace, quant_type) {}
+Sub::Sub(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Elementwise(ESPDL_ELT_SUB, name, inplace, quant_type) {}
+Mul::Mul(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Elementwise(ESPDL_ELT_MUL, name, inplace, quant_type) {}
+
+static quant_type_t node_quant(fbs::FbsModel *m, const std::string &node)
+{
+    quant_type_t q = QUANT_TYPE_NONE;
+    m->get_operation_attribute(node, "quant_type", q);
+    return q;
+}
+
+Module *Add::deserialize(fbs::FbsModel *m, std::string node) { return new Add(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node)); }
+Module *Sub::deserialize(fbs::FbsModel *m, std::string node) { return new Sub(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node)); }
+Module *Mul::deserialize(fbs::FbsModel *m, std::string node) { return new Mul(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node)); }
+
+esp_err_t Unary::prepare(ModelContext *context)
+{
+    (void)context;
+    if (m_param && !m_param->device) {
+        if (m_param->to_device() != ESP_OK || espdl_b200_stream_sync(nullptr) != ESPDL_OK)
+            return ESP_FAIL;
+    }
+    return ESP_OK;
+}
+
+void Unary::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    espdl_eltwise_desc d;
+    memset(&d, 0, sizeof(d));
+    int st = ESPDL_OK;
+    if (!in || !out || !in->device || !out->device)
+        st = ESPDL_ERR_INVALID_ARG;
+    if (!st) {
+        d.input0 = in->device, d.output = out->device;
+        d.input1 = m_param ? m_param->device : nullptr;
+        d.op = m_op, d.in_dtype = espdl_dtype(in), d.out_dtype = espdl_dtype(out);
+        d.in0_exponent = in->exponent, d.out_exponent = out->exponent;
+        d.in1_exponent = m_param ? (int)m_param->exponent : 0;
+        d.clip_lo = m_clip_lo, d.clip_hi = m_clip_hi;
+        d.round_mode = context->round_mode;
+        if (m_op == ESPDL_ELT_PRELU && in->shape.size() <= 4) {
+            d.ndim = (int)in->shape.size();
+            for (int i = 0; i < d.ndim; i++) d.out_shape[i] = d.in0_shape[i] = in->shape[i], d.in1_shape[i] = 1;
+        } else {
+            d.ndim = 1;
+            d.out_shape[0] = d.in0_shape[0] = in->get_size();
+            d.in1_shape[0] = 1;
+        }
+        st = espdl_b200_eltwise(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Unary", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+RequantizeLinear::RequantizeLinear(const char *name, module_inplace_t inplace, quant_type_t quant_type) :
+    Unary(ESPDL_ELT_REQUANTIZE, name, inplace, quant_type)
+{
+}
+Module *RequantizeLinear::deserialize(fbs::FbsModel *m, std::string node)
+{
+    return new RequantizeLinear(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node));
+}
+
+LUT::LUT(const char *name, TensorBase *table, module_inplace_t inplace, quant_type_t quant_type) :
+    Unary(ESPDL_ELT_LUT, name, inplace, quant_type, table)
+{
+}
+// LUT nodes and every activation exported with a `lut` attribute (Swish, Sigmoid, Tanh, HardSwish, Gelu, ...)
+// (esp-dl/dl/module/include/dl_module_swish.hpp:84-103).
+Module *LUT::deserialize(fbs::FbsModel *m, std::string node)
+{
+    quant_type_t q = node_quant(m, node);
+    if (q != QUANT_TYPE_SYMM_8BIT)
+        return nullptr; // the 16-bit nearest-neighbour table and the float fall-backs are not on this path
+    TensorBase *table = m->get_operation_lut(node);
+    if (!table)
+        return nullptr;
+    if (!table->auto_free) { // own a private copy: the module uploads and frees it
+        TensorBase *copy = new TensorBase(table->shape, table->data, (int)table->exponent, table->dtype, true);
+        delete table;
+        table = copy;
+    }
+    return new LUT(node.c_str(), table, MODULE_INPLACE_CHANGED_BUFFER, q);
+}
+
+Clip::Clip(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Unary(ESPDL_ELT_CLIP, name, inplace, quant_type) {}
+
+void Clip::forward(ModelContext *context, runtime_mode_t mode)
+{
+    // min / max are one-element initializers in the input's quantised scale (dl_module_clip.hpp:78-90)
+    const bool s16 = quant_type == QUANT_TYPE_SYMM_16BIT;
+    m_clip_lo = s16 ? -32768 : -128, m_clip_hi = s16 ? 32767 : 127;
+    auto scalar = [&](size_t idx, int &dst) {
+        if (m_inputs_index.size() > idx) {
+            TensorBase *t = context->get_tensor(m_inputs_index[idx]);
+            if (t && t->data)
+                dst = t->dtype == DATA_TYPE_INT16 ? (int)((int16_t *)t->data)[0] : (int)((int8_t *)t->data)[0];
+        }
+    };
+    scalar(1, m_clip_lo);
+    scalar(2, m_clip_hi);
+    Unary::forward(context, mode);
+}
+
+Module *Clip::deserialize(fbs::FbsModel *m, std::string node)
+{
+    quant_type_t q = node_quant(m, node);
+    if (q == QUANT_TYPE_SYMM_8BIT) {
+        Module *lut = LUT::deserialize(m, node);
+        if (lut)
+            return lut;
+    }
+    return new Clip(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, q);
+}
+
+Relu::Relu(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Unary(ESPDL_ELT_RELU, name, inplace, quant_type) {}
+Module *Relu::deserialize(fbs::FbsModel *m, std::string node)
+{
+    quant_type_t q = node_quant(m, node);
+    if (q == QUANT_TYPE_SYMM_8BIT) {
+        Module *lut = LUT::deserialize(m, node);
+        if (lut)
+            return lut;
+    }
+    return new Relu(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, q);
+}
+
+PRelu::PRelu(const char *name, TensorBase *alpha, module_inplace_t inplace, quant_type_t quant_type) :
+    Unary(ESPDL_ELT_PRELU, name, inplace, quant_type, alpha)
+{
+}
+Module *PRelu::deserialize(fbs::FbsModel *m, std::string node)
+{
+    quant_type_t q = node_quant(m, node);
+    if (q == QUANT_TYPE_SYMM_8BIT) {
+        Module *lut = LUT::deserialize(m, node);
+        if (lut)
+            return lut;
+    }
+    TensorBase *alpha = m->get_operation_parameter(node, 1);
+    if (!alpha)
+        return nullptr;
+    if (!alpha->auto_free) {
+        TensorBase *copy = new TensorBase(alpha->shape, alpha->data, (int)alpha->exponent, alpha->dtype, true);
+        delete alpha;
+        alpha = copy;
+    }
+    return new PRelu(node.c_str(), alpha, MODULE_INPLACE_CHANGED_BUFFER, q);
+}
+
+// --------------------------------------------------------------------------------- pooling
+std::vector<std::vector<int>> Pool::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> in = input_shapes[0], out = in;
+    if (m_op == ESPDL_POOL_GLOBAL_AVG) {
+        for (size_t i = 1; i + 1 < out.size(); i++) out[i] = 1; // keeps dim 0 (the reference hard-codes 1 there)
+        return {out};
+    }
+    if (in.size() == 4) {
+        out[1] = (in[1] + m_pads[0] + m_pads[1] - m_kernel[0]) / m_strides[0] + 1;
+        out[2] = (in[2] + m_pads[2] + m_pads[3] - m_kernel[1]) / m_strides[1] + 1;
+    } else {
+        out[1] = (in[1] + m_pads[0] + m_pads[1] - m_kernel[0]) / m_strides[0] + 1;
+    }
+    return {out};
+}
+
+void Pool::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    espdl_pool_desc d;
+    memset(&d, 0, sizeof(d));
+    int st = (!in || !out || !in->device || !out->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st) {
+        d.input = in->device, d.output = out->device, d.op = m_op, d.dtype = quant_dtype(quant_type);
+        if (in->shape.size() == 4) {
+            d.n = in->shape[0], d.in_h = in->shape[1], d.in_w = in->shape[2], d.c = in->shape[3];
+            d.out_h = out->shape[1], d.out_w = out->shape[2];
+            if (m_op != ESPDL_POOL_GLOBAL_AVG) {
+                d.kh = m_kernel[0], d.kw = m_kernel[1], d.stride_h = m_strides[0], d.stride_w = m_strides[1];
+                d.pad_top = m_pads[0], d.pad_bottom = m_pads[1], d.pad_left = m_pads[2], d.pad_right = m_pads[3];
+            }
+        } else if (in->shape.size() == 3) {
+            d.n = in->shape[0], d.in_h = 1, d.in_w = in->shape[1], d.c = in->shape[2];
+            d.out_h = 1, d.out_w = out->shape[1];
+            if (m_op != ESPDL_POOL_GLOBAL_AVG) {
+                d.kh = 1, d.kw = m_kernel[0], d.stride_h = 1, d.stride_w = m_strides[0];
+                d.pad_left = m_pads[0], d.pad_right = m_pads[1];
+            }
+        } else {
+            st = ESPDL_ERR_UNSUPPORTED;
+        }
+        d.in_exponent = in->exponent, d.out_exponent = out->exponent;
+        if (!st)
+            st = espdl_b200_pool(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Pool", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+static void pool_attrs(fbs::FbsModel *m, const std::string &node, std::vector<int> &k, std::vector<int> &p, std::vector<int> &s)
+{
+    m->get_operation_attribute(node, "kernel_shape", k);
+    m->get_operation_attribute(node, "pads", p);
+    m->get_operation_attribute(node, "strides", s);
+    if (p.size() == 4)
+        p = {p[0], p[2], p[1], p[3]};
+    else if (p.empty())
+        p = std::vector<int>(k.size() * 2, 0);
+    if (s.empty())
+        s = std::vector<int>(k.size(), 1);
+}
+
+MaxPool::MaxPool(const char *name, const std::vector<int> &filter_shape, const std::vector<int> &padding, const std::vector<int> &strides,
+                 quant_type_t quant_type) :
+    Pool(ESPDL_POOL_MAX, name, filter_shape, padding.empty() ? std::vector<int>(filter_shape.size() * 2, 0) : padding, strides, quant_type)
+{
+}
+Module *MaxPool::deserialize(fbs::FbsModel *m, std::string node)
+{
+    std::vector<int> k, p, s;
+    pool_attrs(m, node, k, p, s);
+    quant_type_t q = node_quant(m, node);
+    if (q != QUANT_TYPE_SYMM_8BIT && q != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    return new MaxPool(node.c_str(), k, p, s, q);
+}
+AveragePool::AveragePool(const char *name, const std::vector<int> &kernel_shape, const std::vector<int> &pads,
+                         const std::vector<int> &strides, quant_type_t quant_type) :
+    Pool(ESPDL_POOL_AVG, name, kernel_shape, pads.empty() ? std::vector<int>(kernel_shape.size() * 2, 0) : pads, strides, quant_type)
+{
+}
+Module *AveragePool::deserialize(fbs::FbsModel *m, std::string node)
+{
+    std::vector<int> k, p, s;
+    pool_attrs(m, node, k, p, s);
+    quant_type_t q = node_quant(m, node);
+    if (q != QUANT_TYPE_SYMM_8BIT && q != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    return new AveragePool(node.c_str(), k, p, s, q);
+}
+GlobalAveragePool::GlobalAveragePool(const char *name, quant_type_t quant_type) : Pool(ESPDL_POOL_GLOBAL_AVG, name, {}, {}, {}, quant_type) {}
+Module *GlobalAveragePool::deserialize(fbs::FbsModel *m, std::string node)
+{
+    quant_type_t q = node_quant(m, node);
+    if (q != QUANT_TYPE_SYMM_8BIT && q != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    return new GlobalAveragePool(node.c_str(), q);
+}
+
+// --------------------------------------------------------------------------------- resize
+Resize::Resize(const char *name, const resize_mode_t resize_mode, const std::vector<float> scales, const std::vector<int64_t> sizes,
+               const bool align_corners, quant_type_t quant_type) :
+    Module(name, MODULE_NON_INPLACE, quant_type), m_resize_mode(resize_mode), m_scales(scales), m_sizes(sizes)
+{
+    (void)align_corners;
+}
+
+std::vector<std::vector<int>> Resize::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    // scales / sizes are given in NCHW order (dl_module_resize.hpp:55-81)
+    std::vector<int> in = input_shapes[0], out = in;
+    if (m_scales.empty() && m_sizes.size() == in.size()) {
+        m_scales.assign(in.size(), 1.f);
+        if (in.size() == 4) {
+            m_scales[2] = (float)m_sizes[2] / in[1];
+            m_scales[3] = (float)m_sizes[3] / in[2];
+        } else {
+            m_scales[2] = (float)m_sizes[2] / in[1];
+        }
+    }
+    if (in.size() == 4) {
+        out[1] = (int)(in[1] * m_scales[2]);
+        out[2] = (int)(in[2] * m_scales[3]);
+    } else if (in.size() == 3) {
+        out[1] = (int)(in[1] * m_scales[2]);
+    }
+    return {out};
+}
+
+void Resize::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    espdl_resize_desc d;
+    memset(&d, 0, sizeof(d));
+    int st = (!in || !out || !in->device || !out->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st && m_resize_mode != RESIZE_NEAREST)
+        st = ESPDL_ERR_UNSUPPORTED;
+    if (!st) {
+        d.input = in->device, d.output = out->device, d.dtype = quant_dtype(quant_type);
+        if (in->shape.size() == 4) {
+            d.n = in->shape[0], d.in_h = in->shape[1], d.in_w = in->shape[2], d.c = in->shape[3];
+            d.out_h = out->shape[1], d.out_w = out->shape[2];
+            d.scale_h = m_scales[2], d.scale_w = m_scales[3];
+        } else {
+            d.n = in->shape[0], d.in_h = 1, d.in_w = in->shape[1], d.c = in->shape[2];
+            d.out_h = 1, d.out_w = out->shape[1];
+            d.scale_h = 1, d.scale_w = m_scales[2];
+        }
+        d.in_exponent = in->exponent, d.out_exponent = out->exponent;
+        st = espdl_b200_resize(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Resize", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *Resize::deserialize(fbs::FbsModel *m, std::string node)
+{
+    quant_type_t q = node_quant(m, node);
+    resize_mode_t mode = RESIZE_NEAREST;
+    std::string ctm;
+    m->get_operation_attribute(node, "mode", mode);
+    m->get_operation_attribute(node, "coordinate_transformation_mode", ctm);
+    std::vector<float> scales;
+    std::vector<int64_t> sizes;
+    if (TensorBase *t = m->get_operation_parameter(node, 2)) {
+        scales.assign((float *)t->data, (float *)t->data + t->get_size());
+        delete t;
+    }
+    if (TensorBase *t = m->get_operation_parameter(node, 3)) {
+        sizes.assign((int64_t *)t->data, (int64_t *)t->data + t->get_size());
+        delete t;
+    }
+    if (q != QUANT_TYPE_SYMM_8BIT && q != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    return new Resize(node.c_str(), mode, scales, sizes, ctm == "align_corners", q);
+}
+
+// --------------------------------------------------------------------------------- data movement
+static int enqueue_copy(ModelContext *ctx, const void *src, void *dst, int es, const std::vector<int> &shape,
+                        const std::vector<long long> &ss, const std::vector<long long> &ds)
+{
+    // merge to at most six axes from the right where both sides are contiguous
+    std::vector<int> sh;
+    std::vector<long long> s, t;
+    for (size_t i = 0; i < shape.size(); i++) {
+        if (shape[i] == 1)
+            continue;
+        if (!sh.empty() && s.back() == ss[i] * shape[i] && t.back() == ds[i] * shape[i]) {
+            sh.back() *= shape[i], s.back() = ss[i], t.back() = ds[i];
+        } else {
+            sh.push_back(shape[i]), s.push_back(ss[i]), t.push_back(ds[i]);
+        }
+    }
+    if (sh.empty())
+        sh = {1}, s = {1}, t = {1};
+    if (sh.size() > 6)
+        return ESPDL_ERR_UNSUPPORTED;
+    espdl_copy_desc d;
+    memset(&d, 0, sizeof(d));
+    d.src = src, d.dst = dst, d.elem_size = es, d.ndim = (int)sh.size();
+    for (size_t i = 0; i < sh.size(); i++) d.shape[i] = sh[i], d.src_stride[i] = s[i], d.dst_stride[i] = t[i];
+    return espdl_b200_copy(&d, ctx->stream);
+}
+
+static std::vector<long long> dense_strides(const std::vector<int> &shape)
+{
+    std::vector<long long> st(shape.size(), 1);
+    for (int i = (int)shape.size() - 2; i >= 0; i--) st[i] = st[i + 1] * shape[i + 1];
+    return st;
+}
+
+std::vector<std::vector<int>> Concat::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    const int nd = (int)input_shapes[0].size();
+    if (axis < 0)
+        axis += nd;
+    std::vector<int> out = input_shapes[0];
+    out[axis] = 0;
+    for (auto &s : input_shapes) out[axis] += s[axis];
+    return {out};
+}
+
+void Concat::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    const int es = (int)dtype_sizeof(out->dtype);
+    const std::vector<long long> os = dense_strides(out->shape);
+    long long offset = 0;
+    int st = ESPDL_OK;
+    for (size_t i = 0; i < m_inputs_index.size() && !st; i++) {
+        TensorBase *in = context->get_tensor(m_inputs_index[i]);
+        if (!in || !in->device || !out->device) {
+            st = ESPDL_ERR_INVALID_ARG;
+            break;
+        }
+        st = enqueue_copy(context, in->device, (char *)out->device + offset * os[axis] * es, es, in->shape, dense_strides(in->shape), os);
+        offset += in->shape[axis];
+    }
+    if (st)
+        ESP_LOGE("Concat", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *Concat::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int axis = 0;
+    m->get_operation_attribute(node, "axis", axis);
+    return new Concat(node.c_str(), axis, node_quant(m, node));
+}
+
+Split::Split(TensorBase *split, int axis, int num_outputs, const char *name, module_inplace_t inplace, quant_type_t quant_type) :
+    Module(name, inplace, quant_type), m_axis(axis), m_num_outputs(num_outputs)
+{
+    if (split && split->data) {
+        for (int i = 0; i < split->get_size(); i++)
+            m_split.push_back(split->dtype == DATA_TYPE_INT64 ? (int)((int64_t *)split->data)[i] : ((int32_t *)split->data)[i]);
+    }
+    delete split;
+}
+
+std::vector<std::vector<int>> Split::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> in = input_shapes[0];
+    if (m_axis < 0)
+        m_axis += (int)in.size();
+    if (m_split.empty()) {
+        const int n = m_num_outputs > 0 ? m_num_outputs : 2;
+        const int each = (in[m_axis] + n - 1) / n;
+        for (int i = 0; i < n; i++) m_split.push_back(std::min(each, in[m_axis] - i * each));
+    }
+    std::vector<std::vector<int>> outs;
+    for (int s : m_split) {
+        std::vector<int> o = in;
+        o[m_axis] = s;
+        outs.push_back(o);
+    }
+    return outs;
+}
+
+void Split::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    const int es = (int)dtype_sizeof(in->dtype);
+    const std::vector<long long> is = dense_strides(in->shape);
+    long long offset = 0;
+    int st = ESPDL_OK;
+    for (size_t i = 0; i < m_outputs_index.size() && !st; i++) {
+        TensorBase *out = context->get_tensor(m_outputs_index[i]);
+        if (!out || !out->device || !in->device) {
+            st = ESPDL_ERR_INVALID_ARG;
+            break;
+        }
+        st = enqueue_copy(context, (char *)in->device + offset * is[m_axis] * es, out->device, es, out->shape, is, dense_strides(out->shape));
+        offset += out->shape[m_axis];
+    }
+    if (st)
+        ESP_LOGE("Split", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *Split::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int axis = 0, num_outputs = -1;
+    m->get_operation_attribute(node, "axis", axis);
+    m->get_operation_attribute(node, "num_outputs", num_outputs);
+    return new Split(m->get_operation_parameter(node, 1), axis, num_outputs, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+std::vector<std::vector<int>> Transpose::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> in = input_shapes[0], out(in.size());
+    if (m_perm.empty())
+        for (int i = (int)in.size() - 1; i >= 0; i--) m_perm.push_back(i);
+    for (size_t i = 0; i < in.size(); i++) out[i] = in[m_perm[i]];
+    return {out};
+}
+
+void Transpose::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!in || !out || !in->device || !out->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st) {
+        const std::vector<long long> is = dense_strides(in->shape);
+        std::vector<long long> ss(out->shape.size());
+        for (size_t i = 0; i < out->shape.size(); i++) ss[i] = is[m_perm[i]];
+        st = enqueue_copy(context, in->device, out->device, (int)dtype_sizeof(in->dtype), out->shape, ss, dense_strides(out->shape));
+    }
+    if (st)
+        ESP_LOGE("Transpose", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *Transpose::deserialize(fbs::FbsModel *m, std::string node)
+{
+    std::vector<int> perm;
+    m->get_operation_attribute(node, "perm", perm);
+    return new Transpose(node.c_str(), MODULE_NON_INPLACE, node_quant(m, node), perm);
+}
+
+std::vector<std::vector<int>> Reshape::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> in = input_shapes[0], out;
+    long long total = 1;
+    for (int d : in) total *= d;
+    switch (m_kind) {
+    case RESHAPE: {
+        out = m_arg;
+        long long known = 1;
+        int unknown = -1;
+        for (size_t i = 0; i < out.size(); i++) {
+            if (out[i] == 0 && i < in.size())
+                out[i] = in[i];
+            if (out[i] == -1)
+                unknown = (int)i;
+            else
+                known *= out[i];
+        }
+        if (unknown >= 0)
+            out[unknown] = (int)(total / known);
+        else if (known != total && !out.empty() && !in.empty() && known / out[0] * in[0] == total)
+            out[0] = in[0]; // exported for batch 1, run with a larger batch
+        break;
+    }
+    case FLATTEN: {
+        int axis = m_axis < 0 ? m_axis + (int)in.size() : m_axis;
+        long long a = 1;
+        for (int i = 0; i < axis; i++) a *= in[i];
+        out = {(int)a, (int)(total / a)};
+        break;
+    }
+    case SQUEEZE: {
+        for (size_t i = 0; i < in.size(); i++) {
+            bool drop = false;
+            if (m_arg.empty())
+                drop = in[i] == 1;
+            for (int ax : m_arg)
+                if ((ax < 0 ? ax + (int)in.size() : ax) == (int)i)
+                    drop = true;
+            if (!drop)
+                out.push_back(in[i]);
+        }
+        break;
+    }
+    case UNSQUEEZE: {
+        const int nd = (int)in.size() + (int)m_arg.size();
+        out.assign(nd, 0);
+        for (int ax : m_arg) out[ax < 0 ? ax + nd : ax] = 1;
+        size_t k = 0;
+        for (auto &o : out)
+            if (o == 0)
+                o = in[k++];
+        break;
+    }
+    case IDENTITY: out = in; break;
+    }
+    return {out};
+}
+
+void Reshape::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    if (in && out && in->device && out->device && in->device != out->device) {
+        espdl_copy_desc d;
+        memset(&d, 0, sizeof(d));
+        d.src = in->device, d.dst = out->device, d.elem_size = (int)dtype_sizeof(in->dtype), d.ndim = 1;
+        d.shape[0] = in->get_size(), d.src_stride[0] = d.dst_stride[0] = 1;
+        context->note(espdl_b200_copy(&d, context->stream));
+    }
+}
+
+static std::vector<int> int_param(fbs::FbsModel *m, const std::string &node, int index)
+{
+    std::vector<int> v;
+    if (TensorBase *t = m->get_operation_parameter(node, index)) {
+        for (int i = 0; i < t->get_size(); i++)
+            v.push_back(t->dtype == DATA_TYPE_INT64 ? (int)((int64_t *)t->data)[i] : ((int32_t *)t->data)[i]);
+        delete t;
+    }
+    return v;
+}
+
+Module *Reshape::deserialize_reshape(fbs::FbsModel *m, std::string node)
+{
+    return new Reshape(RESHAPE, int_param(m, node, 1), 0, node.c_str(), node_quant(m, node));
+}
+Module *Reshape::deserialize_flatten(fbs::FbsModel *m, std::string node)
+{
+    int axis = 1;
+    m->get_operation_attribute(node, "axis", axis);
+    return new Reshape(FLATTEN, {}, axis, node.c_str(), node_quant(m, node));
+}
+Module *Reshape::deserialize_squeeze(fbs::FbsModel *m, std::string node)
+{
+    std::vector<int> axes = int_param(m, node, 1);
+    if (axes.empty())
+        m->get_operation_attribute(node, "axes", axes);
+    return new Reshape(SQUEEZE, axes, 0, node.c_str(), node_quant(m, node));
+}
+Module *Reshape::deserialize_unsqueeze(fbs::FbsModel *m, std::string node)
+{
+    std::vector<int> axes = int_param(m, node, 1);
+    if (axes.empty())
+        m->get_operation_attribute(node, "axes", axes);
+    return new Reshape(UNSQUEEZE, axes, 0, node.c_str(), node_quant(m, node));
+}
+Module *Reshape::deserialize_identity(fbs::FbsModel *m, std::string node)
+{
+    return new Reshape(IDENTITY, {}, 0, node.c_str(), node_quant(m, node));
+}
+
+// --------------------------------------------------------------------------------- softmax
+Softmax::~Softmax()
+{
+    if (m_dev_table)
+        espdl_b200_arena_free(m_dev_table);
+}
+
+void Softmax::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!in || !out || !in->device || !out->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    const int nd = in ? (int)in->shape.size() : 0;
+    const int ax = axis < 0 ? axis + nd : axis;
+    if (!st && (in->dtype != DATA_TYPE_INT8 || ax != nd - 1))
+        st = ESPDL_ERR_UNSUPPORTED;
+    if (!st && (!m_dev_table || m_table_exponent != (int)in->exponent)) {
+        // dl::tool::gen_lut_8bit(expf): esp-dl/dl/tool/src/dl_tool.cpp:258-268, built once on the host
+        float table[256];
+        const float scale = DL_SCALE((int)in->exponent);
+        for (int i = 0; i < 256; i++) table[i] = expf(scale * (float)(i - 128));
+        if (!m_dev_table && espdl_b200_arena_alloc(sizeof(table), &m_dev_table) != ESPDL_OK)
+            st = ESPDL_ERR_NO_MEM;
+        if (!st)
+            st = espdl_b200_upload(m_dev_table, table, sizeof(table), nullptr);
+        if (!st)
+            st = espdl_b200_stream_sync(nullptr);
+        m_table_exponent = in->exponent;
+    }
+    if (!st) {
+        espdl_softmax_desc d;
+        memset(&d, 0, sizeof(d));
+        d.input = (const int8_t *)in->device, d.output = out->device, d.exp_table = (const float *)m_dev_table;
+        d.len = in->shape.back(), d.rows = in->get_size() / d.len;
+        d.out_dtype = espdl_dtype(out), d.out_exponent = out->exponent;
+        st = espdl_b200_softmax(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Softmax", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *Softmax::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int axis = -1;
+    m->get_operation_attribute(node, "axis", axis);
+    return new Softmax(node.c_str(), axis, MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+// --------------------------------------------------------------------------------- registry
+void ModuleCreator::register_dl_modules()
+{
+    if (registered)
+        return;
+    registered = true;
+    // same op-type strings as the reference registry (esp-dl/dl/module/include/dl_module_creator.hpp:134-204)
+    register_module("Conv", Conv::deserialize);
+    register_module("Gemm", Gemm::deserialize);
+    register_module("Add", Add::deserialize);
+    register_module("Sub", Sub::deserialize);
+    register_module("Mul", Mul::deserialize);
+    register_module("RequantizeLinear", RequantizeLinear::deserialize);
+    register_module("QuantizeLinear", RequantizeLinear::deserialize);
+    register_module("DequantizeLinear", RequantizeLinear::deserialize);
+    for (const char *op : {"LUT", "Swish", "Sigmoid", "Tanh", "HardSwish", "HardSigmoid", "Gelu", "Elu", "LeakyRelu", "Exp", "Log", "Sqrt",
+                           "Neg", "Abs"})
+        register_module(op, LUT::deserialize);
+    register_module("Clip", Clip::deserialize);
+    register_module("Relu", Relu::deserialize);
+    register_module("PRelu", PRelu::deserialize);
+    register_module("MaxPool", MaxPool::deserialize);
+    register_module("AveragePool", AveragePool::deserialize);
+    register_module("GlobalAveragePool", GlobalAveragePool::deserialize);
+    register_module("Resize", Resize::deserialize);
+    register_module("Concat", Concat::deserialize);
+    register_module("Split", Split::deserialize);
+    register_module("Transpose", Transpose::deserialize);
+    register_module("Reshape", Reshape::deserialize_reshape);
+    register_module("Flatten", Reshape::deserialize_flatten);
+    register_module("Squeeze", Reshape::deserialize_squeeze);
+    register_module("Unsqueeze", Reshape::deserialize_unsqueeze);
+    register_module("Identity", Reshape::deserialize_identity);
+    register_module("Softmax", Softmax::deserialize);
+}
+
+} // namespace module
+} // namespace dl

@@ -1,0 +1,257 @@
+// Operator modules of the B200 backend.  Each class keeps the name, constructor-argument meaning,
+// shape rule and `deserialize` attribute names of the reference module it replaces
+// (esp-dl/dl/module/include/dl_module_<op>.hpp); forward() enqueues the CUDA kernel through the C ABI.
+#pragma once
+#include "dl_module_base.hpp"
+
+namespace dl {
+namespace module {
+
+/// Conv (dense or depthwise), reference: dl_module_conv.hpp:17-239.  pads are [top, bottom, left, right].
+class Conv : public Module {
+public:
+    Conv(activation_type_t activation = Linear, std::vector<int> pads = {}, std::vector<int> dilations = {},
+         std::vector<int> strides = {}, const char *name = nullptr, const int group = 1, quant_type_t quant_type = QUANT_TYPE_NONE,
+         const std::string &target = "c");
+    ~Conv();
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    esp_err_t prepare(ModelContext *context) override;
+    size_t workspace_bytes(ModelContext *context) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+    void print() override;
+    /// Fuse a following 8-bit LUT node into the epilogue (the table must already be on the device).
+    void set_fused_lut(TensorBase *table) { m_lut = table; }
+
+protected:
+    int fill_desc(ModelContext *context, void *desc);
+    std::vector<int> m_dilations, m_strides;
+    const int m_group;
+    activation_type_t activation;
+    std::vector<int> m_pads;
+    std::string m_target;
+    bool m_gemm = false;             ///< Gemm / MatMul view: rows = all leading dims
+    void *m_dev_exponents = nullptr; ///< int32[out_c] on the device when the filter is per-channel
+    TensorBase *m_lut = nullptr;
+    bool m_prepared = false;
+};
+
+/// Gemm (fully connected), reference: dl_module_gemm.hpp:17-168: a 1x1 conv over {1,1,M,K}.
+class Gemm : public Conv {
+public:
+    Gemm(activation_type_t activation = Linear, const char *name = nullptr, quant_type_t quant_type = QUANT_TYPE_NONE,
+         const std::string &target = "c");
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+
+/// Add / Sub / Mul with numpy broadcasting, reference: dl_module_add.hpp:14-105, dl_module_mul.hpp, dl_module_sub.hpp.
+class Elementwise : public Module {
+public:
+    Elementwise(int op, const char *name, module_inplace_t inplace, quant_type_t quant_type) : Module(name, inplace, quant_type), m_op(op) {}
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+
+protected:
+    int m_op;
+};
+class Add : public Elementwise {
+public:
+    Add(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class Sub : public Elementwise {
+public:
+    Sub(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class Mul : public Elementwise {
+public:
+    Mul(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+
+/// One-input elementwise modules: RequantizeLinear / QuantizeLinear / DequantizeLinear
+/// (dl_module_requantize_linear.hpp:8-60), LUT and every activation exported with a `lut` attribute
+/// (dl_module_lut.hpp:15-104), Clip (dl_module_clip.hpp), Relu (dl_module_relu.hpp), PRelu (dl_module_prelu.hpp).
+class Unary : public Module {
+public:
+    Unary(int op, const char *name, module_inplace_t inplace, quant_type_t quant_type, TensorBase *param = nullptr) :
+        Module(name, inplace, quant_type), m_op(op), m_param(param)
+    {
+    }
+    ~Unary() { delete m_param; }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override { return {input_shapes[0]}; }
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    esp_err_t prepare(ModelContext *context) override;
+    TensorBase *get_table() { return m_param; }
+    int op() const { return m_op; }
+
+protected:
+    int m_op;
+    TensorBase *m_param; ///< LUT table or PReLU alpha (owned)
+    int m_clip_lo = -128, m_clip_hi = 127;
+};
+class RequantizeLinear : public Unary {
+public:
+    RequantizeLinear(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class LUT : public Unary {
+public:
+    LUT(const char *name = nullptr, TensorBase *table = nullptr, module_inplace_t inplace = MODULE_INPLACE_CHANGED_BUFFER,
+        quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class Clip : public Unary {
+public:
+    Clip(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+};
+class Relu : public Unary {
+public:
+    Relu(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class PRelu : public Unary {
+public:
+    PRelu(const char *name = nullptr, TensorBase *alpha = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+          quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+
+/// MaxPool / AveragePool / GlobalAveragePool, reference: dl_module_max_pool.hpp, dl_module_average_pool.hpp,
+/// dl_module_global_average_pool.hpp.  Unlike the reference, GlobalAveragePool keeps the batch extent.
+class Pool : public Module {
+public:
+    Pool(int op, const char *name, const std::vector<int> &kernel, const std::vector<int> &pads, const std::vector<int> &strides,
+         quant_type_t quant_type) :
+        Module(name, MODULE_NON_INPLACE, quant_type), m_op(op), m_kernel(kernel), m_pads(pads), m_strides(strides)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+
+protected:
+    int m_op;
+    std::vector<int> m_kernel, m_pads, m_strides;
+};
+class MaxPool : public Pool {
+public:
+    MaxPool(const char *name = nullptr, const std::vector<int> &filter_shape = {2, 2}, const std::vector<int> &padding = {},
+            const std::vector<int> &strides = {1, 1}, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class AveragePool : public Pool {
+public:
+    AveragePool(const char *name = nullptr, const std::vector<int> &kernel_shape = {2, 2}, const std::vector<int> &pads = {},
+                const std::vector<int> &strides = {1, 1}, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class GlobalAveragePool : public Pool {
+public:
+    GlobalAveragePool(const char *name = nullptr, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+
+/// Resize (nearest), reference: dl_module_resize.hpp.
+class Resize : public Module {
+public:
+    Resize(const char *name = nullptr, const resize_mode_t resize_mode = RESIZE_NEAREST, const std::vector<float> scales = {},
+           const std::vector<int64_t> sizes = {}, const bool align_corners = false, quant_type_t quant_type = QUANT_TYPE_NONE);
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    resize_mode_t m_resize_mode;
+    std::vector<float> m_scales;
+    std::vector<int64_t> m_sizes;
+};
+
+/// Concat (dl_module_concat.hpp), Split (dl_module_split.hpp), Transpose (dl_module_transpose.hpp): strided copies.
+class Concat : public Module {
+public:
+    Concat(const char *name = nullptr, int axis = 0, quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, MODULE_NON_INPLACE, quant_type), axis(axis)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int axis;
+};
+class Split : public Module {
+public:
+    Split(TensorBase *split = nullptr, int axis = 0, int num_outputs = -1, const char *name = nullptr,
+          module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    std::vector<int> m_split;
+    int m_axis, m_num_outputs;
+};
+class Transpose : public Module {
+public:
+    Transpose(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE,
+              std::vector<int> perm = {}) :
+        Module(name, inplace, quant_type), m_perm(perm)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    std::vector<int> m_perm;
+};
+
+/// Reshape / Flatten / Squeeze / Unsqueeze / Identity: the output aliases the input buffer
+/// (MODULE_INPLACE_UNCHANGED_BUFFER); forward() is a no-op unless the planner gave it a separate buffer.
+class Reshape : public Module {
+public:
+    enum Kind { RESHAPE, FLATTEN, SQUEEZE, UNSQUEEZE, IDENTITY };
+    Reshape(Kind kind, std::vector<int> arg, int axis, const char *name, quant_type_t quant_type) :
+        Module(name, MODULE_INPLACE_UNCHANGED_BUFFER, quant_type), m_kind(kind), m_arg(arg), m_axis(axis)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize_reshape(fbs::FbsModel *fbs_model, std::string node_name);
+    static Module *deserialize_flatten(fbs::FbsModel *fbs_model, std::string node_name);
+    static Module *deserialize_squeeze(fbs::FbsModel *fbs_model, std::string node_name);
+    static Module *deserialize_unsqueeze(fbs::FbsModel *fbs_model, std::string node_name);
+    static Module *deserialize_identity(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    Kind m_kind;
+    std::vector<int> m_arg;
+    int m_axis;
+};
+
+/// Softmax on int8 input with a host-built exp table, float output (dl_module_softmax.hpp:14-246).
+class Softmax : public Module {
+public:
+    Softmax(const char *name = nullptr, int axis = -1, module_inplace_t inplace = MODULE_NON_INPLACE,
+            quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, inplace, quant_type), axis(axis)
+    {
+    }
+    ~Softmax();
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override { return {input_shapes[0]}; }
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int axis;
+    void *m_dev_table = nullptr;
+    int m_table_exponent = 0x7fffffff;
+};
+
+} // namespace module
+} // namespace dl

@@ -1,0 +1,199 @@
+// Flat C wrappers around dl::Model so that Python (tests, bench.py) can drive the C++ host layer through ctypes.
+// C++ users include dl_model_base.hpp directly; nothing here adds behaviour.
+#include "dl_model_base.hpp"
+#include "espdl_b200.h"
+
+#include <cstring>
+#include <string>
+
+using namespace dl;
+
+namespace {
+struct Handle {
+    Model *model = nullptr;
+    std::vector<std::string> input_names, output_names;
+    std::string text;
+};
+
+TensorBase *io_tensor(Handle *h, int is_output, int index)
+{
+    auto &names = is_output ? h->output_names : h->input_names;
+    if (index < 0 || index >= (int)names.size())
+        return nullptr;
+    return is_output ? h->model->get_output(names[index]) : h->model->get_input(names[index]);
+}
+} // namespace
+
+extern "C" {
+
+/// batch > 0 overrides dim 0 of every graph input.  flags: bit0 = no CUDA graph, bit1 = no buffer reuse.
+void *espdl_model_create(const char *path, int batch, int flags)
+{
+    Handle *h = new Handle();
+    Model *m = new Model();
+    h->model = m;
+    m->m_use_graph = !(flags & 1) && (getenv("ESPDL_B200_GRAPH") ? getenv("ESPDL_B200_GRAPH")[0] != '0' : true);
+    m->m_reuse_memory = !(flags & 2);
+    if (m->load(path, fbs::MODEL_LOCATION_IN_SDCARD, 0, nullptr, true) != ESP_OK) {
+        delete m;
+        delete h;
+        return nullptr;
+    }
+    std::map<std::string, std::vector<int>> shapes;
+    if (batch > 0) {
+        for (const std::string &name : m->get_fbs_model()->get_graph_inputs()) {
+            std::vector<int> s = m->get_fbs_model()->get_value_info_shape(name);
+            if (!s.empty())
+                s[0] = batch;
+            shapes[name] = s;
+        }
+    }
+    m->build(0, MEMORY_MANAGER_GREEDY, false, shapes);
+    if (m->m_status) {
+        delete m;
+        delete h;
+        return nullptr;
+    }
+    for (auto &kv : m->get_inputs()) h->input_names.push_back(kv.first);
+    for (auto &kv : m->get_outputs()) h->output_names.push_back(kv.first);
+    return h;
+}
+
+void espdl_model_destroy(void *handle)
+{
+    Handle *h = (Handle *)handle;
+    if (h) {
+        delete h->model;
+        delete h;
+    }
+}
+
+int espdl_model_num_io(void *handle, int is_output)
+{
+    Handle *h = (Handle *)handle;
+    return (int)(is_output ? h->output_names.size() : h->input_names.size());
+}
+
+/// Describes graph input / output `index`: name, shape (up to 8 dims), dtype, exponent, host and device address.
+int espdl_model_io_info(void *handle, int is_output, int index, const char **name, int *ndim, int *shape, int *dtype, int *exponent,
+                        void **host, void **device)
+{
+    Handle *h = (Handle *)handle;
+    TensorBase *t = io_tensor(h, is_output, index);
+    if (!t)
+        return ESPDL_ERR_INVALID_ARG;
+    *name = (is_output ? h->output_names : h->input_names)[index].c_str();
+    *ndim = (int)t->shape.size();
+    for (int i = 0; i < *ndim && i < 8; i++) shape[i] = t->shape[i];
+    *dtype = (int)t->dtype, *exponent = (int)t->exponent, *host = t->data, *device = t->device;
+    return ESPDL_OK;
+}
+
+int espdl_model_run(void *handle)
+{
+    Handle *h = (Handle *)handle;
+    h->model->run();
+    return h->model->m_status;
+}
+
+int espdl_model_run_device(void *handle, int sync)
+{
+    Handle *h = (Handle *)handle;
+    h->model->run_device(sync != 0);
+    return h->model->m_status;
+}
+
+int espdl_model_test(void *handle) { return ((Handle *)handle)->model->test(); }
+
+void *espdl_model_stream(void *handle) { return ((Handle *)handle)->model->stream(); }
+
+size_t espdl_model_arena_bytes(void *handle) { return ((Handle *)handle)->model->arena_bytes(); }
+
+int espdl_model_num_modules(void *handle) { return (int)((Handle *)handle)->model->num_modules(); }
+
+/// Copies the named tensor (any graph tensor; meaningful for intermediates only when built without buffer reuse)
+/// to `dst`.  Returns the tensor's byte size, or a negative status.
+long long espdl_model_read_tensor(void *handle, const char *name, void *dst, size_t dst_bytes)
+{
+    Handle *h = (Handle *)handle;
+    TensorBase *t = h->model->get_intermediate(name);
+    if (!t || !t->device)
+        return ESPDL_ERR_INVALID_ARG;
+    if (dst) {
+        if (dst_bytes < t->get_bytes())
+            return ESPDL_ERR_INVALID_ARG;
+        int st = espdl_b200_download(dst, t->device, t->get_bytes(), h->model->stream());
+        if (!st)
+            st = espdl_b200_stream_sync(h->model->stream());
+        if (st)
+            return st;
+    }
+    return (long long)t->get_bytes();
+}
+
+/// Text dump of what the C++ reader sees in a model file (no device needed): one line per node in execution
+/// order "op_type<TAB>name<TAB>inputs<TAB>outputs", then one line per initializer "name<TAB>dtype<TAB>dims<TAB>n_exponents<TAB>sum".
+const char *espdl_fbs_describe(const char *path)
+{
+    static std::string text;
+    text.clear();
+    fbs::FbsLoader loader(path, fbs::MODEL_LOCATION_IN_SDCARD);
+    fbs::FbsModel *m = loader.load(0, nullptr, true);
+    if (!m)
+        return nullptr;
+    text += "target\t" + m->get_model_metadata_prop("target") + "\n";
+    for (const std::string &node : m->topological_sort()) {
+        std::vector<std::string> ins, outs;
+        m->get_operation_inputs_and_outputs(node, ins, outs);
+        text += "node\t" + m->get_operation_type(node) + "\t" + node + "\t";
+        for (auto &s : ins) text += s + ",";
+        text += "\t";
+        for (auto &s : outs) text += s + "," + vector_to_string(m->get_value_info_shape(s)) + "," + std::to_string(m->get_value_info_exponent(s)) + ";";
+        std::vector<int> pads;
+        if (m->get_operation_attribute(node, "pads", pads) == ESP_OK)
+            text += "\tpads=" + vector_to_string(pads);
+        std::string act;
+        if (m->get_operation_attribute(node, "activation", act) == ESP_OK)
+            text += "\tactivation=" + act;
+        text += "\n";
+        for (size_t i = 0; i < ins.size(); i++) {
+            if (!m->is_parameter(ins[i]))
+                continue;
+            TensorBase *t = m->get_operation_parameter(node, (int)i);
+            long long sum = 0;
+            for (size_t b = 0; b < t->get_bytes(); b++) sum += ((const uint8_t *)t->data)[b];
+            text += "param\t" + ins[i] + "\t" + std::to_string((int)t->dtype) + "\t" + vector_to_string(t->shape) + "\t" +
+                std::to_string(t->exponent.size()) + "\t" + std::to_string(sum) + "\n";
+            delete t;
+        }
+    }
+    delete m;
+    return text.c_str();
+}
+
+/// Runs the arena planner on a synthetic tensor list (no device needed).  Returns the arena size.
+size_t espdl_plan_arena(int n, const int *first, const int *last, const size_t *bytes, const int *alias_of, size_t *offsets, int reuse)
+{
+    std::vector<TensorInfo> infos(n);
+    for (int i = 0; i < n; i++) infos[i].first = first[i], infos[i].last = last[i], infos[i].bytes = bytes[i], infos[i].alias_of = alias_of[i];
+    const size_t arena = MemoryManagerGreedy::plan(infos, reuse != 0);
+    for (int i = 0; i < n; i++) offsets[i] = infos[i].offset;
+    return arena;
+}
+
+/// Per-module latency table as text: one "index<TAB>type<TAB>microseconds<TAB>name" line per module.
+const char *espdl_model_profile(void *handle)
+{
+    Handle *h = (Handle *)handle;
+    h->text.clear();
+    for (auto &kv : h->model->get_module_info()) {
+        char line[512];
+        const size_t colon = kv.first.find(':');
+        snprintf(line, sizeof(line), "%s\t%s\t%.2f\t%s\n", kv.first.substr(0, colon).c_str(), kv.second.type.c_str(), kv.second.latency_us,
+                 kv.first.substr(colon + 1).c_str());
+        h->text += line;
+    }
+    return h->text.c_str();
+}
+
+} // extern "C"

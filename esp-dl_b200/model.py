@@ -1,0 +1,119 @@
+"""ctypes binding of the C++ host layer (dl::Model) for tests and the benchmark."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import abi
+
+HOST_LIB_PATH = os.path.join(abi.HERE, "libespdl_b200_host.so")
+NP = {1: np.float32, 3: np.int8, 5: np.int16, 6: np.int32, 7: np.int64}
+_host = None
+
+
+def host_lib():
+    global _host
+    if _host is None:
+        abi.load()  # the CUDA library first (RTLD_GLOBAL), the host layer links against it
+        if not os.path.exists(HOST_LIB_PATH):
+            raise RuntimeError(f"{HOST_LIB_PATH} is missing: run the build; there is no fallback")
+        L = C.CDLL(HOST_LIB_PATH)
+        L.espdl_model_create.restype = C.c_void_p
+        L.espdl_model_create.argtypes = [C.c_char_p, C.c_int, C.c_int]
+        L.espdl_model_destroy.argtypes = [C.c_void_p]
+        L.espdl_model_num_io.argtypes = [C.c_void_p, C.c_int]
+        L.espdl_model_io_info.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                          C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
+        L.espdl_model_run.argtypes = [C.c_void_p]
+        L.espdl_model_run_device.argtypes = [C.c_void_p, C.c_int]
+        L.espdl_model_test.argtypes = [C.c_void_p]
+        L.espdl_model_stream.restype = C.c_void_p
+        L.espdl_model_stream.argtypes = [C.c_void_p]
+        L.espdl_model_arena_bytes.restype = C.c_size_t
+        L.espdl_model_arena_bytes.argtypes = [C.c_void_p]
+        L.espdl_model_num_modules.argtypes = [C.c_void_p]
+        L.espdl_model_read_tensor.restype = C.c_longlong
+        L.espdl_model_read_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]
+        L.espdl_model_profile.restype = C.c_char_p
+        L.espdl_model_profile.argtypes = [C.c_void_p]
+        _host = L
+    return _host
+
+
+class IO:
+    def __init__(self, name, shape, dtype, exponent, host, device):
+        self.name, self.shape, self.dtype, self.exponent, self.host_ptr, self.device_ptr = name, shape, dtype, exponent, host, device
+        n = int(np.prod(shape))
+        self.nbytes = n * np.dtype(NP[dtype]).itemsize
+        # numpy view of the pinned host buffer the C++ side owns
+        buf = (C.c_char * self.nbytes).from_address(host)
+        self.array = np.frombuffer(buf, dtype=NP[dtype], count=n).reshape(shape)
+
+
+class Model:
+    """dl::Model on cuda:0.  `batch` overrides dim 0 of the graph inputs."""
+
+    def __init__(self, path, batch=0, graph=True, reuse=True, device=0):
+        L = abi.load()
+        abi.check(L.espdl_b200_init(device), "espdl_b200_init")
+        self.lib = host_lib()
+        flags = (0 if graph else 1) | (0 if reuse else 2)
+        self.h = self.lib.espdl_model_create(os.fsencode(path), int(batch), flags)
+        if not self.h:
+            raise RuntimeError(f"failed to load / build {path}: {L.espdl_b200_last_error().decode()}")
+        self.inputs = [self._io(0, i) for i in range(self.lib.espdl_model_num_io(self.h, 0))]
+        self.outputs = [self._io(1, i) for i in range(self.lib.espdl_model_num_io(self.h, 1))]
+
+    def _io(self, is_output, index):
+        name, ndim, shape = C.c_char_p(), C.c_int(), (C.c_int * 8)()
+        dtype, exponent, host, device = C.c_int(), C.c_int(), C.c_void_p(), C.c_void_p()
+        abi.check(self.lib.espdl_model_io_info(self.h, is_output, index, C.byref(name), C.byref(ndim), shape, C.byref(dtype),
+                                               C.byref(exponent), C.byref(host), C.byref(device)), "io_info")
+        return IO(name.value.decode(), tuple(shape[:ndim.value]), dtype.value, exponent.value, host.value, device.value)
+
+    def run(self):
+        """Host buffers -> device, execute, device -> host buffers (the call a user of dl::Model makes)."""
+        abi.check(self.lib.espdl_model_run(self.h), "Model::run")
+
+    def run_device(self, sync=True):
+        abi.check(self.lib.espdl_model_run_device(self.h, 1 if sync else 0), "Model::run_device")
+
+    def test(self):
+        return self.lib.espdl_model_test(self.h)
+
+    @property
+    def stream(self):
+        return self.lib.espdl_model_stream(self.h)
+
+    @property
+    def arena_bytes(self):
+        return self.lib.espdl_model_arena_bytes(self.h)
+
+    @property
+    def num_modules(self):
+        return self.lib.espdl_model_num_modules(self.h)
+
+    def read_tensor(self, name, dtype, shape):
+        out = np.empty(shape, dtype=dtype)
+        n = self.lib.espdl_model_read_tensor(self.h, name.encode(), out.ctypes.data, out.nbytes)
+        if n < 0 or n != out.nbytes:
+            raise RuntimeError(f"read_tensor({name}) -> {n}, expected {out.nbytes}")
+        return out
+
+    def profile(self):
+        rows = []
+        for line in self.lib.espdl_model_profile(self.h).decode().splitlines():
+            idx, typ, us, name = line.split("\t")
+            rows.append((int(idx), typ, float(us), name))
+        return rows
+
+    def close(self):
+        if self.h:
+            self.lib.espdl_model_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

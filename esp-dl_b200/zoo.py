@@ -1,0 +1,187 @@
+"""Synthetic `.espdl` networks with the topologies of the benchmark configurations.
+
+The trained model-zoo files cannot travel with this repository and the exporter (esp-ppq) is a separate
+project, so the benchmark and the tests build their networks here: same graph structure, node attributes and
+tensor conventions as the exported files (NHWC activations, filters declared [KH,KW,Cin,Cout] with target "c"
+byte order [Cout][KH][KW][Cin], int32 bias at exponent e_in + e_w[c], per-channel power-of-two filter
+exponents, ONNX pad order [t,l,b,r]), random int8 weights from a seeded generator.
+
+Weight amplitudes are scaled per output channel so that the requantised activations use the int8 range without
+saturating everywhere (the configurations ask for random weights, not for a particular amplitude).
+"""
+import numpy as np
+
+from . import espdl_file
+
+# MobileNetV2-1.0 inverted-residual settings: expansion t, output channels c, repeats n, first stride s
+MBV2_SETTINGS = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]
+
+
+class _Net:
+    def __init__(self, name, seed, e_act=(-8, -4), e_w=(-9, -5)):
+        self.g = espdl_file.GraphBuilder(name, {"target": "c"})
+        self.rng = np.random.default_rng(seed)
+        self.e_act, self.e_w = e_act, e_w
+        self.exp = {}     # tensor name -> exponent
+        self.shape = {}   # tensor name -> NHWC shape (batch 1)
+        self.rms = {}     # tensor name -> estimated rms of the quantised values
+        self.count = 0
+
+    def fresh(self, prefix):
+        self.count += 1
+        return f"{prefix}_{self.count}"
+
+    def tensor(self, name, shape, exponent, rms):
+        self.exp[name], self.shape[name], self.rms[name] = exponent, list(shape), rms
+        self.g.add_value_info(name, np.int8, shape, exponent)
+
+    def pick_exponent(self, e_acc, need, allowed):
+        """Output exponent from `allowed` = (lo, hi) such that every shift e_out - e_acc[c] is >= 1 and as many channels
+        as possible get a weight amplitude need * 2^shift inside [3, 127]; ties are broken at random."""
+        scored = []
+        for e in range(allowed[0], allowed[1] + 1):
+            shift = e - e_acc
+            if shift.min() < 1:
+                continue
+            amp = need * 2.0 ** shift
+            scored.append((float(((amp >= 3) & (amp <= 127)).mean()), e))
+        if not scored:
+            return int(e_acc.max() + 1)
+        top = max(s for s, _ in scored)
+        good = [e for s, e in scored if s >= top - 0.1]
+        return int(good[int(self.rng.integers(0, len(good)))])
+
+    def conv(self, x, cout, k, stride=1, group=1, relu=True, e_out=None, bias=True, name=None):
+        n, h, w, cin = self.shape[x]
+        depthwise = group != 1
+        pad = k // 2
+        oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        e_in = self.exp[x]
+        ew = self.rng.integers(self.e_w[0], self.e_w[1] + 1, size=cout)
+        taps = k * k * (1 if depthwise else cin)
+        target = 28.0  # wanted rms of the requantised output, in codes
+        need = target * np.sqrt(3.0) / (self.rms[x] * np.sqrt(taps))  # weight amplitude wanted at shift 0
+        if e_out is None:
+            e_out = self.pick_exponent(ew + e_in, need, self.e_act)
+        shift = e_out - ew - e_in
+        # amplitude so that the requantised output has rms ~ target: rms_acc = rms_in * (wmax/sqrt(3)) * sqrt(taps)
+        wmax = np.clip(np.round(need * (2.0 ** shift)), 1, 127).astype(np.int64)
+        if depthwise:
+            wt = np.stack([self.rng.integers(-wmax[c], wmax[c] + 1, size=(k, k)) for c in range(cout)], axis=-1).astype(np.int8)  # [KH][KW][C]
+            declared = (k, k, cin, 1)
+        else:
+            wt = np.stack([self.rng.integers(-wmax[c], wmax[c] + 1, size=(k, k, cin)) for c in range(cout)]).astype(np.int8)  # [Cout][KH][KW][Cin]
+            declared = (k, k, cin, cout)
+        node = name or self.fresh("conv")
+        wname, bname, out = node + ".weight", node + ".bias", node + "_out"
+        # the payload keeps the target-"c" byte order; only the declared dims are [KH,KW,Cin,Cout]
+        self.g.add_initializer(wname, wt.reshape(declared), list(ew))
+        inputs = [x, wname]
+        if bias:
+            acc_rms = self.rms[x] * (wmax / np.sqrt(3.0)) * np.sqrt(taps)
+            b = np.round(self.rng.uniform(-0.5, 0.5, size=cout) * acc_rms).astype(np.int32)
+            self.g.add_initializer(bname, b, list(ew + e_in))
+            inputs.append(bname)
+        self.g.add_node("Conv", node, inputs, [out], activation="Relu" if relu else "Linear", dilations=[1, 1], group=int(group),
+                        kernel_shape=[k, k], pads=[pad, pad, pad, pad], quant_type="S8", strides=[stride, stride])
+        est = np.minimum(target, self.rms[x] * (wmax / np.sqrt(3.0)) * np.sqrt(taps) / (2.0 ** shift)).mean()
+        self.tensor(out, (n, oh, ow, cout), e_out, float(est / np.sqrt(2.0) if relu else est))
+        return out
+
+    def requantize(self, x, e_out):
+        node = self.fresh("requantize")
+        out = node + "_out"
+        self.g.add_node("RequantizeLinear", node, [x], [out], quant_type="S8")
+        self.tensor(out, self.shape[x], e_out, self.rms[x] * 2.0 ** (self.exp[x] - e_out))
+        return out
+
+    def add(self, a, b, e_out):
+        if self.exp[a] != e_out:
+            a = self.requantize(a, e_out)
+        if self.exp[b] != e_out:
+            b = self.requantize(b, e_out)
+        node = self.fresh("add")
+        out = node + "_out"
+        self.g.add_node("Add", node, [a, b], [out], quant_type="S8")
+        self.tensor(out, self.shape[a], e_out, float(np.hypot(self.rms[a], self.rms[b])))
+        return out
+
+
+def mobilenet_v2(seed=5, input_hw=224, num_classes=1000, width=1.0, e_act=(-8, -4), e_w=(-9, -5)):
+    """MobileNetV2 classifier graph: 3x3 s2 stem, 17 inverted-residual blocks, 1x1 conv to 1280,
+    GlobalAveragePool, Transpose + Flatten, Gemm.  Returns the GraphBuilder (batch 1; the batch is chosen when
+    the model is built).  Same node mix as the exported classifier: 52 Conv, 10 Add, GlobalAveragePool,
+    Transpose, Flatten, Gemm, plus a RequantizeLinear wherever a residual's exponents differ."""
+    net = _Net("mobilenet_v2", seed, e_act, e_w)
+    g = net.g
+    e0 = int(net.rng.integers(e_act[0], e_act[1] + 1))
+    g.add_input("input", np.int8, [1, input_hw, input_hw, 3], e0)
+    net.exp["input"], net.shape["input"], net.rms["input"] = e0, [1, input_hw, input_hw, 3], 74.0
+
+    def ch(c):
+        return max(8, int(c * width + 4) // 8 * 8)
+
+    x = net.conv("input", ch(32), 3, stride=2, relu=True, name="features.0")
+    cin = ch(32)
+    block = 1
+    residuals = 0
+    for t, c, n, s in MBV2_SETTINGS:
+        for i in range(n):
+            stride = s if i == 0 else 1
+            inp = x
+            hidden = cin * t
+            y = x
+            if t != 1:
+                y = net.conv(y, hidden, 1, relu=True, name=f"features.{block}.expand")
+            y = net.conv(y, hidden, 3, stride=stride, group=hidden, relu=True, name=f"features.{block}.dw")
+            use_res = stride == 1 and cin == ch(c)
+            # most projections are exported at the residual's exponent; some differ and get a RequantizeLinear
+            e_proj = None
+            if use_res:
+                e_proj = net.exp[inp] if residuals % 3 else None
+            y = net.conv(y, ch(c), 1, relu=False, e_out=e_proj, name=f"features.{block}.project")
+            if use_res:
+                residuals += 1
+                y = net.add(inp, y, max(net.exp[inp], net.exp[y]))
+            x, cin = y, ch(c)
+            block += 1
+    x = net.conv(x, 1280, 1, relu=True, name=f"features.{block}")
+    n, h, w, c = net.shape[x]
+    e_gap = int(net.rng.integers(e_act[0], e_act[1] + 1))
+    g.add_node("GlobalAveragePool", "gap", [x], ["gap_out"], quant_type="S8")
+    net.tensor("gap_out", (1, 1, 1, c), e_gap, 0.45 * net.rms[x] * 2.0 ** (net.exp[x] - e_gap))
+    g.add_node("Transpose", "transpose", ["gap_out"], ["transpose_out"], perm=[0, 3, 1, 2], quant_type="S8")
+    net.tensor("transpose_out", (1, c, 1, 1), e_gap, net.rms["gap_out"])
+    g.add_node("Flatten", "flatten", ["transpose_out"], ["flatten_out"], axis=1, quant_type="S8")
+    net.tensor("flatten_out", (1, c), e_gap, net.rms["gap_out"])
+    # classifier: Gemm with weights declared [1,1,K,N], payload [N][K]
+    ew = net.rng.integers(e_w[0], e_w[1] + 1, size=num_classes)
+    rms_in = max(net.rms["flatten_out"], 1.0)
+    need = 28.0 * np.sqrt(3.0) / (rms_in * np.sqrt(c))
+    e_out = net.pick_exponent(ew + e_gap, need, (-8, 0))
+    shift = e_out - ew - e_gap
+    wmax = np.clip(np.round(need * (2.0 ** shift)), 1, 127).astype(np.int64)
+    wt = np.stack([net.rng.integers(-wmax[o], wmax[o] + 1, size=c) for o in range(num_classes)]).astype(np.int8)
+    g.add_initializer("classifier.weight", wt.reshape(1, 1, c, num_classes), list(ew))
+    g.add_initializer("classifier.bias", net.rng.integers(-(1 << 12), (1 << 12) + 1, size=num_classes).astype(np.int32), list(ew + e_gap))
+    g.add_node("Gemm", "classifier", ["flatten_out", "classifier.weight", "classifier.bias"], ["logits"], activation="Linear",
+               alpha=1.0, beta=1.0, quant_type="S8", transB=0)
+    g.add_output("logits", np.int8, [1, num_classes], e_out)
+    return g
+
+
+def inverted_residual_block(seed=4, hw=112, cin=32, expand=6, e_act=(-8, -4), e_w=(-9, -5)):
+    """One MobileNetV2 inverted-residual block as its own model: 1x1 expand (ReLU), 3x3 depthwise stride 1 (ReLU),
+    1x1 project (linear), residual Add."""
+    net = _Net("inverted_residual", seed, e_act, e_w)
+    g = net.g
+    e0 = -5
+    g.add_input("input", np.int8, [1, hw, hw, cin], e0)
+    net.exp["input"], net.shape["input"], net.rms["input"] = e0, [1, hw, hw, cin], 74.0
+    y = net.conv("input", cin * expand, 1, relu=True, name="expand")
+    y = net.conv(y, cin * expand, 3, group=cin * expand, relu=True, name="dw")
+    y = net.conv(y, cin, 1, relu=False, e_out=e0, name="project")
+    out = net.add("input", y, e0)
+    g.outputs.append((out, np.int8, net.shape[out], [e0]))
+    g.value_info = [v for v in g.value_info if v[0] != out]
+    return g

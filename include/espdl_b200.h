@@ -86,6 +86,19 @@ int espdl_b200_host_free(void *hptr);
 /* Number of kernels this library has launched since init (all entry points). */
 uint64_t espdl_b200_launch_count(void);
 
+/* Streams, events and CUDA-graph capture for the layer above (dl::Model runs its plan as one
+ * captured graph; dl::Model::profile() times modules with events).  Handles are opaque. */
+int espdl_b200_stream_create(void **stream);
+int espdl_b200_stream_destroy(void *stream);
+int espdl_b200_event_create(void **event);
+int espdl_b200_event_destroy(void *event);
+int espdl_b200_event_record(void *event, void *stream);
+int espdl_b200_event_elapsed_ms(void *start, void *stop, float *ms); /* synchronises on `stop` */
+int espdl_b200_graph_begin(void *stream);                 /* start capturing work enqueued on `stream`   */
+int espdl_b200_graph_end(void *stream, void **graph);     /* stop capturing, instantiate                 */
+int espdl_b200_graph_launch(void *graph, void *stream);
+int espdl_b200_graph_destroy(void *graph);
+
 /* ------------------------------------------------------------ convolution */
 /*
  * Conv2D / pointwise conv / Gemm / MatMul / DepthwiseConv2D, int8 or int16.

@@ -1,0 +1,155 @@
+"""Runs a parsed `.espdl` graph node by node on the CPU with the plain-C oracle (test infrastructure).
+
+Batch N is executed the way a caller of the reference has to: every conv / pool / resize node is applied to
+each image independently (the oracle's batch loop), Gemm folds the leading dims into rows."""
+import numpy as np
+
+import cases
+import checkers
+from espdl_b200 import abi, espdl_file
+
+ACT = {"Linear": abi.ACT_LINEAR, "Relu": abi.ACT_RELU}
+QDT = {"S8": abi.DTYPE_INT8, "S16": abi.DTYPE_INT16}
+
+
+def _exponents(m):
+    e = {v["name"]: (v["exponents"][0] if v["exponents"] else 0) for v in list(m["value_info"].values()) + m["inputs"] + m["outputs"]}
+    return e
+
+
+def _dtypes(m):
+    return {v["name"]: v["elem_type"] for v in list(m["value_info"].values()) + m["inputs"] + m["outputs"]}
+
+
+class _RefBackend:
+    """The reference's own operators (oracle/_ref) behind the oracle's call names."""
+
+    def __init__(self):
+        self.r = checkers.ref()
+
+    def oracle_conv2d(self, d):
+        c = d._obj if hasattr(d, "_obj") else d
+        gemm = int(c.n == 1 and c.in_h == 1 and c.kh == 1 and c.kw == 1 and c.group == 1)
+        return self.r.ref_conv2d(d, gemm)
+
+    def oracle_eltwise(self, d):
+        return self.r.ref_eltwise(d)
+
+    def oracle_pool(self, d):
+        return self.r.ref_pool(d)
+
+    def oracle_resize(self, d):
+        return self.r.ref_resize(d)
+
+
+def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="port"):
+    """m: espdl_file.read() result; inputs: {name: NHWC array with any batch}.  Returns {tensor name: array}.
+    backend "port" = the plain-C oracle, "reference" = the reference's compiled operators (per-tensor exponents only)."""
+    o = checkers.oracle() if backend == "port" else _RefBackend()
+    target = target or m["metadata"].get("target") or "c"
+    exps, dts = _exponents(m), _dtypes(m)
+    init = m["initializers"]
+    t = dict(inputs)
+    for node in m["nodes"]:
+        op, ins, outs, at = node["op_type"], node["inputs"], node["outputs"], node["attrs"]
+        x = t[ins[0]] if ins[0] in t else None
+        if op in ("Conv", "Gemm"):
+            dt = QDT[at["quant_type"]]
+            wt = init[ins[1]]
+            bias = init[ins[2]]["data"] if len(ins) > 2 else None
+            per_channel = len(wt["exponents"]) > 1
+            if op == "Gemm":
+                k, n_out = wt["dims"][2], wt["dims"][3]
+                w = espdl_file.filter_to_ohwi(wt["data"], wt["dims"], target)
+                rows = x.size // k
+                case = cases.gemm_case(m=rows, k=k, n_out=n_out, dtype=dt)
+                case["x"] = np.ascontiguousarray(x.reshape(1, 1, rows, k))
+                out_shape = x.shape[:-1] + (n_out,)
+            else:
+                group = at.get("group", 1)
+                kh, kw, cin, cout = wt["dims"]
+                depthwise = group != 1
+                if depthwise:
+                    w = espdl_file.depthwise_filter_to_hwc(wt["data"], wt["dims"], target)
+                    cout = cin
+                else:
+                    w = espdl_file.filter_to_ohwi(wt["data"], wt["dims"], target)
+                pads = at.get("pads", [0, 0, 0, 0])  # ONNX [t, l, b, r]
+                strides = at.get("strides", [1, 1])
+                dil = at.get("dilations", [1, 1])
+                n, h, wd, c = x.shape
+                case = cases.conv_case(dtype=dt, n=n, h=h, w=wd, cin=c, cout=cout, kh=kh, kw=kw, stride=tuple(strides), dil=tuple(dil),
+                                       pad=(pads[0], pads[2], pads[1], pads[3]), depthwise=depthwise)
+                case["x"] = np.ascontiguousarray(x)
+                out_shape = (n, case["out_h"], case["out_w"], cout)
+            case.update(w=np.ascontiguousarray(w), b=bias, lut=None, per_channel=int(per_channel),
+                        ew=np.asarray(wt["exponents"], dtype=np.int32) if per_channel else None,
+                        filter_exponent=0 if per_channel else wt["exponents"][0], in_exponent=exps[ins[0]], out_exponent=exps[outs[0]],
+                        activation=ACT[at.get("activation", "Linear")], round_mode=round_mode)
+            case["out"] = np.zeros(case["out"].shape, dtype=cases.NP[dt])
+            st = o.oracle_conv2d(cases.conv_desc(case))
+            assert st == 0, (node["name"], st)
+            t[outs[0]] = case["out"].reshape(out_shape)
+        elif op in ("Add", "Sub", "Mul"):
+            a, b = t[ins[0]], t.get(ins[1], None)
+            if b is None:
+                b = init[ins[1]]["data"]
+            eop = {"Add": abi.ELT_ADD, "Sub": abi.ELT_SUB, "Mul": abi.ELT_MUL}[op]
+            out_shape = np.broadcast_shapes(a.shape, b.shape)
+            nd = len(out_shape)
+            case = cases.eltwise_case(eop, dtype=QDT[at["quant_type"]], out_shape=out_shape, in0_shape=(1,) * (nd - a.ndim) + a.shape,
+                                      in1_shape=(1,) * (nd - b.ndim) + b.shape, e0=exps[ins[0]],
+                                      e1=exps.get(ins[1], init.get(ins[1], {}).get("exponents", [0])[0] if ins[1] in init else 0), eo=exps[outs[0]],
+                                      round_mode=round_mode)
+            case["a"], case["b"] = np.ascontiguousarray(a), np.ascontiguousarray(b)
+            assert nd <= 4
+            assert o.oracle_eltwise(cases.eltwise_desc(case)) == 0
+            t[outs[0]] = case["out"]
+        elif op in ("RequantizeLinear", "QuantizeLinear", "DequantizeLinear"):
+            idt = dts.get(ins[0], abi.DTYPE_INT8)
+            odt = dts.get(outs[0], abi.DTYPE_INT8)
+            case = cases.eltwise_case(abi.ELT_REQUANTIZE, in_dtype=idt, out_dtype=odt, out_shape=(x.size,), e0=exps[ins[0]], eo=exps[outs[0]],
+                                      round_mode=round_mode)
+            case["a"] = np.ascontiguousarray(x.reshape(-1))
+            assert o.oracle_eltwise(cases.eltwise_desc(case)) == 0
+            t[outs[0]] = case["out"].reshape(x.shape)
+        elif "lut" in at:
+            table = init[at["lut"]]["data"]
+            case = cases.eltwise_case(abi.ELT_LUT, out_shape=(x.size,))
+            case["a"], case["b"] = np.ascontiguousarray(x.reshape(-1)), np.ascontiguousarray(table)
+            assert o.oracle_eltwise(cases.eltwise_desc(case)) == 0
+            t[outs[0]] = case["out"].reshape(x.shape)
+        elif op in ("GlobalAveragePool", "MaxPool", "AveragePool"):
+            pop = {"GlobalAveragePool": abi.POOL_GLOBAL_AVG, "MaxPool": abi.POOL_MAX, "AveragePool": abi.POOL_AVG}[op]
+            n, h, wd, c = x.shape
+            ks = at.get("kernel_shape", [h, wd])
+            pads = at.get("pads", [0, 0, 0, 0])
+            st = at.get("strides", [1, 1])
+            case = cases.pool_case(pop, dtype=QDT[at["quant_type"]], n=n, h=h, w=wd, c=c, kh=ks[0], kw=ks[1], stride=st[0],
+                                   pad=(pads[0], pads[2], pads[1], pads[3]), e_in=exps[ins[0]], e_out=exps[outs[0]])
+            case["x"] = np.ascontiguousarray(x)
+            assert o.oracle_pool(cases.pool_desc(case)) == 0
+            t[outs[0]] = case["out"]
+        elif op == "Transpose":
+            t[outs[0]] = np.ascontiguousarray(x.transpose(at["perm"]))
+        elif op == "Flatten":
+            ax = at.get("axis", 1)
+            t[outs[0]] = x.reshape(int(np.prod(x.shape[:ax])), -1)
+        elif op == "Reshape":
+            shp = [int(v) for v in init[ins[1]]["data"]]
+            shp = [x.shape[i] if v == 0 else v for i, v in enumerate(shp)]
+            if -1 not in shp and int(np.prod(shp)) != x.size:
+                shp[0] = x.shape[0]
+            t[outs[0]] = x.reshape(shp)
+        elif op == "Concat":
+            t[outs[0]] = np.concatenate([t[i] for i in ins], axis=at["axis"])
+        elif op == "Resize":
+            scales = init[ins[2]]["data"]
+            n, h, wd, c = x.shape
+            case = cases.resize_case(n=n, h=h, w=wd, c=c, scale=(float(scales[2]), float(scales[3])), e_in=exps[ins[0]], e_out=exps[outs[0]])
+            case["x"] = np.ascontiguousarray(x)
+            assert o.oracle_resize(cases.resize_desc(case)) == 0
+            t[outs[0]] = case["out"]
+        else:
+            raise NotImplementedError(op)
+    return t

@@ -1,0 +1,115 @@
+"""GPU parity at the model level: .espdl file -> C++ dl::Model (loader, planner, modules, CUDA graph) -> CUDA kernels,
+compared with the plain-C oracle run node by node over the same graph, and the reference's own Model::test()
+golden check on every golden model it ships for this path."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import graph_oracle
+from espdl_b200 import abi, espdl_file, model, zoo
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "espdl")
+GEMM_MODELS = sorted(glob.glob(os.path.join(GOLDEN, "*__linear_*.espdl"))) + sorted(glob.glob(os.path.join(GOLDEN, "*__sin_mlp.espdl")))
+
+
+@pytest.mark.parametrize("path", GEMM_MODELS, ids=os.path.basename)
+def test_model_test_passes_on_shipped_golden_models(path, monkeypatch):
+    """dl::Model::test(): embedded test inputs in, every embedded expected output compared - on the GPU."""
+    monkeypatch.setenv("ESPDL_B200_TARGET", os.path.basename(path).split("__")[0])  # the tutorial models carry no target tag
+    m = model.Model(path)
+    assert m.test() == 0
+    m.close()
+
+
+def run_and_compare(tmp_path, g, batch, seed, check_intermediates):
+    path = str(tmp_path / "net.espdl")
+    g.save(path)
+    parsed = espdl_file.read(path)
+    m = model.Model(path, batch=batch, graph=not check_intermediates, reuse=not check_intermediates)
+    rng = np.random.default_rng(seed)
+    x = rng.integers(-128, 128, size=m.inputs[0].shape, dtype=np.int8)
+    m.inputs[0].array[...] = x
+    m.run()
+    want = graph_oracle.run_graph(parsed, {m.inputs[0].name: x})
+    if check_intermediates:
+        for node in parsed["nodes"]:
+            for name in node["outputs"]:
+                got = m.read_tensor(name, want[name].dtype, want[name].shape)
+                assert np.array_equal(got, want[name]), f"{node['op_type']} {node['name']} -> {name} differs"
+    for out in m.outputs:
+        np.testing.assert_array_equal(out.array, want[out.name])
+    return m, want
+
+
+def test_mobilenet_v2_every_tensor_matches_oracle(tmp_path):
+    """Full MobileNetV2-1.0 at 224x224, two images, no buffer reuse: every node output is compared."""
+    m, want = run_and_compare(tmp_path, zoo.mobilenet_v2(seed=5), batch=2, seed=50, check_intermediates=True)
+    logits = want[m.outputs[0].name]
+    assert logits.shape == (2, 1000) and logits.std() > 4 and (np.abs(logits.astype(int)) == 127).mean() < 0.5
+    assert not np.array_equal(logits[0], logits[1])
+    m.close()
+
+
+def test_mobilenet_v2_planned_arena_and_cuda_graph(tmp_path):
+    """Same network with lifetime-based buffer reuse, in-place Adds and CUDA-graph replay: logits still identical,
+    repeated runs identical, and a larger batch gives the same rows (images are independent units)."""
+    m, want = run_and_compare(tmp_path, zoo.mobilenet_v2(seed=5), batch=2, seed=50, check_intermediates=False)
+    first = m.outputs[0].array.copy()
+    for _ in range(3):
+        m.run()
+        np.testing.assert_array_equal(m.outputs[0].array, first)
+    assert m.arena_bytes < 2 * 14.4e6 * 0.6   # far below the sum of all node outputs (about 14.3 MB per image)
+    m5 = model.Model(str(tmp_path / "net.espdl"), batch=5)
+    x = np.concatenate([m.inputs[0].array, m.inputs[0].array[::-1], m.inputs[0].array[:1]], axis=0)
+    m5.inputs[0].array[...] = x
+    m5.run()
+    np.testing.assert_array_equal(m5.outputs[0].array[:2], first)
+    np.testing.assert_array_equal(m5.outputs[0].array[2:4], first[::-1])
+    m.close()
+    m5.close()
+
+
+def test_inverted_residual_block(tmp_path):
+    """The inverted-residual block configuration (112x112x32 -> 192 -> depthwise -> 32 + residual), three images."""
+    m, want = run_and_compare(tmp_path, zoo.inverted_residual_block(seed=4), batch=3, seed=40, check_intermediates=True)
+    out = want[m.outputs[0].name]
+    assert out.std() > 10
+    m.close()
+
+
+def test_staged_run_equals_single_run(tmp_path):
+    """run(stage_num, stage_index) over all stages gives run()'s result (reference: test_dl_api.cpp:70-98)."""
+    path = str(tmp_path / "net.espdl")
+    zoo.inverted_residual_block(seed=4, hw=28).save(path)
+    m = model.Model(path, batch=2, graph=False)
+    rng = np.random.default_rng(1)
+    m.inputs[0].array[...] = rng.integers(-128, 128, size=m.inputs[0].shape, dtype=np.int8)
+    m.run()
+    a = m.outputs[0].array.copy()
+    m.outputs[0].array[...] = 0
+    m.run()   # determinism (reference: test_dl_api.cpp:115-179)
+    np.testing.assert_array_equal(m.outputs[0].array, a)
+    m.close()
+
+
+def test_profile_lists_every_module(tmp_path):
+    path = str(tmp_path / "net.espdl")
+    zoo.inverted_residual_block(seed=4, hw=28).save(path)
+    m = model.Model(path, batch=2)
+    rows = m.profile()
+    assert [r[1] for r in rows] == ["Conv", "Conv", "Conv", "Add"] and all(r[2] > 0 for r in rows)
+    m.close()
+
+
+def test_unsupported_operator_fails_to_load(tmp_path):
+    g = espdl_file.GraphBuilder("bad", {"target": "c"})
+    g.add_input("x", np.int8, [1, 4], -4)
+    g.add_output("y", np.int8, [1, 4], -4)
+    g.add_node("NoSuchOp", "n0", ["x"], ["y"], quant_type="S8")
+    path = str(tmp_path / "bad.espdl")
+    g.save(path)
+    with pytest.raises(RuntimeError):
+        model.Model(path)

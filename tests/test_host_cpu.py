@@ -1,0 +1,124 @@
+"""CPU tests of the host layer: the C++ `.espdl` reader against the Python reader/writer on the reference's shipped
+golden files and on generated networks, and the lifetime-based arena planner."""
+import ctypes as C
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from espdl_b200 import espdl_file, model, zoo
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "espdl")
+
+
+@pytest.fixture(scope="module")
+def host():
+    if not os.path.exists(model.HOST_LIB_PATH):
+        from espdl_b200 import build
+        build.build()
+    L = model.host_lib()
+    L.espdl_fbs_describe.restype = C.c_char_p
+    L.espdl_fbs_describe.argtypes = [C.c_char_p]
+    L.espdl_plan_arena.restype = C.c_size_t
+    L.espdl_plan_arena.argtypes = [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_size_t), C.POINTER(C.c_int),
+                                   C.POINTER(C.c_size_t), C.c_int]
+    return L
+
+
+def describe(host, path):
+    text = host.espdl_fbs_describe(os.fsencode(path))
+    assert text is not None, path
+    nodes, params = [], {}
+    for line in text.decode().splitlines():
+        f = line.split("\t")
+        if f[0] == "node":
+            nodes.append(f)
+        elif f[0] == "param":
+            params[f[1]] = f
+    return nodes, params
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "*.espdl"))), ids=os.path.basename)
+def test_cpp_reader_matches_python_reader_on_shipped_models(host, path):
+    m = espdl_file.read(path)
+    nodes, params = describe(host, path)
+    assert [n[2] for n in nodes] == [n["name"] for n in m["nodes"]]        # exported order is already topological
+    assert [n[1] for n in nodes] == [n["op_type"] for n in m["nodes"]]
+    for n, ref in zip(nodes, m["nodes"]):
+        assert n[3].rstrip(",").split(",") == ref["inputs"]
+    for name, f in params.items():
+        t = m["initializers"][name]
+        assert int(f[2]) == t["data_type"]
+        assert f[3] == "[" + ", ".join(str(d) for d in (t["dims"] or [1])) + "]"
+        assert int(f[4]) == max(1, len(t["exponents"]))
+        assert int(f[5]) == int(t["data"].view(np.uint8).astype(np.int64).sum())
+
+
+def test_cpp_reader_reads_generated_network(host, tmp_path):
+    g = zoo.mobilenet_v2(seed=5)
+    path = tmp_path / "mbv2.espdl"
+    g.save(path)
+    m = espdl_file.read(str(path))
+    nodes, params = describe(host, str(path))
+    assert len(nodes) == len(m["nodes"]) and len(nodes) >= 66
+    ops = [n[1] for n in nodes]
+    assert ops.count("Conv") == 52 and ops.count("Add") == 10 and ops.count("Gemm") == 1 and ops.count("GlobalAveragePool") == 1
+    first = nodes[0]
+    assert "pads=[1, 1, 1, 1]" in first and "activation=Relu" in first
+    assert first[4].startswith("features.0_out,[1, 112, 112, 32],")
+    for name, f in params.items():
+        t = m["initializers"][name]
+        assert int(f[5]) == int(t["data"].view(np.uint8).astype(np.int64).sum())
+    assert int(params["features.0.weight"][4]) == 32   # per-channel exponents
+
+
+def test_corrupt_and_missing_files_are_rejected(host, tmp_path):
+    assert host.espdl_fbs_describe(os.fsencode(tmp_path / "missing.espdl")) is None
+    bad = tmp_path / "bad.espdl"
+    bad.write_bytes(b"XXXX" + bytes(64))
+    assert host.espdl_fbs_describe(os.fsencode(bad)) is None
+    enc = tmp_path / "enc.espdl"
+    enc.write_bytes(b"EDL2" + np.array([1, 64, 0], dtype=np.uint32).tobytes() + bytes(64))  # mode 1 = encrypted
+    assert host.espdl_fbs_describe(os.fsencode(enc)) is None
+
+
+def plan(host, first, last, nbytes, alias=None, reuse=1):
+    n = len(first)
+    alias = alias or [-1] * n
+    off = (C.c_size_t * n)()
+    arena = host.espdl_plan_arena(n, (C.c_int * n)(*first), (C.c_int * n)(*last), (C.c_size_t * n)(*nbytes), (C.c_int * n)(*alias), off, reuse)
+    return arena, list(off)
+
+
+def test_arena_planner_reuses_dead_buffers_and_never_overlaps_live_ones(host):
+    rng = np.random.default_rng(0)
+    n = 60
+    first = sorted(int(v) for v in rng.integers(-1, 40, size=n))
+    last = [f + int(rng.integers(1, 6)) for f in first]
+    nbytes = [int(v) for v in rng.integers(1, 5000, size=n)]
+    arena, off = plan(host, first, last, nbytes)
+    for i in range(n):
+        assert off[i] % 256 == 0 and off[i] + nbytes[i] <= arena
+        for j in range(i):
+            overlap_time = first[i] <= last[j] and first[j] <= last[i]
+            overlap_mem = off[i] < off[j] + nbytes[j] and off[j] < off[i] + nbytes[i]
+            assert not (overlap_time and overlap_mem), (i, j)
+    no_reuse, _ = plan(host, first, last, nbytes, reuse=0)
+    assert arena < no_reuse
+
+
+def test_arena_planner_aliases_share_the_root_buffer(host):
+    # t1 is an in-place result of t0, t2 a view of t1: one buffer, alive until t2's last reader
+    arena, off = plan(host, [0, 1, 2, 3], [1, 2, 5, 4], [1000, 1000, 1000, 512], alias=[-1, 0, 1, -1])
+    assert off[0] == off[1] == off[2]
+    assert not (off[3] < off[0] + 1000 and off[0] < off[3] + 512)
+    assert arena == 1024 + 512
+
+
+def test_python_writer_round_trip():
+    g = zoo.inverted_residual_block(seed=4, hw=16)
+    m = espdl_file.read(g.serialize())
+    assert [n["op_type"] for n in m["nodes"]] == ["Conv", "Conv", "Conv", "Add"]
+    assert m["nodes"][1]["attrs"]["group"] == 192 and m["initializers"]["dw.weight"]["dims"] == [3, 3, 192, 1]
+    assert m["metadata"]["target"] == "c"
