@@ -142,6 +142,94 @@ __global__ void __launch_bounds__(256) conv_s16_kernel(ConvParams p)
     }
 }
 
+// Stem-style convolutions (a handful of input channels, e.g. the 3-channel 3x3 stride-2 first layer of an image
+// network): K = kh*kw*in_c is tiny, so the whole filter bank sits in shared memory packed four taps per 32-bit
+// word, each thread gathers the K input bytes of ONE output pixel into registers once and then produces every
+// output channel of that pixel with dp4a.  Output bytes of a pixel are contiguous, so stores are 128-bit.
+constexpr int SMALL_MAX_WORDS = 16; // K <= 64
+constexpr int SMALL_MAX_OC = 64;
+
+template <int KH, int KW, int IC>
+__global__ void __launch_bounds__(256) conv_s8_small_k_kernel(ConvParams p)
+{
+    __shared__ int w_s[SMALL_MAX_OC * SMALL_MAX_WORDS];
+    __shared__ int bias_s[SMALL_MAX_OC];
+    __shared__ int shift_s[SMALL_MAX_OC];
+    constexpr int K = KH * KW * IC;
+    constexpr int words = (K + 3) / 4;
+    static_assert(words <= SMALL_MAX_WORDS, "filter too large for the small-K kernel");
+    const int8_t *__restrict__ in = (const int8_t *)p.in;
+    const int8_t *__restrict__ w = (const int8_t *)p.w;
+    for (int i = threadIdx.x; i < p.oc * words; i += blockDim.x) {
+        const int oc = i / words, wd = i % words;
+        uint32_t v = 0;
+        for (int b = 0; b < 4; b++) {
+            const int k = wd * 4 + b;
+            if (k < K)
+                v |= ((uint32_t)(uint8_t)w[(long long)oc * K + k]) << (8 * b);
+        }
+        w_s[i] = (int)v;
+    }
+    for (int oc = threadIdx.x; oc < p.oc; oc += blockDim.x) {
+        bias_s[oc] = p.bias ? ((const int32_t *)p.bias)[oc] : 0;
+        const int e = p.per_channel ? p.ew[oc] : p.ew_scalar;
+        shift_s[oc] = max(-31, min(31, p.e_shift_base - e));
+    }
+    __syncthreads();
+    const long long pixels = (long long)p.n * p.oh * p.ow;
+    const bool vec_store = (p.oc % 16 == 0) && (p.ops % 16 == 0) && (((uintptr_t)p.out) % 16 == 0);
+    for (long long pix = blockIdx.x * (long long)blockDim.x + threadIdx.x; pix < pixels; pix += (long long)gridDim.x * blockDim.x) {
+        const int ox = (int)(pix % p.ow);
+        const int oy = (int)((pix / p.ow) % p.oh);
+        const int n = (int)(pix / ((long long)p.ow * p.oh));
+        int a[words];
+#pragma unroll
+        for (int i = 0; i < words; i++) a[i] = 0;
+        // gather the K input bytes in filter order (ky, kx, c); taps outside the image stay 0
+#pragma unroll
+        for (int ky = 0; ky < KH; ky++) {
+            const int iy = oy * p.sh + ky * p.dh - p.pt;
+#pragma unroll
+            for (int kx = 0; kx < KW; kx++) {
+                const int ix = ox * p.sw + kx * p.dw - p.pl;
+                const bool inside = iy >= 0 && iy < p.ih && ix >= 0 && ix < p.iw;
+                const int8_t *ip = in + (((long long)n * p.ih + iy) * p.iw + ix) * p.ips;
+#pragma unroll
+                for (int c = 0; c < IC; c++) {
+                    constexpr int dummy = 0;
+                    (void)dummy;
+                    const int k = (ky * KW + kx) * IC + c; // compile-time after unrolling: a[] stays in registers
+                    const uint32_t v = inside ? (uint32_t)(uint8_t)__ldg(ip + c) : 0u;
+                    a[k >> 2] |= (int)(v << (8 * (k & 3)));
+                }
+            }
+        }
+        int8_t *op = (int8_t *)p.out + pix * p.ops;
+        for (int oc0 = 0; oc0 < p.oc; oc0 += 16) {
+            uint32_t pk[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int oc = oc0 + j;
+                if (oc < p.oc) {
+                    int acc = 0;
+                    const int *wr = w_s + oc * words;
+#pragma unroll
+                    for (int i = 0; i < words; i++) acc = __dp4a(a[i], wr[i], acc);
+                    int q = requant8(acc, bias_s[oc], shift_s[oc], p.relu, p.half_even);
+                    if (p.lut)
+                        q = p.lut[(uint8_t)q ^ 0x80u];
+                    pk[j >> 2] |= ((uint32_t)q & 0xffu) << (8 * (j & 3));
+                }
+            }
+            if (vec_store) {
+                *(uint4 *)(op + oc0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            } else {
+                for (int j = 0; j < 16 && oc0 + j < p.oc; j++) op[oc0 + j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
+            }
+        }
+    }
+}
+
 int conv2d_simt(const espdl_conv_desc &d, cudaStream_t s)
 {
     ConvParams p;
@@ -162,7 +250,16 @@ int conv2d_simt(const espdl_conv_desc &d, cudaStream_t s)
     const long long max_blocks = (long long)num_sms() * 32;
     if (blocks > max_blocks)
         blocks = max_blocks;
-    if (d.dtype == ESPDL_DTYPE_INT8) {
+    if (d.dtype == ESPDL_DTYPE_INT8 && d.out_c <= SMALL_MAX_OC && d.kh == 3 && d.kw == 3 && (d.in_c == 3 || d.in_c == 1 || d.in_c == 4)) {
+        const long long pixels = (long long)d.n * d.out_h * d.out_w;
+        const unsigned grid = (unsigned)min((pixels + threads - 1) / threads, max_blocks);
+        if (d.in_c == 3)
+            conv_s8_small_k_kernel<3, 3, 3><<<grid, threads, 0, s>>>(p);
+        else if (d.in_c == 1)
+            conv_s8_small_k_kernel<3, 3, 1><<<grid, threads, 0, s>>>(p);
+        else
+            conv_s8_small_k_kernel<3, 3, 4><<<grid, threads, 0, s>>>(p);
+    } else if (d.dtype == ESPDL_DTYPE_INT8) {
         const bool dp4a = d.in_c % 4 == 0 && p.ips % 4 == 0 && ((uintptr_t)d.input % 4) == 0 && ((uintptr_t)d.filter % 4) == 0;
         if (dp4a)
             conv_s8_kernel<OCT, true><<<(unsigned)blocks, threads, 0, s>>>(p);

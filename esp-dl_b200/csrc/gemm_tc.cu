@@ -52,9 +52,16 @@ int read_and_clear_device_error()
 namespace {
 
 constexpr int BLOCK_M = 128;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320; // 1 TMA warp + 1 MMA warp + 2 x 4 epilogue warps
 constexpr int MAX_STAGES = 12;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+// Per-output-channel epilogue constants staged in shared memory.
+struct EpiParams {
+    long long bias; // int32 (int8 op) or int64 (int16 op) bias
+    int shift;      // out_exponent - filter_exponent[n] - in_exponent, clamped
+    int bias_half;  // bias + 2^(shift-1), used by the overflow-free fast form
+};
 
 struct TcParams {
     int M, N, K;
@@ -166,6 +173,22 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, int32_t (&v)[16])
 
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// OR-reduction of a predicate over the 128 threads of one epilogue group (named barrier `bar_id`).
+__device__ __forceinline__ int __syncthreads_or_group(int pred, int bar_id, int *flag)
+{
+    if ((threadIdx.x & 127) == 64 % 128 && false)
+        *flag = 0;
+    // thread 0 of the group clears, everyone ORs, everyone reads
+    const int et = (threadIdx.x - 64) & 127;
+    if (et == 0)
+        *flag = 0;
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    if (pred)
+        atomicOr(flag, 1);
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    return *flag;
+}
+
 // Shared-memory matrix descriptor, K-major operand, swizzled rows of `swz` bytes:
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4 (unused here)
 //   bits [32,46) stride byte offset >> 4 (distance between 8-row groups = 8 * swz)
@@ -203,12 +226,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_bytes = p.block_n * p.swz;
     const int stage_bytes = NPLANE * (a_bytes + b_bytes);
     uint8_t *aux = smem + (size_t)p.stages * stage_bytes;
-    long long *bias_s = (long long *)aux;                 // block_n x 8 bytes
-    int *shift_s = (int *)(aux + 8 * p.block_n);           // block_n x 4 bytes
-    uint64_t *bars = (uint64_t *)(aux + 12 * p.block_n);   // 8-byte aligned: block_n % 16 == 0
+    // aux: 2 x block_n EpiParams (one set per epilogue group, 16 bytes each), then the barriers
+    uint64_t *bars = (uint64_t *)(aux + 2 * sizeof(EpiParams) * p.block_n);
     uint64_t *full_bar = bars, *empty_bar = bars + MAX_STAGES, *tfull_bar = bars + 2 * MAX_STAGES, *tempty_bar = tfull_bar + 2;
     uint32_t *tmem_slot = (uint32_t *)(tempty_bar + 2);
     int *abort_flag = (int *)(tmem_slot + 1);
+    int *par_flags = abort_flag + 1; // [2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
@@ -335,24 +358,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
-        const int et = threadIdx.x - 64;          // 0..127
-        const int lane_group = warp & 3;          // TMEM lanes this warp may read: 32*lane_group ..
+        // ------------------------------------------------------------ epilogue (warps 2..9)
+        // Two groups of four warps; group g owns TMEM accumulator g and every second tile, so the epilogue of one
+        // tile overlaps the accumulator read latency of the other.  (int16: one accumulator set, group 0 only.)
+        const int group = (warp - 2) >> 2;
+        const int et = (threadIdx.x - 64) & 127;  // thread index inside the group
+        const int lane_group = warp & 3;          // TMEM lanes this warp may read: 32*lane_group .. +31
         const int row_in_tile = lane_group * 32 + lane;
-        int acc = 0;
+        EpiParams *par = (EpiParams *)(aux) + (size_t)group * p.block_n;
+        const int acc = group;
         uint32_t acc_phase = 0;
         int loaded_n0 = -1;
+        bool fast = false;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int bar_id = 1 + group;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+            if (local % p.acc_stages != group)
+                continue;
             const int m0 = (tile / p.n_tiles) * BLOCK_M;
             const int n0 = (tile % p.n_tiles) * p.block_n;
             if (n0 != loaded_n0) {
                 // per-channel bias and shift of this N tile (kept across tiles when there is one N tile)
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                int slow = 0;
                 for (int j = et; j < p.block_n; j += 128) {
                     const int n = n0 + j;
                     long long b = 0;
-                    int sh = 0;
+                    int sh = 1;
                     if (n < p.N) {
                         if (p.bias)
                             b = I16 ? ((const long long *)p.bias)[n] : (long long)((const int32_t *)p.bias)[n];
@@ -360,58 +393,109 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const int lim = I16 ? 62 : 31;
                         sh = max(-lim, min(lim, p.e_shift_base - e));
                     }
-                    bias_s[j] = b;
-                    shift_s[j] = sh;
+                    // Fast form q = (acc + bias + 2^(s-1)) >> s: equal to the reference's wrap-add / 64-bit round as long as
+                    // nothing can overflow 32 bits: |acc| <= 2^14 * K < 2^29, |bias| < 2^30, 1 <= s <= 24.
+                    if (sh < 1 || sh > 24 || b >= (1ll << 30) || b <= -(1ll << 30))
+                        slow = 1;
+                    par[j].bias = b;
+                    par[j].shift = sh;
+                    par[j].bias_half = (int)b + (1 << (max(1, min(24, sh)) - 1));
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int any_slow = __syncthreads_or_group(slow, bar_id, &par_flags[group]);
+                fast = !I16 && !any_slow && !p.half_even && !p.lut && p.K <= 32768;
                 loaded_n0 = n0;
             }
             if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase)) {
                 ok = false;
                 break;
             }
+            acc_phase ^= 1;
             tc_fence_after();
             const long long m = (long long)m0 + row_in_tile;
             const uint32_t t0 = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * NACC * p.block_n);
-            for (int c0 = 0; c0 < p.block_n; c0 += 16) {
-                int32_t v[16];
-                tc_ld16(t0 + c0, v);
-                if (!I16) {
+            if (!I16 && fast) {
+                int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
+                const bool row_ok = m < p.M;
+                const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
+                for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+                    const bool two = c0 + 32 <= p.block_n;
+                    int32_t v[32];
+                    tc_ld16(t0 + c0, *(int32_t(*)[16]) & v[0]);
+                    if (two)
+                        tc_ld16(t0 + c0 + 16, *(int32_t(*)[16]) & v[16]);
                     tc_ld_wait();
-                    if (m < p.M && n0 + c0 < p.N) {
-                        uint32_t pk[4];
+                    uint32_t pk[8];
 #pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            uint32_t wd = 0;
+                    for (int q = 0; q < 8; q++) {
+                        int r[4];
 #pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const int j = c0 + q * 4 + i;
-                                int32_t r = requant8(v[q * 4 + i], (int32_t)bias_s[j], shift_s[j], p.relu, p.half_even);
-                                if (p.lut)
-                                    r = p.lut[(uint8_t)r ^ 0x80u];
-                                wd |= ((uint32_t)r & 0xffu) << (8 * i);
-                            }
-                            pk[q] = wd;
+                        for (int i = 0; i < 4; i++) {
+                            const EpiParams e = par[c0 + q * 4 + i];
+                            int t = (v[q * 4 + i] + e.bias_half) >> e.shift;
+                            if (p.relu)
+                                t = max(t, 0);
+                            r[i] = t;
                         }
-                        int8_t *op = (int8_t *)p.out + m * p.ops + n0 + c0;
-                        if (n0 + c0 + 16 <= p.N && (((uintptr_t)op) & 15) == 0) {
-                            *(uint4 *)op = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        uint32_t hi, w;
+                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r[3]), "r"(r[2]));
+                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r[1]), "r"(r[0]), "r"(hi));
+                        pk[q] = w;
+                    }
+                    if (row_ok) {
+                        const int nvalid = p.N - (n0 + c0); // columns of this chunk inside the tensor
+                        if (vec_ok && nvalid >= 16) {
+                            *(uint4 *)(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            if (two && nvalid >= 32)
+                                *(uint4 *)(orow + c0 + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                            else if (two)
+                                for (int j = 16; j < 32 && j < nvalid; j++) orow[c0 + j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
                         } else {
-                            for (int j = 0; j < 16 && n0 + c0 + j < p.N; j++) op[j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
+                            const int lim = two ? 32 : 16;
+                            for (int j = 0; j < lim && j < nvalid; j++) orow[c0 + j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
                         }
                     }
-                } else {
-                    int32_t vm[16], vl[16];
-                    tc_ld16(t0 + p.block_n + c0, vm);
-                    tc_ld16(t0 + 2 * p.block_n + c0, vl);
-                    tc_ld_wait();
-                    if (m < p.M && n0 + c0 < p.N) {
-                        int16_t *op = (int16_t *)p.out + m * p.ops + n0 + c0;
+                }
+            } else {
+                for (int c0 = 0; c0 < p.block_n; c0 += 16) {
+                    int32_t v[16];
+                    tc_ld16(t0 + c0, v);
+                    if (!I16) {
+                        tc_ld_wait();
+                        if (m < p.M && n0 + c0 < p.N) {
+                            uint32_t pk[4];
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            if (n0 + c0 + j < p.N) {
-                                const long long a = ((long long)v[j] << 16) + ((long long)vm[j] << 8) + (long long)vl[j];
-                                op[j] = (int16_t)requant16(a, bias_s[c0 + j], shift_s[c0 + j], p.relu, p.half_even);
+                            for (int q = 0; q < 4; q++) {
+                                uint32_t wd = 0;
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    const int j = c0 + q * 4 + i;
+                                    int32_t r = requant8(v[q * 4 + i], (int32_t)par[j].bias, par[j].shift, p.relu, p.half_even);
+                                    if (p.lut)
+                                        r = p.lut[(uint8_t)r ^ 0x80u];
+                                    wd |= ((uint32_t)r & 0xffu) << (8 * i);
+                                }
+                                pk[q] = wd;
+                            }
+                            int8_t *op = (int8_t *)p.out + m * p.ops + n0 + c0;
+                            if (n0 + c0 + 16 <= p.N && (((uintptr_t)op) & 15) == 0) {
+                                *(uint4 *)op = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            } else {
+                                for (int j = 0; j < 16 && n0 + c0 + j < p.N; j++) op[j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
+                            }
+                        }
+                    } else {
+                        int32_t vm[16], vl[16];
+                        tc_ld16(t0 + p.block_n + c0, vm);
+                        tc_ld16(t0 + 2 * p.block_n + c0, vl);
+                        tc_ld_wait();
+                        if (m < p.M && n0 + c0 < p.N) {
+                            int16_t *op = (int16_t *)p.out + m * p.ops + n0 + c0;
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                if (n0 + c0 + j < p.N) {
+                                    const long long a = ((long long)v[j] << 16) + ((long long)vm[j] << 8) + (long long)vl[j];
+                                    op[j] = (int16_t)requant16(a, par[c0 + j].bias, par[c0 + j].shift, p.relu, p.half_even);
+                                }
                             }
                         }
                     }
@@ -421,10 +505,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(smem_u32(&tempty_bar[acc]));
-            if (++acc == p.acc_stages) {
-                acc = 0;
-                acc_phase ^= 1;
-            }
         }
         if (!ok && lane == 0) {
             atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
@@ -527,7 +607,7 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
         return false;
     p.tmem_cols = pow2;
     const size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
-    const size_t aux = 12 * (size_t)p.block_n + (2 * MAX_STAGES + 4) * 8 + 16;
+    const size_t aux = 2 * sizeof(EpiParams) * (size_t)p.block_n + (2 * MAX_STAGES + 4) * 8 + 32;
     int stages = (int)((SMEM_BUDGET - aux - 1024) / stage_bytes);
     if (stages < 2)
         return false;
@@ -608,7 +688,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
             return st;
     }
     const size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
-    size_t smem = 1024 + (size_t)p.stages * stage_bytes + 12 * (size_t)p.block_n + (2 * MAX_STAGES + 4) * 8 + 16;
+    size_t smem = 1024 + (size_t)p.stages * stage_bytes + 2 * sizeof(EpiParams) * (size_t)p.block_n + (2 * MAX_STAGES + 4) * 8 + 32;
     if (smem < 120 * 1024) // more than half an SM's shared memory: one CTA per SM, so TMEM allocation never waits on a neighbour
         smem = 120 * 1024;
     const int grid = min(p.m_tiles * p.n_tiles, num_sms());

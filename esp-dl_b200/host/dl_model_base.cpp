@@ -256,7 +256,11 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
         auto it = input_shapes.find(name);
         if (it != input_shapes.end())
             shape = it->second;
-        infos[add_info(name, shape, -1)].is_graph_io = true;
+        // Graph inputs keep their buffer for the model's lifetime (the reference lets later tensors reuse it):
+        // the plan can then be replayed on device-resident inputs without another upload.
+        TensorInfo &ti = infos[add_info(name, shape, -1)];
+        ti.is_graph_io = true;
+        ti.last = INT_MAX;
     }
     // shape inference, lifetimes and in-place links along the plan
     for (size_t step = 0; step < m_execution_plan.size(); step++) {

@@ -80,8 +80,9 @@ Conv::Conv(activation_type_t activation, std::vector<int> pads, std::vector<int>
 
 Conv::~Conv()
 {
-    if (m_dev_exponents)
-        espdl_b200_arena_free(m_dev_exponents);
+    for (void *p : {m_dev_exponents, m_grp_filter, m_grp_bias, m_grp_exponents})
+        if (p)
+            espdl_b200_arena_free(p);
 }
 
 std::vector<std::vector<int>> Conv::get_output_shape(std::vector<std::vector<int>> &input_shapes)
@@ -164,6 +165,45 @@ esp_err_t Conv::prepare(ModelContext *context)
     }
     if (m_lut && !m_lut->device && m_lut->to_device() != ESP_OK)
         return ESP_FAIL;
+    // pointwise int8 conv with Cin % 16 != 0: group g pixels so that g * Cin is a multiple of 16
+    TensorBase *input = context->get_tensor(m_inputs_index[0]);
+    TensorBase *bias = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
+    if (!m_gemm && !dw && input && input->shape.size() == 4 && quant_type == QUANT_TYPE_SYMM_8BIT && fs[0] == 1 && fs[1] == 1 &&
+        m_strides[0] == 1 && m_strides[1] == 1 && m_pads[0] + m_pads[1] + m_pads[2] + m_pads[3] == 0 && fs[2] % 16 != 0 && filter->data &&
+        !getenv("ESPDL_B200_NO_PIXEL_GROUPING")) {
+        const int cin = fs[2], cout = fs[3];
+        const long long pixels = (long long)input->shape[1] * input->shape[2];
+        for (int g : {2, 4, 8, 16}) {
+            if ((g * cin) % 16 == 0 && pixels % g == 0 && g * cin <= 256 && g * cout <= 2048) {
+                m_group_px = g;
+                break;
+            }
+        }
+        if (m_group_px > 1) {
+            const int g = m_group_px;
+            std::vector<int8_t> wf((size_t)g * cout * g * cin, 0);
+            const int8_t *w = (const int8_t *)filter->data; // [cout][cin]
+            for (int blk = 0; blk < g; blk++)
+                for (int o = 0; o < cout; o++)
+                    memcpy(&wf[((size_t)(blk * cout + o) * g + blk) * cin], w + (size_t)o * cin, cin);
+            std::vector<int32_t> bf, ef;
+            for (int blk = 0; blk < g; blk++)
+                for (int o = 0; o < cout; o++) {
+                    if (bias && bias->data)
+                        bf.push_back(((const int32_t *)bias->data)[o]);
+                    ef.push_back(filter->exponent.get(filter->exponent.is_per_channel() ? o : 0));
+                }
+            bool ok = espdl_b200_arena_alloc(wf.size(), &m_grp_filter) == ESPDL_OK &&
+                espdl_b200_upload(m_grp_filter, wf.data(), wf.size(), nullptr) == ESPDL_OK &&
+                espdl_b200_arena_alloc(ef.size() * 4, &m_grp_exponents) == ESPDL_OK &&
+                espdl_b200_upload(m_grp_exponents, ef.data(), ef.size() * 4, nullptr) == ESPDL_OK;
+            if (ok && !bf.empty())
+                ok = espdl_b200_arena_alloc(bf.size() * 4, &m_grp_bias) == ESPDL_OK &&
+                    espdl_b200_upload(m_grp_bias, bf.data(), bf.size() * 4, nullptr) == ESPDL_OK;
+            if (!ok || espdl_b200_stream_sync(nullptr) != ESPDL_OK)
+                return ESP_FAIL;
+        }
+    }
     return espdl_b200_stream_sync(nullptr) == ESPDL_OK ? ESP_OK : ESP_FAIL;
 }
 
@@ -209,6 +249,13 @@ int Conv::fill_desc(ModelContext *context, void *desc)
     d.in_exponent = input->exponent, d.out_exponent = output->exponent;
     d.per_channel = filter->exponent.is_per_channel();
     d.filter_exponent = filter->exponent;
+    if (m_group_px > 1) { // same bytes, g pixels per row: [N, 1, H*W/g, g*Cin] x block-diagonal filter -> [N, 1, H*W/g, g*Cout]
+        const int g = m_group_px;
+        d.in_w = d.in_h * d.in_w / g, d.in_h = 1, d.out_w = d.in_w, d.out_h = 1;
+        d.in_c *= g, d.out_c *= g;
+        d.filter = m_grp_filter, d.bias = m_grp_bias, d.filter_exponents = (const int32_t *)m_grp_exponents;
+        d.per_channel = 1;
+    }
     d.activation = activation == ReLU ? ESPDL_ACT_RELU : ESPDL_ACT_LINEAR;
     d.round_mode = context->round_mode;
     d.kernel = ESPDL_KERNEL_AUTO;

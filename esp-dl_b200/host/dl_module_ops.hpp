@@ -32,6 +32,11 @@ protected:
     std::string m_target;
     bool m_gemm = false;             ///< Gemm / MatMul view: rows = all leading dims
     void *m_dev_exponents = nullptr; ///< int32[out_c] on the device when the filter is per-channel
+    // Pixel grouping for pointwise convs whose channel count is not a multiple of 16 (the tensor-core tile kernel
+    // needs 16-byte rows): m_group_px consecutive pixels are treated as one pixel with m_group_px * Cin channels,
+    // and the filter becomes block diagonal, [g*Cout][g*Cin].  NHWC memory is unchanged on both sides.
+    int m_group_px = 1;
+    void *m_grp_filter = nullptr, *m_grp_bias = nullptr, *m_grp_exponents = nullptr;
     TensorBase *m_lut = nullptr;
     bool m_prepared = false;
 };
