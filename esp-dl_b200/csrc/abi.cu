@@ -139,7 +139,10 @@ int espdl_b200_stream_sync(void *stream)
 {
     ESPDL_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
     // a tile kernel whose bounded wait expired leaves its status in a device word
-    const int dev = read_and_clear_device_error();
+    int dev = read_and_clear_device_error();
+    const int dev_dw = read_and_clear_device_error_dw();
+    if (!dev)
+        dev = dev_dw;
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -316,8 +319,11 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
         return ESPDL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (desc->group != 1) {
-        if (desc->kernel == ESPDL_KERNEL_TCGEN05)
+        const bool dw_tc_ok = conv2d_dw_tc_supported(*desc);
+        if (desc->kernel == ESPDL_KERNEL_TCGEN05 && !dw_tc_ok)
             return ESPDL_ERR_UNSUPPORTED;
+        if (dw_tc_ok && desc->kernel != ESPDL_KERNEL_SIMT)
+            return conv2d_dw_tc(*desc, s);
         return conv2d_depthwise(*desc, s);
     }
     const bool tc_ok = conv2d_tc_supported(*desc);

@@ -30,6 +30,9 @@ bool conv2d_tc_supported(const espdl_conv_desc &d);
 size_t conv2d_tc_workspace_bytes(const espdl_conv_desc &d);
 int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes, cudaStream_t s);
 int read_and_clear_device_error(); // status word written by device-side bounded waits (0 = none)
+int read_and_clear_device_error_dw();
+bool conv2d_dw_tc_supported(const espdl_conv_desc &d);
+int conv2d_dw_tc(const espdl_conv_desc &d, cudaStream_t s);
 
 // ------------------------------------------------------------- device math
 // dl::tool::shift_and_round on a 32-bit accumulator (int8 operators).

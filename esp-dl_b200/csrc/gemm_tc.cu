@@ -6,30 +6,30 @@
 // epilogue esp-dl/dl/base/dl_base_activate_buffer.hpp:27-73), which is also what Gemm and MatMul
 // run (esp-dl/dl/module/include/dl_module_gemm.hpp:85-123).
 //
-// Structure (one persistent CTA per SM, 6 warps):
-//   warp 0   TMA producer: cp.async.bulk.tensor 2-D tiles of A (128 rows x SWZ bytes of K) and of
-//            W (BLOCK_N rows x SWZ bytes) into a ring of shared-memory stages, swizzled so that
-//            the MMA reads them without bank conflicts; rows/columns past the tensor are zero-filled
-//            by the TMA unit, so ragged M, N and K need no separate code.
-//   warp 1   MMA issuer: one thread issues tcgen05.mma kind::i8 (M=128, N=BLOCK_N, K=32 per
-//            instruction), accumulating int32 in TMEM; tcgen05.commit releases the stage and,
-//            at the end of a tile, hands the accumulator to the epilogue.
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (each thread owns one output row), add bias,
-//            ESP-DL's shift/round/saturate with per-channel shifts, ReLU, optional 8-bit LUT,
-//            and store NHWC rows with 128-bit writes.  Two TMEM accumulators let the epilogue
-//            of tile i overlap the MMAs of tile i+1.
+// Structure (one persistent CTA per SM, 18 warps):
+//   warp 0    TMA producer: cp.async.bulk.tensor 2-D tiles of A (128 rows x SWZ bytes of K) and of W (BLOCK_N rows x
+//             SWZ bytes) into a ring of shared-memory stages, swizzled so that the MMA reads them without bank
+//             conflicts; rows/columns past the tensor are zero-filled by the TMA unit, so ragged M, N and K need no
+//             separate code.
+//   warp 1    MMA issuer: one thread issues tcgen05.mma kind::i8 (M=128, N=BLOCK_N, K=32 per instruction), accumulating
+//             int32 in TMEM; tcgen05.commit releases the stage and, at the end of a tile, hands the accumulator over.
+//   warps 2-17 epilogue, four groups of four warps (a warp may read only its quarter of the 128 TMEM lanes).  With
+//             four accumulator buffers each group owns one buffer and every fourth tile; with two buffers two groups
+//             share a tile and split its columns.  Each thread owns one output row: tcgen05.ld, bias + ESP-DL's
+//             shift/round/saturate with per-channel shifts, ReLU, optional 8-bit LUT, 256-bit NHWC stores.
+//             Most layers the network workloads bring are memory bound with a few hundred int8 outputs per input
+//             row, so the epilogue's instruction count per output decides the kernel's speed: per-channel constants
+//             are staged once in shared memory in a form that needs one add and one shift per output (see
+//             tc_common.cuh), and saturation happens inside the pack instruction.
 //
-// int16 operands: Blackwell tensor cores have no 16-bit integer MMA.  Each operand is split into
-// a signed high byte and an unsigned low byte (x = 256*hi + lo); a pre-pass writes the byte planes
-// to scratch, and the tile kernel accumulates hi*hi, hi*lo + lo*hi and lo*lo in three TMEM
-// accumulators (kind::i8 takes signedness per operand), recombined in 64 bits by the epilogue.
-// This is exact as long as K <= 16384 (the partial sums stay below 2^31).
+// int16 operands: Blackwell tensor cores have no 16-bit integer MMA.  Each operand is split into a signed high byte
+// and an unsigned low byte (x = 256*hi + lo); a pre-pass writes the byte planes to scratch, and the tile kernel
+// accumulates hi*hi, hi*lo + lo*hi and lo*lo in three TMEM accumulators (kind::i8 takes signedness per operand),
+// recombined in 64 bits by the epilogue.  Exact as long as K <= 16384 (the partial sums stay below 2^31).
 //
-// Every mbarrier wait is bounded (about two seconds); on expiry the kernel records
-// ESPDL_ERR_TIMEOUT in a device word that espdl_b200_stream_sync reports, and all roles leave.
-#include "common.cuh"
-
-#include <cuda.h>
+// Every mbarrier wait is bounded (about two seconds); on expiry the kernel records ESPDL_ERR_TIMEOUT in a device word
+// that espdl_b200_stream_sync reports, and all roles leave.
+#include "tc_common.cuh"
 
 #include <mutex>
 
@@ -51,167 +51,26 @@ int read_and_clear_device_error()
 
 namespace {
 
-constexpr int BLOCK_M = 128;
-constexpr int NUM_THREADS = 320; // 1 TMA warp + 1 MMA warp + 2 x 4 epilogue warps
-constexpr int MAX_STAGES = 12;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+using namespace tc;
 
-// Per-output-channel epilogue constants staged in shared memory.
-struct EpiParams {
-    long long bias; // int32 (int8 op) or int64 (int16 op) bias
-    int shift;      // out_exponent - filter_exponent[n] - in_exponent, clamped
-    int bias_half;  // bias + 2^(shift-1), used by the overflow-free fast form
-};
+constexpr int BLOCK_M = 128;
+constexpr int EPI_WARPS = 16;
+constexpr int NUM_THREADS = 64 + EPI_WARPS * 32; // 1 TMA warp + 1 MMA warp + 16 epilogue warps
+constexpr int MAX_STAGES = 12;
+constexpr int MAX_ACC = 4;
 
 struct TcParams {
     int M, N, K;
     int block_n, n_tiles, m_tiles;
-    int swz;          // bytes of K per stage row: 32, 64 or 128
-    int k_blocks;     // ceil(K / swz)
+    int swz;        // bytes of K per stage row: 32, 64 or 128
+    int k_blocks;   // ceil(K / swz)
     int stages;
-    int acc_stages;   // TMEM accumulator buffers (2 for int8, 1 for int16)
-    int tmem_cols;    // power of two >= 32
+    int acc_stages; // TMEM accumulator buffers: 4 or 2 (int8), 1 (int16)
+    int tmem_cols;  // power of two >= 32
     void *out;
-    long long ops;    // output row stride in elements
-    const void *bias; // int32[N] or int64[N]
-    const int32_t *ew;
-    const int8_t *lut;
-    int e_shift_base, ew_scalar, per_channel, relu, half_even;
+    long long ops;  // output row stride in elements
+    EpiConfig epi;
 };
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
-{
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
-{
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar)
-{
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ unsigned long long globaltimer()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Bounded wait on an mbarrier phase.  Returns false when the limit expires.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t done = 0;
-    for (int spin = 0; spin < 64; spin++) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done)
-            return true;
-    }
-    const unsigned long long t0 = globaltimer();
-    while (true) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done)
-            return true;
-        if (globaltimer() - t0 > WAIT_LIMIT_NS)
-            return false;
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, int32_t (&v)[16])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// OR-reduction of a predicate over the 128 threads of one epilogue group (named barrier `bar_id`).
-__device__ __forceinline__ int __syncthreads_or_group(int pred, int bar_id, int *flag)
-{
-    if ((threadIdx.x & 127) == 64 % 128 && false)
-        *flag = 0;
-    // thread 0 of the group clears, everyone ORs, everyone reads
-    const int et = (threadIdx.x - 64) & 127;
-    if (et == 0)
-        *flag = 0;
-    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-    if (pred)
-        atomicOr(flag, 1);
-    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-    return *flag;
-}
-
-// Shared-memory matrix descriptor, K-major operand, swizzled rows of `swz` bytes:
-//   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4 (unused here)
-//   bits [32,46) stride byte offset >> 4 (distance between 8-row groups = 8 * swz)
-//   bits [46,48) descriptor version 1      bits [61,64) swizzle: 2 = 128B, 4 = 64B, 6 = 32B
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int swz)
-{
-    const uint64_t layout = swz == 128 ? 2ull : (swz == 64 ? 4ull : 6ull);
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)((8u * (uint32_t)swz) >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= layout << 61;
-    return d;
-}
-
-// Instruction descriptor of tcgen05.mma kind::i8: D = S32 (bits 4-5 = 2), A/B format at bits 7-9 /
-// 10-12 (0 = unsigned 8 bit, 1 = signed 8 bit), both operands K-major, N>>3 at bit 17, M>>4 at bit 24.
-__device__ __forceinline__ uint32_t make_idesc(int a_signed, int b_signed, int n)
-{
-    return (2u << 4) | ((uint32_t)a_signed << 7) | ((uint32_t)b_signed << 10) | ((uint32_t)(n >> 3) << 17) |
-        ((uint32_t)(BLOCK_M >> 4) << 24);
-}
 
 template <bool I16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -225,38 +84,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int a_bytes = BLOCK_M * p.swz;
     const int b_bytes = p.block_n * p.swz;
     const int stage_bytes = NPLANE * (a_bytes + b_bytes);
+    const int n_pad = p.n_tiles * p.block_n;
     uint8_t *aux = smem + (size_t)p.stages * stage_bytes;
-    // aux: 2 x block_n EpiParams (one set per epilogue group, 16 bytes each), then the barriers
-    uint64_t *bars = (uint64_t *)(aux + 2 * sizeof(EpiParams) * p.block_n);
-    uint64_t *full_bar = bars, *empty_bar = bars + MAX_STAGES, *tfull_bar = bars + 2 * MAX_STAGES, *tempty_bar = tfull_bar + 2;
-    uint32_t *tmem_slot = (uint32_t *)(tempty_bar + 2);
-    int *abort_flag = (int *)(tmem_slot + 1);
-    int *par_flags = abort_flag + 1; // [2]
+    FastParam *fast_s = (FastParam *)aux; // n_pad entries, 16-byte aligned (block_n % 16 == 0)
+    uint64_t *bars = (uint64_t *)(aux + sizeof(FastParam) * (size_t)n_pad);
+    uint64_t *full_bar = bars, *empty_bar = bars + MAX_STAGES, *tfull_bar = bars + 2 * MAX_STAGES, *tempty_bar = tfull_bar + MAX_ACC;
+    uint32_t *tmem_slot = (uint32_t *)(tempty_bar + MAX_ACC);
+    int *slow_flag = (int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
+    const int parts = 4 / p.acc_stages; // epilogue groups that share one tile (they split its columns)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        for (int a = 0; a < 2; a++) {
+        for (int a = 0; a < MAX_ACC; a++) {
             mbar_init(smem_u32(&tfull_bar[a]), 1);
-            mbar_init(smem_u32(&tempty_bar[a]), 4);
+            mbar_init(smem_u32(&tempty_bar[a]), 4 * parts);
         }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        *slow_flag = 0;
+        fence_barrier_init();
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(p.tmem_cols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
+    if (warp == 1)
+        tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
+    fence_before();
     __syncthreads();
-    tc_fence_after();
+    fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
@@ -288,10 +144,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                 }
             }
-            if (!ok) {
+            if (!ok)
                 atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
-                *abort_flag = 1;
-            }
         }
         __syncwarp();
     } else if (warp == 1) {
@@ -302,42 +156,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            const uint32_t idesc_ss = make_idesc(1, 1, p.block_n);
-            const uint32_t idesc_su = make_idesc(1, 0, p.block_n);
-            const uint32_t idesc_us = make_idesc(0, 1, p.block_n);
-            const uint32_t idesc_uu = make_idesc(0, 0, p.block_n);
+            const uint32_t idesc_ss = idesc_i8(1, 1, BLOCK_M, p.block_n);
+            const uint32_t idesc_su = idesc_i8(1, 0, BLOCK_M, p.block_n);
+            const uint32_t idesc_us = idesc_i8(0, 1, BLOCK_M, p.block_n);
+            const uint32_t idesc_uu = idesc_i8(0, 0, BLOCK_M, p.block_n);
             const int ksteps = p.swz / 32;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1)) {
                     ok = false;
                     break;
                 }
-                tc_fence_after();
+                fence_after();
                 const uint32_t d0 = tmem_base + (uint32_t)(acc * NACC * p.block_n);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
                         ok = false;
                         break;
                     }
-                    tc_fence_after();
+                    fence_after();
                     const uint32_t st = smem_u32(smem + (size_t)stage * stage_bytes);
-                    const uint64_t da = make_smem_desc(st, p.swz);
-                    const uint64_t db = make_smem_desc(st + NPLANE * a_bytes, p.swz);
+                    const uint64_t da = smem_desc_swizzled(st, p.swz);
+                    const uint64_t db = smem_desc_swizzled(st + NPLANE * a_bytes, p.swz);
                     for (int k = 0; k < ksteps; k++) {
                         const uint32_t accum = (kb | k) != 0;
                         const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K, in 16-byte units
                         if (!I16) {
-                            tc_mma_i8(d0, da + koff, db + koff, idesc_ss, accum);
+                            mma_i8(d0, da + koff, db + koff, idesc_ss, accum);
                         } else {
-                            const uint64_t da_lo = make_smem_desc(st + a_bytes, p.swz);
-                            const uint64_t db_lo = make_smem_desc(st + 2 * a_bytes + b_bytes, p.swz);
-                            tc_mma_i8(d0, da + koff, db + koff, idesc_ss, accum);                      // hi * hi
-                            tc_mma_i8(d0 + p.block_n, da + koff, db_lo + koff, idesc_su, accum);       // hi * lo
-                            tc_mma_i8(d0 + p.block_n, da_lo + koff, db + koff, idesc_us, 1u);          // lo * hi
-                            tc_mma_i8(d0 + 2 * p.block_n, da_lo + koff, db_lo + koff, idesc_uu, accum); // lo * lo
+                            const uint64_t da_lo = smem_desc_swizzled(st + a_bytes, p.swz);
+                            const uint64_t db_lo = smem_desc_swizzled(st + 2 * a_bytes + b_bytes, p.swz);
+                            mma_i8(d0, da + koff, db + koff, idesc_ss, accum);                      // hi * hi
+                            mma_i8(d0 + p.block_n, da + koff, db_lo + koff, idesc_su, accum);       // hi * lo
+                            mma_i8(d0 + p.block_n, da_lo + koff, db + koff, idesc_us, 1u);          // lo * hi
+                            mma_i8(d0 + 2 * p.block_n, da_lo + koff, db_lo + koff, idesc_uu, accum); // lo * lo
                         }
                     }
-                    tc_commit(smem_u32(&empty_bar[stage]));
+                    commit(smem_u32(&empty_bar[stage]));
                     if (++stage == p.stages) {
                         stage = 0;
                         phase ^= 1;
@@ -345,178 +199,125 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 if (!ok)
                     break;
-                tc_commit(smem_u32(&tfull_bar[acc]));
+                commit(smem_u32(&tfull_bar[acc]));
                 if (++acc == p.acc_stages) {
                     acc = 0;
                     acc_phase ^= 1;
                 }
             }
-            if (!ok) {
+            if (!ok)
                 atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
-                *abort_flag = 1;
-            }
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..9)
-        // Two groups of four warps; group g owns TMEM accumulator g and every second tile, so the epilogue of one
-        // tile overlaps the accumulator read latency of the other.  (int16: one accumulator set, group 0 only.)
-        const int group = (warp - 2) >> 2;
-        const int et = (threadIdx.x - 64) & 127;  // thread index inside the group
-        const int lane_group = warp & 3;          // TMEM lanes this warp may read: 32*lane_group .. +31
+        // ------------------------------------------------------------ epilogue (warps 2..17)
+        const int ew = warp - 2;
+        const int group = ew >> 2;               // 0..3
+        const int acc = group % p.acc_stages;    // accumulator buffer this group reads
+        const int part = group / p.acc_stages;   // which share of the tile's columns
+        const int lane_group = warp & 3;         // TMEM lanes this warp may read: 32*lane_group .. +31
         const int row_in_tile = lane_group * 32 + lane;
-        EpiParams *par = (EpiParams *)(aux) + (size_t)group * p.block_n;
-        const int acc = group;
-        uint32_t acc_phase = 0;
-        int loaded_n0 = -1;
+        const int et = threadIdx.x - 64;
+
+        // per-channel constants for every output channel, once per kernel
         bool fast = false;
+        if (!I16) {
+            stage_fast_params(p.epi, fast_s, p.N, n_pad, et, EPI_WARPS * 32, slow_flag);
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+            fast = !*slow_flag && !p.epi.half_even && !p.epi.lut && p.K <= 32768;
+        }
+        uint32_t acc_phase = 0;
         bool ok = true;
-        const int bar_id = 1 + group;
         int local = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
-            if (local % p.acc_stages != group)
+            if (local % p.acc_stages != acc)
                 continue;
             const int m0 = (tile / p.n_tiles) * BLOCK_M;
             const int n0 = (tile % p.n_tiles) * p.block_n;
-            if (n0 != loaded_n0) {
-                // per-channel bias and shift of this N tile (kept across tiles when there is one N tile)
-                asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-                int slow = 0;
-                for (int j = et; j < p.block_n; j += 128) {
-                    const int n = n0 + j;
-                    long long b = 0;
-                    int sh = 1;
-                    if (n < p.N) {
-                        if (p.bias)
-                            b = I16 ? ((const long long *)p.bias)[n] : (long long)((const int32_t *)p.bias)[n];
-                        const int e = p.per_channel ? p.ew[n] : p.ew_scalar;
-                        const int lim = I16 ? 62 : 31;
-                        sh = max(-lim, min(lim, p.e_shift_base - e));
-                    }
-                    // Fast form q = (acc + bias + 2^(s-1)) >> s: equal to the reference's wrap-add / 64-bit round as long as
-                    // nothing can overflow 32 bits: |acc| <= 2^14 * K < 2^29, |bias| < 2^30, 1 <= s <= 24.
-                    if (sh < 1 || sh > 24 || b >= (1ll << 30) || b <= -(1ll << 30))
-                        slow = 1;
-                    par[j].bias = b;
-                    par[j].shift = sh;
-                    par[j].bias_half = (int)b + (1 << (max(1, min(24, sh)) - 1));
-                }
-                const int any_slow = __syncthreads_or_group(slow, bar_id, &par_flags[group]);
-                fast = !I16 && !any_slow && !p.half_even && !p.lut && p.K <= 32768;
-                loaded_n0 = n0;
-            }
             if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase)) {
                 ok = false;
                 break;
             }
             acc_phase ^= 1;
-            tc_fence_after();
+            fence_after();
             const long long m = (long long)m0 + row_in_tile;
+            const bool row_ok = m < p.M;
             const uint32_t t0 = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * NACC * p.block_n);
-            if (!I16 && fast) {
+            if (!I16) {
                 int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
-                const bool row_ok = m < p.M;
                 const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
-                for (int c0 = 0; c0 < p.block_n; c0 += 32) {
+                int chunk = 0;
+                for (int c0 = 0; c0 < p.block_n; c0 += 32, chunk++) {
+                    if (chunk % parts != part)
+                        continue;
                     const bool two = c0 + 32 <= p.block_n;
                     int32_t v[32];
-                    tc_ld16(t0 + c0, *(int32_t(*)[16]) & v[0]);
+                    ld16(t0 + c0, v);
                     if (two)
-                        tc_ld16(t0 + c0 + 16, *(int32_t(*)[16]) & v[16]);
-                    tc_ld_wait();
-                    uint32_t pk[8];
-#pragma unroll
-                    for (int q = 0; q < 8; q++) {
-                        int r[4];
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const EpiParams e = par[c0 + q * 4 + i];
-                            int t = (v[q * 4 + i] + e.bias_half) >> e.shift;
-                            if (p.relu)
-                                t = max(t, 0);
-                            r[i] = t;
+                        ld16(t0 + c0 + 16, v + 16);
+                    ld_wait();
+                    uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    if (fast) {
+                        if (p.epi.relu) {
+                            requant16_fast<true>(v, fast_s + n0 + c0, pk);
+                            if (two)
+                                requant16_fast<true>(v + 16, fast_s + n0 + c0 + 16, pk + 4);
+                        } else {
+                            requant16_fast<false>(v, fast_s + n0 + c0, pk);
+                            if (two)
+                                requant16_fast<false>(v + 16, fast_s + n0 + c0 + 16, pk + 4);
                         }
-                        uint32_t hi, w;
-                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r[3]), "r"(r[2]));
-                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r[1]), "r"(r[0]), "r"(hi));
-                        pk[q] = w;
+                    } else {
+                        requant16_general(v, p.epi, n0 + c0, p.N, pk);
+                        if (two)
+                            requant16_general(v + 16, p.epi, n0 + c0 + 16, p.N, pk + 4);
                     }
                     if (row_ok) {
-                        const int nvalid = p.N - (n0 + c0); // columns of this chunk inside the tensor
-                        if (vec_ok && nvalid >= 16) {
-                            *(uint4 *)(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                            if (two && nvalid >= 32)
-                                *(uint4 *)(orow + c0 + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                            else if (two)
-                                for (int j = 16; j < 32 && j < nvalid; j++) orow[c0 + j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
-                        } else {
-                            const int lim = two ? 32 : 16;
-                            for (int j = 0; j < lim && j < nvalid; j++) orow[c0 + j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
-                        }
+                        const int count = min(two ? 32 : 16, p.N - (n0 + c0));
+                        if (count > 0)
+                            store_bytes(orow + c0, pk, count, vec_ok);
                     }
                 }
             } else {
-                for (int c0 = 0; c0 < p.block_n; c0 += 16) {
-                    int32_t v[16];
-                    tc_ld16(t0 + c0, v);
-                    if (!I16) {
-                        tc_ld_wait();
-                        if (m < p.M && n0 + c0 < p.N) {
-                            uint32_t pk[4];
+                int chunk = 0;
+                for (int c0 = 0; c0 < p.block_n; c0 += 16, chunk++) {
+                    if (chunk % parts != part)
+                        continue;
+                    int32_t vh[16], vm[16], vl[16];
+                    ld16(t0 + c0, vh);
+                    ld16(t0 + p.block_n + c0, vm);
+                    ld16(t0 + 2 * p.block_n + c0, vl);
+                    ld_wait();
+                    if (row_ok && n0 + c0 < p.N) {
+                        int16_t *op = (int16_t *)p.out + m * p.ops + n0 + c0;
 #pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                uint32_t wd = 0;
-#pragma unroll
-                                for (int i = 0; i < 4; i++) {
-                                    const int j = c0 + q * 4 + i;
-                                    int32_t r = requant8(v[q * 4 + i], (int32_t)par[j].bias, par[j].shift, p.relu, p.half_even);
-                                    if (p.lut)
-                                        r = p.lut[(uint8_t)r ^ 0x80u];
-                                    wd |= ((uint32_t)r & 0xffu) << (8 * i);
-                                }
-                                pk[q] = wd;
-                            }
-                            int8_t *op = (int8_t *)p.out + m * p.ops + n0 + c0;
-                            if (n0 + c0 + 16 <= p.N && (((uintptr_t)op) & 15) == 0) {
-                                *(uint4 *)op = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                            } else {
-                                for (int j = 0; j < 16 && n0 + c0 + j < p.N; j++) op[j] = (int8_t)(pk[j >> 2] >> (8 * (j & 3)));
-                            }
-                        }
-                    } else {
-                        int32_t vm[16], vl[16];
-                        tc_ld16(t0 + p.block_n + c0, vm);
-                        tc_ld16(t0 + 2 * p.block_n + c0, vl);
-                        tc_ld_wait();
-                        if (m < p.M && n0 + c0 < p.N) {
-                            int16_t *op = (int16_t *)p.out + m * p.ops + n0 + c0;
-#pragma unroll
-                            for (int j = 0; j < 16; j++) {
-                                if (n0 + c0 + j < p.N) {
-                                    const long long a = ((long long)v[j] << 16) + ((long long)vm[j] << 8) + (long long)vl[j];
-                                    op[j] = (int16_t)requant16(a, par[c0 + j].bias, par[c0 + j].shift, p.relu, p.half_even);
-                                }
+                        for (int j = 0; j < 16; j++) {
+                            const int n = n0 + c0 + j;
+                            if (n < p.N) {
+                                const long long a = ((long long)vh[j] << 16) + ((long long)vm[j] << 8) + (long long)vl[j];
+                                const int e = p.epi.per_channel ? __ldg(p.epi.ew + n) : p.epi.ew_scalar;
+                                const int shift = max(-62, min(62, p.epi.e_shift_base - e));
+                                const long long b = p.epi.bias ? __ldg((const long long *)p.epi.bias + n) : 0ll;
+                                op[j] = (int16_t)requant16(a, b, shift, p.epi.relu, p.epi.half_even);
                             }
                         }
                     }
                 }
             }
-            tc_fence_before();
+            fence_before();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(smem_u32(&tempty_bar[acc]));
         }
-        if (!ok && lane == 0) {
+        if (!ok && lane == 0)
             atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
-            *abort_flag = 1;
-        }
     }
 
-    tc_fence_before();
+    fence_before();
     __syncthreads();
     if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+        fence_after();
+        tmem_dealloc(tmem_base, p.tmem_cols);
     }
 }
 
@@ -573,23 +374,26 @@ int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, u
     return ESPDL_OK;
 }
 
+// Bytes of K per stage row (= TMA box width = swizzle width).  Wide rows move fastest through the TMA unit, so
+// 128 is used as soon as K fills three quarters of such a row; columns past K are zero-filled, not fetched.
 int pick_swz(int K)
 {
-    const int pad32 = (K + 31) / 32 * 32;
-    if ((K + 127) / 128 * 128 == pad32)
+    if (K >= 96)
         return 128;
-    if ((K + 63) / 64 * 64 == pad32)
+    if (K > 32)
         return 64;
     return 32;
 }
 
 constexpr size_t SMEM_BUDGET = 200 * 1024;
 
+size_t aux_bytes(const TcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * MAX_STAGES + 2 * MAX_ACC) * 8 + 32; }
+
 bool plan(const espdl_conv_desc &d, TcParams &p)
 {
     const bool i16 = d.dtype == ESPDL_DTYPE_INT16;
     const long long M = (long long)d.n * d.out_h * d.out_w;
-    if (M > 0x7fffffffll)
+    if (M > 0x7fffffffll || d.out_c > 8192)
         return false;
     p.M = (int)M, p.N = d.out_c, p.K = d.in_c;
     const int max_bn = i16 ? 128 : 256;
@@ -599,7 +403,7 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
     p.m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
     p.swz = pick_swz(p.K);
     p.k_blocks = (p.K + p.swz - 1) / p.swz;
-    p.acc_stages = i16 ? 1 : 2;
+    p.acc_stages = i16 ? 1 : (4 * p.block_n <= 512 ? 4 : 2);
     int cols = p.acc_stages * (i16 ? 3 : 1) * p.block_n;
     int pow2 = 32;
     while (pow2 < cols) pow2 *= 2;
@@ -607,8 +411,7 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
         return false;
     p.tmem_cols = pow2;
     const size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
-    const size_t aux = 2 * sizeof(EpiParams) * (size_t)p.block_n + (2 * MAX_STAGES + 4) * 8 + 32;
-    int stages = (int)((SMEM_BUDGET - aux - 1024) / stage_bytes);
+    int stages = (int)((SMEM_BUDGET - aux_bytes(p) - 1024) / stage_bytes);
     if (stages < 2)
         return false;
     p.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
@@ -653,10 +456,10 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
     p.out = d.output;
     p.ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
-    p.bias = d.bias, p.ew = d.filter_exponents, p.lut = d.lut;
-    p.e_shift_base = d.out_exponent - d.in_exponent;
-    p.ew_scalar = d.filter_exponent, p.per_channel = d.per_channel;
-    p.relu = d.activation == ESPDL_ACT_RELU, p.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
+    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut;
+    p.epi.e_shift_base = d.out_exponent - d.in_exponent;
+    p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;
+    p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
 
     CUtensorMap ma, mb, ma_lo, mb_lo;
     int st;
@@ -688,7 +491,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
             return st;
     }
     const size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
-    size_t smem = 1024 + (size_t)p.stages * stage_bytes + 2 * sizeof(EpiParams) * (size_t)p.block_n + (2 * MAX_STAGES + 4) * 8 + 32;
+    size_t smem = 1024 + (size_t)p.stages * stage_bytes + aux_bytes(p);
     if (smem < 120 * 1024) // more than half an SM's shared memory: one CTA per SM, so TMEM allocation never waits on a neighbour
         smem = 120 * 1024;
     const int grid = min(p.m_tiles * p.n_tiles, num_sms());

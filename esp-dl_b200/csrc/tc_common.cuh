@@ -1,0 +1,271 @@
+// Building blocks shared by the tensor-core (tcgen05) tile kernels: PTX wrappers for mbarriers, TMA loads,
+// tcgen05 MMA / TMEM access, descriptor encoders, and the requantising epilogue that turns one TMEM
+// accumulator row (one output pixel, a run of output channels) into saturated int8 and stores it.
+#pragma once
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace espdl {
+namespace tc {
+
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // every device-side wait gives up after ~2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long globaltimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+
+// Bounded wait on an mbarrier phase.  Returns false when the limit expires.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+{
+    for (int spin = 0; spin < 64; spin++)
+        if (mbar_try(bar, parity))
+            return true;
+    const unsigned long long t0 = globaltimer();
+    while (true) {
+        if (mbar_try(bar, parity))
+            return true;
+        if (globaltimer() - t0 > WAIT_LIMIT_NS)
+            return false;
+    }
+}
+
+__device__ __forceinline__ void fence_barrier_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, int c3, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+
+// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp receives lane (base lane + t), columns c .. c+15.
+__device__ __forceinline__ void ld16(uint32_t taddr, int32_t *v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (64 bit):
+//   [0,14) start address >> 4   [16,30) leading-dimension byte offset >> 4   [32,46) stride-dimension byte offset >> 4
+//   [46,48) version = 1         [61,64) layout: 0 = no swizzle, 2 = 128B, 4 = 64B, 6 = 32B swizzle
+// K-major operands.  Swizzled (rows of `swz` bytes): 8-row groups are 8*swz bytes apart (stride offset), the leading
+// offset is unused.  Not swizzled: a core matrix is 8 rows x 16 bytes stored contiguously (128 bytes); `lbo` is the
+// distance between core matrices that are neighbours along K, `sbo` between neighbours along M/N.
+__device__ __forceinline__ uint64_t smem_desc_swizzled(uint32_t addr, int swz)
+{
+    const uint64_t layout = swz == 128 ? 2ull : (swz == 64 ? 4ull : 6ull);
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)((8u * (uint32_t)swz) >> 4) << 32) | ((uint64_t)1 << 46) |
+        (layout << 61);
+}
+
+__device__ __forceinline__ uint64_t smem_desc_plain(uint32_t addr, uint32_t lbo, uint32_t sbo)
+{
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((lbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFF) << 32) |
+        ((uint64_t)1 << 46);
+}
+
+// Instruction descriptor of tcgen05.mma kind::i8: D = S32 (bits 4-5 = 2), A/B format at bits 7-9 / 10-12
+// (0 = unsigned 8 bit, 1 = signed 8 bit), both operands K-major, N>>3 at bit 17, M>>4 at bit 24.
+__device__ __forceinline__ uint32_t idesc_i8(int a_signed, int b_signed, int m, int n)
+{
+    return (2u << 4) | ((uint32_t)a_signed << 7) | ((uint32_t)b_signed << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------ epilogue
+// Per-output-channel constants of the fast form, staged in shared memory: q = (acc + bias_half) >> shift with
+// bias_half = bias + 2^(shift-1).  Equal to the reference's wrapping 32-bit bias add followed by a 64-bit
+// round-half-up shift whenever nothing can overflow 32 bits: |acc| < 2^29, |bias| < 2^30, 1 <= shift <= 24.
+struct FastParam {
+    int bias_half;
+    int shift;
+};
+
+struct EpiConfig {
+    const void *bias;   // int32[N] (int8 op) / int64[N] (int16 op) or null
+    const int32_t *ew;  // per-channel filter exponents or null
+    const int8_t *lut;  // optional fused 256-entry table
+    int e_shift_base, ew_scalar, per_channel, relu, half_even;
+};
+
+// Fills fast[j] for channels [0, n_pad) with `nthreads` cooperating threads (tid in [0, nthreads)).
+// Returns 1 in *slow (shared int, pre-zeroed) if any real channel violates the fast form's conditions.
+__device__ __forceinline__ void stage_fast_params(const EpiConfig &c, FastParam *fast, int N, int n_pad, int tid, int nthreads, int *slow)
+{
+    int bad = 0;
+    for (int n = tid; n < n_pad; n += nthreads) {
+        int b = 0, sh = 1;
+        if (n < N) {
+            if (c.bias)
+                b = ((const int32_t *)c.bias)[n];
+            const int e = c.per_channel ? c.ew[n] : c.ew_scalar;
+            sh = c.e_shift_base - e;
+            if (sh < 1 || sh > 24 || b >= (1 << 30) || b <= -(1 << 30))
+                bad = 1;
+            sh = max(1, min(24, sh));
+        }
+        fast[n].bias_half = b + (1 << (sh - 1));
+        fast[n].shift = sh;
+    }
+    if (bad)
+        atomicOr(slow, 1);
+}
+
+// Requantises 16 accumulator columns with the fast form and packs them to 16 int8 (4 words).
+template <bool RELU>
+__device__ __forceinline__ void requant16_fast(const int32_t *v, const FastParam *fp, uint32_t *pk)
+{
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        // two channels per 128-bit shared-memory load
+        const int4 p01 = *(const int4 *)(fp + q * 4);
+        const int4 p23 = *(const int4 *)(fp + q * 4 + 2);
+        const int r0 = (v[q * 4 + 0] + p01.x) >> p01.y;
+        const int r1 = (v[q * 4 + 1] + p01.z) >> p01.w;
+        const int r2 = (v[q * 4 + 2] + p23.x) >> p23.y;
+        const int r3 = (v[q * 4 + 3] + p23.z) >> p23.w;
+        uint32_t hi, w;
+        if (RELU) {
+            // ReLU + saturation: clamp to [0, 255] while packing, then a per-byte minimum with 127
+            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r3), "r"(r2));
+            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r1), "r"(r0), "r"(hi));
+            w = __vminu4(w, 0x7f7f7f7fu);
+        } else {
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r3), "r"(r2));
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r1), "r"(r0), "r"(hi));
+        }
+        pk[q] = w;
+    }
+}
+
+// General form (any rounding mode, any shift, optional LUT), constants read from global memory.
+__device__ __forceinline__ void requant16_general(const int32_t *v, const EpiConfig &c, int n_first, int N, uint32_t *pk)
+{
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        uint32_t wd = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int n = min(n_first + q * 4 + i, N - 1);
+            const int e = c.per_channel ? __ldg(c.ew + n) : c.ew_scalar;
+            const int shift = max(-31, min(31, c.e_shift_base - e));
+            const int b = c.bias ? __ldg((const int32_t *)c.bias + n) : 0;
+            int32_t r = requant8(v[q * 4 + i], b, shift, c.relu, c.half_even);
+            if (c.lut)
+                r = c.lut[(uint8_t)r ^ 0x80u];
+            wd |= ((uint32_t)r & 0xffu) << (8 * i);
+        }
+        pk[q] = wd;
+    }
+}
+
+// Stores `count` (<= 32) packed int8 starting at `dst`; `words` holds them little-endian.
+__device__ __forceinline__ void store_bytes(int8_t *dst, const uint32_t *words, int count, bool aligned16)
+{
+    if (count >= 32 && aligned16 && (((uintptr_t)dst) & 31) == 0) {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(words[0]), "r"(words[1]), "r"(words[2]),
+                     "r"(words[3]), "r"(words[4]), "r"(words[5]), "r"(words[6]), "r"(words[7])
+                     : "memory");
+        return;
+    }
+    if (aligned16 && (((uintptr_t)dst) & 15) == 0) {
+        if (count >= 16)
+            *(uint4 *)dst = make_uint4(words[0], words[1], words[2], words[3]);
+        if (count >= 32)
+            *(uint4 *)(dst + 16) = make_uint4(words[4], words[5], words[6], words[7]);
+        const int done = count >= 32 ? 32 : (count >= 16 ? 16 : 0);
+#pragma unroll
+        for (int j = 0; j < 32; j++) // unrolled with static indices so that `words` stays in registers
+            if (j >= done && j < count)
+                dst[j] = (int8_t)(words[j >> 2] >> (8 * (j & 3)));
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j++)
+        if (j < count)
+            dst[j] = (int8_t)(words[j >> 2] >> (8 * (j & 3)));
+}
+
+} // namespace tc
+} // namespace espdl

@@ -165,20 +165,30 @@ esp_err_t Conv::prepare(ModelContext *context)
     }
     if (m_lut && !m_lut->device && m_lut->to_device() != ESP_OK)
         return ESP_FAIL;
-    // pointwise int8 conv with Cin % 16 != 0: group g pixels so that g * Cin is a multiple of 16
+    // Pointwise int8 conv whose input rows are narrow: group g pixels so that a row has g * Cin channels.  Needed
+    // when Cin is not a multiple of 16 (the tile kernel wants 16-byte rows) and wanted when Cin is small: the TMA
+    // unit moves rows of 16-64 bytes at a fraction of HBM speed, rows of 128 bytes at full speed.  The widest
+    // grouping whose block-diagonal filter stays small is used (ESPDL_B200_GROUP_K overrides the target width).
     TensorBase *input = context->get_tensor(m_inputs_index[0]);
     TensorBase *bias = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
     if (!m_gemm && !dw && input && input->shape.size() == 4 && quant_type == QUANT_TYPE_SYMM_8BIT && fs[0] == 1 && fs[1] == 1 &&
-        m_strides[0] == 1 && m_strides[1] == 1 && m_pads[0] + m_pads[1] + m_pads[2] + m_pads[3] == 0 && fs[2] % 16 != 0 && filter->data &&
+        m_strides[0] == 1 && m_strides[1] == 1 && m_pads[0] + m_pads[1] + m_pads[2] + m_pads[3] == 0 && filter->data &&
         !getenv("ESPDL_B200_NO_PIXEL_GROUPING")) {
         const int cin = fs[2], cout = fs[3];
         const long long pixels = (long long)input->shape[1] * input->shape[2];
+        const int target = getenv("ESPDL_B200_GROUP_K") ? atoi(getenv("ESPDL_B200_GROUP_K")) : 128;
+        int best = 1;
         for (int g : {2, 4, 8, 16}) {
-            if ((g * cin) % 16 == 0 && pixels % g == 0 && g * cin <= 256 && g * cout <= 2048) {
-                m_group_px = g;
-                break;
-            }
+            if ((g * cin) % 16 != 0 || pixels % g != 0 || g * cout > 1024)
+                continue;
+            if (cin % 16 != 0 && best == 1)
+                best = g; // smallest legal grouping is the fallback
+            if (g * cin <= target)
+                best = g; // widest row not beyond the target
         }
+        if (cin % 16 == 0 && cin >= target)
+            best = 1;
+        m_group_px = best;
         if (m_group_px > 1) {
             const int g = m_group_px;
             std::vector<int8_t> wf((size_t)g * cout * g * cin, 0);
