@@ -162,6 +162,9 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_tc_kernel(const __grid_const
                 }
                 fence_after();
                 const uint32_t st = smem_u32(smem + (size_t)stage * stage_bytes);
+                // Channel-block-major order: the nine taps of one accumulator are issued back to back (measured: alternating
+                // accumulators between consecutive MMAs is 1.5x slower).  Each M=128 MMA occupies the pipe for about
+                // 150 cycles whatever N is, which is what bounds this kernel (9 taps x 128 pixels x 32 channels each).
                 for (int cb = 0; cb < cblocks; cb++) {
                     const uint32_t d = tmem_base + (uint32_t)(acc * DW_CG + cb * 32);
 #pragma unroll
@@ -169,15 +172,13 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_tc_kernel(const __grid_const
                         const int ky = tap / 3, kx = tap % 3;
                         const int ph = (ky % p.S) * p.S + (kx % p.S);
                         const int off = (ky / p.S) * p.P + (kx / p.S);
-                        // row `off` of the plane, 32-byte channel block cb inside the row.  The swizzle is a function of the
-                        // absolute shared-memory address (as for the TMA write), so a start address in the middle of the
-                        // pattern needs nothing else: the descriptor's base-offset field stays 0 (measured: any other
-                        // value breaks the 64- and 128-byte modes).
+                        // Row `off` of the plane, 32-byte channel block cb inside the row.  The swizzle is a function of
+                        // the absolute shared-memory address (as for the TMA write), so a start address in the middle of
+                        // the pattern needs nothing else: the descriptor's base-offset field stays 0 (measured: any
+                        // other value breaks the 64- and 128-byte modes).
                         const uint32_t a_addr = st + (uint32_t)(ph * plane_bytes + off * p.cg + cb * 32);
                         const uint32_t b_addr = smem_u32(b_smem + (cb * 9 + tap) * 1024);
-                        const uint64_t da = smem_desc_swizzled(a_addr, p.cg);
-                        const uint64_t db = smem_desc_plain(b_addr, 512, 128);
-                        mma_i8(d, da, db, idesc, tap != 0);
+                        mma_i8(d, smem_desc_swizzled(a_addr, p.cg), smem_desc_plain(b_addr, 512, 128), idesc, tap != 0);
                     }
                 }
                 commit(smem_u32(&empty_bar[stage]));
