@@ -106,6 +106,7 @@ SYMBOLS = {
     "espdl_b200_conv2d": (C.c_int, [C.POINTER(ConvDesc), C.c_void_p]),
     "espdl_b200_conv2d_workspace_bytes": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_size_t)]),
     "espdl_b200_conv2d_ws": (C.c_int, [C.POINTER(ConvDesc), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "espdl_b200_gemm_s16_static": (C.c_int, [C.POINTER(ConvDesc), C.c_void_p]),
     "espdl_b200_eltwise": (C.c_int, [C.POINTER(EltwiseDesc), C.c_void_p]),
     "espdl_b200_pool": (C.c_int, [C.POINTER(PoolDesc), C.c_void_p]),
     "espdl_b200_resize": (C.c_int, [C.POINTER(ResizeDesc), C.c_void_p]),

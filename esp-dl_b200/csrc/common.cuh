@@ -11,6 +11,7 @@ namespace espdl {
 
 // ---------------------------------------------------------------- host state
 int set_cuda_error(cudaError_t e, const char *what); // records text, returns ESPDL_ERR_CUDA
+int set_error_text(int status, const char *fmt, ...); // records text for espdl_b200_last_error, returns status
 void count_launch(int n = 1);
 int num_sms();
 // Records the most recent failed launch (cudaGetLastError) if any.

@@ -513,3 +513,49 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
 }
 
 } // namespace espdl
+
+// ------------------------------------------------------------------ allocation-free int16 Gemm / pointwise conv
+// Fixed scratch for espdl_b200_gemm_s16_static: the byte planes of both int16 operands live in this array
+// instead of a caller-provided or cached cudaMalloc buffer.  It is part of the library image, so every GPU
+// that loads the library carries it until the process exits.
+namespace espdl {
+static __device__ __align__(256) unsigned char g_static_limb_scratch[ESPDL_B200_STATIC_SCRATCH_BYTES];
+}
+
+extern "C" int espdl_b200_gemm_s16_static(const espdl_conv_desc *desc, void *stream)
+{
+    using namespace espdl;
+    if (!desc || !desc->input || !desc->filter || !desc->output)
+        return ESPDL_ERR_INVALID_ARG;
+    if (desc->dtype != ESPDL_DTYPE_INT16 || !conv2d_tc_supported(*desc))
+        return ESPDL_ERR_UNSUPPORTED;
+    const size_t need = conv2d_tc_workspace_bytes(*desc);
+    if (need > (size_t)ESPDL_B200_STATIC_SCRATCH_BYTES)
+        return set_error_text(ESPDL_ERR_TOO_LARGE,
+                              "espdl_b200_gemm_s16_static: %zu bytes of scratch needed, the fixed array holds %u; use "
+                              "espdl_b200_conv2d_ws with a caller-owned buffer",
+                              need, (unsigned)ESPDL_B200_STATIC_SCRATCH_BYTES);
+    // In host code the array's name is only a handle; the device address comes from cudaGetSymbolAddress, asked
+    // once per device with that device current.
+    static void *addr_of_device[64] = {nullptr};
+    static std::mutex addr_mutex;
+    int dev = -1;
+    ESPDL_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64)
+        return ESPDL_ERR_NO_DEVICE;
+    void *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(addr_mutex);
+        if (!addr_of_device[dev]) {
+            void *p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_static_limb_scratch);
+            if (e != cudaSuccess)
+                return set_cuda_error(e, "cudaGetSymbolAddress(g_static_limb_scratch)");
+            addr_of_device[dev] = p;
+        }
+        scratch = addr_of_device[dev];
+    }
+    if (desc->n == 0)
+        return ESPDL_OK;
+    return conv2d_tc(*desc, scratch, (size_t)ESPDL_B200_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+}

@@ -154,6 +154,28 @@ int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream);
 int espdl_b200_conv2d_workspace_bytes(const espdl_conv_desc *desc, size_t *bytes);
 int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * int16 Gemm / pointwise conv (the shapes espdl_b200_conv2d runs on the tensor cores) for callers that must not
+ * allocate device memory.  No counterpart in the reference: ESP-DL's int16 Gemm needs no scratch at all.
+ *
+ * Who needs it: code that runs where cudaMalloc / cudaFree are off limits - inside a region the host application
+ * has fenced against allocation (a real-time control or audio loop, a serving process with a fixed memory budget
+ * checked at start-up), or under a memory pool that owns the whole device - and that therefore cannot use
+ * espdl_b200_conv2d (it grows a cached scratch buffer on demand) and has no buffer to hand to
+ * espdl_b200_conv2d_ws.  The 8-bit limb planes of both operands go into an array that is part of the library
+ * image, ESPDL_B200_STATIC_SCRATCH_BYTES large; every GPU that loads the library holds it until the process ends.
+ *
+ *  - scratch needed is what espdl_b200_conv2d_workspace_bytes reports, 2*(M*K + N*K) bytes rounded up; a larger
+ *    problem is rejected with ESPDL_ERR_TOO_LARGE, shapes the tensor-core int16 path does not take (K % 16 != 0,
+ *    filters other than 1x1, K > 16384) with ESPDL_ERR_UNSUPPORTED;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress) and keeps it;
+ *  - the call itself runs no cudaMalloc, cudaFree or allocating library routine;
+ *  - all calls share the one array and it keeps the previous call's bytes: every call rewrites the part it reads,
+ *    so nothing has to be cleared, but two calls that overlap on the GPU (different streams, no ordering) race.
+ */
+#define ESPDL_B200_STATIC_SCRATCH_BYTES (16u << 20)
+int espdl_b200_gemm_s16_static(const espdl_conv_desc *desc, void *stream);
+
 /* ------------------------------------------------------------ elementwise */
 typedef enum {
     ESPDL_ELT_ADD = 0,        /* sat(a + b), numpy broadcasting       esp-dl/dl/base/dl_base_add.cpp:8-44          */
