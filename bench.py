@@ -123,7 +123,7 @@ def module_traffic(parsed, batch):
             macs = int(np.prod(out)) * batch * w[0] * w[1] * (1 if group != 1 else w[2])
             if group != 1:
                 kind = "depthwise"
-            elif w[0] == 1 and w[1] == 1 and w[2] % 16 == 0:
+            elif w[0] == 1 and w[1] == 1:
                 kind = "pointwise_tc"
             else:
                 kind = "conv_simt"
@@ -309,7 +309,7 @@ def main():
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = dom["bytes"] / (dom["us"] * 1e-6) / 1e9
-        kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw_s8_vec16_kernel", "conv_simt": "conv_s8_kernel"}
+        kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw_tc_kernel", "conv_simt": "conv_s8_kernel"}
         roofline = {"bound": "hbm", "kernel": kernel_names.get(dom_kind, dom_kind), "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
                     "launches_per_step": dom["launches"], "algorithmic_bytes_per_step": dom["bytes"],
