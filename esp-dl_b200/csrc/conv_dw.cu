@@ -200,6 +200,214 @@ __global__ void __launch_bounds__(128) dw3x3_s8_kernel(DwParams p, int xtiles, i
     }
 }
 
+// 3x3 depthwise on dp4a, int8, dilation 1, stride S (1 or 2).
+// dp4a sums four byte products, but a depthwise filter never sums across channels: the four bytes of a dp4a
+// operand have to be four TAPS of one channel.  So a thread (four consecutive channels, one 32-bit word per
+// pixel) byte-transposes every group of four horizontally adjacent pixels P0..P3 into one word per channel,
+// (P0[c], P1[c], P2[c], P3[c]), with eight PRMTs (two of them shared with the neighbouring group).  Against the
+// filter row (w0, w1, w2, 0) that word gives the output centred on P1, against (0, w0, w1, w2) the one centred
+// on P2: one dp4a per output, channel and filter row.  Groups step by two pixels (stride 1) so that each yields
+// two outputs; with stride 2 groups step by four pixels and the second output of a group takes its third tap
+// from the next group ((0,0,w0,w1) here, (w2,0,0,0) there).  Transposed rows stay in registers while the thread
+// walks down its column, so every input word is loaded and transposed once per thread.
+// Per output that is 3 (S=1) or 4.5 (S=2) dp4a, about one PRMT, one shift and three quarters of a pack,
+// instead of nine multiply-adds on unpacked bytes.
+template <int S, int NG>
+struct DwRow {
+    uint32_t t[NG + (S == 2 ? 1 : 0)][4]; // [group][channel] -> four pixels of that channel
+};
+
+template <int S, int NG>
+__device__ __forceinline__ void dw_load_raw(uint32_t (&raw)[(S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4)], const int8_t *__restrict__ in,
+                                            int iy, int ix0, int ih, int iw, int ips)
+{
+    constexpr int NP = (S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4);
+    constexpr int USED = S == 1 ? NP : NP - 3; // stride 2 reads only the first pixel of its extra group
+    const bool row_in = iy >= 0 && iy < ih;
+    const int8_t *rp = in + ((long long)iy * iw + ix0) * ips;
+#pragma unroll
+    for (int x = 0; x < NP; x++) {
+        const int ix = ix0 + x;
+        raw[x] = 0;
+        if (x < USED && row_in && ix >= 0 && ix < iw)
+            raw[x] = __ldg((const uint32_t *)(rp + (long long)x * ips));
+    }
+}
+
+template <int S, int NG>
+__device__ __forceinline__ void dw_transpose(DwRow<S, NG> &row, const uint32_t (&raw)[(S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4)])
+{
+    constexpr int NP = (S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4);
+    uint32_t lo[NP / 2], hi[NP / 2];
+#pragma unroll
+    for (int j = 0; j < NP / 2; j++) {
+        lo[j] = __byte_perm(raw[2 * j], raw[2 * j + 1], 0x5140); // channels 0,1 of the pixel pair, interleaved
+        hi[j] = __byte_perm(raw[2 * j], raw[2 * j + 1], 0x7362); // channels 2,3
+    }
+    constexpr int GROUPS = NG + (S == 2 ? 1 : 0);
+    constexpr int PAIR_STEP = S == 1 ? 1 : 2;
+#pragma unroll
+    for (int g = 0; g < GROUPS; g++) {
+        const int a = g * PAIR_STEP, b = a + 1;
+        row.t[g][0] = __byte_perm(lo[a], lo[b], 0x5410);
+        row.t[g][1] = __byte_perm(lo[a], lo[b], 0x7632);
+        row.t[g][2] = __byte_perm(hi[a], hi[b], 0x5410);
+        row.t[g][3] = __byte_perm(hi[a], hi[b], 0x7632);
+    }
+}
+
+template <int S, int NG>
+__global__ void __launch_bounds__(128) dw3x3_dp4a_kernel(DwParams p, int xtiles, int ytiles, int rows_per_thread)
+{
+    constexpr int NP = (S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4);
+    constexpr int TW = 2 * NG; // outputs per thread and row
+    const int quads = p.c >> 2;
+    const long long item = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (item >= p.total)
+        return;
+    const int cq = (int)(item % quads);
+    long long r = item / quads;
+    const int xt = (int)(r % xtiles);
+    r /= xtiles;
+    const int yt = (int)(r % ytiles);
+    const int n = (int)(r / ytiles);
+    const int c0 = cq * 4;
+    const int8_t *__restrict__ in = (const int8_t *)p.in + (long long)n * p.ih * p.iw * p.ips + c0;
+    int8_t *__restrict__ out = (int8_t *)p.out + (long long)n * p.oh * p.ow * p.ops + c0;
+
+    // filter rows as dp4a operands: wa = (w0,w1,w2,0) per channel and row; the shifted forms are derived from it
+    uint32_t wa[3][4];
+#pragma unroll
+    for (int ky = 0; ky < 3; ky++) {
+        uint32_t f[3];
+#pragma unroll
+        for (int kx = 0; kx < 3; kx++) f[kx] = __ldg((const uint32_t *)((const int8_t *)p.w + (long long)(ky * 3 + kx) * p.c + c0));
+        const uint32_t lo0 = __byte_perm(f[0], f[1], 0x5140), hi0 = __byte_perm(f[0], f[1], 0x7362);
+        const uint32_t lo1 = __byte_perm(f[2], 0u, 0x5140), hi1 = __byte_perm(f[2], 0u, 0x7362);
+        wa[ky][0] = __byte_perm(lo0, lo1, 0x5410);
+        wa[ky][1] = __byte_perm(lo0, lo1, 0x7632);
+        wa[ky][2] = __byte_perm(hi0, hi1, 0x5410);
+        wa[ky][3] = __byte_perm(hi0, hi1, 0x7632);
+    }
+    int bias[4], shift[4];
+    bool fast = !p.half_even && !p.lut;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        bias[i] = p.bias ? __ldg((const int32_t *)p.bias + c0 + i) : 0;
+        const int e = p.per_channel ? __ldg(p.ew + c0 + i) : p.ew_scalar;
+        shift[i] = max(-31, min(31, p.e_shift_base - e));
+        // (acc + bias + 2^(s-1)) >> s is exact while nothing can overflow: |acc| <= 9 * 2^14, |bias| < 2^30, 1 <= s <= 24
+        fast = fast && shift[i] >= 1 && shift[i] <= 24 && bias[i] < (1 << 30) && bias[i] > -(1 << 30);
+    }
+    int init[4]; // what the accumulators start from: bias plus the rounding half on the fast path, else 0
+#pragma unroll
+    for (int i = 0; i < 4; i++) init[i] = fast ? bias[i] + (1 << (shift[i] - 1)) : 0;
+
+    const int ox0 = xt * TW, oy0 = yt * rows_per_thread;
+    const int ix0 = ox0 * S - p.pl;
+    const int oy_end = min(p.oh, oy0 + rows_per_thread);
+
+    DwRow<S, NG> ra, rb, rc;
+    uint32_t raw[NP], raw2[NP];
+
+    auto emit = [&](const DwRow<S, NG> &r0, const DwRow<S, NG> &r1, const DwRow<S, NG> &r2, int oy) {
+#pragma unroll
+        for (int g = 0; g < NG; g++) {
+            int acc0[4], acc1[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                acc0[i] = init[i];
+                acc1[i] = init[i];
+            }
+#pragma unroll
+            for (int ky = 0; ky < 3; ky++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const DwRow<S, NG> &rr = ky == 0 ? r0 : (ky == 1 ? r1 : r2);
+                    const uint32_t w = wa[ky][i];
+                    acc0[i] = __dp4a((int)rr.t[g][i], (int)w, acc0[i]);
+                    if (S == 1) {
+                        acc1[i] = __dp4a((int)rr.t[g][i], (int)(w << 8), acc1[i]);
+                    } else {
+                        acc1[i] = __dp4a((int)rr.t[g][i], (int)(w << 16), acc1[i]);
+                        acc1[i] = __dp4a((int)rr.t[g + (S == 2 ? 1 : 0)][i], (int)((w >> 16) & 0xffu), acc1[i]);
+                    }
+                }
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int ox = ox0 + 2 * g + half;
+                const int *acc = half ? acc1 : acc0;
+                if (ox < p.ow) {
+                    uint32_t wd;
+                    if (fast) {
+                        const int q0 = acc[0] >> shift[0], q1 = acc[1] >> shift[1], q2 = acc[2] >> shift[2], q3 = acc[3] >> shift[3];
+                        uint32_t hi;
+                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
+                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
+                        if (p.relu)
+                            wd = __vmaxs4(wd, 0u);
+                    } else {
+                        wd = 0;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            int32_t v = requant8(acc[i], bias[i], shift[i], p.relu, p.half_even);
+                            if (p.lut)
+                                v = p.lut[(uint8_t)v ^ 0x80u];
+                            wd |= ((uint32_t)v & 0xffu) << (8 * i);
+                        }
+                    }
+                    *(uint32_t *)(out + ((long long)oy * p.ow + ox) * p.ops) = wd;
+                }
+            }
+        }
+    };
+
+    const int iy0 = oy0 * S - p.pt;
+    if (S == 1) {
+        // rows iy0, iy0+1 prime the window; each step brings one new row in, already requested one step earlier
+        dw_load_raw<S, NG>(raw, in, iy0, ix0, p.ih, p.iw, p.ips);
+        dw_transpose<S, NG>(ra, raw);
+        dw_load_raw<S, NG>(raw, in, iy0 + 1, ix0, p.ih, p.iw, p.ips);
+        dw_transpose<S, NG>(rb, raw);
+        dw_load_raw<S, NG>(raw, in, iy0 + 2, ix0, p.ih, p.iw, p.ips);
+        for (int oy = oy0; oy < oy_end; oy += 3) {
+            dw_transpose<S, NG>(rc, raw);
+            dw_load_raw<S, NG>(raw, in, oy + 3 - p.pt, ix0, p.ih, p.iw, p.ips);
+            emit(ra, rb, rc, oy);
+            if (oy + 1 >= oy_end)
+                break;
+            dw_transpose<S, NG>(ra, raw);
+            dw_load_raw<S, NG>(raw, in, oy + 4 - p.pt, ix0, p.ih, p.iw, p.ips);
+            emit(rb, rc, ra, oy + 1);
+            if (oy + 2 >= oy_end)
+                break;
+            dw_transpose<S, NG>(rb, raw);
+            dw_load_raw<S, NG>(raw, in, oy + 5 - p.pt, ix0, p.ih, p.iw, p.ips);
+            emit(rc, ra, rb, oy + 2);
+        }
+    } else {
+        // output row oy reads input rows 2*oy - pt + {0,1,2}; the last of them is the first of the next output row
+        dw_load_raw<S, NG>(raw, in, iy0, ix0, p.ih, p.iw, p.ips);
+        dw_transpose<S, NG>(ra, raw);
+        dw_load_raw<S, NG>(raw, in, iy0 + 1, ix0, p.ih, p.iw, p.ips);
+        dw_load_raw<S, NG>(raw2, in, iy0 + 2, ix0, p.ih, p.iw, p.ips);
+        for (int oy = oy0; oy < oy_end; oy += 2) {
+            dw_transpose<S, NG>(rb, raw);
+            dw_transpose<S, NG>(rc, raw2);
+            dw_load_raw<S, NG>(raw, in, 2 * oy + 3 - p.pt, ix0, p.ih, p.iw, p.ips);
+            dw_load_raw<S, NG>(raw2, in, 2 * oy + 4 - p.pt, ix0, p.ih, p.iw, p.ips);
+            emit(ra, rb, rc, oy);
+            if (oy + 1 >= oy_end)
+                break;
+            dw_transpose<S, NG>(rb, raw);
+            dw_transpose<S, NG>(ra, raw2);
+            dw_load_raw<S, NG>(raw, in, 2 * oy + 5 - p.pt, ix0, p.ih, p.iw, p.ips);
+            dw_load_raw<S, NG>(raw2, in, 2 * oy + 6 - p.pt, ix0, p.ih, p.iw, p.ips);
+            emit(rc, rb, ra, oy + 1);
+        }
+    }
+}
+
 template <typename T, typename ACC, typename BIAS>
 __global__ void __launch_bounds__(256) dw_generic_kernel(DwParams p)
 {
@@ -262,18 +470,23 @@ int conv2d_depthwise(const espdl_conv_desc &d, cudaStream_t s)
         d.stride_h == d.stride_w && (d.stride_h == 1 || d.stride_h == 2) && d.in_c % 4 == 0 && p.ips % 4 == 0 && p.ops % 4 == 0 &&
         ((uintptr_t)d.input % 4) == 0 && ((uintptr_t)d.output % 4) == 0 && ((uintptr_t)d.filter % 4) == 0;
     if (k3) {
-        constexpr int TH = 4;
+        // a thread walks down a whole column of the image when the batch gives enough threads without splitting it
         const int tw = d.stride_h == 1 ? 4 : 2;
-        const int xtiles = (d.out_w + tw - 1) / tw, ytiles = (d.out_h + TH - 1) / TH;
-        const long long items = (long long)d.n * ytiles * xtiles * (d.in_c / 4);
+        const int xtiles = (d.out_w + tw - 1) / tw;
+        const long long per_row_tile = (long long)d.n * xtiles * (d.in_c / 4);
+        const long long want = (long long)num_sms() * 4096;
+        int rows = d.out_h;
+        while (rows > 6 && per_row_tile * ((d.out_h + rows - 1) / rows) < want) rows = (rows + 1) / 2;
+        const int ytiles = (d.out_h + rows - 1) / rows;
+        const long long items = per_row_tile * ytiles;
         p.total = items, p.chunks = 0;
         const long long blocks = (items + 127) / 128;
         if (blocks > 0x7fffffffll)
             return ESPDL_ERR_TOO_LARGE;
         if (d.stride_h == 1)
-            dw3x3_s8_kernel<1, 4, TH><<<(unsigned)blocks, 128, 0, s>>>(p, xtiles, ytiles);
+            dw3x3_dp4a_kernel<1, 2><<<(unsigned)blocks, 128, 0, s>>>(p, xtiles, ytiles, rows);
         else
-            dw3x3_s8_kernel<2, 2, TH><<<(unsigned)blocks, 128, 0, s>>>(p, xtiles, ytiles);
+            dw3x3_dp4a_kernel<2, 1><<<(unsigned)blocks, 128, 0, s>>>(p, xtiles, ytiles, rows);
     } else if (vec) {
         p.chunks = d.in_c / 16;
         p.total = pixels * p.chunks;
