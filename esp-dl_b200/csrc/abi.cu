@@ -332,7 +332,10 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
         const bool dw_tc_ok = conv2d_dw_tc_supported(*desc);
         if (desc->kernel == ESPDL_KERNEL_TCGEN05 && !dw_tc_ok)
             return ESPDL_ERR_UNSUPPORTED;
-        if (dw_tc_ok && desc->kernel != ESPDL_KERNEL_SIMT)
+        // the dp4a kernel on the CUDA cores is the faster one for every shape measured (a tcgen05 MMA of M=128
+        // takes ~143 cycles however small N is, which caps the diagonal-filter formulation), so the tensor-core
+        // depthwise kernel runs only on request
+        if (dw_tc_ok && desc->kernel == ESPDL_KERNEL_TCGEN05)
             return conv2d_dw_tc(*desc, s);
         return conv2d_depthwise(*desc, s);
     }

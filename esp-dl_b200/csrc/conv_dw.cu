@@ -202,92 +202,77 @@ __global__ void __launch_bounds__(128) dw3x3_s8_kernel(DwParams p, int xtiles, i
 
 // 3x3 depthwise on dp4a, int8, dilation 1, stride S (1 or 2).
 // dp4a sums four byte products, but a depthwise filter never sums across channels: the four bytes of a dp4a
-// operand have to be four TAPS of one channel.  So a thread (four consecutive channels, one 32-bit word per
-// pixel) byte-transposes every group of four horizontally adjacent pixels P0..P3 into one word per channel,
-// (P0[c], P1[c], P2[c], P3[c]), with eight PRMTs (two of them shared with the neighbouring group).  Against the
-// filter row (w0, w1, w2, 0) that word gives the output centred on P1, against (0, w0, w1, w2) the one centred
-// on P2: one dp4a per output, channel and filter row.  Groups step by two pixels (stride 1) so that each yields
-// two outputs; with stride 2 groups step by four pixels and the second output of a group takes its third tap
-// from the next group ((0,0,w0,w1) here, (w2,0,0,0) there).  Transposed rows stay in registers while the thread
-// walks down its column, so every input word is loaded and transposed once per thread.
-// Per output that is 3 (S=1) or 4.5 (S=2) dp4a, about one PRMT, one shift and three quarters of a pack,
-// instead of nine multiply-adds on unpacked bytes.
-template <int S, int NG>
-struct DwRow {
-    uint32_t t[NG + (S == 2 ? 1 : 0)][4]; // [group][channel] -> four pixels of that channel
+// operand have to be four TAPS of one channel.  A thread owns four consecutive channels (one 32-bit word of an
+// NHWC pixel) and a band of output rows, and walks along the row.  Each input column it meets (the band's input
+// rows at one x) is byte-transposed once, eight PRMTs per four rows: word i of a group holds channel i of four
+// vertically adjacent pixels.  Against the filter column (w[0][kx], w[1][kx], w[2][kx], 0) that word gives the
+// output row whose window starts at the group's first row, against the same word shifted by one byte the next
+// row (stride 1, two overlapping groups per band -> four output rows from six input rows).  With stride 2 the
+// second output row of a band takes two taps from the group ((0,0,w0,w1)) and its third from a fifth input row,
+// read untransposed with the tap placed in the byte of its channel.  Three transposed columns are live; per
+// output that is 3 (S=1) or 4.5 (S=2) dp4a, about one PRMT, a shift, a max and half a pack.
+// Rows outside the image read a zero word through a pointer that does not advance, so the walk has no per-load
+// bounds checks; columns outside the image are skipped as a whole.
+__device__ const uint32_t g_dw_zero_word[4] = {0u, 0u, 0u, 0u};
+
+template <int S>
+struct DwCol {
+    uint32_t t[S == 1 ? 2 : 1][4]; // [row group][channel]: four vertically adjacent pixels of that channel
+    uint32_t extra;                // stride 2: the fifth input row, untransposed
 };
 
-template <int S, int NG>
-__device__ __forceinline__ void dw_load_raw(uint32_t (&raw)[(S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4)], const int8_t *__restrict__ in,
-                                            int iy, int ix0, int ih, int iw, int ips)
+template <int S>
+__device__ __forceinline__ void dw_transpose_col(DwCol<S> &col, const uint32_t (&raw)[S == 1 ? 6 : 5])
 {
-    constexpr int NP = (S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4);
-    constexpr int USED = S == 1 ? NP : NP - 3; // stride 2 reads only the first pixel of its extra group
-    const bool row_in = iy >= 0 && iy < ih;
-    const int8_t *rp = in + ((long long)iy * iw + ix0) * ips;
+    constexpr int PAIRS = S == 1 ? 3 : 2;
+    uint32_t lo[PAIRS], hi[PAIRS];
 #pragma unroll
-    for (int x = 0; x < NP; x++) {
-        const int ix = ix0 + x;
-        raw[x] = 0;
-        if (x < USED && row_in && ix >= 0 && ix < iw)
-            raw[x] = __ldg((const uint32_t *)(rp + (long long)x * ips));
-    }
-}
-
-template <int S, int NG>
-__device__ __forceinline__ void dw_transpose(DwRow<S, NG> &row, const uint32_t (&raw)[(S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4)])
-{
-    constexpr int NP = (S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4);
-    uint32_t lo[NP / 2], hi[NP / 2];
-#pragma unroll
-    for (int j = 0; j < NP / 2; j++) {
-        lo[j] = __byte_perm(raw[2 * j], raw[2 * j + 1], 0x5140); // channels 0,1 of the pixel pair, interleaved
+    for (int j = 0; j < PAIRS; j++) {
+        lo[j] = __byte_perm(raw[2 * j], raw[2 * j + 1], 0x5140); // channels 0,1 of the row pair, interleaved
         hi[j] = __byte_perm(raw[2 * j], raw[2 * j + 1], 0x7362); // channels 2,3
     }
-    constexpr int GROUPS = NG + (S == 2 ? 1 : 0);
-    constexpr int PAIR_STEP = S == 1 ? 1 : 2;
 #pragma unroll
-    for (int g = 0; g < GROUPS; g++) {
-        const int a = g * PAIR_STEP, b = a + 1;
-        row.t[g][0] = __byte_perm(lo[a], lo[b], 0x5410);
-        row.t[g][1] = __byte_perm(lo[a], lo[b], 0x7632);
-        row.t[g][2] = __byte_perm(hi[a], hi[b], 0x5410);
-        row.t[g][3] = __byte_perm(hi[a], hi[b], 0x7632);
+    for (int g = 0; g < (S == 1 ? 2 : 1); g++) {
+        col.t[g][0] = __byte_perm(lo[g], lo[g + 1], 0x5410);
+        col.t[g][1] = __byte_perm(lo[g], lo[g + 1], 0x7632);
+        col.t[g][2] = __byte_perm(hi[g], hi[g + 1], 0x5410);
+        col.t[g][3] = __byte_perm(hi[g], hi[g + 1], 0x7632);
     }
+    col.extra = S == 2 ? raw[S == 2 ? 4 : 0] : 0u;
 }
 
-template <int S, int NG>
-__global__ void __launch_bounds__(128) dw3x3_dp4a_kernel(DwParams p, int xtiles, int ytiles, int rows_per_thread)
+template <int S>
+__global__ void __launch_bounds__(128, S == 1 ? 3 : 4) dw3x3_dp4a_kernel(DwParams p, int xsegs, int ytiles, int cols_per_thread)
 {
-    constexpr int NP = (S == 1 ? 2 : 4) * NG + (S == 1 ? 2 : 4);
-    constexpr int TW = 2 * NG; // outputs per thread and row
+    constexpr int ROWS_IN = S == 1 ? 6 : 5;
+    constexpr int ROWS_OUT = S == 1 ? 4 : 2;
     const int quads = p.c >> 2;
     const long long item = blockIdx.x * (long long)blockDim.x + threadIdx.x;
     if (item >= p.total)
         return;
     const int cq = (int)(item % quads);
     long long r = item / quads;
-    const int xt = (int)(r % xtiles);
-    r /= xtiles;
     const int yt = (int)(r % ytiles);
-    const int n = (int)(r / ytiles);
+    r /= ytiles;
+    const int xs = (int)(r % xsegs);
+    const int n = (int)(r / xsegs);
     const int c0 = cq * 4;
-    const int8_t *__restrict__ in = (const int8_t *)p.in + (long long)n * p.ih * p.iw * p.ips + c0;
-    int8_t *__restrict__ out = (int8_t *)p.out + (long long)n * p.oh * p.ow * p.ops + c0;
 
-    // filter rows as dp4a operands: wa = (w0,w1,w2,0) per channel and row; the shifted forms are derived from it
-    uint32_t wa[3][4];
+    // filter columns as dp4a operands: wv[kx][i] = (w[0][kx][i], w[1][kx][i], w[2][kx][i], 0)
+    uint32_t wv[3][4], wsel[3][4];
 #pragma unroll
-    for (int ky = 0; ky < 3; ky++) {
+    for (int kx = 0; kx < 3; kx++) {
         uint32_t f[3];
 #pragma unroll
-        for (int kx = 0; kx < 3; kx++) f[kx] = __ldg((const uint32_t *)((const int8_t *)p.w + (long long)(ky * 3 + kx) * p.c + c0));
+        for (int ky = 0; ky < 3; ky++) f[ky] = __ldg((const uint32_t *)((const int8_t *)p.w + (long long)(ky * 3 + kx) * p.c + c0));
         const uint32_t lo0 = __byte_perm(f[0], f[1], 0x5140), hi0 = __byte_perm(f[0], f[1], 0x7362);
         const uint32_t lo1 = __byte_perm(f[2], 0u, 0x5140), hi1 = __byte_perm(f[2], 0u, 0x7362);
-        wa[ky][0] = __byte_perm(lo0, lo1, 0x5410);
-        wa[ky][1] = __byte_perm(lo0, lo1, 0x7632);
-        wa[ky][2] = __byte_perm(hi0, hi1, 0x5410);
-        wa[ky][3] = __byte_perm(hi0, hi1, 0x7632);
+        wv[kx][0] = __byte_perm(lo0, lo1, 0x5410);
+        wv[kx][1] = __byte_perm(lo0, lo1, 0x7632);
+        wv[kx][2] = __byte_perm(hi0, hi1, 0x5410);
+        wv[kx][3] = __byte_perm(hi0, hi1, 0x7632);
+#pragma unroll
+        for (int i = 0; i < 4; i++) wsel[kx][i] = S == 2 ? (f[2] & (0xffu << (8 * i))) : 0u; // w[2][kx][i] in byte i
     }
     int bias[4], shift[4];
     bool fast = !p.half_even && !p.lut;
@@ -299,111 +284,142 @@ __global__ void __launch_bounds__(128) dw3x3_dp4a_kernel(DwParams p, int xtiles,
         // (acc + bias + 2^(s-1)) >> s is exact while nothing can overflow: |acc| <= 9 * 2^14, |bias| < 2^30, 1 <= s <= 24
         fast = fast && shift[i] >= 1 && shift[i] <= 24 && bias[i] < (1 << 30) && bias[i] > -(1 << 30);
     }
-    int init[4]; // what the accumulators start from: bias plus the rounding half on the fast path, else 0
+    int init[4]; // accumulators start from bias plus the rounding half on the fast path, else from 0
 #pragma unroll
     for (int i = 0; i < 4; i++) init[i] = fast ? bias[i] + (1 << (shift[i] - 1)) : 0;
+    const int floor_q = p.relu ? 0 : INT_MIN;
 
-    const int ox0 = xt * TW, oy0 = yt * rows_per_thread;
-    const int ix0 = ox0 * S - p.pl;
-    const int oy_end = min(p.oh, oy0 + rows_per_thread);
+    const int oy0 = yt * ROWS_OUT;
+    const int x_begin = xs * cols_per_thread, x_end = min(p.ow, x_begin + cols_per_thread);
+    const int iy0 = oy0 * S - p.pt;
+    int ix = x_begin * S - p.pl; // column the row pointers stand on
 
-    DwRow<S, NG> ra, rb, rc;
-    uint32_t raw[NP], raw2[NP];
-
-    auto emit = [&](const DwRow<S, NG> &r0, const DwRow<S, NG> &r1, const DwRow<S, NG> &r2, int oy) {
+    // one pointer per input row of the band; rows outside the image stand still on a zero word
+    const int8_t *rp[ROWS_IN];
+    int rinc[ROWS_IN];
+    {
+        const int8_t *img = (const int8_t *)p.in + (long long)n * p.ih * p.iw * p.ips + c0;
 #pragma unroll
-        for (int g = 0; g < NG; g++) {
-            int acc0[4], acc1[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                acc0[i] = init[i];
-                acc1[i] = init[i];
-            }
-#pragma unroll
-            for (int ky = 0; ky < 3; ky++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const DwRow<S, NG> &rr = ky == 0 ? r0 : (ky == 1 ? r1 : r2);
-                    const uint32_t w = wa[ky][i];
-                    acc0[i] = __dp4a((int)rr.t[g][i], (int)w, acc0[i]);
-                    if (S == 1) {
-                        acc1[i] = __dp4a((int)rr.t[g][i], (int)(w << 8), acc1[i]);
-                    } else {
-                        acc1[i] = __dp4a((int)rr.t[g][i], (int)(w << 16), acc1[i]);
-                        acc1[i] = __dp4a((int)rr.t[g + (S == 2 ? 1 : 0)][i], (int)((w >> 16) & 0xffu), acc1[i]);
-                    }
-                }
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                const int ox = ox0 + 2 * g + half;
-                const int *acc = half ? acc1 : acc0;
-                if (ox < p.ow) {
-                    uint32_t wd;
-                    if (fast) {
-                        const int q0 = acc[0] >> shift[0], q1 = acc[1] >> shift[1], q2 = acc[2] >> shift[2], q3 = acc[3] >> shift[3];
-                        uint32_t hi;
-                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
-                        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
-                        if (p.relu)
-                            wd = __vmaxs4(wd, 0u);
-                    } else {
-                        wd = 0;
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            int32_t v = requant8(acc[i], bias[i], shift[i], p.relu, p.half_even);
-                            if (p.lut)
-                                v = p.lut[(uint8_t)v ^ 0x80u];
-                            wd |= ((uint32_t)v & 0xffu) << (8 * i);
-                        }
-                    }
-                    *(uint32_t *)(out + ((long long)oy * p.ow + ox) * p.ops) = wd;
-                }
-            }
+        for (int rr = 0; rr < ROWS_IN; rr++) {
+            const int iy = iy0 + rr;
+            const bool ok = iy >= 0 && iy < p.ih;
+            rp[rr] = ok ? img + ((long long)iy * p.iw + ix) * p.ips : (const int8_t *)g_dw_zero_word;
+            rinc[rr] = ok ? p.ips : 0;
         }
+    }
+    int8_t *op = (int8_t *)p.out + (((long long)n * p.oh + oy0) * p.ow + x_begin) * p.ops + c0;
+    const int orow = p.ow * p.ops;
+    bool ovalid[ROWS_OUT];
+#pragma unroll
+    for (int ro = 0; ro < ROWS_OUT; ro++) ovalid[ro] = oy0 + ro < p.oh;
+
+    uint32_t raw[ROWS_IN], raw2[ROWS_IN];
+    auto load_col = [&](uint32_t (&dst)[ROWS_IN]) {
+        const bool ok = ix >= 0 && ix < p.iw;
+#pragma unroll
+        for (int rr = 0; rr < ROWS_IN; rr++) {
+            dst[rr] = ok ? __ldg((const uint32_t *)rp[rr]) : 0u;
+            rp[rr] += rinc[rr];
+        }
+        ix++;
     };
 
-    const int iy0 = oy0 * S - p.pt;
+    auto emit = [&](const DwCol<S> &k0, const DwCol<S> &k1, const DwCol<S> &k2) {
+        int acc[ROWS_OUT][4];
+#pragma unroll
+        for (int ro = 0; ro < ROWS_OUT; ro++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[ro][i] = init[i];
+#pragma unroll
+        for (int kx = 0; kx < 3; kx++) {
+            const DwCol<S> &k = kx == 0 ? k0 : (kx == 1 ? k1 : k2);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t w = wv[kx][i];
+                if constexpr (S == 1) {
+                    acc[0][i] = __dp4a((int)k.t[0][i], (int)w, acc[0][i]);
+                    acc[1][i] = __dp4a((int)k.t[0][i], (int)(w << 8), acc[1][i]);
+                    acc[2][i] = __dp4a((int)k.t[1][i], (int)w, acc[2][i]);
+                    acc[3][i] = __dp4a((int)k.t[1][i], (int)(w << 8), acc[3][i]);
+                } else {
+                    acc[0][i] = __dp4a((int)k.t[0][i], (int)w, acc[0][i]);
+                    acc[1][i] = __dp4a((int)k.t[0][i], (int)(w << 16), acc[1][i]);
+                    acc[1][i] = __dp4a((int)k.extra, (int)wsel[kx][i], acc[1][i]);
+                }
+            }
+        }
+        if (fast) {
+#pragma unroll
+            for (int ro = 0; ro < ROWS_OUT; ro++) {
+                const int q0 = max(acc[ro][0] >> shift[0], floor_q), q1 = max(acc[ro][1] >> shift[1], floor_q);
+                const int q2 = max(acc[ro][2] >> shift[2], floor_q), q3 = max(acc[ro][3] >> shift[3], floor_q);
+                uint32_t hi, wd;
+                asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
+                asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
+                if (ovalid[ro])
+                    *(uint32_t *)(op + (long long)ro * orow) = wd;
+            }
+        } else {
+#pragma unroll
+            for (int ro = 0; ro < ROWS_OUT; ro++) {
+                uint32_t wd = 0;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    int32_t v = requant8(acc[ro][i], bias[i], shift[i], p.relu, p.half_even);
+                    if (p.lut)
+                        v = p.lut[(uint8_t)v ^ 0x80u];
+                    wd |= ((uint32_t)v & 0xffu) << (8 * i);
+                }
+                if (oy0 + ro < p.oh)
+                    *(uint32_t *)(op + (long long)ro * orow) = wd;
+            }
+        }
+        op += p.ops;
+    };
+
+    DwCol<S> ca, cb, cc;
     if (S == 1) {
-        // rows iy0, iy0+1 prime the window; each step brings one new row in, already requested one step earlier
-        dw_load_raw<S, NG>(raw, in, iy0, ix0, p.ih, p.iw, p.ips);
-        dw_transpose<S, NG>(ra, raw);
-        dw_load_raw<S, NG>(raw, in, iy0 + 1, ix0, p.ih, p.iw, p.ips);
-        dw_transpose<S, NG>(rb, raw);
-        dw_load_raw<S, NG>(raw, in, iy0 + 2, ix0, p.ih, p.iw, p.ips);
-        for (int oy = oy0; oy < oy_end; oy += 3) {
-            dw_transpose<S, NG>(rc, raw);
-            dw_load_raw<S, NG>(raw, in, oy + 3 - p.pt, ix0, p.ih, p.iw, p.ips);
-            emit(ra, rb, rc, oy);
-            if (oy + 1 >= oy_end)
+        // output x reads input columns x - pl + {0,1,2}: two columns prime the window, every step brings one in,
+        // requested one step before it is needed
+        load_col(raw);
+        dw_transpose_col<S>(ca, raw);
+        load_col(raw);
+        dw_transpose_col<S>(cb, raw);
+        load_col(raw);
+        for (int x = x_begin; x < x_end; x += 3) {
+            dw_transpose_col<S>(cc, raw);
+            load_col(raw);
+            emit(ca, cb, cc);
+            if (x + 1 >= x_end)
                 break;
-            dw_transpose<S, NG>(ra, raw);
-            dw_load_raw<S, NG>(raw, in, oy + 4 - p.pt, ix0, p.ih, p.iw, p.ips);
-            emit(rb, rc, ra, oy + 1);
-            if (oy + 2 >= oy_end)
+            dw_transpose_col<S>(ca, raw);
+            load_col(raw);
+            emit(cb, cc, ca);
+            if (x + 2 >= x_end)
                 break;
-            dw_transpose<S, NG>(rb, raw);
-            dw_load_raw<S, NG>(raw, in, oy + 5 - p.pt, ix0, p.ih, p.iw, p.ips);
-            emit(rc, ra, rb, oy + 2);
+            dw_transpose_col<S>(cb, raw);
+            load_col(raw);
+            emit(cc, ca, cb);
         }
     } else {
-        // output row oy reads input rows 2*oy - pt + {0,1,2}; the last of them is the first of the next output row
-        dw_load_raw<S, NG>(raw, in, iy0, ix0, p.ih, p.iw, p.ips);
-        dw_transpose<S, NG>(ra, raw);
-        dw_load_raw<S, NG>(raw, in, iy0 + 1, ix0, p.ih, p.iw, p.ips);
-        dw_load_raw<S, NG>(raw2, in, iy0 + 2, ix0, p.ih, p.iw, p.ips);
-        for (int oy = oy0; oy < oy_end; oy += 2) {
-            dw_transpose<S, NG>(rb, raw);
-            dw_transpose<S, NG>(rc, raw2);
-            dw_load_raw<S, NG>(raw, in, 2 * oy + 3 - p.pt, ix0, p.ih, p.iw, p.ips);
-            dw_load_raw<S, NG>(raw2, in, 2 * oy + 4 - p.pt, ix0, p.ih, p.iw, p.ips);
-            emit(ra, rb, rc, oy);
-            if (oy + 1 >= oy_end)
+        // output x reads input columns 2x - pl + {0,1,2}; the last of them is the first of the next output
+        load_col(raw);
+        dw_transpose_col<S>(ca, raw);
+        load_col(raw);
+        load_col(raw2);
+        for (int x = x_begin; x < x_end; x += 2) {
+            dw_transpose_col<S>(cb, raw);
+            dw_transpose_col<S>(cc, raw2);
+            load_col(raw);
+            load_col(raw2);
+            emit(ca, cb, cc);
+            if (x + 1 >= x_end)
                 break;
-            dw_transpose<S, NG>(rb, raw);
-            dw_transpose<S, NG>(ra, raw2);
-            dw_load_raw<S, NG>(raw, in, 2 * oy + 5 - p.pt, ix0, p.ih, p.iw, p.ips);
-            dw_load_raw<S, NG>(raw2, in, 2 * oy + 6 - p.pt, ix0, p.ih, p.iw, p.ips);
-            emit(rc, rb, ra, oy + 1);
+            dw_transpose_col<S>(cb, raw);
+            dw_transpose_col<S>(ca, raw2);
+            load_col(raw);
+            load_col(raw2);
+            emit(cc, cb, ca);
         }
     }
 }
@@ -470,23 +486,23 @@ int conv2d_depthwise(const espdl_conv_desc &d, cudaStream_t s)
         d.stride_h == d.stride_w && (d.stride_h == 1 || d.stride_h == 2) && d.in_c % 4 == 0 && p.ips % 4 == 0 && p.ops % 4 == 0 &&
         ((uintptr_t)d.input % 4) == 0 && ((uintptr_t)d.output % 4) == 0 && ((uintptr_t)d.filter % 4) == 0;
     if (k3) {
-        // a thread walks down a whole column of the image when the batch gives enough threads without splitting it
-        const int tw = d.stride_h == 1 ? 4 : 2;
-        const int xtiles = (d.out_w + tw - 1) / tw;
-        const long long per_row_tile = (long long)d.n * xtiles * (d.in_c / 4);
-        const long long want = (long long)num_sms() * 4096;
-        int rows = d.out_h;
-        while (rows > 6 && per_row_tile * ((d.out_h + rows - 1) / rows) < want) rows = (rows + 1) / 2;
-        const int ytiles = (d.out_h + rows - 1) / rows;
-        const long long items = per_row_tile * ytiles;
+        // a thread walks along a whole band of rows when the batch gives enough threads without cutting the band
+        const int rows_out = d.stride_h == 1 ? 4 : 2;
+        const int ytiles = (d.out_h + rows_out - 1) / rows_out;
+        const long long per_seg = (long long)d.n * ytiles * (d.in_c / 4);
+        const long long want = (long long)num_sms() * 2048;
+        int cols = d.out_w;
+        while (cols > 8 && per_seg * ((d.out_w + cols - 1) / cols) < want) cols = (cols + 1) / 2;
+        const int xsegs = (d.out_w + cols - 1) / cols;
+        const long long items = per_seg * xsegs;
         p.total = items, p.chunks = 0;
         const long long blocks = (items + 127) / 128;
         if (blocks > 0x7fffffffll)
             return ESPDL_ERR_TOO_LARGE;
         if (d.stride_h == 1)
-            dw3x3_dp4a_kernel<1, 2><<<(unsigned)blocks, 128, 0, s>>>(p, xtiles, ytiles, rows);
+            dw3x3_dp4a_kernel<1><<<(unsigned)blocks, 128, 0, s>>>(p, xsegs, ytiles, cols);
         else
-            dw3x3_dp4a_kernel<2, 1><<<(unsigned)blocks, 128, 0, s>>>(p, xtiles, ytiles, rows);
+            dw3x3_dp4a_kernel<2><<<(unsigned)blocks, 128, 0, s>>>(p, xsegs, ytiles, cols);
     } else if (vec) {
         p.chunks = d.in_c / 16;
         p.total = pixels * p.chunks;
