@@ -241,8 +241,35 @@ __device__ __forceinline__ void dw_transpose_col(DwCol<S> &col, const uint32_t (
     col.extra = S == 2 ? raw[S == 2 ? 4 : 0] : 0u;
 }
 
+// Band of a thread whose channels do not qualify for the one-add-one-shift epilogue (a shift outside 1..24, a
+// huge bias, half-even rounding or a fused table): plain loops with the general requantisation.  Kept out of line
+// so that the walk below carries none of its registers.
+__device__ __noinline__ void dw3x3_band_general(const DwParams &p, int S, int n, int c0, int oy0, int rows, int x_begin, int x_end)
+{
+    const int8_t *__restrict__ in = (const int8_t *)p.in + (long long)n * p.ih * p.iw * p.ips;
+    int8_t *__restrict__ out = (int8_t *)p.out + (long long)n * p.oh * p.ow * p.ops;
+    for (int oy = oy0; oy < min(p.oh, oy0 + rows); oy++)
+        for (int ox = x_begin; ox < x_end; ox++)
+            for (int i = 0; i < 4; i++) {
+                const int c = c0 + i;
+                int32_t acc = 0;
+                for (int ky = 0; ky < 3; ky++)
+                    for (int kx = 0; kx < 3; kx++) {
+                        const int iy = oy * S - p.pt + ky, ix = ox * S - p.pl + kx;
+                        if (iy >= 0 && iy < p.ih && ix >= 0 && ix < p.iw)
+                            acc += (int)in[((long long)iy * p.iw + ix) * p.ips + c] * (int)((const int8_t *)p.w)[(ky * 3 + kx) * p.c + c];
+                    }
+                const int e = p.per_channel ? p.ew[c] : p.ew_scalar;
+                const int shift = max(-31, min(31, p.e_shift_base - e));
+                int32_t v = requant8(acc, p.bias ? ((const int32_t *)p.bias)[c] : 0, shift, p.relu, p.half_even);
+                if (p.lut)
+                    v = p.lut[(uint8_t)v ^ 0x80u];
+                out[((long long)oy * p.ow + ox) * p.ops + c] = (int8_t)v;
+            }
+}
+
 template <int S>
-__global__ void __launch_bounds__(128, S == 1 ? 3 : 4) dw3x3_dp4a_kernel(DwParams p, int xsegs, int ytiles, int cols_per_thread)
+__global__ void __launch_bounds__(128, 4) dw3x3_dp4a_kernel(DwParams p, int xsegs, int ytiles, int cols_per_thread)
 {
     constexpr int ROWS_IN = S == 1 ? 6 : 5;
     constexpr int ROWS_OUT = S == 1 ? 4 : 2;
@@ -259,7 +286,7 @@ __global__ void __launch_bounds__(128, S == 1 ? 3 : 4) dw3x3_dp4a_kernel(DwParam
     const int c0 = cq * 4;
 
     // filter columns as dp4a operands: wv[kx][i] = (w[0][kx][i], w[1][kx][i], w[2][kx][i], 0)
-    uint32_t wv[3][4], wsel[3][4];
+    uint32_t wv[3][4], wv1[3][4], wsel[3][4];
 #pragma unroll
     for (int kx = 0; kx < 3; kx++) {
         uint32_t f[3];
@@ -272,7 +299,10 @@ __global__ void __launch_bounds__(128, S == 1 ? 3 : 4) dw3x3_dp4a_kernel(DwParam
         wv[kx][2] = __byte_perm(hi0, hi1, 0x5410);
         wv[kx][3] = __byte_perm(hi0, hi1, 0x7632);
 #pragma unroll
-        for (int i = 0; i < 4; i++) wsel[kx][i] = S == 2 ? (f[2] & (0xffu << (8 * i))) : 0u; // w[2][kx][i] in byte i
+        for (int i = 0; i < 4; i++) {
+            wv1[kx][i] = wv[kx][i] << (S == 1 ? 8 : 16);                           // the band's next output row
+            wsel[kx][i] = S == 2 ? (f[2] & (0xffu << (8 * i))) : 0u;               // w[2][kx][i] in byte i
+        }
     }
     int bias[4], shift[4];
     bool fast = !p.half_even && !p.lut;
@@ -284,13 +314,16 @@ __global__ void __launch_bounds__(128, S == 1 ? 3 : 4) dw3x3_dp4a_kernel(DwParam
         // (acc + bias + 2^(s-1)) >> s is exact while nothing can overflow: |acc| <= 9 * 2^14, |bias| < 2^30, 1 <= s <= 24
         fast = fast && shift[i] >= 1 && shift[i] <= 24 && bias[i] < (1 << 30) && bias[i] > -(1 << 30);
     }
-    int init[4]; // accumulators start from bias plus the rounding half on the fast path, else from 0
-#pragma unroll
-    for (int i = 0; i < 4; i++) init[i] = fast ? bias[i] + (1 << (shift[i] - 1)) : 0;
-    const int floor_q = p.relu ? 0 : INT_MIN;
-
     const int oy0 = yt * ROWS_OUT;
     const int x_begin = xs * cols_per_thread, x_end = min(p.ow, x_begin + cols_per_thread);
+    if (!fast) {
+        dw3x3_band_general(p, S, n, c0, oy0, ROWS_OUT, x_begin, x_end);
+        return;
+    }
+    int init[4]; // accumulators start from bias plus the rounding half
+#pragma unroll
+    for (int i = 0; i < 4; i++) init[i] = bias[i] + (1 << (shift[i] - 1));
+    const int floor_q = p.relu ? 0 : INT_MIN;
     const int iy0 = oy0 * S - p.pt;
     int ix = x_begin * S - p.pl; // column the row pointers stand on
 
@@ -327,52 +360,32 @@ __global__ void __launch_bounds__(128, S == 1 ? 3 : 4) dw3x3_dp4a_kernel(DwParam
     auto emit = [&](const DwCol<S> &k0, const DwCol<S> &k1, const DwCol<S> &k2) {
         int acc[ROWS_OUT][4];
 #pragma unroll
-        for (int ro = 0; ro < ROWS_OUT; ro++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[ro][i] = init[i];
-#pragma unroll
         for (int kx = 0; kx < 3; kx++) {
             const DwCol<S> &k = kx == 0 ? k0 : (kx == 1 ? k1 : k2);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const uint32_t w = wv[kx][i];
+                const uint32_t w = wv[kx][i], w1 = wv1[kx][i];
                 if constexpr (S == 1) {
-                    acc[0][i] = __dp4a((int)k.t[0][i], (int)w, acc[0][i]);
-                    acc[1][i] = __dp4a((int)k.t[0][i], (int)(w << 8), acc[1][i]);
-                    acc[2][i] = __dp4a((int)k.t[1][i], (int)w, acc[2][i]);
-                    acc[3][i] = __dp4a((int)k.t[1][i], (int)(w << 8), acc[3][i]);
+                    acc[0][i] = __dp4a((int)k.t[0][i], (int)w, kx == 0 ? init[i] : acc[0][i]);
+                    acc[1][i] = __dp4a((int)k.t[0][i], (int)w1, kx == 0 ? init[i] : acc[1][i]);
+                    acc[2][i] = __dp4a((int)k.t[1][i], (int)w, kx == 0 ? init[i] : acc[2][i]);
+                    acc[3][i] = __dp4a((int)k.t[1][i], (int)w1, kx == 0 ? init[i] : acc[3][i]);
                 } else {
-                    acc[0][i] = __dp4a((int)k.t[0][i], (int)w, acc[0][i]);
-                    acc[1][i] = __dp4a((int)k.t[0][i], (int)(w << 16), acc[1][i]);
+                    acc[0][i] = __dp4a((int)k.t[0][i], (int)w, kx == 0 ? init[i] : acc[0][i]);
+                    acc[1][i] = __dp4a((int)k.t[0][i], (int)w1, kx == 0 ? init[i] : acc[1][i]);
                     acc[1][i] = __dp4a((int)k.extra, (int)wsel[kx][i], acc[1][i]);
                 }
             }
         }
-        if (fast) {
 #pragma unroll
-            for (int ro = 0; ro < ROWS_OUT; ro++) {
-                const int q0 = max(acc[ro][0] >> shift[0], floor_q), q1 = max(acc[ro][1] >> shift[1], floor_q);
-                const int q2 = max(acc[ro][2] >> shift[2], floor_q), q3 = max(acc[ro][3] >> shift[3], floor_q);
-                uint32_t hi, wd;
-                asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
-                asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
-                if (ovalid[ro])
-                    *(uint32_t *)(op + (long long)ro * orow) = wd;
-            }
-        } else {
-#pragma unroll
-            for (int ro = 0; ro < ROWS_OUT; ro++) {
-                uint32_t wd = 0;
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    int32_t v = requant8(acc[ro][i], bias[i], shift[i], p.relu, p.half_even);
-                    if (p.lut)
-                        v = p.lut[(uint8_t)v ^ 0x80u];
-                    wd |= ((uint32_t)v & 0xffu) << (8 * i);
-                }
-                if (oy0 + ro < p.oh)
-                    *(uint32_t *)(op + (long long)ro * orow) = wd;
-            }
+        for (int ro = 0; ro < ROWS_OUT; ro++) {
+            const int q0 = max(acc[ro][0] >> shift[0], floor_q), q1 = max(acc[ro][1] >> shift[1], floor_q);
+            const int q2 = max(acc[ro][2] >> shift[2], floor_q), q3 = max(acc[ro][3] >> shift[3], floor_q);
+            uint32_t hi, wd;
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
+            if (ovalid[ro])
+                *(uint32_t *)(op + (long long)ro * orow) = wd;
         }
         op += p.ops;
     };
