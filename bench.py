@@ -316,7 +316,7 @@ def main():
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = dom["bytes"] / (dom["us"] * 1e-6) / 1e9
-        kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw_tc_kernel", "conv_simt": "conv_s8_kernel"}
+        kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw3x3_dp4a_kernel", "conv_simt": "conv_s8_kernel"}
         roofline = {"bound": "hbm", "kernel": kernel_names.get(dom_kind, dom_kind), "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
                     "launches_per_step": dom["launches"], "algorithmic_bytes_per_step": dom["bytes"],

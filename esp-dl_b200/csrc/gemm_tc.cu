@@ -246,6 +246,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!I16) {
                 int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
                 const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
+                if (fast && vec_ok && p.N % 16 == 0) {
+                    // the common case: whole 16-column groups, aligned rows, one-add-one-shift constants
+                    const bool wide = (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
+                    const uint32_t fp = smem_u32(fast_s + n0);
+                    const int ncols = min(p.block_n, p.N - n0);
+                    if (p.epi.relu)
+                        epilogue_lean<true>(t0, fp, orow, ncols, parts, part, row_ok, wide);
+                    else
+                        epilogue_lean<false>(t0, fp, orow, ncols, parts, part, row_ok, wide);
+                    fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(smem_u32(&tempty_bar[acc]));
+                    continue;
+                }
                 int chunk = 0;
                 for (int c0 = 0; c0 < p.block_n; c0 += 32, chunk++) {
                     if (chunk % parts != part)

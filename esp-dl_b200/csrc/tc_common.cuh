@@ -125,6 +125,20 @@ __device__ __forceinline__ void ld16(uint32_t taddr, int32_t *v)
         : "memory");
 }
 
+// 32 consecutive columns per thread in one instruction.
+__device__ __forceinline__ void ld32(uint32_t taddr, int32_t *v)
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
 __device__ __forceinline__ void ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (64 bit):
@@ -216,6 +230,70 @@ __device__ __forceinline__ void requant16_fast(const int32_t *v, const FastParam
             asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r1), "r"(r0), "r"(hi));
         }
         pk[q] = w;
+    }
+}
+
+// Four accumulator columns -> one word of four saturated int8, constants of the fast form read from shared memory
+// (address `fp`, 8 bytes per column) with two 128-bit loads.  With ReLU the add and the lower clamp are one
+// instruction (max(acc + bias_half, 0)), which commutes with the arithmetic shift; the pack saturates the top.
+template <bool RELU>
+__device__ __forceinline__ uint32_t requant4_lean(const int32_t *v, uint32_t fp)
+{
+    int b0, s0, b1, s1, b2, s2, b3, s3;
+    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(s0), "=r"(b1), "=r"(s1) : "r"(fp));
+    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(b2), "=r"(s2), "=r"(b3), "=r"(s3) : "r"(fp + 16));
+    int r0, r1, r2, r3;
+    if (RELU) {
+        r0 = __viaddmax_s32(v[0], b0, 0) >> s0;
+        r1 = __viaddmax_s32(v[1], b1, 0) >> s1;
+        r2 = __viaddmax_s32(v[2], b2, 0) >> s2;
+        r3 = __viaddmax_s32(v[3], b3, 0) >> s3;
+    } else {
+        r0 = (v[0] + b0) >> s0;
+        r1 = (v[1] + b1) >> s1;
+        r2 = (v[2] + b2) >> s2;
+        r3 = (v[3] + b3) >> s3;
+    }
+    uint32_t hi, w;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r3), "r"(r2));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r1), "r"(r0), "r"(hi));
+    return w;
+}
+
+// One accumulator row (this thread's TMEM lane), columns [0, ncols) of a tile, ncols % 16 == 0, every `parts`-th
+// 32-column chunk starting with chunk `part`: requantise with the fast form and store.  `orow` is 16-byte
+// aligned; `wide` says it is 32-byte aligned as well (256-bit stores).
+template <bool RELU>
+__device__ __forceinline__ void epilogue_lean(uint32_t t0, uint32_t fp, int8_t *orow, int ncols, int parts, int part, bool row_ok, bool wide)
+{
+    for (int c0 = part * 32; c0 + 32 <= ncols; c0 += parts * 32) {
+        int32_t v[32];
+        ld32(t0 + c0, v);
+        ld_wait();
+        uint32_t pk[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) pk[q] = requant4_lean<RELU>(v + 4 * q, fp + (uint32_t)(c0 + 4 * q) * 8u);
+        if (row_ok) {
+            if (wide) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + c0), "r"(pk[0]), "r"(pk[1]),
+                             "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
+                             : "memory");
+            } else {
+                *(uint4 *)(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *(uint4 *)(orow + c0 + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+        }
+    }
+    if ((ncols & 16) && (ncols >> 5) % parts == part) { // trailing half chunk
+        const int c0 = ncols - 16;
+        int32_t v[16];
+        ld16(t0 + c0, v);
+        ld_wait();
+        uint32_t pk[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) pk[q] = requant4_lean<RELU>(v + 4 * q, fp + (uint32_t)(c0 + 4 * q) * 8u);
+        if (row_ok)
+            *(uint4 *)(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
 }
 

@@ -3,6 +3,7 @@
 
 #include <cassert>
 #include <cmath>
+#include <algorithm>
 #include <cstring>
 
 namespace dl {
@@ -176,18 +177,24 @@ esp_err_t Conv::prepare(ModelContext *context)
         !getenv("ESPDL_B200_NO_PIXEL_GROUPING")) {
         const int cin = fs[2], cout = fs[3];
         const long long pixels = (long long)input->shape[1] * input->shape[2];
-        const int target = getenv("ESPDL_B200_GROUP_K") ? atoi(getenv("ESPDL_B200_GROUP_K")) : 128;
+        // Score of a grouping g: input row width towards 128 bytes, output rows made of whole 16-byte groups and at
+        // least 32 bytes wide, minus the extra L2 traffic of the g*g times larger filter (bytes per pixel relative to
+        // the activations).  ESPDL_B200_GROUP_K, when set, caps g * Cin.
+        const int cap = getenv("ESPDL_B200_GROUP_K") ? atoi(getenv("ESPDL_B200_GROUP_K")) : 1 << 20;
         int best = 1;
-        for (int g : {2, 4, 8, 16}) {
-            if ((g * cin) % 16 != 0 || pixels % g != 0 || g * cout > 1024)
+        double best_score = -1.0;
+        for (int g : {1, 2, 4, 8, 16}) {
+            if ((g * cin) % 16 != 0 || pixels % g != 0 || g * cout > 1024 || (g > 1 && g * cin > cap))
                 continue;
-            if (cin % 16 != 0 && best == 1)
-                best = g; // smallest legal grouping is the fallback
-            if (g * cin <= target)
-                best = g; // widest row not beyond the target
+            const double in_score = std::min(g * cin, 128) / 128.0;
+            const double out_score = ((g * cout) % 16 == 0 ? 1.0 : 0.0) + 0.5 * std::min(g * cout, 32) / 32.0;
+            const double filter_cost = g == 1 ? 0.0 : 0.5 * ((double)g * cin * cout / 128.0) / (cin + cout);
+            const double score = in_score + out_score - filter_cost;
+            if (score > best_score + 1e-9) {
+                best_score = score;
+                best = g;
+            }
         }
-        if (cin % 16 == 0 && cin >= target)
-            best = 1;
         m_group_px = best;
         if (m_group_px > 1) {
             const int g = m_group_px;
