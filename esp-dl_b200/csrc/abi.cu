@@ -151,8 +151,9 @@ int espdl_b200_stream_sync(void *stream)
     // a tile kernel whose bounded wait expired leaves its status in a device word
     int dev = read_and_clear_device_error();
     const int dev_dw = read_and_clear_device_error_dw();
+    const int dev_stem = read_and_clear_device_error_stem();
     if (!dev)
-        dev = dev_dw;
+        dev = dev_dw ? dev_dw : dev_stem;
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -339,6 +340,8 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
             return conv2d_dw_tc(*desc, s);
         return conv2d_depthwise(*desc, s);
     }
+    if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_stem_tc_supported(*desc))
+        return conv2d_stem_tc(*desc, s); // 3x3 stride-2 RGB first layer: banded-filter tensor-core kernel
     const bool tc_ok = conv2d_tc_supported(*desc);
     if (desc->kernel == ESPDL_KERNEL_TCGEN05 && !tc_ok)
         return ESPDL_ERR_UNSUPPORTED;

@@ -110,3 +110,24 @@ def test_gpu_reproduces_golden_gemm(path):
     m, tensors = replay_gemm_chain(path, lambda case: gpu_util.run_conv_gpu(case), mode)
     for name, t in m["test_outputs"].items():
         np.testing.assert_array_equal(tensors[name].reshape(-1), t["data"].reshape(-1))
+
+
+STEM_SHAPES = [
+    dict(n=2, h=224, w=224, cout=32, pad=(0, 1, 0, 1)),     # the classifier's first layer
+    dict(n=1, h=96, w=96, cout=16, pad=(1, 1, 1, 1)),       # left/top padding: window shifted by 16 bytes, first row index -1
+    dict(n=3, h=64, w=80, cout=32, pad=(0, 1, 0, 1), act=abi.ACT_LINEAR, bias=False),
+    dict(n=9, h=32, w=48, cout=32, pad=(1, 0, 1, 0)),       # two image groups, the second almost empty
+    dict(n=5, h=33, w=48, cout=16, pad=(0, 0, 0, 0)),       # 23 output columns (ragged last group of eight), odd height
+    dict(n=2, h=48, w=64, cout=32, pad=(1, 1, 1, 1), round_mode=abi.ROUND_HALF_EVEN),   # general epilogue
+    dict(n=2, h=48, w=64, cout=16, pad=(0, 1, 0, 1), lut=True),
+]
+
+
+@pytest.mark.parametrize("kw", STEM_SHAPES, ids=lambda k: f"n{k['n']}-{k['h']}x{k['w']}-c{k['cout']}-p{''.join(map(str, k['pad']))}")
+def test_stem_conv_tensor_core(kw):
+    """3x3 stride-2 RGB first layer through the banded-filter tensor-core kernel, against the oracle and the CUDA-core kernel."""
+    case = cases.conv_case(seed=91, cin=3, kh=3, kw=3, stride=2, per_channel=True, e_in=-7, e_out=-5, e_w=(-8, -6), **kw)
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT), want)
+    assert want.std() > 0
