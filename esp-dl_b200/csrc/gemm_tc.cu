@@ -67,6 +67,8 @@ struct TcParams {
     int stages;
     int acc_stages; // TMEM accumulator buffers: 4 or 2 (int8), 1 (int16)
     int tmem_cols;  // power of two >= 32
+    int out_pw;     // staged epilogue: bytes per row of a group's output piece (0 = rows are stored directly)
+    int out_mask;   // swizzle mask of the staging tiles (7, 3, 1, 0)
     void *out;
     long long ops;  // output row stride in elements
     EpiConfig epi;
@@ -75,7 +77,8 @@ struct TcParams {
 template <bool I16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo, const TcParams p)
+               const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
+               const __grid_constant__ CUtensorMap map_out, const TcParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -85,7 +88,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int b_bytes = p.block_n * p.swz;
     const int stage_bytes = NPLANE * (a_bytes + b_bytes);
     const int n_pad = p.n_tiles * p.block_n;
-    uint8_t *aux = smem + (size_t)p.stages * stage_bytes;
+    uint8_t *out_stage = smem + (size_t)p.stages * stage_bytes; // 4 tiles of [128][out_pw] bytes, 1024-byte aligned each
+    const int out_tile_bytes = (BLOCK_M * p.out_pw + 1023) & ~1023;
+    uint8_t *aux = out_stage + 4 * (size_t)out_tile_bytes;
     FastParam *fast_s = (FastParam *)aux; // n_pad entries, 16-byte aligned (block_n % 16 == 0)
     uint64_t *bars = (uint64_t *)(aux + sizeof(FastParam) * (size_t)n_pad);
     uint64_t *full_bar = bars, *empty_bar = bars + MAX_STAGES, *tfull_bar = bars + 2 * MAX_STAGES, *tempty_bar = tfull_bar + MAX_ACC;
@@ -226,6 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
             fast = !*slow_flag && !p.epi.half_even && !p.epi.lut && p.K <= 32768;
         }
+        const uint32_t fp_base = epi_param_base(fast_s);
         uint32_t acc_phase = 0;
         bool ok = true;
         int local = 0;
@@ -246,10 +252,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!I16) {
                 int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
                 const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
+                if (fast && p.out_pw) {
+                    // staged: requantise into this group's shared-memory tile, one TMA store per piece
+                    const bool leader = (ew & 3) == 0 && lane == 0;
+                    const uint32_t buf = smem_u32(out_stage + (size_t)group * out_tile_bytes);
+                    if (leader)
+                        bulk_wait_read_all(); // the previous store out of this tile has been read
+                    named_bar(2 + group, 128);
+                    const int col0 = part * p.out_pw;
+                    if (p.epi.relu)
+                        epilogue_stage<true>(t0 + col0, fp_base + (uint32_t)(n0 + col0) * 8u, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask);
+                    else
+                        epilogue_stage<false>(t0 + col0, fp_base + (uint32_t)(n0 + col0) * 8u, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask);
+                    fence_before();
+                    fence_async_smem();
+                    named_bar(2 + group, 128);
+                    if (leader) {
+                        tma_store_2d(&map_out, buf, n0 + col0, m0); // rows >= M and columns >= N are clipped
+                        bulk_commit();
+                    }
+                    if (lane == 0)
+                        mbar_arrive(smem_u32(&tempty_bar[acc]));
+                    continue;
+                }
                 if (fast && vec_ok && p.N % 16 == 0) {
                     // the common case: whole 16-column groups, aligned rows, one-add-one-shift constants
                     const bool wide = (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
-                    const uint32_t fp = smem_u32(fast_s + n0);
+                    const uint32_t fp = fp_base + (uint32_t)n0 * 8u;
                     const int ncols = min(p.block_n, p.N - n0);
                     if (p.epi.relu)
                         epilogue_lean<true>(t0, fp, orow, ncols, parts, part, row_ok, wide);
@@ -326,6 +355,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!ok && lane == 0)
             atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+        if (!I16 && p.out_pw && (ew & 3) == 0 && lane == 0)
+            bulk_wait_all(); // shared memory stays allocated until the last store has left it
     }
 
     fence_before();
@@ -379,7 +410,8 @@ int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, u
     cuuint64_t strides[1] = {row_stride};
     cuuint32_t box[2] = {box_cols, box_rows};
     cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapSwizzle sw = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (swz == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    const CUtensorMapSwizzle sw = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+        : (swz == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (swz == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -425,8 +457,24 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
     if (pow2 > 512)
         return false;
     p.tmem_cols = pow2;
+    // staged epilogue (int8): each group of four epilogue warps owns a piece of block_n / parts columns
+    const long long ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
+    p.out_pw = 0, p.out_mask = 0;
+    if (!i16 && ops % 16 == 0 && ((uintptr_t)d.output % 16) == 0 && !getenv("ESPDL_B200_DIRECT_STORES")) {
+        const int parts = 4 / p.acc_stages;
+        if (p.block_n % (16 * parts) == 0 && p.block_n / parts <= 128) {
+            p.out_pw = p.block_n / parts;
+            p.out_mask = p.out_pw == 128 ? 7 : (p.out_pw == 64 ? 3 : (p.out_pw == 32 ? 1 : 0));
+        }
+    }
+    size_t out_bytes = 4 * (size_t)((BLOCK_M * p.out_pw + 1023) & ~1023);
     const size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
-    int stages = (int)((SMEM_BUDGET - aux_bytes(p) - 1024) / stage_bytes);
+    int stages = (int)((SMEM_BUDGET - aux_bytes(p) - out_bytes - 1024) / stage_bytes);
+    if (p.out_pw && p.k_blocks > 2 && stages < 4) {
+        // a long reduction needs the deep load pipeline more than the output needs staging
+        p.out_pw = 0, p.out_mask = 0, out_bytes = 0;
+        stages = (int)((SMEM_BUDGET - aux_bytes(p) - 1024) / stage_bytes);
+    }
     if (stages < 2)
         return false;
     p.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
@@ -506,7 +554,13 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
             return st;
     }
     const size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
-    size_t smem = 1024 + (size_t)p.stages * stage_bytes + aux_bytes(p);
+    size_t smem = 1024 + (size_t)p.stages * stage_bytes + 4 * (size_t)((BLOCK_M * p.out_pw + 1023) & ~1023) + aux_bytes(p);
+    CUtensorMap mo = ma;
+    if (p.out_pw) {
+        const int osw = p.out_pw == 128 ? 128 : (p.out_pw == 64 ? 64 : (p.out_pw == 32 ? 32 : 0));
+        if ((st = make_map(&mo, d.output, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.ops, BLOCK_M, (uint32_t)p.out_pw, osw)))
+            return st;
+    }
     if (smem < 120 * 1024) // more than half an SM's shared memory: one CTA per SM, so TMEM allocation never waits on a neighbour
         smem = 120 * 1024;
     const int grid = min(p.m_tiles * p.n_tiles, num_sms());
@@ -520,9 +574,9 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     if (attr_err != cudaSuccess)
         return set_cuda_error(attr_err, "cudaFuncSetAttribute(gemm_tc_kernel)");
     if (i16)
-        gemm_tc_kernel<true><<<grid, NUM_THREADS, smem, s>>>(ma, mb, ma_lo, mb_lo, p);
+        gemm_tc_kernel<true><<<grid, NUM_THREADS, smem, s>>>(ma, mb, ma_lo, mb_lo, mo, p);
     else
-        gemm_tc_kernel<false><<<grid, NUM_THREADS, smem, s>>>(ma, mb, ma_lo, mb_lo, p);
+        gemm_tc_kernel<false><<<grid, NUM_THREADS, smem, s>>>(ma, mb, ma_lo, mb_lo, mo, p);
     count_launch();
     return check_launch("gemm_tc");
 }

@@ -96,11 +96,13 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
     }
     // banded filter planes, written in the 64-byte-swizzled K-major layout the MMA reads: the 16-byte chunk index
     // of a row is XORed with bits 7-8 of the byte offset (planes start on 1024-byte boundaries)
-    for (int i = threadIdx.x; i < 3 * ncol * (ST_K / 4); i += ST_THREADS) {
-        const int ky = i / (ncol * (ST_K / 4));
-        const int rem = i % (ncol * (ST_K / 4));
-        const int row = rem / (ST_K / 4), k0 = (rem % (ST_K / 4)) * 4;
-        const int j = row / p.cout, co = row % p.cout;
+    const int cout_log2 = p.cout == 32 ? 5 : 4; // Cout is 16 or 32: shifts instead of divisions
+    for (int i = threadIdx.x; i < 3 * 256 * (ST_K / 4); i += ST_THREADS) {
+        const int ky = i >> 12;                 // 256 rows x 16 words per plane
+        const int row = (i >> 4) & 255, k0 = (i & 15) * 4;
+        if (row >= ncol)
+            continue;
+        const int j = row >> cout_log2, co = row & (p.cout - 1);
         uint32_t word = 0;
 #pragma unroll
         for (int b = 0; b < 4; b++) {
@@ -220,7 +222,7 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
         asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
         const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut;
         const bool wide = ((uintptr_t)p.out % 32 == 0) && ((p.ow * p.cout) % 32 == 0);
-        const uint32_t fp = smem_u32(fast_s);
+        const uint32_t fp = epi_param_base(fast_s);
         uint32_t acc_phase = 0;
         bool ok = true;
         int local = 0;

@@ -93,6 +93,26 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// TMA stores (shared -> global), bulk-group completion
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src), "r"(c0), "r"(c1),
+                 "r"(c2)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void named_bar(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
+
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -244,6 +264,7 @@ __device__ __forceinline__ void requant16_fast(const int32_t *v, const FastParam
 // Four accumulator columns -> one word of four saturated int8, constants of the fast form read from shared memory
 // (address `fp`, 8 bytes per column) with two 128-bit loads.  With ReLU the add and the lower clamp are one
 // instruction (max(acc + bias_half, 0)), which commutes with the arithmetic shift; the pack saturates the top.
+// (Volatile loads: letting the compiler hoist them ahead of the TMEM wait cost registers and measured slower.)
 template <bool RELU>
 __device__ __forceinline__ uint32_t requant4_lean(const int32_t *v, uint32_t fp)
 {
@@ -268,19 +289,46 @@ __device__ __forceinline__ uint32_t requant4_lean(const int32_t *v, uint32_t fp)
     return w;
 }
 
+// Shared-memory address of the staged constants, produced by a volatile asm: call it AFTER the barrier that follows
+// stage_fast_params, so that no load that depends on it can be scheduled before the constants are written.
+__device__ __forceinline__ uint32_t epi_param_base(const FastParam *fast)
+{
+    uint32_t a;
+    asm volatile("mov.u32 %0, %1;" : "=r"(a) : "r"(smem_u32(fast)) : "memory");
+    return a;
+}
+
+template <bool RELU>
+__device__ __forceinline__ void requant16_lean(const int32_t *v, uint32_t fp, uint32_t *pk)
+{
+#pragma unroll
+    for (int q = 0; q < 4; q++) pk[q] = requant4_lean<RELU>(v + 4 * q, fp + (uint32_t)(4 * q) * 8u);
+}
+
 // One accumulator row (this thread's TMEM lane), columns [0, ncols) of a tile, ncols % 16 == 0, every `parts`-th
 // 32-column chunk starting with chunk `part`: requantise with the fast form and store.  `orow` is 16-byte
-// aligned; `wide` says it is 32-byte aligned as well (256-bit stores).
+// aligned; `wide` says it is 32-byte aligned as well (256-bit stores).  TMEM is read 16 columns at a time into
+// two register sets in turn: while one half chunk is requantised the load of the next is in flight.
 template <bool RELU>
 __device__ __forceinline__ void epilogue_lean(uint32_t t0, uint32_t fp, int8_t *orow, int ncols, int parts, int part, bool row_ok, bool wide)
 {
-    for (int c0 = part * 32; c0 + 32 <= ncols; c0 += parts * 32) {
-        int32_t v[32];
-        ld32(t0 + c0, v);
-        ld_wait();
+    const int step = parts * 32;
+    int c0 = part * 32;
+    bool have = c0 + 32 <= ncols;
+    int32_t va[16], vb[16];
+    if (have)
+        ld16(t0 + c0, va);
+    while (have) {
         uint32_t pk[8];
-#pragma unroll
-        for (int q = 0; q < 8; q++) pk[q] = requant4_lean<RELU>(v + 4 * q, fp + (uint32_t)(c0 + 4 * q) * 8u);
+        ld_wait();
+        ld16(t0 + c0 + 16, vb);
+        requant16_lean<RELU>(va, fp + (uint32_t)c0 * 8u, pk);
+        ld_wait();
+        const int c1 = c0 + step;
+        have = c1 + 32 <= ncols;
+        if (have)
+            ld16(t0 + c1, va);
+        requant16_lean<RELU>(vb, fp + (uint32_t)(c0 + 16) * 8u, pk + 4);
         if (row_ok) {
             if (wide) {
                 asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(orow + c0), "r"(pk[0]), "r"(pk[1]),
@@ -291,17 +339,51 @@ __device__ __forceinline__ void epilogue_lean(uint32_t t0, uint32_t fp, int8_t *
                 *(uint4 *)(orow + c0 + 16) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             }
         }
+        c0 = c1;
     }
     if ((ncols & 16) && (ncols >> 5) % parts == part) { // trailing half chunk
-        const int c0 = ncols - 16;
+        const int ch = ncols - 16;
         int32_t v[16];
-        ld16(t0 + c0, v);
+        ld16(t0 + ch, v);
         ld_wait();
         uint32_t pk[4];
 #pragma unroll
-        for (int q = 0; q < 4; q++) pk[q] = requant4_lean<RELU>(v + 4 * q, fp + (uint32_t)(c0 + 4 * q) * 8u);
+        for (int q = 0; q < 4; q++) pk[q] = requant4_lean<RELU>(v + 4 * q, fp + (uint32_t)(ch + 4 * q) * 8u);
         if (row_ok)
-            *(uint4 *)(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *(uint4 *)(orow + ch) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
+
+// Staged form of the lean epilogue: this thread's accumulator row, `pw` columns (16..128, multiple of 16) starting at
+// TMEM address t0, requantised and written as row `row` of a [128][pw] byte tile in shared memory, from where one
+// TMA store moves the whole tile to global memory in full lines (a thread storing its own row 32 bytes at a time
+// reaches less than half of the write bandwidth).  The tile uses the TMA swizzle that matches pw (`mask` = 7, 3, 1
+// for 128-, 64-, 32-byte rows, 0 = none): 16-byte chunk index XOR bits 7.. of the byte offset.
+template <bool RELU>
+__device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, uint32_t mask)
+{
+    const uint32_t rbase = (uint32_t)(row * pw);
+    int32_t va[16], vb[16];
+    ld16(t0, va);
+    for (int c = 0; c < pw; c += 32) {
+        uint32_t pk[4];
+        ld_wait();
+        const bool second = c + 16 < pw;
+        if (second)
+            ld16(t0 + c + 16, vb);
+        requant16_lean<RELU>(va, fp + (uint32_t)c * 8u, pk);
+        uint32_t off = rbase + (uint32_t)c;
+        off ^= ((off >> 7) & mask) << 4;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + off), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+        if (!second)
+            break;
+        ld_wait();
+        if (c + 32 < pw)
+            ld16(t0 + c + 32, va);
+        requant16_lean<RELU>(vb, fp + (uint32_t)(c + 16) * 8u, pk);
+        off = rbase + (uint32_t)c + 16u;
+        off ^= ((off >> 7) & mask) << 4;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + off), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
     }
 }
 
