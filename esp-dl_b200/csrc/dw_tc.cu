@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_tc_kernel(const __grid_const
                 if (row_ok) {
                     const int count = min(32, n_valid - c0);
                     if (count > 0)
-                        store_bytes(orow + c0, pk, count, vec_ok);
+                        store_bytes(orow + c0, pk, count, vec_ok ? 16 : 1);
                 }
             }
             fence_before();

@@ -252,6 +252,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!I16) {
                 int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
                 const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
+                // what every row start (and every 16-column step from it) is aligned to
+                const uintptr_t amix = (uintptr_t)p.ops | (((uintptr_t)p.out) + (uintptr_t)n0) | 16u;
+                const int out_align = (int)(amix & (~amix + 1));
                 if (fast && p.out_pw) {
                     // staged: requantise into this group's shared-memory tile, one TMA store per piece
                     const bool leader = (ew & 3) == 0 && lane == 0;
@@ -319,7 +322,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (row_ok) {
                         const int count = min(two ? 32 : 16, p.N - (n0 + c0));
                         if (count > 0)
-                            store_bytes(orow + c0, pk, count, vec_ok);
+                            store_bytes(orow + c0, pk, count, out_align);
                     }
                 }
             } else {

@@ -55,6 +55,35 @@ __global__ void __launch_bounds__(256) pool_kernel(PoolParams p)
     }
 }
 
+// Global average pool, int8, C % 4 == 0: a thread owns four channels (one word of each pixel) of one image and sums
+// the whole plane; lanes are consecutive words, so every load of a warp is one contiguous run.  The four byte sums
+// come from dp4a against one-hot byte selectors.  Same arithmetic as pool_kernel (int32 sum, one fp32 multiply).
+__global__ void __launch_bounds__(256) gap_s8_kernel(PoolParams p)
+{
+    const int quads = p.c >> 2;
+    const long long item = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (item >= (long long)p.n * quads)
+        return;
+    const int q = (int)(item % quads);
+    const long long n = item / quads;
+    const int pixels = p.ih * p.iw;
+    const uint32_t *src = (const uint32_t *)((const int8_t *)p.in + n * (long long)pixels * p.c) + q;
+    int s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+#pragma unroll 7
+    for (int i = 0; i < pixels; i++) {
+        const int w = (int)__ldg(src + (long long)i * quads);
+        s0 = __dp4a(w, 0x00000001, s0);
+        s1 = __dp4a(w, 0x00000100, s1);
+        s2 = __dp4a(w, 0x00010000, s2);
+        s3 = __dp4a(w, 0x01000000, s3);
+    }
+    const int r0 = sat8(fround_half_up(__fmul_rn(__int2float_rn(s0), p.scale)));
+    const int r1 = sat8(fround_half_up(__fmul_rn(__int2float_rn(s1), p.scale)));
+    const int r2 = sat8(fround_half_up(__fmul_rn(__int2float_rn(s2), p.scale)));
+    const int r3 = sat8(fround_half_up(__fmul_rn(__int2float_rn(s3), p.scale)));
+    ((uint32_t *)p.out)[item] = (uint32_t)(r0 & 0xff) | ((uint32_t)(r1 & 0xff) << 8) | ((uint32_t)(r2 & 0xff) << 16) | ((uint32_t)(r3 & 0xff) << 24);
+}
+
 struct ResizeParams {
     const int8_t *in;
     int8_t *out;
@@ -140,6 +169,12 @@ extern "C" int espdl_b200_pool(const espdl_pool_desc *d, void *stream)
     p.total = (long long)p.n * p.oh * p.ow * p.c;
     if (p.total == 0)
         return ESPDL_OK;
+    if (d->op == ESPDL_POOL_GLOBAL_AVG && !p.is16 && p.c % 4 == 0 && ((uintptr_t)d->input % 4) == 0 && ((uintptr_t)d->output % 4) == 0) {
+        const long long items = (long long)p.n * (p.c / 4);
+        gap_s8_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
+        count_launch();
+        return check_launch("global average pool");
+    }
     long long blocks = min((p.total + 255) / 256, (long long)num_sms() * 32);
     pool_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
     count_launch();

@@ -9,7 +9,6 @@
 namespace espdl {
 namespace tc {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull; // every device-side wait gives up after ~2 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -28,13 +27,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ unsigned long long globaltimer()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
 __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
 {
     uint32_t done;
@@ -48,17 +40,22 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
     return done;
 }
 
-// Bounded wait on an mbarrier phase.  Returns false when the limit expires.
+// Bounded wait on an mbarrier phase.  Returns false when the limit expires.  The limit is counted on the SM's own
+// cycle counter (a read of %globaltimer costs on the order of a microsecond, which a waiter that polls it pays on
+// every hand-over of the pipeline); WAIT_LIMIT_CYCLES is about two seconds at the lowest clocks the part runs at.
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
 {
-    for (int spin = 0; spin < 64; spin++)
-        if (mbar_try(bar, parity))
-            return true;
-    const unsigned long long t0 = globaltimer();
+    if (mbar_try(bar, parity))
+        return true;
+    const long long t0 = clock64();
     while (true) {
-        if (mbar_try(bar, parity))
-            return true;
-        if (globaltimer() - t0 > WAIT_LIMIT_NS)
+#pragma unroll 1
+        for (int spin = 0; spin < 256; spin++)
+            if (mbar_try(bar, parity))
+                return true;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES)
             return false;
     }
 }
@@ -408,30 +405,42 @@ __device__ __forceinline__ void requant16_general(const int32_t *v, const EpiCon
     }
 }
 
-// Stores `count` (<= 32) packed int8 starting at `dst`; `words` holds them little-endian.
-__device__ __forceinline__ void store_bytes(int8_t *dst, const uint32_t *words, int count, bool aligned16)
+// Stores `count` (<= 32) packed int8 starting at `dst`; `words` holds them little-endian.  `align` is what the
+// caller knows about dst: 16 (16-byte aligned), 8, 4 or 1; the widest stores that alignment allows are used and
+// the ragged tail goes out byte by byte.
+__device__ __forceinline__ void store_bytes(int8_t *dst, const uint32_t *words, int count, int align)
 {
-    if (count >= 32 && aligned16 && (((uintptr_t)dst) & 31) == 0) {
+    if (count >= 32 && align >= 16 && (((uintptr_t)dst) & 31) == 0) {
         asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(words[0]), "r"(words[1]), "r"(words[2]),
                      "r"(words[3]), "r"(words[4]), "r"(words[5]), "r"(words[6]), "r"(words[7])
                      : "memory");
         return;
     }
-    if (aligned16 && (((uintptr_t)dst) & 15) == 0) {
+    int done = 0;
+    if (align >= 16) {
         if (count >= 16)
             *(uint4 *)dst = make_uint4(words[0], words[1], words[2], words[3]);
         if (count >= 32)
             *(uint4 *)(dst + 16) = make_uint4(words[4], words[5], words[6], words[7]);
-        const int done = count >= 32 ? 32 : (count >= 16 ? 16 : 0);
+        done = count >= 32 ? 32 : (count >= 16 ? 16 : 0);
+    } else if (align >= 8) {
 #pragma unroll
-        for (int j = 0; j < 32; j++) // unrolled with static indices so that `words` stays in registers
-            if (j >= done && j < count)
-                dst[j] = (int8_t)(words[j >> 2] >> (8 * (j & 3)));
-        return;
+        for (int j = 0; j < 4; j++)
+            if (8 * j + 8 <= count) {
+                *(uint2 *)(dst + 8 * j) = make_uint2(words[2 * j], words[2 * j + 1]);
+                done = 8 * j + 8;
+            }
+    } else if (align >= 4) {
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (4 * j + 4 <= count) {
+                *(uint32_t *)(dst + 4 * j) = words[j];
+                done = 4 * j + 4;
+            }
     }
 #pragma unroll
-    for (int j = 0; j < 32; j++)
-        if (j < count)
+    for (int j = 0; j < 32; j++) // unrolled with static indices so that `words` stays in registers
+        if (j >= done && j < count)
             dst[j] = (int8_t)(words[j >> 2] >> (8 * (j & 3)));
 }
 
