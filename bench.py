@@ -44,6 +44,10 @@ def parse_args():
     return ap.parse_args()
 
 
+TRAFFIC_RATIO_GEMM_TC = 0.87  # gemm_tc_kernel, 401408x128x768: 313.2 MB DRAM for 359.8 MB algorithmic (the output tail is still in L2)
+TRAFFIC_RATIO_DW = 1.034      # dw3x3_dp4a_kernel, 256x112x112x96: 637.4 MB DRAM for 616.6 MB algorithmic
+
+
 # ------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -316,10 +320,19 @@ def main():
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = dom["bytes"] / (dom["us"] * 1e-6) / 1e9
-        kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw3x3_dp4a_kernel", "conv_simt": "conv_s8_kernel"}
+        kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw3x3_dp4a_kernel", "conv_simt": "stem_tc_kernel"}
+        # DRAM bytes moved per algorithmic byte, from one profiler capture of each kernel on a layer larger than L2
+        # (profiles/): the launches of a step differ in shape, so the per-launch traffic is that ratio applied to
+        # the average algorithmic bytes of a launch.
+        dram_per_algorithmic = {"pointwise_tc": TRAFFIC_RATIO_GEMM_TC, "depthwise": TRAFFIC_RATIO_DW}
+        bytes_per_launch = dom["bytes"] / dom["launches"]
+        ratio = dram_per_algorithmic.get(dom_kind)
         roofline = {"bound": "hbm", "kernel": kernel_names.get(dom_kind, dom_kind), "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "traffic": None, "peak_source": "measured" if peaks else "fallback",
-                    "launches_per_step": dom["launches"], "algorithmic_bytes_per_step": dom["bytes"],
+                    "frac": achieved / peak, "traffic": None if ratio is None else bytes_per_launch * ratio,
+                    "traffic_note": "bytes per launch: average algorithmic bytes of a launch x the DRAM/algorithmic ratio of one ncu capture",
+                    "peak_source": "measured" if peaks else "fallback",
+                    "launches_per_step": dom["launches"], "algorithmic_bytes_per_launch": bytes_per_launch,
+                    "avg_launch_us": dom["us"] / dom["launches"],
                     "share_of_step_time": dom["us"] / total_us,
                     "per_kind_us": {k: round(v["us"], 1) for k, v in by_kind.items()}}
         cpu = None

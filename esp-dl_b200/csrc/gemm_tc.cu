@@ -74,6 +74,62 @@ struct TcParams {
     EpiConfig epi;
 };
 
+// Epilogue of one int8 tile for outputs that cannot go through the staged path (piece widths that are not whole
+// 16-byte groups, unaligned rows, channels outside the fast form): rows are stored directly from registers.  Out of
+// line on purpose: the staged path in the kernel then carries none of this code's registers.
+__device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastParam *fast_s, uint32_t fp_base, uint32_t t0, long long m, int n0,
+                                                  bool row_ok, bool fast, int parts, int part)
+{
+    int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
+    const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
+    // what every row start (and every 16-column step from it) is aligned to
+    const uintptr_t amix = (uintptr_t)p.ops | (((uintptr_t)p.out) + (uintptr_t)n0) | 16u;
+    const int out_align = (int)(amix & (~amix + 1));
+    if (fast && vec_ok && p.N % 16 == 0) {
+        // whole 16-column groups, aligned rows, one-add-one-shift constants
+        const bool wide = (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
+        const uint32_t fp = fp_base + (uint32_t)n0 * 8u;
+        const int ncols = min(p.block_n, p.N - n0);
+        if (p.epi.relu)
+            epilogue_lean<true>(t0, fp, orow, ncols, parts, part, row_ok, wide);
+        else
+            epilogue_lean<false>(t0, fp, orow, ncols, parts, part, row_ok, wide);
+        return;
+    }
+    int chunk = 0;
+    for (int c0 = 0; c0 < p.block_n; c0 += 32, chunk++) {
+        if (chunk % parts != part)
+            continue;
+        const bool two = c0 + 32 <= p.block_n;
+        int32_t v[32];
+        ld16(t0 + c0, v);
+        if (two)
+            ld16(t0 + c0 + 16, v + 16);
+        ld_wait();
+        uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (fast) {
+            if (p.epi.relu) {
+                requant16_fast<true>(v, fast_s + n0 + c0, pk);
+                if (two)
+                    requant16_fast<true>(v + 16, fast_s + n0 + c0 + 16, pk + 4);
+            } else {
+                requant16_fast<false>(v, fast_s + n0 + c0, pk);
+                if (two)
+                    requant16_fast<false>(v + 16, fast_s + n0 + c0 + 16, pk + 4);
+            }
+        } else {
+            requant16_general(v, p.epi, n0 + c0, p.N, pk);
+            if (two)
+                requant16_general(v + 16, p.epi, n0 + c0 + 16, p.N, pk + 4);
+        }
+        if (row_ok) {
+            const int count = min(two ? 32 : 16, p.N - (n0 + c0));
+            if (count > 0)
+                store_bytes(orow + c0, pk, count, out_align);
+        }
+    }
+}
+
 template <bool I16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -250,11 +306,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const bool row_ok = m < p.M;
             const uint32_t t0 = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * NACC * p.block_n);
             if (!I16) {
-                int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
-                const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
-                // what every row start (and every 16-column step from it) is aligned to
-                const uintptr_t amix = (uintptr_t)p.ops | (((uintptr_t)p.out) + (uintptr_t)n0) | 16u;
-                const int out_align = (int)(amix & (~amix + 1));
                 if (fast && p.out_pw) {
                     // staged: requantise into this group's shared-memory tile, one TMA store per piece
                     const bool leader = (ew & 3) == 0 && lane == 0;
@@ -278,53 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         mbar_arrive(smem_u32(&tempty_bar[acc]));
                     continue;
                 }
-                if (fast && vec_ok && p.N % 16 == 0) {
-                    // the common case: whole 16-column groups, aligned rows, one-add-one-shift constants
-                    const bool wide = (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
-                    const uint32_t fp = fp_base + (uint32_t)n0 * 8u;
-                    const int ncols = min(p.block_n, p.N - n0);
-                    if (p.epi.relu)
-                        epilogue_lean<true>(t0, fp, orow, ncols, parts, part, row_ok, wide);
-                    else
-                        epilogue_lean<false>(t0, fp, orow, ncols, parts, part, row_ok, wide);
-                    fence_before();
-                    __syncwarp();
-                    if (lane == 0)
-                        mbar_arrive(smem_u32(&tempty_bar[acc]));
-                    continue;
-                }
-                int chunk = 0;
-                for (int c0 = 0; c0 < p.block_n; c0 += 32, chunk++) {
-                    if (chunk % parts != part)
-                        continue;
-                    const bool two = c0 + 32 <= p.block_n;
-                    int32_t v[32];
-                    ld16(t0 + c0, v);
-                    if (two)
-                        ld16(t0 + c0 + 16, v + 16);
-                    ld_wait();
-                    uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    if (fast) {
-                        if (p.epi.relu) {
-                            requant16_fast<true>(v, fast_s + n0 + c0, pk);
-                            if (two)
-                                requant16_fast<true>(v + 16, fast_s + n0 + c0 + 16, pk + 4);
-                        } else {
-                            requant16_fast<false>(v, fast_s + n0 + c0, pk);
-                            if (two)
-                                requant16_fast<false>(v + 16, fast_s + n0 + c0 + 16, pk + 4);
-                        }
-                    } else {
-                        requant16_general(v, p.epi, n0 + c0, p.N, pk);
-                        if (two)
-                            requant16_general(v + 16, p.epi, n0 + c0 + 16, p.N, pk + 4);
-                    }
-                    if (row_ok) {
-                        const int count = min(two ? 32 : 16, p.N - (n0 + c0));
-                        if (count > 0)
-                            store_bytes(orow + c0, pk, count, out_align);
-                    }
-                }
+                epilogue_direct_tile(p, fast_s, fp_base, t0, m, n0, row_ok, fast, parts, part);
             } else {
                 int chunk = 0;
                 for (int c0 = 0; c0 < p.block_n; c0 += 16, chunk++) {
