@@ -202,6 +202,9 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank == 0:
+        # the host-core legs use every core: launchers such as torchrun export OMP_NUM_THREADS=1 for their children
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     if args.impl == "reference":
         reference_arm(args, rank)
         return
