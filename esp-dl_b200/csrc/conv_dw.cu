@@ -211,9 +211,11 @@ __global__ void __launch_bounds__(128) dw3x3_s8_kernel(DwParams p, int xtiles, i
 // second output row of a band takes two taps from the group ((0,0,w0,w1)) and its third from a fifth input row,
 // read untransposed with the tap placed in the byte of its channel.  Three transposed columns are live; per
 // output that is 3 (S=1) or 4.5 (S=2) dp4a, about one PRMT, a shift, a max and half a pack.
-// Rows outside the image read a zero word through a pointer that does not advance, so the walk has no per-load
-// bounds checks; columns outside the image are skipped as a whole.
-__device__ const uint32_t g_dw_zero_word[4] = {0u, 0u, 0u, 0u};
+// Rows outside the image walk along a row of zeros instead (g_dw_zero_row), so the walk has no per-load bounds
+// checks and one step size; columns outside the image are skipped as a whole.  Three columns are always in flight
+// (stride 1): with 16 warps per SM it is the bytes in flight, not the arithmetic, that set the speed.
+constexpr int DW_ZERO_ROW_BYTES = 128 * 1024;
+__device__ uint32_t g_dw_zero_row[DW_ZERO_ROW_BYTES / 4]; // never written: what rows outside the image read
 
 template <int S>
 struct DwCol {
@@ -327,17 +329,15 @@ __global__ void __launch_bounds__(128, 4) dw3x3_dp4a_kernel(DwParams p, int xseg
     const int iy0 = oy0 * S - p.pt;
     int ix = x_begin * S - p.pl; // column the row pointers stand on
 
-    // one pointer per input row of the band; rows outside the image stand still on a zero word
+    // one pointer per input row of the band; rows outside the image walk along the row of zeros
     const int8_t *rp[ROWS_IN];
-    int rinc[ROWS_IN];
     {
         const int8_t *img = (const int8_t *)p.in + (long long)n * p.ih * p.iw * p.ips + c0;
 #pragma unroll
         for (int rr = 0; rr < ROWS_IN; rr++) {
             const int iy = iy0 + rr;
             const bool ok = iy >= 0 && iy < p.ih;
-            rp[rr] = ok ? img + ((long long)iy * p.iw + ix) * p.ips : (const int8_t *)g_dw_zero_word;
-            rinc[rr] = ok ? p.ips : 0;
+            rp[rr] = ok ? img + ((long long)iy * p.iw + ix) * p.ips : (const int8_t *)g_dw_zero_row + (long long)(ix + 2) * p.ips;
         }
     }
     int8_t *op = (int8_t *)p.out + (((long long)n * p.oh + oy0) * p.ow + x_begin) * p.ops + c0;
@@ -346,13 +346,13 @@ __global__ void __launch_bounds__(128, 4) dw3x3_dp4a_kernel(DwParams p, int xseg
 #pragma unroll
     for (int ro = 0; ro < ROWS_OUT; ro++) ovalid[ro] = oy0 + ro < p.oh;
 
-    uint32_t raw[ROWS_IN], raw2[ROWS_IN];
+    uint32_t raw[ROWS_IN], raw2[ROWS_IN], raw3[ROWS_IN], raw4[ROWS_IN];
     auto load_col = [&](uint32_t (&dst)[ROWS_IN]) {
         const bool ok = ix >= 0 && ix < p.iw;
 #pragma unroll
         for (int rr = 0; rr < ROWS_IN; rr++) {
             dst[rr] = ok ? __ldg((const uint32_t *)rp[rr]) : 0u;
-            rp[rr] += rinc[rr];
+            rp[rr] += p.ips;
         }
         ix++;
     };
@@ -391,7 +391,7 @@ __global__ void __launch_bounds__(128, 4) dw3x3_dp4a_kernel(DwParams p, int xseg
     };
 
     DwCol<S> ca, cb, cc;
-    if (S == 1) {
+    if constexpr (S == 1) {
         // output x reads input columns x - pl + {0,1,2}: two columns prime the window, every step brings one in,
         // requested one step before it is needed
         load_col(raw);
@@ -399,19 +399,22 @@ __global__ void __launch_bounds__(128, 4) dw3x3_dp4a_kernel(DwParams p, int xseg
         load_col(raw);
         dw_transpose_col<S>(cb, raw);
         load_col(raw);
+        load_col(raw2);
+        load_col(raw3);
+        // three column registers and three load buffers rotate together: the pattern repeats every three outputs
         for (int x = x_begin; x < x_end; x += 3) {
             dw_transpose_col<S>(cc, raw);
             load_col(raw);
             emit(ca, cb, cc);
             if (x + 1 >= x_end)
                 break;
-            dw_transpose_col<S>(ca, raw);
-            load_col(raw);
+            dw_transpose_col<S>(ca, raw2);
+            load_col(raw2);
             emit(cb, cc, ca);
             if (x + 2 >= x_end)
                 break;
-            dw_transpose_col<S>(cb, raw);
-            load_col(raw);
+            dw_transpose_col<S>(cb, raw3);
+            load_col(raw3);
             emit(cc, ca, cb);
         }
     } else {
@@ -420,6 +423,9 @@ __global__ void __launch_bounds__(128, 4) dw3x3_dp4a_kernel(DwParams p, int xseg
         dw_transpose_col<S>(ca, raw);
         load_col(raw);
         load_col(raw2);
+        load_col(raw3);
+        load_col(raw4);
+        // two pairs of load buffers alternate, so four columns are in flight
         for (int x = x_begin; x < x_end; x += 2) {
             dw_transpose_col<S>(cb, raw);
             dw_transpose_col<S>(cc, raw2);
@@ -428,10 +434,10 @@ __global__ void __launch_bounds__(128, 4) dw3x3_dp4a_kernel(DwParams p, int xseg
             emit(ca, cb, cc);
             if (x + 1 >= x_end)
                 break;
-            dw_transpose_col<S>(cb, raw);
-            dw_transpose_col<S>(ca, raw2);
-            load_col(raw);
-            load_col(raw2);
+            dw_transpose_col<S>(cb, raw3);
+            dw_transpose_col<S>(ca, raw4);
+            load_col(raw3);
+            load_col(raw4);
             emit(cc, cb, ca);
         }
     }
@@ -498,7 +504,7 @@ int conv2d_depthwise(const espdl_conv_desc &d, cudaStream_t s)
     const bool k3 = d.dtype == ESPDL_DTYPE_INT8 && d.kh == 3 && d.kw == 3 && d.dilation_h == 1 && d.dilation_w == 1 &&
         d.stride_h == d.stride_w && (d.stride_h == 1 || d.stride_h == 2) && d.in_c % 4 == 0 && p.ips % 4 == 0 && p.ops % 4 == 0 &&
         ((uintptr_t)d.input % 4) == 0 && ((uintptr_t)d.output % 4) == 0 && ((uintptr_t)d.filter % 4) == 0;
-    if (k3) {
+    if (k3 && ((long long)d.in_w + 10) * p.ips <= DW_ZERO_ROW_BYTES) {
         // a thread walks along a whole band of rows when the batch gives enough threads without cutting the band
         const int rows_out = d.stride_h == 1 ? 4 : 2;
         const int ytiles = (d.out_h + rows_out - 1) / rows_out;
