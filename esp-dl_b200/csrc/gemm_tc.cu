@@ -314,10 +314,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         bulk_wait_read_all(); // the previous store out of this tile has been read
                     named_bar(2 + group, 128);
                     const int col0 = part * p.out_pw;
-                    if (p.epi.relu)
-                        epilogue_stage<true>(t0 + col0, fp_base + (uint32_t)(n0 + col0) * 8u, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask);
+                    const uint32_t fpp = fp_base + (uint32_t)(n0 + col0) * 8u;
+                    const int floor_q = p.epi.relu ? 0 : INT_MIN;
+                    if (p.out_pw == 128)
+                        epilogue_stage<128>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q);
+                    else if (p.out_pw == 96)
+                        epilogue_stage<96>(t0 + col0, fpp, buf, row_in_tile, 96, floor_q);
+                    else if (p.out_pw == 64)
+                        epilogue_stage<64>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q);
                     else
-                        epilogue_stage<false>(t0 + col0, fp_base + (uint32_t)(n0 + col0) * 8u, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask);
+                        epilogue_stage<0>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q);
                     fence_before();
                     fence_async_smem();
                     named_bar(2 + group, 128);
@@ -454,6 +460,8 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
     const int max_bn = i16 ? 128 : 256;
     p.n_tiles = (p.N + max_bn - 1) / max_bn;
     p.block_n = (((p.N + p.n_tiles - 1) / p.n_tiles) + 15) / 16 * 16;
+    if (!i16 && p.block_n > 128)
+        p.block_n = (p.block_n + 31) / 32 * 32; // two epilogue groups split a wide tile into whole 16-byte pieces
     p.n_tiles = (p.N + p.block_n - 1) / p.block_n;
     p.m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
     p.swz = pick_swz(p.K);
@@ -472,7 +480,7 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
         const int parts = 4 / p.acc_stages;
         if (p.block_n % (16 * parts) == 0 && p.block_n / parts <= 128) {
             p.out_pw = p.block_n / parts;
-            p.out_mask = p.out_pw == 128 ? 7 : (p.out_pw == 64 ? 3 : (p.out_pw == 32 ? 1 : 0));
+            p.out_mask = p.out_pw == 128 ? 7 : (p.out_pw == 64 ? 3 : 0);
         }
     }
     size_t out_bytes = 4 * (size_t)((BLOCK_M * p.out_pw + 1023) & ~1023);
@@ -565,7 +573,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     size_t smem = 1024 + (size_t)p.stages * stage_bytes + 4 * (size_t)((BLOCK_M * p.out_pw + 1023) & ~1023) + aux_bytes(p);
     CUtensorMap mo = ma;
     if (p.out_pw) {
-        const int osw = p.out_pw == 128 ? 128 : (p.out_pw == 64 ? 64 : (p.out_pw == 32 ? 32 : 0));
+        const int osw = p.out_pw == 128 ? 128 : (p.out_pw == 64 ? 64 : 0);
         if ((st = make_map(&mo, d.output, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.ops, BLOCK_M, (uint32_t)p.out_pw, osw)))
             return st;
     }

@@ -351,36 +351,68 @@ __device__ __forceinline__ void epilogue_lean(uint32_t t0, uint32_t fp, int8_t *
     }
 }
 
-// Staged form of the lean epilogue: this thread's accumulator row, `pw` columns (16..128, multiple of 16) starting at
-// TMEM address t0, requantised and written as row `row` of a [128][pw] byte tile in shared memory, from where one
-// TMA store moves the whole tile to global memory in full lines (a thread storing its own row 32 bytes at a time
-// reaches less than half of the write bandwidth).  The tile uses the TMA swizzle that matches pw (`mask` = 7, 3, 1
-// for 128-, 64-, 32-byte rows, 0 = none): 16-byte chunk index XOR bits 7.. of the byte offset.
-template <bool RELU>
-__device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, uint32_t mask)
+// Four accumulator columns -> one word of four saturated int8; `floor_q` is 0 with ReLU and INT_MIN without, so
+// the add and the lower clamp are one instruction either way (max commutes with the arithmetic shift).
+__device__ __forceinline__ uint32_t requant4_floor(const int32_t *v, uint32_t fp, int floor_q)
 {
-    const uint32_t rbase = (uint32_t)(row * pw);
+    int b0, s0, b1, s1, b2, s2, b3, s3;
+    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(b0), "=r"(s0), "=r"(b1), "=r"(s1) : "r"(fp));
+    asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(b2), "=r"(s2), "=r"(b3), "=r"(s3) : "r"(fp + 16));
+    const int r0 = __viaddmax_s32(v[0], b0, floor_q) >> s0;
+    const int r1 = __viaddmax_s32(v[1], b1, floor_q) >> s1;
+    const int r2 = __viaddmax_s32(v[2], b2, floor_q) >> s2;
+    const int r3 = __viaddmax_s32(v[3], b3, floor_q) >> s3;
+    uint32_t hi, w;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(r3), "r"(r2));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r1), "r"(r0), "r"(hi));
+    return w;
+}
+
+// Staged epilogue: this thread's accumulator row, PW columns (multiple of 16, at most 128) starting at TMEM address
+// t0, requantised and written as row `row` of a [128][PW] byte tile in shared memory, from where one TMA store moves
+// the whole tile to global memory in full lines (a thread storing its own row 32 bytes at a time reaches less than
+// half of the write bandwidth).  The tile uses the TMA swizzle that matches PW (128-, 64-, 32-byte rows; none for
+// other widths): 16-byte chunk index XOR bits 7.. of the byte offset, which for these widths is a function of the
+// row alone.  PW is a template parameter so that the walk over the columns is straight-line code; PW = 0 is the
+// generic form for any width (`pw`).  TMEM is read 16 columns at a time into two register sets in turn.
+template <int PW>
+__device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, int floor_q)
+{
+    const int width = PW ? PW : pw;
+    uint32_t rx = 0; // what the chunk offset of this row is XORed with
+    if (PW == 128)
+        rx = ((uint32_t)row & 7u) << 4;
+    else if (PW == 64)
+        rx = (((uint32_t)row >> 1) & 3u) << 4;
+    else if (PW == 32)
+        rx = (((uint32_t)row >> 2) & 1u) << 4;
+    const uint32_t rb = buf + (uint32_t)(row * width);
     int32_t va[16], vb[16];
     ld16(t0, va);
-    for (int c = 0; c < pw; c += 32) {
+#pragma unroll
+    for (int c = 0; c < (PW ? PW : 128); c += 32) {
+        if (!PW && c >= pw)
+            break;
         uint32_t pk[4];
         ld_wait();
-        const bool second = c + 16 < pw;
+        const bool second = PW ? (c + 16 < PW) : (c + 16 < pw);
         if (second)
             ld16(t0 + c + 16, vb);
-        requant16_lean<RELU>(va, fp + (uint32_t)c * 8u, pk);
-        uint32_t off = rbase + (uint32_t)c;
-        off ^= ((off >> 7) & mask) << 4;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + off), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+#pragma unroll
+        for (int q = 0; q < 4; q++) pk[q] = requant4_floor(va + 4 * q, fp + (uint32_t)(c + 4 * q) * 8u, floor_q);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)c ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                     : "memory");
         if (!second)
             break;
         ld_wait();
-        if (c + 32 < pw)
+        const bool more = PW ? (c + 32 < PW) : (c + 32 < pw);
+        if (more)
             ld16(t0 + c + 32, va);
-        requant16_lean<RELU>(vb, fp + (uint32_t)(c + 16) * 8u, pk);
-        off = rbase + (uint32_t)c + 16u;
-        off ^= ((off >> 7) & mask) << 4;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + off), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+#pragma unroll
+        for (int q = 0; q < 4; q++) pk[q] = requant4_floor(vb + 4 * q, fp + (uint32_t)(c + 16 + 4 * q) * 8u, floor_q);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)(c + 16) ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
+                     "r"(pk[3])
+                     : "memory");
     }
 }
 
