@@ -235,7 +235,8 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_tc_kernel(const __grid_const
                 int32_t v[32];
                 ld16(t0 + c0, v);
                 ld16(t0 + c0 + 16, v + 16);
-                ld_wait();
+                ld_wait16(v);
+                tie16(v + 16);
                 uint32_t pk[8];
                 if (fast) {
                     if (epi.relu) {

@@ -105,7 +105,8 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
         ld16(t0 + c0, v);
         if (two)
             ld16(t0 + c0 + 16, v + 16);
-        ld_wait();
+        ld_wait16(v);
+        tie16(v + 16);
         uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (fast) {
             if (p.epi.relu) {
@@ -345,7 +346,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ld16(t0 + c0, vh);
                     ld16(t0 + p.block_n + c0, vm);
                     ld16(t0 + 2 * p.block_n + c0, vl);
-                    ld_wait();
+                    ld_wait16(vh);
+                    tie16(vm);
+                    tie16(vl);
                     if (row_ok && n0 + c0 < p.N) {
                         int16_t *op = (int16_t *)p.out + m * p.ops + n0 + c0;
 #pragma unroll

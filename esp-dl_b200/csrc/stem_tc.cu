@@ -256,7 +256,7 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
                         continue;
                     int32_t v[16];
                     ld16(t0 + c0, v);
-                    ld_wait();
+                    ld_wait16(v);
                     uint32_t pk[4] = {0, 0, 0, 0};
 #pragma unroll
                     for (int i = 0; i < 16; i++) {

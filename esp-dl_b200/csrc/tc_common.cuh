@@ -166,6 +166,28 @@ __device__ __forceinline__ void ld32(uint32_t taddr, int32_t *v)
 
 __device__ __forceinline__ void ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Waits for the TMEM loads and ties the 16 destination registers to the wait: to the compiler the values only exist
+// after this statement, so no arithmetic on them can be scheduled ahead of tcgen05.wait::ld (a tcgen05.ld asm alone
+// looks as if it had already produced them).
+__device__ __forceinline__ void ld_wait16(int32_t *v)
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                   "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
+
+// Same tie for registers whose load was already waited for by an earlier statement (no instruction is emitted).
+__device__ __forceinline__ void tie16(int32_t *v)
+{
+    asm volatile(""
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                   "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
+
 // Shared-memory matrix descriptor (64 bit):
 //   [0,14) start address >> 4   [16,30) leading-dimension byte offset >> 4   [32,46) stride-dimension byte offset >> 4
 //   [46,48) version = 1         [61,64) layout: 0 = no swizzle, 2 = 128B, 4 = 64B, 6 = 32B swizzle
@@ -317,10 +339,10 @@ __device__ __forceinline__ void epilogue_lean(uint32_t t0, uint32_t fp, int8_t *
         ld16(t0 + c0, va);
     while (have) {
         uint32_t pk[8];
-        ld_wait();
+        ld_wait16(va);
         ld16(t0 + c0 + 16, vb);
         requant16_lean<RELU>(va, fp + (uint32_t)c0 * 8u, pk);
-        ld_wait();
+        ld_wait16(vb);
         const int c1 = c0 + step;
         have = c1 + 32 <= ncols;
         if (have)
@@ -342,7 +364,7 @@ __device__ __forceinline__ void epilogue_lean(uint32_t t0, uint32_t fp, int8_t *
         const int ch = ncols - 16;
         int32_t v[16];
         ld16(t0 + ch, v);
-        ld_wait();
+        ld_wait16(v);
         uint32_t pk[4];
 #pragma unroll
         for (int q = 0; q < 4; q++) pk[q] = requant4_lean<RELU>(v + 4 * q, fp + (uint32_t)(ch + 4 * q) * 8u);
@@ -394,7 +416,7 @@ __device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_
         if (!PW && c >= pw)
             break;
         uint32_t pk[4];
-        ld_wait();
+        ld_wait16(va);
         const bool second = PW ? (c + 16 < PW) : (c + 16 < pw);
         if (second)
             ld16(t0 + c + 16, vb);
@@ -404,7 +426,7 @@ __device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_
                      : "memory");
         if (!second)
             break;
-        ld_wait();
+        ld_wait16(vb);
         const bool more = PW ? (c + 32 < PW) : (c + 32 < pw);
         if (more)
             ld16(t0 + c + 32, va);

@@ -131,3 +131,14 @@ def test_stem_conv_tensor_core(kw):
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT), want)
     assert want.std() > 0
+
+
+@pytest.mark.parametrize("m,k,n,rm", [(1, 64, 32, abi.ROUND_HALF_EVEN), (130, 64, 32, abi.ROUND_HALF_UP), (200, 128, 256, abi.ROUND_HALF_UP),
+                                      (300, 96, 1000, abi.ROUND_HALF_UP), (77, 160, 240, abi.ROUND_HALF_EVEN)])
+def test_tile_kernel_direct_row_stores(m, k, n, rm, monkeypatch):
+    """The same tiles with the staged (TMA-store) epilogue switched off: rows go out of registers directly."""
+    case = cases.gemm_case(seed=17, m=m, k=k, n_out=n, round_mode=rm, per_channel=True)
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+    monkeypatch.setenv("ESPDL_B200_DIRECT_STORES", "1")
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
