@@ -152,8 +152,9 @@ int espdl_b200_stream_sync(void *stream)
     int dev = read_and_clear_device_error();
     const int dev_dw = read_and_clear_device_error_dw();
     const int dev_stem = read_and_clear_device_error_stem();
+    const int dev_conv = read_and_clear_device_error_conv();
     if (!dev)
-        dev = dev_dw ? dev_dw : dev_stem;
+        dev = dev_dw ? dev_dw : (dev_stem ? dev_stem : dev_conv);
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -342,6 +343,9 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
     }
     if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_stem_tc_supported(*desc))
         return conv2d_stem_tc(*desc, s); // 3x3 stride-2 RGB first layer: banded-filter tensor-core kernel
+    const bool conv_tc_ok = conv2d_conv_tc_supported(*desc);
+    if (conv_tc_ok && desc->kernel != ESPDL_KERNEL_SIMT)
+        return conv2d_conv_tc(*desc, s); // filters larger than 1x1 (or strided): implicit GEMM over the taps
     const bool tc_ok = conv2d_tc_supported(*desc);
     if (desc->kernel == ESPDL_KERNEL_TCGEN05 && !tc_ok)
         return ESPDL_ERR_UNSUPPORTED;

@@ -33,6 +33,9 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
 int read_and_clear_device_error(); // status word written by device-side bounded waits (0 = none)
 int read_and_clear_device_error_dw();
 int read_and_clear_device_error_stem();
+int read_and_clear_device_error_conv();
+bool conv2d_conv_tc_supported(const espdl_conv_desc &d);
+int conv2d_conv_tc(const espdl_conv_desc &d, cudaStream_t s);
 bool conv2d_stem_tc_supported(const espdl_conv_desc &d);
 int conv2d_stem_tc(const espdl_conv_desc &d, cudaStream_t s);
 bool conv2d_dw_tc_supported(const espdl_conv_desc &d);

@@ -142,3 +142,41 @@ def test_tile_kernel_direct_row_stores(m, k, n, rm, monkeypatch):
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
     monkeypatch.setenv("ESPDL_B200_DIRECT_STORES", "1")
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+
+
+CONV_TC_SHAPES = [
+    dict(n=1, h=56, w=56, cin=64, cout=64),                                   # the single-image 3x3 configuration
+    dict(n=3, h=20, w=17, cin=16, cout=48),                                   # ragged tiles, 16-channel rows
+    dict(n=2, h=14, w=14, cin=96, cout=200),                                  # Cin fills three quarters of a 128-byte row, ragged Cout
+    dict(n=2, h=28, w=28, cin=160, cout=64),                                  # two channel blocks per tap
+    dict(n=2, h=33, w=29, cin=32, cout=32, stride=2, pad=(0, 1, 0, 1)),       # stride 2 through TMA element strides
+    dict(n=2, h=31, w=30, cin=48, cout=80, stride=2),
+    dict(n=1, h=24, w=24, cin=32, cout=64, kh=5, kw=5, pad=(2, 2, 2, 2)),     # 25 taps
+    dict(n=2, h=19, w=23, cin=32, cout=16, kh=3, kw=3, dil=2, pad=(2, 2, 2, 2)),
+    dict(n=2, h=12, w=40, cin=64, cout=320, kh=1, kw=3, pad=(0, 0, 1, 1)),    # two tiles along Cout
+    dict(n=2, h=16, w=16, cin=64, cout=64, kh=1, kw=1, stride=2, pad=(0, 0, 0, 0)),  # strided pointwise (downsample shortcut)
+    dict(n=2, h=9, w=9, cin=32, cout=32, pad=(0, 0, 0, 0)),                   # no padding
+]
+
+
+@pytest.mark.parametrize("kw", CONV_TC_SHAPES, ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items() if a != "pad"))
+def test_conv_implicit_gemm_tensor_core(kw):
+    """Dense conv with a real filter window through the implicit-GEMM tile kernel, against the oracle and the CUDA-core kernel."""
+    kw = dict(kw)
+    kw.setdefault("kh", 3)
+    kw.setdefault("kw", 3)
+    case = cases.conv_case(seed=77, per_channel=True, e_in=-7, e_out=-6, e_w=(-9, -6), **kw)
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT), want)
+    assert want.std() > 0
+
+
+@pytest.mark.parametrize("round_mode,act,bias,lut,direct", [(abi.ROUND_HALF_EVEN, abi.ACT_RELU, True, False, False), (abi.ROUND_HALF_UP, abi.ACT_LINEAR, False, False, False),
+                                                            (abi.ROUND_HALF_UP, abi.ACT_RELU, True, True, False), (abi.ROUND_HALF_UP, abi.ACT_RELU, True, False, True)])
+def test_conv_implicit_gemm_epilogue_variants(round_mode, act, bias, lut, direct, monkeypatch):
+    if direct:
+        monkeypatch.setenv("ESPDL_B200_DIRECT_STORES", "1")
+    case = cases.conv_case(seed=78, n=2, h=18, w=22, cin=32, cout=48, kh=3, kw=3, per_channel=True, round_mode=round_mode, act=act, bias=bias, lut=lut,
+                           e_in=-7, e_out=-6, e_w=(-9, -6))
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), gpu_util.run_conv_oracle(case))
