@@ -58,8 +58,9 @@ def test_tc_and_simt_agree_and_auto_picks_tc():
 def test_tc_rejects_shapes_it_cannot_run():
     case = cases.gemm_case(seed=9, m=64, k=24, n_out=16)  # K not a multiple of 16
     gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05, expect=abi.ERR_UNSUPPORTED)
-    case = cases.conv_case(seed=9, cin=16, cout=16, kh=3, kw=3)
+    case = cases.conv_case(seed=9, cin=24, cout=16, kh=3, kw=3)  # 3x3 with Cin not a multiple of 16
     gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05, expect=abi.ERR_UNSUPPORTED)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), gpu_util.run_conv_oracle(case))
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(cases.gemm_case(seed=9, m=64, k=24, n_out=16)),
                                   gpu_util.run_conv_oracle(cases.gemm_case(seed=9, m=64, k=24, n_out=16)))
 
