@@ -99,6 +99,9 @@ SYMBOLS = {
     "espdl_b200_event_destroy": (C.c_int, [C.c_void_p]),
     "espdl_b200_event_record": (C.c_int, [C.c_void_p, C.c_void_p]),
     "espdl_b200_event_elapsed_ms": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]),
+    "espdl_b200_event_sync": (C.c_int, [C.c_void_p]),
+    "espdl_b200_stream_wait_event": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "espdl_b200_device_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "espdl_b200_graph_begin": (C.c_int, [C.c_void_p]),
     "espdl_b200_graph_end": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "espdl_b200_graph_launch": (C.c_int, [C.c_void_p, C.c_void_p]),

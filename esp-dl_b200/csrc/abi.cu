@@ -230,6 +230,30 @@ int espdl_b200_event_elapsed_ms(void *start, void *stop, float *ms)
     return ESPDL_OK;
 }
 
+int espdl_b200_event_sync(void *event)
+{
+    if (!event)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaEventSynchronize((cudaEvent_t)event));
+    return ESPDL_OK;
+}
+
+int espdl_b200_stream_wait_event(void *stream, void *event)
+{
+    if (!event)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaStreamWaitEvent((cudaStream_t)stream, (cudaEvent_t)event, 0));
+    return ESPDL_OK;
+}
+
+int espdl_b200_device_copy(void *dst_dev, const void *src_dev, size_t bytes, void *stream)
+{
+    if ((!dst_dev || !src_dev) && bytes)
+        return ESPDL_ERR_INVALID_ARG;
+    ESPDL_CUDA_TRY(cudaMemcpyAsync(dst_dev, src_dev, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
 int espdl_b200_graph_begin(void *stream)
 {
     if (!stream)

@@ -128,8 +128,39 @@ Model::Model(fbs::FbsModel *fbs_model, int internal_size, memory_manager_t mm_ty
         build(internal_size, mm_type, false, input_shapes);
 }
 
+void Model::release_pipeline()
+{
+    if (m_copy_stream)
+        espdl_b200_stream_sync(m_copy_stream);
+    for (auto &kv : m_in_stage)
+        if (kv.second)
+            espdl_b200_arena_free(kv.second);
+    m_in_stage.clear();
+    for (int s = 0; s < 2; s++) {
+        for (auto &kv : m_out_stage[s])
+            if (kv.second)
+                espdl_b200_host_free(kv.second);
+        m_out_stage[s].clear();
+        if (m_ev_done[s])
+            espdl_b200_event_destroy(m_ev_done[s]);
+        m_ev_done[s] = nullptr;
+    }
+    if (m_ev_uploaded)
+        espdl_b200_event_destroy(m_ev_uploaded);
+    if (m_ev_consumed)
+        espdl_b200_event_destroy(m_ev_consumed);
+    m_ev_uploaded = m_ev_consumed = nullptr;
+    if (m_copy_stream)
+        espdl_b200_stream_destroy(m_copy_stream);
+    m_copy_stream = nullptr;
+    m_submitted = m_collected = 0;
+}
+
 void Model::release()
 {
+    if (m_model_context && m_model_context->stream)
+        espdl_b200_stream_sync(m_model_context->stream);
+    release_pipeline();
     if (m_graph)
         espdl_b200_graph_destroy(m_graph);
     m_graph = nullptr;
@@ -443,6 +474,77 @@ void Model::run(runtime_mode_t mode)
     int st = espdl_b200_stream_sync(ctx->stream);
     if (st)
         m_status = st;
+}
+
+esp_err_t Model::submit()
+{
+    if (!m_built || m_submitted - m_collected >= 2)
+        return ESP_FAIL;
+    ModelContext *ctx = m_model_context;
+    int st = ESPDL_OK;
+    if (!m_copy_stream) {
+        // first use: second stream, events, a device staging buffer per input, two pinned slots per output
+        st = espdl_b200_stream_create(&m_copy_stream);
+        if (!st) st = espdl_b200_event_create(&m_ev_uploaded);
+        if (!st) st = espdl_b200_event_create(&m_ev_consumed);
+        for (int s = 0; s < 2 && !st; s++) st = espdl_b200_event_create(&m_ev_done[s]);
+        for (auto &kv : m_inputs)
+            if (!st)
+                st = espdl_b200_arena_alloc(kv.second->get_bytes(), &m_in_stage[kv.first]);
+        for (int s = 0; s < 2; s++)
+            for (auto &kv : m_outputs)
+                if (!st)
+                    st = espdl_b200_host_alloc(kv.second->get_bytes(), &m_out_stage[s][kv.first]);
+        if (!st && !m_graph && m_use_graph) // capture the plan before the first pipelined pass
+            st = run_device(true) == ESP_OK ? ESPDL_OK : (m_status ? m_status : ESPDL_ERR_CUDA);
+    }
+    // upload on the copy stream as soon as the previous submission has taken its inputs out of the staging buffers
+    if (!st && m_submitted > 0)
+        st = espdl_b200_stream_wait_event(m_copy_stream, m_ev_consumed);
+    for (auto &kv : m_inputs)
+        if (!st && kv.second->data)
+            st = espdl_b200_upload(m_in_stage[kv.first], kv.second->data, kv.second->get_bytes(), m_copy_stream);
+    if (!st) st = espdl_b200_event_record(m_ev_uploaded, m_copy_stream);
+    if (!st) st = espdl_b200_event_sync(m_ev_uploaded); // the host buffers are free again when submit() returns
+    // plan on the compute stream: staging -> input tensors, forward pass, outputs -> this submission's pinned slot
+    if (!st) st = espdl_b200_stream_wait_event(ctx->stream, m_ev_uploaded);
+    for (auto &kv : m_inputs)
+        if (!st)
+            st = espdl_b200_device_copy(kv.second->device, m_in_stage[kv.first], kv.second->get_bytes(), ctx->stream);
+    if (!st) st = espdl_b200_event_record(m_ev_consumed, ctx->stream);
+    if (!st && run_device(false) != ESP_OK)
+        st = m_status ? m_status : ESPDL_ERR_CUDA;
+    const int slot = (int)(m_submitted & 1);
+    for (auto &kv : m_outputs)
+        if (!st)
+            st = espdl_b200_download(m_out_stage[slot][kv.first], kv.second->device, kv.second->get_bytes(), ctx->stream);
+    if (!st) st = espdl_b200_event_record(m_ev_done[slot], ctx->stream);
+    if (st) {
+        m_status = st;
+        return ESP_FAIL;
+    }
+    m_submitted++;
+    return ESP_OK;
+}
+
+esp_err_t Model::wait()
+{
+    if (m_collected >= m_submitted)
+        return ESP_FAIL;
+    const int slot = (int)(m_collected & 1);
+    int st = espdl_b200_event_sync(m_ev_done[slot]);
+    if (!st)
+        for (auto &kv : m_outputs)
+            if (kv.second->data)
+                memcpy(kv.second->data, m_out_stage[slot][kv.first], kv.second->get_bytes());
+    m_collected++;
+    if (!st && m_collected == m_submitted) // queue drained: a good moment to pick up a kernel's bounded-wait status
+        st = espdl_b200_stream_sync(m_model_context->stream);
+    if (st) {
+        m_status = st;
+        return ESP_FAIL;
+    }
+    return ESP_OK;
 }
 
 void Model::run(TensorBase *input, runtime_mode_t mode)

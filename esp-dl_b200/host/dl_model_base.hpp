@@ -76,6 +76,13 @@ public:
     virtual void run(int stage_num, int stage_index, runtime_mode_t mode = RUNTIME_MODE_SINGLE_CORE);
     /// Execute the plan on the device-resident inputs only (no host copies); asynchronous unless `sync`.
     esp_err_t run_device(bool sync = true);
+    /// Pipelined form of run() for a stream of batches.  submit() uploads the inputs' host buffers (it returns once
+    /// that copy is done, so the buffers may be refilled at once), then enqueues the plan and the download of the
+    /// outputs without waiting for them; the upload of one submission overlaps the execution of the one before it
+    /// (second stream, a staging buffer per input).  wait() blocks until the OLDEST outstanding submission has
+    /// finished and copies its outputs into the outputs' host buffers.  At most two submissions may be outstanding.
+    esp_err_t submit();
+    esp_err_t wait();
 
     esp_err_t test();
     std::map<std::string, module_info> get_module_info();
@@ -120,6 +127,12 @@ protected:
     void *m_arena = nullptr;
     size_t m_arena_bytes = 0;
     void *m_graph = nullptr;
+    // submit()/wait() state
+    void *m_copy_stream = nullptr, *m_ev_uploaded = nullptr, *m_ev_consumed = nullptr, *m_ev_done[2] = {nullptr, nullptr};
+    std::map<std::string, void *> m_in_stage;                 ///< device staging buffer per graph input
+    std::map<std::string, void *> m_out_stage[2];             ///< pinned host staging per graph output, two slots
+    long long m_submitted = 0, m_collected = 0;
+    void release_pipeline();
     bool m_built = false;
     std::vector<TensorInfo> m_tensor_infos;
 };

@@ -103,6 +103,18 @@ int espdl_model_run_device(void *handle, int sync)
     return h->model->m_status;
 }
 
+int espdl_model_submit(void *handle)
+{
+    Handle *h = (Handle *)handle;
+    return h->model->submit() == ESP_OK ? 0 : (h->model->m_status ? h->model->m_status : -1);
+}
+
+int espdl_model_wait(void *handle)
+{
+    Handle *h = (Handle *)handle;
+    return h->model->wait() == ESP_OK ? 0 : (h->model->m_status ? h->model->m_status : -1);
+}
+
 int espdl_model_test(void *handle) { return ((Handle *)handle)->model->test(); }
 
 void *espdl_model_stream(void *handle) { return ((Handle *)handle)->model->stream(); }

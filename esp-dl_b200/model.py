@@ -26,6 +26,8 @@ def host_lib():
                                           C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
         L.espdl_model_run.argtypes = [C.c_void_p]
         L.espdl_model_run_device.argtypes = [C.c_void_p, C.c_int]
+        L.espdl_model_submit.argtypes = [C.c_void_p]
+        L.espdl_model_wait.argtypes = [C.c_void_p]
         L.espdl_model_test.argtypes = [C.c_void_p]
         L.espdl_model_stream.restype = C.c_void_p
         L.espdl_model_stream.argtypes = [C.c_void_p]
@@ -74,6 +76,14 @@ class Model:
     def run(self):
         """Host buffers -> device, execute, device -> host buffers (the call a user of dl::Model makes)."""
         abi.check(self.lib.espdl_model_run(self.h), "Model::run")
+
+    def submit(self):
+        """Pipelined run(): uploads the input arrays (they may be refilled when this returns) and enqueues the pass."""
+        abi.check(self.lib.espdl_model_submit(self.h), "Model::submit")
+
+    def wait(self):
+        """Blocks until the oldest submitted pass is done; its results are then in the output arrays."""
+        abi.check(self.lib.espdl_model_wait(self.h), "Model::wait")
 
     def run_device(self, sync=True):
         abi.check(self.lib.espdl_model_run_device(self.h, 1 if sync else 0), "Model::run_device")

@@ -94,6 +94,9 @@ int espdl_b200_event_create(void **event);
 int espdl_b200_event_destroy(void *event);
 int espdl_b200_event_record(void *event, void *stream);
 int espdl_b200_event_elapsed_ms(void *start, void *stop, float *ms); /* synchronises on `stop` */
+int espdl_b200_event_sync(void *event);                    /* host waits until the event has happened      */
+int espdl_b200_stream_wait_event(void *stream, void *event); /* later work on `stream` waits for the event */
+int espdl_b200_device_copy(void *dst_dev, const void *src_dev, size_t bytes, void *stream); /* device to device */
 int espdl_b200_graph_begin(void *stream);                 /* start capturing work enqueued on `stream`   */
 int espdl_b200_graph_end(void *stream, void **graph);     /* stop capturing, instantiate                 */
 int espdl_b200_graph_launch(void *graph, void *stream);

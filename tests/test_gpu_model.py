@@ -80,6 +80,63 @@ def test_inverted_residual_block(tmp_path):
     m.close()
 
 
+def test_inverted_residual_block_full_batch(tmp_path):
+    """The block configuration at its full size, 256 images of 112x112x32: the images are independent units, so the
+    oracle (run on eight images picked from all over the batch) pins those rows, and every row must equal the row a
+    batch of eight gives for the same image."""
+    path = str(tmp_path / "block.espdl")
+    zoo.inverted_residual_block(seed=4).save(path)
+    parsed = espdl_file.read(path)
+    m = model.Model(path, batch=256)
+    rng = np.random.default_rng(41)
+    x = rng.integers(-128, 128, size=m.inputs[0].shape, dtype=np.int8)
+    x[17] = x[200]                      # two equal images far apart must give equal rows
+    m.inputs[0].array[...] = x
+    m.run()
+    got = m.outputs[0].array.copy()
+    m.close()
+    picks = [0, 1, 17, 63, 128, 200, 254, 255]
+    want = graph_oracle.run_graph(parsed, {"input": np.ascontiguousarray(x[picks])})[parsed["outputs"][0]["name"]]
+    np.testing.assert_array_equal(got[picks], want)
+    np.testing.assert_array_equal(got[17], got[200])
+    m8 = model.Model(path, batch=8)
+    for start in (8, 120, 248):
+        m8.inputs[0].array[...] = x[start:start + 8]
+        m8.run()
+        np.testing.assert_array_equal(m8.outputs[0].array, got[start:start + 8])
+    m8.close()
+
+
+def test_submit_wait_pipeline_equals_run(tmp_path):
+    """submit()/wait(): a stream of different batches through the pipelined entry points gives run()'s results, in
+    order, with the input array refilled right after every submit."""
+    path = str(tmp_path / "net.espdl")
+    zoo.inverted_residual_block(seed=4, hw=28).save(path)
+    m = model.Model(path, batch=4)
+    rng = np.random.default_rng(2)
+    batches = [rng.integers(-128, 128, size=m.inputs[0].shape, dtype=np.int8) for _ in range(5)]
+    want = []
+    for b in batches:
+        m.inputs[0].array[...] = b
+        m.run()
+        want.append(m.outputs[0].array.copy())
+    got = []
+    for i, b in enumerate(batches):
+        m.inputs[0].array[...] = b
+        m.submit()
+        m.inputs[0].array[...] = 0x11        # the host buffer is free again
+        if i >= 1:
+            m.wait()
+            got.append(m.outputs[0].array.copy())
+    m.wait()
+    got.append(m.outputs[0].array.copy())
+    for g, w in zip(got, want):
+        np.testing.assert_array_equal(g, w)
+    with pytest.raises(RuntimeError):
+        m.wait()                             # nothing outstanding
+    m.close()
+
+
 def test_staged_run_equals_single_run(tmp_path):
     """run(stage_num, stage_index) over all stages gives run()'s result (reference: test_dl_api.cpp:70-98)."""
     path = str(tmp_path / "net.espdl")
