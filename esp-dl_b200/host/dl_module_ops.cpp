@@ -372,6 +372,128 @@ Module *Gemm::deserialize(fbs::FbsModel *fbs_model, std::string node_name)
     return new Gemm(activation_type, node_name.c_str(), quant_type, model_target(fbs_model));
 }
 
+// --------------------------------------------------------------------------------- MatMul
+static std::vector<int> broadcast_shape(const std::vector<int> &a, const std::vector<int> &b);
+
+std::vector<std::vector<int>> MatMul::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    // torch.matmul shapes, as dl_module_matmul.hpp:48-113
+    const std::vector<int> &a = input_shapes[0], &b = input_shapes[1];
+    std::vector<int> out;
+    if (a.size() == 1 && b.size() == 1) {
+        out = {1};
+    } else if (a.size() == 1) {
+        out.assign(b.begin(), b.end() - 2);
+        out.push_back(b.back());
+    } else if (b.size() == 1) {
+        out.assign(a.begin(), a.end() - 1);
+    } else {
+        const size_t n = std::max(a.size(), b.size());
+        out = broadcast_shape(std::vector<int>(a.begin(), a.end() - 2), std::vector<int>(b.begin(), b.end() - 2));
+        while (out.size() + 2 < n) out.insert(out.begin(), 1);
+        out.push_back(a[a.size() - 2]);
+        out.push_back(b.back());
+    }
+    return {out};
+}
+
+// Leading (batch) dims of both operands, right-aligned to the output's, and the matrix extents.
+bool MatMul::slices(ModelContext *context, std::vector<int> &b0, std::vector<int> &b1, int &M, int &K, int &N)
+{
+    TensorBase *in0 = context->get_tensor(m_inputs_index[0]), *in1 = context->get_tensor(m_inputs_index[1]);
+    if (!in0 || !in1 || in0->shape.empty() || in1->shape.empty() || in0->shape.size() > 4 || in1->shape.size() > 4)
+        return false;
+    const std::vector<int> &a = in0->shape, &b = in1->shape;
+    K = a.back();
+    M = a.size() == 1 ? 1 : a[a.size() - 2];
+    N = b.size() == 1 ? 1 : b.back();
+    if ((b.size() == 1 ? b[0] : b[b.size() - 2]) != K)
+        return false;
+    b0.assign(a.begin(), a.size() >= 2 ? a.end() - 2 : a.begin());
+    b1.assign(b.begin(), b.size() >= 2 ? b.end() - 2 : b.begin());
+    const size_t nb = std::max(b0.size(), b1.size());
+    while (b0.size() < nb) b0.insert(b0.begin(), 1);
+    while (b1.size() < nb) b1.insert(b1.begin(), 1);
+    for (size_t i = 0; i < nb; i++)
+        if (b0[i] != b1[i] && b0[i] != 1 && b1[i] != 1)
+            return false;
+    return true;
+}
+
+size_t MatMul::workspace_bytes(ModelContext *context)
+{
+    std::vector<int> b0, b1;
+    int M, K, N;
+    if (quant_type != QUANT_TYPE_SYMM_16BIT || !slices(context, b0, b1, M, K, N))
+        return 0;
+    espdl_conv_desc d;
+    memset(&d, 0, sizeof(d));
+    d.dtype = ESPDL_DTYPE_INT16, d.n = 1, d.in_h = d.out_h = 1, d.in_w = d.out_w = M, d.in_c = K, d.out_c = N, d.kh = d.kw = 1;
+    d.stride_h = d.stride_w = d.dilation_h = d.dilation_w = 1, d.group = 1;
+    size_t bytes = 0;
+    return espdl_b200_conv2d_workspace_bytes(&d, &bytes) == ESPDL_OK ? bytes : 0;
+}
+
+void MatMul::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in0 = context->get_tensor(m_inputs_index[0]), *in1 = context->get_tensor(m_inputs_index[1]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    std::vector<int> b0, b1;
+    int M = 0, K = 0, N = 0, st = ESPDL_OK;
+    if (!in0 || !in1 || !out || !in0->device || !in1->device || !out->device || !slices(context, b0, b1, M, K, N)) {
+        context->note(ESPDL_ERR_INVALID_ARG);
+        return;
+    }
+    const size_t es = quant_type == QUANT_TYPE_SYMM_16BIT ? 2 : 1;
+    // one Gemm per batch slice, the operand with extent 1 in a batch dim is reused (dl_module_matmul.hpp:191-520)
+    std::vector<int> ob(b0.size());
+    long long count = 1;
+    for (size_t i = 0; i < b0.size(); i++) {
+        ob[i] = std::max(b0[i], b1[i]);
+        count *= ob[i];
+    }
+    for (long long s = 0; s < count && !st; s++) {
+        long long rem = s, i0 = 0, i1 = 0, m0 = 1, m1 = 1;
+        for (int i = (int)ob.size() - 1; i >= 0; i--) {
+            const int idx = (int)(rem % ob[i]);
+            rem /= ob[i];
+            i0 += (b0[i] == 1 ? 0 : idx) * m0;
+            i1 += (b1[i] == 1 ? 0 : idx) * m1;
+            m0 *= b0[i];
+            m1 *= b1[i];
+        }
+        espdl_conv_desc d;
+        memset(&d, 0, sizeof(d));
+        d.input = (const char *)in0->device + (size_t)i0 * M * K * es;
+        d.filter = (const char *)in1->device + (size_t)i1 * K * N * es; // read as [N][K], as the reference's conv kernel does
+        d.output = (char *)out->device + (size_t)s * M * N * es;
+        d.dtype = quant_dtype(quant_type);
+        d.n = 1, d.in_h = d.out_h = 1, d.in_w = d.out_w = M, d.in_c = K, d.out_c = N, d.kh = d.kw = 1;
+        d.stride_h = d.stride_w = d.dilation_h = d.dilation_w = 1, d.group = 1;
+        d.in_exponent = in0->exponent, d.out_exponent = out->exponent, d.filter_exponent = in1->exponent, d.per_channel = 0;
+        d.activation = m_activation == ReLU ? ESPDL_ACT_RELU : ESPDL_ACT_LINEAR;
+        d.round_mode = context->round_mode;
+        st = espdl_b200_conv2d_ws(&d, context->workspace, context->workspace_bytes, context->stream);
+    }
+    if (st)
+        ESP_LOGE("MatMul", "%s failed: %s %s", name ? name : "?", espdl_b200_strerror(st), espdl_b200_last_error());
+    context->note(st);
+}
+
+Module *MatMul::deserialize(fbs::FbsModel *fbs_model, std::string node_name)
+{
+    activation_type_t activation_type = Linear;
+    quant_type_t quant_type = QUANT_TYPE_NONE;
+    fbs_model->get_operation_attribute(node_name, "activation", activation_type);
+    fbs_model->get_operation_attribute(node_name, "quant_type", quant_type);
+    if (quant_type != QUANT_TYPE_SYMM_8BIT && quant_type != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    if (activation_type != Linear && activation_type != ReLU)
+        return nullptr;
+    return new MatMul(activation_type, node_name.c_str(), quant_type);
+}
+
 // --------------------------------------------------------------------------------- elementwise
 static std::vector<int> broadcast_shape(const std::vector<int> &a, const std::vector<int> &b)
 {
@@ -1118,6 +1240,7 @@ void ModuleCreator::register_dl_modules()
     // same op-type strings as the reference registry (esp-dl/dl/module/include/dl_module_creator.hpp:134-204)
     register_module("Conv", Conv::deserialize);
     register_module("Gemm", Gemm::deserialize);
+    register_module("MatMul", MatMul::deserialize);
     register_module("Add", Add::deserialize);
     register_module("Sub", Sub::deserialize);
     register_module("Mul", Mul::deserialize);

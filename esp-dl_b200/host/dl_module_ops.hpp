@@ -50,6 +50,25 @@ public:
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
 };
 
+/// MatMul of two activations, reference: dl_module_matmul.hpp:16-526.  Shapes of one to four dims with the reference's
+/// broadcasting of the leading dims; per-tensor exponents, no bias, optional ReLU.  The reference hands input1 to its
+/// conv kernel as the FILTER, and its generic C kernel reads a filter's memory as [N][K] (dl_base_conv2d.cpp:23-32):
+/// out[m][n] = act(rnd(sum_k in0[m][k] * in1_flat[n*K + k])).  That reading is reproduced here, so results equal the
+/// reference's C path bit for bit (for a mathematically plain product the graph has to store input1 as [N][K]).
+class MatMul : public Module {
+public:
+    MatMul(activation_type_t activation = Linear, const char *name = nullptr, quant_type_t quant_type = QUANT_TYPE_NONE)
+        : Module(name, MODULE_NON_INPLACE, quant_type), m_activation(activation) {}
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    size_t workspace_bytes(ModelContext *context) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    activation_type_t m_activation;
+    bool slices(ModelContext *context, std::vector<int> &b0, std::vector<int> &b1, int &M, int &K, int &N);
+};
+
 /// Add / Sub / Mul with numpy broadcasting, reference: dl_module_add.hpp:14-105, dl_module_mul.hpp, dl_module_sub.hpp.
 class Elementwise : public Module {
 public:

@@ -28,6 +28,7 @@
 #include "dl_module_gemm.hpp"
 #include "dl_module_global_average_pool.hpp"
 #include "dl_module_lut.hpp"
+#include "dl_module_matmul.hpp"
 #include "dl_module_max_pool.hpp"
 #include "dl_module_mul.hpp"
 #include "dl_module_prelu.hpp"
@@ -252,6 +253,20 @@ int ref_concat2(const int8_t *a, const int8_t *b, int8_t *out, const int *shape_
     m.get_output_shape(shapes);
     m.run({ta.get(), tb.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
     return ESPDL_OK;
+}
+
+/* MatMul through the reference's own module (dl_module_matmul.hpp:125-526): shapes of up to four dims with its
+ * broadcasting rules, per-tensor exponents, no bias. */
+int ref_matmul(const void *a, const int *shape_a, int ndim_a, int e_a, const void *b, const int *shape_b, int ndim_b, int e_b, void *out,
+               int e_out, int dtype, int relu)
+{
+    std::vector<int> sa(shape_a, shape_a + ndim_a), sb(shape_b, shape_b + ndim_b);
+    module::MatMul m(relu ? ReLU : Linear, "matmul", to_quant(dtype));
+    std::vector<std::vector<int>> in_shapes = {sa, sb};
+    std::vector<int> so = m.get_output_shape(in_shapes)[0];
+    std::unique_ptr<TensorBase> ta(view(sa, a, e_a, dtype)), tb(view(sb, b, e_b, dtype)), to(view(so, out, e_out, dtype));
+    m.run({ta.get(), tb.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
 }
 
 } /* extern "C" */

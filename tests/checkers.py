@@ -52,6 +52,9 @@ def ref():
         lib.ref_softmax.argtypes = [C.POINTER(abi.SoftmaxDesc), C.c_int]
         lib.ref_concat2.restype = C.c_int
         lib.ref_concat2.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int, C.c_int]
+        lib.ref_matmul.restype = C.c_int
+        lib.ref_matmul.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p,
+                                   C.c_int, C.c_int, C.c_int]
         lib.ref_num_threads.restype = C.c_int
         _ref = lib
     return _ref

@@ -42,6 +42,36 @@ class _RefBackend:
         return self.r.ref_resize(d)
 
 
+def matmul(o, a, b, e_a, e_b, e_out, dtype, act, round_mode):
+    """MatMul as the reference's generic C path computes it (dl_module_matmul.hpp:125-526 over dl_base_conv2d.cpp:23-32):
+    one Gemm per broadcast batch slice with input1's memory read as the filter, i.e. as [N][K]."""
+    K = a.shape[-1]
+    M = 1 if a.ndim == 1 else a.shape[-2]
+    N = 1 if b.ndim == 1 else b.shape[-1]
+    ba, bb = a.shape[:-2] if a.ndim >= 2 else (), b.shape[:-2] if b.ndim >= 2 else ()
+    nb = max(len(ba), len(bb))
+    ba, bb = (1,) * (nb - len(ba)) + tuple(ba), (1,) * (nb - len(bb)) + tuple(bb)
+    ob = tuple(max(x, y) for x, y in zip(ba, bb))
+    a3, b3 = a.reshape(ba + (M, K)), b.reshape(bb + (K * N,))
+    out = np.zeros(ob + (M, N), dtype=a.dtype)
+    for idx in np.ndindex(*ob):
+        ia = tuple(0 if ba[i] == 1 else idx[i] for i in range(nb))
+        ib = tuple(0 if bb[i] == 1 else idx[i] for i in range(nb))
+        case = cases.gemm_case(seed=0, dtype=dtype, m=M, k=K, n_out=N, e_in=e_a, e_w=(e_b, e_b), e_out=e_out, act=act, bias=False,
+                               round_mode=round_mode)
+        case["x"] = np.ascontiguousarray(a3[ia]).reshape(case["x"].shape)
+        case["w"] = np.ascontiguousarray(b3[ib]).reshape(case["w"].shape)
+        assert o.oracle_conv2d(cases.conv_desc(case)) == 0
+        out[idx] = case["out"].reshape(M, N)
+    if a.ndim == 1 and b.ndim == 1:
+        return out.reshape(1)
+    if a.ndim == 1:
+        return out.reshape(ob + (N,))
+    if b.ndim == 1:
+        return out.reshape(ob + (M,))
+    return out
+
+
 def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="port"):
     """m: espdl_file.read() result; inputs: {name: NHWC array with any batch}.  Returns {tensor name: array}.
     backend "port" = the plain-C oracle, "reference" = the reference's compiled operators (per-tensor exponents only)."""
@@ -150,6 +180,9 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             case["x"] = np.ascontiguousarray(x)
             assert o.oracle_resize(cases.resize_desc(case)) == 0
             t[outs[0]] = case["out"]
+        elif op == "MatMul":
+            t[outs[0]] = matmul(o, x, t[ins[1]], exps[ins[0]], exps[ins[1]], exps[outs[0]], QDT[at["quant_type"]],
+                                ACT[at.get("activation", "Linear")], round_mode)
         else:
             raise NotImplementedError(op)
     return t

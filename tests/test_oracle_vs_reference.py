@@ -197,3 +197,24 @@ def test_concat_copy_matches_reference():
     assert o.oracle_copy(cases.copy_desc(a.ctypes.data, out_o.ctypes.data, 1, (24, 8), (8, 1), (32, 1))) == 0
     assert o.oracle_copy(cases.copy_desc(b.ctypes.data, out_o.ctypes.data + 8, 1, (24, 24), (24, 1), (32, 1))) == 0
     np.testing.assert_array_equal(out_o, out_r)
+
+
+@pytest.mark.parametrize("sa,sb", [((3, 16), (16, 5)), ((16,), (16, 7)), ((4, 32), (32,)), ((2, 3, 16), (2, 16, 5)), ((2, 3, 16), (16, 5)),
+                                   ((2, 2, 3, 8), (2, 2, 8, 4)), ((1, 2, 3, 8), (2, 1, 8, 4)), ((5, 24), (24, 9))])
+@pytest.mark.parametrize("relu", [0, 1])
+def test_matmul_matches_reference(sa, sb, relu):
+    """MatMul of two activations: the restatement (input1's memory read as [N][K], one Gemm per broadcast slice) against
+    the reference's own MatMul module compiled for the host."""
+    import ctypes as C
+    import graph_oracle
+    rng = np.random.default_rng(31)
+    a = rng.integers(-128, 128, size=sa, dtype=np.int8)
+    b = rng.integers(-128, 128, size=sb, dtype=np.int8)
+    e_a, e_b, e_out = -5, -6, -3
+    want_shape = np.matmul(np.zeros(sa), np.zeros(sb)).shape or (1,)
+    out_r = np.zeros(want_shape, dtype=np.int8)
+    assert checkers.ref().ref_matmul(a.ctypes.data, (C.c_int * len(sa))(*sa), len(sa), e_a, b.ctypes.data, (C.c_int * len(sb))(*sb), len(sb), e_b,
+                                     out_r.ctypes.data, e_out, abi.DTYPE_INT8, relu) == 0
+    got = graph_oracle.matmul(checkers.oracle(), a, b, e_a, e_b, e_out, abi.DTYPE_INT8, abi.ACT_RELU if relu else abi.ACT_LINEAR, abi.ROUND_HALF_UP)
+    np.testing.assert_array_equal(got.reshape(out_r.shape), out_r)
+    assert out_r.std() > 0
