@@ -353,8 +353,10 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
                     if (rk == r && (int)k != out && infos[k].last > (int)step)
                         root_dies = false;
                 }
+                // equal element sizes only: the kernels run one thread per element, and an output element of another
+                // width would land on input elements that other threads have not read yet (float Softmax -> int8)
                 if (root_dies && !in.is_graph_io && !infos[r].is_graph_io && !has_view[r] && infos[out].last != INT_MAX &&
-                    in.bytes >= infos[out].bytes) {
+                    in.bytes >= infos[out].bytes && in.dtype == infos[out].dtype) {
                     infos[out].alias_of = it->second;
                     break;
                 }

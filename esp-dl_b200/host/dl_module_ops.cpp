@@ -540,6 +540,16 @@ static bool pack_shapes(const std::vector<int> &out, const std::vector<int> &a, 
     return true;
 }
 
+esp_err_t Elementwise::prepare(ModelContext *context)
+{
+    for (int idx : m_inputs_index) {
+        TensorBase *t = context->get_tensor(idx);
+        if (t && t->data && !t->device && t->to_device() != ESP_OK) // host data and no device copy: a parameter
+            return ESP_FAIL;
+    }
+    return espdl_b200_stream_sync(nullptr) == ESPDL_OK ? ESP_OK : ESP_FAIL;
+}
+
 void Elementwise::forward(ModelContext *context, runtime_mode_t mode)
 {
     (void)mode;

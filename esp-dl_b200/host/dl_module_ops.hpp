@@ -73,6 +73,7 @@ protected:
 class Elementwise : public Module {
 public:
     Elementwise(int op, const char *name, module_inplace_t inplace, quant_type_t quant_type) : Module(name, inplace, quant_type), m_op(op) {}
+    esp_err_t prepare(ModelContext *context) override; ///< uploads an operand that is a parameter (e.g. a scalar factor)
     std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
 

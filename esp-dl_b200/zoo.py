@@ -185,3 +185,205 @@ def inverted_residual_block(seed=4, hw=112, cin=32, expand=6, e_act=(-8, -4), e_
     g.outputs.append((out, np.int8, net.shape[out], [e0]))
     g.value_info = [v for v in g.value_info if v[0] != out]
     return g
+
+
+# ------------------------------------------------------------------------------------------ YOLO11n-style detector
+class _DetNet(_Net):
+    """Helpers for the detector graph on top of _Net: 8-bit LUT activations, pools, resize, concat / split, the
+    shape-only nodes and the attention block's MatMul / Mul / Softmax / QuantizeLinear chain."""
+
+    def swish(self, x):
+        """Swish as the exported graphs carry it: a node with a 256-entry int8 table built with the reference's own
+        formula, sat(round(x * sigmoid(x) * 2^-e_out)) over the input codes (dl_module_swish.hpp:62-76); the table is
+        indexed with (uint8)q ^ 0x80, i.e. entry i belongs to code i - 128."""
+        e_in = self.exp[x]
+        e_out = e_in
+        q = np.arange(-128, 128, dtype=np.float32)
+        v = q * np.float32(2.0 ** e_in)
+        y = (v / (np.float32(1.0) + np.exp(-v, dtype=np.float32))) * np.float32(2.0 ** -e_out)
+        table = np.clip(np.floor(y.astype(np.float64) + 0.5), -128, 127).astype(np.int8)
+        node = self.fresh("swish")
+        out = node + "_out"
+        self.g.add_initializer(node + ".lut", table, [e_out])
+        self.g.add_node("Swish", node, [x], [out], quant_type="S8", lut=node + ".lut")
+        self.tensor(out, self.shape[x], e_out, 0.6 * self.rms[x])
+        return out
+
+    def cbs(self, x, cout, k, stride=1, name=None):
+        """Conv (linear) + Swish: the detector's basic unit."""
+        return self.swish(self.conv(x, cout, k, stride=stride, relu=False, name=name))
+
+    def maxpool(self, x, k):
+        node = self.fresh("maxpool")
+        out = node + "_out"
+        p = k // 2
+        self.g.add_node("MaxPool", node, [x], [out], kernel_shape=[k, k], pads=[p, p, p, p], strides=[1, 1], quant_type="S8")
+        self.tensor(out, self.shape[x], self.exp[x], 1.3 * self.rms[x])
+        return out
+
+    def resize2(self, x):
+        node = self.fresh("resize")
+        out = node + "_out"
+        n, h, w, c = self.shape[x]
+        self.g.add_initializer(node + ".roi", np.zeros(0, dtype=np.float32))
+        self.g.add_initializer(node + ".scales", np.array([1.0, 1.0, 2.0, 2.0], dtype=np.float32))  # ONNX order: N, C, H, W
+        self.g.add_node("Resize", node, [x, node + ".roi", node + ".scales"], [out], mode="nearest", coordinate_transformation_mode="asymmetric",
+                        nearest_mode="floor", quant_type="S8")
+        self.tensor(out, (n, 2 * h, 2 * w, c), self.exp[x], self.rms[x])
+        return out
+
+    def concat(self, xs, axis=3):
+        e = max(self.exp[x] for x in xs)  # a pure copy: every input is brought to one exponent first
+        xs = [x if self.exp[x] == e else self.requantize(x, e) for x in xs]
+        node = self.fresh("concat")
+        out = node + "_out"
+        shape = list(self.shape[xs[0]])
+        shape[axis] = sum(self.shape[x][axis] for x in xs)
+        self.g.add_node("Concat", node, xs, [out], axis=axis, quant_type="S8")
+        self.tensor(out, shape, e, float(np.mean([self.rms[x] for x in xs])))
+        return out
+
+    def split(self, x, sizes, axis=3):
+        node = self.fresh("split")
+        outs = [f"{node}_out{i}" for i in range(len(sizes))]
+        self.g.add_initializer(node + ".split", np.array(sizes, dtype=np.int64))
+        self.g.add_node("Split", node, [x, node + ".split"], outs, axis=axis, num_outputs=len(sizes), quant_type="S8")
+        for o, s in zip(outs, sizes):
+            shape = list(self.shape[x])
+            shape[axis] = s
+            self.tensor(o, shape, self.exp[x], self.rms[x])
+        return outs
+
+    def reshape(self, x, shape):
+        """`shape` starts with 0 (keep the batch extent, whatever it is at run time)."""
+        node = self.fresh("reshape")
+        out = node + "_out"
+        self.g.add_initializer(node + ".shape", np.array(shape, dtype=np.int64))
+        self.g.add_node("Reshape", node, [x, node + ".shape"], [out], quant_type="S8")
+        self.tensor(out, [self.shape[x][0]] + list(shape[1:]), self.exp[x], self.rms[x])
+        return out
+
+    def transpose(self, x, perm):
+        node = self.fresh("transpose")
+        out = node + "_out"
+        self.g.add_node("Transpose", node, [x], [out], perm=list(perm), quant_type="S8")
+        self.tensor(out, [self.shape[x][p] for p in perm], self.exp[x], self.rms[x])
+        return out
+
+    def matmul(self, a, b, rms_target=28.0):
+        """MatMul of two activations; b is declared [.., K, N] and holds its values as [N][K] (see MatMul in the host
+        layer: that is how the reference's generic C kernel reads the second operand)."""
+        node = self.fresh("matmul")
+        out = node + "_out"
+        k = self.shape[a][-1]
+        acc = self.rms[a] * self.rms[b] * np.sqrt(k)
+        e_acc = self.exp[a] + self.exp[b]
+        shift = max(1, int(np.round(np.log2(max(acc / rms_target, 1.0)))))
+        e_out = e_acc + shift
+        self.g.add_node("MatMul", node, [a, b], [out], quant_type="S8", activation="Linear")
+        self.tensor(out, list(self.shape[a][:-1]) + [self.shape[b][-1]], e_out, float(min(acc / 2.0 ** shift, 60.0)))
+        return out
+
+    def mul_scalar(self, x, code, e_scalar, e_out):
+        node = self.fresh("mul")
+        out = node + "_out"
+        self.g.add_initializer(node + ".scale", np.array([code], dtype=np.int8), [e_scalar])
+        self.g.add_node("Mul", node, [x, node + ".scale"], [out], quant_type="S8")
+        self.tensor(out, self.shape[x], e_out, self.rms[x] * code * 2.0 ** (self.exp[x] + e_scalar - e_out))
+        return out
+
+    def softmax_q(self, x, e_out=-7):
+        """Softmax (float32 out, as the reference's int8 Softmax produces) followed by QuantizeLinear back to int8."""
+        node = self.fresh("softmax")
+        f = node + "_out"
+        self.g.add_node("Softmax", node, [x], [f], axis=-1, quant_type="S8")
+        self.g.add_value_info(f, np.float32, self.shape[x], None)
+        self.exp[f], self.shape[f], self.rms[f] = 0, list(self.shape[x]), 0.1
+        qn = self.fresh("quantize")
+        out = qn + "_out"
+        self.g.add_node("QuantizeLinear", qn, [f], [out], quant_type="S8")
+        self.tensor(out, self.shape[x], e_out, 12.0)
+        return out
+
+    def c3k2(self, x, cout, hidden):
+        """cv1 (1x1) -> split in two -> a bottleneck of two 3x3 convs with a shortcut on the second half -> concat of
+        the three pieces -> cv2 (1x1)."""
+        y = self.cbs(x, 2 * hidden, 1)
+        a, b = self.split(y, [hidden, hidden])
+        z = self.cbs(self.cbs(b, hidden, 3), hidden, 3)
+        z = self.add(b, z, max(self.exp[b], self.exp[z]))
+        return self.cbs(self.concat([a, b, z]), cout, 1)
+
+    def sppf(self, x, cout):
+        c = self.shape[x][3] // 2
+        y0 = self.cbs(x, c, 1)
+        y1 = self.maxpool(y0, 5)
+        y2 = self.maxpool(y1, 5)
+        y3 = self.maxpool(y2, 5)
+        return self.cbs(self.concat([y0, y1, y2, y3]), cout, 1)
+
+    def c2psa(self, x, heads=2, key_dim=32):
+        """cv1 -> split -> [attention + feed-forward, both with shortcuts] on one half -> concat -> cv2."""
+        n, h, w, c = self.shape[x]
+        half = c // 2
+        head_dim = half // heads
+        y = self.cbs(x, c, 1)
+        a, b = self.split(y, [half, half])
+        per_head = 2 * key_dim + head_dim
+        qkv = self.conv(b, heads * per_head, 1, relu=False)
+        t = self.transpose(self.reshape(qkv, [0, h * w, heads, per_head]), (0, 2, 1, 3))      # [N, heads, HW, per_head]
+        q, k, v = self.split(t, [key_dim, key_dim, head_dim], axis=3)
+        kt = self.reshape(k, [0, heads, key_dim, h * w])          # same bytes: the second operand is read as [N][K]
+        logits = self.matmul(q, kt)
+        # Scale factor of the logits: random weights give nearly flat logits, and a flat softmax over hundreds of tokens
+        # quantises to all zeros.  The scalar (code 91, its exponent chosen here) brings the real-valued spread to
+        # about four units, so that the quantised attention has a few large entries per row, as a trained one has.
+        real = self.rms[logits] * 2.0 ** self.exp[logits]
+        e_s = int(np.round(np.log2(16.0 / max(real * 91.0, 1e-9))))      # the estimate of `real` runs about 4x high
+        e_l = int(np.round(np.log2(16.0 / 28.0)))
+        logits = self.mul_scalar(logits, 91, e_s, e_l)
+        attn = self.softmax_q(logits)
+        vt = self.reshape(self.transpose(v, (0, 1, 3, 2)), [0, heads, h * w, head_dim])   # values stored [head_dim][HW]
+        o = self.matmul(attn, vt)
+        o = self.reshape(self.transpose(o, (0, 2, 1, 3)), [0, h, w, half])
+        o = self.conv(o, half, 1, relu=False)
+        b = self.add(b, o, max(self.exp[b], self.exp[o]))
+        f = self.conv(self.cbs(b, 2 * half, 1), half, 1, relu=False)
+        b = self.add(b, f, max(self.exp[b], self.exp[f]))
+        return self.cbs(self.concat([a, b]), c, 1)
+
+
+def yolo11n_style(seed=6, input_hw=640, num_classes=80, e_act=(-8, -4), e_w=(-9, -5)):
+    """A YOLO11n-shaped detector: Conv + Swish (8-bit LUT) units, C3k2 blocks (Split / Add / Concat), SPPF (three
+    5x5 max-pools), a C2PSA attention block (int8 MatMul for QK^T and for the value product, LUT-exp Softmax followed by
+    QuantizeLinear), a top-down / bottom-up neck (nearest Resize x2 + Concat, stride-2 convs) and three detection heads
+    with a box and a class branch each.  Channel widths are those of the "n" scale (16 ... 256).  Six outputs."""
+    net = _DetNet("yolo11n_style", seed, e_act, e_w)
+    g = net.g
+    e0 = -7
+    g.add_input("input", np.int8, [1, input_hw, input_hw, 3], e0)
+    net.exp["input"], net.shape["input"], net.rms["input"] = e0, [1, input_hw, input_hw, 3], 74.0
+    x = net.cbs("input", 16, 3, stride=2, name="model.0")
+    x = net.cbs(x, 32, 3, stride=2, name="model.1")
+    x = net.c3k2(x, 64, 16)
+    x = net.cbs(x, 64, 3, stride=2, name="model.3")
+    p3 = net.c3k2(x, 128, 32)
+    x = net.cbs(p3, 128, 3, stride=2, name="model.5")
+    p4 = net.c3k2(x, 128, 64)
+    x = net.cbs(p4, 256, 3, stride=2, name="model.7")
+    x = net.c3k2(x, 256, 128)
+    x = net.sppf(x, 256)
+    p5 = net.c2psa(x)
+    # neck
+    n4 = net.c3k2(net.concat([net.resize2(p5), p4]), 128, 64)
+    n3 = net.c3k2(net.concat([net.resize2(n4), p3]), 64, 32)
+    m4 = net.c3k2(net.concat([net.cbs(n3, 64, 3, stride=2), n4]), 128, 64)
+    m5 = net.c3k2(net.concat([net.cbs(m4, 128, 3, stride=2), p5]), 256, 128)
+    # heads
+    for i, f in enumerate((n3, m4, m5)):
+        box = net.conv(net.cbs(net.cbs(f, 64, 3), 64, 3), 64, 1, relu=False, name=f"head{i}.box")
+        cls = net.conv(net.cbs(net.cbs(f, num_classes, 3), num_classes, 3), num_classes, 1, relu=False, name=f"head{i}.cls")
+        for t in (box, cls):
+            g.outputs.append((t, np.int8, net.shape[t], [net.exp[t]]))
+            g.value_info = [v for v in g.value_info if v[0] != t]
+    return g

@@ -180,6 +180,25 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             case["x"] = np.ascontiguousarray(x)
             assert o.oracle_resize(cases.resize_desc(case)) == 0
             t[outs[0]] = case["out"]
+        elif op == "Split":
+            ax = at.get("axis", 0) % x.ndim
+            if len(ins) > 1 and ins[1] in init:
+                sizes = [int(v) for v in init[ins[1]]["data"]]
+            else:
+                sizes = [x.shape[ax] // len(outs)] * len(outs)
+            pos = 0
+            for name, sz in zip(outs, sizes):
+                t[name] = np.ascontiguousarray(np.take(x, range(pos, pos + sz), axis=ax))
+                pos += sz
+        elif op == "Softmax":
+            ax = at.get("axis", -1) % x.ndim
+            assert ax == x.ndim - 1
+            table = np.zeros(256, dtype=np.float32)
+            o.oracle_softmax_table(table.ctypes.data, exps[ins[0]])
+            xs = np.ascontiguousarray(x.reshape(-1, x.shape[-1]))
+            y = np.zeros(xs.shape, dtype=np.float32)
+            assert o.oracle_softmax(cases.softmax_desc(xs.ctypes.data, y.ctypes.data, table.ctypes.data, xs.shape[0], xs.shape[1], abi.DTYPE_FLOAT, 0)) == 0
+            t[outs[0]] = y.reshape(x.shape)
         elif op == "MatMul":
             t[outs[0]] = matmul(o, x, t[ins[1]], exps[ins[0]], exps[ins[1]], exps[outs[0]], QDT[at["quant_type"]],
                                 ACT[at.get("activation", "Linear")], round_mode)

@@ -164,6 +164,27 @@ def test_matmul_module(tmp_path, sa, sb):
     m.close()
 
 
+def test_yolo11n_style_every_tensor_matches_oracle(tmp_path):
+    """The detector-shaped graph (Conv + Swish LUT, C3k2 with Split / Add / Concat, SPPF max-pools, the attention
+    block with two int8 MatMuls, Mul, Softmax and QuantizeLinear, Resize + Concat neck, three heads) at 96x96, two
+    images, no buffer reuse: every one of its node outputs is compared."""
+    m, want = run_and_compare(tmp_path, zoo.yolo11n_style(seed=6, input_hw=96), batch=2, seed=60, check_intermediates=True)
+    assert len(m.outputs) == 6
+    for out in m.outputs:
+        assert want[out.name].std() > 5
+    m.close()
+
+
+def test_yolo11n_style_planned_arena_and_cuda_graph(tmp_path):
+    """Same graph at 160x160 (25 tokens in the attention block), three images, with buffer reuse and CUDA-graph replay."""
+    m, want = run_and_compare(tmp_path, zoo.yolo11n_style(seed=6, input_hw=160), batch=3, seed=61, check_intermediates=False)
+    first = [o.array.copy() for o in m.outputs]
+    m.run()
+    for o, f in zip(m.outputs, first):
+        np.testing.assert_array_equal(o.array, f)
+    m.close()
+
+
 def test_staged_run_equals_single_run(tmp_path):
     """run(stage_num, stage_index) over all stages gives run()'s result (reference: test_dl_api.cpp:70-98)."""
     path = str(tmp_path / "net.espdl")

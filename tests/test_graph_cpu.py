@@ -41,3 +41,24 @@ def test_generated_mobilenet_activations_are_not_degenerate():
             v = t[node["outputs"][0]].astype(np.int32)
             assert (np.abs(v) >= 127).mean() < 0.35, node["name"]
             assert v.std() > 2, node["name"]
+
+
+def test_yolo11n_style_generator_runs_through_the_oracle(tmp_path):
+    """The detector-shaped graph: node mix of the configuration, and a full oracle pass at 64x64 whose attention block
+    and heads produce non-degenerate values."""
+    import collections
+    g = zoo.yolo11n_style(seed=6, input_hw=64)
+    path = str(tmp_path / "det.espdl")
+    g.save(path)
+    m = espdl_file.read(path)
+    ops = collections.Counter(n["op_type"] for n in m["nodes"])
+    assert ops["Conv"] >= 60 and ops["Swish"] >= 50 and ops["MatMul"] == 2 and ops["Softmax"] == 1 and ops["MaxPool"] == 3
+    assert ops["Resize"] == 2 and ops["Concat"] >= 10 and ops["Split"] >= 8 and len(m["outputs"]) == 6
+    x = np.random.default_rng(3).integers(-128, 128, size=(1, 64, 64, 3), dtype=np.int8)
+    t = graph_oracle.run_graph(m, {"input": x})
+    for node in m["nodes"]:
+        if node["op_type"] in ("MatMul", "QuantizeLinear"):
+            assert t[node["outputs"][0]].std() > 0.5, node["name"]
+    for o in m["outputs"]:
+        v = t[o["name"]].astype(int)
+        assert v.std() > 5 and (np.abs(v) >= 127).mean() < 0.3
