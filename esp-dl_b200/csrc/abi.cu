@@ -317,6 +317,8 @@ static int conv_validate(const espdl_conv_desc *d)
         return ESPDL_ERR_UNSUPPORTED;
     if ((d->in_pixel_stride && d->in_pixel_stride < d->in_c) || (d->out_pixel_stride && d->out_pixel_stride < d->out_c))
         return ESPDL_ERR_INVALID_ARG;
+    if (d->filter_image_stride != 0 && d->group != 1)
+        return ESPDL_ERR_INVALID_ARG;
     // output extents must be the ones the reference derives (dl_module_conv.hpp:81-102)
     const int oh = (d->in_h + d->pad_top + d->pad_bottom - d->dilation_h * (d->kh - 1) - 1) / d->stride_h + 1;
     const int ow = (d->in_w + d->pad_left + d->pad_right - d->dilation_w * (d->kw - 1) - 1) / d->stride_w + 1;
@@ -367,6 +369,31 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
     }
     if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_stem_tc_supported(*desc))
         return conv2d_stem_tc(*desc, s); // 3x3 stride-2 RGB first layer: banded-filter tensor-core kernel
+    if (desc->filter_image_stride != 0) {
+        // a batch of matrix products: image i multiplies by the filter at filter + i * filter_image_stride
+        if (desc->kh != 1 || desc->kw != 1 || desc->stride_h != 1 || desc->stride_w != 1 || desc->pad_top || desc->pad_bottom ||
+            desc->pad_left || desc->pad_right || desc->filter_image_stride < 0)
+            return ESPDL_ERR_INVALID_ARG;
+        if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_tc_supported(*desc))
+            return conv2d_tc(*desc, workspace, workspace_bytes, s);
+        if (desc->kernel == ESPDL_KERNEL_TCGEN05)
+            return ESPDL_ERR_UNSUPPORTED;
+        // shapes the tile kernel does not take: one call per image
+        const size_t es = desc->dtype == ESPDL_DTYPE_INT16 ? 2 : 1;
+        const long long ips = desc->in_pixel_stride ? desc->in_pixel_stride : desc->in_c;
+        const long long ops = desc->out_pixel_stride ? desc->out_pixel_stride : desc->out_c;
+        for (int i = 0; i < desc->n; i++) {
+            espdl_conv_desc one = *desc;
+            one.n = 1, one.filter_image_stride = 0;
+            one.input = (const char *)desc->input + (size_t)i * desc->in_h * desc->in_w * ips * es;
+            one.filter = (const char *)desc->filter + (size_t)i * desc->filter_image_stride * es;
+            one.output = (char *)desc->output + (size_t)i * desc->out_h * desc->out_w * ops * es;
+            const int st1 = espdl_b200_conv2d_ws(&one, workspace, workspace_bytes, stream);
+            if (st1)
+                return st1;
+        }
+        return ESPDL_OK;
+    }
     const bool conv_tc_ok = conv2d_conv_tc_supported(*desc);
     if (conv_tc_ok && desc->kernel != ESPDL_KERNEL_SIMT)
         return conv2d_conv_tc(*desc, s); // filters larger than 1x1 (or strided): implicit GEMM over the taps

@@ -60,7 +60,8 @@ constexpr int MAX_STAGES = 12;
 constexpr int MAX_ACC = 4;
 
 struct TcParams {
-    int M, N, K;
+    int M, N, K;    // rows per matrix, output channels, reduction length
+    int batch;      // independent matrices (1 unless every image has its own filter)
     int block_n, n_tiles, m_tiles;
     int swz;        // bytes of K per stage row: 32, 64 or 128
     int k_blocks;   // ceil(K / swz)
@@ -155,7 +156,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int *slow_flag = (int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int tiles_per_matrix = p.m_tiles * p.n_tiles;
+    const int total_tiles = p.batch * tiles_per_matrix;
     const int parts = 4 / p.acc_stages; // epilogue groups that share one tile (they split its columns)
 
     if (threadIdx.x == 0) {
@@ -184,8 +186,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / p.n_tiles) * BLOCK_M;
-                const int n0 = (tile % p.n_tiles) * p.block_n;
+                const int bi = tile / tiles_per_matrix, tm = tile % tiles_per_matrix;
+                const int m0 = (tm / p.n_tiles) * BLOCK_M;
+                const int n0 = (tm % p.n_tiles) * p.block_n;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
                         ok = false;
@@ -194,11 +197,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t bar = smem_u32(&full_bar[stage]);
                     uint8_t *st = smem + (size_t)stage * stage_bytes;
                     mbar_arrive_expect_tx(bar, (uint32_t)stage_bytes);
-                    tma_load_2d(smem_u32(st), &map_a, kb * p.swz, m0, bar);
-                    tma_load_2d(smem_u32(st + NPLANE * a_bytes), &map_b, kb * p.swz, n0, bar);
+                    tma_load_3d(smem_u32(st), &map_a, kb * p.swz, m0, bi, bar);
+                    tma_load_3d(smem_u32(st + NPLANE * a_bytes), &map_b, kb * p.swz, n0, bi, bar);
                     if (I16) {
-                        tma_load_2d(smem_u32(st + a_bytes), &map_a_lo, kb * p.swz, m0, bar);
-                        tma_load_2d(smem_u32(st + 2 * a_bytes + b_bytes), &map_b_lo, kb * p.swz, n0, bar);
+                        tma_load_3d(smem_u32(st + a_bytes), &map_a_lo, kb * p.swz, m0, bi, bar);
+                        tma_load_3d(smem_u32(st + 2 * a_bytes + b_bytes), &map_b_lo, kb * p.swz, n0, bi, bar);
                     }
                     if (++stage == p.stages) {
                         stage = 0;
@@ -295,16 +298,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
             if (local % p.acc_stages != acc)
                 continue;
-            const int m0 = (tile / p.n_tiles) * BLOCK_M;
-            const int n0 = (tile % p.n_tiles) * p.block_n;
+            const int bi = tile / tiles_per_matrix, tm = tile % tiles_per_matrix;
+            const int m0 = (tm / p.n_tiles) * BLOCK_M;
+            const int n0 = (tm % p.n_tiles) * p.block_n;
             if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase)) {
                 ok = false;
                 break;
             }
             acc_phase ^= 1;
             fence_after();
-            const long long m = (long long)m0 + row_in_tile;
-            const bool row_ok = m < p.M;
+            const bool row_ok = m0 + row_in_tile < p.M;
+            const long long m = (long long)bi * p.M + m0 + row_in_tile; // row of the output tensor
             const uint32_t t0 = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * NACC * p.block_n);
             if (!I16) {
                 if (fast && p.out_pw) {
@@ -329,7 +333,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     fence_async_smem();
                     named_bar(2 + group, 128);
                     if (leader) {
-                        tma_store_2d(&map_out, buf, n0 + col0, m0); // rows >= M and columns >= N are clipped
+                        tma_store_3d(&map_out, buf, n0 + col0, m0, bi); // rows >= M and columns >= N are clipped
                         bulk_commit();
                     }
                     if (lane == 0)
@@ -416,20 +420,23 @@ EncodeTiledFn get_encode()
     return fn;
 }
 
-// 2-D uint8 tensor [rows][cols] with `row_stride` bytes between rows; box = box_rows x box_cols.
+// uint8 tensor [mats][rows][cols] with `row_stride` bytes between rows and `mat_stride` bytes between matrices;
+// box = 1 x box_rows x box_cols.
 int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t row_stride, uint32_t box_rows,
-             uint32_t box_cols, int swz)
+             uint32_t box_cols, int swz, uint64_t mats = 1, uint64_t mat_stride = 0)
 {
     EncodeTiledFn enc = get_encode();
     if (!enc)
         return set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");
-    cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {row_stride};
-    cuuint32_t box[2] = {box_cols, box_rows};
-    cuuint32_t estr[2] = {1, 1};
+    if (mats <= 1)
+        mat_stride = (rows * row_stride + 15) / 16 * 16; // unused with a single matrix, but it must be a legal stride
+    cuuint64_t dims[3] = {cols, rows, mats ? mats : 1};
+    cuuint64_t strides[2] = {row_stride, mat_stride};
+    cuuint32_t box[3] = {box_cols, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapSwizzle sw = swz == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
         : (swz == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (swz == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled");
@@ -456,10 +463,15 @@ size_t aux_bytes(const TcParams &p) { return sizeof(FastParam) * (size_t)p.n_til
 bool plan(const espdl_conv_desc &d, TcParams &p)
 {
     const bool i16 = d.dtype == ESPDL_DTYPE_INT16;
-    const long long M = (long long)d.n * d.out_h * d.out_w;
+    // one matrix over all pixels of all images, or - when every image has its own filter - one matrix per image
+    const bool batched = d.filter_image_stride != 0;
+    if (batched && (i16 || d.filter_image_stride % 16 != 0))
+        return false;
+    const long long M = (batched ? 1ll : (long long)d.n) * d.out_h * d.out_w;
     if (M > 0x7fffffffll || d.out_c > 8192)
         return false;
     p.M = (int)M, p.N = d.out_c, p.K = d.in_c;
+    p.batch = batched ? d.n : 1;
     const int max_bn = i16 ? 128 : 256;
     p.n_tiles = (p.N + max_bn - 1) / max_bn;
     p.block_n = (((p.N + p.n_tiles - 1) / p.n_tiles) + 15) / 16 * 16;
@@ -546,9 +558,11 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     CUtensorMap ma, mb, ma_lo, mb_lo;
     int st;
     if (!i16) {
-        if ((st = make_map(&ma, d.input, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)ips, BLOCK_M, (uint32_t)p.swz, p.swz)))
+        if ((st = make_map(&ma, d.input, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)ips, BLOCK_M, (uint32_t)p.swz, p.swz, (uint64_t)p.batch,
+                           (uint64_t)p.M * ips)))
             return st;
-        if ((st = make_map(&mb, d.filter, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, (uint32_t)p.block_n, (uint32_t)p.swz, p.swz)))
+        if ((st = make_map(&mb, d.filter, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, (uint32_t)p.block_n, (uint32_t)p.swz, p.swz, (uint64_t)p.batch,
+                           (uint64_t)d.filter_image_stride)))
             return st;
         ma_lo = ma, mb_lo = mb;
     } else {
@@ -577,12 +591,16 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     CUtensorMap mo = ma;
     if (p.out_pw) {
         const int osw = p.out_pw == 128 ? 128 : (p.out_pw == 64 ? 64 : 0);
-        if ((st = make_map(&mo, d.output, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.ops, BLOCK_M, (uint32_t)p.out_pw, osw)))
+        if ((st = make_map(&mo, d.output, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.ops, BLOCK_M, (uint32_t)p.out_pw, osw, (uint64_t)p.batch,
+                           (uint64_t)p.M * (uint64_t)p.ops)))
             return st;
     }
     if (smem < 120 * 1024) // more than half an SM's shared memory: one CTA per SM, so TMEM allocation never waits on a neighbour
         smem = 120 * 1024;
-    const int grid = min(p.m_tiles * p.n_tiles, num_sms());
+    const long long all_tiles = (long long)p.batch * p.m_tiles * p.n_tiles;
+    if (all_tiles > 0x7fffffffll)
+        return ESPDL_ERR_TOO_LARGE;
+    const int grid = (int)min(all_tiles, (long long)num_sms());
     static std::once_flag attr_once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once, [] {

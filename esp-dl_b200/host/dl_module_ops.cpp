@@ -453,6 +453,28 @@ void MatMul::forward(ModelContext *context, runtime_mode_t mode)
         ob[i] = std::max(b0[i], b1[i]);
         count *= ob[i];
     }
+    // all slices in one launch when the batch dims need no index arithmetic: both operands carry every slice (the
+    // filter then steps K*N per slice), or input1 is one matrix shared by all slices (a plain Gemm over all rows)
+    bool full0 = true, full1 = true, none1 = true;
+    for (size_t i = 0; i < ob.size(); i++) {
+        full0 = full0 && b0[i] == ob[i];
+        full1 = full1 && b1[i] == ob[i];
+        none1 = none1 && b1[i] == 1;
+    }
+    if (count > 1 && full0 && (full1 || none1) && count <= 0x7fffffffll && (long long)K * N <= 0x7fffffffll) {
+        espdl_conv_desc d;
+        memset(&d, 0, sizeof(d));
+        d.input = in0->device, d.filter = in1->device, d.output = out->device;
+        d.dtype = quant_dtype(quant_type);
+        d.n = (int)count, d.in_h = d.out_h = 1, d.in_w = d.out_w = M, d.in_c = K, d.out_c = N, d.kh = d.kw = 1;
+        d.stride_h = d.stride_w = d.dilation_h = d.dilation_w = 1, d.group = 1;
+        d.filter_image_stride = none1 ? 0 : K * N;
+        d.in_exponent = in0->exponent, d.out_exponent = out->exponent, d.filter_exponent = in1->exponent, d.per_channel = 0;
+        d.activation = m_activation == ReLU ? ESPDL_ACT_RELU : ESPDL_ACT_LINEAR;
+        d.round_mode = context->round_mode;
+        st = espdl_b200_conv2d_ws(&d, context->workspace, context->workspace_bytes, context->stream);
+        count = 0; // nothing left for the per-slice loop
+    }
     for (long long s = 0; s < count && !st; s++) {
         long long rem = s, i0 = 0, i1 = 0, m0 = 1, m1 = 1;
         for (int i = (int)ob.size() - 1; i >= 0; i--) {

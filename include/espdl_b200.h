@@ -144,7 +144,10 @@ typedef struct espdl_conv_desc {
     int32_t activation;               /* espdl_act_t: LINEAR or RELU                                   */
     int32_t round_mode;               /* espdl_round_t                                                 */
     int32_t kernel;                   /* espdl_kernel_t                                                */
-    int32_t reserved;
+    int32_t filter_image_stride;      /* 0: one filter for all n images (a convolution).  Non-zero: image i uses the
+                                         filter at filter + i * filter_image_stride elements - a batch of n
+                                         independent matrix products (1x1, group 1 only), which is how MatMul
+                                         runs all its slices in one launch                                */
 } espdl_conv_desc;
 
 int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream);

@@ -160,7 +160,8 @@ int oracle_conv2d(const espdl_conv_desc *d)
                             const int64_t wi = ((int64_t)ky * d->kw + kx) * d->in_c + oc;
                             acc += is16 ? (int64_t)in16[ibase + oc] * w16[wi] : (int64_t)in8[ibase + oc] * w8[wi];
                         } else {
-                            const int64_t wbase = (((int64_t)oc * d->kh + ky) * d->kw + kx) * d->in_c;
+                            /* filter_image_stride != 0: every image has its own filter (a batch of matrix products) */
+                            const int64_t wbase = (int64_t)n * d->filter_image_stride + (((int64_t)oc * d->kh + ky) * d->kw + kx) * d->in_c;
                             if (is16) {
                                 for (int c = 0; c < d->in_c; c++) acc += (int64_t)in16[ibase + c] * w16[wbase + c];
                             } else {

@@ -53,7 +53,8 @@ def conv_case(seed=0, dtype=abi.DTYPE_INT8, n=1, h=8, w=8, cin=16, cout=16, kh=3
                 out_c=cout, kh=kh, kw=kw, stride_h=sh, stride_w=sw, dilation_h=dh, dilation_w=dw, pad_top=pt,
                 pad_bottom=pb, pad_left=pl, pad_right=pr, group=cin if depthwise else 1,
                 in_pixel_stride=in_stride, out_pixel_stride=out_stride, in_exponent=e_in, out_exponent=e_out,
-                filter_exponent=ew_scalar, per_channel=int(per_channel), activation=act, round_mode=round_mode, kernel=0)
+                filter_exponent=ew_scalar, per_channel=int(per_channel), activation=act, round_mode=round_mode, kernel=0,
+                filter_image_stride=0)
 
 
 def gemm_case(seed=0, dtype=abi.DTYPE_INT8, m=64, k=64, n_out=32, **kw):

@@ -181,3 +181,22 @@ def test_conv_implicit_gemm_epilogue_variants(round_mode, act, bias, lut, direct
     case = cases.conv_case(seed=78, n=2, h=18, w=22, cin=32, cout=48, kh=3, kw=3, per_channel=True, round_mode=round_mode, act=act, bias=bias, lut=lut,
                            e_in=-7, e_out=-6, e_w=(-9, -6))
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), gpu_util.run_conv_oracle(case))
+
+
+@pytest.mark.parametrize("n,m,k,nout,kernel", [(6, 100, 32, 100, abi.KERNEL_TCGEN05), (3, 400, 400, 64, abi.KERNEL_TCGEN05), (5, 130, 64, 40, abi.KERNEL_AUTO),
+                                               (4, 9, 24, 7, abi.KERNEL_AUTO)])
+def test_batched_matrix_products(n, m, k, nout, kernel):
+    """filter_image_stride: image i multiplies by its own filter - all slices of a MatMul in one launch of the tile
+    kernel (the last case, K = 24, takes the one-call-per-image fallback)."""
+    rng = np.random.default_rng(5)
+    case = cases.conv_case(seed=21, n=n, h=1, w=m, cin=k, cout=nout, kh=1, kw=1, pad=(0, 0, 0, 0), per_channel=False, bias=False,
+                           act=abi.ACT_LINEAR, e_in=-6, e_w=(-7, -7), e_out=-4)
+    case["w"] = rng.integers(-127, 128, size=(n, nout, 1, 1, k), dtype=np.int8)   # one [N][K] filter per image
+    case["filter_image_stride"] = nout * k
+    want = gpu_util.run_conv_oracle(case)
+    assert want.std() > 5
+    for i in range(n):   # the oracle's batched form equals n separate Gemms
+        one = cases.gemm_case(seed=0, m=m, k=k, n_out=nout, per_channel=False, bias=False, e_in=-6, e_w=(-7, -7), e_out=-4)
+        one["x"], one["w"] = np.ascontiguousarray(case["x"][i:i + 1]), np.ascontiguousarray(case["w"][i])
+        np.testing.assert_array_equal(gpu_util.run_conv_oracle(one)[0], want[i])
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=kernel), want)
