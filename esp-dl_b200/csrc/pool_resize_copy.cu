@@ -55,6 +55,35 @@ __global__ void __launch_bounds__(256) pool_kernel(PoolParams p)
     }
 }
 
+// Max pool, int8, C % 16 == 0: 16 channels per thread, 128-bit loads and stores, per-byte signed maximum over the
+// in-bounds taps (padding is excluded, as in pool_kernel).
+__global__ void __launch_bounds__(256) maxpool_s8_vec16_kernel(PoolParams p)
+{
+    const int chunks = p.c >> 4;
+    const long long total = (long long)p.n * p.oh * p.ow * chunks;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int ch = (int)(i % chunks) * 16;
+        const long long pix = i / chunks;
+        const int ox = (int)(pix % p.ow);
+        const int oy = (int)((pix / p.ow) % p.oh);
+        const int n = (int)(pix / ((long long)p.ow * p.oh));
+        uint4 m = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u); // -128 in every byte
+        for (int ky = 0; ky < p.kh; ky++) {
+            const int iy = oy * p.sh + ky - p.pt;
+            if (iy < 0 || iy >= p.ih)
+                continue;
+            for (int kx = 0; kx < p.kw; kx++) {
+                const int ix = ox * p.sw + kx - p.pl;
+                if (ix < 0 || ix >= p.iw)
+                    continue;
+                const uint4 v = __ldg((const uint4 *)((const int8_t *)p.in + (((long long)n * p.ih + iy) * p.iw + ix) * p.c + ch));
+                m.x = __vmaxs4(m.x, v.x), m.y = __vmaxs4(m.y, v.y), m.z = __vmaxs4(m.z, v.z), m.w = __vmaxs4(m.w, v.w);
+            }
+        }
+        *(uint4 *)((int8_t *)p.out + pix * p.c + ch) = m;
+    }
+}
+
 // Global average pool, int8, C % 4 == 0: a thread owns four channels (one word of each pixel) of one image and sums
 // the whole plane; lanes are consecutive words, so every load of a warp is one contiguous run.  The four byte sums
 // come from dp4a against one-hot byte selectors.  Same arithmetic as pool_kernel (int32 sum, one fp32 multiply).
@@ -195,6 +224,12 @@ extern "C" int espdl_b200_pool(const espdl_pool_desc *d, void *stream)
         gap_s8_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
         count_launch();
         return check_launch("global average pool");
+    }
+    if (d->op == ESPDL_POOL_MAX && !p.is16 && p.c % 16 == 0 && ((uintptr_t)d->input % 16) == 0 && ((uintptr_t)d->output % 16) == 0) {
+        const long long items = p.total / 16;
+        maxpool_s8_vec16_kernel<<<(unsigned)min((items + 255) / 256, (long long)num_sms() * 32), 256, 0, (cudaStream_t)stream>>>(p);
+        count_launch();
+        return check_launch("max pool");
     }
     long long blocks = min((p.total + 255) / 256, (long long)num_sms() * 32);
     pool_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
