@@ -2,11 +2,10 @@
 // Replaces dl::base::depthwise_conv2d<> (esp-dl/dl/base/dl_base_depthwise_conv2d.cpp:47-66,
 // shell esp-dl/dl/base/dl_base.hpp:1209-2107): out[y,x,c] = epilogue(sum_{ky,kx} in[..,c] * w[ky,kx,c] + bias[c]).
 //
-// The op is bandwidth bound (9 MACs per byte read): the int8 kernel moves 16 channels per
-// thread with 128-bit loads and stores; consecutive threads own consecutive 16-channel
-// chunks of one pixel, so a warp reads and writes contiguous 512-byte runs of the NHWC tensor.
-// The filter taps, bias and per-channel shifts of a chunk are the same for every pixel and
-// stay resident in L1.
+// The op is bandwidth bound by design (9 MACs per byte read).  3x3 filters with stride 1 or 2 - the shapes of
+// MobileNet-style networks - run on dw3x3_dp4a_kernel (a thread walks along a band of rows, dp4a over byte-transposed
+// columns); other int8 shapes with C % 16 == 0 on dw_s8_vec16_kernel (16 channels per thread, 128-bit loads and
+// stores, a warp reads and writes contiguous runs of the NHWC tensor); everything else on dw_generic_kernel.
 #include "common.cuh"
 
 namespace espdl {
@@ -75,128 +74,6 @@ __global__ void __launch_bounds__(256) dw_s8_vec16_kernel(DwParams p)
             packed[q] = wd;
         }
         *(uint4 *)(out + pix * p.ops + ch) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-    }
-}
-
-// 3x3 depthwise, stride S (1 or 2), dilation 1, int8: the workhorse of MobileNet-style networks.
-// A thread owns four consecutive channels (one 32-bit word of the NHWC pixel) and a patch of TW x TH output
-// pixels.  Its nine filter words, bias and shift stay in registers for the whole patch; input rows slide
-// through a three-row register window, so every input word is loaded and unpacked once per patch row; lanes of
-// a warp are consecutive channel words of the same pixels, so loads and stores are contiguous runs.
-template <int S, int TW, int TH>
-__global__ void __launch_bounds__(128) dw3x3_s8_kernel(DwParams p, int xtiles, int ytiles)
-{
-    constexpr int TWIN = (TW - 1) * S + 3; // input columns feeding TW outputs
-    const int quads = p.c >> 2;
-    const long long items = (long long)p.n * ytiles * xtiles * quads;
-    const long long item = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-    if (item >= items)
-        return;
-    const int cq = (int)(item % quads);
-    long long r = item / quads;
-    const int xt = (int)(r % xtiles);
-    r /= xtiles;
-    const int yt = (int)(r % ytiles);
-    const int n = (int)(r / ytiles);
-    const int c0 = cq * 4;
-    const int8_t *__restrict__ in = (const int8_t *)p.in + (long long)n * p.ih * p.iw * p.ips + c0;
-    int8_t *__restrict__ out = (int8_t *)p.out + (long long)n * p.oh * p.ow * p.ops + c0;
-
-    int wt[9][4];
-#pragma unroll
-    for (int t = 0; t < 9; t++) {
-        const uint32_t w = __ldg((const uint32_t *)((const int8_t *)p.w + (long long)t * p.c + c0));
-#pragma unroll
-        for (int i = 0; i < 4; i++) wt[t][i] = sbyte(w, i);
-    }
-    int bias[4], shift[4];
-    bool fast = !p.half_even && !p.lut;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        bias[i] = p.bias ? __ldg((const int32_t *)p.bias + c0 + i) : 0;
-        const int e = p.per_channel ? __ldg(p.ew + c0 + i) : p.ew_scalar;
-        shift[i] = max(-31, min(31, p.e_shift_base - e));
-        // (acc + bias + 2^(s-1)) >> s is exact while nothing can overflow: |acc| <= 9 * 2^14, |bias| < 2^30, 1 <= s <= 24
-        fast = fast && shift[i] >= 1 && shift[i] <= 24 && bias[i] < (1 << 30) && bias[i] > -(1 << 30);
-    }
-    int bias_half[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) bias_half[i] = bias[i] + (1 << (max(1, min(24, shift[i])) - 1));
-
-    const int ox0 = xt * TW, oy0 = yt * TH;
-    const int ix0 = ox0 * S - p.pl;
-    int win[3][TWIN][4];
-
-    auto load_row = [&](int slot, int iy) {
-        const bool row_in = iy >= 0 && iy < p.ih;
-        const int8_t *rp = in + ((long long)iy * p.iw + ix0) * p.ips;
-#pragma unroll
-        for (int x = 0; x < TWIN; x++) {
-            const int ix = ix0 + x;
-            uint32_t w = 0;
-            if (row_in && ix >= 0 && ix < p.iw)
-                w = __ldg((const uint32_t *)(rp + (long long)x * p.ips));
-#pragma unroll
-            for (int i = 0; i < 4; i++) win[slot][x][i] = sbyte(w, i);
-        }
-    };
-
-    // rows oy0*S - pt + {0, 1} fill the window before the first output row
-    load_row(0, oy0 * S - p.pt);
-    load_row(1, oy0 * S - p.pt + 1);
-#pragma unroll
-    for (int ry = 0; ry < TH; ry++) {
-        const int oy = oy0 + ry;
-        if (oy >= p.oh)
-            break;
-        // window slots rotate: output row ry reads input rows ry*S + {0,1,2}, held in slots (ry*S + k) % 3
-        load_row((ry * S + 2) % 3, oy * S - p.pt + 2);
-        if (S == 2 && ry > 0) {
-            // stride 2 advanced by two rows: the middle row of this window was not loaded by the previous step
-            load_row((ry * S + 1) % 3, oy * S - p.pt + 1);
-        }
-        int acc[TW][4];
-#pragma unroll
-        for (int x = 0; x < TW; x++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[x][i] = 0;
-#pragma unroll
-        for (int ky = 0; ky < 3; ky++)
-#pragma unroll
-            for (int kx = 0; kx < 3; kx++)
-#pragma unroll
-                for (int x = 0; x < TW; x++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) acc[x][i] += win[(ry * S + ky) % 3][x * S + kx][i] * wt[ky * 3 + kx][i];
-#pragma unroll
-        for (int x = 0; x < TW; x++) {
-            const int ox = ox0 + x;
-            if (ox < p.ow) {
-                uint32_t wd;
-                if (fast) {
-                    int q[4];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        q[i] = (acc[x][i] + bias_half[i]) >> shift[i];
-                        if (p.relu)
-                            q[i] = max(q[i], 0);
-                    }
-                    uint32_t hi;
-                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q[3]), "r"(q[2]));
-                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q[1]), "r"(q[0]), "r"(hi));
-                } else {
-                    wd = 0;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        int32_t v = requant8(acc[x][i], bias[i], shift[i], p.relu, p.half_even);
-                        if (p.lut)
-                            v = p.lut[(uint8_t)v ^ 0x80u];
-                        wd |= ((uint32_t)v & 0xffu) << (8 * i);
-                    }
-                }
-                *(uint32_t *)(out + ((long long)oy * p.ow + ox) * p.ops) = wd;
-            }
-        }
     }
 }
 

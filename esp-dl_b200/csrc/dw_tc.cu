@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(DW_THREADS, 1) dw_tc_kernel(const __grid_const
         if (c < p.c)
             b_smem[(cb * 9 + tap) * 1024 + (n / 16) * 512 + n * 16 + (n % 16)] = (uint8_t)p.w[(long long)tap * p.c + c];
     }
-    // the unused tail of every stage is read by overhang rows only, but must not hold stale NaN-free garbage: ints are fine
+    // the unused tail of every stage is read by overhang rows only; whatever integers it holds end up in rows that are not stored
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 1)
         tmem_alloc(smem_u32(tmem_slot), 512);

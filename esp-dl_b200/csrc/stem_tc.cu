@@ -64,7 +64,7 @@ struct StemParams {
 
 __global__ void __launch_bounds__(ST_THREADS, 1)
 stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1, const __grid_constant__ CUtensorMap map2,
-               const StemParams p)
+               const __grid_constant__ CUtensorMap map_out, const StemParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -72,7 +72,10 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
     const int b_bytes = ncol * ST_K;           // one ky plane of B
     uint8_t *b_s = smem;                                        // 3 planes
     uint8_t *a_s = smem + 3 * 256 * ST_K;                       // stages x 3 planes
-    uint8_t *aux = a_s + ST_STAGES * 3 * ST_A_BYTES;
+    uint8_t *out_stage = a_s + ST_STAGES * 3 * ST_A_BYTES;      // four [128][ncol/2] byte tiles, one per epilogue group
+    const int out_pw = ncol / 2;
+    const int out_tile_bytes = 128 * out_pw;
+    uint8_t *aux = out_stage + 4 * 128 * 128;
     FastParam *fast_s = (FastParam *)aux;                       // one entry per accumulator column
     uint64_t *bars = (uint64_t *)(aux + sizeof(FastParam) * 256);
     uint64_t *full_bar = bars, *empty_bar = bars + ST_STAGES, *tfull_bar = bars + 2 * ST_STAGES, *tempty_bar = tfull_bar + ST_ACC;
@@ -221,7 +224,6 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
         }
         asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
         const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut;
-        const bool wide = ((uintptr_t)p.out % 32 == 0) && ((p.ow * p.cout) % 32 == 0);
         const uint32_t fp = epi_param_base(fast_s);
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -245,10 +247,26 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
             int8_t *orow = (int8_t *)p.out + (((long long)n * p.oh + y) * p.ow + ST_J * s) * p.cout;
             const uint32_t t0 = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * 256);
             if (fast) {
-                if (p.epi.relu)
-                    epilogue_lean<true>(t0, fp, orow, ncols, 2, part, row_ok, wide);
+                // rows are requantised into this group's shared-memory tile and leave through one 3-D TMA store,
+                // which also clips the ragged last group of eight outputs and rows outside the image
+                const bool leader = (ew & 3) == 0 && lane == 0;
+                const uint32_t buf = smem_u32(out_stage + (size_t)group * out_tile_bytes);
+                if (leader)
+                    bulk_wait_read_all();
+                named_bar(2 + group, 128);
+                const int col0 = part * out_pw;
+                const int floor_q = p.epi.relu ? 0 : INT_MIN;
+                if (out_pw == 128)
+                    epilogue_stage<128>(t0 + col0, fp + (uint32_t)col0 * 8u, buf, row_in_tile, 128, floor_q);
                 else
-                    epilogue_lean<false>(t0, fp, orow, ncols, 2, part, row_ok, wide);
+                    epilogue_stage<64>(t0 + col0, fp + (uint32_t)col0 * 8u, buf, row_in_tile, 64, floor_q);
+                fence_before();
+                fence_async_smem();
+                named_bar(2 + group, 128);
+                if (leader) {
+                    tma_store_3d(&map_out, buf, ST_J * s * p.cout + col0, yb * p.rows_y, ng * p.rows_n);
+                    bulk_commit();
+                }
             } else {
                 int chunk = 0;
                 for (int c0 = 0; c0 < ncols; c0 += 16, chunk++) {
@@ -279,6 +297,8 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
         }
         if (!ok && lane == 0)
             atomicExch(&g_stem_tc_error, ESPDL_ERR_TIMEOUT);
+        if ((ew & 3) == 0 && lane == 0)
+            bulk_wait_all(); // shared memory stays allocated until the last store has left it
     }
 
     fence_before();
@@ -367,15 +387,29 @@ int conv2d_stem_tc(const espdl_conv_desc &d, cudaStream_t s)
         if (res != CUDA_SUCCESS)
             return set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(stem)");
     }
-    const size_t smem = 1024 + 3 * 256 * ST_K + (size_t)ST_STAGES * 3 * ST_A_BYTES + sizeof(FastParam) * 256 + (2 * ST_STAGES + 2 * ST_ACC) * 8 + 32;
+    // output as a 3-D tensor {OW*Cout bytes, OH, N}; a group's piece is half of a tile row
+    CUtensorMap mo;
+    {
+        const int pw = ST_J * d.out_c / 2;
+        cuuint64_t dims[3] = {(cuuint64_t)d.out_w * d.out_c, (cuuint64_t)d.out_h, (cuuint64_t)d.n};
+        cuuint64_t strides[2] = {(cuuint64_t)d.out_w * d.out_c, (cuuint64_t)d.out_h * d.out_w * d.out_c};
+        cuuint32_t box[3] = {(cuuint32_t)pw, (cuuint32_t)p.rows_y, (cuuint32_t)p.rows_n};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (enc(&mo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.output, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                pw == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(stem output)");
+    }
+    const size_t smem = 1024 + 3 * 256 * ST_K + (size_t)ST_STAGES * 3 * ST_A_BYTES + 4 * 128 * 128 + sizeof(FastParam) * 256 +
+        (2 * ST_STAGES + 2 * ST_ACC) * 8 + 32;
     static std::once_flag attr_once;
     static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute(stem_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); });
+    std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute(stem_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); });
     if (attr_err != cudaSuccess)
         return set_cuda_error(attr_err, "cudaFuncSetAttribute(stem_tc_kernel)");
     const int total = p.ngroups * p.yblocks * p.segs;
     const int grid = min(total, num_sms());
-    stem_tc_kernel<<<grid, ST_THREADS, max(smem, (size_t)120 * 1024), s>>>(maps[0], maps[1], maps[2], p);
+    stem_tc_kernel<<<grid, ST_THREADS, max(smem, (size_t)120 * 1024), s>>>(maps[0], maps[1], maps[2], mo, p);
     count_launch();
     return check_launch("stem_tc");
 }
