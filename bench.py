@@ -330,9 +330,19 @@ def main():
     if rank == 0:
         # roofline of the dominant kernel, from per-module CUDA-event times measured now (eager launches on the model's stream)
         prof = m.profile()
-        traffic = module_traffic(parsed, args.batch)
+        traffic = {tr["name"]: tr for tr in module_traffic(parsed, args.batch)}
+        executed = {name for (_, _, _, name) in prof}
+        # an Add that the model folded into the conv before it (espdl_conv_desc::residual) has no launch of its own:
+        # the conv then also reads the Add's other input and writes the Add's output instead of its own
+        shapes = {v["name"]: v["shape"] for v in list(parsed["value_info"].values()) + parsed["inputs"] + parsed["outputs"]}
+        for node in parsed["nodes"]:
+            if node["op_type"] == "Add" and node["name"] not in executed:
+                for prod in parsed["nodes"]:
+                    if prod["name"] in executed and prod["op_type"] == "Conv" and prod["outputs"][0] in node["inputs"]:
+                        traffic[prod["name"]]["bytes"] += int(np.prod(shapes[node["outputs"][0]])) * args.batch
         by_kind = {}
-        for (idx, typ, us, name), tr in zip(prof, traffic):
+        for (idx, typ, us, name) in prof:
+            tr = traffic[name]
             k = by_kind.setdefault(tr["kind"], dict(us=0.0, bytes=0, macs=0, launches=0))
             k["us"] += us
             k["bytes"] += tr["bytes"]

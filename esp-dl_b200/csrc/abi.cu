@@ -319,6 +319,9 @@ static int conv_validate(const espdl_conv_desc *d)
         return ESPDL_ERR_INVALID_ARG;
     if (d->filter_image_stride != 0 && d->group != 1)
         return ESPDL_ERR_INVALID_ARG;
+    if (d->residual && (d->dtype != ESPDL_DTYPE_INT8 || d->group != 1 || d->kh != 1 || d->kw != 1 || d->stride_h != 1 || d->stride_w != 1 ||
+                        (d->residual_pixel_stride && d->residual_pixel_stride < d->out_c)))
+        return ESPDL_ERR_UNSUPPORTED; // the folded Add is implemented for pointwise int8 convs / Gemm
     // output extents must be the ones the reference derives (dl_module_conv.hpp:81-102)
     const int oh = (d->in_h + d->pad_top + d->pad_bottom - d->dilation_h * (d->kh - 1) - 1) / d->stride_h + 1;
     const int ow = (d->in_w + d->pad_left + d->pad_right - d->dilation_w * (d->kw - 1) - 1) / d->stride_w + 1;

@@ -16,6 +16,8 @@ struct ConvParams {
     void *out;
     const int32_t *ew;
     const int8_t *lut;
+    const int8_t *res; // optional residual added to the result (a folded Add), or null
+    int rps;           // residual pixel stride
     int n, ih, iw, ic, oh, ow, oc, kh, kw, sh, sw, dh, dw, pt, pl, ips, ops;
     int e_shift_base; // out_exponent - in_exponent; shift = base - e_w
     int ew_scalar, per_channel, relu, half_even;
@@ -84,6 +86,8 @@ __global__ void __launch_bounds__(256) conv_s8_kernel(ConvParams p)
                 int32_t q = requant8(acc[j], bias ? bias[oc] : 0, shift, p.relu, p.half_even);
                 if (p.lut)
                     q = p.lut[(uint8_t)q ^ 0x80u];
+                if (p.res)
+                    q = sat8(q + (int)p.res[pix * p.rps + oc]);
                 op[j] = (int8_t)q;
             }
         }
@@ -233,6 +237,7 @@ __global__ void __launch_bounds__(256) conv_s8_small_k_kernel(ConvParams p)
 int conv2d_simt(const espdl_conv_desc &d, cudaStream_t s)
 {
     ConvParams p;
+    p.res = (const int8_t *)d.residual, p.rps = d.residual_pixel_stride ? d.residual_pixel_stride : d.out_c;
     p.in = d.input, p.w = d.filter, p.bias = d.bias, p.out = d.output, p.ew = d.filter_exponents, p.lut = d.lut;
     p.n = d.n, p.ih = d.in_h, p.iw = d.in_w, p.ic = d.in_c, p.oh = d.out_h, p.ow = d.out_w, p.oc = d.out_c;
     p.kh = d.kh, p.kw = d.kw, p.sh = d.stride_h, p.sw = d.stride_w, p.dh = d.dilation_h, p.dw = d.dilation_w;

@@ -72,6 +72,8 @@ struct TcParams {
     int out_mask;   // swizzle mask of the staging tiles (7, 3, 1, 0)
     void *out;
     long long ops;  // output row stride in elements
+    const int8_t *res; // optional residual added to the result (same rows as the output), or null
+    long long rps;     // residual row stride in elements
     EpiConfig epi;
 };
 
@@ -86,7 +88,7 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
     // what every row start (and every 16-column step from it) is aligned to
     const uintptr_t amix = (uintptr_t)p.ops | (((uintptr_t)p.out) + (uintptr_t)n0) | 16u;
     const int out_align = (int)(amix & (~amix + 1));
-    if (fast && vec_ok && p.N % 16 == 0) {
+    if (fast && vec_ok && p.N % 16 == 0 && !p.res) {
         // whole 16-column groups, aligned rows, one-add-one-shift constants
         const bool wide = (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
         const uint32_t fp = fp_base + (uint32_t)n0 * 8u;
@@ -126,6 +128,15 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
         }
         if (row_ok) {
             const int count = min(two ? 32 : 16, p.N - (n0 + c0));
+            if (count > 0 && p.res) { // folded Add: saturating byte sums with the residual's row
+                const int8_t *rrow = p.res + m * p.rps + n0 + c0;
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    if (j < count) {
+                        const int sum = (int)(int8_t)(pk[j >> 2] >> (8 * (j & 3))) + (int)rrow[j];
+                        pk[j >> 2] = (pk[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (((uint32_t)max(-128, min(127, sum)) & 0xffu) << (8 * (j & 3)));
+                    }
+            }
             if (count > 0)
                 store_bytes(orow + c0, pk, count, out_align);
         }
@@ -321,7 +332,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int col0 = part * p.out_pw;
                     const uint32_t fpp = fp_base + (uint32_t)(n0 + col0) * 8u;
                     const int floor_q = p.epi.relu ? 0 : INT_MIN;
-                    if (p.out_pw == 128)
+                    if (p.res)
+                        epilogue_stage_residual(t0 + col0, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q,
+                                                p.res + m * p.rps + n0 + col0, row_ok, p.N - (n0 + col0));
+                    else if (p.out_pw == 128)
                         epilogue_stage<128>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q);
                     else if (p.out_pw == 96)
                         epilogue_stage<96>(t0 + col0, fpp, buf, row_in_tile, 96, floor_q);
@@ -491,7 +505,9 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
     // staged epilogue (int8): each group of four epilogue warps owns a piece of block_n / parts columns
     const long long ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
     p.out_pw = 0, p.out_mask = 0;
-    if (!i16 && ops % 16 == 0 && ((uintptr_t)d.output % 16) == 0 && !getenv("ESPDL_B200_DIRECT_STORES")) {
+    const long long rps = d.residual_pixel_stride ? d.residual_pixel_stride : d.out_c;
+    const bool res_ok = !d.residual || (rps % 16 == 0 && ((uintptr_t)d.residual % 16) == 0);
+    if (!i16 && ops % 16 == 0 && ((uintptr_t)d.output % 16) == 0 && res_ok && !getenv("ESPDL_B200_DIRECT_STORES")) {
         const int parts = 4 / p.acc_stages;
         if (p.block_n % (16 * parts) == 0 && p.block_n / parts <= 128) {
             p.out_pw = p.block_n / parts;
@@ -550,6 +566,8 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
     p.out = d.output;
     p.ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
+    p.res = (const int8_t *)d.residual;
+    p.rps = d.residual_pixel_stride ? d.residual_pixel_stride : d.out_c;
     p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut;
     p.epi.e_shift_base = d.out_exponent - d.in_exponent;
     p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;

@@ -438,6 +438,47 @@ __device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_
     }
 }
 
+// Staged epilogue with a folded Add: as epilogue_stage<0>, and every requantised value is first clamped to int8, then
+// summed with the residual byte of the same row and column and saturated again (out = sat(sat(q) + r)).  `res` is
+// this thread's residual row at the piece's first column (16-byte aligned); `valid` = columns of the piece inside N.
+__device__ __forceinline__ void epilogue_stage_residual(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, uint32_t mask, int floor_q,
+                                                        const int8_t *res, bool row_ok, int valid)
+{
+    const uint32_t rbase = (uint32_t)(row * pw);
+    for (int c = 0; c < pw; c += 16) {
+        int32_t v[16];
+        ld16(t0 + c, v);
+        ld_wait16(v);
+        uint4 rr = make_uint4(0u, 0u, 0u, 0u);
+        if (row_ok && c + 16 <= valid)
+            rr = __ldg((const uint4 *)(res + c));
+        else if (row_ok)
+            for (int j = 0; j < 16; j++)
+                if (c + j < valid)
+                    ((uint8_t *)&rr)[j] = (uint8_t)res[c + j];
+        const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+        uint32_t pk[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            int b[4], s[4];
+            asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(b[0]), "=r"(s[0]), "=r"(b[1]), "=r"(s[1]) : "r"(fp + (uint32_t)(c + 4 * q) * 8u));
+            asm volatile("ld.shared.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(b[2]), "=r"(s[2]), "=r"(b[3]), "=r"(s[3]) : "r"(fp + (uint32_t)(c + 4 * q) * 8u + 16u));
+            int t[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int qv = min(max(__viaddmax_s32(v[4 * q + i], b[i], floor_q) >> s[i], -128), 127);
+                t[i] = qv + (int)(int8_t)(rw[q] >> (8 * i));
+            }
+            uint32_t hi;
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(t[3]), "r"(t[2]));
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(pk[q]) : "r"(t[1]), "r"(t[0]), "r"(hi));
+        }
+        uint32_t off = rbase + (uint32_t)c;
+        off ^= ((off >> 7) & mask) << 4;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + off), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+    }
+}
+
 // General form (any rounding mode, any shift, optional LUT), constants read from global memory.
 __device__ __forceinline__ void requant16_general(const int32_t *v, const EpiConfig &c, int n_first, int N, uint32_t *pk)
 {

@@ -1,4 +1,5 @@
 #include "dl_model_base.hpp"
+#include "dl_module_ops.hpp"
 #include "espdl_b200.h"
 
 #include <algorithm>
@@ -258,6 +259,60 @@ esp_err_t Model::load(fbs::FbsModel *fbs_model)
     return ESP_OK;
 }
 
+// Add(x, y) where y is produced by a pointwise int8 Conv, is read by nothing else and has the exponent of x and of the
+// sum: the conv adds x to its own result (espdl_conv_desc::residual) and writes the Add's output; the Add leaves the
+// plan.  ESP-DL's Add of equal exponents is a saturating sum (esp-dl/dl/base/dl_base_add.cpp:8-44), which is what the
+// conv epilogue computes.  ESPDL_B200_FOLD_ADD=0 keeps the Add nodes.
+void Model::fold_residual_adds()
+{
+    if (!env_flag("ESPDL_B200_FOLD_ADD", true) || !m_reuse_memory)
+        return; // with every tensor kept (tests that read intermediates) the graph stays as exported
+    std::vector<std::string> graph_outputs = m_fbs_model->get_graph_outputs();
+    auto is_graph_output = [&](const std::string &n) { return std::find(graph_outputs.begin(), graph_outputs.end(), n) != graph_outputs.end(); };
+    for (size_t s = 0; s < m_execution_plan.size(); s++) {
+        if (m_module_types[s] != "Add" || m_module_inputs[s].size() != 2 || m_module_outputs[s].size() != 1)
+            continue;
+        const std::string out = m_module_outputs[s][0];
+        for (int which = 0; which < 2; which++) {
+            const std::string y = m_module_inputs[s][which], x = m_module_inputs[s][1 - which];
+            if (x == y || m_fbs_model->is_parameter(x) || m_fbs_model->is_parameter(y) || is_graph_output(y))
+                continue;
+            int producer = -1, x_producer = -1, readers = 0;
+            for (size_t k = 0; k < m_execution_plan.size(); k++) {
+                for (const std::string &o : m_module_outputs[k]) {
+                    if (o == y) producer = (int)k;
+                    if (o == x) x_producer = (int)k;
+                }
+                for (const std::string &i : m_module_inputs[k])
+                    if (i == y) readers++;
+            }
+            if (producer < 0 || producer >= (int)s || readers != 1 || m_module_types[producer] != "Conv" || x_producer >= producer)
+                continue;
+            module::Conv *conv = dynamic_cast<module::Conv *>(m_execution_plan[producer]);
+            if (!conv || !conv->can_fold_add() || m_module_outputs[producer].size() != 1)
+                continue;
+            if (m_fbs_model->get_value_info_dtype(x) != DATA_TYPE_INT8 || m_fbs_model->get_value_info_dtype(y) != DATA_TYPE_INT8 ||
+                m_fbs_model->get_value_info_dtype(out) != DATA_TYPE_INT8)
+                continue;
+            const int ex = m_fbs_model->get_value_info_exponent(x), ey = m_fbs_model->get_value_info_exponent(y);
+            if (ex != ey || ex != m_fbs_model->get_value_info_exponent(out))
+                continue;
+            if (m_fbs_model->get_value_info_shape(x) != m_fbs_model->get_value_info_shape(y))
+                continue;
+            conv->set_residual();
+            m_module_inputs[producer].push_back(x);
+            m_module_outputs[producer][0] = out;
+            delete m_execution_plan[s];
+            m_execution_plan.erase(m_execution_plan.begin() + s);
+            m_module_types.erase(m_module_types.begin() + s);
+            m_module_inputs.erase(m_module_inputs.begin() + s);
+            m_module_outputs.erase(m_module_outputs.begin() + s);
+            s--;
+            break;
+        }
+    }
+}
+
 void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool preload, const std::map<std::string, std::vector<int>> &input_shapes)
 {
     (void)max_internal_size;
@@ -265,6 +320,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
     (void)preload;
     if (!m_fbs_model || !m_model_context || m_built)
         return;
+    fold_residual_adds();
     ModelContext *ctx = m_model_context;
     std::vector<TensorInfo> &infos = m_tensor_infos;
     std::map<std::string, int> info_index;

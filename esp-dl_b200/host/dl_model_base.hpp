@@ -133,6 +133,7 @@ protected:
     std::map<std::string, void *> m_out_stage[2];             ///< pinned host staging per graph output, two slots
     long long m_submitted = 0, m_collected = 0;
     void release_pipeline();
+    void fold_residual_adds();
     bool m_built = false;
     std::vector<TensorInfo> m_tensor_infos;
 };

@@ -273,12 +273,31 @@ int Conv::fill_desc(ModelContext *context, void *desc)
         d.filter = m_grp_filter, d.bias = m_grp_bias, d.filter_exponents = (const int32_t *)m_grp_exponents;
         d.per_channel = 1;
     }
+    if (m_residual) {
+        TensorBase *r = context->get_tensor(m_inputs_index.back());
+        if (!r || !r->device)
+            return ESPDL_ERR_INVALID_ARG;
+        d.residual = r->device; // same NHWC memory as the output, also under pixel grouping
+    }
     d.activation = activation == ReLU ? ESPDL_ACT_RELU : ESPDL_ACT_LINEAR;
     d.round_mode = context->round_mode;
     d.kernel = ESPDL_KERNEL_AUTO;
     if (activation != Linear && activation != ReLU)
         return ESPDL_ERR_UNSUPPORTED;
     return ESPDL_OK;
+}
+
+bool Conv::can_fold_add() const
+{
+    if (m_gemm || m_group != 1 || quant_type != QUANT_TYPE_SYMM_8BIT || m_lut)
+        return false;
+    for (int v : m_strides)
+        if (v != 1)
+            return false;
+    for (int v : m_pads)
+        if (v != 0)
+            return false;
+    return activation == Linear || activation == ReLU;
 }
 
 size_t Conv::workspace_bytes(ModelContext *context)

@@ -22,6 +22,11 @@ public:
     void print() override;
     /// Fuse a following 8-bit LUT node into the epilogue (the table must already be on the device).
     void set_fused_lut(TensorBase *table) { m_lut = table; }
+    /// True for a pointwise int8 conv (1x1, stride 1, no padding, group 1) without a fused table: the shapes whose
+    /// kernels can add a residual to their result.
+    bool can_fold_add() const;
+    /// Fold a following Add into the epilogue: the module's LAST input is then the residual tensor.
+    void set_residual() { m_residual = true; }
 
 protected:
     int fill_desc(ModelContext *context, void *desc);
@@ -31,6 +36,7 @@ protected:
     std::vector<int> m_pads;
     std::string m_target;
     bool m_gemm = false;             ///< Gemm / MatMul view: rows = all leading dims
+    bool m_residual = false;         ///< the last input is a residual added to the result (a folded Add)
     void *m_dev_exponents = nullptr; ///< int32[out_c] on the device when the filter is per-channel
     // Pixel grouping for pointwise convs whose channel count is not a multiple of 16 (the tensor-core tile kernel
     // needs 16-byte rows): m_group_px consecutive pixels are treated as one pixel with m_group_px * Cin channels,

@@ -148,6 +148,13 @@ typedef struct espdl_conv_desc {
                                          filter at filter + i * filter_image_stride elements - a batch of n
                                          independent matrix products (1x1, group 1 only), which is how MatMul
                                          runs all its slices in one launch                                */
+    const void *residual;             /* optional NHWC int8 tensor of the output's shape and exponent that is added
+                                         to the result with saturation: out = sat(q + residual), q being the
+                                         saturated, activated conv result - a following dl::module::Add with equal
+                                         exponents (esp-dl/dl/base/dl_base_add.cpp:8-44) folded into the conv.
+                                         int8, group 1, filters without a window only; NULL = none          */
+    int32_t residual_pixel_stride;    /* elements between consecutive residual pixels; 0 = out_c (dense)  */
+    int32_t reserved;
 } espdl_conv_desc;
 
 int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream);

@@ -110,6 +110,8 @@ static int conv_check(const espdl_conv_desc *d)
         return ESPDL_ERR_INVALID_ARG;
     if (d->activation != ESPDL_ACT_LINEAR && d->activation != ESPDL_ACT_RELU)
         return ESPDL_ERR_UNSUPPORTED;
+    if (d->residual && (d->dtype != ESPDL_DTYPE_INT8 || d->group != 1))
+        return ESPDL_ERR_UNSUPPORTED;
     return ESPDL_OK;
 }
 
@@ -183,7 +185,13 @@ int oracle_conv2d(const espdl_conv_desc *d)
                     o16[oi] = (int16_t)q;
                 } else {
                     /* fused dl::module::LUT node: esp-dl/dl/base/dl_base_lut.cpp:10-15 */
-                    o8[oi] = d->lut ? d->lut[(uint8_t)(int8_t)q ^ 0x80u] : (int8_t)q;
+                    int32_t r8 = d->lut ? d->lut[(uint8_t)(int8_t)q ^ 0x80u] : (int8_t)q;
+                    if (d->residual) { /* a following Add with equal exponents: saturating sum, dl_base_add.cpp:8-44 */
+                        const int rps = d->residual_pixel_stride ? d->residual_pixel_stride : d->out_c;
+                        r8 += ((const int8_t *)d->residual)[(((int64_t)n * d->out_h + oy) * d->out_w + ox) * rps + oc];
+                        r8 = r8 > 127 ? 127 : (r8 < -128 ? -128 : r8);
+                    }
+                    o8[oi] = (int8_t)r8;
                 }
             }
         }

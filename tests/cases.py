@@ -63,21 +63,21 @@ def gemm_case(seed=0, dtype=abi.DTYPE_INT8, m=64, k=64, n_out=32, **kw):
     return conv_case(seed=seed, dtype=dtype, n=1, h=1, w=m, cin=k, cout=n_out, kh=1, kw=1, pad=(0, 0, 0, 0), **kw)
 
 
-_SCALARS = [f for f, _ in abi.ConvDesc._fields_][6:]
+_SCALARS = [f for f, t in abi.ConvDesc._fields_ if t is abi.i32 and f != "reserved"]
 
 
 def conv_desc(case, ptrs=None):
     """ptrs: optional dict name -> integer address overriding the host arrays (device copies)."""
     d = abi.ConvDesc()
-    host = dict(input=case["x"], filter=case["w"], bias=case["b"], output=case["out"], filter_exponents=case["ew"], lut=case["lut"])
+    host = dict(input=case["x"], filter=case["w"], bias=case["b"], output=case["out"], filter_exponents=case["ew"], lut=case["lut"],
+                residual=case.get("res"))
     for k, a in host.items():
         if ptrs is not None:
             setattr(d, k, ptrs.get(k))
         else:
             setattr(d, k, None if a is None else a.ctypes.data)
     for f in _SCALARS:
-        if f != "reserved":
-            setattr(d, f, int(case[f]))
+        setattr(d, f, int(case.get(f, 0)))
     return d
 
 

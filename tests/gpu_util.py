@@ -59,7 +59,7 @@ def run_conv_gpu(case, kernel=abi.KERNEL_AUTO, expect=abi.OK):
     import cases
     with DeviceBuffers() as dev:
         ptrs = dict(input=dev.upload(case["x"]), filter=dev.upload(case["w"]), bias=dev.upload(case["b"]),
-                    filter_exponents=dev.upload(case["ew"]), lut=dev.upload(case["lut"]),
+                    filter_exponents=dev.upload(case["ew"]), lut=dev.upload(case["lut"]), residual=dev.upload(case.get("res")),
                     output=dev.upload(np.full_like(case["out"], 0x55)))
         d = cases.conv_desc(dict(case, kernel=kernel), ptrs)
         st = dev.lib.espdl_b200_conv2d(C.byref(d), None)

@@ -200,3 +200,19 @@ def test_batched_matrix_products(n, m, k, nout, kernel):
         one["x"], one["w"] = np.ascontiguousarray(case["x"][i:i + 1]), np.ascontiguousarray(case["w"][i])
         np.testing.assert_array_equal(gpu_util.run_conv_oracle(one)[0], want[i])
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=kernel), want)
+
+
+@pytest.mark.parametrize("m,k,n,act,kernel,direct", [(300, 96, 32, abi.ACT_LINEAR, abi.KERNEL_TCGEN05, False), (1000, 384, 64, abi.ACT_RELU, abi.KERNEL_TCGEN05, False),
+                                                    (200, 64, 250, abi.ACT_LINEAR, abi.KERNEL_TCGEN05, False), (257, 144, 24, abi.ACT_LINEAR, abi.KERNEL_TCGEN05, True),
+                                                    (90, 24, 40, abi.ACT_LINEAR, abi.KERNEL_SIMT, False)])
+def test_pointwise_conv_with_folded_add(m, k, n, act, kernel, direct, monkeypatch):
+    """espdl_conv_desc::residual: out = sat(sat(conv) + residual), the Add of equal exponents that follows a project conv."""
+    if direct:
+        monkeypatch.setenv("ESPDL_B200_DIRECT_STORES", "1")
+    case = cases.gemm_case(seed=33, m=m, k=k, n_out=n, per_channel=True, act=act, e_in=-7, e_out=-6, e_w=(-9, -7))
+    case["res"] = np.random.default_rng(34).integers(-128, 128, size=case["out"].shape, dtype=np.int8)
+    want = gpu_util.run_conv_oracle(case)
+    plain = gpu_util.run_conv_oracle(dict(case, res=None))
+    np.testing.assert_array_equal(want, np.clip(plain.astype(np.int32) + case["res"], -128, 127).astype(np.int8))
+    assert (want != plain).mean() > 0.5 and (np.abs(want.astype(int)) == 127).mean() < 0.6
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=kernel), want)
