@@ -39,3 +39,100 @@ def gather_logits(local, total, group=None, out=None):
     dist.all_gather(pieces, padded, group=group)
     rows = [pieces[r][: shard_range(total, r, world)[1] - shard_range(total, r, world)[0]] for r in range(world)]
     return torch.cat(rows, dim=0)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# N-sharded Gemm: the filter [N][K] is split along N into one block of rows per rank, every rank holds all of the
+# input [M][K] and computes out[:, n0:n1]; one all-gather along N assembles the [M][N] result on every rank.  K is
+# not split, so no int32 partial sum ever crosses a GPU and every output is rounded exactly as on one GPU.
+# (Gemm = conv2d on a {1,1,M,K} input with a {1,1,K,N} filter: esp-dl/dl/module/include/dl_module_gemm.hpp:85-123.)
+# ---------------------------------------------------------------------------------------------------------------
+
+def _interleave_columns(staging, out):
+    """out[m, r*n_loc + j] = staging[r, m, j].  On a GPU this is one launch of the library's strided-copy kernel
+    (espdl_b200_copy); host tensors (the gloo tests) are re-ordered by torch."""
+    world, m, n_loc = staging.shape
+    if not staging.is_cuda:
+        out.copy_(staging.permute(1, 0, 2).reshape(m, world * n_loc))
+        return out
+    import ctypes as C
+    from . import abi
+    d = abi.CopyDesc()
+    d.src, d.dst, d.elem_size, d.ndim = staging.data_ptr(), out.data_ptr(), staging.element_size(), 3
+    for i, (s, a, b) in enumerate(zip((world, m, n_loc), (m * n_loc, n_loc, 1), (n_loc, world * n_loc, 1))):
+        d.shape[i], d.src_stride[i], d.dst_stride[i] = s, a, b
+    stream = C.c_void_p(torch.cuda.current_stream(staging.device).cuda_stream)
+    abi.check(abi.load().espdl_b200_copy(C.byref(d), stream), "espdl_b200_copy")
+    return out
+
+
+def gather_columns(local, group=None, staging=None, out=None):
+    """Every rank passes its [M, N/world] block of output columns and gets the whole [M, N] matrix: one
+    all_gather_into_tensor into a [world, M, N/world] staging buffer, then a local re-ordering copy."""
+    world = dist.get_world_size(group)
+    m, n_loc = local.shape
+    if staging is None:
+        staging = torch.empty((world, m, n_loc), dtype=local.dtype, device=local.device)
+    if out is None:
+        out = torch.empty((m, world * n_loc), dtype=local.dtype, device=local.device)
+    # collectives move bytes: NCCL has no 16-bit integer type
+    dist.all_gather_into_tensor(staging.view(world * m, n_loc).view(torch.uint8), local.contiguous().view(torch.uint8),
+                                group=group)
+    return _interleave_columns(staging, out)
+
+
+class NShardedGemm:
+    """out[M][N] = requantise(in[M][K] . filter[N][K]^T + bias) with the filter rows split over the ranks of `group`.
+
+    filter: numpy int8/int16 [N][K] (the reference's generic-C order), bias: int32/int64 [N] or None,
+    filter_exponents: int (per tensor) or int array [N] (per channel).  N must be a multiple of the world size.
+    Every rank passes the same arrays and keeps only its block of rows on its GPU.  forward() takes the whole input
+    as a device tensor [M][K] and returns the whole output on every rank."""
+
+    def __init__(self, filter, bias, in_exponent, filter_exponents, out_exponent, activation=0, round_mode=0,
+                 group=None, device=None):
+        import numpy as np
+        from . import abi
+        self.abi, self.lib, self.group = abi, abi.load(), group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        n, self.k = filter.shape
+        if n % self.world:
+            raise ValueError(f"N={n} is not a multiple of the {self.world} ranks")
+        self.n, self.n_loc = n, n // self.world
+        n0, n1 = self.rank * self.n_loc, (self.rank + 1) * self.n_loc
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        up = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
+        self.dtype = {np.dtype(np.int8): abi.DTYPE_INT8, np.dtype(np.int16): abi.DTYPE_INT16}[filter.dtype]
+        self.torch_dtype = torch.int8 if filter.dtype == np.int8 else torch.int16
+        self.filter = up(filter[n0:n1])
+        self.bias = None if bias is None else up(bias[n0:n1])
+        self.per_channel = int(np.ndim(filter_exponents) > 0)
+        self.ew = up(np.asarray(filter_exponents, dtype=np.int32)[n0:n1]) if self.per_channel else None
+        self.e_w = 0 if self.per_channel else int(filter_exponents)
+        self.e_in, self.e_out, self.activation, self.round_mode = in_exponent, out_exponent, activation, round_mode
+        self._bufs = {}
+
+    def forward(self, x):
+        import ctypes as C
+        m, k = x.shape
+        if k != self.k or x.dtype != self.torch_dtype or not x.is_cuda or not x.is_contiguous():
+            raise ValueError("input must be a contiguous device tensor [M][K] of the filter's type")
+        if m not in self._bufs:
+            self._bufs[m] = (torch.empty((self.world, m, self.n_loc), dtype=self.torch_dtype, device=self.device),
+                             torch.empty((m, self.n), dtype=self.torch_dtype, device=self.device))
+        staging, out = self._bufs[m]
+        local = staging[self.rank]
+        d = self.abi.ConvDesc()
+        d.input, d.filter, d.output = x.data_ptr(), self.filter.data_ptr(), local.data_ptr()
+        d.bias = None if self.bias is None else self.bias.data_ptr()
+        d.filter_exponents = None if self.ew is None else self.ew.data_ptr()
+        d.dtype, d.n, d.in_h, d.in_w, d.in_c = self.dtype, 1, 1, m, k
+        d.out_h, d.out_w, d.out_c, d.kh, d.kw = 1, m, self.n_loc, 1, 1
+        d.stride_h = d.stride_w = d.dilation_h = d.dilation_w = d.group = 1
+        d.in_exponent, d.out_exponent, d.filter_exponent = self.e_in, self.e_out, self.e_w
+        d.per_channel, d.activation, d.round_mode = self.per_channel, self.activation, self.round_mode
+        stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        self.abi.check(self.lib.espdl_b200_conv2d(C.byref(d), stream), "espdl_b200_conv2d")
+        dist.all_gather_into_tensor(staging.view(self.world * m, self.n_loc).view(torch.uint8), local.view(torch.uint8),
+                                    group=self.group)
+        return _interleave_columns(staging, out)

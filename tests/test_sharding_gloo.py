@@ -73,3 +73,37 @@ def test_shard_range_covers_everything_once():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         sharding.shard_range(4, 2, 2)
+
+
+def _columns_worker(rank, world, port, ret):
+    sys.path.insert(0, HERE)
+    import conftest  # noqa: F401
+    from espdl_b200 import sharding
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        full = np.random.default_rng(9).integers(-128, 128, size=(5, 12), dtype=np.int8)
+        n_loc = 12 // world
+        local = torch.from_numpy(full[:, rank * n_loc:(rank + 1) * n_loc].copy())
+        got = sharding.gather_columns(local)
+        ret.put((rank, got.numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_blocks_gather_into_the_whole_matrix():
+    """N-sharded Gemm exchange: each rank owns a block of output columns; every rank ends with [M][N]."""
+    ctx = mp.get_context("spawn")
+    ret = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_columns_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(ret.get(timeout=120) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    full = np.random.default_rng(9).integers(-128, 128, size=(5, 12), dtype=np.int8)
+    for r in range(2):
+        np.testing.assert_array_equal(got[r], full)
