@@ -79,6 +79,22 @@ class SoftmaxDesc(C.Structure):
     ]
 
 
+class BlockDesc(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("output", C.c_void_p),
+        ("expand_filter", C.c_void_p), ("expand_bias", C.c_void_p), ("expand_filter_exponents", C.c_void_p),
+        ("dw_filter", C.c_void_p), ("dw_bias", C.c_void_p), ("dw_filter_exponents", C.c_void_p),
+        ("project_filter", C.c_void_p), ("project_bias", C.c_void_p), ("project_filter_exponents", C.c_void_p),
+        ("residual", C.c_void_p),
+        ("dtype", i32), ("n", i32), ("in_h", i32), ("in_w", i32), ("in_c", i32), ("hidden_c", i32),
+        ("out_h", i32), ("out_w", i32), ("out_c", i32), ("stride", i32), ("pad_top", i32), ("pad_left", i32),
+        ("in_exponent", i32), ("expand_exponent", i32), ("dw_exponent", i32), ("out_exponent", i32),
+        ("expand_filter_exponent", i32), ("dw_filter_exponent", i32), ("project_filter_exponent", i32),
+        ("per_channel", i32), ("expand_activation", i32), ("dw_activation", i32), ("project_activation", i32),
+        ("expand_clip_max", i32), ("dw_clip_max", i32), ("round_mode", i32), ("reserved", i32 * 2),
+    ]
+
+
 # every symbol include/espdl_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "espdl_b200_init": (C.c_int, [C.c_int]),
@@ -116,6 +132,7 @@ SYMBOLS = {
     "espdl_b200_resize": (C.c_int, [C.POINTER(ResizeDesc), C.c_void_p]),
     "espdl_b200_copy": (C.c_int, [C.POINTER(CopyDesc), C.c_void_p]),
     "espdl_b200_softmax": (C.c_int, [C.POINTER(SoftmaxDesc), C.c_void_p]),
+    "espdl_b200_fused_block": (C.c_int, [C.POINTER(BlockDesc), C.c_void_p]),
 }
 
 _lib = None

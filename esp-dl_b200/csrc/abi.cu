@@ -153,8 +153,9 @@ int espdl_b200_stream_sync(void *stream)
     const int dev_dw = read_and_clear_device_error_dw();
     const int dev_stem = read_and_clear_device_error_stem();
     const int dev_conv = read_and_clear_device_error_conv();
+    const int dev_block = read_and_clear_device_error_block();
     if (!dev)
-        dev = dev_dw ? dev_dw : (dev_stem ? dev_stem : dev_conv);
+        dev = dev_dw ? dev_dw : (dev_stem ? dev_stem : (dev_conv ? dev_conv : dev_block));
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -438,6 +439,13 @@ int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream)
         g_ws_bytes = need;
     }
     return espdl_b200_conv2d_ws(desc, g_ws, g_ws_bytes, stream);
+}
+
+int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream)
+{
+    if (!desc)
+        return ESPDL_ERR_INVALID_ARG;
+    return fused_block_tc(*desc, (cudaStream_t)stream);
 }
 
 } // extern "C"

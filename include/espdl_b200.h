@@ -292,6 +292,45 @@ typedef struct espdl_softmax_desc {
 
 int espdl_b200_softmax(const espdl_softmax_desc *desc, void *stream);
 
+/* ---------------------------------------------------------- fused inverted-residual block */
+/* One launch for the MobileNetV2 block: 1x1 expand conv -> 3x3 depthwise conv (stride 1 or 2) -> 1x1 project conv
+ * (-> residual Add).  In the reference these are three or four nodes, each a dl::module::Conv / Add forward
+ * (esp-dl/dl/module/include/dl_module_conv.hpp, dl_module_add.hpp:43-82) over dl::base::conv2d<int8_t,...>,
+ * depthwise_conv2d<int8_t,...> and elemwise_add (esp-dl/dl/base/dl_base_conv2d.cpp:9-163,
+ * dl_base_depthwise_conv2d.cpp:9-66, dl_base_add.cpp:8-44); every intermediate tensor is requantised to int8
+ * exactly as the separate nodes do, it just never leaves the SM.  expand_filter == NULL starts the block at the
+ * depthwise conv (hidden_c == in_c), which is the reference's depthwise -> pointwise pair.
+ * Returns ESPDL_ERR_UNSUPPORTED for shapes the kernel does not take (int16, in_c or hidden_c not a multiple of 16,
+ * a filter other than 3x3, ...): the caller then issues the separate convolutions. */
+typedef struct espdl_block_desc {
+    const void *input;                      /* [n][in_h][in_w][in_c] int8                                       */
+    void *output;                           /* [n][out_h][out_w][out_c] int8                                    */
+    const void *expand_filter;              /* [hidden_c][in_c] int8, or NULL                                   */
+    const void *expand_bias;                /* int32[hidden_c] or NULL                                          */
+    const int32_t *expand_filter_exponents; /* int32[hidden_c] when per_channel bit 0 is set                    */
+    const void *dw_filter;                  /* [3][3][hidden_c] int8                                            */
+    const void *dw_bias;
+    const int32_t *dw_filter_exponents;     /* per_channel bit 1                                                */
+    const void *project_filter;             /* [out_c][hidden_c] int8                                           */
+    const void *project_bias;
+    const int32_t *project_filter_exponents;/* per_channel bit 2                                                */
+    const void *residual;                   /* NULL, or a tensor of the output's shape and exponent that is added
+                                               with saturation (out = sat(sat(q) + r))                          */
+    int32_t dtype;                          /* ESPDL_DTYPE_INT8                                                 */
+    int32_t n, in_h, in_w, in_c, hidden_c, out_h, out_w, out_c;
+    int32_t stride, pad_top, pad_left;      /* of the depthwise conv; taps outside the image count as zero      */
+    int32_t in_exponent, expand_exponent, dw_exponent, out_exponent; /* of the four activation tensors           */
+    int32_t expand_filter_exponent, dw_filter_exponent, project_filter_exponent; /* per-tensor filter exponents  */
+    int32_t per_channel;
+    int32_t expand_activation, dw_activation, project_activation;   /* espdl_act_t: LINEAR or RELU               */
+    int32_t expand_clip_max, dw_clip_max;   /* upper clamp of that stage's int8 result: a Clip node of equal
+                                               exponents folded in ("ReLU6 via clamp"); 127 = none              */
+    int32_t round_mode;
+    int32_t reserved[2];
+} espdl_block_desc;
+
+int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -185,3 +185,53 @@ def softmax_desc(inp, out, table, rows, length, out_dtype, out_exponent):
     d.input, d.output, d.exp_table = inp, out, table
     d.rows, d.len, d.out_dtype, d.out_exponent = rows, length, out_dtype, out_exponent
     return d
+
+
+# ------------------------------------------------------------------------------------------ fused inverted-residual block
+def block_case(seed=0, n=1, h=14, w=14, cin=32, chid=192, cout=32, stride=1, expand=True, residual=None, per_channel=True,
+               clip1=127, clipdw=127, round_mode=abi.ROUND_HALF_UP, e=(-5, -6, -5, -5), bias_mag=1 << 10, relu=(True, True, False)):
+    """expand 1x1 (ReLU) -> depthwise 3x3 (ReLU) -> project 1x1 (linear) [-> Add] as three conv cases that share
+    their tensors, the way the separate nodes of the reference's graph do.  e = exponents of input, expanded,
+    depthwise output and block output."""
+    rng = np.random.default_rng(seed)
+    if residual is None:
+        residual = stride == 1 and cin == cout
+    acts = [abi.ACT_RELU if r else abi.ACT_LINEAR for r in relu]
+    x = rng.integers(-128, 128, size=(n, h, w, cin), dtype=np.int8)
+    stages = []
+    if expand:
+        c1 = conv_case(seed=seed * 7 + 1, n=n, h=h, w=w, cin=cin, cout=chid, kh=1, kw=1, pad=(0, 0, 0, 0), per_channel=per_channel,
+                       act=acts[0], round_mode=round_mode, e_in=e[0], e_out=e[1], e_w=(-12, -9), bias_mag=bias_mag)
+        c1["x"] = x
+        stages.append(c1)
+    else:
+        chid = cin
+    c2 = conv_case(seed=seed * 7 + 2, n=n, h=h, w=w, cin=chid, kh=3, kw=3, stride=stride, depthwise=True, per_channel=per_channel,
+                   act=acts[1], round_mode=round_mode, e_in=e[1] if expand else e[0], e_out=e[2], e_w=(-9, -7), bias_mag=bias_mag)
+    oh, ow = c2["out_h"], c2["out_w"]
+    c3 = conv_case(seed=seed * 7 + 3, n=n, h=oh, w=ow, cin=chid, cout=cout, kh=1, kw=1, pad=(0, 0, 0, 0), per_channel=per_channel,
+                   act=acts[2], round_mode=round_mode, e_in=e[2], e_out=e[3], e_w=(-12, -9), bias_mag=bias_mag)
+    if residual:
+        c3["res"] = x
+    return dict(x=x, expand=stages[0] if expand else None, dw=c2, project=c3, clip1=clip1, clipdw=clipdw, residual=residual,
+                out=np.zeros((n, oh, ow, cout), dtype=np.int8))
+
+
+def block_desc(case, ptrs):
+    """ptrs: name -> address (host arrays' or device copies') for input, output, residual and w/b/ew of each stage."""
+    d = abi.BlockDesc()
+    for k, v in ptrs.items():
+        setattr(d, k, v)
+    c1, c2, c3 = case["expand"], case["dw"], case["project"]
+    d.dtype, d.n, d.in_h, d.in_w, d.in_c = abi.DTYPE_INT8, c2["n"], c2["in_h"], c2["in_w"], case["x"].shape[3]
+    d.hidden_c, d.out_h, d.out_w, d.out_c = c2["in_c"], c2["out_h"], c2["out_w"], c3["out_c"]
+    d.stride, d.pad_top, d.pad_left = c2["stride_h"], c2["pad_top"], c2["pad_left"]
+    d.in_exponent = c1["in_exponent"] if c1 else c2["in_exponent"]
+    d.expand_exponent, d.dw_exponent, d.out_exponent = c2["in_exponent"], c2["out_exponent"], c3["out_exponent"]
+    d.expand_filter_exponent = c1["filter_exponent"] if c1 else 0
+    d.dw_filter_exponent, d.project_filter_exponent = c2["filter_exponent"], c3["filter_exponent"]
+    d.per_channel = ((c1["per_channel"] if c1 else 0) | (c2["per_channel"] << 1) | (c3["per_channel"] << 2))
+    d.expand_activation = c1["activation"] if c1 else 0
+    d.dw_activation, d.project_activation = c2["activation"], c3["activation"]
+    d.expand_clip_max, d.dw_clip_max, d.round_mode = case["clip1"], case["clipdw"], c2["round_mode"]
+    return d

@@ -76,3 +76,44 @@ def run_conv_oracle(case):
     out = np.full_like(case["out"], 0x55)
     assert checkers.oracle().oracle_conv2d(cases.conv_desc(dict(case, out=out))) == 0
     return out
+
+
+def run_block_oracle(case):
+    """The block as the reference runs it: one conv per node, every intermediate tensor in memory."""
+    import cases
+    import checkers
+    h = case["x"]
+    if case["expand"] is not None:
+        c1 = dict(case["expand"], x=h, out=np.zeros_like(case["expand"]["out"]))
+        assert checkers.oracle().oracle_conv2d(cases.conv_desc(c1)) == 0
+        h = np.minimum(c1["out"], case["clip1"]).astype(np.int8)
+    c2 = dict(case["dw"], x=h, out=np.zeros_like(case["dw"]["out"]))
+    assert checkers.oracle().oracle_conv2d(cases.conv_desc(c2)) == 0
+    h = np.minimum(c2["out"], case["clipdw"]).astype(np.int8)
+    c3 = dict(case["project"], x=h, out=np.zeros_like(case["project"]["out"]))
+    if case["residual"]:
+        c3["res"] = np.ascontiguousarray(case["x"])
+    assert checkers.oracle().oracle_conv2d(cases.conv_desc(c3)) == 0
+    return c3["out"]
+
+
+def run_block_gpu(case, expect=abi.OK):
+    import cases
+    with DeviceBuffers() as dev:
+        x = dev.upload(case["x"])
+        ptrs = dict(input=x, output=dev.upload(np.full_like(case["out"], 0x55)), residual=x if case["residual"] else None)
+        for name, key in (("expand", "expand"), ("dw", "dw"), ("project", "project")):
+            c = case[key]
+            if c is None:
+                continue
+            ptrs[name + "_filter"] = dev.upload(c["w"])
+            ptrs[name + "_bias"] = dev.upload(c["b"])
+            ptrs[name + "_filter_exponents"] = dev.upload(c["ew"])
+        d = cases.block_desc(case, ptrs)
+        st = dev.lib.espdl_b200_fused_block(C.byref(d), None)
+        if expect != abi.OK:
+            assert st == expect
+            return None
+        abi.check(st, "espdl_b200_fused_block")
+        abi.check(dev.lib.espdl_b200_stream_sync(None), "stream_sync")
+        return dev.download(ptrs["output"], case["out"])
