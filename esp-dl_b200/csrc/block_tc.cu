@@ -46,14 +46,15 @@ using namespace tc;
 
 constexpr int BK_E_WARPS = 8;
 constexpr int BK_DW_WARPS = 8;
-constexpr int BK_THREADS = 64 + 32 * (BK_E_WARPS + BK_DW_WARPS);
+constexpr int BK_CTRL_WARPS = 3; // TMA producer, expand MMA issuer, project MMA issuer
+constexpr int BK_THREADS = 32 * (BK_CTRL_WARPS + BK_E_WARPS + BK_DW_WARPS);
 constexpr int BK_CH = 64;      // hidden channels per chunk
 constexpr int BK_PIX = 80;     // bytes between pixels of the hidden buffer: 64 + 16 keeps 128-bit stores of
                                // neighbouring pixels and 32-bit loads of neighbouring rows off each other's banks
 constexpr size_t BK_SMEM_LIMIT = 226 * 1024;
 
-enum { X_FULL = 0, X_EMPTY = 2, W_FULL = 4, W_EMPTY = 6, D1_FULL = 8, D1_EMPTY = 10, H_FULL = 12, H_EMPTY = 14, A2_FULL = 16, A2_EMPTY = 18,
-       D2_FULL = 20, D2_EMPTY = 21, BK_NBARS = 22 };
+enum { X_FULL = 0, X_EMPTY = 2, W1_FULL = 4, W1_EMPTY = 6, D1_FULL = 8, D1_EMPTY = 10, H_FULL = 12, H_EMPTY = 14, A2_FULL = 16, A2_EMPTY = 18,
+       W2_FULL = 20, W2_EMPTY = 22, D2_FULL = 24, D2_EMPTY = 25, BK_NBARS = 26 };
 
 struct BlockParams {
     int n, ih, iw, cin, chid, cout, oh, ow, S, pt, pl;
@@ -153,7 +154,7 @@ __device__ __noinline__ void bk_band_general(const BlockParams &p, uint32_t hid,
 // the hidden buffer in shared memory into the project MMA's A operand.  dp4a sums four byte products of ONE channel:
 // each input column is byte-transposed once (word i = channel i of four vertically adjacent pixels) and multiplied
 // with the filter column (w[0][kx], w[1][kx], w[2][kx], 0) and its byte-shifted forms.
-template <int S>
+template <int S, bool CLIP>
 __device__ __forceinline__ void bk_band(const BlockParams &p, uint32_t hid, uint32_t a2, int band, int xb, int xe, int cq, int c0)
 {
     constexpr int ROWS_OUT = S == 1 ? 4 : 2;
@@ -193,8 +194,11 @@ __device__ __forceinline__ void bk_band(const BlockParams &p, uint32_t hid, uint
     }
     const int floor_q = p.edw.relu ? 0 : INT_MIN;
     const int clip = p.clipdw;
-    uint32_t hp = hid + (uint32_t)(band * ROWS_OUT * S * p.hpitch + xb * S * BK_PIX + cq * 4);
-    int m0 = band * ROWS_OUT * p.TW + xb;
+    const int pitch = p.hpitch, tw = p.TW;
+    uint32_t hp = hid + (uint32_t)(band * ROWS_OUT * S * pitch + xb * S * BK_PIX + cq * 4);
+    int m0 = band * ROWS_OUT * tw + xb;
+    const uint32_t a2w = a2 + (uint32_t)((cq & 3) * 4);
+    const int chi = cq >> 2;
     bool ovalid[ROWS_OUT];
 #pragma unroll
     for (int ro = 0; ro < ROWS_OUT; ro++) ovalid[ro] = band * ROWS_OUT + ro < p.TH;
@@ -221,46 +225,50 @@ __device__ __forceinline__ void bk_band(const BlockParams &p, uint32_t hid, uint
         }
 #pragma unroll
         for (int ro = 0; ro < ROWS_OUT; ro++) {
-            const int q0 = min(max(acc[ro][0] >> shift[0], floor_q), clip), q1 = min(max(acc[ro][1] >> shift[1], floor_q), clip);
-            const int q2 = min(max(acc[ro][2] >> shift[2], floor_q), clip), q3 = min(max(acc[ro][3] >> shift[3], floor_q), clip);
+            int q0 = max(acc[ro][0] >> shift[0], floor_q), q1 = max(acc[ro][1] >> shift[1], floor_q);
+            int q2 = max(acc[ro][2] >> shift[2], floor_q), q3 = max(acc[ro][3] >> shift[3], floor_q);
+            if constexpr (CLIP)
+                q0 = min(q0, clip), q1 = min(q1, clip), q2 = min(q2, clip), q3 = min(q3, clip);
             uint32_t hi, wd;
             asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
             asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
-            if (ovalid[ro])
-                sts32(a2 + a2_offset(m0 + ro * p.TW, cq), wd);
+            if (ovalid[ro]) {
+                const int m = m0 + ro * tw;
+                sts32(a2w + (uint32_t)((m << 6) + (((chi ^ (m >> 1)) & 3) << 4)), wd);
+            }
         }
         m0++;
     };
 
     BkCol<S> ca, cb, cc;
     if constexpr (S == 1) {
-        bk_load_col<S>(ca, hp, p.hpitch);
-        bk_load_col<S>(cb, hp + BK_PIX, p.hpitch);
+        bk_load_col<S>(ca, hp, pitch);
+        bk_load_col<S>(cb, hp + BK_PIX, pitch);
         hp += 2 * BK_PIX;
         for (int x = xb; x < xe; x += 3) {
-            bk_load_col<S>(cc, hp, p.hpitch);
+            bk_load_col<S>(cc, hp, pitch);
             emit(ca, cb, cc);
             if (x + 1 >= xe)
                 break;
-            bk_load_col<S>(ca, hp + BK_PIX, p.hpitch);
+            bk_load_col<S>(ca, hp + BK_PIX, pitch);
             emit(cb, cc, ca);
             if (x + 2 >= xe)
                 break;
-            bk_load_col<S>(cb, hp + 2 * BK_PIX, p.hpitch);
+            bk_load_col<S>(cb, hp + 2 * BK_PIX, pitch);
             emit(cc, ca, cb);
             hp += 3 * BK_PIX;
         }
     } else {
-        bk_load_col<S>(ca, hp, p.hpitch);
+        bk_load_col<S>(ca, hp, pitch);
         hp += BK_PIX;
         for (int x = xb; x < xe; x += 2) {
-            bk_load_col<S>(cb, hp, p.hpitch);
-            bk_load_col<S>(cc, hp + BK_PIX, p.hpitch);
+            bk_load_col<S>(cb, hp, pitch);
+            bk_load_col<S>(cc, hp + BK_PIX, pitch);
             emit(ca, cb, cc);
             if (x + 1 >= xe)
                 break;
-            bk_load_col<S>(cb, hp + 2 * BK_PIX, p.hpitch);
-            bk_load_col<S>(ca, hp + 3 * BK_PIX, p.hpitch);
+            bk_load_col<S>(cb, hp + 2 * BK_PIX, pitch);
+            bk_load_col<S>(ca, hp + 3 * BK_PIX, pitch);
             emit(cc, cb, ca);
             hp += 4 * BK_PIX;
         }
@@ -303,9 +311,28 @@ __device__ __forceinline__ uint32_t add_bytes_sat(uint32_t q, uint32_t r)
     return w;
 }
 
+// Bounded wait for the hand-overs of this kernel, which are thousands of cycles apart: a failed poll sleeps a little, so
+// that the ten or so warps that wait at any time leave the issue slots to the ones that compute.
+__device__ __forceinline__ bool bk_wait(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try(bar, parity))
+        return true;
+    const long long t0 = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int spin = 0; spin < 64; spin++) {
+            if (mbar_try(bar, parity))
+                return true;
+            __nanosleep(40);
+        }
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES)
+            return false;
+    }
+}
+
 __global__ void __launch_bounds__(BK_THREADS, 1)
 block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUtensorMap map_w2,
-                const BlockParams p)
+                const __grid_constant__ BlockParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -325,7 +352,7 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     if (threadIdx.x == 0) {
         const int counts[BK_NBARS] = {1, 1, 1, 1, 1, 1, 1, 1, 1, 1, BK_E_WARPS, BK_E_WARPS, BK_E_WARPS, BK_E_WARPS, BK_DW_WARPS / 2, BK_DW_WARPS / 2,
-                                      BK_DW_WARPS / 2, BK_DW_WARPS / 2, 1, 1, 1, BK_E_WARPS};
+                                      BK_DW_WARPS / 2, BK_DW_WARPS / 2, 1, 1, 1, 1, 1, 1, 1, BK_E_WARPS};
         for (int i = 0; i < BK_NBARS; i++) mbar_init(BAR(i), (uint32_t)counts[i]);
         slow[0] = slow[1] = 0;
         fence_barrier_init();
@@ -353,7 +380,7 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const int ty = (tile / p.xtiles) % p.ytiles, tx = tile % p.xtiles;
                 if (p.has_expand) {
                     const int tb = lt & 1;
-                    if (!mbar_wait(BAR(X_EMPTY + tb), ((lt >> 1) & 1) ^ 1)) {
+                    if (!bk_wait(BAR(X_EMPTY + tb), ((lt >> 1) & 1) ^ 1)) {
                         ok = false;
                         break;
                     }
@@ -364,17 +391,23 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 }
                 for (int c = 0; c < p.n_chunks; c++, g++) {
                     const int buf = g & 1;
-                    if (!mbar_wait(BAR(W_EMPTY + buf), ((g >> 1) & 1) ^ 1)) {
+                    const uint32_t ph = (g >> 1) & 1;
+                    if (p.has_expand) {
+                        if (!bk_wait(BAR(W1_EMPTY + buf), ph ^ 1)) {
+                            ok = false;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(BAR(W1_FULL + buf), (uint32_t)(p.kx_blocks * w1_kblock_bytes));
+                        for (int cb = 0; cb < p.kx_blocks; cb++)
+                            tma_load_2d(sbase + p.off_w1 + buf * p.w1_bytes + cb * w1_kblock_bytes, &map_w1, cb * p.kx_swz, c * BK_CH, BAR(W1_FULL + buf));
+                    }
+                    if (!bk_wait(BAR(W2_EMPTY + buf), ph ^ 1)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t bytes = (uint32_t)((p.has_expand ? p.kx_blocks * w1_kblock_bytes : 0) + p.n_split * p.npiece * 64);
-                    mbar_arrive_expect_tx(BAR(W_FULL + buf), bytes);
-                    if (p.has_expand)
-                        for (int cb = 0; cb < p.kx_blocks; cb++)
-                            tma_load_2d(sbase + p.off_w1 + buf * p.w1_bytes + cb * w1_kblock_bytes, &map_w1, cb * p.kx_swz, c * BK_CH, BAR(W_FULL + buf));
+                    mbar_arrive_expect_tx(BAR(W2_FULL + buf), (uint32_t)(p.n_split * p.npiece * 64));
                     for (int piece = 0; piece < p.n_split; piece++)
-                        tma_load_2d(sbase + p.off_w2 + buf * p.w2_bytes + piece * p.npiece * 64, &map_w2, c * BK_CH, piece * p.npiece, BAR(W_FULL + buf));
+                        tma_load_2d(sbase + p.off_w2 + buf * p.w2_bytes + piece * p.npiece * 64, &map_w2, c * BK_CH, piece * p.npiece, BAR(W2_FULL + buf));
                 }
             }
             if (!ok)
@@ -382,79 +415,79 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // ------------------------------------------------------------------ expand MMA issuer
+        if (lane == 0 && p.has_expand) {
             int g = 0, lt = 0;
             bool ok = true;
             const uint32_t idesc1 = idesc_i8(1, 1, 128, BK_CH);
-            const uint32_t idesc2 = idesc_i8(1, 1, 128, p.npiece);
-            // project MMAs of chunk c (pipeline slot gg) of the tile with local index lt
-            auto project = [&](int gg, int c, int tile_lt) -> bool {
-                const int buf = gg & 1;
-                if (c == 0 && !mbar_wait(BAR(D2_EMPTY), (tile_lt & 1) ^ 1))
-                    return false;
-                if (!mbar_wait(BAR(A2_FULL + buf), (gg >> 1) & 1))
-                    return false;
-                fence_after();
-                const int ksteps = (min(BK_CH, p.chid - c * BK_CH) + 31) / 32;
-                for (int mb = 0; mb < p.mb_out; mb++)
-                    for (int piece = 0; piece < p.n_split; piece++) {
-                        const uint64_t da = smem_desc_swizzled(sbase + p.off_a2 + buf * p.a2_bytes + mb * 128 * 64, 64);
-                        const uint64_t db = smem_desc_swizzled(sbase + p.off_w2 + buf * p.w2_bytes + piece * p.npiece * 64, 64);
-                        const uint32_t d = tmem_base + (uint32_t)(p.d2_col + mb * p.cout_pad + piece * p.npiece);
-                        for (int k = 0; k < ksteps; k++) mma_i8(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc2, (c | k) != 0);
-                    }
-                commit(BAR(A2_EMPTY + buf));
-                commit(BAR(W_EMPTY + buf));
-                return true;
-            };
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, lt++) {
                 const int tb = lt & 1;
-                if (p.has_expand && !mbar_wait(BAR(X_FULL + tb), (lt >> 1) & 1)) {
+                if (!bk_wait(BAR(X_FULL + tb), (lt >> 1) & 1)) {
                     ok = false;
                     break;
                 }
-                for (int c = 0; c < p.n_chunks && ok; c++, g++) {
+                for (int c = 0; c < p.n_chunks; c++, g++) {
                     const int buf = g & 1;
                     const uint32_t ph = (g >> 1) & 1;
-                    if (!mbar_wait(BAR(W_FULL + buf), ph)) {
+                    if (!bk_wait(BAR(W1_FULL + buf), ph) || !bk_wait(BAR(D1_EMPTY + buf), ph ^ 1)) {
                         ok = false;
                         break;
                     }
-                    if (p.has_expand) {
-                        if (!mbar_wait(BAR(D1_EMPTY + buf), ph ^ 1)) {
-                            ok = false;
-                            break;
+                    fence_after();
+                    for (int mb = 0; mb < p.mb_in; mb++)
+                        for (int cb = 0; cb < p.kx_blocks; cb++) {
+                            const int ksteps = (min(p.kx_swz, p.cin - cb * p.kx_swz) + 31) / 32;
+                            const uint64_t da = smem_desc_swizzled(sbase + p.off_x + tb * p.x_bytes + cb * x_kblock_bytes + mb * 128 * p.kx_swz, p.kx_swz);
+                            const uint64_t db = smem_desc_swizzled(sbase + p.off_w1 + buf * p.w1_bytes + cb * w1_kblock_bytes, p.kx_swz);
+                            const uint32_t d = tmem_base + (uint32_t)(buf * p.mb_in * BK_CH + mb * BK_CH);
+                            for (int k = 0; k < ksteps; k++) mma_i8(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc1, (cb | k) != 0);
                         }
-                        fence_after();
-                        for (int mb = 0; mb < p.mb_in; mb++)
-                            for (int cb = 0; cb < p.kx_blocks; cb++) {
-                                const int ksteps = (min(p.kx_swz, p.cin - cb * p.kx_swz) + 31) / 32;
-                                const uint64_t da = smem_desc_swizzled(sbase + p.off_x + tb * p.x_bytes + cb * x_kblock_bytes + mb * 128 * p.kx_swz, p.kx_swz);
-                                const uint64_t db = smem_desc_swizzled(sbase + p.off_w1 + buf * p.w1_bytes + cb * w1_kblock_bytes, p.kx_swz);
-                                const uint32_t d = tmem_base + (uint32_t)(buf * p.mb_in * BK_CH + mb * BK_CH);
-                                for (int k = 0; k < ksteps; k++) mma_i8(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc1, (cb | k) != 0);
-                            }
-                        commit(BAR(D1_FULL + buf));
-                        if (c == p.n_chunks - 1)
-                            commit(BAR(X_EMPTY + tb));
-                    }
-                    if (c > 0)
-                        ok = project(g - 1, c - 1, lt);
+                    commit(BAR(D1_FULL + buf));
+                    commit(BAR(W1_EMPTY + buf));
+                    if (c == p.n_chunks - 1)
+                        commit(BAR(X_EMPTY + tb));
                 }
-                if (!ok)
-                    break;
-                ok = project(g - 1, p.n_chunks - 1, lt);
-                if (ok)
-                    commit(BAR(D2_FULL));
             }
             if (!ok)
                 atomicExch(&g_block_tc_error, ESPDL_ERR_TIMEOUT);
         }
         __syncwarp();
-    } else if (warp < 2 + BK_E_WARPS) {
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ project MMA issuer
+        if (lane == 0) {
+            int g = 0, lt = 0;
+            bool ok = true;
+            const uint32_t idesc2 = idesc_i8(1, 1, 128, p.npiece);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, lt++) {
+                for (int c = 0; c < p.n_chunks; c++, g++) {
+                    const int buf = g & 1;
+                    const uint32_t ph = (g >> 1) & 1;
+                    if ((c == 0 && !bk_wait(BAR(D2_EMPTY), (lt & 1) ^ 1)) || !bk_wait(BAR(W2_FULL + buf), ph) || !bk_wait(BAR(A2_FULL + buf), ph)) {
+                        ok = false;
+                        break;
+                    }
+                    fence_after();
+                    const int ksteps = (min(BK_CH, p.chid - c * BK_CH) + 31) / 32;
+                    for (int mb = 0; mb < p.mb_out; mb++)
+                        for (int piece = 0; piece < p.n_split; piece++) {
+                            const uint64_t da = smem_desc_swizzled(sbase + p.off_a2 + buf * p.a2_bytes + mb * 128 * 64, 64);
+                            const uint64_t db = smem_desc_swizzled(sbase + p.off_w2 + buf * p.w2_bytes + piece * p.npiece * 64, 64);
+                            const uint32_t d = tmem_base + (uint32_t)(p.d2_col + mb * p.cout_pad + piece * p.npiece);
+                            for (int k = 0; k < ksteps; k++) mma_i8(d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc2, (c | k) != 0);
+                        }
+                    commit(BAR(A2_EMPTY + buf));
+                    commit(BAR(W2_EMPTY + buf));
+                    if (c == p.n_chunks - 1)
+                        commit(BAR(D2_FULL));
+                }
+            }
+            if (!ok)
+                atomicExch(&g_block_tc_error, ESPDL_ERR_TIMEOUT);
+        }
+        __syncwarp();
+    } else if (warp < BK_CTRL_WARPS + BK_E_WARPS) {
         // ------------------------------------------------------------------ epilogue warps: hidden tensor, then output
-        const int e = warp - 2;
+        const int e = warp - BK_CTRL_WARPS;
         const int q = e >> 2;      // which half of the work this quad of warps takes
         const int lg = warp & 3;   // TMEM lanes 32*lg .. 32*lg+31 are the ones this warp may read
         const bool fast1 = !slow[0] && !p.e1.half_even && p.cin <= 32768;
@@ -468,7 +501,7 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         bool ok = true;
 
         auto epilogue2 = [&](int tile, int tile_lt) -> bool {
-            if (!mbar_wait(BAR(D2_FULL), tile_lt & 1))
+            if (!bk_wait(BAR(D2_FULL), tile_lt & 1))
                 return false;
             fence_after();
             const int img = tile / tiles_per_image;
@@ -533,13 +566,13 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 const uint32_t ph = (g >> 1) & 1;
                 const uint32_t hid = sbase + p.off_h + buf * p.h_bytes;
                 if (p.has_expand) {
-                    if (!mbar_wait(BAR(D1_FULL + buf), ph)) {
+                    if (!bk_wait(BAR(D1_FULL + buf), ph)) {
                         ok = false;
                         break;
                     }
                     fence_after();
                 }
-                if (!mbar_wait(BAR(H_EMPTY + buf), ph ^ 1)) {
+                if (!bk_wait(BAR(H_EMPTY + buf), ph ^ 1)) {
                     ok = false;
                     break;
                 }
@@ -552,10 +585,9 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const bool inside = iy0 + py >= 0 && iy0 + py < p.ih && ix0 + px >= 0 && ix0 + px < p.iw;
                     const uint32_t t0 = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(buf * p.mb_in * BK_CH + mb * BK_CH);
                     const uint32_t dst = hid + (uint32_t)(py * p.hpitch + px * BK_PIX);
-                    for (int cc = col_begin; cc < col_end; cc += 16) {
-                        int32_t v[16];
-                        ld16(t0 + cc, v);
-                        ld_wait16(v);
+                    // 16 columns at a time into two register sets in turn: the load of the next set is in flight while
+                    // this one is requantised
+                    auto put16 = [&](int32_t *v, int cc) {
                         uint32_t pk[4];
                         if (fast1) {
                             const uint32_t fpp = fp1_base + (uint32_t)(c * BK_CH + cc) * 8u;
@@ -576,6 +608,20 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             pk[0] = pk[1] = pk[2] = pk[3] = 0u; // the depthwise conv pads the HIDDEN tensor with zeros
                         if (in_patch)
                             sts128(dst + (uint32_t)cc, pk[0], pk[1], pk[2], pk[3]);
+                    };
+                    int32_t va[16], vb[16];
+                    ld16(t0 + col_begin, va);
+                    ld_wait16(va);
+                    for (int cc = col_begin; cc < col_end; cc += 32) {
+                        ld16(t0 + cc + 16, vb);
+                        put16(va, cc);
+                        ld_wait16(vb);
+                        const bool more = cc + 32 < col_end;
+                        if (more)
+                            ld16(t0 + cc + 32, va);
+                        put16(vb, cc + 16);
+                        if (more)
+                            ld_wait16(va);
                     }
                     fence_before();
                     __syncwarp();
@@ -621,7 +667,7 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             atomicExch(&g_block_tc_error, ESPDL_ERR_TIMEOUT);
     } else {
         // ------------------------------------------------------------------ depthwise warps
-        const int d = warp - 2 - BK_E_WARPS;
+        const int d = warp - BK_CTRL_WARPS - BK_E_WARPS;
         const int grp = d >> 2;
         const int t = (d & 3) * 32 + lane;
         const int cq = t & 15;
@@ -636,7 +682,7 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if ((g & 1) != grp)
                     continue;
                 const uint32_t ph = (g >> 1) & 1;
-                if (!mbar_wait(BAR(H_FULL + grp), ph) || !mbar_wait(BAR(A2_EMPTY + grp), ph ^ 1)) {
+                if (!bk_wait(BAR(H_FULL + grp), ph) || !bk_wait(BAR(A2_EMPTY + grp), ph ^ 1)) {
                     ok = false;
                     break;
                 }
@@ -644,10 +690,16 @@ block_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if (band < p.nb && c0 < p.chid && xb < xe) {
                     const uint32_t hid = sbase + p.off_h + grp * p.h_bytes;
                     const uint32_t a2 = sbase + p.off_a2 + grp * p.a2_bytes;
-                    if (p.S == 1)
-                        bk_band<1>(p, hid, a2, band, xb, xe, cq, c0);
-                    else
-                        bk_band<2>(p, hid, a2, band, xb, xe, cq, c0);
+                    if (p.clipdw < 127) { // a folded Clip node: rare, kept out of the common path's instruction count
+                        if (p.S == 1)
+                            bk_band<1, true>(p, hid, a2, band, xb, xe, cq, c0);
+                        else
+                            bk_band<2, true>(p, hid, a2, band, xb, xe, cq, c0);
+                    } else if (p.S == 1) {
+                        bk_band<1, false>(p, hid, a2, band, xb, xe, cq, c0);
+                    } else {
+                        bk_band<2, false>(p, hid, a2, band, xb, xe, cq, c0);
+                    }
                 }
                 fence_async_smem(); // the MMA reads what these threads wrote through the async proxy
                 __syncwarp();

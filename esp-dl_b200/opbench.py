@@ -3,6 +3,7 @@
 
     python esp-dl_b200/opbench.py --case pw32_192 [--iters 10] [--kernel auto|simt|tc]
     python esp-dl_b200/opbench.py --conv n,h,w,cin,cout,k,stride,depthwise(0/1),bits(8/16)
+    python esp-dl_b200/opbench.py --block n,h,w,cin,hidden,cout,stride      (or a name from BLOCKS)
     python esp-dl_b200/opbench.py --list
 
 Device memory, streams and events come from the library itself; between timed launches a buffer larger than the
@@ -38,6 +39,16 @@ CASES = {
     "gemm_4096": (1, 1, 4096, 1024, 1024, 1, 1, 0, 8),
     "gemm_65536": (1, 1, 65536, 1024, 1024, 1, 1, 0, 8),
     "gemm_4096_s16": (1, 1, 4096, 1024, 1024, 1, 1, 0, 16),
+}
+BLOCKS = {
+    # inverted-residual blocks: n, h, w, cin, hidden, cout, stride  (hidden == cin and no expand conv when hidden = 0)
+    "block_c3": (256, 112, 112, 32, 192, 32, 1),      # the benchmark's block configuration
+    "block_16_96_24": (256, 112, 112, 16, 96, 24, 2),
+    "block_32_192_64": (512, 28, 28, 32, 192, 64, 2),
+    "block_64_384_64": (1024, 14, 14, 64, 384, 64, 1),
+    "block_96_576_96": (1024, 14, 14, 96, 576, 96, 1),
+    "block_160_960_160": (1024, 7, 7, 160, 960, 160, 1),
+    "block_dw32_16": (256, 112, 112, 32, 0, 16, 1),
 }
 KERNELS = {"auto": abi.KERNEL_AUTO, "simt": abi.KERNEL_SIMT, "tc": abi.KERNEL_TCGEN05}
 FLUSH_BYTES = 256 << 20
@@ -119,10 +130,96 @@ def run_case(dev, spec, iters, warm, kernel):
     return ms, 2 * macs / ms / 1e9, algo / ms / 1e6, algo
 
 
+def _time(L, flush, fn, iters, warm):
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    L.espdl_b200_event_create(C.byref(e0))
+    L.espdl_b200_event_create(C.byref(e1))
+    times = []
+    for i in range(warm + iters):
+        abi.check(L.espdl_b200_memset(flush, i & 0x7F, FLUSH_BYTES, None), "flush")
+        L.espdl_b200_event_record(e0, None)
+        fn()
+        L.espdl_b200_event_record(e1, None)
+        ms = C.c_float()
+        abi.check(L.espdl_b200_event_elapsed_ms(e0, e1, C.byref(ms)), "elapsed")
+        if i >= warm:
+            times.append(ms.value)
+    abi.check(L.espdl_b200_stream_sync(None), "final sync")
+    L.espdl_b200_event_destroy(e0)
+    L.espdl_b200_event_destroy(e1)
+    return float(np.median(times))
+
+
+def run_block(dev, spec, iters, warm):
+    """One inverted-residual block: the fused launch (espdl_b200_fused_block) and the same block as separate
+    convolutions with the Add folded into the project conv, which is how the model runs it without the fusion."""
+    n, h, w, cin, chid, cout, stride = spec
+    L = dev.L
+    expand = chid > 0
+    chid = chid or cin
+    oh, ow = (h + 2 - 3) // stride + 1, (w + 2 - 3) // stride + 1
+    residual = stride == 1 and cin == cout
+    rng = np.random.default_rng(4)
+    x = dev.put(rng.integers(-128, 128, size=(n, h, w, cin), dtype=np.int8))
+    hid = dev.empty(n * h * w * chid)
+    hid2 = dev.empty(n * oh * ow * chid)
+    out = dev.empty(n * oh * ow * cout)
+
+    def params(co, shape):
+        return (dev.put(rng.integers(-127, 128, size=shape, dtype=np.int8)), dev.put(rng.integers(-1024, 1024, size=co).astype(np.int32)),
+                dev.put(rng.integers(-11, -8, size=co).astype(np.int32)))
+    w1 = params(chid, (chid, cin)) if expand else (None, None, None)
+    w2 = params(chid, (3, 3, chid))
+    w3 = params(cout, (cout, chid))
+    b = abi.BlockDesc()
+    b.input, b.output, b.residual = x, out, (x if residual else None)
+    b.expand_filter, b.expand_bias, b.expand_filter_exponents = w1
+    b.dw_filter, b.dw_bias, b.dw_filter_exponents = w2
+    b.project_filter, b.project_bias, b.project_filter_exponents = w3
+    b.dtype, b.n, b.in_h, b.in_w, b.in_c, b.hidden_c, b.out_h, b.out_w, b.out_c = abi.DTYPE_INT8, n, h, w, cin, chid, oh, ow, cout
+    b.stride, b.pad_top, b.pad_left = stride, 1, 1
+    b.in_exponent, b.expand_exponent, b.dw_exponent, b.out_exponent = -5, -6, -6, -5
+    b.per_channel, b.expand_activation, b.dw_activation, b.project_activation = 7, abi.ACT_RELU, abi.ACT_RELU, abi.ACT_LINEAR
+    b.expand_clip_max = b.dw_clip_max = 127
+
+    def conv(inp, outp, prm, ih, iw, ci, co, k, s, dw, e_in, e_out, act, res=None):
+        d = abi.ConvDesc()
+        d.input, d.output, d.filter, d.bias, d.filter_exponents, d.residual = inp, outp, prm[0], prm[1], prm[2], res
+        d.dtype, d.n, d.in_h, d.in_w, d.in_c = abi.DTYPE_INT8, n, ih, iw, ci
+        d.out_h, d.out_w, d.out_c = (ih + 2 * (k // 2) - k) // s + 1, (iw + 2 * (k // 2) - k) // s + 1, co
+        d.kh = d.kw = k
+        d.stride_h = d.stride_w = s
+        d.dilation_h = d.dilation_w = 1
+        d.pad_top = d.pad_bottom = d.pad_left = d.pad_right = k // 2
+        d.group = ci if dw else 1
+        d.in_exponent, d.out_exponent, d.per_channel, d.activation = e_in, e_out, 1, act
+        return d
+    chain = []
+    if expand:
+        chain.append(conv(x, hid, w1, h, w, cin, chid, 1, 1, 0, -5, -6, abi.ACT_RELU))
+    chain.append(conv(hid if expand else x, hid2, w2, h, w, chid, chid, 3, stride, 1, -6 if expand else -5, -6, abi.ACT_RELU))
+    chain.append(conv(hid2, out, w3, oh, ow, chid, cout, 1, 1, 0, -6, -5, abi.ACT_LINEAR, x if residual else None))
+    flush = dev.empty(FLUSH_BYTES)
+
+    def fused():
+        abi.check(L.espdl_b200_fused_block(C.byref(b), None), "fused_block")
+
+    def separate():
+        for d in chain:
+            abi.check(L.espdl_b200_conv2d(C.byref(d), None), "conv2d")
+    ms_f = _time(L, flush, fused, iters, warm)
+    ms_s = _time(L, flush, separate, iters, warm)
+    dev.close()
+    macs = n * (h * w * cin * chid * (1 if expand else 0) + oh * ow * chid * 9 + oh * ow * chid * cout)
+    algo = n * (h * w * cin + oh * ow * cout * (2 if residual else 1))  # input once, output once (+ the residual read)
+    return ms_f, ms_s, 2 * macs / ms_f / 1e9, algo / ms_f / 1e6, algo
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", action="append", default=[])
     ap.add_argument("--conv", action="append", default=[])
+    ap.add_argument("--block", action="append", default=[])
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -132,13 +229,22 @@ def main():
     if a.list:
         for name, spec in CASES.items():
             print(name, spec)
+        for name, spec in BLOCKS.items():
+            print(name, spec)
         return
-    todo = [(name, CASES[name]) for name in (a.case or ([] if a.conv else list(CASES)))]
+    todo = [(name, CASES[name]) for name in (a.case or ([] if (a.conv or a.block) else list(CASES)))]
     todo += [(c, tuple(int(v) for v in c.split(","))) for c in a.conv]
     dev = Dev(a.device)
     for name, spec in todo:
         ms, tops, gbs, algo = run_case(dev, spec, a.iters, a.warmup, KERNELS[a.kernel])
         print(f"{name:16s} {ms:9.4f} ms {tops:9.2f} TOPS {gbs:9.1f} GB/s  algorithmic_bytes={algo}", flush=True)
+
+
+    for name in a.block:
+        spec = BLOCKS[name] if name in BLOCKS else tuple(int(v) for v in name.split(","))
+        ms_f, ms_s, tops, gbs, algo = run_block(dev, spec, a.iters, a.warmup)
+        print(f"{name:20s} fused {ms_f:9.4f} ms  separate convs {ms_s:9.4f} ms  {tops:8.2f} TOPS {gbs:8.1f} GB/s  "
+              f"algorithmic_bytes={algo}", flush=True)
 
 
 if __name__ == "__main__":
