@@ -133,6 +133,7 @@ SYMBOLS = {
     "espdl_b200_copy": (C.c_int, [C.POINTER(CopyDesc), C.c_void_p]),
     "espdl_b200_softmax": (C.c_int, [C.POINTER(SoftmaxDesc), C.c_void_p]),
     "espdl_b200_fused_block": (C.c_int, [C.POINTER(BlockDesc), C.c_void_p]),
+    "espdl_b200_fused_block_supported": (C.c_int, [C.POINTER(BlockDesc)]),
 }
 
 _lib = None

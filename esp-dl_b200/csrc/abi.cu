@@ -448,4 +448,11 @@ int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream)
     return fused_block_tc(*desc, (cudaStream_t)stream);
 }
 
+int espdl_b200_fused_block_supported(const espdl_block_desc *desc)
+{
+    if (!desc)
+        return ESPDL_ERR_INVALID_ARG;
+    return fused_block_supported(*desc) ? ESPDL_OK : ESPDL_ERR_UNSUPPORTED;
+}
+
 } // extern "C"

@@ -747,7 +747,7 @@ CUtensorMapSwizzle block_swizzle(int bytes)
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-bool block_plan(const espdl_block_desc &d, BlockParams &p, size_t &smem_bytes)
+bool block_plan(const espdl_block_desc &d, BlockParams &p, size_t &smem_bytes, bool check_pointers)
 {
     if (d.dtype != ESPDL_DTYPE_INT8 || d.n <= 0 || (d.stride != 1 && d.stride != 2))
         return false;
@@ -757,17 +757,19 @@ bool block_plan(const espdl_block_desc &d, BlockParams &p, size_t &smem_bytes)
         return false;
     if ((d.out_h - 1) * d.stride - d.pad_top >= d.in_h || (d.out_w - 1) * d.stride - d.pad_left >= d.in_w)
         return false;
-    if (!d.input || !d.output || !d.dw_filter || !d.project_filter || (!d.expand_filter && d.hidden_c != d.in_c))
-        return false;
-    if (((uintptr_t)d.input % 16) || ((uintptr_t)d.expand_filter % 16) || ((uintptr_t)d.project_filter % 16) || ((uintptr_t)d.dw_filter % 4))
-        return false;
+    if (check_pointers) {
+        if (!d.input || !d.output || !d.dw_filter || !d.project_filter || (!d.expand_filter && d.hidden_c != d.in_c))
+            return false;
+        if (((uintptr_t)d.input % 16) || ((uintptr_t)d.expand_filter % 16) || ((uintptr_t)d.project_filter % 16) || ((uintptr_t)d.dw_filter % 4))
+            return false;
+    }
     const int acts[3] = {d.expand_activation, d.dw_activation, d.project_activation};
     for (int a : acts)
         if (a != ESPDL_ACT_LINEAR && a != ESPDL_ACT_RELU)
             return false;
     p.n = d.n, p.ih = d.in_h, p.iw = d.in_w, p.cin = d.in_c, p.chid = d.hidden_c, p.cout = d.out_c, p.oh = d.out_h, p.ow = d.out_w;
     p.S = d.stride, p.pt = d.pad_top, p.pl = d.pad_left;
-    p.has_expand = d.expand_filter != nullptr;
+    p.has_expand = d.expand_filter != nullptr || (!check_pointers && d.reserved[0] != 0);
     const int tmax = p.S == 1 ? 14 : 7;
     p.TW = d.out_w < tmax ? d.out_w : tmax, p.TH = d.out_h < tmax ? d.out_h : tmax;
     p.PHB = (p.TH - 1) * p.S + 3, p.PWB = (p.TW - 1) * p.S + 3;
@@ -810,14 +812,14 @@ bool fused_block_supported(const espdl_block_desc &d)
 {
     BlockParams p;
     size_t smem;
-    return block_plan(d, p, smem);
+    return block_plan(d, p, smem, false); // shapes only: the caller may not have buffers yet
 }
 
 int fused_block_tc(const espdl_block_desc &d, cudaStream_t s)
 {
     BlockParams p;
     size_t smem;
-    if (!block_plan(d, p, smem))
+    if (!block_plan(d, p, smem, true))
         return ESPDL_ERR_UNSUPPORTED;
     EncodeTiledFn enc = block_encode();
     if (!enc)

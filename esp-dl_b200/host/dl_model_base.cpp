@@ -263,6 +263,129 @@ esp_err_t Model::load(fbs::FbsModel *fbs_model)
 // sum: the conv adds x to its own result (espdl_conv_desc::residual) and writes the Add's output; the Add leaves the
 // plan.  ESP-DL's Add of equal exponents is a saturating sum (esp-dl/dl/base/dl_base_add.cpp:8-44), which is what the
 // conv epilogue computes.  ESPDL_B200_FOLD_ADD=0 keeps the Add nodes.
+// Block fusion: a depthwise 3x3 conv whose input comes from a pointwise conv (optional) and whose output feeds a
+// pointwise conv, optionally followed by a residual Add, becomes ONE FusedBlock module (espdl_b200_fused_block);
+// the tensors between the stages then never exist in the arena.  Only tensors with a single reader that are not
+// graph outputs may disappear.  Off unless ESPDL_B200_FUSE_BLOCKS=1: on the networks measured so far the separate
+// kernels are as fast, because all of them are bound by integer instruction issue rather than by memory.
+void Model::fuse_blocks()
+{
+    if (!env_flag("ESPDL_B200_FUSE_BLOCKS", false) || !m_reuse_memory)
+        return;
+    ModelContext *ctx = m_model_context;
+    std::vector<std::string> graph_outputs = m_fbs_model->get_graph_outputs();
+    auto is_graph_output = [&](const std::string &n) { return std::find(graph_outputs.begin(), graph_outputs.end(), n) != graph_outputs.end(); };
+    auto readers = [&](const std::string &n) {
+        int r = 0;
+        for (const auto &ins : m_module_inputs)
+            for (const std::string &i : ins)
+                if (i == n) r++;
+        return r;
+    };
+    auto producer = [&](const std::string &n) {
+        for (size_t k = 0; k < m_module_outputs.size(); k++)
+            for (const std::string &o : m_module_outputs[k])
+                if (o == n) return (int)k;
+        return -1;
+    };
+    auto is_int8 = [&](const std::string &n) { return m_fbs_model->get_value_info_dtype(n) == DATA_TYPE_INT8; };
+    auto private_tensor = [&](const std::string &n) { return readers(n) == 1 && !is_graph_output(n) && !m_fbs_model->is_parameter(n) && is_int8(n); };
+    for (size_t s = 0; s < m_execution_plan.size(); s++) {
+        if (m_module_types[s] != "Conv" || m_module_outputs[s].size() != 1)
+            continue;
+        module::Conv *dw = dynamic_cast<module::Conv *>(m_execution_plan[s]);
+        TensorBase *dwf = m_module_inputs[s].size() > 1 ? ctx->get_tensor(m_module_inputs[s][1]) : nullptr;
+        if (!dw || !dw->is_dw3x3() || !dwf || dwf->shape.size() != 4 || dwf->shape[0] != 3 || dwf->shape[1] != 3)
+            continue;
+        const std::string y1 = m_module_inputs[s][0], y2 = m_module_outputs[s][0];
+        if (!private_tensor(y2) || !is_int8(y1))
+            continue;
+        int P = -1;
+        for (size_t k = s + 1; k < m_execution_plan.size() && P < 0; k++)
+            if (!m_module_inputs[k].empty() && m_module_inputs[k][0] == y2)
+                P = (int)k;
+        module::Conv *proj = P >= 0 && m_module_types[P] == "Conv" ? dynamic_cast<module::Conv *>(m_execution_plan[P]) : nullptr;
+        if (!proj || !proj->is_pointwise() || m_module_outputs[P].size() != 1)
+            continue;
+        int E = producer(y1);
+        module::Conv *expand = nullptr;
+        if (E >= 0 && E < (int)s && m_module_types[E] == "Conv" && private_tensor(y1) && m_module_outputs[E].size() == 1) {
+            expand = dynamic_cast<module::Conv *>(m_execution_plan[E]);
+            if (expand && !expand->is_pointwise())
+                expand = nullptr;
+        }
+        if (!expand)
+            E = -1;
+        const std::string x = expand ? m_module_inputs[E][0] : y1;
+        std::string y3 = m_module_outputs[P][0];
+        if (!is_int8(x) || !is_int8(y3))
+            continue;
+        // a residual Add behind the project conv
+        int A = -1;
+        std::string res;
+        if (private_tensor(y3)) {
+            for (size_t k = P + 1; k < m_execution_plan.size() && A < 0; k++)
+                if (m_module_types[k] == "Add" && m_module_inputs[k].size() == 2 && m_module_outputs[k].size() == 1 &&
+                    (m_module_inputs[k][0] == y3 || m_module_inputs[k][1] == y3))
+                    A = (int)k;
+            if (A >= 0) {
+                res = m_module_inputs[A][0] == y3 ? m_module_inputs[A][1] : m_module_inputs[A][0];
+                const std::string out = m_module_outputs[A][0];
+                const int e3 = m_fbs_model->get_value_info_exponent(y3);
+                if (res == y3 || m_fbs_model->is_parameter(res) || !is_int8(res) || !is_int8(out) || m_fbs_model->get_value_info_exponent(res) != e3 ||
+                    m_fbs_model->get_value_info_exponent(out) != e3 || m_fbs_model->get_value_info_shape(res) != m_fbs_model->get_value_info_shape(y3))
+                    A = -1;
+            }
+        }
+        // does the kernel take these extents?
+        const std::vector<int> xs = m_fbs_model->get_value_info_shape(x), hs = m_fbs_model->get_value_info_shape(y1),
+                               os = m_fbs_model->get_value_info_shape(y3);
+        if (xs.size() != 4 || hs.size() != 4 || os.size() != 4)
+            continue;
+        espdl_block_desc probe;
+        memset(&probe, 0, sizeof(probe));
+        probe.dtype = ESPDL_DTYPE_INT8;
+        probe.n = xs[0], probe.in_h = xs[1], probe.in_w = xs[2], probe.in_c = xs[3], probe.hidden_c = hs[3];
+        probe.out_h = os[1], probe.out_w = os[2], probe.out_c = os[3];
+        probe.stride = dw->stride(), probe.pad_top = dw->pads()[0], probe.pad_left = dw->pads()[2];
+        probe.reserved[0] = expand ? 1 : 0;
+        if (espdl_b200_fused_block_supported(&probe) != ESPDL_OK)
+            continue;
+        // build the module; each conv remembers how many inputs it had (data + parameters)
+        std::vector<std::string> inputs = {x};
+        for (int k : {E, (int)s, P}) {
+            if (k < 0)
+                continue;
+            m_execution_plan[k]->m_inputs_index.assign(m_module_inputs[k].size(), -1);
+            for (size_t i = 1; i < m_module_inputs[k].size(); i++) inputs.push_back(m_module_inputs[k][i]);
+        }
+        if (A >= 0)
+            inputs.push_back(res);
+        module::FusedBlock *fb = new module::FusedBlock(expand, dw, proj, m_fbs_model->get_value_info_exponent(y1),
+                                                        m_fbs_model->get_value_info_exponent(y2), A >= 0, m_execution_plan[P]->name);
+        const int last = A >= 0 ? A : P;
+        const std::string out_name = m_module_outputs[last][0];
+        if (A >= 0)
+            delete m_execution_plan[A];
+        m_execution_plan[last] = fb;
+        m_module_types[last] = "FusedBlock";
+        m_module_inputs[last] = inputs;
+        m_module_outputs[last] = {out_name};
+        std::vector<int> gone;
+        for (int k : {E, (int)s, P})
+            if (k >= 0 && k != last)
+                gone.push_back(k);
+        std::sort(gone.rbegin(), gone.rend());
+        for (int k : gone) {
+            m_execution_plan.erase(m_execution_plan.begin() + k);
+            m_module_types.erase(m_module_types.begin() + k);
+            m_module_inputs.erase(m_module_inputs.begin() + k);
+            m_module_outputs.erase(m_module_outputs.begin() + k);
+        }
+        s = 0; // indices moved: scan again (fused steps are no Conv any more)
+    }
+}
+
 void Model::fold_residual_adds()
 {
     if (!env_flag("ESPDL_B200_FOLD_ADD", true) || !m_reuse_memory)
@@ -320,6 +443,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
     (void)preload;
     if (!m_fbs_model || !m_model_context || m_built)
         return;
+    fuse_blocks();
     fold_residual_adds();
     ModelContext *ctx = m_model_context;
     std::vector<TensorInfo> &infos = m_tensor_infos;

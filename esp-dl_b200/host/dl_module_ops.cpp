@@ -172,7 +172,7 @@ esp_err_t Conv::prepare(ModelContext *context)
     // grouping whose block-diagonal filter stays small is used (ESPDL_B200_GROUP_K overrides the target width).
     TensorBase *input = context->get_tensor(m_inputs_index[0]);
     TensorBase *bias = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
-    if (!m_gemm && !dw && input && input->shape.size() == 4 && quant_type == QUANT_TYPE_SYMM_8BIT && fs[0] == 1 && fs[1] == 1 &&
+    if (!m_no_grouping && !m_gemm && !dw && input && input->shape.size() == 4 && quant_type == QUANT_TYPE_SYMM_8BIT && fs[0] == 1 && fs[1] == 1 &&
         m_strides[0] == 1 && m_strides[1] == 1 && m_pads[0] + m_pads[1] + m_pads[2] + m_pads[3] == 0 && filter->data &&
         !getenv("ESPDL_B200_NO_PIXEL_GROUPING")) {
         const int cin = fs[2], cout = fs[3];
@@ -298,6 +298,119 @@ bool Conv::can_fold_add() const
         if (v != 0)
             return false;
     return activation == Linear || activation == ReLU;
+}
+
+bool Conv::is_pointwise() const { return can_fold_add(); }
+
+bool Conv::is_dw3x3() const
+{
+    if (m_group == 1 || quant_type != QUANT_TYPE_SYMM_8BIT || m_lut || m_strides.size() != 2 || m_strides[0] != m_strides[1] ||
+        (m_strides[0] != 1 && m_strides[0] != 2) || m_dilations[0] != 1 || m_dilations[1] != 1 || m_pads.size() != 4)
+        return false;
+    for (int v : m_pads)
+        if (v < 0 || v > 1)
+            return false;
+    return activation == Linear || activation == ReLU;
+}
+
+// --------------------------------------------------------------------------------- FusedBlock
+FusedBlock::FusedBlock(Conv *expand, Conv *dw, Conv *project, int e_expand, int e_dw, bool residual, const char *name) :
+    Module(name, MODULE_NON_INPLACE, QUANT_TYPE_SYMM_8BIT), m_expand(expand), m_dw(dw), m_project(project), m_e_expand(e_expand), m_e_dw(e_dw),
+    m_residual(residual)
+{
+}
+
+FusedBlock::~FusedBlock()
+{
+    delete m_expand;
+    delete m_dw;
+    delete m_project;
+}
+
+// inputs: x, [expand filter, (bias)], dw filter, (bias), project filter, (bias), [residual]; a conv has a bias iff its
+// module was given three inputs, which the fusion pass recorded in the conv's own index list
+std::vector<std::vector<int>> FusedBlock::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> cur = input_shapes[0];
+    size_t at = 1;
+    for (Conv *c : {m_expand, m_dw, m_project}) {
+        if (!c)
+            continue;
+        const size_t n_params = c->m_inputs_index.size() - 1;
+        std::vector<std::vector<int>> in = {cur, input_shapes[at]};
+        cur = c->get_output_shape(in)[0];
+        at += n_params;
+    }
+    return {cur};
+}
+
+esp_err_t FusedBlock::prepare(ModelContext *context)
+{
+    // hand every conv the context indices of its parameters (slot 0, its data input, is not used by Conv::prepare)
+    size_t at = 1;
+    for (Conv *c : {m_expand, m_dw, m_project}) {
+        if (!c)
+            continue;
+        const size_t n_params = c->m_inputs_index.size() - 1;
+        for (size_t i = 0; i < n_params; i++) c->m_inputs_index[1 + i] = m_inputs_index[at + i];
+        c->m_inputs_index[0] = m_inputs_index[0];
+        at += n_params;
+        c->skip_pixel_grouping();
+        if (c->prepare(context) != ESP_OK)
+            return ESP_FAIL;
+    }
+    return ESP_OK;
+}
+
+void FusedBlock::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    espdl_block_desc d;
+    memset(&d, 0, sizeof(d));
+    TensorBase *x = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = ESPDL_OK;
+    if (!x || !out || !x->device || !out->device || x->shape.size() != 4) {
+        st = ESPDL_ERR_INVALID_ARG;
+    } else {
+        auto stage = [&](Conv *c, const void *&filter, const void *&bias, const int32_t *&exps, int32_t &e_scalar, int32_t &act, int bit) {
+            TensorBase *f = context->get_tensor(c->m_inputs_index[1]);
+            TensorBase *b = c->m_inputs_index.size() > 2 ? context->get_tensor(c->m_inputs_index[2]) : nullptr;
+            filter = f->device, bias = b ? b->device : nullptr, exps = (const int32_t *)c->m_dev_exponents;
+            e_scalar = f->exponent;
+            if (f->exponent.is_per_channel())
+                d.per_channel |= 1 << bit;
+            act = c->activation == ReLU ? ESPDL_ACT_RELU : ESPDL_ACT_LINEAR;
+            return f;
+        };
+        d.input = x->device, d.output = out->device;
+        d.dtype = ESPDL_DTYPE_INT8;
+        d.n = x->shape[0], d.in_h = x->shape[1], d.in_w = x->shape[2], d.in_c = x->shape[3];
+        d.out_h = out->shape[1], d.out_w = out->shape[2], d.out_c = out->shape[3];
+        d.hidden_c = d.in_c;
+        if (m_expand) {
+            TensorBase *f = stage(m_expand, d.expand_filter, d.expand_bias, d.expand_filter_exponents, d.expand_filter_exponent, d.expand_activation, 0);
+            d.hidden_c = f->shape.back();
+        }
+        stage(m_dw, d.dw_filter, d.dw_bias, d.dw_filter_exponents, d.dw_filter_exponent, d.dw_activation, 1);
+        stage(m_project, d.project_filter, d.project_bias, d.project_filter_exponents, d.project_filter_exponent, d.project_activation, 2);
+        d.stride = m_dw->m_strides[0], d.pad_top = m_dw->m_pads[0], d.pad_left = m_dw->m_pads[2];
+        d.in_exponent = x->exponent, d.expand_exponent = m_expand ? m_e_expand : (int)x->exponent, d.dw_exponent = m_e_dw, d.out_exponent = out->exponent;
+        d.expand_clip_max = d.dw_clip_max = 127;
+        d.round_mode = context->round_mode;
+        if (m_residual) {
+            TensorBase *r = context->get_tensor(m_inputs_index.back());
+            if (!r || !r->device)
+                st = ESPDL_ERR_INVALID_ARG;
+            else
+                d.residual = r->device;
+        }
+        if (st == ESPDL_OK)
+            st = espdl_b200_fused_block(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("FusedBlock", "%s failed: %s %s", name ? name : "?", espdl_b200_strerror(st), espdl_b200_last_error());
+    context->note(st);
 }
 
 size_t Conv::workspace_bytes(ModelContext *context)

@@ -28,8 +28,18 @@ public:
     /// Fold a following Add into the epilogue: the module's LAST input is then the residual tensor.
     void set_residual() { m_residual = true; }
 
+    /// Geometry the block-fusion pass of dl::Model looks at.
+    bool is_depthwise() const { return m_group != 1; }
+    bool is_pointwise() const;   ///< 1x1, stride 1, no padding, group 1, not a Gemm view, no fused table
+    bool is_dw3x3() const;       ///< depthwise, stride 1 or 2 (both axes), dilation 1, pads of at most 1
+    void skip_pixel_grouping() { m_no_grouping = true; }
+    int stride() const { return m_strides[0]; }
+    const std::vector<int> &pads() const { return m_pads; }
+    friend class FusedBlock;
+
 protected:
     int fill_desc(ModelContext *context, void *desc);
+    bool m_no_grouping = false;
     std::vector<int> m_dilations, m_strides;
     const int m_group;
     activation_type_t activation;
@@ -45,6 +55,24 @@ protected:
     void *m_grp_filter = nullptr, *m_grp_bias = nullptr, *m_grp_exponents = nullptr;
     TensorBase *m_lut = nullptr;
     bool m_prepared = false;
+};
+
+/// An inverted-residual block run as ONE launch of espdl_b200_fused_block: [1x1 expand conv ->] 3x3 depthwise conv ->
+/// 1x1 project conv [-> Add].  Built by dl::Model's fusion pass from the Conv modules of the separate nodes (which it
+/// owns from then on); the reference runs those nodes one by one (dl_module_conv.hpp, dl_module_add.hpp:43-82).
+/// Inputs: x, then the parameters of the convs in their order, then (with a folded Add) the residual tensor.
+class FusedBlock : public Module {
+public:
+    FusedBlock(Conv *expand, Conv *dw, Conv *project, int e_expand, int e_dw, bool residual, const char *name);
+    ~FusedBlock();
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    esp_err_t prepare(ModelContext *context) override;
+
+private:
+    Conv *m_expand, *m_dw, *m_project;
+    int m_e_expand, m_e_dw;
+    bool m_residual;
 };
 
 /// Gemm (fully connected), reference: dl_module_gemm.hpp:17-168: a 1x1 conv over {1,1,M,K}.

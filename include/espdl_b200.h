@@ -330,6 +330,10 @@ typedef struct espdl_block_desc {
 } espdl_block_desc;
 
 int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream);
+/* Shape-only question, asked while a graph is planned and no buffer exists yet: ESPDL_OK if espdl_b200_fused_block
+ * takes a block of these extents, strides and pads, ESPDL_ERR_UNSUPPORTED otherwise.  Pointers are ignored;
+ * reserved[0] != 0 says that the block has an expand conv. */
+int espdl_b200_fused_block_supported(const espdl_block_desc *desc);
 
 #ifdef __cplusplus
 }

@@ -222,3 +222,24 @@ def test_unsupported_operator_fails_to_load(tmp_path):
     g.save(path)
     with pytest.raises(RuntimeError):
         model.Model(path)
+
+
+def test_block_fusion_pass(tmp_path, monkeypatch):
+    """ESPDL_B200_FUSE_BLOCKS=1: expand -> depthwise -> project (-> Add) chains become one FusedBlock module each, the
+    tensors between the stages never exist, and the network's output is still the oracle's bit for bit."""
+    monkeypatch.setenv("ESPDL_B200_FUSE_BLOCKS", "1")
+    path = str(tmp_path / "block.espdl")
+    zoo.inverted_residual_block(seed=4, hw=28).save(path)
+    m = model.Model(path, batch=2)
+    assert [r[1] for r in m.profile()] == ["FusedBlock"]
+    m.close()
+    m, want = run_and_compare(tmp_path, zoo.inverted_residual_block(seed=4, hw=56), batch=3, seed=42, check_intermediates=False)
+    m.close()
+    # MobileNetV2: the blocks whose input channels are a multiple of 16 are fused (14 of 17), the others stay as they were
+    m, want = run_and_compare(tmp_path, zoo.mobilenet_v2(seed=5), batch=2, seed=50, check_intermediates=False)
+    kinds = [r[1] for r in m.profile()]
+    assert kinds.count("FusedBlock") >= 12, kinds
+    first = m.outputs[0].array.copy()
+    m.run()
+    np.testing.assert_array_equal(m.outputs[0].array, first)
+    m.close()
