@@ -311,20 +311,32 @@ __device__ __forceinline__ uint32_t add_bytes_sat(uint32_t q, uint32_t r)
     return w;
 }
 
-// Bounded wait for the hand-overs of this kernel, which are thousands of cycles apart: a failed poll sleeps a little, so
-// that the ten or so warps that wait at any time leave the issue slots to the ones that compute.
+// Bounded wait for the hand-overs of this kernel, which are thousands of cycles apart: the poll carries a suspend-time
+// hint, so a waiting warp is parked by the hardware until the phase completes (or the hint runs out) instead of
+// spinning through the issue slots that the computing warps need.
+__device__ __forceinline__ uint32_t bk_try(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(200000u)
+        : "memory");
+    return done;
+}
+
 __device__ __forceinline__ bool bk_wait(uint32_t bar, uint32_t parity)
 {
-    if (mbar_try(bar, parity))
+    if (bk_try(bar, parity))
         return true;
     const long long t0 = clock64();
     while (true) {
 #pragma unroll 1
-        for (int spin = 0; spin < 64; spin++) {
-            if (mbar_try(bar, parity))
+        for (int spin = 0; spin < 64; spin++)
+            if (bk_try(bar, parity))
                 return true;
-            __nanosleep(40);
-        }
         if (clock64() - t0 > WAIT_LIMIT_CYCLES)
             return false;
     }
