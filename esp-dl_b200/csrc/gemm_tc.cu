@@ -81,7 +81,7 @@ struct TcParams {
 // 16-byte groups, unaligned rows, channels outside the fast form): rows are stored directly from registers.  Out of
 // line on purpose: the staged path in the kernel then carries none of this code's registers.
 __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastParam *fast_s, uint32_t fp_base, uint32_t t0, long long m, int n0,
-                                                  bool row_ok, bool fast, int parts, int part)
+                                                  bool row_ok, bool fast, int parts, int part, bool allow_wide = true)
 {
     int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
     const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
@@ -90,7 +90,7 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
     const int out_align = (int)(amix & (~amix + 1));
     if (fast && vec_ok && p.N % 16 == 0 && !p.res) {
         // whole 16-column groups, aligned rows, one-add-one-shift constants
-        const bool wide = (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
+        const bool wide = allow_wide && (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
         const uint32_t fp = fp_base + (uint32_t)n0 * 8u;
         const int ncols = min(p.block_n, p.N - n0);
         if (p.epi.relu)
@@ -137,8 +137,13 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
                         pk[j >> 2] = (pk[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (((uint32_t)max(-128, min(127, sum)) & 0xffu) << (8 * (j & 3)));
                     }
             }
-            if (count > 0)
+            if (count > 0 && allow_wide) {
                 store_bytes(orow + c0, pk, count, out_align);
+            } else if (count > 0) {
+                store_bytes(orow + c0, pk, min(count, 16), out_align);
+                if (count > 16)
+                    store_bytes(orow + c0 + 16, pk + 4, count - 16, out_align);
+            }
         }
     }
 }
@@ -402,6 +407,237 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------------------------ CTA pairs (large int8 Gemm)
+// For a reduction long enough to be bound by the tensor pipe, the tile above needs (128 + 256) * 128 bytes per 4 MMA
+// steps and SM; the bytes a shared memory can keep in flight then cover less than the load latency and the tensor
+// pipe idles about half of the time (measured: 45 % active at 65536x1024x1024).  Here two CTAs of a cluster (the two
+// SMs of a TPC) work on one 256 x block_n tile with tcgen05.mma.cta_group::2: each loads its own 128 rows of A and only
+// HALF of the B tile (the tensor cores read the other half from the peer's shared memory), i.e. a third fewer bytes
+// per MMA and SM, so the same shared memory holds half as many more stages.  The even CTA of the pair issues the MMAs
+// for both; barriers: every TMA load of either CTA completes bytes on the even CTA's "full" barrier, the MMA
+// issuer's commits arrive on both CTAs' "empty" and "accumulator full" barriers (one commit per CTA, addressed with
+// mapa), both CTAs' epilogue warps arrive on the even CTA's "accumulator empty" barrier.  Epilogue: direct row stores.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory variable in the CTA with rank `rank`
+__device__ __forceinline__ uint32_t mapa_rank(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2, uint32_t leader_bar)
+{
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    const uint32_t z = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void commit_pair(uint32_t cluster_bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t base, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(cols) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b_half, const TcParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int a_bytes = BLOCK_M * p.swz;
+    const int bh_bytes = (p.block_n / 2) * p.swz;
+    const int stage_bytes = a_bytes + bh_bytes;
+    const int n_pad = p.n_tiles * p.block_n;
+    uint8_t *aux = smem + (size_t)p.stages * stage_bytes;
+    FastParam *fast_s = (FastParam *)aux;
+    uint64_t *bars = (uint64_t *)(aux + sizeof(FastParam) * (size_t)n_pad);
+    uint64_t *full_bar = bars, *empty_bar = bars + MAX_STAGES, *tfull_bar = bars + 2 * MAX_STAGES, *tempty_bar = tfull_bar + MAX_ACC;
+    uint32_t *tmem_slot = (uint32_t *)(tempty_bar + MAX_ACC);
+    int *slow_flag = (int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair_m_tiles = (p.m_tiles + 1) / 2;
+    const int total_pairs = pair_m_tiles * p.n_tiles;
+    const int pair_id = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int parts = 4 / p.acc_stages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < MAX_ACC; a++) {
+            mbar_init(smem_u32(&tfull_bar[a]), 1);
+            mbar_init(smem_u32(&tempty_bar[a]), 2 * 4 * parts); // the epilogue warps of both CTAs
+        }
+        *slow_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1)
+        tmem_alloc_pair(smem_u32(tmem_slot), p.tmem_cols); // the same warp of both CTAs, the same slot address
+    fence_before();
+    __syncthreads();
+    cluster_sync_all(); // both CTAs' barriers exist before either touches the other's
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair_id; t < total_pairs && ok; t += n_pairs) {
+                const int m0 = (t / p.n_tiles) * 2 * BLOCK_M + (int)rank * BLOCK_M;
+                const int n0 = (t % p.n_tiles) * p.block_n + (int)rank * (p.block_n / 2);
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
+                        ok = false;
+                        break;
+                    }
+                    if (rank == 0)
+                        mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), (uint32_t)(2 * stage_bytes)); // the bytes of both CTAs
+                    const uint32_t bar = mapa_rank(smem_u32(&full_bar[stage]), 0);
+                    uint8_t *st = smem + (size_t)stage * stage_bytes;
+                    tma_load_3d_pair(smem_u32(st), &map_a, kb * p.swz, m0, 0, bar);
+                    tma_load_3d_pair(smem_u32(st + a_bytes), &map_b_half, kb * p.swz, n0, 0, bar);
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok)
+                atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer (even CTA only)
+        if (lane == 0 && rank == 0) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            const uint32_t idesc = idesc_i8(1, 1, 2 * BLOCK_M, p.block_n);
+            const int ksteps = p.swz / 32;
+            for (int t = pair_id; t < total_pairs && ok; t += n_pairs) {
+                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1)) {
+                    ok = false;
+                    break;
+                }
+                fence_after();
+                const uint32_t d0 = tmem_base + (uint32_t)(acc * p.block_n);
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+                        ok = false;
+                        break;
+                    }
+                    fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)stage * stage_bytes);
+                    const uint64_t da = smem_desc_swizzled(st, p.swz);
+                    const uint64_t db = smem_desc_swizzled(st + a_bytes, p.swz);
+                    for (int k = 0; k < ksteps; k++) mma_i8_pair(d0, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                    commit_pair(mapa_rank(smem_u32(&empty_bar[stage]), 0));
+                    commit_pair(mapa_rank(smem_u32(&empty_bar[stage]), 1));
+                    if (++stage == p.stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok)
+                    break;
+                commit_pair(mapa_rank(smem_u32(&tfull_bar[acc]), 0));
+                commit_pair(mapa_rank(smem_u32(&tfull_bar[acc]), 1));
+                if (++acc == p.acc_stages) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+            if (!ok)
+                atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..17 of both CTAs)
+        const int ew = warp - 2;
+        const int group = ew >> 2;
+        const int acc = group % p.acc_stages;
+        const int part = group / p.acc_stages;
+        const int lane_group = warp & 3;
+        const int row_in_tile = lane_group * 32 + lane;
+        const int et = threadIdx.x - 64;
+        stage_fast_params(p.epi, fast_s, p.N, n_pad, et, EPI_WARPS * 32, slow_flag);
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+        const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut && p.K <= 32768;
+        const uint32_t fp_base = epi_param_base(fast_s);
+        const uint32_t tempty_leader = mapa_rank(smem_u32(&tempty_bar[acc]), 0);
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        int local = 0;
+        for (int t = pair_id; t < total_pairs && ok; t += n_pairs, local++) {
+            if (local % p.acc_stages != acc)
+                continue;
+            const int m0 = (t / p.n_tiles) * 2 * BLOCK_M + (int)rank * BLOCK_M;
+            const int n0 = (t % p.n_tiles) * p.block_n;
+            if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase)) {
+                ok = false;
+                break;
+            }
+            acc_phase ^= 1;
+            fence_after();
+            const bool row_ok = m0 + row_in_tile < p.M;
+            const long long m = (long long)m0 + row_in_tile;
+            const uint32_t t0 = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * p.block_n);
+            // 128-bit stores: in this kernel the 256-bit form stored only the first word of each 32 bytes
+            epilogue_direct_tile(p, fast_s, fp_base, t0, m, n0, row_ok, fast, parts, part, false);
+            fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive_cluster(tempty_leader);
+        }
+        if (!ok && lane == 0)
+            atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+    }
+
+    fence_before();
+    __syncthreads();
+    cluster_sync_all(); // neither CTA leaves (or frees TMEM) while the other may still read its shared memory or barriers
+    if (warp == 1) {
+        fence_after();
+        tmem_dealloc_pair(tmem_base, p.tmem_cols);
+    }
+}
+
 // int16 [rows][K] (row stride `stride` elements) -> dense byte planes hi (signed) and lo (unsigned).
 __global__ void __launch_bounds__(256) split_limbs_kernel(const int16_t *__restrict__ src, long long stride, int K, long long total,
                                                           int8_t *__restrict__ hi, uint8_t *__restrict__ lo)
@@ -470,7 +706,7 @@ int pick_swz(int K)
     return 32;
 }
 
-constexpr size_t SMEM_BUDGET = 200 * 1024;
+constexpr size_t SMEM_BUDGET = 225 * 1024;
 
 size_t aux_bytes(const TcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * MAX_STAGES + 2 * MAX_ACC) * 8 + 32; }
 
@@ -528,6 +764,59 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
     return true;
 }
 
+// The CTA-pair kernel takes large int8 products without a per-image filter: long reductions, wide outputs, enough tiles.
+bool pair_plan(const espdl_conv_desc &d, TcParams &p)
+{
+    // Off unless ESPDL_B200_CTA_PAIRS=1: measured slower than the one-CTA kernel so far (65536x1024x1024: 79 us against 70 us).
+    const char *on = getenv("ESPDL_B200_CTA_PAIRS");
+    if (d.dtype != ESPDL_DTYPE_INT8 || d.filter_image_stride != 0 || !on || atoi(on) == 0)
+        return false;
+    const long long M = (long long)d.n * d.out_h * d.out_w;
+    if (M > 0x7fffffffll || d.out_c > 8192 || d.out_c < 256 || d.in_c < 512 || M < 2048)
+        return false;
+    p.M = (int)M, p.N = d.out_c, p.K = d.in_c, p.batch = 1;
+    p.n_tiles = (p.N + 255) / 256;
+    p.block_n = ((p.N + p.n_tiles - 1) / p.n_tiles + 31) / 32 * 32;
+    p.n_tiles = (p.N + p.block_n - 1) / p.block_n;
+    p.m_tiles = (p.M + BLOCK_M - 1) / BLOCK_M;
+    p.swz = 128;
+    p.k_blocks = (p.K + p.swz - 1) / p.swz;
+    p.acc_stages = 2 * p.block_n <= 512 ? 2 : 1;
+    if (p.acc_stages < 2)
+        return false;
+    p.tmem_cols = 512;
+    p.out_pw = 0, p.out_mask = 0;
+    const size_t stage_bytes = (size_t)(BLOCK_M + p.block_n / 2) * p.swz;
+    const int stages = (int)((SMEM_BUDGET - aux_bytes(p) - 1024) / stage_bytes);
+    if (stages < 3)
+        return false;
+    p.stages = stages > MAX_STAGES ? MAX_STAGES : stages;
+    return true;
+}
+
+int launch_pair(const espdl_conv_desc &d, TcParams &p, cudaStream_t s)
+{
+    const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
+    CUtensorMap ma, mb;
+    int st;
+    if ((st = make_map(&ma, d.input, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)ips, BLOCK_M, (uint32_t)p.swz, p.swz, 1, (uint64_t)p.M * ips)))
+        return st;
+    if ((st = make_map(&mb, d.filter, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, (uint32_t)(p.block_n / 2), (uint32_t)p.swz, p.swz, 1, 0)))
+        return st;
+    const size_t stage_bytes = (size_t)(BLOCK_M + p.block_n / 2) * p.swz;
+    const size_t smem = 1024 + (size_t)p.stages * stage_bytes + aux_bytes(p);
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM_BUDGET + 2048)); });
+    if (attr_err != cudaSuccess)
+        return set_cuda_error(attr_err, "cudaFuncSetAttribute(gemm_tc_pair_kernel)");
+    const long long pairs = (long long)((p.m_tiles + 1) / 2) * p.n_tiles;
+    const int grid = 2 * (int)min(pairs, (long long)(num_sms() / 2));
+    gemm_tc_pair_kernel<<<grid, NUM_THREADS, smem, s>>>(ma, mb, p); // cluster size 2 is a compile-time attribute of the kernel
+    count_launch();
+    return check_launch("gemm_tc_pair");
+}
+
 } // namespace
 
 bool conv2d_tc_supported(const espdl_conv_desc &d)
@@ -572,6 +861,11 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     p.epi.e_shift_base = d.out_exponent - d.in_exponent;
     p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;
     p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
+    {
+        TcParams pp = p;
+        if (!i16 && ips % 16 == 0 && pair_plan(d, pp))
+            return launch_pair(d, pp, s);
+    }
 
     CUtensorMap ma, mb, ma_lo, mb_lo;
     int st;

@@ -216,3 +216,25 @@ def test_pointwise_conv_with_folded_add(m, k, n, act, kernel, direct, monkeypatc
     np.testing.assert_array_equal(want, np.clip(plain.astype(np.int32) + case["res"], -128, 127).astype(np.int8))
     assert (want != plain).mean() > 0.5 and (np.abs(want.astype(int)) == 127).mean() < 0.6
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=kernel), want)
+
+
+@pytest.mark.parametrize("m,k,n,rm,act", [
+    (4096, 1024, 1024, abi.ROUND_HALF_UP, abi.ACT_LINEAR),    # benchmark configuration 2
+    (2304, 512, 256, abi.ROUND_HALF_UP, abi.ACT_RELU),        # one tile column, nine row pairs
+    (2200, 528, 320, abi.ROUND_HALF_UP, abi.ACT_LINEAR),      # ragged M and K, two tiles of 160 columns
+    (2176, 640, 1000, abi.ROUND_HALF_UP, abi.ACT_RELU),       # odd number of row tiles: the last pair's second CTA has no rows; ragged N
+    (2048, 512, 512, abi.ROUND_HALF_EVEN, abi.ACT_LINEAR),    # general epilogue
+])
+def test_gemm_s8_cta_pairs(m, k, n, rm, act, monkeypatch):
+    """Large int8 products on pairs of CTAs (tcgen05.mma.cta_group::2, 256-row tiles; ESPDL_B200_CTA_PAIRS=1): same
+    bits as the oracle."""
+    monkeypatch.setenv("ESPDL_B200_CTA_PAIRS", "1")
+    case = cases.gemm_case(seed=m + n, m=m, k=k, n_out=n, per_channel=True, e_in=-7, e_out=-5 + (k > 512), e_w=(-9, -6), act=act, round_mode=rm)
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+
+
+def test_gemm_s8_same_shape_without_cta_pairs(monkeypatch):
+    monkeypatch.delenv("ESPDL_B200_CTA_PAIRS", raising=False)
+    case = cases.gemm_case(seed=77, m=2304, k=512, n_out=256, per_channel=True, e_in=-7, e_out=-5, e_w=(-9, -6))
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), gpu_util.run_conv_oracle(case))
