@@ -42,7 +42,7 @@ using namespace tc;
 constexpr int CV_THREADS = 64 + 16 * 32; // TMA warp, MMA warp, 16 epilogue warps in four groups
 constexpr int CV_MAX_STAGES = 8;
 constexpr int CV_MAX_ACC = 4;
-constexpr size_t CV_SMEM_BUDGET = 225 * 1024;
+constexpr size_t CV_SMEM_BUDGET = 200 * 1024;
 
 struct ConvTcParams {
     int n, oh, ow, cin, cout;
