@@ -132,6 +132,10 @@ SYMBOLS = {
     "espdl_b200_resize": (C.c_int, [C.POINTER(ResizeDesc), C.c_void_p]),
     "espdl_b200_copy": (C.c_int, [C.POINTER(CopyDesc), C.c_void_p]),
     "espdl_b200_softmax": (C.c_int, [C.POINTER(SoftmaxDesc), C.c_void_p]),
+    "espdl_b200_gemm_scatter": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_void_p), C.c_int, C.c_void_p]),
+    "espdl_b200_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "espdl_b200_ipc_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "espdl_b200_ipc_close": (C.c_int, [C.c_void_p]),
     "espdl_b200_fused_block": (C.c_int, [C.POINTER(BlockDesc), C.c_void_p]),
     "espdl_b200_fused_block_supported": (C.c_int, [C.POINTER(BlockDesc)]),
 }

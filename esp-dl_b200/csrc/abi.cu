@@ -441,6 +441,47 @@ int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream)
     return espdl_b200_conv2d_ws(desc, g_ws, g_ws_bytes, stream);
 }
 
+int espdl_b200_gemm_scatter(const espdl_conv_desc *desc, void *const *peer_outputs, int n_peers, void *stream)
+{
+    if (!desc || !desc->input || !desc->filter || !desc->output || n_peers < 0 || n_peers > 7 || (n_peers > 0 && !peer_outputs))
+        return ESPDL_ERR_INVALID_ARG;
+    if (desc->dtype != ESPDL_DTYPE_INT8 || !conv2d_tc_supported(*desc))
+        return ESPDL_ERR_UNSUPPORTED;
+    long long delta[7] = {0, 0, 0, 0, 0, 0, 0};
+    for (int i = 0; i < n_peers; i++) {
+        if (!peer_outputs[i] || ((uintptr_t)peer_outputs[i] % 16) != ((uintptr_t)desc->output % 16))
+            return set_error_text(ESPDL_ERR_INVALID_ARG, "espdl_b200_gemm_scatter: peer output %d is null or aligned differently from the local output", i);
+        delta[i] = (long long)((intptr_t)peer_outputs[i] - (intptr_t)desc->output);
+    }
+    return conv2d_tc(*desc, nullptr, 0, (cudaStream_t)stream, delta, n_peers);
+}
+
+int espdl_b200_ipc_export(const void *dptr, void *handle64)
+{
+    if (!dptr || !handle64)
+        return ESPDL_ERR_INVALID_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI passes IPC handles as 64 bytes");
+    ESPDL_CUDA_TRY(cudaIpcGetMemHandle((cudaIpcMemHandle_t *)handle64, const_cast<void *>(dptr)));
+    return ESPDL_OK;
+}
+
+int espdl_b200_ipc_open(const void *handle64, void **dptr)
+{
+    if (!handle64 || !dptr)
+        return ESPDL_ERR_INVALID_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    ESPDL_CUDA_TRY(cudaIpcOpenMemHandle(dptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return ESPDL_OK;
+}
+
+int espdl_b200_ipc_close(void *dptr)
+{
+    if (dptr)
+        ESPDL_CUDA_TRY(cudaIpcCloseMemHandle(dptr));
+    return ESPDL_OK;
+}
+
 int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream)
 {
     if (!desc)

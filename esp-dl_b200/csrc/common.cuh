@@ -29,7 +29,8 @@ int conv2d_simt(const espdl_conv_desc &d, cudaStream_t s);
 int conv2d_depthwise(const espdl_conv_desc &d, cudaStream_t s);
 bool conv2d_tc_supported(const espdl_conv_desc &d);
 size_t conv2d_tc_workspace_bytes(const espdl_conv_desc &d);
-int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes, cudaStream_t s);
+int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes, cudaStream_t s, const long long *peer_delta = nullptr,
+              int n_peer = 0); // peer_delta: byte distances to copies of the output on other GPUs that receive every row as well
 int read_and_clear_device_error(); // status word written by device-side bounded waits (0 = none)
 int read_and_clear_device_error_dw();
 int read_and_clear_device_error_stem();

@@ -74,6 +74,8 @@ struct TcParams {
     long long ops;  // output row stride in elements
     const int8_t *res; // optional residual added to the result (same rows as the output), or null
     long long rps;     // residual row stride in elements
+    long long peer_delta[7]; // byte distance from `out` to the same buffer on other GPUs: every result row is stored there too
+    int n_peer;
     EpiConfig epi;
 };
 
@@ -88,7 +90,7 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
     // what every row start (and every 16-column step from it) is aligned to
     const uintptr_t amix = (uintptr_t)p.ops | (((uintptr_t)p.out) + (uintptr_t)n0) | 16u;
     const int out_align = (int)(amix & (~amix + 1));
-    if (fast && vec_ok && p.N % 16 == 0 && !p.res) {
+    if (fast && vec_ok && p.N % 16 == 0 && !p.res && p.n_peer == 0) {
         // whole 16-column groups, aligned rows, one-add-one-shift constants
         const bool wide = allow_wide && (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
         const uint32_t fp = fp_base + (uint32_t)n0 * 8u;
@@ -136,6 +138,13 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
                         const int sum = (int)(int8_t)(pk[j >> 2] >> (8 * (j & 3))) + (int)rrow[j];
                         pk[j >> 2] = (pk[j >> 2] & ~(0xffu << (8 * (j & 3)))) | (((uint32_t)max(-128, min(127, sum)) & 0xffu) << (8 * (j & 3)));
                     }
+            }
+            // copies of the rows in other GPUs' memory (peer-mapped pointers): plain stores, the same words
+            for (int pi = 0; pi < p.n_peer && count > 0; pi++) {
+                int8_t *prow = orow + c0 + p.peer_delta[pi];
+                store_bytes(prow, pk, min(count, 16), out_align);
+                if (count > 16)
+                    store_bytes(prow + 16, pk + 4, count - 16, out_align);
             }
             if (count > 0 && allow_wide) {
                 store_bytes(orow + c0, pk, count, out_align);
@@ -712,7 +721,7 @@ constexpr size_t SMEM_BUDGET_DEEP = 225 * 1024; // long reductions with direct r
 
 size_t aux_bytes(const TcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * MAX_STAGES + 2 * MAX_ACC) * 8 + 32; }
 
-bool plan(const espdl_conv_desc &d, TcParams &p)
+bool plan(const espdl_conv_desc &d, TcParams &p, bool force_direct = false)
 {
     const bool i16 = d.dtype == ESPDL_DTYPE_INT16;
     // one matrix over all pixels of all images, or - when every image has its own filter - one matrix per image
@@ -745,7 +754,7 @@ bool plan(const espdl_conv_desc &d, TcParams &p)
     p.out_pw = 0, p.out_mask = 0;
     const long long rps = d.residual_pixel_stride ? d.residual_pixel_stride : d.out_c;
     const bool res_ok = !d.residual || (rps % 16 == 0 && ((uintptr_t)d.residual % 16) == 0);
-    if (!i16 && ops % 16 == 0 && ((uintptr_t)d.output % 16) == 0 && res_ok && !getenv("ESPDL_B200_DIRECT_STORES")) {
+    if (!i16 && ops % 16 == 0 && ((uintptr_t)d.output % 16) == 0 && res_ok && !force_direct && !getenv("ESPDL_B200_DIRECT_STORES")) {
         const int parts = 4 / p.acc_stages;
         if (p.block_n % (16 * parts) == 0 && p.block_n / parts <= 128) {
             p.out_pw = p.block_n / parts;
@@ -848,11 +857,15 @@ size_t conv2d_tc_workspace_bytes(const espdl_conv_desc &d)
     return 2 * a + 2 * b;
 }
 
-int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes, cudaStream_t s)
+int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes, cudaStream_t s, const long long *peer_delta, int n_peer)
 {
     TcParams p;
-    if (!plan(d, p))
+    if (n_peer < 0 || n_peer > 7 || (n_peer > 0 && (d.dtype != ESPDL_DTYPE_INT8 || !peer_delta)))
         return ESPDL_ERR_UNSUPPORTED;
+    if (!plan(d, p, n_peer > 0))
+        return ESPDL_ERR_UNSUPPORTED;
+    p.n_peer = n_peer;
+    for (int i = 0; i < 7; i++) p.peer_delta[i] = i < n_peer ? peer_delta[i] : 0;
     const bool i16 = d.dtype == ESPDL_DTYPE_INT16;
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
     p.out = d.output;
@@ -865,7 +878,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
     {
         TcParams pp = p;
-        if (!i16 && ips % 16 == 0 && pair_plan(d, pp))
+        if (!i16 && n_peer == 0 && ips % 16 == 0 && pair_plan(d, pp))
             return launch_pair(d, pp, s);
     }
 

@@ -90,7 +90,11 @@ class NShardedGemm:
     as a device tensor [M][K] and returns the whole output on every rank."""
 
     def __init__(self, filter, bias, in_exponent, filter_exponents, out_exponent, activation=0, round_mode=0,
-                 group=None, device=None):
+                 group=None, device=None, mode="gather"):
+        """mode "gather": every rank computes its block, one all-gather and an interleaving copy assemble [M][N].
+        mode "peer" (int8, one machine): every rank's kernel stores its columns straight into the [M][N] result of
+        all ranks through peer-mapped pointers (espdl_b200_gemm_scatter); a one-element all-reduce on the stream then
+        orders every rank's reads behind every rank's kernel.  No gather, no copy."""
         import numpy as np
         from . import abi
         self.abi, self.lib, self.group = abi, abi.load(), group
@@ -111,12 +115,19 @@ class NShardedGemm:
         self.e_w = 0 if self.per_channel else int(filter_exponents)
         self.e_in, self.e_out, self.activation, self.round_mode = in_exponent, out_exponent, activation, round_mode
         self._bufs = {}
+        if mode not in ("gather", "peer") or (mode == "peer" and self.dtype != abi.DTYPE_INT8):
+            raise ValueError("mode is 'gather' or 'peer'; 'peer' takes int8 only")
+        self.mode = mode
+        self._peer = {}   # M -> (own buffer, peers' mapped buffers, tensor view)
+        self._flag = None
 
     def forward(self, x):
         import ctypes as C
         m, k = x.shape
         if k != self.k or x.dtype != self.torch_dtype or not x.is_cuda or not x.is_contiguous():
             raise ValueError("input must be a contiguous device tensor [M][K] of the filter's type")
+        if self.mode == "peer":
+            return self._forward_peer(x)
         if m not in self._bufs:
             self._bufs[m] = (torch.empty((self.world, m, self.n_loc), dtype=self.torch_dtype, device=self.device),
                              torch.empty((m, self.n), dtype=self.torch_dtype, device=self.device))
@@ -136,3 +147,73 @@ class NShardedGemm:
         dist.all_gather_into_tensor(staging.view(self.world * m, self.n_loc).view(torch.uint8), local.view(torch.uint8),
                                     group=self.group)
         return _interleave_columns(staging, out)
+
+    # ------------------------------------------------------------------------------------------------ peer stores
+    class _DeviceArray:
+        """A device buffer of the library seen by torch without a copy (the CUDA array interface)."""
+
+        def __init__(self, ptr, shape, typestr):
+            self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+    def _peer_buffers(self, m):
+        import ctypes as C
+        if m in self._peer:
+            return self._peer[m]
+        own = C.c_void_p()
+        self.abi.check(self.lib.espdl_b200_arena_alloc(m * self.n, C.byref(own)), "arena_alloc")
+        handle = (C.c_ubyte * 64)()
+        self.abi.check(self.lib.espdl_b200_ipc_export(own, handle), "ipc_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=self.group)
+        peers = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                continue
+            mapped = C.c_void_p()
+            buf = (C.c_ubyte * 64).from_buffer_copy(h)
+            self.abi.check(self.lib.espdl_b200_ipc_open(buf, C.byref(mapped)), "ipc_open")
+            peers.append(mapped)
+        view = torch.as_tensor(self._DeviceArray(own.value, (m, self.n), "|i1"), device=self.device)
+        self._peer[m] = (own, peers, view)
+        return self._peer[m]
+
+    def _forward_peer(self, x):
+        import ctypes as C
+        m = x.shape[0]
+        own, peers, view = self._peer_buffers(m)
+        n0 = self.rank * self.n_loc
+        d = self.abi.ConvDesc()
+        d.input, d.filter, d.output = x.data_ptr(), self.filter.data_ptr(), own.value + n0
+        d.bias = None if self.bias is None else self.bias.data_ptr()
+        d.filter_exponents = None if self.ew is None else self.ew.data_ptr()
+        d.dtype, d.n, d.in_h, d.in_w, d.in_c = self.dtype, 1, 1, m, self.k
+        d.out_h, d.out_w, d.out_c, d.kh, d.kw = 1, m, self.n_loc, 1, 1
+        d.stride_h = d.stride_w = d.dilation_h = d.dilation_w = d.group = 1
+        d.out_pixel_stride = self.n
+        d.in_exponent, d.out_exponent, d.filter_exponent = self.e_in, self.e_out, self.e_w
+        d.per_channel, d.activation, d.round_mode = self.per_channel, self.activation, self.round_mode
+        targets = (C.c_void_p * max(len(peers), 1))(*[C.c_void_p(p.value + n0) for p in peers])
+        stream = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        self.abi.check(self.lib.espdl_b200_gemm_scatter(C.byref(d), targets, len(peers), stream), "espdl_b200_gemm_scatter")
+        if self.world > 1:
+            # stream-ordered exchange: it completes on a rank only after every rank's kernel before it has completed
+            if self._flag is None:
+                self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+            dist.all_reduce(self._flag, group=self.group)
+        return view
+
+    def close(self):
+        """Unmaps the peers' buffers and frees the own ones; every rank calls it (it synchronises the ranks first)."""
+        if not self._peer:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for own, peers, _ in self._peer.values():
+            for p in peers:
+                self.lib.espdl_b200_ipc_close(p)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        for own, _, _ in self._peer.values():
+            self.lib.espdl_b200_arena_free(own)
+        self._peer = {}

@@ -292,6 +292,22 @@ typedef struct espdl_softmax_desc {
 
 int espdl_b200_softmax(const espdl_softmax_desc *desc, void *stream);
 
+/* ---------------------------------------------------------- Gemm whose rows also go to other GPUs */
+/* N-sharded Gemm without a gather: every rank computes its block of output columns (espdl_conv_desc with the
+ * 1x1 / Gemm geometry of dl::module::Gemm, esp-dl/dl/module/include/dl_module_gemm.hpp:85-123; output = its column
+ * offset inside the [M][N] result, out_pixel_stride = N) and the kernel's epilogue stores every row into the local
+ * result and into the same place of up to seven peers' results (peer-mapped device pointers, plain stores over NVLink).
+ * int8 only.  The stores are complete when the kernel is; ranks order their reads behind one another's kernels with
+ * whatever they already use between steps (a stream-ordered collective, an event).  K is not split, so no partial
+ * sum crosses a GPU and the result equals the one-GPU Gemm bit for bit.
+ * espdl_b200_ipc_export / _open / _close hand a buffer of espdl_b200_arena_alloc to another process of the same
+ * machine (64-byte handle, cudaIpcMemHandle_t); a pointer returned by _open is valid in calls of this library only
+ * as an output of espdl_b200_gemm_scatter or as an operand of espdl_b200_device_copy. */
+int espdl_b200_gemm_scatter(const espdl_conv_desc *desc, void *const *peer_outputs, int n_peers, void *stream);
+int espdl_b200_ipc_export(const void *dptr, void *handle64);
+int espdl_b200_ipc_open(const void *handle64, void **dptr);
+int espdl_b200_ipc_close(void *dptr);
+
 /* ---------------------------------------------------------- fused inverted-residual block */
 /* One launch for the MobileNetV2 block: 1x1 expand conv -> 3x3 depthwise conv (stride 1 or 2) -> 1x1 project conv
  * (-> residual Add).  In the reference these are three or four nodes, each a dl::module::Conv / Add forward

@@ -32,7 +32,7 @@ def _expected(case):
     return out.reshape(case["in_w"], case["out_c"])
 
 
-def _worker(rank, world, port, dtype_name, ret):
+def _worker(rank, world, port, dtype_name, mode, ret):
     sys.path.insert(0, HERE)
     import conftest  # noqa: F401
     from espdl_b200 import abi, sharding
@@ -46,10 +46,16 @@ def _worker(rank, world, port, dtype_name, ret):
         c = _case(dtype_name)
         ew = c["ew"] if c["per_channel"] else c["filter_exponent"]
         gemm = sharding.NShardedGemm(c["w"].reshape(c["out_c"], c["in_c"]), c["b"], c["in_exponent"], ew,
-                                     c["out_exponent"], activation=c["activation"])
-        out = gemm.forward(torch.from_numpy(c["x"].reshape(c["in_w"], c["in_c"])).cuda())
+                                     c["out_exponent"], activation=c["activation"], mode=mode)
+        x = torch.from_numpy(c["x"].reshape(c["in_w"], c["in_c"])).cuda()
+        out = gemm.forward(x)
         torch.cuda.synchronize()
-        ret.put((rank, out.cpu().numpy()))
+        first = out.cpu().numpy().copy()
+        out2 = gemm.forward(x)              # buffers are reused from the second call on
+        torch.cuda.synchronize()
+        assert np.array_equal(out2.cpu().numpy(), first)
+        ret.put((rank, first))
+        gemm.close()
     finally:
         dist.destroy_process_group()
 
@@ -60,15 +66,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("dtype_name", ["int8", "int16"])
+@pytest.mark.parametrize("dtype_name,mode", [("int8", "gather"), ("int16", "gather"), ("int8", "peer")])
 @pytest.mark.parametrize("world", [1, 2])
-def test_n_sharded_gemm_equals_whole_gemm(world, dtype_name):
+def test_n_sharded_gemm_equals_whole_gemm(world, dtype_name, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     ret = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, dtype_name, ret)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, dtype_name, mode, ret)) for r in range(world)]
     for p in procs:
         p.start()
     got = dict(ret.get(timeout=120) for _ in range(world))
