@@ -145,12 +145,30 @@ long long espdl_model_read_tensor(void *handle, const char *name, void *dst, siz
 
 /// Text dump of what the C++ reader sees in a model file (no device needed): one line per node in execution
 /// order "op_type<TAB>name<TAB>inputs<TAB>outputs", then one line per initializer "name<TAB>dtype<TAB>dims<TAB>n_exponents<TAB>sum".
-const char *espdl_fbs_describe(const char *path)
+const char *espdl_fbs_describe_key(const char *path, const unsigned char *key);
+const char *espdl_fbs_describe(const char *path) { return espdl_fbs_describe_key(path, nullptr); }
+
+/// PDL3 package check (no device needed): 1 = digest matches, 0 = it does not, -1 = not a PDL3 package.
+/// `version16` (may be null) receives the version string, `package_size` (may be null) the header field.
+int espdl_fbs_verify_package(const char *path, char *version16, unsigned *package_size)
+{
+    fbs::FbsLoader loader(path, fbs::MODEL_LOCATION_IN_SDCARD);
+    if (!loader.is_pdl3())
+        return -1;
+    if (version16)
+        loader.get_package_version(version16, 16);
+    if (package_size)
+        *package_size = loader.get_package_size();
+    return loader.verify_package_sha256() ? 1 : 0;
+}
+
+/// As espdl_fbs_describe, with the 16-byte AES key of an encrypted model (null for a plain one).
+const char *espdl_fbs_describe_key(const char *path, const unsigned char *key)
 {
     static std::string text;
     text.clear();
     fbs::FbsLoader loader(path, fbs::MODEL_LOCATION_IN_SDCARD);
-    fbs::FbsModel *m = loader.load(0, nullptr, true);
+    fbs::FbsModel *m = loader.load(0, key, true);
     if (!m)
         return nullptr;
     text += "target\t" + m->get_model_metadata_prop("target") + "\n";

@@ -1,5 +1,7 @@
 #include "fbs_model.hpp"
 
+#include "fbs_crypto.hpp"
+
 #include <cstring>
 #include <fstream>
 #include <set>
@@ -499,7 +501,8 @@ FbsLoader::FbsLoader(const char *name, model_location_type_t location) : m_locat
     if (magic == "EDL1" || magic == "EDL2") {
         m_models.push_back({"", 0});
     } else if (magic == "PDL1" || magic == "PDL2" || magic == "PDL3") {
-        size_t o = magic == "PDL3" ? 4 + 16 + 4 + 32 : 4;
+        m_pdl3 = magic == "PDL3";
+        size_t o = m_pdl3 ? 4 + 16 + 4 + 32 : 4;
         const uint32_t n = u32(o);
         o += 4;
         for (uint32_t i = 0; i < n; i++, o += 12) {
@@ -526,17 +529,62 @@ const char *FbsLoader::get_model_location_string()
     return m_location == MODEL_LOCATION_IN_SDCARD ? "file" : "memory";
 }
 
-FbsModel *FbsLoader::make(size_t offset, bool param_copy)
+esp_err_t FbsLoader::get_package_version(char *out_version, size_t out_size)
+{
+    if (!out_version || out_size < 16)
+        return ESP_FAIL;
+    if (!m_pdl3 || !m_buf)
+        return ESP_FAIL;
+    memcpy(out_version, m_buf + 4, 16);
+    out_version[15] = '\0';
+    return ESP_OK;
+}
+
+uint32_t FbsLoader::get_package_size() { return m_pdl3 && m_buf ? Table::rd<uint32_t>(m_buf + 20) : 0; }
+
+esp_err_t FbsLoader::get_package_sha256(uint8_t out_sha256[32])
+{
+    if (!out_sha256 || !m_pdl3 || !m_buf)
+        return ESP_FAIL;
+    memcpy(out_sha256, m_buf + 24, 32);
+    return ESP_OK;
+}
+
+esp_err_t FbsLoader::calc_package_sha256(uint8_t out_sha256[32])
+{
+    if (!out_sha256 || !m_pdl3 || !m_buf)
+        return ESP_FAIL;
+    const uint32_t package_size = get_package_size();
+    if (package_size <= 24 + 32 || (m_buf_size && package_size > m_buf_size))
+        return ESP_FAIL;
+    const uint8_t zeros[32] = {0};
+    Sha256 h;
+    h.update(m_buf, 24);                 // magic, version, package_size
+    h.update(zeros, 32);                 // the digest field counts as zeros
+    h.update(m_buf + 56, package_size - 56);
+    h.finish(out_sha256);
+    return ESP_OK;
+}
+
+bool FbsLoader::verify_package_sha256()
+{
+    uint8_t stored[32], fresh[32];
+    return get_package_sha256(stored) == ESP_OK && calc_package_sha256(fresh) == ESP_OK && memcmp(stored, fresh, 32) == 0;
+}
+
+FbsModel *FbsLoader::make(size_t offset, const uint8_t *key, bool param_copy)
 {
     if (!m_buf)
         return nullptr;
     const uint8_t *h = m_buf + offset;
     const bool v1 = h[3] == '1';
     const uint32_t mode = Table::rd<uint32_t>(h + 4), size = Table::rd<uint32_t>(h + 8);
-    if (mode != 0) {
-        ESP_LOGE("FbsLoader", "This is a cryptographic model: encrypted payloads are not supported by this loader.");
+    if (mode != 0 && !key) {
+        ESP_LOGE("FbsLoader", "This is a cryptographic model, please enter the secret key!"); // fbs_loader.cpp:311-315
         return nullptr;
     }
+    if (mode == 0 && key)
+        ESP_LOGW("FbsLoader", "This is not a cryptographic model, the secret key is ignored.");
     const uint8_t *payload = h + (v1 ? 12 : 16);
     if (m_buf_size && offset + (v1 ? 12 : 16) + size > m_buf_size) {
         ESP_LOGE("FbsLoader", "model payload is truncated");
@@ -546,24 +594,48 @@ FbsModel *FbsLoader::make(size_t offset, bool param_copy)
     void *copy = nullptr;
     if (posix_memalign(&copy, 64, size ? size : 16))
         return nullptr;
-    memcpy(copy, payload, size);
-    return new FbsModel(copy, size, m_location, false, false, true, param_copy);
+    if (mode != 0) {
+        // AES-128-CTR with the fixed counter block 10 11 .. 1F (fbs_loader.cpp:86-124)
+        const uint8_t nonce[16] = {0x10, 0x11, 0x12, 0x13, 0x14, 0x15, 0x16, 0x17, 0x18, 0x19, 0x1A, 0x1B, 0x1C, 0x1D, 0x1E, 0x1F};
+        aes128_ctr(payload, (uint8_t *)copy, size, key, nonce);
+    } else {
+        memcpy(copy, payload, size);
+    }
+    // A FlatBuffer starts with the offset of its root table, which starts with the distance back to its vtable: reject
+    // bytes that cannot be one (a wrong key, a damaged file) before anything walks them.
+    bool sane = size >= 16;
+    if (sane) {
+        const uint32_t root = Table::rd<uint32_t>((const uint8_t *)copy);
+        sane = root >= 4 && root % 4 == 0 && (uint64_t)root + 4 <= size;
+        if (sane) {
+            const int64_t vt = (int64_t)root - (int64_t)Table::rd<int32_t>((const uint8_t *)copy + root);
+            sane = vt >= 4 && vt % 2 == 0 && vt + 4 <= (int64_t)size;
+            if (sane) {
+                const uint16_t vt_size = Table::rd<uint16_t>((const uint8_t *)copy + vt);
+                sane = vt_size >= 4 && vt_size % 2 == 0 && vt + vt_size <= (int64_t)size;
+            }
+        }
+    }
+    if (!sane) {
+        ESP_LOGE("FbsLoader", "%s", mode != 0 ? "the payload does not decrypt to a model: wrong key?" : "the payload is not a FlatBuffers model");
+        free(copy);
+        return nullptr;
+    }
+    return new FbsModel(copy, size, m_location, mode != 0, false, true, param_copy);
 }
 
 FbsModel *FbsLoader::load(const int model_index, const uint8_t *key, bool param_copy)
 {
-    (void)key;
     if (model_index < 0 || model_index >= (int)m_models.size())
         return nullptr;
-    return make(m_models[model_index].second, param_copy);
+    return make(m_models[model_index].second, key, param_copy);
 }
 
 FbsModel *FbsLoader::load(const char *model_name, const uint8_t *key, bool param_copy)
 {
-    (void)key;
     for (auto &m : m_models)
         if (model_name && m.first == model_name)
-            return make(m.second, param_copy);
+            return make(m.second, key, param_copy);
     ESP_LOGE("FbsLoader", "Model %s is not found.", model_name ? model_name : "(null)");
     return nullptr;
 }

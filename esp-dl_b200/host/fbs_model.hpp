@@ -96,9 +96,19 @@ public:
     int get_model_num();
     void list_models();
     const char *get_model_location_string();
+    /// PDL3 packages (magic, version[16], package_size, sha256[32], model table): the header fields and the
+    /// integrity check of fbs_loader.hpp:195-262.  The digest covers bytes [0, package_size) with the 32 bytes of
+    /// the stored digest taken as zeros.
+    bool is_pdl3() const { return m_pdl3; }
+    esp_err_t get_package_version(char *out_version, size_t out_size);
+    uint32_t get_package_size();
+    esp_err_t get_package_sha256(uint8_t out_sha256[32]);
+    esp_err_t calc_package_sha256(uint8_t out_sha256[32]);
+    bool verify_package_sha256();
 
 private:
-    FbsModel *make(size_t offset, bool param_copy);
+    FbsModel *make(size_t offset, const uint8_t *key, bool param_copy);
+    bool m_pdl3 = false;
     std::vector<uint8_t> m_file; ///< file contents when loaded from a path
     const uint8_t *m_buf = nullptr;
     size_t m_buf_size = 0; ///< 0 = unknown (in-memory model)

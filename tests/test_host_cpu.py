@@ -80,7 +80,72 @@ def test_corrupt_and_missing_files_are_rejected(host, tmp_path):
     assert host.espdl_fbs_describe(os.fsencode(bad)) is None
     enc = tmp_path / "enc.espdl"
     enc.write_bytes(b"EDL2" + np.array([1, 64, 0], dtype=np.uint32).tobytes() + bytes(64))  # mode 1 = encrypted
-    assert host.espdl_fbs_describe(os.fsencode(enc)) is None
+    assert host.espdl_fbs_describe(os.fsencode(enc)) is None                                  # no key given
+
+
+def _golden_model():
+    here = os.path.dirname(os.path.abspath(__file__))
+    return os.path.join(here, "golden", "espdl", "c__linear_ishap_1_64_kshap_32_64_relu_s8.espdl")
+
+
+def test_encrypted_model_loads_with_its_key(host, tmp_path):
+    """EDL2 with mode 1: the FlatBuffer is AES-128-CTR encrypted, counter block 10..1F (fbs_loader.cpp:86-124).  The
+    file is produced here with an independent AES implementation."""
+    from cryptography.hazmat.primitives.ciphers import Cipher, algorithms, modes
+    host.espdl_fbs_describe_key.restype = C.c_char_p
+    host.espdl_fbs_describe_key.argtypes = [C.c_char_p, C.c_char_p]
+    plain = open(_golden_model(), "rb").read()
+    assert plain[:4] == b"EDL2"
+    mode, size = np.frombuffer(plain[4:12], dtype=np.uint32)
+    assert mode == 0
+    key = bytes(range(0x40, 0x50))
+    enc = Cipher(algorithms.AES(key), modes.CTR(bytes(range(0x10, 0x20)))).encryptor()
+    body = enc.update(plain[16:16 + int(size)]) + enc.finalize()
+    path = tmp_path / "secret.espdl"
+    path.write_bytes(b"EDL2" + np.array([1, size, 0], dtype=np.uint32).tobytes() + body)
+    want = host.espdl_fbs_describe(os.fsencode(_golden_model()))
+    assert want is not None
+    want = bytes(want)
+    assert host.espdl_fbs_describe(os.fsencode(path)) is None
+    got = host.espdl_fbs_describe_key(os.fsencode(path), key)
+    assert got is not None and bytes(got) == want
+    wrong = host.espdl_fbs_describe_key(os.fsencode(path), bytes(16))
+    assert wrong is None or bytes(wrong) != want
+
+
+def test_pdl3_package_digest(host, tmp_path):
+    """PDL3: magic, version[16], package_size, sha256[32], model count, (data offset, name offset, name length) per
+    model (fbs_loader.hpp:13-97); the digest covers [0, package_size) with its own field zeroed."""
+    import hashlib
+    host.espdl_fbs_verify_package.restype = C.c_int
+    host.espdl_fbs_verify_package.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(C.c_uint)]
+    model = open(_golden_model(), "rb").read()
+    name = b"linear"
+    header = 60 + 12
+    name_off = header
+    data_off = (name_off + len(name) + 15) // 16 * 16
+    total = data_off + len(model)
+    pkg = bytearray(total + 32)                                  # trailing bytes outside package_size are not hashed
+    pkg[0:4] = b"PDL3"
+    pkg[4:4 + 6] = b"1.2.3\0"
+    pkg[20:24] = np.uint32(total).tobytes()
+    pkg[56:60] = np.uint32(1).tobytes()
+    pkg[60:72] = np.array([data_off, name_off, len(name)], dtype=np.uint32).tobytes()
+    pkg[name_off:name_off + len(name)] = name
+    pkg[data_off:data_off + len(model)] = model
+    digest = hashlib.sha256(bytes(pkg[:24]) + bytes(32) + bytes(pkg[56:total])).digest()
+    pkg[24:56] = digest
+    path = tmp_path / "pack.espdl"
+    path.write_bytes(bytes(pkg))
+    version = C.create_string_buffer(16)
+    size = C.c_uint(0)
+    assert host.espdl_fbs_verify_package(os.fsencode(path), version, C.byref(size)) == 1
+    assert version.value == b"1.2.3" and size.value == total
+    assert bytes(host.espdl_fbs_describe(os.fsencode(path))) == bytes(host.espdl_fbs_describe(os.fsencode(_golden_model())))
+    pkg[data_off + 40] ^= 1                                      # one flipped bit inside the package
+    path.write_bytes(bytes(pkg))
+    assert host.espdl_fbs_verify_package(os.fsencode(path), None, None) == 0
+    assert host.espdl_fbs_verify_package(os.fsencode(_golden_model()), None, None) == -1   # not a PDL3 package
 
 
 def plan(host, first, last, nbytes, alias=None, reuse=1):
