@@ -95,6 +95,16 @@ class BlockDesc(C.Structure):
     ]
 
 
+class ImageDesc(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("output", C.c_void_p), ("lut", C.c_void_p),
+        ("n", i32), ("src_h", i32), ("src_w", i32), ("channels", i32), ("dst_h", i32), ("dst_w", i32), ("out_dtype", i32),
+        ("crop_x0", i32), ("crop_y0", i32), ("crop_x1", i32), ("crop_y1", i32),
+        ("border_top", i32), ("border_bottom", i32), ("border_left", i32), ("border_right", i32),
+        ("swap_rb", i32), ("bg", C.c_uint8 * 4), ("inv_scale_x", C.c_float), ("inv_scale_y", C.c_float),
+    ]
+
+
 # every symbol include/espdl_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "espdl_b200_init": (C.c_int, [C.c_int]),
@@ -138,6 +148,7 @@ SYMBOLS = {
     "espdl_b200_ipc_close": (C.c_int, [C.c_void_p]),
     "espdl_b200_fused_block": (C.c_int, [C.POINTER(BlockDesc), C.c_void_p]),
     "espdl_b200_fused_block_supported": (C.c_int, [C.POINTER(BlockDesc)]),
+    "espdl_b200_image_preprocess": (C.c_int, [C.POINTER(ImageDesc), C.c_void_p]),
 }
 
 _lib = None

@@ -489,6 +489,13 @@ int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream)
     return fused_block_tc(*desc, (cudaStream_t)stream);
 }
 
+int espdl_b200_image_preprocess(const espdl_image_desc *desc, void *stream)
+{
+    if (!desc)
+        return ESPDL_ERR_INVALID_ARG;
+    return image_preprocess(*desc, (cudaStream_t)stream);
+}
+
 int espdl_b200_fused_block_supported(const espdl_block_desc *desc)
 {
     if (!desc)

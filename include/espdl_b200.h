@@ -351,6 +351,30 @@ int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream);
  * reserved[0] != 0 says that the block has an expand conv. */
 int espdl_b200_fused_block_supported(const espdl_block_desc *desc);
 
+/* ---------------------------------------------------------- image pre-processing */
+/* dl::image::ImagePreprocessor::preprocess (esp-dl/vision/image/dl_image_preprocessor.cpp:106-135) on the device:
+ * crop, nearest-neighbour resize (index maps of ImageTransformer::gen_xy_map, esp-dl/vision/image/dl_image_process.cpp:
+ * 488-536: source x = min((int)(x * inv_scale_x) + crop_x0, crop_x1 - 1), the same for y, identity when the sizes
+ * agree), optional letterbox border, optional R/B swap, and normalise + quantise through a 256-entry table per
+ * DESTINATION channel (NormQuant, esp-dl/vision/image/dl_image_norm_quant.hpp:13-49: table[c][v] =
+ * quantize((v - mean[c]) * (1/std[c]), 2^-exponent); RGB8882RGB888, dl_image_color_rgb8882rgb888.hpp:51-63).
+ * A batch of n images of one size is converted in one launch, straight into the model's input tensor. */
+typedef struct espdl_image_desc {
+    const uint8_t *input;  /* [n][src_h][src_w][channels] uint8: RGB888 (channels = 3) or GRAY (1)          */
+    void *output;          /* [n][dst_h][dst_w][channels] int8 or int16                                     */
+    const void *lut;       /* device table [channels][256] of the output type                               */
+    int32_t n, src_h, src_w, channels, dst_h, dst_w;
+    int32_t out_dtype;     /* ESPDL_DTYPE_INT8 or ESPDL_DTYPE_INT16                                         */
+    int32_t crop_x0, crop_y0, crop_x1, crop_y1; /* source area that is resized, x1/y1 exclusive; all 0 = whole image */
+    int32_t border_top, border_bottom, border_left, border_right; /* letterbox: destination pixels outside the
+                              resized area take the background value                                        */
+    int32_t swap_rb;       /* destination channel c reads source channel 2 - c                              */
+    uint8_t bg[4];         /* background, in SOURCE channel order                                           */
+    float inv_scale_x, inv_scale_y; /* (float)crop_width / inner_dst_width, (float)crop_height / inner_dst_height */
+} espdl_image_desc;
+
+int espdl_b200_image_preprocess(const espdl_image_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

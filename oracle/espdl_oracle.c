@@ -476,6 +476,74 @@ int oracle_softmax(const espdl_softmax_desc *d)
     return ESPDL_OK;
 }
 
+/* ---------------------------------------------------------------- image pre-processing */
+/* Table of NormQuant (esp-dl/vision/image/dl_image_norm_quant.hpp:13-31): entry [c][v] =
+ * quantize((v - mean[c]) * (1/std[c]), inv_scale), quantize = clip(round(x * inv_scale))
+ * (esp-dl/dl/tensor/src/dl_tensor_base.cpp:18-30), inv_scale = 2^-exponent.  `table` holds channels*256 entries
+ * of int8 (bits 8) or int16 (bits 16). */
+void oracle_norm_quant_table(void *table, int channels, const float *mean, const float *std, int exponent, int bits, int round_mode)
+{
+    const float inv_scale = exponent > 0 ? 1.f / (float)(1 << exponent) : (float)(1 << -exponent);
+    for (int c = 0; c < channels; c++) {
+        const float inv_std = 1.f / std[c];
+        for (int j = 0; j < 256; j++) {
+            const float x = ((float)j - mean[c]) * inv_std;
+            int q = fround(x * inv_scale, round_mode);
+            if (bits == 8) {
+                q = q < -128 ? -128 : (q > 127 ? 127 : q);
+                ((int8_t *)table)[c * 256 + j] = (int8_t)q;
+            } else {
+                q = q < -32768 ? -32768 : (q > 32767 ? 32767 : q);
+                ((int16_t *)table)[c * 256 + j] = (int16_t)q;
+            }
+        }
+    }
+}
+
+/* ImagePreprocessor::preprocess with the nearest-neighbour maps of ImageTransformer::gen_xy_map
+ * (esp-dl/vision/image/dl_image_process.cpp:488-536), the letterbox border (dl_image_preprocessor.cpp:108-131,
+ * background converted like a pixel: dl_image_process.cpp:438-474) and RGB8882RGB888
+ * (dl_image_color_rgb8882rgb888.hpp:51-63).  Host pointers. */
+int oracle_image_preprocess(const espdl_image_desc *d)
+{
+    if (!d || !d->input || !d->output || !d->lut || (d->channels != 1 && d->channels != 3))
+        return ESPDL_ERR_INVALID_ARG;
+    const int whole = d->crop_x0 == 0 && d->crop_y0 == 0 && d->crop_x1 == 0 && d->crop_y1 == 0;
+    const int x0 = whole ? 0 : d->crop_x0, y0 = whole ? 0 : d->crop_y0, x1 = whole ? d->src_w : d->crop_x1, y1 = whole ? d->src_h : d->crop_y1;
+    const int inner_w = d->dst_w - d->border_left - d->border_right, inner_h = d->dst_h - d->border_top - d->border_bottom;
+    const int src_w = x1 - x0, src_h = y1 - y0;
+    const int same = src_w == inner_w && src_h == inner_h;
+    const float isx = (float)src_w / (float)inner_w, isy = (float)src_h / (float)inner_h;
+    const int ch = d->channels, is8 = d->out_dtype == ESPDL_DTYPE_INT8;
+    for (int n = 0; n < d->n; n++)
+        for (int y = 0; y < d->dst_h; y++)
+            for (int x = 0; x < d->dst_w; x++) {
+                const int xi = x - d->border_left, yi = y - d->border_top;
+                uint8_t v[3] = {0, 0, 0};
+                if (xi < 0 || xi >= inner_w || yi < 0 || yi >= inner_h) {
+                    for (int c = 0; c < ch; c++) v[c] = d->bg[c];
+                } else {
+                    int sx = same ? xi + x0 : (int)((float)xi * isx) + x0;
+                    int sy = same ? yi + y0 : (int)((float)yi * isy) + y0;
+                    if (!same) {
+                        sx = sx < x1 - 1 ? sx : x1 - 1;
+                        sy = sy < y1 - 1 ? sy : y1 - 1;
+                    }
+                    const uint8_t *src = d->input + (((int64_t)n * d->src_h + sy) * d->src_w + sx) * ch;
+                    for (int c = 0; c < ch; c++) v[c] = src[c];
+                }
+                const int64_t o = (((int64_t)n * d->dst_h + y) * d->dst_w + x) * ch;
+                for (int c = 0; c < ch; c++) {
+                    const int sc = (ch == 3 && d->swap_rb) ? 2 - c : c;
+                    if (is8)
+                        ((int8_t *)d->output)[o + c] = ((const int8_t *)d->lut)[c * 256 + v[sc]];
+                    else
+                        ((int16_t *)d->output)[o + c] = ((const int16_t *)d->lut)[c * 256 + v[sc]];
+                }
+            }
+    return ESPDL_OK;
+}
+
 int oracle_num_threads(void)
 {
 #if defined(_OPENMP)
