@@ -110,6 +110,7 @@ public:
     size_t arena_bytes() const { return m_arena_bytes; }
     size_t num_modules() const { return m_execution_plan.size(); }
     void *stream() { return m_model_context ? m_model_context->stream : nullptr; }
+    int round_mode() const { return m_model_context ? (int)m_model_context->round_mode : 0; }
 
 protected:
     esp_err_t execute(int first, int last);

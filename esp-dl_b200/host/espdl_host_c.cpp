@@ -1,5 +1,7 @@
 // Flat C wrappers around dl::Model so that Python (tests, bench.py) can drive the C++ host layer through ctypes.
 // C++ users include dl_model_base.hpp directly; nothing here adds behaviour.
+#include "dl_cls_postprocessor.hpp"
+#include "dl_image_preprocessor.hpp"
 #include "dl_model_base.hpp"
 #include "espdl_b200.h"
 
@@ -141,6 +143,44 @@ long long espdl_model_read_tensor(void *handle, const char *name, void *dst, siz
             return st;
     }
     return (long long)t->get_bytes();
+}
+
+/// dl::cls::ClsPostprocessor on the model's first output: up to `top_k` (category, score) pairs of image `image`,
+/// best first.  Returns the number of results, -1 on error.
+int espdl_model_classify(void *handle, int image, int top_k, float score_thr, int need_softmax, int *categories, float *scores)
+{
+    Model *model = ((Handle *)handle)->model;
+    cls::ClsPostprocessor post(model, top_k, score_thr, need_softmax != 0);
+    std::vector<cls::result_t> &r = post.postprocess(image);
+    for (size_t i = 0; i < r.size(); i++) categories[i] = r[i].category, scores[i] = r[i].score;
+    return (int)r.size();
+}
+
+/// dl::image::ImagePreprocessor over `n` host images [n][h][w][channels] (uint8) into the model's first input:
+/// mean/std hold `channels` floats; crop = {x0, y0, x1, y1} or null; letterbox < 0 = off, else the background value.
+int espdl_model_preprocess(void *handle, const unsigned char *images, int n, int h, int w, int channels, const float *mean, const float *stdv,
+                           int rgb_swap, int letterbox_bg, const int *crop)
+{
+    Model *model = ((Handle *)handle)->model;
+    image::ImagePreprocessor *pre = channels == 3
+        ? new image::ImagePreprocessor(model, std::array<float, 3>{mean[0], mean[1], mean[2]}, std::array<float, 3>{stdv[0], stdv[1], stdv[2]}, rgb_swap != 0)
+        : new image::ImagePreprocessor(model, mean[0], stdv[0]);
+    if (letterbox_bg >= 0) {
+        if (channels == 3)
+            pre->enable_letterbox(std::array<uint8_t, 3>{(uint8_t)letterbox_bg, (uint8_t)letterbox_bg, (uint8_t)letterbox_bg});
+        else
+            pre->enable_letterbox((uint8_t)letterbox_bg);
+    }
+    std::vector<image::img_t> imgs;
+    for (int i = 0; i < n; i++)
+        imgs.push_back({(void *)(images + (size_t)i * h * w * channels), (uint16_t)w, (uint16_t)h,
+                        channels == 3 ? image::DL_IMAGE_PIX_TYPE_RGB888 : image::DL_IMAGE_PIX_TYPE_GRAY});
+    std::vector<int> crop_area;
+    if (crop)
+        crop_area.assign(crop, crop + 4);
+    const esp_err_t e = pre->preprocess(imgs, crop_area);
+    delete pre;
+    return e == ESP_OK ? 0 : -1;
 }
 
 /// Text dump of what the C++ reader sees in a model file (no device needed): one line per node in execution

@@ -36,6 +36,9 @@ def host_lib():
         L.espdl_model_num_modules.argtypes = [C.c_void_p]
         L.espdl_model_read_tensor.restype = C.c_longlong
         L.espdl_model_read_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]
+        L.espdl_model_preprocess.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float),
+                                             C.POINTER(C.c_float), C.c_int, C.c_int, C.POINTER(C.c_int)]
+        L.espdl_model_classify.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float)]
         L.espdl_model_profile.restype = C.c_char_p
         L.espdl_model_profile.argtypes = [C.c_void_p]
         _host = L
@@ -84,6 +87,28 @@ class Model:
     def wait(self):
         """Blocks until the oldest submitted pass is done; its results are then in the output arrays."""
         abi.check(self.lib.espdl_model_wait(self.h), "Model::wait")
+
+    def preprocess(self, images, mean, std, rgb_swap=False, letterbox=None, crop=None):
+        """dl::image::ImagePreprocessor: uint8 images [n][h][w][c] (host) -> the model's first input tensor on the device
+        (crop, nearest resize, optional letterbox with that background value, normalise + quantise).  Follow with
+        run_device(), which executes on what is resident."""
+        images = np.ascontiguousarray(images, dtype=np.uint8)
+        n, h, w, c = images.shape
+        mean = (C.c_float * 3)(*(list(np.atleast_1d(mean)) + [0, 0])[:3])
+        std = (C.c_float * 3)(*(list(np.atleast_1d(std)) + [1, 1])[:3])
+        crop_arr = (C.c_int * 4)(*crop) if crop is not None else None
+        st = self.lib.espdl_model_preprocess(self.h, images.ctypes.data, n, h, w, c, mean, std, int(rgb_swap),
+                                             -1 if letterbox is None else int(letterbox), crop_arr)
+        if st != 0:
+            raise RuntimeError("ImagePreprocessor::preprocess failed")
+
+    def classify(self, image=0, top_k=5, score_thr=0.0, need_softmax=True):
+        """dl::cls::ClsPostprocessor: [(category, score)] of one image of the batch, best first."""
+        cats, scores = (C.c_int * top_k)(), (C.c_float * top_k)()
+        n = self.lib.espdl_model_classify(self.h, image, top_k, score_thr, int(need_softmax), cats, scores)
+        if n < 0:
+            raise RuntimeError("ClsPostprocessor::postprocess failed")
+        return [(cats[i], scores[i]) for i in range(n)]
 
     def run_device(self, sync=True):
         abi.check(self.lib.espdl_model_run_device(self.h, 1 if sync else 0), "Model::run_device")

@@ -124,3 +124,45 @@ def test_gpu_matches_oracle(kw):
         abi.check(dev.lib.espdl_b200_image_preprocess(C.byref(d), None), "image_preprocess")
         got = dev.download(out, want)
     np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("letterbox,swap,crop", [(None, False, None), (114, True, None), (None, False, (40, 20, 600, 440))])
+def test_model_preprocessor_fills_the_input_tensor(tmp_path, letterbox, swap, crop):
+    """dl::image::ImagePreprocessor on a model: host images -> device conversion -> the model's input tensor; the network
+    then runs on what is resident and gives the logits of the oracle-converted input."""
+    from espdl_b200 import model, zoo, espdl_file
+    import graph_oracle
+    path = str(tmp_path / "net.espdl")
+    zoo.mobilenet_v2(seed=5, input_hw=96).save(path)
+    m = model.Model(path, batch=3)
+    name = m.inputs[0].name
+    e_in = m.inputs[0].exponent
+    imgs = np.random.default_rng(11).integers(0, 256, size=(3, 480, 640, 3), dtype=np.uint8)
+    m.preprocess(imgs, MEAN, STD, rgb_swap=swap, letterbox=letterbox, crop=crop)
+    case = dict(x=imgs, dst=(96, 96), bits=8, lut=table(3, e_in), swap=swap, crop=crop, letterbox=letterbox is not None,
+                bg=(letterbox or 0,) * 3)
+    want_in = run_oracle(case)
+    got_in = m.read_tensor(name, np.int8, want_in.shape)
+    np.testing.assert_array_equal(got_in, want_in)
+    m.run_device()
+    want = graph_oracle.run_graph(espdl_file.read(path), {name: want_in})
+    out = m.outputs[0]
+    got = m.read_tensor(out.name, np.int8, out.array.shape)
+    np.testing.assert_array_equal(got, want[out.name])
+    # dl::cls::ClsPostprocessor: softmax of the logits with the reference's exp table, threshold, sort, top-k
+    import cases
+    logits = want[out.name]
+    table_f = np.zeros(256, dtype=np.float32)
+    checkers.oracle().oracle_softmax_table(table_f.ctypes.data, out.exponent)
+    probs = np.zeros(logits.shape, dtype=np.float32)
+    assert checkers.oracle().oracle_softmax(cases.softmax_desc(logits.ctypes.data, probs.ctypes.data, table_f.ctypes.data, logits.shape[0],
+                                                               logits.shape[1], abi.DTYPE_FLOAT, 0)) == 0
+    for image in range(3):
+        top = m.classify(image=image, top_k=5, score_thr=0.0)
+        order = np.argsort(-probs[image], kind="stable")[:5]
+        assert len(top) == 5
+        np.testing.assert_array_equal(np.array([s for _, s in top], dtype=np.float32), probs[image][order])
+        for cat, score in top:
+            assert probs[image][cat] == np.float32(score)
+    m.close()
