@@ -105,6 +105,17 @@ class ImageDesc(C.Structure):
     ]
 
 
+class DetectRecord(C.Structure):
+    _fields_ = [("image", C.c_uint16), ("stage", C.c_uint16), ("y", C.c_uint16), ("x", C.c_uint16), ("category", C.c_uint16),
+                ("score", C.c_int8), ("pad", C.c_uint8), ("reserved", C.c_uint32), ("box", C.c_int8 * 64)]
+
+
+class DetectDesc(C.Structure):
+    _fields_ = [("score", C.c_void_p), ("box", C.c_void_p), ("records", C.c_void_p), ("count", C.c_void_p),
+                ("n", i32), ("h", i32), ("w", i32), ("classes", i32), ("box_channels", i32),
+                ("score_threshold", i32), ("capacity", i32), ("stage", i32)]
+
+
 # every symbol include/espdl_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "espdl_b200_init": (C.c_int, [C.c_int]),
@@ -149,6 +160,7 @@ SYMBOLS = {
     "espdl_b200_fused_block": (C.c_int, [C.POINTER(BlockDesc), C.c_void_p]),
     "espdl_b200_fused_block_supported": (C.c_int, [C.POINTER(BlockDesc)]),
     "espdl_b200_image_preprocess": (C.c_int, [C.POINTER(ImageDesc), C.c_void_p]),
+    "espdl_b200_detect_candidates": (C.c_int, [C.POINTER(DetectDesc), C.c_void_p]),
 }
 
 _lib = None

@@ -496,6 +496,13 @@ int espdl_b200_image_preprocess(const espdl_image_desc *desc, void *stream)
     return image_preprocess(*desc, (cudaStream_t)stream);
 }
 
+int espdl_b200_detect_candidates(const espdl_detect_desc *desc, void *stream)
+{
+    if (!desc)
+        return ESPDL_ERR_INVALID_ARG;
+    return detect_candidates(*desc, (cudaStream_t)stream);
+}
+
 int espdl_b200_fused_block_supported(const espdl_block_desc *desc)
 {
     if (!desc)

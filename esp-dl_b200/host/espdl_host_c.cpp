@@ -1,6 +1,7 @@
 // Flat C wrappers around dl::Model so that Python (tests, bench.py) can drive the C++ host layer through ctypes.
 // C++ users include dl_model_base.hpp directly; nothing here adds behaviour.
 #include "dl_cls_postprocessor.hpp"
+#include "dl_detect_postprocessor.hpp"
 #include "dl_image_preprocessor.hpp"
 #include "dl_model_base.hpp"
 #include "espdl_b200.h"
@@ -143,6 +144,34 @@ long long espdl_model_read_tensor(void *handle, const char *name, void *dst, siz
             return st;
     }
     return (long long)t->get_bytes();
+}
+
+/// dl::detect::yolo11PostProcessor over the outputs named names[2*i] (box) / names[2*i+1] (score) of `stages` heads with
+/// strides[i] (offset = stride / 2): results of image `image`, at most `max_results`, as rows {category, x0, y0, x1, y1}
+/// in `boxes` and scores in `scores`.  Returns the number of results, -1 on error.
+int espdl_model_detect(void *handle, int image, int stages, const char *const *names, const int *strides, float score_thr, float nms_thr,
+                       int top_k, int width, int height, int max_results, int *boxes, float *scores)
+{
+    Model *model = ((Handle *)handle)->model;
+    std::vector<detect::anchor_point_stage_t> st;
+    std::vector<std::pair<std::string, std::string>> nm;
+    for (int i = 0; i < stages; i++) {
+        st.push_back({strides[i], strides[i], strides[i] / 2, strides[i] / 2});
+        nm.push_back({names[2 * i], names[2 * i + 1]});
+    }
+    detect::yolo11PostProcessor post(model, nullptr, score_thr, nms_thr, top_k, st);
+    post.set_output_names(nm);
+    if (post.postprocess() != ESP_OK)
+        return -1;
+    int k = 0;
+    for (const detect::result_t &r : post.get_result(width, height, image)) {
+        if (k >= max_results)
+            break;
+        boxes[5 * k] = r.category;
+        for (int j = 0; j < 4; j++) boxes[5 * k + 1 + j] = r.box[j];
+        scores[k++] = r.score;
+    }
+    return k;
 }
 
 /// dl::cls::ClsPostprocessor on the model's first output: up to `top_k` (category, score) pairs of image `image`,

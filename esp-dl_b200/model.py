@@ -39,6 +39,8 @@ def host_lib():
         L.espdl_model_preprocess.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float),
                                              C.POINTER(C.c_float), C.c_int, C.c_int, C.POINTER(C.c_int)]
         L.espdl_model_classify.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float)]
+        L.espdl_model_detect.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.c_float, C.c_float, C.c_int,
+                                         C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float)]
         L.espdl_model_profile.restype = C.c_char_p
         L.espdl_model_profile.argtypes = [C.c_void_p]
         _host = L
@@ -109,6 +111,17 @@ class Model:
         if n < 0:
             raise RuntimeError("ClsPostprocessor::postprocess failed")
         return [(cats[i], scores[i]) for i in range(n)]
+
+    def detect(self, heads, strides, score_thr, nms_thr, top_k, width, height, image=0, max_results=300):
+        """dl::detect::yolo11PostProcessor: heads = [(box output name, score output name)] per stage.  Returns
+        [(category, score, (x0, y0, x1, y1))] of one image, best first."""
+        names = (C.c_char_p * (2 * len(heads)))(*[n.encode() for pair in heads for n in pair])
+        boxes, scores = (C.c_int * (5 * max_results))(), (C.c_float * max_results)()
+        n = self.lib.espdl_model_detect(self.h, image, len(heads), names, (C.c_int * len(heads))(*strides), score_thr, nms_thr, top_k,
+                                        width, height, max_results, boxes, scores)
+        if n < 0:
+            raise RuntimeError("yolo11PostProcessor::postprocess failed")
+        return [(boxes[5 * i], scores[i], tuple(boxes[5 * i + 1:5 * i + 5])) for i in range(n)]
 
     def run_device(self, sync=True):
         abi.check(self.lib.espdl_model_run_device(self.h, 1 if sync else 0), "Model::run_device")

@@ -375,6 +375,35 @@ typedef struct espdl_image_desc {
 
 int espdl_b200_image_preprocess(const espdl_image_desc *desc, void *stream);
 
+/* ---------------------------------------------------------- detection post-processing: candidate scan */
+/* The scan of dl::detect::yolo11PostProcessor::parse_stage (esp-dl/vision/detect/dl_detect_yolo11_postprocessor.cpp:
+ * 8-73) over one head: every class score above the quantised threshold becomes a candidate.  The device finds the
+ * candidates and packs, per candidate, where it was found, its score code and the box-distribution codes of its
+ * pixel; decoding (DFL integral, sigmoid), sorting and NMS are done by the caller with the reference's float
+ * arithmetic on these few records.  Records are appended at records[*count ...] (the caller zeroes *count before the
+ * first head and may call once per head); the order of the records is not defined, each carries its scan position.
+ * int8 tensors. */
+typedef struct espdl_detect_record {
+    uint16_t image, stage, y, x;
+    uint16_t category;
+    int8_t score;
+    uint8_t pad;
+    uint32_t reserved;
+    int8_t box[64];            /* the box_channels (<= 64) codes of the pixel                                     */
+} espdl_detect_record;
+
+typedef struct espdl_detect_desc {
+    const int8_t *score;       /* [n][h][w][classes]                                                              */
+    const int8_t *box;         /* [n][h][w][box_channels]                                                         */
+    espdl_detect_record *records; /* device array of `capacity` records                                           */
+    uint32_t *count;           /* device counter: records found so far (may exceed capacity: then some were dropped) */
+    int32_t n, h, w, classes, box_channels;
+    int32_t score_threshold;   /* candidates have score code > score_threshold                                    */
+    int32_t capacity, stage;
+} espdl_detect_desc;
+
+int espdl_b200_detect_candidates(const espdl_detect_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -544,6 +544,122 @@ int oracle_image_preprocess(const espdl_image_desc *d)
     return ESPDL_OK;
 }
 
+/* ---------------------------------------------------------------- detection post-processing (one image) */
+/* dl::detect::yolo11PostProcessor::parse_stage + DetectPostprocessor::nms + get_result
+ * (esp-dl/vision/detect/dl_detect_yolo11_postprocessor.cpp:8-73, dl_detect_postprocessor.cpp:5-50) with the helpers of
+ * esp-dl/dl/math/include/dl_math.hpp:200-258.  Candidates are kept in a list sorted by descending score, a new one
+ * goes behind those of equal score (std::upper_bound with greater_box). */
+typedef struct oracle_det_stage {
+    const int8_t *score; /* [h][w][classes] */
+    const int8_t *box;   /* [h][w][64] */
+    int h, w, classes;
+    int score_exponent, box_exponent;
+    int stride_y, stride_x, offset_y, offset_x;
+} oracle_det_stage;
+
+typedef struct { int category; float score; int box[4]; } det_t;
+
+static float det_sigmoid(float x) { return 1.0 / (1.0 + expf(-x)); }
+static float det_inverse_sigmoid(float x) { return -logf(1.0 / x - 1); }
+static float det_dfl_integral(float *data, int reg_max)
+{
+    float max_input = data[0];
+    for (int i = 1; i <= reg_max; i++) max_input = max_input > data[i] ? max_input : data[i];
+    float sum = 0;
+    for (int i = 0; i <= reg_max; i++) {
+        data[i] = expf(data[i] - max_input);
+        sum += data[i];
+    }
+    for (int i = 0; i <= reg_max; i++) data[i] /= sum;
+    float acc = 0;
+    for (int i = 0; i <= reg_max; i++) acc += data[i] * i;
+    return acc;
+}
+
+int oracle_yolo11_postprocess(const oracle_det_stage *stages, int n_stages, float score_thr, float nms_thr, int top_k, float inv_scale_x,
+                              float inv_scale_y, int border_left, int border_top, int width, int height, int round_mode, int max_results,
+                              int *boxes, float *scores)
+{
+    int cap = 1024, n = 0;
+    det_t *list = (det_t *)malloc(sizeof(det_t) * cap);
+    for (int s = 0; s < n_stages; s++) {
+        const oracle_det_stage *st = &stages[s];
+        const float score_exp = dl_scale(st->score_exponent), box_exp = dl_scale(st->box_exponent);
+        int thr = fround(det_inverse_sigmoid(score_thr) * (1.f / score_exp), round_mode);
+        thr = thr < -128 ? -128 : (thr > 127 ? 127 : thr);
+        const int8_t *sp = st->score, *bp = st->box;
+        for (int y = 0; y < st->h; y++)
+            for (int x = 0; x < st->w; x++, bp += 64)
+                for (int c = 0; c < st->classes; c++, sp++) {
+                    if (*sp <= (int8_t)thr)
+                        continue;
+                    const int center_y = y * st->stride_y + st->offset_y, center_x = x * st->stride_x + st->offset_x;
+                    float d[64];
+                    for (int i = 0; i < 64; i++) d[i] = (float)bp[i] * box_exp;
+                    det_t nb;
+                    nb.category = c;
+                    nb.score = det_sigmoid((float)*sp * score_exp);
+                    nb.box[0] = (int)(((center_x - det_dfl_integral(d, 15) * st->stride_x) - border_left) * inv_scale_x);
+                    nb.box[1] = (int)(((center_y - det_dfl_integral(d + 16, 15) * st->stride_y) - border_top) * inv_scale_y);
+                    nb.box[2] = (int)(((center_x + det_dfl_integral(d + 32, 15) * st->stride_x) - border_left) * inv_scale_x);
+                    nb.box[3] = (int)(((center_y + det_dfl_integral(d + 48, 15) * st->stride_y) - border_top) * inv_scale_y);
+                    int pos = 0; /* first element with a strictly lower score */
+                    while (pos < n && !(nb.score > list[pos].score)) pos++;
+                    if (n == cap) {
+                        cap *= 2;
+                        list = (det_t *)realloc(list, sizeof(det_t) * cap);
+                    }
+                    memmove(list + pos + 1, list + pos, sizeof(det_t) * (size_t)(n - pos));
+                    list[pos] = nb;
+                    n++;
+                }
+    }
+    /* nms */
+    char *dead = (char *)calloc((size_t)n + 1, 1);
+    int kept_number = 0, end = n;
+    for (int k = 0; k < end; k++) {
+        if (dead[k])
+            continue;
+        kept_number++;
+        if (kept_number >= top_k) {
+            end = k + 1;
+            break;
+        }
+        const int kept_area = (list[k].box[2] - list[k].box[0] + 1) * (list[k].box[3] - list[k].box[1] + 1);
+        for (int o = k + 1; o < end; o++) {
+            if (dead[o])
+                continue;
+            const int lx = list[k].box[0] > list[o].box[0] ? list[k].box[0] : list[o].box[0];
+            const int ly = list[k].box[1] > list[o].box[1] ? list[k].box[1] : list[o].box[1];
+            const int rx = list[k].box[2] < list[o].box[2] ? list[k].box[2] : list[o].box[2];
+            const int ry = list[k].box[3] < list[o].box[3] ? list[k].box[3] : list[o].box[3];
+            const int ih = ry - ly + 1, iw = rx - lx + 1;
+            if (ih > 0 && iw > 0) {
+                const int other_area = (list[o].box[2] - list[o].box[0] + 1) * (list[o].box[3] - list[o].box[1] + 1);
+                const int inter = ih * iw;
+                const float iou = (float)inter / (kept_area + other_area - inter);
+                if (iou > nms_thr)
+                    dead[o] = 1;
+            }
+        }
+    }
+    int out = 0;
+    for (int k = 0; k < end && out < max_results; k++) {
+        if (dead[k])
+            continue;
+        boxes[5 * out] = list[k].category;
+        for (int j = 0; j < 4; j++) {
+            const int lim = (j % 2 == 0 ? width : height) - 1;
+            const int v = list[k].box[j];
+            boxes[5 * out + 1 + j] = v < 0 ? 0 : (v > lim ? lim : v);
+        }
+        scores[out++] = list[k].score;
+    }
+    free(dead);
+    free(list);
+    return out;
+}
+
 int oracle_num_threads(void)
 {
 #if defined(_OPENMP)
