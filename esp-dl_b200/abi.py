@@ -116,6 +116,14 @@ class DetectDesc(C.Structure):
                 ("score_threshold", i32), ("capacity", i32), ("stage", i32)]
 
 
+class ReduceDesc(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("op", i32), ("dtype", i32), ("ndim", i32), ("shape", i32 * 6),
+                ("reduce", i32 * 6), ("in_exponent", i32), ("out_exponent", i32), ("round_mode", i32)]
+
+
+REDUCE_MEAN, REDUCE_SUM, REDUCE_MAX, REDUCE_MIN = range(4)
+
+
 # every symbol include/espdl_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "espdl_b200_init": (C.c_int, [C.c_int]),
@@ -161,6 +169,7 @@ SYMBOLS = {
     "espdl_b200_fused_block_supported": (C.c_int, [C.POINTER(BlockDesc)]),
     "espdl_b200_image_preprocess": (C.c_int, [C.POINTER(ImageDesc), C.c_void_p]),
     "espdl_b200_detect_candidates": (C.c_int, [C.POINTER(DetectDesc), C.c_void_p]),
+    "espdl_b200_reduce": (C.c_int, [C.POINTER(ReduceDesc), C.c_void_p]),
 }
 
 _lib = None

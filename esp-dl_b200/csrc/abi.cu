@@ -503,6 +503,13 @@ int espdl_b200_detect_candidates(const espdl_detect_desc *desc, void *stream)
     return detect_candidates(*desc, (cudaStream_t)stream);
 }
 
+int espdl_b200_reduce(const espdl_reduce_desc *desc, void *stream)
+{
+    if (!desc)
+        return ESPDL_ERR_INVALID_ARG;
+    return reduce_op(*desc, (cudaStream_t)stream);
+}
+
 int espdl_b200_fused_block_supported(const espdl_block_desc *desc)
 {
     if (!desc)

@@ -1,0 +1,113 @@
+// Reductions over any set of axes of an int8 / int16 tensor: ReduceMean, ReduceSum, ReduceMax, ReduceMin.
+// Replaces dl::module::ReduceBase::forward_template and the reduce functions of the modules built on it
+// (esp-dl/dl/module/include/dl_module_reduce_base.hpp:121-262, dl_module_reduce_mean.hpp:17-45, dl_module_reduce_sum.hpp:
+// 17-42).  A thread owns one output element and walks the reduced axes; with channels innermost and kept (the usual
+// spatial mean of an NHWC map) neighbouring threads read neighbouring bytes.  Integer sums are exact, so the order
+// of the walk does not matter; the mean's fp32 expression is evaluated in the reference's order.
+#include "common.cuh"
+
+namespace espdl {
+
+namespace {
+
+struct ReduceParams {
+    const void *in;
+    void *out;
+    int op, half_even, e_in, e_out;
+    int nk, nr;            // kept / reduced axes
+    int ksize[6], rsize[6];
+    long long kstride[6], rstride[6];
+    long long outputs, count;
+};
+
+template <typename T, typename ACC>
+__global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
+{
+    const T *in = (const T *)p.in;
+    T *out = (T *)p.out;
+    const int lo = sizeof(T) == 1 ? -128 : -32768, hi = sizeof(T) == 1 ? 127 : 32767;
+    for (long long o = blockIdx.x * (long long)blockDim.x + threadIdx.x; o < p.outputs; o += (long long)gridDim.x * blockDim.x) {
+        long long base = 0, rem = o;
+        for (int k = p.nk - 1; k >= 0; k--) {
+            base += (rem % p.ksize[k]) * p.kstride[k];
+            rem /= p.ksize[k];
+        }
+        int idx[6] = {0, 0, 0, 0, 0, 0};
+        long long off = base;
+        ACC acc = p.op == ESPDL_REDUCE_MAX ? (ACC)lo : (p.op == ESPDL_REDUCE_MIN ? (ACC)hi : (ACC)0);
+        for (long long i = 0; i < p.count; i++) {
+            const ACC v = (ACC)in[off];
+            if (p.op == ESPDL_REDUCE_MAX)
+                acc = acc > v ? acc : v;
+            else if (p.op == ESPDL_REDUCE_MIN)
+                acc = acc < v ? acc : v;
+            else
+                acc += v;
+            for (int r = p.nr - 1; r >= 0; r--) { // odometer over the reduced axes
+                off += p.rstride[r];
+                if (++idx[r] < p.rsize[r])
+                    break;
+                off -= (long long)p.rsize[r] * p.rstride[r];
+                idx[r] = 0;
+            }
+        }
+        long long q;
+        if (p.op == ESPDL_REDUCE_MEAN) {
+            // tool::round(tmp * input_scale / count * output_scale), all in fp32
+            float f = __fmul_rn((float)acc, dl_scale(p.e_in));
+            f = __fdiv_rn(f, (float)(unsigned long long)p.count);
+            f = __fmul_rn(f, dl_rescale(p.e_out));
+            q = fround(f, p.half_even);
+        } else if (p.op == ESPDL_REDUCE_SUM) {
+            const int shift = max(-62, min(62, p.e_out - p.e_in));
+            q = sizeof(ACC) == 4 ? (long long)shift_round32((int32_t)acc, max(-31, min(31, shift)), p.half_even)
+                                 : shift_round64((long long)acc, shift, p.half_even);
+        } else {
+            q = (long long)acc;
+        }
+        out[o] = (T)max((long long)lo, min((long long)hi, q));
+    }
+}
+
+} // namespace
+
+int reduce_op(const espdl_reduce_desc &d, cudaStream_t s)
+{
+    if (!d.input || !d.output || d.ndim < 1 || d.ndim > 6 || d.op < 0 || d.op > 3)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d.dtype != ESPDL_DTYPE_INT8 && d.dtype != ESPDL_DTYPE_INT16)
+        return ESPDL_ERR_UNSUPPORTED;
+    ReduceParams p;
+    p.in = d.input, p.out = d.output, p.op = d.op, p.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
+    p.e_in = d.in_exponent, p.e_out = d.out_exponent;
+    p.nk = p.nr = 0, p.outputs = 1, p.count = 1;
+    long long stride = 1;
+    long long strides[6];
+    for (int i = d.ndim - 1; i >= 0; i--) {
+        if (d.shape[i] <= 0)
+            return ESPDL_ERR_INVALID_ARG;
+        strides[i] = stride;
+        stride *= d.shape[i];
+    }
+    for (int i = 0; i < d.ndim; i++) {
+        if (d.reduce[i]) {
+            p.rsize[p.nr] = d.shape[i], p.rstride[p.nr] = strides[i], p.nr++;
+            p.count *= d.shape[i];
+        } else {
+            p.ksize[p.nk] = d.shape[i], p.kstride[p.nk] = strides[i], p.nk++;
+            p.outputs *= d.shape[i];
+        }
+    }
+    if (abs(p.e_in) > 30 || abs(p.e_out) > 30)
+        return ESPDL_ERR_UNSUPPORTED;
+    const long long blocks = (p.outputs + 255) / 256;
+    const int grid = (int)(blocks < (long long)num_sms() * 8 ? blocks : (long long)num_sms() * 8);
+    if (d.dtype == ESPDL_DTYPE_INT8)
+        reduce_kernel<int8_t, int32_t><<<grid, 256, 0, s>>>(p);
+    else
+        reduce_kernel<int16_t, long long><<<grid, 256, 0, s>>>(p);
+    count_launch();
+    return check_launch("reduce");
+}
+
+} // namespace espdl

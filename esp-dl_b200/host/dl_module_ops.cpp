@@ -1199,6 +1199,167 @@ Module *Split::deserialize(fbs::FbsModel *m, std::string node)
     return new Split(m->get_operation_parameter(node, 1), axis, num_outputs, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
 }
 
+// --------------------------------------------------------------------------------- Reduce / Slice
+std::vector<std::vector<int>> Reduce::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    // dl_module_reduce_base.hpp:43-70
+    const std::vector<int> &in = input_shapes[0];
+    std::vector<int> out;
+    size_t reduced = 0;
+    for (size_t i = 0; i < in.size(); i++) {
+        if (i < m_axes_reduce_flag.size() && m_axes_reduce_flag[i]) {
+            reduced++;
+            if (m_keepdims)
+                out.push_back(1);
+        } else {
+            out.push_back(in[i]);
+        }
+    }
+    if (!m_keepdims && reduced == in.size())
+        out = {1};
+    return {out};
+}
+
+void Reduce::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = ESPDL_OK;
+    espdl_reduce_desc d;
+    memset(&d, 0, sizeof(d));
+    if (!in || !out || !in->device || !out->device || in->shape.size() > 6 || in->shape.empty()) {
+        st = ESPDL_ERR_INVALID_ARG;
+    } else {
+        d.input = in->device, d.output = out->device, d.op = m_op, d.dtype = quant_dtype(quant_type), d.ndim = (int)in->shape.size();
+        for (size_t i = 0; i < in->shape.size(); i++) d.shape[i] = in->shape[i], d.reduce[i] = i < m_axes_reduce_flag.size() && m_axes_reduce_flag[i];
+        d.in_exponent = in->exponent, d.out_exponent = out->exponent, d.round_mode = context->round_mode;
+        st = espdl_b200_reduce(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Reduce", "%s failed: %s %s", name ? name : "?", espdl_b200_strerror(st), espdl_b200_last_error());
+    context->note(st);
+}
+
+Module *Reduce::deserialize(fbs::FbsModel *m, std::string node)
+{
+    // ReduceBase::get_attributes, dl_module_reduce_base.hpp:265-298
+    const std::string type = m->get_operation_type(node);
+    int op = type == "ReduceMean" ? ESPDL_REDUCE_MEAN : (type == "ReduceSum" ? ESPDL_REDUCE_SUM : (type == "ReduceMax" ? ESPDL_REDUCE_MAX : ESPDL_REDUCE_MIN));
+    int keepdims = 1, noop = 0;
+    m->get_operation_attribute(node, "keepdims", keepdims);
+    m->get_operation_attribute(node, "noop_with_empty_axes", noop);
+    std::vector<std::string> ins, outs;
+    m->get_operation_inputs_and_outputs(node, ins, outs);
+    const std::vector<int> in_shape = ins.empty() ? std::vector<int>() : m->get_value_info_shape(ins[0]);
+    std::vector<bool> flags(in_shape.size(), false);
+    TensorBase *axes = m->get_operation_parameter(node, 1);
+    if (axes && axes->get_size() > 0) {
+        for (int i = 0; i < axes->get_size(); i++) {
+            int a = axes->dtype == DATA_TYPE_INT64 ? (int)axes->get_element<int64_t>(i) : axes->get_element<int32_t>(i);
+            if (a < 0)
+                a += (int)in_shape.size();
+            if (a >= 0 && a < (int)flags.size())
+                flags[a] = true;
+        }
+    } else if (!noop) {
+        std::fill(flags.begin(), flags.end(), true);
+    }
+    delete axes;
+    const quant_type_t q = node_quant(m, node);
+    if (q != QUANT_TYPE_SYMM_8BIT && q != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    return new Reduce(op, keepdims, flags, node.c_str(), q);
+}
+
+bool Slice::resolve(const std::vector<int> &shape, std::vector<int> &first, std::vector<int> &count, std::vector<int> &step) const
+{
+    // get_slice_shape / _slice: dl_base_shape.cpp:68-120, dl_tensor_base.cpp:1049-1100 (positive steps)
+    const int dims = (int)shape.size();
+    first.assign(dims, 0), step.assign(dims, 1);
+    count = shape;
+    for (size_t i = 0; i < m_start.size(); i++) {
+        int axis = (int)i;
+        if (!m_axes.empty())
+            axis = (m_axes[i] + dims) % dims;
+        const int st = m_step.empty() ? 1 : m_step[i];
+        if (st <= 0 || axis < 0 || axis >= dims)
+            return false;
+        int s0 = m_start[i], e0 = m_end[i];
+        if (e0 > shape[axis])
+            e0 = shape[axis];
+        else if (e0 < 0)
+            e0 += shape[axis];
+        if (s0 > shape[axis])
+            s0 = shape[axis];
+        else if (s0 < 0)
+            s0 += shape[axis];
+        if (s0 < 0 || s0 >= e0)
+            return false;
+        first[axis] = s0, step[axis] = st, count[axis] = 1 + (e0 - s0 - 1) / st;
+    }
+    return true;
+}
+
+std::vector<std::vector<int>> Slice::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> first, count, step;
+    if (!resolve(input_shapes[0], first, count, step))
+        return {{}};
+    return {count};
+}
+
+void Slice::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = ESPDL_OK;
+    std::vector<int> first, count, step;
+    if (!in || !out || !in->device || !out->device || !resolve(in->shape, first, count, step)) {
+        st = ESPDL_ERR_INVALID_ARG;
+    } else {
+        const int es = (int)dtype_sizeof(in->dtype);
+        std::vector<long long> is = dense_strides(in->shape);
+        long long offset = 0;
+        for (size_t i = 0; i < is.size(); i++) {
+            offset += (long long)first[i] * is[i];
+            is[i] *= step[i];
+        }
+        st = enqueue_copy(context, (char *)in->device + offset * es, out->device, es, count, is, dense_strides(count));
+    }
+    if (st)
+        ESP_LOGE("Slice", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *Slice::deserialize(fbs::FbsModel *m, std::string node)
+{
+    // dl_module_slice.hpp:58-121; negative steps (the reference flips those axes) are not taken
+    TensorBase *p[4] = {m->get_operation_parameter(node, 1), m->get_operation_parameter(node, 2), m->get_operation_parameter(node, 3),
+                        m->get_operation_parameter(node, 4)};
+    std::vector<int> v[4];
+    bool ok = p[0] && p[1];
+    for (int k = 0; k < 4 && ok; k++) {
+        if (!p[k])
+            continue;
+        for (int i = 0; i < p[k]->get_size(); i++) {
+            long long x = p[k]->dtype == DATA_TYPE_INT64 ? (long long)p[k]->get_element<int64_t>(i) : (long long)p[k]->get_element<int32_t>(i);
+            x = x > INT32_MAX ? INT32_MAX : (x < INT32_MIN ? INT32_MIN : x); // tool::truncate
+            v[k].push_back((int)x);
+        }
+    }
+    for (int k = 0; k < 4; k++) delete p[k];
+    for (int s : v[3])
+        if (s <= 0)
+            ok = false;
+    if (!ok) {
+        ESP_LOGE("Slice", "%s: missing bounds or a step that is not positive", node.c_str());
+        return nullptr;
+    }
+    return new Slice(v[0], v[1], v[2], v[3], node.c_str(), node_quant(m, node));
+}
+
 std::vector<std::vector<int>> Transpose::get_output_shape(std::vector<std::vector<int>> &input_shapes)
 {
     std::vector<int> in = input_shapes[0], out(in.size());
@@ -1414,6 +1575,8 @@ void ModuleCreator::register_dl_modules()
     for (const char *op : {"LUT", "Swish", "Sigmoid", "Tanh", "HardSwish", "HardSigmoid", "Gelu", "Elu", "LeakyRelu", "Exp", "Log", "Sqrt",
                            "Neg", "Abs"})
         register_module(op, LUT::deserialize);
+    for (const char *op : {"ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin"}) register_module(op, Reduce::deserialize);
+    register_module("Slice", Slice::deserialize);
     register_module("Clip", Clip::deserialize);
     register_module("Relu", Relu::deserialize);
     register_module("PRelu", PRelu::deserialize);

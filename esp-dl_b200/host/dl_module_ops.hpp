@@ -255,6 +255,40 @@ protected:
     std::vector<int> m_split;
     int m_axis, m_num_outputs;
 };
+/// ReduceMean / ReduceSum / ReduceMax / ReduceMin (reference: dl_module_reduce_base.hpp:15-262 and the modules built on it).
+class Reduce : public Module {
+public:
+    Reduce(int op, int keepdims, std::vector<bool> axes_reduce_flag, const char *name = nullptr, quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, MODULE_NON_INPLACE, quant_type), m_op(op), m_keepdims(keepdims), m_axes_reduce_flag(axes_reduce_flag)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int m_op, m_keepdims;
+    std::vector<bool> m_axes_reduce_flag;
+};
+
+/// Slice with positive steps (reference: dl_module_slice.hpp:10-128, TensorBase::slice); a strided device copy.
+class Slice : public Module {
+public:
+    Slice(std::vector<int> start, std::vector<int> end, std::vector<int> axes = {}, std::vector<int> step = {}, const char *name = nullptr,
+          quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, MODULE_NON_INPLACE, quant_type), m_start(start), m_end(end), m_axes(axes), m_step(step)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    /// per input axis: first index, count, step (after the reference's normalisation of negative and oversized bounds)
+    bool resolve(const std::vector<int> &shape, std::vector<int> &first, std::vector<int> &count, std::vector<int> &step) const;
+    std::vector<int> m_start, m_end, m_axes, m_step;
+};
+
 class Transpose : public Module {
 public:
     Transpose(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE,

@@ -404,6 +404,24 @@ typedef struct espdl_detect_desc {
 
 int espdl_b200_detect_candidates(const espdl_detect_desc *desc, void *stream);
 
+/* ---------------------------------------------------------- reductions */
+/* ReduceMean / ReduceSum / ReduceMax / ReduceMin over any set of axes (esp-dl/dl/module/include/dl_module_reduce_base.hpp:
+ * 121-262 with dl_module_reduce_mean.hpp:17-45, dl_module_reduce_sum.hpp:17-42, dl_module_reduce_max.hpp, _min.hpp).
+ * int8 sums in int32, int16 sums in int64.  Mean: round(sum * 2^e_in / count * 2^-e_out) in fp32, in that order;
+ * sum: shift_and_round(sum, e_out - e_in); max/min: the code itself.  All saturate to the output type. */
+typedef enum { ESPDL_REDUCE_MEAN = 0, ESPDL_REDUCE_SUM = 1, ESPDL_REDUCE_MAX = 2, ESPDL_REDUCE_MIN = 3 } espdl_reduce_op_t;
+
+typedef struct espdl_reduce_desc {
+    const void *input;
+    void *output;            /* the kept dims in their order (keepdims only changes the declared shape)  */
+    int32_t op, dtype, ndim; /* ndim <= 6                                                                 */
+    int32_t shape[6];
+    int32_t reduce[6];       /* 1 = this axis is reduced                                                  */
+    int32_t in_exponent, out_exponent, round_mode;
+} espdl_reduce_desc;
+
+int espdl_b200_reduce(const espdl_reduce_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

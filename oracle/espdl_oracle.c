@@ -660,6 +660,64 @@ int oracle_yolo11_postprocess(const oracle_det_stage *stages, int n_stages, floa
     return out;
 }
 
+/* ---------------------------------------------------------------- reductions */
+/* ReduceBase::forward_template with ReduceMean / ReduceSum / ReduceMax / ReduceMin::reduce
+ * (esp-dl/dl/module/include/dl_module_reduce_base.hpp:121-262, dl_module_reduce_mean.hpp:17-45,
+ * dl_module_reduce_sum.hpp:17-42, dl_module_reduce_max.hpp:12-37, dl_module_reduce_min.hpp:13-38). */
+int oracle_reduce(const espdl_reduce_desc *d)
+{
+    if (!d || !d->input || !d->output || d->ndim < 1 || d->ndim > 6)
+        return ESPDL_ERR_INVALID_ARG;
+    const int is8 = d->dtype == ESPDL_DTYPE_INT8;
+    int64_t strides[6], total = 1, count = 1;
+    for (int i = d->ndim - 1; i >= 0; i--) {
+        strides[i] = total;
+        total *= d->shape[i];
+    }
+    for (int i = 0; i < d->ndim; i++)
+        if (d->reduce[i])
+            count *= d->shape[i];
+    const int64_t outputs = total / count;
+    const int64_t lo = is8 ? -128 : -32768, hi = is8 ? 127 : 32767;
+    for (int64_t o = 0; o < outputs; o++) {
+        int64_t base = 0, rem = o;
+        for (int i = d->ndim - 1; i >= 0; i--)
+            if (!d->reduce[i]) {
+                base += (rem % d->shape[i]) * strides[i];
+                rem /= d->shape[i];
+            }
+        int64_t acc = d->op == ESPDL_REDUCE_MAX ? lo : (d->op == ESPDL_REDUCE_MIN ? hi : 0);
+        for (int64_t r = 0; r < count; r++) {
+            int64_t off = base, rr = r;
+            for (int i = d->ndim - 1; i >= 0; i--)
+                if (d->reduce[i]) {
+                    off += (rr % d->shape[i]) * strides[i];
+                    rr /= d->shape[i];
+                }
+            const int64_t v = load_int(d->input, d->dtype, off);
+            if (d->op == ESPDL_REDUCE_MAX)
+                acc = acc > v ? acc : v;
+            else if (d->op == ESPDL_REDUCE_MIN)
+                acc = acc < v ? acc : v;
+            else
+                acc += v;
+        }
+        int64_t q = acc;
+        if (d->op == ESPDL_REDUCE_MEAN) {
+            /* tool::round(tmp * input_scale / count * output_scale): the sum is an int32 (int8) or int64 (int16) */
+            float f = is8 ? (float)(int32_t)acc : (float)acc;
+            f = f * dl_scale(d->in_exponent);
+            f = f / (float)(size_t)count;
+            f = f * dl_rescale(d->out_exponent);
+            q = fround(f, d->round_mode);
+        } else if (d->op == ESPDL_REDUCE_SUM) {
+            q = shift_and_round(acc, d->out_exponent - d->in_exponent, d->round_mode, is8 ? 32 : 64);
+        }
+        store_sat(d->output, d->dtype, o, q);
+    }
+    return ESPDL_OK;
+}
+
 int oracle_num_threads(void)
 {
 #if defined(_OPENMP)

@@ -32,6 +32,10 @@
 #include "dl_module_max_pool.hpp"
 #include "dl_module_mul.hpp"
 #include "dl_module_prelu.hpp"
+#include "dl_module_reduce_max.hpp"
+#include "dl_module_reduce_mean.hpp"
+#include "dl_module_reduce_min.hpp"
+#include "dl_module_reduce_sum.hpp"
 #include "dl_module_relu.hpp"
 #include "dl_module_requantize_linear.hpp"
 #include "dl_module_resize.hpp"
@@ -266,6 +270,29 @@ int ref_matmul(const void *a, const int *shape_a, int ndim_a, int e_a, const voi
     std::vector<int> so = m.get_output_shape(in_shapes)[0];
     std::unique_ptr<TensorBase> ta(view(sa, a, e_a, dtype)), tb(view(sb, b, e_b, dtype)), to(view(so, out, e_out, dtype));
     m.run({ta.get(), tb.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* ReduceMean / ReduceSum / ReduceMax / ReduceMin through the reference's own modules (dl_module_reduce_*.hpp). */
+int ref_reduce(const espdl_reduce_desc *d)
+{
+    std::vector<int> shape(d->shape, d->shape + d->ndim);
+    std::vector<bool> flags;
+    for (int i = 0; i < d->ndim; i++) flags.push_back(d->reduce[i] != 0);
+    std::unique_ptr<module::Module> m;
+    const quant_type_t q = to_quant(d->dtype);
+    if (d->op == ESPDL_REDUCE_MEAN)
+        m.reset(new module::ReduceMean(1, flags, "ReduceMean", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_SUM)
+        m.reset(new module::ReduceSum(1, flags, "ReduceSum", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_MAX)
+        m.reset(new module::ReduceMax(1, flags, "ReduceMax", "reduce", MODULE_NON_INPLACE, q));
+    else
+        m.reset(new module::ReduceMin(1, flags, "ReduceMin", "reduce", MODULE_NON_INPLACE, q));
+    std::vector<std::vector<int>> in_shapes = {shape};
+    std::vector<int> so = m->get_output_shape(in_shapes)[0];
+    std::unique_ptr<TensorBase> ti(view(shape, d->input, d->in_exponent, d->dtype)), to(view(so, d->output, d->out_exponent, d->dtype));
+    m->run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
     return 0;
 }
 

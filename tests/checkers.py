@@ -23,7 +23,8 @@ def oracle():
             subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "oracle"], stdout=subprocess.DEVNULL)
         lib = C.CDLL(ORACLE_SO)
         for name, desc in [("oracle_conv2d", abi.ConvDesc), ("oracle_eltwise", abi.EltwiseDesc), ("oracle_pool", abi.PoolDesc),
-                           ("oracle_resize", abi.ResizeDesc), ("oracle_copy", abi.CopyDesc), ("oracle_softmax", abi.SoftmaxDesc)]:
+                           ("oracle_resize", abi.ResizeDesc), ("oracle_copy", abi.CopyDesc), ("oracle_softmax", abi.SoftmaxDesc),
+                           ("oracle_reduce", abi.ReduceDesc)]:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(desc)]
@@ -55,6 +56,8 @@ def ref():
         lib.ref_matmul.restype = C.c_int
         lib.ref_matmul.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p,
                                    C.c_int, C.c_int, C.c_int]
+        lib.ref_reduce.restype = C.c_int
+        lib.ref_reduce.argtypes = [C.POINTER(abi.ReduceDesc)]
         lib.ref_num_threads.restype = C.c_int
         _ref = lib
     return _ref

@@ -2,6 +2,8 @@
 
 Batch N is executed the way a caller of the reference has to: every conv / pool / resize node is applied to
 each image independently (the oracle's batch loop), Gemm folds the leading dims into rows."""
+import ctypes as C
+
 import numpy as np
 
 import cases
@@ -202,6 +204,29 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
         elif op == "MatMul":
             t[outs[0]] = matmul(o, x, t[ins[1]], exps[ins[0]], exps[ins[1]], exps[outs[0]], QDT[at["quant_type"]],
                                 ACT[at.get("activation", "Linear")], round_mode)
+        elif op in ("ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin"):
+            axes = [int(a) % x.ndim for a in init[ins[1]]["data"]] if len(ins) > 1 and ins[1] in init else list(range(x.ndim))
+            d = abi.ReduceDesc()
+            d.op = {"ReduceMean": abi.REDUCE_MEAN, "ReduceSum": abi.REDUCE_SUM, "ReduceMax": abi.REDUCE_MAX, "ReduceMin": abi.REDUCE_MIN}[op]
+            d.dtype, d.ndim = QDT[at["quant_type"]], x.ndim
+            for i, sz in enumerate(x.shape):
+                d.shape[i], d.reduce[i] = sz, int(i in axes)
+            d.in_exponent, d.out_exponent, d.round_mode = exps[ins[0]], exps[outs[0]], round_mode
+            keep = at.get("keepdims", 1)
+            shape = [1 if i in axes else sz for i, sz in enumerate(x.shape)] if keep else ([sz for i, sz in enumerate(x.shape) if i not in axes] or [1])
+            y = np.zeros(shape, dtype=x.dtype)
+            xc = np.ascontiguousarray(x)
+            d.input, d.output = xc.ctypes.data, y.ctypes.data
+            assert o.oracle_reduce(C.byref(d)) == 0
+            t[outs[0]] = y
+        elif op == "Slice":
+            starts, ends = [int(v) for v in init[ins[1]]["data"]], [int(v) for v in init[ins[2]]["data"]]
+            axes = [int(v) for v in init[ins[3]]["data"]] if len(ins) > 3 else list(range(len(starts)))
+            steps = [int(v) for v in init[ins[4]]["data"]] if len(ins) > 4 else [1] * len(starts)
+            idx = [slice(None)] * x.ndim
+            for s0, e0, a, st in zip(starts, ends, axes, steps):
+                idx[a % x.ndim] = slice(s0, min(e0, x.shape[a % x.ndim]) if e0 >= 0 else e0, st)   # ONNX Slice = numpy slicing for st > 0
+            t[outs[0]] = np.ascontiguousarray(x[tuple(idx)])
         else:
             raise NotImplementedError(op)
     return t
