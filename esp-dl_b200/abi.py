@@ -124,6 +124,14 @@ class ReduceDesc(C.Structure):
 REDUCE_MEAN, REDUCE_SUM, REDUCE_MAX, REDUCE_MIN = range(4)
 
 
+class PadDesc(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("elem_size", i32), ("ndim", i32), ("mode", i32), ("shape", i32 * 6),
+                ("pad_begin", i32 * 6), ("pad_end", i32 * 6), ("constant", C.c_int64)]
+
+
+PAD_CONSTANT, PAD_EDGE, PAD_REFLECT = range(3)
+
+
 # every symbol include/espdl_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "espdl_b200_init": (C.c_int, [C.c_int]),
@@ -170,6 +178,7 @@ SYMBOLS = {
     "espdl_b200_image_preprocess": (C.c_int, [C.POINTER(ImageDesc), C.c_void_p]),
     "espdl_b200_detect_candidates": (C.c_int, [C.POINTER(DetectDesc), C.c_void_p]),
     "espdl_b200_reduce": (C.c_int, [C.POINTER(ReduceDesc), C.c_void_p]),
+    "espdl_b200_pad": (C.c_int, [C.POINTER(PadDesc), C.c_void_p]),
 }
 
 _lib = None

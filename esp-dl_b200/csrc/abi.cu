@@ -510,6 +510,13 @@ int espdl_b200_reduce(const espdl_reduce_desc *desc, void *stream)
     return reduce_op(*desc, (cudaStream_t)stream);
 }
 
+int espdl_b200_pad(const espdl_pad_desc *desc, void *stream)
+{
+    if (!desc)
+        return ESPDL_ERR_INVALID_ARG;
+    return pad_op(*desc, (cudaStream_t)stream);
+}
+
 int espdl_b200_fused_block_supported(const espdl_block_desc *desc)
 {
     if (!desc)

@@ -39,6 +39,7 @@ int read_and_clear_device_error_block();
 int image_preprocess(const espdl_image_desc &d, cudaStream_t s);
 int detect_candidates(const espdl_detect_desc &d, cudaStream_t s);
 int reduce_op(const espdl_reduce_desc &d, cudaStream_t s);
+int pad_op(const espdl_pad_desc &d, cudaStream_t s);
 bool fused_block_supported(const espdl_block_desc &d);
 int fused_block_tc(const espdl_block_desc &d, cudaStream_t s);
 bool conv2d_conv_tc_supported(const espdl_conv_desc &d);

@@ -110,4 +110,79 @@ int reduce_op(const espdl_reduce_desc &d, cudaStream_t s)
     return check_launch("reduce");
 }
 
+
+// ------------------------------------------------------------------------------------------ Pad
+// dl::module::Pad (esp-dl/dl/module/include/dl_module_pad.hpp:10-100; per-axis rules of esp-dl/dl/base/dl_base_pad.cpp:18-66).
+namespace {
+
+struct PadParams {
+    const void *in;
+    void *out;
+    int ndim, mode;
+    int ishape[6], oshape[6], begin[6];
+    long long istride[6];
+    long long total;
+    long long constant;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) pad_kernel(PadParams p)
+{
+    const T *in = (const T *)p.in;
+    T *out = (T *)p.out;
+    for (long long o = blockIdx.x * (long long)blockDim.x + threadIdx.x; o < p.total; o += (long long)gridDim.x * blockDim.x) {
+        long long rem = o, off = 0;
+        bool inside = true;
+        for (int k = p.ndim - 1; k >= 0; k--) {
+            int i = (int)(rem % p.oshape[k]) - p.begin[k];
+            rem /= p.oshape[k];
+            const int n = p.ishape[k];
+            if (i < 0 || i >= n) {
+                if (p.mode == ESPDL_PAD_CONSTANT)
+                    inside = false;
+                else if (p.mode == ESPDL_PAD_EDGE)
+                    i = i < 0 ? 0 : n - 1;
+                else
+                    i = i < 0 ? -i : 2 * (n - 1) - i; // mirror, the edge element is not repeated
+                i = max(0, min(n - 1, i));
+            }
+            off += (long long)i * p.istride[k];
+        }
+        out[o] = inside ? in[off] : (T)p.constant;
+    }
+}
+
+} // namespace
+
+int pad_op(const espdl_pad_desc &d, cudaStream_t s)
+{
+    if (!d.input || !d.output || d.ndim < 1 || d.ndim > 6 || d.mode < 0 || d.mode > 2)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d.elem_size != 1 && d.elem_size != 2 && d.elem_size != 4)
+        return ESPDL_ERR_UNSUPPORTED;
+    PadParams p;
+    p.in = d.input, p.out = d.output, p.ndim = d.ndim, p.mode = d.mode, p.constant = d.constant, p.total = 1;
+    long long stride = 1;
+    for (int i = d.ndim - 1; i >= 0; i--) {
+        if (d.shape[i] <= 0 || d.pad_begin[i] < 0 || d.pad_end[i] < 0)
+            return ESPDL_ERR_INVALID_ARG;
+        if (d.mode == ESPDL_PAD_REFLECT && (d.pad_begin[i] >= d.shape[i] || d.pad_end[i] >= d.shape[i]))
+            return ESPDL_ERR_INVALID_ARG;
+        p.ishape[i] = d.shape[i], p.begin[i] = d.pad_begin[i], p.oshape[i] = d.shape[i] + d.pad_begin[i] + d.pad_end[i];
+        p.istride[i] = stride;
+        stride *= d.shape[i];
+        p.total *= p.oshape[i];
+    }
+    const long long blocks = (p.total + 255) / 256;
+    const int grid = (int)(blocks < (long long)num_sms() * 16 ? blocks : (long long)num_sms() * 16);
+    if (d.elem_size == 1)
+        pad_kernel<int8_t><<<grid, 256, 0, s>>>(p);
+    else if (d.elem_size == 2)
+        pad_kernel<int16_t><<<grid, 256, 0, s>>>(p);
+    else
+        pad_kernel<int32_t><<<grid, 256, 0, s>>>(p);
+    count_launch();
+    return check_launch("pad");
+}
+
 } // namespace espdl

@@ -1360,6 +1360,59 @@ Module *Slice::deserialize(fbs::FbsModel *m, std::string node)
     return new Slice(v[0], v[1], v[2], v[3], node.c_str(), node_quant(m, node));
 }
 
+std::vector<std::vector<int>> Pad::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> out = input_shapes[0];
+    const size_t n = out.size();
+    for (size_t i = 0; i < n && n + i < m_pads.size(); i++) out[i] += m_pads[i] + m_pads[n + i];
+    return {out};
+}
+
+void Pad::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = ESPDL_OK;
+    espdl_pad_desc d;
+    memset(&d, 0, sizeof(d));
+    const size_t n = in ? in->shape.size() : 0;
+    if (!in || !out || !in->device || !out->device || n == 0 || n > 6 || m_pads.size() != 2 * n) {
+        st = ESPDL_ERR_INVALID_ARG;
+    } else {
+        d.input = in->device, d.output = out->device, d.elem_size = (int)dtype_sizeof(in->dtype), d.ndim = (int)n, d.mode = m_mode;
+        for (size_t i = 0; i < n; i++) d.shape[i] = in->shape[i], d.pad_begin[i] = m_pads[i], d.pad_end[i] = m_pads[n + i];
+        d.constant = m_constant;
+        st = espdl_b200_pad(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Pad", "%s failed: %s %s", name ? name : "?", espdl_b200_strerror(st), espdl_b200_last_error());
+    context->note(st);
+}
+
+Module *Pad::deserialize(fbs::FbsModel *m, std::string node)
+{
+    std::string mode = "constant";
+    m->get_operation_attribute(node, "mode", mode);
+    const int pm = mode == "constant" ? ESPDL_PAD_CONSTANT : (mode == "edge" ? ESPDL_PAD_EDGE : (mode == "reflect" ? ESPDL_PAD_REFLECT : -1));
+    TensorBase *pads = m->get_operation_parameter(node, 1);
+    TensorBase *cv = m->get_operation_parameter(node, 2);
+    if (pm < 0 || !pads || pads->dtype != DATA_TYPE_INT64) {
+        ESP_LOGE("Pad", "%s: mode %s or pads are not supported", node.c_str(), mode.c_str());
+        delete pads;
+        delete cv;
+        return nullptr;
+    }
+    std::vector<int> p;
+    for (int i = 0; i < pads->get_size(); i++) p.push_back((int)pads->get_element<int64_t>(i));
+    long long c = 0;
+    if (cv && cv->get_size() > 0)
+        c = cv->dtype == DATA_TYPE_INT8 ? cv->get_element<int8_t>(0) : (cv->dtype == DATA_TYPE_INT16 ? cv->get_element<int16_t>(0) : 0);
+    delete pads;
+    delete cv;
+    return new Pad(p, pm, c, node.c_str(), node_quant(m, node));
+}
+
 std::vector<std::vector<int>> Transpose::get_output_shape(std::vector<std::vector<int>> &input_shapes)
 {
     std::vector<int> in = input_shapes[0], out(in.size());
@@ -1577,6 +1630,7 @@ void ModuleCreator::register_dl_modules()
         register_module(op, LUT::deserialize);
     for (const char *op : {"ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin"}) register_module(op, Reduce::deserialize);
     register_module("Slice", Slice::deserialize);
+    register_module("Pad", Pad::deserialize);
     register_module("Clip", Clip::deserialize);
     register_module("Relu", Relu::deserialize);
     register_module("PRelu", PRelu::deserialize);

@@ -289,6 +289,23 @@ protected:
     std::vector<int> m_start, m_end, m_axes, m_step;
 };
 
+/// Pad (reference: dl_module_pad.hpp:10-100): constant / edge / reflect, pads = [begin per axis ..., end per axis ...].
+class Pad : public Module {
+public:
+    Pad(std::vector<int> pads, int mode, long long constant, const char *name = nullptr, quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, MODULE_NON_INPLACE, quant_type), m_pads(pads), m_mode(mode), m_constant(constant)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    std::vector<int> m_pads;
+    int m_mode;
+    long long m_constant;
+};
+
 class Transpose : public Module {
 public:
     Transpose(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE,

@@ -422,6 +422,22 @@ typedef struct espdl_reduce_desc {
 
 int espdl_b200_reduce(const espdl_reduce_desc *desc, void *stream);
 
+/* ---------------------------------------------------------- Pad */
+/* dl::module::Pad / TensorBase::pad (esp-dl/dl/module/include/dl_module_pad.hpp:10-100, esp-dl/dl/base/dl_base_pad.cpp:
+ * 18-66 per axis): constant (the given code), edge (nearest element) or reflect (mirror without repeating the edge). */
+typedef enum { ESPDL_PAD_CONSTANT = 0, ESPDL_PAD_EDGE = 1, ESPDL_PAD_REFLECT = 2 } espdl_pad_mode_t;
+
+typedef struct espdl_pad_desc {
+    const void *input;
+    void *output;
+    int32_t elem_size, ndim, mode; /* elem_size 1, 2 or 4 bytes; ndim <= 6 */
+    int32_t shape[6];              /* input shape */
+    int32_t pad_begin[6], pad_end[6];
+    int64_t constant;              /* element value for ESPDL_PAD_CONSTANT (low elem_size bytes) */
+} espdl_pad_desc;
+
+int espdl_b200_pad(const espdl_pad_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -718,6 +718,46 @@ int oracle_reduce(const espdl_reduce_desc *d)
     return ESPDL_OK;
 }
 
+/* ---------------------------------------------------------------- Pad */
+/* TensorBase::pad / base::padND (esp-dl/dl/base/dl_base_pad.cpp:18-66 per axis): constant, edge, reflect. */
+int oracle_pad(const espdl_pad_desc *d)
+{
+    if (!d || !d->input || !d->output || d->ndim < 1 || d->ndim > 6)
+        return ESPDL_ERR_INVALID_ARG;
+    int64_t istride[6], oshape[6], total = 1, stride = 1;
+    for (int i = d->ndim - 1; i >= 0; i--) {
+        istride[i] = stride;
+        stride *= d->shape[i];
+        oshape[i] = d->shape[i] + d->pad_begin[i] + d->pad_end[i];
+        total *= oshape[i];
+    }
+    for (int64_t o = 0; o < total; o++) {
+        int64_t rem = o, off = 0;
+        int inside = 1;
+        for (int k = d->ndim - 1; k >= 0; k--) {
+            int64_t i = rem % oshape[k] - d->pad_begin[k];
+            rem /= oshape[k];
+            const int64_t n = d->shape[k];
+            if (i < 0 || i >= n) {
+                if (d->mode == ESPDL_PAD_CONSTANT)
+                    inside = 0;
+                else if (d->mode == ESPDL_PAD_EDGE)
+                    i = i < 0 ? 0 : n - 1;
+                else
+                    i = i < 0 ? -i : 2 * (n - 1) - i;
+                if (i < 0) i = 0;
+                if (i > n - 1) i = n - 1;
+            }
+            off += i * istride[k];
+        }
+        if (inside)
+            memcpy((char *)d->output + o * d->elem_size, (const char *)d->input + off * d->elem_size, (size_t)d->elem_size);
+        else
+            memcpy((char *)d->output + o * d->elem_size, &d->constant, (size_t)d->elem_size); /* little endian */
+    }
+    return ESPDL_OK;
+}
+
 int oracle_num_threads(void)
 {
 #if defined(_OPENMP)

@@ -31,6 +31,7 @@
 #include "dl_module_matmul.hpp"
 #include "dl_module_max_pool.hpp"
 #include "dl_module_mul.hpp"
+#include "dl_module_pad.hpp"
 #include "dl_module_prelu.hpp"
 #include "dl_module_reduce_max.hpp"
 #include "dl_module_reduce_mean.hpp"
@@ -293,6 +294,26 @@ int ref_reduce(const espdl_reduce_desc *d)
     std::vector<int> so = m->get_output_shape(in_shapes)[0];
     std::unique_ptr<TensorBase> ti(view(shape, d->input, d->in_exponent, d->dtype)), to(view(so, d->output, d->out_exponent, d->dtype));
     m->run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* Pad through the reference's own module (dl_module_pad.hpp): int8 / int16 tensors. */
+int ref_pad(const espdl_pad_desc *d)
+{
+    std::vector<int> shape(d->shape, d->shape + d->ndim), pads;
+    for (int i = 0; i < d->ndim; i++) pads.push_back(d->pad_begin[i]);
+    for (int i = 0; i < d->ndim; i++) pads.push_back(d->pad_end[i]);
+    const int dtype = d->elem_size == 1 ? ESPDL_DTYPE_INT8 : ESPDL_DTYPE_INT16;
+    const padding_mode_t mode = d->mode == ESPDL_PAD_CONSTANT ? PADDING_CONSTANT : (d->mode == ESPDL_PAD_EDGE ? PADDING_EDGE : PADDING_REFLECT);
+    int8_t c8 = (int8_t)d->constant;
+    int16_t c16 = (int16_t)d->constant;
+    TensorBase *cv = view({1}, d->elem_size == 1 ? (const void *)&c8 : (const void *)&c16, 0, dtype);
+    module::Pad m(pads, mode, new TensorBase({1}, cv->data, 0, cv->dtype, true), "pad", MODULE_NON_INPLACE, to_quant(dtype));
+    delete cv;
+    std::vector<std::vector<int>> in_shapes = {shape};
+    std::vector<int> so = m.get_output_shape(in_shapes)[0];
+    std::unique_ptr<TensorBase> ti(view(shape, d->input, 0, dtype)), to(view(so, d->output, 0, dtype));
+    m.run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
     return 0;
 }
 

@@ -24,7 +24,7 @@ def oracle():
         lib = C.CDLL(ORACLE_SO)
         for name, desc in [("oracle_conv2d", abi.ConvDesc), ("oracle_eltwise", abi.EltwiseDesc), ("oracle_pool", abi.PoolDesc),
                            ("oracle_resize", abi.ResizeDesc), ("oracle_copy", abi.CopyDesc), ("oracle_softmax", abi.SoftmaxDesc),
-                           ("oracle_reduce", abi.ReduceDesc)]:
+                           ("oracle_reduce", abi.ReduceDesc), ("oracle_pad", abi.PadDesc)]:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(desc)]
@@ -56,6 +56,8 @@ def ref():
         lib.ref_matmul.restype = C.c_int
         lib.ref_matmul.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p,
                                    C.c_int, C.c_int, C.c_int]
+        lib.ref_pad.restype = C.c_int
+        lib.ref_pad.argtypes = [C.POINTER(abi.PadDesc)]
         lib.ref_reduce.restype = C.c_int
         lib.ref_reduce.argtypes = [C.POINTER(abi.ReduceDesc)]
         lib.ref_num_threads.restype = C.c_int
