@@ -42,7 +42,7 @@ class EltwiseDesc(C.Structure):
         ("op", i32), ("in_dtype", i32), ("out_dtype", i32), ("ndim", i32),
         ("out_shape", i32 * 4), ("in0_shape", i32 * 4), ("in1_shape", i32 * 4),
         ("in0_exponent", i32), ("in1_exponent", i32), ("out_exponent", i32),
-        ("clip_lo", i32), ("clip_hi", i32), ("round_mode", i32), ("reserved", i32),
+        ("clip_lo", i32), ("clip_hi", i32), ("round_mode", i32), ("lut_shift", i32),
     ]
 
 

@@ -21,7 +21,7 @@ struct EltParams {
     long long sa[4], sb[4]; // element strides (0 on broadcast axes)
     int e0, e1, eo, lo, hi, half_even;
     float mul_scale, clip_rescale, in_scale, out_rescale, inv_scale;
-    int prelu_shift;
+    int prelu_shift, lut_shift;
     long long total;
 };
 
@@ -91,7 +91,18 @@ __global__ void __launch_bounds__(256) elt_generic_kernel(EltParams p)
         const int i3 = (int)(r / p.os[1]);
         const long long ai = i3 * p.sa[0] + i2 * p.sa[1] + i1 * p.sa[2] + i0 * p.sa[3];
         const long long bi = i3 * p.sb[0] + i2 * p.sb[1] + i1 * p.sb[2] + i0 * p.sb[3];
-        if (p.op == ESPDL_ELT_LUT) {
+        if (p.op == ESPDL_ELT_LUT && p.idt == ESPDL_DTYPE_INT16) {
+            // nearest table entry: index = ((uint16)x ^ 0x8000) >> shift, rounded (dl_base_lut.cpp:50-69)
+            const uint32_t value = (uint32_t)(uint16_t)((const int16_t *)p.a)[ai] ^ 0x8000u;
+            uint32_t index = value;
+            if (p.lut_shift > 0) {
+                index = value >> p.lut_shift;
+                const uint32_t rem = value & ((1u << p.lut_shift) - 1u), half = 1u << (p.lut_shift - 1);
+                if (p.half_even ? (rem > half || (rem == half && (index & 1u))) : rem >= half)
+                    index++;
+            }
+            ((int16_t *)p.out)[i] = ((const int16_t *)p.b)[index];
+        } else if (p.op == ESPDL_ELT_LUT) {
             ((int8_t *)p.out)[i] = ((const int8_t *)p.b)[(uint8_t)((const int8_t *)p.a)[ai] ^ 0x80u];
         } else if (p.op == ESPDL_ELT_REQUANTIZE && p.idt == ESPDL_DTYPE_FLOAT) {
             st_sat(p.out, p.odt, i, fround(__fmul_rn(((const float *)p.a)[ai], p.out_rescale), p.half_even));
@@ -181,7 +192,7 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
         if (!ok)
             return ESPDL_ERR_UNSUPPORTED;
     } else if (d->op == ESPDL_ELT_LUT) {
-        if (d->in_dtype != ESPDL_DTYPE_INT8 || d->out_dtype != ESPDL_DTYPE_INT8)
+        if (d->in_dtype != d->out_dtype || !is_int(d->in_dtype) || d->lut_shift < 0 || d->lut_shift > 15)
             return ESPDL_ERR_UNSUPPORTED;
     } else if (!is_int(d->in_dtype) || d->in_dtype != d->out_dtype) {
         return ESPDL_ERR_UNSUPPORTED;
@@ -212,6 +223,7 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     p.op = d->op, p.idt = d->in_dtype, p.odt = d->out_dtype;
     p.e0 = d->in0_exponent, p.e1 = d->in1_exponent, p.eo = d->out_exponent;
     p.lo = d->clip_lo, p.hi = d->clip_hi, p.half_even = d->round_mode == ESPDL_ROUND_HALF_EVEN;
+    p.lut_shift = d->lut_shift;
     for (int e : {p.e0, p.e1, p.eo})
         if (e > 30 || e < -30)
             return ESPDL_ERR_INVALID_ARG;

@@ -771,6 +771,11 @@ void Unary::forward(ModelContext *context, runtime_mode_t mode)
         d.in1_exponent = m_param ? (int)m_param->exponent : 0;
         d.clip_lo = m_clip_lo, d.clip_hi = m_clip_hi;
         d.round_mode = context->round_mode;
+        if (m_op == ESPDL_ELT_LUT && in->dtype == DATA_TYPE_INT16 && m_param && m_param->get_size() > 1) {
+            // step = 65536 / (entries - 1), a power of two (dl_module_lut.hpp:33-36, :64-67)
+            int step = 65536 / (m_param->get_size() - 1);
+            while (step > 1) d.lut_shift++, step >>= 1;
+        }
         if (m_op == ESPDL_ELT_PRELU && in->shape.size() <= 4) {
             d.ndim = (int)in->shape.size();
             for (int i = 0; i < d.ndim; i++) d.out_shape[i] = d.in0_shape[i] = in->shape[i], d.in1_shape[i] = 1;
@@ -804,8 +809,8 @@ LUT::LUT(const char *name, TensorBase *table, module_inplace_t inplace, quant_ty
 Module *LUT::deserialize(fbs::FbsModel *m, std::string node)
 {
     quant_type_t q = node_quant(m, node);
-    if (q != QUANT_TYPE_SYMM_8BIT)
-        return nullptr; // the 16-bit nearest-neighbour table and the float fall-backs are not on this path
+    if (q != QUANT_TYPE_SYMM_8BIT && q != QUANT_TYPE_SYMM_16BIT)
+        return nullptr; // the float fall-backs are not on this path
     TensorBase *table = m->get_operation_lut(node);
     if (!table)
         return nullptr;

@@ -205,7 +205,8 @@ typedef enum {
 
 typedef struct espdl_eltwise_desc {
     const void *input0;
-    const void *input1;       /* ADD/MUL/SUB: second operand; LUT: int8[256] table; PRELU: alpha[c]; else NULL */
+    const void *input1;       /* ADD/MUL/SUB: second operand; LUT: int8[256] table, or for int16 tensors an int16 table of
+                                 (65536 >> lut_shift) + 1 entries; PRELU: alpha[c]; else NULL                    */
     void *output;             /* may alias input0 or input1 (the planner runs these ops in place)              */
     int32_t op;               /* espdl_eltwise_op_t                                                            */
     int32_t in_dtype;         /* dtype of input0 (and input1 for ADD/MUL/SUB)                                  */
@@ -217,7 +218,9 @@ typedef struct espdl_eltwise_desc {
     int32_t in0_exponent, in1_exponent, out_exponent;
     int32_t clip_lo, clip_hi; /* CLIP: bounds in the input's quantised scale                                   */
     int32_t round_mode;
-    int32_t reserved;
+    int32_t lut_shift;        /* int16 LUT: log2 of the table step (5 for the usual 2049 entries): index = ((uint16)x ^ 0x8000)
+                                 >> lut_shift, rounded to nearest (ties up, or to even with ROUND_HALF_EVEN), esp-dl/dl/base/
+                                 dl_base_lut.cpp:50-107; 0 = a full 65536-entry table                             */
 } espdl_eltwise_desc;
 
 int espdl_b200_eltwise(const espdl_eltwise_desc *desc, void *stream);

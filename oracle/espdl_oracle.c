@@ -287,7 +287,19 @@ int oracle_eltwise(const espdl_eltwise_desc *d)
                         }
                         break;
                     }
-                    case ESPDL_ELT_LUT: /* esp-dl/dl/base/dl_base_lut.cpp:10-15 */
+                    case ESPDL_ELT_LUT: /* esp-dl/dl/base/dl_base_lut.cpp:10-15 (int8), :50-77 (int16) */
+                        if (idt == ESPDL_DTYPE_INT16) {
+                            const uint32_t value = (uint32_t)(uint16_t)((const int16_t *)d->input0)[a_i] ^ 0x8000u;
+                            uint32_t index = value;
+                            if (d->lut_shift > 0) {
+                                index = value >> d->lut_shift;
+                                const uint32_t rem = value & ((1u << d->lut_shift) - 1u), half = 1u << (d->lut_shift - 1);
+                                if (mode == ESPDL_ROUND_HALF_EVEN ? (rem > half || (rem == half && (index & 1u))) : rem >= half)
+                                    index++;
+                            }
+                            ((int16_t *)d->output)[oi] = ((const int16_t *)d->input1)[index];
+                            break;
+                        }
                         ((int8_t *)d->output)[oi] =
                             ((const int8_t *)d->input1)[(uint8_t)((const int8_t *)d->input0)[a_i] ^ 0x80u];
                         break;

@@ -155,7 +155,8 @@ int ref_eltwise(const espdl_eltwise_desc *d)
         return ESPDL_OK;
     }
     case ESPDL_ELT_LUT: {
-        TensorBase *table = new TensorBase({256}, d->input1, d->out_exponent, DATA_TYPE_INT8, true); /* owned by LUT */
+        const int entries = d->in_dtype == ESPDL_DTYPE_INT16 ? (65536 >> d->lut_shift) + 1 : 256;
+        TensorBase *table = new TensorBase({entries}, d->input1, d->out_exponent, to_dtype(d->in_dtype), true); /* owned by LUT */
         module::LUT m(nullptr, table, MODULE_NON_INPLACE, qt);
         m.run(in0.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
         return ESPDL_OK;

@@ -82,7 +82,7 @@ def conv_desc(case, ptrs=None):
 
 
 def eltwise_case(op, seed=0, dtype=abi.DTYPE_INT8, out_shape=(2, 5, 7, 16), in0_shape=None, in1_shape=None,
-                 e0=-5, e1=-6, eo=-4, out_dtype=None, in_dtype=None, clip=(0, 96), round_mode=abi.ROUND_HALF_UP):
+                 e0=-5, e1=-6, eo=-4, out_dtype=None, in_dtype=None, clip=(0, 96), round_mode=abi.ROUND_HALF_UP, lut_shift=5):
     rng = np.random.default_rng(seed)
     in_dtype = in_dtype or dtype
     out_dtype = out_dtype or dtype
@@ -99,6 +99,9 @@ def eltwise_case(op, seed=0, dtype=abi.DTYPE_INT8, out_shape=(2, 5, 7, 16), in0_
     b = None
     if op in (abi.ELT_ADD, abi.ELT_MUL, abi.ELT_SUB):
         b = rnd(in1_shape, in_dtype)
+    elif op == abi.ELT_LUT and in_dtype == abi.DTYPE_INT16:
+        b = rng.integers(-32768, 32768, size=((65536 >> lut_shift) + 1,), dtype=np.int16)
+        in1_shape = (1,) * len(out_shape)
     elif op == abi.ELT_LUT:
         b = rng.integers(-128, 128, size=(256,), dtype=np.int8)
         in1_shape = (1,) * len(out_shape)
@@ -110,7 +113,7 @@ def eltwise_case(op, seed=0, dtype=abi.DTYPE_INT8, out_shape=(2, 5, 7, 16), in0_
     out = np.zeros(out_shape, dtype=NP[out_dtype])
     return dict(a=a, b=b, out=out, op=op, in_dtype=in_dtype, out_dtype=out_dtype, ndim=len(out_shape), out_shape=out_shape,
                 in0_shape=in0_shape, in1_shape=in1_shape, in0_exponent=e0, in1_exponent=e1, out_exponent=eo,
-                clip_lo=clip[0], clip_hi=clip[1], round_mode=round_mode)
+                clip_lo=clip[0], clip_hi=clip[1], round_mode=round_mode, lut_shift=lut_shift if in_dtype == abi.DTYPE_INT16 else 0)
 
 
 def eltwise_desc(case, ptrs=None):
@@ -120,6 +123,7 @@ def eltwise_desc(case, ptrs=None):
         setattr(d, k, (ptrs.get(k) if ptrs is not None else (None if a is None else a.ctypes.data)))
     for f in ("op", "in_dtype", "out_dtype", "ndim", "in0_exponent", "in1_exponent", "out_exponent", "clip_lo", "clip_hi", "round_mode"):
         setattr(d, f, int(case[f]))
+    d.lut_shift = int(case.get("lut_shift", 0))
     for f in ("out_shape", "in0_shape", "in1_shape"):
         arr = getattr(d, f)
         for i, v in enumerate(case[f]):

@@ -163,6 +163,9 @@ def test_requantize(idt, odt, e0, eo):
 @pytest.mark.parametrize("shape", [(1, 4, 6, 24), (2, 8, 8, 32)])  # scalar and 128-bit paths
 @pytest.mark.parametrize("op,dtype,kw", [
     (abi.ELT_LUT, abi.DTYPE_INT8, {}),
+    (abi.ELT_LUT, abi.DTYPE_INT16, dict(lut_shift=5)),
+    (abi.ELT_LUT, abi.DTYPE_INT16, dict(lut_shift=5, round_mode=abi.ROUND_HALF_EVEN)),
+    (abi.ELT_LUT, abi.DTYPE_INT16, dict(lut_shift=0)),
     (abi.ELT_CLIP, abi.DTYPE_INT8, dict(e0=-4, eo=-4, clip=(0, 96))),
     (abi.ELT_CLIP, abi.DTYPE_INT8, dict(e0=-4, eo=-5, clip=(0, 96))),
     (abi.ELT_CLIP, abi.DTYPE_INT16, dict(e0=-10, eo=-9, clip=(-3000, 6000))),

@@ -124,6 +124,8 @@ def test_requantize_matches_reference(idt, odt, e0, eo):
 
 @pytest.mark.parametrize("op,dtype,kw", [
     (abi.ELT_LUT, abi.DTYPE_INT8, {}),
+    (abi.ELT_LUT, abi.DTYPE_INT16, dict(eo=-4, lut_shift=5)),   # the 2049-entry table with nearest-index rounding
+    (abi.ELT_LUT, abi.DTYPE_INT16, dict(eo=-4, lut_shift=3)),
     (abi.ELT_CLIP, abi.DTYPE_INT8, dict(e0=-4, eo=-4, clip=(0, 96))),
     (abi.ELT_CLIP, abi.DTYPE_INT8, dict(e0=-4, eo=-5, clip=(0, 96))),
     (abi.ELT_CLIP, abi.DTYPE_INT16, dict(e0=-10, eo=-9, clip=(-3000, 6000))),
