@@ -61,7 +61,7 @@ class ResizeDesc(C.Structure):
         ("input", C.c_void_p), ("output", C.c_void_p), ("dtype", i32),
         ("n", i32), ("in_h", i32), ("in_w", i32), ("c", i32), ("out_h", i32), ("out_w", i32),
         ("scale_h", C.c_float), ("scale_w", C.c_float),
-        ("in_exponent", i32), ("out_exponent", i32), ("out_pixel_stride", i32), ("reserved", i32),
+        ("in_exponent", i32), ("out_exponent", i32), ("out_pixel_stride", i32), ("mode", i32),
     ]
 
 

@@ -237,6 +237,60 @@ extern "C" int espdl_b200_pool(const espdl_pool_desc *d, void *stream)
     return check_launch("pool");
 }
 
+// Linear resize (esp-dl/dl/base/dl_base_resize.cpp:80-236): source coordinate and the two weights per axis as
+// linear_coeffs computes them, products and sums rounded one by one in fp32 (no fused multiply-add), then
+// quantize = clip(round(v * 2^-e_out)).
+struct ResizeLinearParams {
+    const int8_t *in;
+    int8_t *out;
+    int n, ih, iw, c, oh, ow, ops, align, one_d;
+    float sh_inv, sw_inv, in_scale, out_rescale;
+    long long total;
+};
+
+__device__ __forceinline__ void linear_coeffs_dev(int o, int &i, float &r0, float &r1, int in_length, float scale_inv, int align)
+{
+    float fx = align ? __fmul_rn((float)o, scale_inv) : __fsub_rn(__fmul_rn(__fadd_rn((float)o, 0.5f), scale_inv), 0.5f);
+    i = (int)floorf(fx);
+    fx = __fsub_rn(fx, (float)i);
+    if (i < 0) {
+        i = 0;
+        fx = 0.f;
+    }
+    if (i >= in_length - 1) {
+        i = in_length - 2;
+        fx = 1.f;
+    }
+    r0 = __fsub_rn(1.f, fx);
+    r1 = fx;
+}
+
+__global__ void __launch_bounds__(256) resize_linear_kernel(ResizeLinearParams p)
+{
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < p.total; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % p.c);
+        const long long pix = i / p.c;
+        const int x = (int)(pix % p.ow);
+        const int y = (int)((pix / p.ow) % p.oh);
+        const int n = (int)(pix / ((long long)p.ow * p.oh));
+        int ix, iy = 0;
+        float xr0, xr1, yr0 = 1.f, yr1 = 0.f;
+        linear_coeffs_dev(x, ix, xr0, xr1, p.iw, p.sw_inv, p.align);
+        if (!p.one_d)
+            linear_coeffs_dev(y, iy, yr0, yr1, p.ih, p.sh_inv, p.align);
+        const int8_t *row0 = p.in + (((long long)n * p.ih + iy) * p.iw + ix) * p.c + c;
+        const float a0 = __fmul_rn((float)row0[0], p.in_scale), a1 = __fmul_rn((float)row0[p.c], p.in_scale);
+        float v = __fadd_rn(__fmul_rn(a0, xr0), __fmul_rn(a1, xr1));
+        if (!p.one_d) {
+            const int8_t *row1 = row0 + (long long)p.iw * p.c;
+            const float b0 = __fmul_rn((float)row1[0], p.in_scale), b1 = __fmul_rn((float)row1[p.c], p.in_scale);
+            const float w = __fadd_rn(__fmul_rn(b0, xr0), __fmul_rn(b1, xr1));
+            v = __fadd_rn(__fmul_rn(v, yr0), __fmul_rn(w, yr1));
+        }
+        p.out[pix * p.ops + c] = (int8_t)sat8(fround_half_up(__fmul_rn(v, p.out_rescale)));
+    }
+}
+
 extern "C" int espdl_b200_resize(const espdl_resize_desc *d, void *stream)
 {
     if (!d || !d->input || !d->output)
@@ -245,6 +299,30 @@ extern "C" int espdl_b200_resize(const espdl_resize_desc *d, void *stream)
         return ESPDL_ERR_UNSUPPORTED;
     if (d->n < 0 || d->in_h <= 0 || d->in_w <= 0 || d->c <= 0 || d->out_h <= 0 || d->out_w <= 0 || d->scale_h <= 0 || d->scale_w <= 0)
         return ESPDL_ERR_INVALID_ARG;
+    if (d->mode < 0 || d->mode > 2)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->mode != 0) {
+        ResizeLinearParams q;
+        q.in = (const int8_t *)d->input, q.out = (int8_t *)d->output;
+        q.n = d->n, q.ih = d->in_h, q.iw = d->in_w, q.c = d->c, q.oh = d->out_h, q.ow = d->out_w;
+        q.ops = d->out_pixel_stride ? d->out_pixel_stride : d->c;
+        q.align = d->mode == 2, q.one_d = d->in_h == 1 && d->out_h == 1;
+        if (d->in_w < 2 || (!q.one_d && d->in_h < 2) || abs(d->in_exponent) > 30 || abs(d->out_exponent) > 30)
+            return ESPDL_ERR_UNSUPPORTED;
+        float sh = d->scale_h, sw = d->scale_w;
+        if (q.align) { // dl_base_resize.hpp:46-62
+            sh = q.one_d ? 1.f : (d->out_h - 1) / (float)(d->in_h - 1);
+            sw = (d->out_w - 1) / (float)(d->in_w - 1);
+        }
+        q.sh_inv = 1 / sh, q.sw_inv = 1 / sw;
+        q.in_scale = dl_scale(d->in_exponent), q.out_rescale = dl_rescale(d->out_exponent);
+        q.total = (long long)q.n * q.oh * q.ow * q.c;
+        if (q.total == 0)
+            return ESPDL_OK;
+        resize_linear_kernel<<<(unsigned)min((q.total + 255) / 256, (long long)num_sms() * 32), 256, 0, (cudaStream_t)stream>>>(q);
+        count_launch();
+        return check_launch("resize_linear");
+    }
     ResizeParams p;
     p.in = (const int8_t *)d->input, p.out = (int8_t *)d->output;
     p.n = d->n, p.ih = d->in_h, p.iw = d->in_w, p.c = d->c, p.oh = d->out_h, p.ow = d->out_w;

@@ -993,9 +993,9 @@ Module *GlobalAveragePool::deserialize(fbs::FbsModel *m, std::string node)
 // --------------------------------------------------------------------------------- resize
 Resize::Resize(const char *name, const resize_mode_t resize_mode, const std::vector<float> scales, const std::vector<int64_t> sizes,
                const bool align_corners, quant_type_t quant_type) :
-    Module(name, MODULE_NON_INPLACE, quant_type), m_resize_mode(resize_mode), m_scales(scales), m_sizes(sizes)
+    Module(name, MODULE_NON_INPLACE, quant_type), m_resize_mode(resize_mode), m_scales(scales), m_sizes(sizes),
+    m_align_corners(align_corners)
 {
-    (void)align_corners;
 }
 
 std::vector<std::vector<int>> Resize::get_output_shape(std::vector<std::vector<int>> &input_shapes)
@@ -1028,7 +1028,7 @@ void Resize::forward(ModelContext *context, runtime_mode_t mode)
     espdl_resize_desc d;
     memset(&d, 0, sizeof(d));
     int st = (!in || !out || !in->device || !out->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
-    if (!st && m_resize_mode != RESIZE_NEAREST)
+    if (!st && m_resize_mode != RESIZE_NEAREST && m_resize_mode != RESIZE_LINEAR)
         st = ESPDL_ERR_UNSUPPORTED;
     if (!st) {
         d.input = in->device, d.output = out->device, d.dtype = quant_dtype(quant_type);
@@ -1042,6 +1042,7 @@ void Resize::forward(ModelContext *context, runtime_mode_t mode)
             d.scale_h = 1, d.scale_w = m_scales[2];
         }
         d.in_exponent = in->exponent, d.out_exponent = out->exponent;
+        d.mode = m_resize_mode == RESIZE_NEAREST ? 0 : (m_align_corners ? 2 : 1);
         st = espdl_b200_resize(&d, context->stream);
     }
     if (st)

@@ -227,6 +227,7 @@ protected:
     resize_mode_t m_resize_mode;
     std::vector<float> m_scales;
     std::vector<int64_t> m_sizes;
+    bool m_align_corners;
 };
 
 /// Concat (dl_module_concat.hpp), Split (dl_module_split.hpp), Transpose (dl_module_transpose.hpp): strided copies.

@@ -258,7 +258,9 @@ typedef struct espdl_resize_desc {
     float scale_h, scale_w;
     int32_t in_exponent, out_exponent;
     int32_t out_pixel_stride; /* 0 = c */
-    int32_t reserved;
+    int32_t mode;             /* 0 nearest (asymmetric, floor); 1 linear with half-pixel coordinates; 2 linear with
+                                 align_corners (esp-dl/dl/base/dl_base_resize.cpp:80-236): bilinear for 4-D tensors,
+                                 linear along w when in_h == out_h == 1 */
 } espdl_resize_desc;
 
 int espdl_b200_resize(const espdl_resize_desc *desc, void *stream);

@@ -393,12 +393,73 @@ int oracle_pool(const espdl_pool_desc *d)
 /* esp-dl/dl/base/dl_base_resize.cpp:7-35 (value), :239-268 (coordinates),
  * esp-dl/dl/base/dl_base_resize.hpp:80-85 (scale/shift).  The value is a plain cast
  * of round(), without saturation. */
+/* linear_coeffs + resize_linear_c1: esp-dl/dl/base/dl_base_resize.cpp:80-236 */
+static void oracle_linear_coeffs(int out_x, int *in_x, float *r0, float *r1, int in_length, float scale_inv, int align)
+{
+    float fx = align ? out_x * scale_inv : (out_x + 0.5f) * scale_inv - 0.5f;
+    *in_x = (int)floorf(fx);
+    fx -= *in_x;
+    if (*in_x < 0) {
+        *in_x = 0;
+        fx = 0.f;
+    }
+    if (*in_x >= in_length - 1) {
+        *in_x = in_length - 2;
+        fx = 1.f;
+    }
+    *r0 = 1.f - fx;
+    *r1 = fx;
+}
+
+static int oracle_resize_linear(const espdl_resize_desc *d)
+{
+    const int align = d->mode == 2, one_d = d->in_h == 1 && d->out_h == 1;
+    if (d->in_w < 2 || (!one_d && d->in_h < 2))
+        return ESPDL_ERR_UNSUPPORTED;
+    float sh = d->scale_h, sw = d->scale_w;
+    if (align) {
+        sh = one_d ? 1.f : (d->out_h - 1) / (float)(d->in_h - 1);
+        sw = (d->out_w - 1) / (float)(d->in_w - 1);
+    }
+    const float sh_inv = 1 / sh, sw_inv = 1 / sw;
+    const float in_scale = dl_scale(d->in_exponent), out_rescale = dl_rescale(d->out_exponent);
+    const int ops = d->out_pixel_stride ? d->out_pixel_stride : d->c;
+    const int8_t *in = (const int8_t *)d->input;
+    for (int n = 0; n < d->n; n++)
+        for (int y = 0; y < d->out_h; y++) {
+            int iy = 0;
+            float yr0 = 1.f, yr1 = 0.f;
+            if (!one_d)
+                oracle_linear_coeffs(y, &iy, &yr0, &yr1, d->in_h, sh_inv, align);
+            for (int x = 0; x < d->out_w; x++) {
+                int ix;
+                float xr0, xr1;
+                oracle_linear_coeffs(x, &ix, &xr0, &xr1, d->in_w, sw_inv, align);
+                for (int c = 0; c < d->c; c++) {
+                    const int8_t *row0 = in + (((int64_t)n * d->in_h + iy) * d->in_w + ix) * d->c + c;
+                    float v = (float)row0[0] * in_scale * xr0 + (float)row0[d->c] * in_scale * xr1;
+                    if (!one_d) {
+                        const int8_t *row1 = row0 + (int64_t)d->in_w * d->c;
+                        const float w = (float)row1[0] * in_scale * xr0 + (float)row1[d->c] * in_scale * xr1;
+                        v = v * yr0 + w * yr1;
+                    }
+                    int q = fround_half_up(v * out_rescale);
+                    q = q < -128 ? -128 : (q > 127 ? 127 : q);
+                    ((int8_t *)d->output)[(((int64_t)n * d->out_h + y) * d->out_w + x) * ops + c] = (int8_t)q;
+                }
+            }
+        }
+    return ESPDL_OK;
+}
+
 int oracle_resize(const espdl_resize_desc *d)
 {
     if (!d || !d->input || !d->output)
         return ESPDL_ERR_INVALID_ARG;
     if (d->dtype != ESPDL_DTYPE_INT8) /* resize<int16_t> is an empty function: esp-dl/dl/base/dl_base_resize.cpp:298-309 */
         return ESPDL_ERR_UNSUPPORTED;
+    if (d->mode != 0)
+        return oracle_resize_linear(d);
     int shift = d->out_exponent - d->in_exponent, oscale = 1;
     if (shift < 0) {
         oscale = 1 << (-shift);

@@ -227,9 +227,17 @@ int ref_resize(const espdl_resize_desc *d)
     for (int n = 0; n < d->n; n++) {
         const char *ip = (const char *)d->input + (size_t)n * d->in_h * d->in_w * d->c * es;
         char *op = (char *)d->output + (size_t)n * d->out_h * d->out_w * d->c * es;
+        if (d->mode != 0 && d->in_h == 1 && d->out_h == 1) { // linear along w: the reference's 3-D (NWC) form
+            std::unique_ptr<TensorBase> in(view({1, d->in_w, d->c}, ip, d->in_exponent, d->dtype));
+            std::unique_ptr<TensorBase> out(view({1, d->out_w, d->c}, op, d->out_exponent, d->dtype));
+            module::Resize m(nullptr, RESIZE_LINEAR, {1.f, 1.f, d->scale_w}, {}, d->mode == 2, to_quant(d->dtype));
+            m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+            continue;
+        }
         std::unique_ptr<TensorBase> in(view({1, d->in_h, d->in_w, d->c}, ip, d->in_exponent, d->dtype));
         std::unique_ptr<TensorBase> out(view({1, d->out_h, d->out_w, d->c}, op, d->out_exponent, d->dtype));
-        module::Resize m(nullptr, RESIZE_NEAREST, {1.f, 1.f, d->scale_h, d->scale_w}, {}, false, to_quant(d->dtype));
+        module::Resize m(nullptr, d->mode == 0 ? RESIZE_NEAREST : RESIZE_LINEAR, {1.f, 1.f, d->scale_h, d->scale_w}, {}, d->mode == 2,
+                         to_quant(d->dtype));
         m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
     }
     return ESPDL_OK;

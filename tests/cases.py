@@ -156,21 +156,21 @@ def pool_desc(case, ptrs=None):
     return d
 
 
-def resize_case(seed=0, dtype=abi.DTYPE_INT8, n=2, h=5, w=6, c=16, scale=(2.0, 2.0), e_in=-5, e_out=-5, out_stride=0):
+def resize_case(seed=0, dtype=abi.DTYPE_INT8, n=2, h=5, w=6, c=16, scale=(2.0, 2.0), e_in=-5, e_out=-5, out_stride=0, mode=0):
     rng = np.random.default_rng(seed)
     info = np.iinfo(NP[dtype])
     x = rng.integers(info.min, info.max + 1, size=(n, h, w, c), dtype=NP[dtype])
     oh, ow = int(h * np.float32(scale[0])), int(w * np.float32(scale[1]))
     out = np.zeros((n, oh, ow, out_stride or c), dtype=NP[dtype])
     return dict(x=x, out=out, dtype=dtype, n=n, in_h=h, in_w=w, c=c, out_h=oh, out_w=ow, scale_h=scale[0], scale_w=scale[1],
-                in_exponent=e_in, out_exponent=e_out, out_pixel_stride=out_stride)
+                in_exponent=e_in, out_exponent=e_out, out_pixel_stride=out_stride, mode=mode)
 
 
 def resize_desc(case, ptrs=None):
     d = abi.ResizeDesc()
     d.input = ptrs["input"] if ptrs is not None else case["x"].ctypes.data
     d.output = ptrs["output"] if ptrs is not None else case["out"].ctypes.data
-    for f in ("dtype", "n", "in_h", "in_w", "c", "out_h", "out_w", "in_exponent", "out_exponent", "out_pixel_stride"):
+    for f in ("dtype", "n", "in_h", "in_w", "c", "out_h", "out_w", "in_exponent", "out_exponent", "out_pixel_stride", "mode"):
         setattr(d, f, int(case[f]))
     d.scale_h, d.scale_w = case["scale_h"], case["scale_w"]
     return d

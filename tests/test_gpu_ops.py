@@ -227,6 +227,22 @@ def test_resize(kw):
     np.testing.assert_array_equal(got, want)
 
 
+@pytest.mark.parametrize("kw", [dict(scale=(2.0, 2.0), mode=1), dict(scale=(2.0, 2.0), mode=2), dict(scale=(2.0, 2.0), e_in=-5, e_out=-4, mode=1),
+          dict(scale=(1.5, 2.5), h=8, w=8, e_in=-5, e_out=-6, mode=1), dict(scale=(0.5, 0.5), h=8, w=10, mode=1),
+          dict(scale=(3.0, 1.7), h=7, w=9, c=5, mode=2), dict(scale=(1.0, 2.0), h=1, w=12, c=24, mode=1),
+          dict(scale=(1.0, 3.5), h=1, w=9, c=7, e_in=-6, e_out=-5, mode=2), dict(scale=(4.0, 4.0), n=3, h=13, w=11, c=32, mode=1)] + [dict(scale=(2.0, 2.0), n=2, h=20, w=20, c=64, out_stride=192, mode=1)])
+def test_linear_resize(kw):
+    case = cases.resize_case(seed=19, **kw)
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input=dev.upload(case["x"]), output=dev.upload(case["out"]))
+        d = cases.resize_desc(case, ptrs)
+        abi.check(dev.lib.espdl_b200_resize(C.byref(d), None), "resize")
+        got = dev.download(ptrs["output"], case["out"])
+    want = case["out"].copy()
+    assert checkers.oracle().oracle_resize(cases.resize_desc(dict(case, out=want))) == 0
+    np.testing.assert_array_equal(got, want)
+
+
 def test_resize_int16_is_rejected():
     case = cases.resize_case(seed=17, dtype=abi.DTYPE_INT16)
     with gpu_util.DeviceBuffers() as dev:

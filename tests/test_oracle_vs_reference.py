@@ -171,6 +171,23 @@ def test_resize_matches_reference(kw, dtype):
     np.testing.assert_array_equal(co["out"], cr["out"])
 
 
+LINEAR_RESIZE = [dict(scale=(2.0, 2.0), mode=1), dict(scale=(2.0, 2.0), mode=2), dict(scale=(2.0, 2.0), e_in=-5, e_out=-4, mode=1),
+          dict(scale=(1.5, 2.5), h=8, w=8, e_in=-5, e_out=-6, mode=1), dict(scale=(0.5, 0.5), h=8, w=10, mode=1),
+          dict(scale=(3.0, 1.7), h=7, w=9, c=5, mode=2), dict(scale=(1.0, 2.0), h=1, w=12, c=24, mode=1),
+          dict(scale=(1.0, 3.5), h=1, w=9, c=7, e_in=-6, e_out=-5, mode=2), dict(scale=(4.0, 4.0), n=3, h=13, w=11, c=32, mode=1)]
+
+
+@pytest.mark.parametrize("kw", LINEAR_RESIZE)
+def test_linear_resize_matches_reference(kw):
+    """Linear resize (half-pixel and align_corners coordinates, 2-D and along w only) against the reference's Resize module."""
+    case = cases.resize_case(seed=19, **kw)
+    co, cr = dict(case, out=case["out"].copy()), dict(case, out=case["out"].copy())
+    assert checkers.oracle().oracle_resize(cases.resize_desc(co)) == 0
+    assert checkers.ref().ref_resize(cases.resize_desc(cr)) == 0
+    assert co["out"].any()
+    np.testing.assert_array_equal(co["out"], cr["out"])
+
+
 @pytest.mark.parametrize("e_in,rows,length", [(-4, 6, 400), (-3, 3, 37), (-6, 5, 64)])
 def test_softmax_matches_reference(e_in, rows, length):
     rng = np.random.default_rng(19)
