@@ -11,11 +11,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libespdl_b200.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_NO_DEVICE, ERR_NO_MEM, ERR_TIMEOUT, ERR_TOO_LARGE = 0, -1, -2, -3, -4, -5, -6, -7
-DTYPE_FLOAT, DTYPE_INT8, DTYPE_INT16, DTYPE_INT32, DTYPE_INT64 = 1, 3, 5, 6, 7
+DTYPE_FLOAT, DTYPE_INT8, DTYPE_INT16, DTYPE_INT32, DTYPE_INT64, DTYPE_BOOL = 1, 3, 5, 6, 7, 9
 ACT_LINEAR, ACT_RELU = 0, 1
 ROUND_HALF_UP, ROUND_HALF_EVEN = 0, 1
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
 ELT_ADD, ELT_MUL, ELT_REQUANTIZE, ELT_LUT, ELT_CLIP, ELT_RELU, ELT_PRELU, ELT_SUB = range(8)
+ELT_MAX, ELT_MIN, ELT_DIV, ELT_MOD, ELT_GREATER, ELT_GREATER_EQUAL, ELT_EQUAL, ELT_LESS, ELT_LESS_EQUAL = range(8, 17)
 POOL_MAX, POOL_AVG, POOL_GLOBAL_AVG = 0, 1, 2
 
 i32 = C.c_int32

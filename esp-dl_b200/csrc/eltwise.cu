@@ -9,6 +9,8 @@
 //   assign   esp-dl/dl/tensor/src/dl_tensor_base.cpp:223-404
 //   LUT      esp-dl/dl/base/dl_base_lut.cpp:10-15     Clip  esp-dl/dl/module/include/dl_module_clip.hpp:78-90
 //   ReLU     esp-dl/dl/module/include/dl_module_relu.hpp:66-91   PReLU esp-dl/dl/base/dl_base_prelu.cpp:5-19
+//   Max/Min  esp-dl/dl/base/dl_base_max.cpp, dl_base_min.cpp     Div   esp-dl/dl/base/dl_base_div.cpp:87-207
+//   Mod      esp-dl/dl/base/dl_base_mod.cpp:9-62                 comparisons esp-dl/dl/base/dl_base_greater.cpp:9-44 (and siblings)
 #include "common.cuh"
 
 namespace espdl {
@@ -20,10 +22,17 @@ struct EltParams {
     int os[4];
     long long sa[4], sb[4]; // element strides (0 on broadcast axes)
     int e0, e1, eo, lo, hi, half_even;
-    float mul_scale, clip_rescale, in_scale, out_rescale, inv_scale;
+    float mul_scale, clip_rescale, in_scale, in1_scale, out_rescale, inv_scale;
     int prelu_shift, lut_shift;
+    int div_n1, div_table0; // Div: divisor broadcast along the innermost axis; int8 dividend of one element (table form)
+    float div_scale;
     long long total;
 };
+
+__host__ __device__ __forceinline__ bool elt_two_operands(int op)
+{
+    return op == ESPDL_ELT_ADD || op == ESPDL_ELT_SUB || op == ESPDL_ELT_MUL || (op >= ESPDL_ELT_MAX && op <= ESPDL_ELT_LESS_EQUAL);
+}
 
 __device__ __forceinline__ long long ld_int(const void *p, int dt, long long i)
 {
@@ -34,6 +43,8 @@ __device__ __forceinline__ void st_sat(void *p, int dt, long long i, long long v
 {
     if (dt == ESPDL_DTYPE_INT8)
         ((int8_t *)p)[i] = (int8_t)max(-128ll, min(127ll, v));
+    else if (dt == ESPDL_DTYPE_BOOL)
+        ((uint8_t *)p)[i] = v != 0;
     else
         ((int16_t *)p)[i] = (int16_t)max(-32768ll, min(32767ll, v));
 }
@@ -75,6 +86,30 @@ __device__ __forceinline__ long long elt_int(const EltParams &p, long long a, lo
             v = (int)v;
         return v;
     }
+    case ESPDL_ELT_MAX: return max(a, b);
+    case ESPDL_ELT_MIN: return min(a, b);
+    case ESPDL_ELT_DIV: {
+        const long long hi = p.idt == ESPDL_DTYPE_INT8 ? 127 : 32767, lo = -hi - 1;
+        if (p.div_table0) // int8 dividend of one element: the reference tabulates by divisor (dl_base_div.cpp:17-31)
+            return b == 0 ? (a > 0 ? hi : lo) : (long long)fround(__fdiv_rn(__fmul_rn(__int2float_rn((int)a), p.div_scale), __int2float_rn((int)b)), p.half_even);
+        if (a == 0)
+            return 0;
+        if (b == 0)
+            return a > 0 ? hi : lo;
+        const float fa = __int2float_rn((int)a), fb = __int2float_rn((int)b);
+        const float q = p.div_n1 ? __fmul_rn(fa, __fdiv_rn(p.div_scale, fb)) : __fdiv_rn(__fmul_rn(fa, p.div_scale), fb);
+        return fround(q, p.half_even);
+    }
+    case ESPDL_ELT_MOD: {
+        const float av = __fmul_rn(__int2float_rn((int)a), p.in_scale), bv = __fmul_rn(__int2float_rn((int)b), p.in1_scale);
+        const float r = bv != 0.f ? fmodf(av, bv) : 0.f;
+        return fround(__fmul_rn(r, p.out_rescale), p.half_even);
+    }
+    case ESPDL_ELT_GREATER: return a > b;
+    case ESPDL_ELT_GREATER_EQUAL: return a >= b;
+    case ESPDL_ELT_EQUAL: return a == b;
+    case ESPDL_ELT_LESS: return a < b;
+    case ESPDL_ELT_LESS_EQUAL: return a <= b;
     default: return 0;
     }
 }
@@ -111,7 +146,7 @@ __global__ void __launch_bounds__(256) elt_generic_kernel(EltParams p)
         } else {
             const long long a = ld_int(p.a, p.idt, ai);
             long long b = 0;
-            if (p.op == ESPDL_ELT_ADD || p.op == ESPDL_ELT_SUB || p.op == ESPDL_ELT_MUL)
+            if (elt_two_operands(p.op))
                 b = ld_int(p.b, p.idt, bi);
             else if (p.op == ESPDL_ELT_PRELU)
                 b = ld_int(p.b, p.idt, i0);
@@ -132,7 +167,7 @@ __global__ void __launch_bounds__(256) elt_s8_vec16_kernel(EltParams p, long lon
     for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
         const uint4 a4 = ((const uint4 *)p.a)[v];
         uint4 b4 = make_uint4(0, 0, 0, 0);
-        if (OP == ESPDL_ELT_ADD || OP == ESPDL_ELT_SUB || OP == ESPDL_ELT_MUL)
+        if (elt_two_operands(OP))
             b4 = ((const uint4 *)p.b)[v];
         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
@@ -180,10 +215,11 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
 {
     if (!d || !d->input0 || !d->output || d->ndim < 1 || d->ndim > 4)
         return ESPDL_ERR_INVALID_ARG;
-    const bool binary = d->op == ESPDL_ELT_ADD || d->op == ESPDL_ELT_SUB || d->op == ESPDL_ELT_MUL;
+    const bool binary = elt_two_operands(d->op);
+    const bool compare = d->op >= ESPDL_ELT_GREATER && d->op <= ESPDL_ELT_LESS_EQUAL;
     if ((binary || d->op == ESPDL_ELT_LUT || d->op == ESPDL_ELT_PRELU) && !d->input1)
         return ESPDL_ERR_INVALID_ARG;
-    if (d->op < ESPDL_ELT_ADD || d->op > ESPDL_ELT_SUB)
+    if (d->op < ESPDL_ELT_ADD || d->op > ESPDL_ELT_LESS_EQUAL)
         return ESPDL_ERR_INVALID_ARG;
     auto is_int = [](int t) { return t == ESPDL_DTYPE_INT8 || t == ESPDL_DTYPE_INT16; };
     if (d->op == ESPDL_ELT_REQUANTIZE) {
@@ -193,6 +229,9 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
             return ESPDL_ERR_UNSUPPORTED;
     } else if (d->op == ESPDL_ELT_LUT) {
         if (d->in_dtype != d->out_dtype || !is_int(d->in_dtype) || d->lut_shift < 0 || d->lut_shift > 15)
+            return ESPDL_ERR_UNSUPPORTED;
+    } else if (compare) {
+        if (!is_int(d->in_dtype) || d->out_dtype != ESPDL_DTYPE_BOOL)
             return ESPDL_ERR_UNSUPPORTED;
     } else if (!is_int(d->in_dtype) || d->in_dtype != d->out_dtype) {
         return ESPDL_ERR_UNSUPPORTED;
@@ -230,12 +269,23 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     p.mul_scale = dl_scale(p.e0) * dl_scale(p.e1) * dl_rescale(p.eo);
     p.clip_rescale = dl_scale(p.e0) * dl_rescale(p.eo);
     p.in_scale = dl_scale(p.e0);
+    p.in1_scale = dl_scale(p.e1);
+    if (d->op == ESPDL_ELT_DIV) {
+        // which operand the reference sees as a scalar along the innermost merged axis (dl_base_elemwise.cpp:38-100,
+        // dl_base_div.cpp:208-250): that is the innermost axis on which the output is longer than 1
+        int ax = 3;
+        while (ax > 0 && os[ax] == 1) ax--;
+        const bool in0_1 = s0[ax] == 1, in1_1 = s1[ax] == 1;
+        p.div_table0 = d->in_dtype == ESPDL_DTYPE_INT8 && a == 1; // a = element count of input0 here
+        p.div_n1 = d->in_dtype == ESPDL_DTYPE_INT8 ? (in1_1 && !in0_1) : in1_1;
+        p.div_scale = dl_rescale(p.eo) * dl_scale(p.e0) / dl_scale(p.e1); // dl_base_div.cpp:66
+    }
     p.out_rescale = dl_rescale(p.eo);
     p.inv_scale = (float)(1.0 / (double)dl_scale(p.eo));
     p.prelu_shift = p.eo - p.e0 - p.e1;
     p.total = total;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = same && d->in_dtype == ESPDL_DTYPE_INT8 && d->out_dtype == ESPDL_DTYPE_INT8 && total % 16 == 0 &&
+    const bool vec = same && d->in_dtype == ESPDL_DTYPE_INT8 && (d->out_dtype == ESPDL_DTYPE_INT8 || compare) && total % 16 == 0 &&
         ((uintptr_t)d->input0 % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && (!binary || ((uintptr_t)d->input1 % 16) == 0) &&
         d->op != ESPDL_ELT_PRELU;
     if (vec) {
@@ -248,6 +298,15 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
         case ESPDL_ELT_LUT: launch_vec<ESPDL_ELT_LUT>(p, nvec, s); break;
         case ESPDL_ELT_CLIP: launch_vec<ESPDL_ELT_CLIP>(p, nvec, s); break;
         case ESPDL_ELT_RELU: launch_vec<ESPDL_ELT_RELU>(p, nvec, s); break;
+        case ESPDL_ELT_MAX: launch_vec<ESPDL_ELT_MAX>(p, nvec, s); break;
+        case ESPDL_ELT_MIN: launch_vec<ESPDL_ELT_MIN>(p, nvec, s); break;
+        case ESPDL_ELT_DIV: launch_vec<ESPDL_ELT_DIV>(p, nvec, s); break;
+        case ESPDL_ELT_MOD: launch_vec<ESPDL_ELT_MOD>(p, nvec, s); break;
+        case ESPDL_ELT_GREATER: launch_vec<ESPDL_ELT_GREATER>(p, nvec, s); break;
+        case ESPDL_ELT_GREATER_EQUAL: launch_vec<ESPDL_ELT_GREATER_EQUAL>(p, nvec, s); break;
+        case ESPDL_ELT_EQUAL: launch_vec<ESPDL_ELT_EQUAL>(p, nvec, s); break;
+        case ESPDL_ELT_LESS: launch_vec<ESPDL_ELT_LESS>(p, nvec, s); break;
+        case ESPDL_ELT_LESS_EQUAL: launch_vec<ESPDL_ELT_LESS_EQUAL>(p, nvec, s); break;
         default: return ESPDL_ERR_UNSUPPORTED;
         }
     } else {

@@ -743,6 +743,20 @@ Module *Add::deserialize(fbs::FbsModel *m, std::string node) { return new Add(no
 Module *Sub::deserialize(fbs::FbsModel *m, std::string node) { return new Sub(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node)); }
 Module *Mul::deserialize(fbs::FbsModel *m, std::string node) { return new Mul(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node)); }
 
+#define ESPDL_B200_TWO_OPERAND_MODULE(NAME, OP)                                                                                  \
+    NAME::NAME(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Elementwise(OP, name, inplace, quant_type) {} \
+    Module *NAME::deserialize(fbs::FbsModel *m, std::string node) { return new NAME(node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node)); }
+ESPDL_B200_TWO_OPERAND_MODULE(Max, ESPDL_ELT_MAX)
+ESPDL_B200_TWO_OPERAND_MODULE(Min, ESPDL_ELT_MIN)
+ESPDL_B200_TWO_OPERAND_MODULE(Div, ESPDL_ELT_DIV)
+ESPDL_B200_TWO_OPERAND_MODULE(Mod, ESPDL_ELT_MOD)
+ESPDL_B200_TWO_OPERAND_MODULE(Greater, ESPDL_ELT_GREATER)
+ESPDL_B200_TWO_OPERAND_MODULE(GreaterOrEqual, ESPDL_ELT_GREATER_EQUAL)
+ESPDL_B200_TWO_OPERAND_MODULE(Equal, ESPDL_ELT_EQUAL)
+ESPDL_B200_TWO_OPERAND_MODULE(Less, ESPDL_ELT_LESS)
+ESPDL_B200_TWO_OPERAND_MODULE(LessOrEqual, ESPDL_ELT_LESS_EQUAL)
+#undef ESPDL_B200_TWO_OPERAND_MODULE
+
 esp_err_t Unary::prepare(ModelContext *context)
 {
     (void)context;
@@ -1628,6 +1642,15 @@ void ModuleCreator::register_dl_modules()
     register_module("Add", Add::deserialize);
     register_module("Sub", Sub::deserialize);
     register_module("Mul", Mul::deserialize);
+    register_module("Max", Max::deserialize);
+    register_module("Min", Min::deserialize);
+    register_module("Div", Div::deserialize);
+    register_module("Mod", Mod::deserialize);
+    register_module("Greater", Greater::deserialize);
+    register_module("GreaterOrEqual", GreaterOrEqual::deserialize);
+    register_module("Equal", Equal::deserialize);
+    register_module("Less", Less::deserialize);
+    register_module("LessOrEqual", LessOrEqual::deserialize);
     register_module("RequantizeLinear", RequantizeLinear::deserialize);
     register_module("QuantizeLinear", RequantizeLinear::deserialize);
     register_module("DequantizeLinear", RequantizeLinear::deserialize);

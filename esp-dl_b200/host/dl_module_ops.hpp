@@ -129,6 +129,25 @@ public:
     Mul(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
 };
+/// Max / Min (dl_module_max.hpp, dl_module_min.hpp), Div (dl_module_div.hpp), Mod (dl_module_mod.hpp, fmod form) and the
+/// comparisons with a bool output (dl_module_greater.hpp, dl_module_greater_or_equal.hpp, dl_module_equal.hpp,
+/// dl_module_less.hpp, dl_module_less_or_equal.hpp): same broadcasting and construction as Add.
+#define ESPDL_B200_TWO_OPERAND_MODULE(NAME)                                                                                        \
+    class NAME : public Elementwise {                                                                                              \
+    public:                                                                                                                        \
+        NAME(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE); \
+        static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);                                               \
+    };
+ESPDL_B200_TWO_OPERAND_MODULE(Max)
+ESPDL_B200_TWO_OPERAND_MODULE(Min)
+ESPDL_B200_TWO_OPERAND_MODULE(Div)
+ESPDL_B200_TWO_OPERAND_MODULE(Mod)
+ESPDL_B200_TWO_OPERAND_MODULE(Greater)
+ESPDL_B200_TWO_OPERAND_MODULE(GreaterOrEqual)
+ESPDL_B200_TWO_OPERAND_MODULE(Equal)
+ESPDL_B200_TWO_OPERAND_MODULE(Less)
+ESPDL_B200_TWO_OPERAND_MODULE(LessOrEqual)
+#undef ESPDL_B200_TWO_OPERAND_MODULE
 
 /// One-input elementwise modules: RequantizeLinear / QuantizeLinear / DequantizeLinear
 /// (dl_module_requantize_linear.hpp:8-60), LUT and every activation exported with a `lut` attribute

@@ -7,7 +7,7 @@ import numpy as np
 from . import abi
 
 HOST_LIB_PATH = os.path.join(abi.HERE, "libespdl_b200_host.so")
-NP = {1: np.float32, 3: np.int8, 5: np.int16, 6: np.int32, 7: np.int64}
+NP = {1: np.float32, 3: np.int8, 5: np.int16, 6: np.int32, 7: np.int64, 9: np.uint8}
 _host = None
 
 

@@ -49,7 +49,8 @@ typedef enum {
     ESPDL_DTYPE_INT8 = 3,
     ESPDL_DTYPE_INT16 = 5,
     ESPDL_DTYPE_INT32 = 6,
-    ESPDL_DTYPE_INT64 = 7
+    ESPDL_DTYPE_INT64 = 7,
+    ESPDL_DTYPE_BOOL = 9
 } espdl_dtype_t;
 
 /* Same numeric values as dl::activation_type_t (esp-dl/dl/dl_define.hpp:108-114). */
@@ -200,16 +201,29 @@ typedef enum {
     ESPDL_ELT_RELU = 5,       /* max(q,0) then requantise if exponents differ
                                                                       esp-dl/dl/module/include/dl_module_relu.hpp  */
     ESPDL_ELT_PRELU = 6,      /* q<0 ? sat((q*alpha[c]) >> shift) : q esp-dl/dl/base/dl_base_prelu.cpp:5-19        */
-    ESPDL_ELT_SUB = 7         /* sat(a - b)                           esp-dl/dl/base/dl_base_sub.cpp               */
+    ESPDL_ELT_SUB = 7,        /* sat(a - b)                           esp-dl/dl/base/dl_base_sub.cpp               */
+    ESPDL_ELT_MAX = 8,        /* max(a, b) of the raw integers        esp-dl/dl/base/dl_base_max.cpp:9-50          */
+    ESPDL_ELT_MIN = 9,        /* min(a, b) of the raw integers        esp-dl/dl/base/dl_base_min.cpp               */
+    ESPDL_ELT_DIV = 10,       /* a == 0 ? 0 : b == 0 ? (a > 0 ? max : min) : sat(round(a * R / b)), R = 2^(ea-eb-eo); the
+                                 fp32 order depends on which operand is broadcast along the innermost axis: divisor
+                                 broadcast -> a * (R / b), else (a * R) / b  esp-dl/dl/base/dl_base_div.cpp:87-207    */
+    ESPDL_ELT_MOD = 11,       /* sat(round(fmodf(a*2^ea, b*2^eb) * 2^-eo)), 0 where b == 0
+                                                                      esp-dl/dl/base/dl_base_mod.cpp:9-62          */
+    ESPDL_ELT_GREATER = 12,   /* comparisons of the raw integers (exponents are not looked at), one bool byte per
+                                 element: out_dtype = ESPDL_DTYPE_BOOL  esp-dl/dl/base/dl_base_greater.cpp:9-44      */
+    ESPDL_ELT_GREATER_EQUAL = 13,
+    ESPDL_ELT_EQUAL = 14,
+    ESPDL_ELT_LESS = 15,
+    ESPDL_ELT_LESS_EQUAL = 16
 } espdl_eltwise_op_t;
 
 typedef struct espdl_eltwise_desc {
     const void *input0;
-    const void *input1;       /* ADD/MUL/SUB: second operand; LUT: int8[256] table, or for int16 tensors an int16 table of
+    const void *input1;       /* ADD/MUL/SUB and MAX..LESS_EQUAL: second operand; LUT: int8[256] table, or for int16 tensors an int16 table of
                                  (65536 >> lut_shift) + 1 entries; PRELU: alpha[c]; else NULL                    */
     void *output;             /* may alias input0 or input1 (the planner runs these ops in place)              */
     int32_t op;               /* espdl_eltwise_op_t                                                            */
-    int32_t in_dtype;         /* dtype of input0 (and input1 for ADD/MUL/SUB)                                  */
+    int32_t in_dtype;         /* dtype of input0 (and input1 for the two-operand ops)                          */
     int32_t out_dtype;
     int32_t ndim;             /* 1..4; shapes are right-aligned, every input extent is 1 or the output extent  */
     int32_t out_shape[4];

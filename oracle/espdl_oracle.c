@@ -210,6 +210,8 @@ static inline void store_sat(void *p, int dtype, int64_t i, int64_t v)
 {
     if (dtype == ESPDL_DTYPE_INT8)
         ((int8_t *)p)[i] = (int8_t)clamp64(v, INT8_MIN, INT8_MAX);
+    else if (dtype == ESPDL_DTYPE_BOOL)
+        ((uint8_t *)p)[i] = v != 0;
     else
         ((int16_t *)p)[i] = (int16_t)clamp64(v, INT16_MIN, INT16_MAX);
 }
@@ -227,7 +229,8 @@ int oracle_eltwise(const espdl_eltwise_desc *d)
         s0[4 - d->ndim + i] = d->in0_shape[i];
         s1[4 - d->ndim + i] = d->in1_shape[i];
     }
-    const int binary = d->op == ESPDL_ELT_ADD || d->op == ESPDL_ELT_MUL || d->op == ESPDL_ELT_SUB;
+    const int binary = d->op == ESPDL_ELT_ADD || d->op == ESPDL_ELT_MUL || d->op == ESPDL_ELT_SUB ||
+        (d->op >= ESPDL_ELT_MAX && d->op <= ESPDL_ELT_LESS_EQUAL);
     if ((binary || d->op == ESPDL_ELT_LUT || d->op == ESPDL_ELT_PRELU) && !d->input1)
         return ESPDL_ERR_INVALID_ARG;
     int64_t st0[4], st1[4];
@@ -251,6 +254,20 @@ int oracle_eltwise(const espdl_eltwise_desc *d)
     /* Clip: esp-dl/dl/module/include/dl_module_clip.hpp:85 */
     const float clip_rescale = dl_scale(d->in0_exponent) * dl_rescale(d->out_exponent);
     const int C = os[3];
+    /* Div: esp-dl/dl/base/dl_base_div.cpp:66 (scale), :208-250 (which loop body runs: chosen by the operand that is a
+     * scalar along the innermost merged axis, esp-dl/dl/base/dl_base_elemwise.cpp:38-100 - the innermost axis on which
+     * the output is longer than 1; int8 asks for the dividend first, int16 for the divisor first), :17-31 (an int8
+     * dividend of one element is tabulated by divisor, which differs from the loop body at 0 / 0). */
+    int div_n1 = 0, div_table0 = 0;
+    float div_scale = 0;
+    if (d->op == ESPDL_ELT_DIV) {
+        int ax = 3;
+        while (ax > 0 && os[ax] == 1) ax--;
+        const int in0_1 = s0[ax] == 1, in1_1 = s1[ax] == 1;
+        div_table0 = idt == ESPDL_DTYPE_INT8 && (int64_t)s0[0] * s0[1] * s0[2] * s0[3] == 1;
+        div_n1 = idt == ESPDL_DTYPE_INT8 ? (in1_1 && !in0_1) : in1_1;
+        div_scale = dl_rescale(d->out_exponent) * dl_scale(d->in0_exponent) / dl_scale(d->in1_exponent);
+    }
     int64_t oi = 0;
     for (int i3 = 0; i3 < os[0]; i3++)
         for (int i2 = 0; i2 < os[1]; i2++)
@@ -334,6 +351,49 @@ int oracle_eltwise(const espdl_eltwise_desc *d)
                                 v = (int32_t)v;
                         }
                         store_sat(d->output, odt, oi, v);
+                        break;
+                    }
+                    case ESPDL_ELT_MAX:   /* esp-dl/dl/base/dl_base_max.cpp:9-50: raw integers, exponents not looked at */
+                    case ESPDL_ELT_MIN: { /* esp-dl/dl/base/dl_base_min.cpp */
+                        const int64_t a = load_int(d->input0, idt, a_i), b = load_int(d->input1, idt, b_i);
+                        store_sat(d->output, odt, oi, d->op == ESPDL_ELT_MAX ? (a > b ? a : b) : (a < b ? a : b));
+                        break;
+                    }
+                    case ESPDL_ELT_DIV: { /* esp-dl/dl/base/dl_base_div.cpp:87-207 */
+                        const int64_t a = load_int(d->input0, idt, a_i), b = load_int(d->input1, idt, b_i);
+                        const int64_t hi = idt == ESPDL_DTYPE_INT8 ? INT8_MAX : INT16_MAX, lo = -hi - 1;
+                        if (div_table0) {
+                            const float a_f = (float)a * div_scale;
+                            store_sat(d->output, odt, oi, b == 0 ? (a_f > 0 ? hi : lo) : fround(a_f / (float)b, mode));
+                        } else if (a == 0) {
+                            store_sat(d->output, odt, oi, 0);
+                        } else if (b == 0) {
+                            store_sat(d->output, odt, oi, a > 0 ? hi : lo);
+                        } else if (div_n1) {
+                            const float rescale = div_scale / (float)b;
+                            store_sat(d->output, odt, oi, fround((float)a * rescale, mode));
+                        } else {
+                            const float scaled = (float)a * div_scale;
+                            store_sat(d->output, odt, oi, fround(scaled / (float)b, mode));
+                        }
+                        break;
+                    }
+                    case ESPDL_ELT_MOD: { /* esp-dl/dl/base/dl_base_mod.cpp:9-62 */
+                        const float a_val = (float)load_int(d->input0, idt, a_i) * dl_scale(d->in0_exponent);
+                        const float b_val = (float)load_int(d->input1, idt, b_i) * dl_scale(d->in1_exponent);
+                        const float r = b_val != 0.0f ? fmodf(a_val, b_val) : 0.0f;
+                        store_sat(d->output, odt, oi, fround(r * dl_rescale(d->out_exponent), mode));
+                        break;
+                    }
+                    case ESPDL_ELT_GREATER: /* esp-dl/dl/base/dl_base_greater.cpp:9-44 and its siblings: raw integers */
+                    case ESPDL_ELT_GREATER_EQUAL:
+                    case ESPDL_ELT_EQUAL:
+                    case ESPDL_ELT_LESS:
+                    case ESPDL_ELT_LESS_EQUAL: {
+                        const int64_t a = load_int(d->input0, idt, a_i), b = load_int(d->input1, idt, b_i);
+                        const int r = d->op == ESPDL_ELT_GREATER ? a > b : d->op == ESPDL_ELT_GREATER_EQUAL ? a >= b :
+                            d->op == ESPDL_ELT_EQUAL ? a == b : d->op == ESPDL_ELT_LESS ? a < b : a <= b;
+                        ((uint8_t *)d->output)[oi] = (uint8_t)r;
                         break;
                     }
                     default:

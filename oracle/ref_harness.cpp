@@ -25,11 +25,20 @@
 #include "dl_module_clip.hpp"
 #include "dl_module_concat.hpp"
 #include "dl_module_conv.hpp"
+#include "dl_module_div.hpp"
+#include "dl_module_equal.hpp"
+#include "dl_module_greater.hpp"
+#include "dl_module_greater_or_equal.hpp"
+#include "dl_module_less.hpp"
+#include "dl_module_less_or_equal.hpp"
 #include "dl_module_gemm.hpp"
 #include "dl_module_global_average_pool.hpp"
 #include "dl_module_lut.hpp"
 #include "dl_module_matmul.hpp"
+#include "dl_module_max.hpp"
 #include "dl_module_max_pool.hpp"
+#include "dl_module_min.hpp"
+#include "dl_module_mod.hpp"
 #include "dl_module_mul.hpp"
 #include "dl_module_pad.hpp"
 #include "dl_module_prelu.hpp"
@@ -57,7 +66,7 @@ static quant_type_t to_quant(int d)
 {
     return d == ESPDL_DTYPE_INT8 ? QUANT_TYPE_SYMM_8BIT : d == ESPDL_DTYPE_INT16 ? QUANT_TYPE_SYMM_16BIT : QUANT_TYPE_FLOAT32;
 }
-static size_t esize(int d) { return d == ESPDL_DTYPE_INT8 ? 1 : d == ESPDL_DTYPE_INT16 ? 2 : d == ESPDL_DTYPE_INT64 ? 8 : 4; }
+static size_t esize(int d) { return d == ESPDL_DTYPE_INT8 || d == ESPDL_DTYPE_BOOL ? 1 : d == ESPDL_DTYPE_INT16 ? 2 : d == ESPDL_DTYPE_INT64 ? 8 : 4; }
 
 static TensorBase *view(std::vector<int> shape, const void *p, int exponent, int dtype)
 {
@@ -137,13 +146,40 @@ int ref_eltwise(const espdl_eltwise_desc *d)
     switch (d->op) {
     case ESPDL_ELT_ADD:
     case ESPDL_ELT_SUB:
-    case ESPDL_ELT_MUL: {
+    case ESPDL_ELT_MUL:
+    case ESPDL_ELT_MAX:
+    case ESPDL_ELT_MIN:
+    case ESPDL_ELT_DIV:
+    case ESPDL_ELT_MOD:
+    case ESPDL_ELT_GREATER:
+    case ESPDL_ELT_GREATER_EQUAL:
+    case ESPDL_ELT_EQUAL:
+    case ESPDL_ELT_LESS:
+    case ESPDL_ELT_LESS_EQUAL: {
         std::unique_ptr<TensorBase> in1(view(s1, d->input1, d->in1_exponent, d->in_dtype));
         std::unique_ptr<module::Module> m;
         if (d->op == ESPDL_ELT_ADD)
             m.reset(new module::Add(nullptr, MODULE_NON_INPLACE, qt));
         else if (d->op == ESPDL_ELT_SUB)
             m.reset(new module::Sub(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_MAX)
+            m.reset(new module::Max(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_MIN)
+            m.reset(new module::Min(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_DIV)
+            m.reset(new module::Div(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_MOD)
+            m.reset(new module::Mod(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_GREATER)
+            m.reset(new module::Greater(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_GREATER_EQUAL)
+            m.reset(new module::GreaterOrEqual(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_EQUAL)
+            m.reset(new module::Equal(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_LESS)
+            m.reset(new module::Less(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_LESS_EQUAL)
+            m.reset(new module::LessOrEqual(nullptr, MODULE_NON_INPLACE, qt));
         else
             m.reset(new module::Mul(nullptr, MODULE_NON_INPLACE, qt));
         m->run({in0.get(), in1.get()}, {out.get()}, RUNTIME_MODE_SINGLE_CORE);

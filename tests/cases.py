@@ -8,7 +8,8 @@ import numpy as np
 
 from espdl_b200 import abi
 
-NP = {abi.DTYPE_INT8: np.int8, abi.DTYPE_INT16: np.int16, abi.DTYPE_FLOAT: np.float32}
+NP = {abi.DTYPE_INT8: np.int8, abi.DTYPE_INT16: np.int16, abi.DTYPE_FLOAT: np.float32, abi.DTYPE_BOOL: np.uint8}
+TWO_OPERAND_OPS = (abi.ELT_ADD, abi.ELT_MUL, abi.ELT_SUB) + tuple(range(abi.ELT_MAX, abi.ELT_LESS_EQUAL + 1))
 
 
 def conv_out(size, k, s, d, p0, p1):
@@ -97,8 +98,19 @@ def eltwise_case(op, seed=0, dtype=abi.DTYPE_INT8, out_shape=(2, 5, 7, 16), in0_
 
     a = rnd(in0_shape, in_dtype)
     b = None
-    if op in (abi.ELT_ADD, abi.ELT_MUL, abi.ELT_SUB):
+    if op in TWO_OPERAND_OPS:
         b = rnd(in1_shape, in_dtype)
+        if op in (abi.ELT_DIV, abi.ELT_MOD) or op >= abi.ELT_GREATER:
+            # zeros in both operands (division by zero, 0 / x, 0 / 0) and equal pairs for the comparisons
+            if a.size > 1:
+                a.reshape(-1)[rng.integers(0, a.size, size=max(a.size // 8, 1))] = 0
+            if b.size > 1:
+                b.reshape(-1)[rng.integers(0, b.size, size=max(b.size // 8, 1))] = 0
+            elif b.reshape(-1)[0] == 0:
+                b.reshape(-1)[0] = 3  # the reference's table for a zero scalar divisor converts an infinity to int
+            if op >= abi.ELT_GREATER and a.shape == b.shape:
+                idx = rng.integers(0, a.size, size=max(a.size // 6, 1))
+                b.reshape(-1)[idx] = a.reshape(-1)[idx]
     elif op == abi.ELT_LUT and in_dtype == abi.DTYPE_INT16:
         b = rng.integers(-32768, 32768, size=((65536 >> lut_shift) + 1,), dtype=np.int16)
         in1_shape = (1,) * len(out_shape)

@@ -24,6 +24,38 @@ def test_model_test_passes_on_shipped_golden_models(path, monkeypatch):
     m.close()
 
 
+@pytest.mark.parametrize("op_type,op,bool_out", [("Max", abi.ELT_MAX, False), ("Min", abi.ELT_MIN, False), ("Div", abi.ELT_DIV, False),
+                                                 ("Mod", abi.ELT_MOD, False), ("Greater", abi.ELT_GREATER, True),
+                                                 ("GreaterOrEqual", abi.ELT_GREATER_EQUAL, True), ("Equal", abi.ELT_EQUAL, True),
+                                                 ("Less", abi.ELT_LESS, True), ("LessOrEqual", abi.ELT_LESS_EQUAL, True)])
+@pytest.mark.parametrize("sa,sb", [((2, 6, 5, 16), (2, 6, 5, 16)), ((2, 6, 5, 16), (1, 1, 1, 16)), ((2, 6, 5, 16), (2, 6, 5, 1)), ((3, 1, 8), (4, 1))])
+def test_two_operand_modules(tmp_path, op_type, op, bool_out, sa, sb):
+    """Max / Min / Div / Mod and the comparisons loaded from a one-node .espdl graph and run through the C++ module
+    (the module merges the broadcast shapes before it fills the descriptor) against the oracle on the unmerged shapes."""
+    import cases
+    e_a, e_b, e_out = -5, -4, -6
+    so = list(np.broadcast_shapes(sa, sb))
+    g = espdl_file.GraphBuilder("two", metadata={"target": "c"})
+    g.add_input("a", np.int8, list(sa), e_a)
+    g.add_input("b", np.int8, list(sb), e_b)
+    g.add_node(op_type, "n", ["a", "b"], ["y"], quant_type="S8")
+    g.add_output("y", np.bool_ if bool_out else np.int8, so, 0 if bool_out else e_out)
+    path = str(tmp_path / "two.espdl")
+    g.save(path)
+    m = model.Model(path)
+    nd = len(so)
+    case = cases.eltwise_case(op, seed=31, in_dtype=abi.DTYPE_INT8, out_dtype=abi.DTYPE_BOOL if bool_out else abi.DTYPE_INT8, out_shape=tuple(so),
+                              in0_shape=(1,) * (nd - len(sa)) + tuple(sa), in1_shape=(1,) * (nd - len(sb)) + tuple(sb), e0=e_a, e1=e_b,
+                              eo=0 if bool_out else e_out)
+    ins = {t.name: t for t in m.inputs}
+    ins["a"].array[...] = case["a"].reshape(sa)
+    ins["b"].array[...] = case["b"].reshape(sb)
+    m.run()
+    assert __import__("checkers").oracle().oracle_eltwise(cases.eltwise_desc(case)) == 0
+    np.testing.assert_array_equal(np.asarray(m.outputs[0].array).view(np.uint8 if bool_out else np.int8).reshape(so), case["out"])
+    m.close()
+
+
 def run_and_compare(tmp_path, g, batch, seed, check_intermediates):
     path = str(tmp_path / "net.espdl")
     g.save(path)

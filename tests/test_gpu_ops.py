@@ -122,6 +122,47 @@ def run_eltwise(case, inplace=None):
     return got, want
 
 
+BROADCASTS = [
+    ((2, 5, 7, 16), None, None), ((2, 5, 7, 16), (2, 5, 7, 16), (1, 1, 1, 16)), ((2, 5, 7, 16), (2, 5, 7, 16), (1, 1, 1, 1)),
+    ((2, 5, 7, 16), (1, 1, 1, 1), (2, 5, 7, 16)), ((2, 5, 7, 16), (2, 5, 7, 1), (2, 5, 7, 16)), ((2, 5, 7, 16), (2, 5, 7, 16), (2, 5, 7, 1)),
+    ((2, 5, 7, 16), (2, 1, 7, 1), (1, 5, 1, 16)), ((2, 5, 7, 1), (2, 5, 7, 1), (1, 5, 1, 1)), ((3, 20), (3, 1), (1, 20)), ((37,), None, None),
+    ((1,), None, None),
+]
+
+
+@pytest.mark.parametrize("round_mode", [abi.ROUND_HALF_UP, abi.ROUND_HALF_EVEN])
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("op", [abi.ELT_MAX, abi.ELT_MIN, abi.ELT_DIV, abi.ELT_MOD])
+@pytest.mark.parametrize("shapes", BROADCASTS)
+def test_max_min_div_mod(op, dtype, shapes, round_mode):
+    e = dict(e0=-5, e1=-5, eo=-5)
+    if op == abi.ELT_DIV:
+        e = dict(e0=-5, e1=-4, eo=-6) if dtype == abi.DTYPE_INT8 else dict(e0=-12, e1=-9, eo=-10)
+    if op == abi.ELT_MOD:
+        e = dict(e0=-5, e1=-6, eo=-6) if dtype == abi.DTYPE_INT8 else dict(e0=-12, e1=-13, eo=-11)
+    case = cases.eltwise_case(op, seed=23, dtype=dtype, out_shape=shapes[0], in0_shape=shapes[1], in1_shape=shapes[2], round_mode=round_mode, **e)
+    got, want = run_eltwise(case)
+    np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("op", [abi.ELT_GREATER, abi.ELT_GREATER_EQUAL, abi.ELT_EQUAL, abi.ELT_LESS, abi.ELT_LESS_EQUAL])
+@pytest.mark.parametrize("shapes", BROADCASTS[:3] + BROADCASTS[6:10])
+def test_comparisons(op, dtype, shapes):
+    case = cases.eltwise_case(op, seed=29, in_dtype=dtype, out_dtype=abi.DTYPE_BOOL, out_shape=shapes[0], in0_shape=shapes[1],
+                              in1_shape=shapes[2], e0=-5, e1=-5, eo=0)
+    got, want = run_eltwise(case)
+    np.testing.assert_array_equal(got, want)
+    assert op == abi.ELT_EQUAL or (want.any() and not want.all())
+
+
+def test_comparison_needs_a_bool_output():
+    case = cases.eltwise_case(abi.ELT_LESS, seed=1)
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input0=dev.upload(case["a"]), input1=dev.upload(case["b"]), output=dev.upload(case["out"]))
+        assert dev.lib.espdl_b200_eltwise(C.byref(cases.eltwise_desc(case, ptrs)), None) == abi.ERR_UNSUPPORTED
+
+
 @pytest.mark.parametrize("round_mode", [abi.ROUND_HALF_UP, abi.ROUND_HALF_EVEN])
 @pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
 @pytest.mark.parametrize("op", [abi.ELT_ADD, abi.ELT_SUB, abi.ELT_MUL])

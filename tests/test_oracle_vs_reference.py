@@ -109,6 +109,46 @@ def test_binary_matches_reference(op, dtype, shapes):
     assert a.std() > 0
 
 
+BROADCASTS = [
+    ((2, 5, 7, 16), None, None),
+    ((2, 5, 7, 16), (2, 5, 7, 16), (1, 1, 1, 16)),
+    ((2, 5, 7, 16), (2, 5, 7, 16), (1, 1, 1, 1)),      # scalar divisor: a * (R / b), tabulated for int8
+    ((2, 5, 7, 16), (1, 1, 1, 1), (2, 5, 7, 16)),      # scalar dividend: tabulated by divisor for int8
+    ((2, 5, 7, 16), (2, 5, 7, 1), (2, 5, 7, 16)),      # dividend broadcast along the innermost axis
+    ((2, 5, 7, 16), (2, 5, 7, 16), (2, 5, 7, 1)),      # divisor broadcast along the innermost axis
+    ((2, 5, 7, 16), (2, 1, 7, 1), (1, 5, 1, 16)),
+    ((2, 5, 7, 1), (2, 5, 7, 1), (1, 5, 1, 1)),
+    ((3, 20), (3, 1), (1, 20)),
+    ((37,), None, None),
+    ((1,), None, None),
+]
+
+
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("op", [abi.ELT_MAX, abi.ELT_MIN, abi.ELT_DIV, abi.ELT_MOD])
+@pytest.mark.parametrize("shapes", BROADCASTS)
+def test_max_min_div_mod_match_reference(op, dtype, shapes):
+    e = dict(e0=-5, e1=-5, eo=-5)
+    if op == abi.ELT_DIV:
+        e = dict(e0=-5, e1=-4, eo=-6) if dtype == abi.DTYPE_INT8 else dict(e0=-12, e1=-9, eo=-10)
+    if op == abi.ELT_MOD:
+        e = dict(e0=-5, e1=-6, eo=-6) if dtype == abi.DTYPE_INT8 else dict(e0=-12, e1=-13, eo=-11)
+    case = cases.eltwise_case(op, seed=23, dtype=dtype, out_shape=shapes[0], in0_shape=shapes[1], in1_shape=shapes[2], **e)
+    a, b = run_elt_both(case)
+    np.testing.assert_array_equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("op", [abi.ELT_GREATER, abi.ELT_GREATER_EQUAL, abi.ELT_EQUAL, abi.ELT_LESS, abi.ELT_LESS_EQUAL])
+@pytest.mark.parametrize("shapes", BROADCASTS[:3] + BROADCASTS[6:10])
+def test_comparisons_match_reference(op, dtype, shapes):
+    case = cases.eltwise_case(op, seed=29, in_dtype=dtype, out_dtype=abi.DTYPE_BOOL, out_shape=shapes[0], in0_shape=shapes[1],
+                              in1_shape=shapes[2], e0=-5, e1=-5, eo=0)
+    a, b = run_elt_both(case)
+    np.testing.assert_array_equal(a, b)
+    assert set(np.unique(a)) <= {0, 1}
+
+
 @pytest.mark.parametrize("idt,odt,e0,eo", [
     (abi.DTYPE_INT8, abi.DTYPE_INT8, -4, -2), (abi.DTYPE_INT8, abi.DTYPE_INT8, -4, -6), (abi.DTYPE_INT8, abi.DTYPE_INT8, -4, -4),
     (abi.DTYPE_INT16, abi.DTYPE_INT16, -10, -7), (abi.DTYPE_INT16, abi.DTYPE_INT8, -10, -5), (abi.DTYPE_INT8, abi.DTYPE_INT16, -5, -10),
