@@ -122,7 +122,7 @@ class ReduceDesc(C.Structure):
                 ("reduce", i32 * 6), ("in_exponent", i32), ("out_exponent", i32), ("round_mode", i32)]
 
 
-REDUCE_MEAN, REDUCE_SUM, REDUCE_MAX, REDUCE_MIN = range(4)
+REDUCE_MEAN, REDUCE_SUM, REDUCE_MAX, REDUCE_MIN, REDUCE_L1, REDUCE_SUM_SQUARE, REDUCE_L2 = range(7)
 
 
 class PadDesc(C.Structure):

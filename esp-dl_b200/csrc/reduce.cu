@@ -1,4 +1,5 @@
-// Reductions over any set of axes of an int8 / int16 tensor: ReduceMean, ReduceSum, ReduceMax, ReduceMin.
+// Reductions over any set of axes of an int8 / int16 tensor: ReduceMean, ReduceSum, ReduceMax, ReduceMin, ReduceL1,
+// ReduceSumSquare, ReduceL2 (dl_module_reduce_l1.hpp, dl_module_reduce_sum_square.hpp, dl_module_reduce_l2.hpp).
 // Replaces dl::module::ReduceBase::forward_template and the reduce functions of the modules built on it
 // (esp-dl/dl/module/include/dl_module_reduce_base.hpp:121-262, dl_module_reduce_mean.hpp:17-45, dl_module_reduce_sum.hpp:
 // 17-42).  A thread owns one output element and walks the reduced axes; with channels innermost and kept (the usual
@@ -41,6 +42,10 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
                 acc = acc > v ? acc : v;
             else if (p.op == ESPDL_REDUCE_MIN)
                 acc = acc < v ? acc : v;
+            else if (p.op == ESPDL_REDUCE_L1)
+                acc += v < 0 ? -v : v;
+            else if (p.op == ESPDL_REDUCE_SUM_SQUARE || p.op == ESPDL_REDUCE_L2)
+                acc += (ACC)((int)v * (int)v);
             else
                 acc += v;
             for (int r = p.nr - 1; r >= 0; r--) { // odometer over the reduced axes
@@ -58,8 +63,21 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
             f = __fdiv_rn(f, (float)(unsigned long long)p.count);
             f = __fmul_rn(f, dl_rescale(p.e_out));
             q = fround(f, p.half_even);
-        } else if (p.op == ESPDL_REDUCE_SUM) {
-            const int shift = max(-62, min(62, p.e_out - p.e_in));
+        } else if (p.op == ESPDL_REDUCE_L2) {
+            // math::sqrt_newton (dl_math.hpp:83-97): r = (r + x / r) * 0.5 until |r - last| <= 1e-5, every step rounded to fp32
+            const float x = __fmul_rn(sizeof(ACC) == 4 ? __int2float_rn((int)acc) : __ll2float_rn((long long)acc), dl_scale(2 * p.e_in));
+            float r = x;
+            if (x != 0.f) {
+                for (int it = 0; it < 100; it++) {
+                    const float last = r;
+                    r = __fmul_rn(__fadd_rn(last, __fdiv_rn(x, last)), 0.5f);
+                    if (!(fabsf(__fsub_rn(r, last)) > 0.00001f))
+                        break;
+                }
+            }
+            q = fround(__fmul_rn(r, dl_rescale(p.e_out)), p.half_even);
+        } else if (p.op == ESPDL_REDUCE_SUM || p.op == ESPDL_REDUCE_L1 || p.op == ESPDL_REDUCE_SUM_SQUARE) {
+            const int shift = max(-62, min(62, p.e_out - (p.op == ESPDL_REDUCE_SUM_SQUARE ? 2 * p.e_in : p.e_in)));
             q = sizeof(ACC) == 4 ? (long long)shift_round32((int32_t)acc, max(-31, min(31, shift)), p.half_even)
                                  : shift_round64((long long)acc, shift, p.half_even);
         } else {
@@ -73,7 +91,7 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
 
 int reduce_op(const espdl_reduce_desc &d, cudaStream_t s)
 {
-    if (!d.input || !d.output || d.ndim < 1 || d.ndim > 6 || d.op < 0 || d.op > 3)
+    if (!d.input || !d.output || d.ndim < 1 || d.ndim > 6 || d.op < 0 || d.op > ESPDL_REDUCE_L2)
         return ESPDL_ERR_INVALID_ARG;
     if (d.dtype != ESPDL_DTYPE_INT8 && d.dtype != ESPDL_DTYPE_INT16)
         return ESPDL_ERR_UNSUPPORTED;

@@ -1265,7 +1265,12 @@ Module *Reduce::deserialize(fbs::FbsModel *m, std::string node)
 {
     // ReduceBase::get_attributes, dl_module_reduce_base.hpp:265-298
     const std::string type = m->get_operation_type(node);
-    int op = type == "ReduceMean" ? ESPDL_REDUCE_MEAN : (type == "ReduceSum" ? ESPDL_REDUCE_SUM : (type == "ReduceMax" ? ESPDL_REDUCE_MAX : ESPDL_REDUCE_MIN));
+    int op = ESPDL_REDUCE_MIN;
+    for (auto &kv : std::initializer_list<std::pair<const char *, int>>{{"ReduceMean", ESPDL_REDUCE_MEAN}, {"ReduceSum", ESPDL_REDUCE_SUM},
+                                                                       {"ReduceMax", ESPDL_REDUCE_MAX}, {"ReduceL1", ESPDL_REDUCE_L1},
+                                                                       {"ReduceSumSquare", ESPDL_REDUCE_SUM_SQUARE}, {"ReduceL2", ESPDL_REDUCE_L2}})
+        if (type == kv.first)
+            op = kv.second;
     int keepdims = 1, noop = 0;
     m->get_operation_attribute(node, "keepdims", keepdims);
     m->get_operation_attribute(node, "noop_with_empty_axes", noop);
@@ -1657,7 +1662,7 @@ void ModuleCreator::register_dl_modules()
     for (const char *op : {"LUT", "Swish", "Sigmoid", "Tanh", "HardSwish", "HardSigmoid", "Gelu", "Elu", "LeakyRelu", "Exp", "Log", "Sqrt",
                            "Neg", "Abs"})
         register_module(op, LUT::deserialize);
-    for (const char *op : {"ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin"}) register_module(op, Reduce::deserialize);
+    for (const char *op : {"ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin", "ReduceL1", "ReduceSumSquare", "ReduceL2"}) register_module(op, Reduce::deserialize);
     register_module("Slice", Slice::deserialize);
     register_module("Pad", Pad::deserialize);
     register_module("Clip", Clip::deserialize);

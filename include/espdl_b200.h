@@ -428,7 +428,17 @@ int espdl_b200_detect_candidates(const espdl_detect_desc *desc, void *stream);
  * 121-262 with dl_module_reduce_mean.hpp:17-45, dl_module_reduce_sum.hpp:17-42, dl_module_reduce_max.hpp, _min.hpp).
  * int8 sums in int32, int16 sums in int64.  Mean: round(sum * 2^e_in / count * 2^-e_out) in fp32, in that order;
  * sum: shift_and_round(sum, e_out - e_in); max/min: the code itself.  All saturate to the output type. */
-typedef enum { ESPDL_REDUCE_MEAN = 0, ESPDL_REDUCE_SUM = 1, ESPDL_REDUCE_MAX = 2, ESPDL_REDUCE_MIN = 3 } espdl_reduce_op_t;
+typedef enum {
+    ESPDL_REDUCE_MEAN = 0,
+    ESPDL_REDUCE_SUM = 1,
+    ESPDL_REDUCE_MAX = 2,
+    ESPDL_REDUCE_MIN = 3,
+    ESPDL_REDUCE_L1 = 4,         /* shift_and_round(sum |x|, e_out - e_in)      esp-dl/dl/module/include/dl_module_reduce_l1.hpp:18-50 */
+    ESPDL_REDUCE_SUM_SQUARE = 5, /* shift_and_round(sum x*x, e_out - 2*e_in)    esp-dl/dl/module/include/dl_module_reduce_sum_square.hpp:18-45 */
+    ESPDL_REDUCE_L2 = 6          /* round(sqrt_newton(sum x*x * 2^(2*e_in)) * 2^-e_out), the Newton iteration of
+                                    esp-dl/dl/math/include/dl_math.hpp:83-97 in fp32 (at most 100 steps here)
+                                    esp-dl/dl/module/include/dl_module_reduce_l2.hpp:17-48 */
+} espdl_reduce_op_t;
 
 typedef struct espdl_reduce_desc {
     const void *input;

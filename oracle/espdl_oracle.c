@@ -832,9 +832,15 @@ int oracle_reduce(const espdl_reduce_desc *d)
                 acc = acc > v ? acc : v;
             else if (d->op == ESPDL_REDUCE_MIN)
                 acc = acc < v ? acc : v;
+            else if (d->op == ESPDL_REDUCE_L1) /* esp-dl/dl/module/include/dl_module_reduce_l1.hpp:18-21 */
+                acc += v < 0 ? -v : v;
+            else if (d->op == ESPDL_REDUCE_SUM_SQUARE || d->op == ESPDL_REDUCE_L2) /* dl_module_reduce_base.hpp:77-80 */
+                acc += v * v;
             else
                 acc += v;
         }
+        if (is8)
+            acc = (int32_t)acc; /* the int8 accumulator is an int32_t */
         int64_t q = acc;
         if (d->op == ESPDL_REDUCE_MEAN) {
             /* tool::round(tmp * input_scale / count * output_scale): the sum is an int32 (int8) or int64 (int16) */
@@ -843,8 +849,24 @@ int oracle_reduce(const espdl_reduce_desc *d)
             f = f / (float)(size_t)count;
             f = f * dl_rescale(d->out_exponent);
             q = fround(f, d->round_mode);
-        } else if (d->op == ESPDL_REDUCE_SUM) {
+        } else if (d->op == ESPDL_REDUCE_SUM || d->op == ESPDL_REDUCE_L1) {
             q = shift_and_round(acc, d->out_exponent - d->in_exponent, d->round_mode, is8 ? 32 : 64);
+        } else if (d->op == ESPDL_REDUCE_SUM_SQUARE) { /* esp-dl/dl/module/include/dl_module_reduce_sum_square.hpp:36-39 */
+            q = shift_and_round(acc, d->out_exponent - 2 * d->in_exponent, d->round_mode, is8 ? 32 : 64);
+        } else if (d->op == ESPDL_REDUCE_L2) {
+            /* esp-dl/dl/module/include/dl_module_reduce_l2.hpp:37-42 with math::sqrt_newton, esp-dl/dl/math/include/
+             * dl_math.hpp:83-97 (the iteration is capped at 100 steps here; it ends by itself long before) */
+            const float x = (is8 ? (float)(int32_t)acc : (float)acc) * dl_scale(2 * d->in_exponent);
+            float r = x;
+            if (x != 0.f) {
+                for (int it = 0; it < 100; it++) {
+                    const float last = r;
+                    r = (float)((last + x / last) * 0.5);
+                    if (!(fabsf(r - last) > 0.00001f))
+                        break;
+                }
+            }
+            q = fround(r * dl_rescale(d->out_exponent), d->round_mode);
         }
         store_sat(d->output, d->dtype, o, q);
     }

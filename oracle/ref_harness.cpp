@@ -42,10 +42,13 @@
 #include "dl_module_mul.hpp"
 #include "dl_module_pad.hpp"
 #include "dl_module_prelu.hpp"
+#include "dl_module_reduce_l1.hpp"
+#include "dl_module_reduce_l2.hpp"
 #include "dl_module_reduce_max.hpp"
 #include "dl_module_reduce_mean.hpp"
 #include "dl_module_reduce_min.hpp"
 #include "dl_module_reduce_sum.hpp"
+#include "dl_module_reduce_sum_square.hpp"
 #include "dl_module_relu.hpp"
 #include "dl_module_requantize_linear.hpp"
 #include "dl_module_resize.hpp"
@@ -333,6 +336,12 @@ int ref_reduce(const espdl_reduce_desc *d)
         m.reset(new module::ReduceSum(1, flags, "ReduceSum", "reduce", MODULE_NON_INPLACE, q));
     else if (d->op == ESPDL_REDUCE_MAX)
         m.reset(new module::ReduceMax(1, flags, "ReduceMax", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_L1)
+        m.reset(new module::ReduceL1(1, flags, "ReduceL1", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_SUM_SQUARE)
+        m.reset(new module::ReduceSumSquare(1, flags, "ReduceSumSquare", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_L2)
+        m.reset(new module::ReduceL2(1, flags, "ReduceL2", "reduce", MODULE_NON_INPLACE, q));
     else
         m.reset(new module::ReduceMin(1, flags, "ReduceMin", "reduce", MODULE_NON_INPLACE, q));
     std::vector<std::vector<int>> in_shapes = {shape};

@@ -1,4 +1,4 @@
-"""ReduceMean / ReduceSum / ReduceMax / ReduceMin: the oracle against the reference's own modules compiled for the
+"""ReduceMean / ReduceSum / ReduceMax / ReduceMin / ReduceL1 / ReduceSumSquare / ReduceL2: the oracle against the reference's own modules compiled for the
 host (pin), the CUDA kernel against the oracle."""
 import ctypes as C
 
@@ -30,7 +30,7 @@ def make(op, dtype, shape, axes, e_in, e_out, seed, inp=None, out=None):
     return d, x, y
 
 
-CASES = [(op, dt, sh, ax) for op in range(4) for dt in (abi.DTYPE_INT8, abi.DTYPE_INT16) for sh, ax in SHAPES]
+CASES = [(op, dt, sh, ax) for op in range(7) for dt in (abi.DTYPE_INT8, abi.DTYPE_INT16) for sh, ax in SHAPES]
 
 
 def exps(op, dt):
@@ -38,6 +38,12 @@ def exps(op, dt):
         return (-7, -3) if dt == abi.DTYPE_INT8 else (-14, -9)
     if op == abi.REDUCE_MEAN:
         return (-6, -7) if dt == abi.DTYPE_INT8 else (-12, -13)
+    if op == abi.REDUCE_L1:
+        return (-6, -1) if dt == abi.DTYPE_INT8 else (-14, -8)
+    if op == abi.REDUCE_SUM_SQUARE:
+        return (-6, 0) if dt == abi.DTYPE_INT8 else (-14, -7)
+    if op == abi.REDUCE_L2:
+        return (-6, -3) if dt == abi.DTYPE_INT8 else (-14, -11)
     return (-5, -5)
 
 
