@@ -133,6 +133,11 @@ class PadDesc(C.Structure):
 PAD_CONSTANT, PAD_EDGE, PAD_REFLECT = range(3)
 
 
+class GatherDesc(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("indices", C.c_void_p), ("elem_size", i32), ("num_indices", i32),
+                ("outer", C.c_int64), ("axis_size", C.c_int64), ("inner", C.c_int64)]
+
+
 # every symbol include/espdl_b200.h declares: name -> (restype, argtypes)
 SYMBOLS = {
     "espdl_b200_init": (C.c_int, [C.c_int]),
@@ -180,6 +185,7 @@ SYMBOLS = {
     "espdl_b200_detect_candidates": (C.c_int, [C.POINTER(DetectDesc), C.c_void_p]),
     "espdl_b200_reduce": (C.c_int, [C.POINTER(ReduceDesc), C.c_void_p]),
     "espdl_b200_pad": (C.c_int, [C.POINTER(PadDesc), C.c_void_p]),
+    "espdl_b200_gather": (C.c_int, [C.POINTER(GatherDesc), C.c_void_p]),
 }
 
 _lib = None

@@ -352,6 +352,45 @@ extern "C" int espdl_b200_resize(const espdl_resize_desc *d, void *stream)
     return check_launch("resize");
 }
 
+// Gather along one axis (dl_module_gather.hpp:66-96): rows of `inner` elements picked by index.  A thread moves one
+// unit of the row: 16 bytes when rows and pointers allow it, else one element.
+template <typename U>
+__global__ void __launch_bounds__(256) gather_kernel(const U *in, U *out, const int *indices, int num, long long outer, long long axis, long long inner)
+{
+    const long long total = outer * num * inner;
+    for (long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+        const long long col = t % inner, row = t / inner;
+        const int idx = indices[row % num];
+        if (idx >= 0 && idx < axis)
+            out[t] = in[((row / num) * axis + idx) * inner + col];
+    }
+}
+
+extern "C" int espdl_b200_gather(const espdl_gather_desc *d, void *stream)
+{
+    if (!d || !d->input || !d->output || !d->indices || d->num_indices < 0 || d->outer < 0 || d->axis_size <= 0 || d->inner < 0)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d->elem_size != 1 && d->elem_size != 2 && d->elem_size != 4 && d->elem_size != 8)
+        return ESPDL_ERR_INVALID_ARG;
+    long long inner = d->inner;
+    int es = d->elem_size;
+    if (d->outer * d->num_indices * inner == 0)
+        return ESPDL_OK;
+    while (es < 16 && inner % 2 == 0 && ((uintptr_t)d->input % (es * 2)) == 0 && ((uintptr_t)d->output % (es * 2)) == 0) inner /= 2, es *= 2;
+    const long long total = d->outer * d->num_indices * inner;
+    const unsigned blocks = (unsigned)min((total + 255) / 256, (long long)num_sms() * 32);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (es) {
+    case 1: gather_kernel<uint8_t><<<blocks, 256, 0, s>>>((const uint8_t *)d->input, (uint8_t *)d->output, d->indices, d->num_indices, d->outer, d->axis_size, inner); break;
+    case 2: gather_kernel<uint16_t><<<blocks, 256, 0, s>>>((const uint16_t *)d->input, (uint16_t *)d->output, d->indices, d->num_indices, d->outer, d->axis_size, inner); break;
+    case 4: gather_kernel<uint32_t><<<blocks, 256, 0, s>>>((const uint32_t *)d->input, (uint32_t *)d->output, d->indices, d->num_indices, d->outer, d->axis_size, inner); break;
+    case 8: gather_kernel<uint2><<<blocks, 256, 0, s>>>((const uint2 *)d->input, (uint2 *)d->output, d->indices, d->num_indices, d->outer, d->axis_size, inner); break;
+    default: gather_kernel<uint4><<<blocks, 256, 0, s>>>((const uint4 *)d->input, (uint4 *)d->output, d->indices, d->num_indices, d->outer, d->axis_size, inner); break;
+    }
+    count_launch();
+    return check_launch("gather");
+}
+
 extern "C" int espdl_b200_copy(const espdl_copy_desc *d, void *stream)
 {
     if (!d || !d->src || !d->dst || d->ndim < 1 || d->ndim > 6)

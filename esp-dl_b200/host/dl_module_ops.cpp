@@ -1471,6 +1471,165 @@ Module *Transpose::deserialize(fbs::FbsModel *m, std::string node)
     return new Transpose(node.c_str(), MODULE_NON_INPLACE, node_quant(m, node), perm);
 }
 
+// --------------------------------------------------------------------------------- SpaceToDepth / DepthToSpace / Gather
+std::vector<std::vector<int>> SpaceToDepth::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> in = input_shapes[0], out = in;
+    if (in.size() != 4 || m_blocksize < 1 || in[1] % m_blocksize || in[2] % m_blocksize) {
+        ESP_LOGE("SpaceToDepth", "input must be [N, H, W, C] with H and W divisible by blocksize %d", m_blocksize);
+        return {in};
+    }
+    out[1] = in[1] / m_blocksize, out[2] = in[2] / m_blocksize, out[3] = in[3] * m_blocksize * m_blocksize;
+    return {out};
+}
+
+void SpaceToDepth::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!in || !out || !in->device || !out->device || in->shape.size() != 4 || out->shape.size() != 4) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st && (in->shape[1] % m_blocksize || in->shape[2] % m_blocksize || in->get_size() != out->get_size()))
+        st = ESPDL_ERR_INVALID_ARG;
+    if (!st) {
+        // out[n][oh][ow][c][hb][wb] = in[n][oh*bs + hb][ow*bs + wb][c]  (dl_module_space_to_depth.hpp:31-40)
+        const long long bs = m_blocksize, W = in->shape[2], Cc = in->shape[3], H = in->shape[1];
+        const std::vector<int> shape = {in->shape[0], (int)(H / bs), (int)(W / bs), (int)Cc, (int)bs, (int)bs};
+        const std::vector<long long> ss = {H * W * Cc, bs * W * Cc, bs * Cc, 1, W * Cc, Cc};
+        st = enqueue_copy(context, in->device, out->device, (int)dtype_sizeof(in->dtype), shape, ss, dense_strides(shape));
+    }
+    if (st)
+        ESP_LOGE("SpaceToDepth", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *SpaceToDepth::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int blocksize = 2;
+    m->get_operation_attribute(node, "blocksize", blocksize);
+    return new SpaceToDepth(blocksize, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+std::vector<std::vector<int>> DepthToSpace::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> in = input_shapes[0], out = in;
+    if (in.size() != 4 || m_blocksize < 1 || in[3] % (m_blocksize * m_blocksize)) {
+        ESP_LOGE("DepthToSpace", "input must be [N, H, W, C] with C divisible by blocksize^2");
+        return {in};
+    }
+    out[1] = in[1] * m_blocksize, out[2] = in[2] * m_blocksize, out[3] = in[3] / (m_blocksize * m_blocksize);
+    return {out};
+}
+
+void DepthToSpace::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!in || !out || !in->device || !out->device || in->shape.size() != 4 || out->shape.size() != 4) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    const long long bs = m_blocksize;
+    if (!st && (in->shape[3] % (bs * bs) || in->get_size() != out->get_size()))
+        st = ESPDL_ERR_INVALID_ARG;
+    const bool crd = m_mode == "CRD";
+    if (!st && !crd && in->shape[3] / (bs * bs) != bs) // see the class comment
+        st = ESPDL_ERR_UNSUPPORTED;
+    if (!st) {
+        // out[n][h][hb][w][wb][co] = in[n][h][w][c], c = co*bs*bs + hb*bs + wb (CRD) or hb*bs*bs + wb*bs + co (DCR, co < bs)
+        const long long H = in->shape[1], W = in->shape[2], Cc = in->shape[3], Co = Cc / (bs * bs);
+        const std::vector<int> shape = {in->shape[0], (int)H, (int)bs, (int)W, (int)bs, (int)Co};
+        const std::vector<long long> ss = crd ? std::vector<long long>{H * W * Cc, W * Cc, bs, Cc, 1, bs * bs}
+                                              : std::vector<long long>{H * W * Cc, W * Cc, bs * bs, Cc, bs, 1};
+        st = enqueue_copy(context, in->device, out->device, (int)dtype_sizeof(in->dtype), shape, ss, dense_strides(shape));
+    }
+    if (st)
+        ESP_LOGE("DepthToSpace", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *DepthToSpace::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int blocksize = 2;
+    std::string mode;
+    m->get_operation_attribute(node, "blocksize", blocksize);
+    m->get_operation_attribute(node, "mode", mode);
+    return new DepthToSpace(blocksize, mode.empty() ? "DCR" : mode, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+Gather::~Gather()
+{
+    delete m_indices;
+    delete m_dev_indices;
+}
+
+std::vector<std::vector<int>> Gather::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    const std::vector<int> &in = input_shapes[0];
+    if (m_axis < 0)
+        m_axis += (int)in.size();
+    std::vector<int> out;
+    for (int i = 0; i < (int)in.size(); i++) {
+        if (i == m_axis && m_indices)
+            out.insert(out.end(), m_indices->shape.begin(), m_indices->shape.end());
+        else
+            out.push_back(in[i]);
+    }
+    return {out};
+}
+
+esp_err_t Gather::prepare(ModelContext *context)
+{
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    if (!in || !m_indices || m_axis < 0 || m_axis >= (int)in->shape.size())
+        return ESP_FAIL;
+    if (m_indices->dtype != DATA_TYPE_INT64 && m_indices->dtype != DATA_TYPE_INT32)
+        return ESP_FAIL;
+    std::vector<int32_t> idx(m_indices->get_size());
+    for (int i = 0; i < m_indices->get_size(); i++) {
+        const long long v = m_indices->dtype == DATA_TYPE_INT64 ? (long long)m_indices->get_element<int64_t>(i) : m_indices->get_element<int32_t>(i);
+        if (v < 0 || v >= in->shape[m_axis]) { // the reference would read outside the tensor
+            ESP_LOGE("Gather", "%s: index %lld outside [0, %d)", name ? name : "?", v, in->shape[m_axis]);
+            return ESP_FAIL;
+        }
+        idx[i] = (int32_t)v;
+    }
+    delete m_dev_indices;
+    m_dev_indices = new TensorBase({(int)idx.size()}, idx.data(), 0, DATA_TYPE_INT32, true);
+    if (m_dev_indices->to_device() != ESP_OK || espdl_b200_stream_sync(nullptr) != ESPDL_OK)
+        return ESP_FAIL;
+    return ESP_OK;
+}
+
+void Gather::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!in || !out || !in->device || !out->device || !m_dev_indices || !m_dev_indices->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st) {
+        espdl_gather_desc d;
+        memset(&d, 0, sizeof(d));
+        d.input = in->device, d.output = out->device, d.indices = (const int32_t *)m_dev_indices->device;
+        d.elem_size = (int)dtype_sizeof(in->dtype), d.num_indices = m_dev_indices->get_size();
+        d.outer = 1, d.inner = 1, d.axis_size = in->shape[m_axis];
+        for (int i = 0; i < m_axis; i++) d.outer *= in->shape[i];
+        for (size_t i = m_axis + 1; i < in->shape.size(); i++) d.inner *= in->shape[i];
+        st = espdl_b200_gather(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Gather", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *Gather::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int axis = 0;
+    m->get_operation_attribute(node, "axis", axis);
+    TensorBase *indices = m->get_operation_parameter(node, 1);
+    if (!indices)
+        return nullptr;
+    return new Gather(indices, axis, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
+}
+
 std::vector<std::vector<int>> Reshape::get_output_shape(std::vector<std::vector<int>> &input_shapes)
 {
     std::vector<int> in = input_shapes[0], out;
@@ -1675,6 +1834,9 @@ void ModuleCreator::register_dl_modules()
     register_module("Concat", Concat::deserialize);
     register_module("Split", Split::deserialize);
     register_module("Transpose", Transpose::deserialize);
+    register_module("SpaceToDepth", SpaceToDepth::deserialize);
+    register_module("DepthToSpace", DepthToSpace::deserialize);
+    register_module("Gather", Gather::deserialize);
     register_module("Reshape", Reshape::deserialize_reshape);
     register_module("Flatten", Reshape::deserialize_flatten);
     register_module("Squeeze", Reshape::deserialize_squeeze);

@@ -341,6 +341,60 @@ protected:
     std::vector<int> m_perm;
 };
 
+/// SpaceToDepth (dl_module_space_to_depth.hpp) and DepthToSpace "DCR" / "CRD" (dl_module_depth_to_space.hpp) of an NHWC
+/// tensor: one launch of the strided-copy kernel over a six-axis view.  The reference's DCR index rule addresses the output
+/// consistently only when the output has `blocksize` channels; any other DCR shape fails with ESPDL_ERR_UNSUPPORTED.
+class SpaceToDepth : public Module {
+public:
+    SpaceToDepth(int blocksize = 2, const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+                 quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, inplace, quant_type), m_blocksize(blocksize)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int m_blocksize;
+};
+class DepthToSpace : public Module {
+public:
+    DepthToSpace(int blocksize = 2, std::string mode = "DCR", const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+                 quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, inplace, quant_type), m_blocksize(blocksize), m_mode(mode)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int m_blocksize;
+    std::string m_mode;
+};
+
+/// Gather along one axis with constant indices (dl_module_gather.hpp): the module owns `indices` (int32 or int64, any
+/// shape); prepare() checks them against the axis length and uploads them as int32.
+class Gather : public Module {
+public:
+    Gather(TensorBase *indices, int axis = 0, const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+           quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, inplace, quant_type), m_indices(indices), m_axis(axis), m_dev_indices(nullptr)
+    {
+    }
+    ~Gather();
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    esp_err_t prepare(ModelContext *context) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    TensorBase *m_indices;
+    int m_axis;
+    TensorBase *m_dev_indices; ///< the indices as int32 with a device copy
+};
+
 /// Reshape / Flatten / Squeeze / Unsqueeze / Identity: the output aliases the input buffer
 /// (MODULE_INPLACE_UNCHANGED_BUFFER); forward() is a no-op unless the planner gave it a separate buffer.
 class Reshape : public Module {

@@ -295,6 +295,23 @@ typedef struct espdl_copy_desc {
 
 int espdl_b200_copy(const espdl_copy_desc *desc, void *stream);
 
+/* ----------------------------------------------------------------- gather */
+/* dl::module::Gather (esp-dl/dl/module/include/dl_module_gather.hpp:66-96): out[o][i][:] = in[o][indices[i]][:] for
+ * o < outer, i < num_indices, rows of `inner` elements.  Indices are int32 in device memory and must lie in
+ * [0, axis_size): the reference reads whatever an index outside that range points at, this entry point writes
+ * nothing for it and returns ESPDL_ERR_INVALID_ARG only for a bad descriptor (the host module checks the values
+ * when it loads the node). */
+typedef struct espdl_gather_desc {
+    const void *input;
+    void *output;
+    const int32_t *indices; /* device */
+    int32_t elem_size;      /* bytes: 1, 2, 4 or 8 */
+    int32_t num_indices;
+    int64_t outer, axis_size, inner;
+} espdl_gather_desc;
+
+int espdl_b200_gather(const espdl_gather_desc *desc, void *stream);
+
 /* ---------------------------------------------------------------- softmax */
 /* int8 Softmax along the last axis with the reference's 256-entry exp table
  * (esp-dl/dl/module/include/dl_module_softmax.hpp:148-187): the row sum is a

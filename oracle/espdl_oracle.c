@@ -921,3 +921,58 @@ int oracle_num_threads(void)
     return 1;
 #endif
 }
+
+/* ---------------------------------------------------------------- Gather, SpaceToDepth, DepthToSpace */
+/* dl::module::Gather::forward_template (esp-dl/dl/module/include/dl_module_gather.hpp:66-77). */
+int oracle_gather(const espdl_gather_desc *d)
+{
+    if (!d || !d->input || !d->output || !d->indices)
+        return ESPDL_ERR_INVALID_ARG;
+    const size_t row = (size_t)d->inner * d->elem_size;
+    for (int64_t o = 0; o < d->outer; o++)
+        for (int i = 0; i < d->num_indices; i++) {
+            const int idx = d->indices[i];
+            if (idx < 0 || idx >= d->axis_size)
+                continue;
+            memcpy((char *)d->output + (size_t)(o * d->num_indices + i) * row, (const char *)d->input + (size_t)(o * d->axis_size + idx) * row, row);
+        }
+    return ESPDL_OK;
+}
+
+/* mode 0: SpaceToDepth (esp-dl/dl/module/include/dl_module_space_to_depth.hpp:20-47); mode 1 / 2: DepthToSpace "DCR" /
+ * "CRD" (esp-dl/dl/module/include/dl_module_depth_to_space.hpp:20-72).  NHWC, h / w / c are the INPUT extents.  The
+ * reference's DCR index rule (out_c = c % blocksize, row = c / blocksize^2) addresses the output consistently only
+ * when the output has `blocksize` channels; other shapes are rejected here. */
+int oracle_depth_space(const void *input, void *output, int elem_size, int n, int h, int w, int c, int bs, int mode)
+{
+    if (!input || !output || bs < 1)
+        return ESPDL_ERR_INVALID_ARG;
+    const int b2 = bs * bs;
+    if (mode == 0 ? (h % bs || w % bs) : (c % b2))
+        return ESPDL_ERR_INVALID_ARG;
+    if (mode == 1 && c / b2 != bs)
+        return ESPDL_ERR_UNSUPPORTED;
+    const char *in = (const char *)input;
+    for (int b = 0; b < n; b++)
+        for (int y = 0; y < h; y++)
+            for (int x = 0; x < w; x++)
+                for (int ch = 0; ch < c; ch++, in += elem_size) {
+                    int64_t idx;
+                    if (mode == 0) {
+                        const int oc = c * b2, out_c = ch * b2 + (y % bs) * bs + x % bs;
+                        idx = (int64_t)b * h * w * c + (int64_t)(y / bs) * (w / bs) * oc + (int64_t)(x / bs) * oc + out_c;
+                    } else {
+                        const int oc = c / b2;
+                        const int64_t h_offset = (int64_t)w * bs * oc;
+                        int out_c, oy, ox;
+                        if (mode == 2) {
+                            out_c = ch / b2, oy = y * bs + (ch % b2) / bs, ox = x * bs + ch % bs;
+                        } else {
+                            out_c = ch % bs, oy = y * bs + ch / b2, ox = x * bs + (ch % b2) / bs;
+                        }
+                        idx = (int64_t)b * h * w * c + oy * h_offset + (int64_t)ox * oc + out_c;
+                    }
+                    memcpy((char *)output + idx * elem_size, in, elem_size);
+                }
+    return ESPDL_OK;
+}

@@ -25,12 +25,14 @@
 #include "dl_module_clip.hpp"
 #include "dl_module_concat.hpp"
 #include "dl_module_conv.hpp"
+#include "dl_module_depth_to_space.hpp"
 #include "dl_module_div.hpp"
 #include "dl_module_equal.hpp"
 #include "dl_module_greater.hpp"
 #include "dl_module_greater_or_equal.hpp"
 #include "dl_module_less.hpp"
 #include "dl_module_less_or_equal.hpp"
+#include "dl_module_gather.hpp"
 #include "dl_module_gemm.hpp"
 #include "dl_module_global_average_pool.hpp"
 #include "dl_module_lut.hpp"
@@ -53,6 +55,7 @@
 #include "dl_module_requantize_linear.hpp"
 #include "dl_module_resize.hpp"
 #include "dl_module_softmax.hpp"
+#include "dl_module_space_to_depth.hpp"
 #include "dl_module_sub.hpp"
 
 #include <memory>
@@ -347,6 +350,34 @@ int ref_reduce(const espdl_reduce_desc *d)
     std::vector<std::vector<int>> in_shapes = {shape};
     std::vector<int> so = m->get_output_shape(in_shapes)[0];
     std::unique_ptr<TensorBase> ti(view(shape, d->input, d->in_exponent, d->dtype)), to(view(so, d->output, d->out_exponent, d->dtype));
+    m->run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* Gather through the reference's own module; `shape` is the input shape, the indices are a 1-D int32 tensor. */
+int ref_gather(const void *input, void *output, const int32_t *indices, int num_indices, const int *shape, int ndim, int axis, int dtype)
+{
+    std::vector<int> sh(shape, shape + ndim);
+    module::Gather m(new TensorBase({num_indices}, indices, 0, DATA_TYPE_INT32, true), axis, "gather", MODULE_NON_INPLACE, to_quant(dtype));
+    std::vector<std::vector<int>> in_shapes = {sh};
+    std::vector<int> so = m.get_output_shape(in_shapes)[0];
+    std::unique_ptr<TensorBase> ti(view(sh, input, 0, dtype)), to(view(so, output, 0, dtype));
+    m.run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* mode 0 SpaceToDepth, 1 DepthToSpace "DCR", 2 DepthToSpace "CRD" through the reference's own modules (NHWC input extents). */
+int ref_depth_space(const void *input, void *output, int dtype, int n, int h, int w, int c, int bs, int mode)
+{
+    std::unique_ptr<module::Module> m;
+    if (mode == 0)
+        m.reset(new module::SpaceToDepth(bs, "s2d", MODULE_NON_INPLACE, to_quant(dtype)));
+    else
+        m.reset(new module::DepthToSpace(bs, mode == 1 ? "DCR" : "CRD", "d2s", MODULE_NON_INPLACE, to_quant(dtype)));
+    std::vector<int> sh = {n, h, w, c};
+    std::vector<std::vector<int>> in_shapes = {sh};
+    std::vector<int> so = m->get_output_shape(in_shapes)[0];
+    std::unique_ptr<TensorBase> ti(view(sh, input, 0, dtype)), to(view(so, output, 0, dtype));
     m->run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
     return 0;
 }

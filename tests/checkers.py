@@ -24,13 +24,15 @@ def oracle():
         lib = C.CDLL(ORACLE_SO)
         for name, desc in [("oracle_conv2d", abi.ConvDesc), ("oracle_eltwise", abi.EltwiseDesc), ("oracle_pool", abi.PoolDesc),
                            ("oracle_resize", abi.ResizeDesc), ("oracle_copy", abi.CopyDesc), ("oracle_softmax", abi.SoftmaxDesc),
-                           ("oracle_reduce", abi.ReduceDesc), ("oracle_pad", abi.PadDesc)]:
+                           ("oracle_reduce", abi.ReduceDesc), ("oracle_pad", abi.PadDesc), ("oracle_gather", abi.GatherDesc)]:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(desc)]
         lib.oracle_softmax_table.restype = None
         lib.oracle_softmax_table.argtypes = [C.c_void_p, C.c_int]
         lib.oracle_num_threads.restype = C.c_int
+        lib.oracle_depth_space.restype = C.c_int
+        lib.oracle_depth_space.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 7
         _oracle = lib
     return _oracle
 
@@ -61,6 +63,10 @@ def ref():
         lib.ref_reduce.restype = C.c_int
         lib.ref_reduce.argtypes = [C.POINTER(abi.ReduceDesc)]
         lib.ref_num_threads.restype = C.c_int
+        lib.ref_gather.restype = C.c_int
+        lib.ref_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]
+        lib.ref_depth_space.restype = C.c_int
+        lib.ref_depth_space.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 7
         _ref = lib
     return _ref
 
