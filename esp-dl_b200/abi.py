@@ -133,6 +133,16 @@ class PadDesc(C.Structure):
 PAD_CONSTANT, PAD_EDGE, PAD_REFLECT = range(3)
 
 
+class NormDesc(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("scale", C.c_void_p), ("bias", C.c_void_p), ("mean", C.c_void_p),
+                ("inv_std_dev", C.c_void_p), ("op", i32), ("dtype", i32), ("rows", C.c_int64), ("len", i32), ("in_exponent", i32),
+                ("out_exponent", i32), ("scale_exponent", i32), ("bias_exponent", i32), ("mean_exponent", i32),
+                ("inv_std_dev_exponent", i32), ("epsilon", C.c_float), ("round_mode", i32)]
+
+
+NORM_RMS, NORM_LAYER = range(2)
+
+
 class GatherDesc(C.Structure):
     _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("indices", C.c_void_p), ("elem_size", i32), ("num_indices", i32),
                 ("outer", C.c_int64), ("axis_size", C.c_int64), ("inner", C.c_int64)]
@@ -186,6 +196,7 @@ SYMBOLS = {
     "espdl_b200_reduce": (C.c_int, [C.POINTER(ReduceDesc), C.c_void_p]),
     "espdl_b200_pad": (C.c_int, [C.POINTER(PadDesc), C.c_void_p]),
     "espdl_b200_gather": (C.c_int, [C.POINTER(GatherDesc), C.c_void_p]),
+    "espdl_b200_norm": (C.c_int, [C.POINTER(NormDesc), C.c_void_p]),
 }
 
 _lib = None

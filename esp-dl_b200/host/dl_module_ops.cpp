@@ -1,6 +1,7 @@
 #include "dl_module_ops.hpp"
 #include "espdl_b200.h"
 
+#include <climits>
 #include <cassert>
 #include <cmath>
 #include <algorithm>
@@ -1630,6 +1631,97 @@ Module *Gather::deserialize(fbs::FbsModel *m, std::string node)
     return new Gather(indices, axis, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
 }
 
+// --------------------------------------------------------------------------------- RMSNormalization / LayerNormalization
+std::vector<std::vector<int>> Normalization::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    const std::vector<int> &x = input_shapes[0];
+    if (m_op == ESPDL_NORM_RMS)
+        return {x};
+    // LayerNormalization::calculate_normalized_shape, dl_module_layer_normalization.hpp:186-196
+    const int axis = m_axis < 0 ? (int)x.size() + m_axis : m_axis;
+    std::vector<int> stat(x.size(), 1);
+    for (int i = 0; i < axis && i < (int)x.size(); i++) stat[i] = x[i];
+    return {x, stat, stat};
+}
+
+esp_err_t Normalization::prepare(ModelContext *context)
+{
+    for (size_t i = 1; i < m_inputs_index.size(); i++) {
+        TensorBase *t = context->get_tensor(m_inputs_index[i]);
+        if (t && t->data && !t->device && t->to_device() != ESP_OK)
+            return ESP_FAIL;
+    }
+    return espdl_b200_stream_sync(nullptr) == ESPDL_OK ? ESP_OK : ESP_FAIL;
+}
+
+void Normalization::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *x = context->get_tensor(m_inputs_index[0]);
+    TensorBase *scale = m_inputs_index.size() > 1 ? context->get_tensor(m_inputs_index[1]) : nullptr;
+    TensorBase *bias = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
+    TensorBase *y = context->get_tensor(m_outputs_index[0]);
+    TensorBase *mean = m_outputs_index.size() > 1 ? context->get_tensor(m_outputs_index[1]) : nullptr;
+    TensorBase *inv = m_outputs_index.size() > 2 ? context->get_tensor(m_outputs_index[2]) : nullptr;
+    espdl_norm_desc d;
+    memset(&d, 0, sizeof(d));
+    int st = (!x || !y || !x->device || !y->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st && m_op == ESPDL_NORM_RMS && (!scale || !scale->device || scale->dtype != DATA_TYPE_FLOAT))
+        st = ESPDL_ERR_INVALID_ARG;
+    if (!st && ((scale && !scale->device) || (bias && !bias->device) || (mean && !mean->device) || (inv && !inv->device)))
+        st = ESPDL_ERR_INVALID_ARG;
+    if (!st) {
+        const int axis = m_axis < 0 ? (int)x->shape.size() + m_axis : m_axis;
+        long long rows = 1, len = 1;
+        for (int i = 0; i < (int)x->shape.size(); i++) (i < axis ? rows : len) *= x->shape[i];
+        d.input = x->device, d.output = y->device, d.op = m_op, d.dtype = quant_dtype(quant_type);
+        d.scale = scale ? scale->device : nullptr, d.bias = bias ? bias->device : nullptr;
+        d.mean = mean ? mean->device : nullptr, d.inv_std_dev = inv ? inv->device : nullptr;
+        d.rows = rows, d.len = (int)len;
+        d.in_exponent = x->exponent, d.out_exponent = y->exponent;
+        d.scale_exponent = scale ? (int)scale->exponent : 0, d.bias_exponent = bias ? (int)bias->exponent : 0;
+        d.mean_exponent = mean ? (int)mean->exponent : 0, d.inv_std_dev_exponent = inv ? (int)inv->exponent : 0;
+        d.epsilon = m_epsilon, d.round_mode = context->round_mode;
+        if (len > INT_MAX || (scale && scale->get_size() < len) || (bias && bias->get_size() < len))
+            st = ESPDL_ERR_INVALID_ARG;
+        else
+            st = espdl_b200_norm(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Normalization", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+RMSNormalization::RMSNormalization(int axis, float epsilon, const char *name, module_inplace_t inplace, quant_type_t quant_type) :
+    Normalization(ESPDL_NORM_RMS, axis, epsilon, name, inplace, quant_type)
+{
+}
+
+LayerNormalization::LayerNormalization(int axis, float epsilon, int stash_type, const char *name, module_inplace_t inplace,
+                                       quant_type_t quant_type) :
+    Normalization(ESPDL_NORM_LAYER, axis, epsilon, name, inplace, quant_type)
+{
+    (void)stash_type;
+}
+
+static Module *deserialize_norm(fbs::FbsModel *m, const std::string &node, bool rms)
+{
+    int axis = -1;
+    float epsilon = 1e-5f;
+    m->get_operation_attribute(node, "axis", axis);
+    m->get_operation_attribute(node, "epsilon", epsilon);
+    const quant_type_t q = node_quant(m, node);
+    if (q != QUANT_TYPE_SYMM_8BIT && q != QUANT_TYPE_SYMM_16BIT)
+        return nullptr;
+    if (rms)
+        return new RMSNormalization(axis, epsilon, node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, q);
+    int stash_type = 1;
+    m->get_operation_attribute(node, "stash_type", stash_type);
+    return new LayerNormalization(axis, epsilon, stash_type, node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, q);
+}
+Module *RMSNormalization::deserialize(fbs::FbsModel *m, std::string node) { return deserialize_norm(m, node, true); }
+Module *LayerNormalization::deserialize(fbs::FbsModel *m, std::string node) { return deserialize_norm(m, node, false); }
+
 std::vector<std::vector<int>> Reshape::get_output_shape(std::vector<std::vector<int>> &input_shapes)
 {
     std::vector<int> in = input_shapes[0], out;
@@ -1837,6 +1929,8 @@ void ModuleCreator::register_dl_modules()
     register_module("SpaceToDepth", SpaceToDepth::deserialize);
     register_module("DepthToSpace", DepthToSpace::deserialize);
     register_module("Gather", Gather::deserialize);
+    register_module("RMSNormalization", RMSNormalization::deserialize);
+    register_module("LayerNormalization", LayerNormalization::deserialize);
     register_module("Reshape", Reshape::deserialize_reshape);
     register_module("Flatten", Reshape::deserialize_flatten);
     register_module("Squeeze", Reshape::deserialize_squeeze);

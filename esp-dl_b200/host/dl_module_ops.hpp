@@ -395,6 +395,36 @@ protected:
     TensorBase *m_dev_indices; ///< the indices as int32 with a device copy
 };
 
+/// RMSNormalization (dl_module_rms_normalization.hpp; inputs x and a float scale) and LayerNormalization
+/// (dl_module_layer_normalization.hpp; inputs x [, scale [, bias]], outputs y [, mean, inv_std_dev]) over the axes from
+/// `axis` to the last one.
+class Normalization : public Module {
+public:
+    Normalization(int op, int axis, float epsilon, const char *name, module_inplace_t inplace, quant_type_t quant_type) :
+        Module(name, inplace, quant_type), m_op(op), m_axis(axis), m_epsilon(epsilon)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    esp_err_t prepare(ModelContext *context) override; ///< uploads scale / bias when they are parameters
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+
+protected:
+    int m_op, m_axis;
+    float m_epsilon;
+};
+class RMSNormalization : public Normalization {
+public:
+    RMSNormalization(int axis = -1, float epsilon = 1e-5f, const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+                     quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class LayerNormalization : public Normalization {
+public:
+    LayerNormalization(int axis = -1, float epsilon = 1e-5f, int stash_type = 1, const char *name = nullptr,
+                       module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+
 /// Reshape / Flatten / Squeeze / Unsqueeze / Identity: the output aliases the input buffer
 /// (MODULE_INPLACE_UNCHANGED_BUFFER); forward() is a no-op unless the planner gave it a separate buffer.
 class Reshape : public Module {

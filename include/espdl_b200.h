@@ -468,6 +468,34 @@ typedef struct espdl_reduce_desc {
 
 int espdl_b200_reduce(const espdl_reduce_desc *desc, void *stream);
 
+/* ---------------------------------------------------------- normalisation */
+/* RMSNormalization: dl::module::RMSNormalization::forward_int8 / forward_int16 (esp-dl/dl/module/include/
+ * dl_module_rms_normalization.hpp:57-113) with dl::base::rms_norm (esp-dl/dl/base/dl_base_norm.cpp:9-38):
+ *   rms = 1 / sqrtf(sum(x*x) * 2^(2*e_in) / len + epsilon) * (2^e_in * 2^-e_out);  y = sat(round((x * rms) * scale[j])),
+ * scale float[len].  LayerNormalization: the quantized branch of dl::module::LayerNormalization::forward_template
+ * (esp-dl/dl/module/include/dl_module_layer_normalization.hpp:141-214): integer row sum, fp32 variance summed in element
+ * order, 1 / sqrt_newton(var + epsilon), y = sat(round((((x*2^e_in - mean) * inv_std) * scale + bias) * 2^-e_out)) with
+ * scale / bias of the tensor's integer type (either may be NULL); the optional mean / inv_std_dev outputs hold one
+ * value per row.  Rows are the leading axes, len the product of the normalised trailing axes; output may alias input. */
+typedef enum { ESPDL_NORM_RMS = 0, ESPDL_NORM_LAYER = 1 } espdl_norm_op_t;
+
+typedef struct espdl_norm_desc {
+    const void *input;
+    void *output;
+    const void *scale;  /* RMS: float[len]; LAYER: dtype[len] at scale_exponent, or NULL (= 1)                 */
+    const void *bias;   /* LAYER: dtype[len] at bias_exponent, or NULL (= 0)                                    */
+    void *mean;         /* LAYER: dtype[rows] at mean_exponent, or NULL                                         */
+    void *inv_std_dev;  /* LAYER: dtype[rows] at inv_std_dev_exponent, or NULL                                  */
+    int32_t op, dtype;  /* espdl_norm_op_t; ESPDL_DTYPE_INT8 or ESPDL_DTYPE_INT16                               */
+    int64_t rows;
+    int32_t len;
+    int32_t in_exponent, out_exponent, scale_exponent, bias_exponent, mean_exponent, inv_std_dev_exponent;
+    float epsilon;
+    int32_t round_mode;
+} espdl_norm_desc;
+
+int espdl_b200_norm(const espdl_norm_desc *desc, void *stream);
+
 /* ---------------------------------------------------------- Pad */
 /* dl::module::Pad / TensorBase::pad (esp-dl/dl/module/include/dl_module_pad.hpp:10-100, esp-dl/dl/base/dl_base_pad.cpp:
  * 18-66 per axis): constant (the given code), edge (nearest element) or reflect (mirror without repeating the edge). */

@@ -976,3 +976,75 @@ int oracle_depth_space(const void *input, void *output, int elem_size, int n, in
                 }
     return ESPDL_OK;
 }
+
+/* ---------------------------------------------------------------- RMSNormalization / LayerNormalization */
+/* math::sqrt_newton, esp-dl/dl/math/include/dl_math.hpp:83-97 (capped at 100 steps; it ends by itself long before) */
+static float oracle_sqrt_newton(float x)
+{
+    if (x == 0.f)
+        return 0.f;
+    float r = x;
+    for (int it = 0; it < 100; it++) {
+        const float last = r;
+        r = (float)((last + x / last) * 0.5);
+        if (!(fabsf(r - last) > 0.00001f))
+            break;
+    }
+    return r;
+}
+
+int oracle_norm(const espdl_norm_desc *d)
+{
+    if (!d || !d->input || !d->output || d->len <= 0)
+        return ESPDL_ERR_INVALID_ARG;
+    const int is8 = d->dtype == ESPDL_DTYPE_INT8, mode = d->round_mode;
+    const float input_scale = dl_scale(d->in_exponent), output_scale = dl_rescale(d->out_exponent);
+    for (int64_t i = 0; i < d->rows; i++) {
+        const int64_t base = i * d->len;
+        if (d->op == ESPDL_NORM_RMS) { /* esp-dl/dl/module/include/dl_module_rms_normalization.hpp:57-84, dl_base_norm.cpp:16-20 */
+            const float input_scale_sq = input_scale * input_scale;
+            const float scale_factor = input_scale * output_scale;
+            int64_t sum_sq = 0;
+            for (int j = 0; j < d->len; j++) {
+                const int64_t v = load_int(d->input, d->dtype, base + j);
+                sum_sq += v * v;
+            }
+            const float mean_sq = (is8 ? (float)(int32_t)sum_sq : (float)sum_sq) * input_scale_sq / d->len;
+            float rms = 1.0f / sqrtf(mean_sq + d->epsilon); /* math::fast_inv_sqrt with DL_FAST_MATH 0, dl_math.hpp:60-72 */
+            rms *= scale_factor;
+            for (int j = 0; j < d->len; j++) {
+                float result = (float)load_int(d->input, d->dtype, base + j) * rms;
+                result *= ((const float *)d->scale)[j];
+                store_sat(d->output, d->dtype, base + j, fround(result, mode));
+            }
+        } else { /* esp-dl/dl/module/include/dl_module_layer_normalization.hpp:141-214 */
+            const float scale_scale = d->scale ? dl_scale(d->scale_exponent) : 1.0f;
+            const float bias_scale = d->bias ? dl_scale(d->bias_exponent) : 0.0f;
+            int sum_val = 0;
+            for (int j = 0; j < d->len; j++) sum_val += (int)load_int(d->input, d->dtype, base + j);
+            float mean_val = (float)(sum_val * 1.0 / d->len);
+            if (d->mean)
+                store_sat(d->mean, d->dtype, i, fround(mean_val * dl_rescale(d->mean_exponent) * input_scale, mode));
+            float variance = 0.0f;
+            for (int j = 0; j < d->len; j++) {
+                const float diff = (float)load_int(d->input, d->dtype, base + j) - mean_val;
+                variance += diff * diff;
+            }
+            mean_val *= input_scale;
+            variance *= input_scale * input_scale;
+            variance /= d->len;
+            const float inv_std = 1.0f / oracle_sqrt_newton(variance + d->epsilon);
+            if (d->inv_std_dev)
+                store_sat(d->inv_std_dev, d->dtype, i, fround(inv_std * dl_rescale(d->inv_std_dev_exponent), mode));
+            for (int j = 0; j < d->len; j++) {
+                const float x_val = (float)load_int(d->input, d->dtype, base + j) * input_scale;
+                const float normalized = (x_val - mean_val) * inv_std;
+                const float scale_val = d->scale ? (float)load_int(d->scale, d->dtype, j) * scale_scale : 1.0f;
+                const float bias_val = d->bias ? (float)load_int(d->bias, d->dtype, j) * bias_scale : 0.0f;
+                const float result = normalized * scale_val + bias_val;
+                store_sat(d->output, d->dtype, base + j, fround(result * output_scale, mode));
+            }
+        }
+    }
+    return ESPDL_OK;
+}

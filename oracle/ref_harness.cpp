@@ -34,6 +34,7 @@
 #include "dl_module_less_or_equal.hpp"
 #include "dl_module_gather.hpp"
 #include "dl_module_gemm.hpp"
+#include "dl_module_layer_normalization.hpp"
 #include "dl_module_global_average_pool.hpp"
 #include "dl_module_lut.hpp"
 #include "dl_module_matmul.hpp"
@@ -54,6 +55,7 @@
 #include "dl_module_relu.hpp"
 #include "dl_module_requantize_linear.hpp"
 #include "dl_module_resize.hpp"
+#include "dl_module_rms_normalization.hpp"
 #include "dl_module_softmax.hpp"
 #include "dl_module_space_to_depth.hpp"
 #include "dl_module_sub.hpp"
@@ -379,6 +381,36 @@ int ref_depth_space(const void *input, void *output, int dtype, int n, int h, in
     std::vector<int> so = m->get_output_shape(in_shapes)[0];
     std::unique_ptr<TensorBase> ti(view(sh, input, 0, dtype)), to(view(so, output, 0, dtype));
     m->run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* RMSNormalization / LayerNormalization through the reference's own modules (rows x len, normalised over the last axis). */
+int ref_norm(const espdl_norm_desc *d)
+{
+    const int rows = (int)d->rows, len = d->len;
+    std::vector<std::unique_ptr<TensorBase>> keep;
+    auto mk = [&](std::vector<int> shape, const void *p, int e, int dtype) {
+        keep.emplace_back(view(shape, p, e, dtype));
+        return keep.back().get();
+    };
+    std::vector<TensorBase *> ins = {mk({rows, len}, d->input, d->in_exponent, d->dtype)}, outs;
+    std::unique_ptr<module::Module> m;
+    if (d->op == ESPDL_NORM_RMS) {
+        ins.push_back(mk({len}, d->scale, 0, ESPDL_DTYPE_FLOAT));
+        m.reset(new module::RMSNormalization(-1, d->epsilon, "rms", MODULE_NON_INPLACE, to_quant(d->dtype)));
+    } else {
+        if (d->scale)
+            ins.push_back(mk({len}, d->scale, d->scale_exponent, d->dtype));
+        if (d->scale && d->bias)
+            ins.push_back(mk({len}, d->bias, d->bias_exponent, d->dtype));
+        m.reset(new module::LayerNormalization(-1, d->epsilon, 1, "ln", MODULE_NON_INPLACE, to_quant(d->dtype)));
+    }
+    outs.push_back(mk({rows, len}, d->output, d->out_exponent, d->dtype));
+    if (d->op == ESPDL_NORM_LAYER && d->mean && d->inv_std_dev) {
+        outs.push_back(mk({rows, 1}, d->mean, d->mean_exponent, d->dtype));
+        outs.push_back(mk({rows, 1}, d->inv_std_dev, d->inv_std_dev_exponent, d->dtype));
+    }
+    m->run(ins, outs, RUNTIME_MODE_SINGLE_CORE);
     return 0;
 }
 

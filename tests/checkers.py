@@ -24,7 +24,7 @@ def oracle():
         lib = C.CDLL(ORACLE_SO)
         for name, desc in [("oracle_conv2d", abi.ConvDesc), ("oracle_eltwise", abi.EltwiseDesc), ("oracle_pool", abi.PoolDesc),
                            ("oracle_resize", abi.ResizeDesc), ("oracle_copy", abi.CopyDesc), ("oracle_softmax", abi.SoftmaxDesc),
-                           ("oracle_reduce", abi.ReduceDesc), ("oracle_pad", abi.PadDesc), ("oracle_gather", abi.GatherDesc)]:
+                           ("oracle_reduce", abi.ReduceDesc), ("oracle_pad", abi.PadDesc), ("oracle_gather", abi.GatherDesc), ("oracle_norm", abi.NormDesc)]:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(desc)]
@@ -65,6 +65,8 @@ def ref():
         lib.ref_num_threads.restype = C.c_int
         lib.ref_gather.restype = C.c_int
         lib.ref_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]
+        lib.ref_norm.restype = C.c_int
+        lib.ref_norm.argtypes = [C.POINTER(abi.NormDesc)]
         lib.ref_depth_space.restype = C.c_int
         lib.ref_depth_space.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 7
         _ref = lib

@@ -31,13 +31,13 @@ def test_every_declared_symbol_is_exported(library):
 
 def test_struct_sizes_match_the_header(tmp_path):
     src = tmp_path / "sizes.c"
-    src.write_text('#include <stdio.h>\n#include "espdl_b200.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include <stdio.h>\n#include "espdl_b200.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                    "sizeof(espdl_conv_desc),sizeof(espdl_eltwise_desc),sizeof(espdl_pool_desc),sizeof(espdl_resize_desc),"
-                   "sizeof(espdl_copy_desc),sizeof(espdl_softmax_desc),sizeof(espdl_gather_desc));return 0;}\n")
+                   "sizeof(espdl_copy_desc),sizeof(espdl_softmax_desc),sizeof(espdl_gather_desc),sizeof(espdl_norm_desc));return 0;}\n")
     exe = tmp_path / "sizes"
     subprocess.check_call(["/usr/bin/gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
     sizes = [int(x) for x in subprocess.check_output([str(exe)]).split()]
-    mirrors = [abi.ConvDesc, abi.EltwiseDesc, abi.PoolDesc, abi.ResizeDesc, abi.CopyDesc, abi.SoftmaxDesc, abi.GatherDesc]
+    mirrors = [abi.ConvDesc, abi.EltwiseDesc, abi.PoolDesc, abi.ResizeDesc, abi.CopyDesc, abi.SoftmaxDesc, abi.GatherDesc, abi.NormDesc]
     assert sizes == [C.sizeof(m) for m in mirrors]
 
 
