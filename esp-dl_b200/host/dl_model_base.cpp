@@ -488,6 +488,18 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
                 in_shapes.push_back({});
             }
         }
+        bool shapes_known = true;
+        for (size_t i = 0; i < in_shapes.size(); i++) {
+            if (in_shapes[i].empty() && !m_module_inputs[step][i].empty() && !ctx->get_tensor(m_module_inputs[step][i])) {
+                ESP_LOGE("Model", "%s %s: input %s has no producer, no value_info shape and is no parameter", m_module_types[step].c_str(),
+                         mod->name ? mod->name : "?", m_module_inputs[step][i].c_str());
+                shapes_known = false;
+            }
+        }
+        if (!shapes_known) {
+            m_status = ESPDL_ERR_INVALID_ARG;
+            return;
+        }
         std::vector<std::vector<int>> out_shapes = mod->get_output_shape(in_shapes);
         for (size_t o = 0; o < m_module_outputs[step].size() && o < out_shapes.size(); o++)
             add_info(m_module_outputs[step][o], out_shapes[o], (int)step);

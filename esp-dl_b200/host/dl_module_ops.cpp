@@ -1444,7 +1444,17 @@ std::vector<std::vector<int>> Transpose::get_output_shape(std::vector<std::vecto
     std::vector<int> in = input_shapes[0], out(in.size());
     if (m_perm.empty())
         for (int i = (int)in.size() - 1; i >= 0; i--) m_perm.push_back(i);
-    for (size_t i = 0; i < in.size(); i++) out[i] = in[m_perm[i]];
+    if (m_perm.size() != in.size()) {
+        ESP_LOGE("Transpose", "%s: perm has %d entries for a tensor of rank %d", name ? name : "?", (int)m_perm.size(), (int)in.size());
+        return {{}};
+    }
+    for (size_t i = 0; i < in.size(); i++) {
+        if (m_perm[i] < 0) // negative entries count from the last axis (dl_module_transpose.hpp:43-46)
+            m_perm[i] += (int)m_perm.size();
+        if (m_perm[i] < 0 || m_perm[i] >= (int)in.size())
+            return {{}};
+        out[i] = in[m_perm[i]];
+    }
     return {out};
 }
 

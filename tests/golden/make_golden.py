@@ -4,6 +4,10 @@ Run in a container that has the reference checkout:  python tests/golden/make_go
 It copies the small `.espdl` test models that embed `test_inputs_value` / `test_outputs_value`
 (the data the reference's own `Model::test()` checks, test_apps/esp-dl/main/test_dl_model.cpp:14-52)
 into tests/golden/espdl/<target>__<name>.espdl, byte for byte.  They are data files, a few KB each.
+
+It also copies two of the model-zoo files (models/imagenet_cls, models/coco_detect; 3-4 MB each, ESP32-P4 filter layout,
+per-channel exponents, no embedded test vectors): the ImageNet MobileNetV2 classifier and the YOLO11n detector at 320x320.
+The tests run them on seeded random images and compare the backend with the graph oracle.
 """
 import os
 import shutil
@@ -25,6 +29,9 @@ for chip, target in (("p4", "esp32p4"), ("s3", "esp32s3")):
 for target in ("esp32p4", "esp32s3"):
     SOURCES.append((os.path.join(REF, "examples/tutorial/how_to_deploy_streaming_model/test_streaming_model/main/models",
                                  target, "model.espdl"), f"{target}__streaming_tcn.espdl"))
+
+SOURCES.append((os.path.join(REF, "models/imagenet_cls/models/p4/imagenet_cls_mobilenetv2_s8_v1.espdl"), "esp32p4__zoo_mobilenetv2.espdl"))
+SOURCES.append((os.path.join(REF, "models/coco_detect/models/p4/coco_detect_yolo11n_320_s8_v1.espdl"), "esp32p4__zoo_yolo11n_320.espdl"))
 
 if __name__ == "__main__":
     os.makedirs(OUT, exist_ok=True)

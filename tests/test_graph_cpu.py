@@ -6,7 +6,7 @@ import pytest
 
 import checkers
 import graph_oracle
-from espdl_b200 import espdl_file, zoo
+from espdl_b200 import abi, espdl_file, zoo
 
 
 def per_tensor(g):
@@ -62,3 +62,19 @@ def test_yolo11n_style_generator_runs_through_the_oracle(tmp_path):
     for o in m["outputs"]:
         v = t[o["name"]].astype(int)
         assert v.std() > 5 and (np.abs(v) >= 127).mean() < 0.3
+
+
+@pytest.mark.parametrize("name", ["esp32p4__zoo_mobilenetv2.espdl", "esp32p4__zoo_yolo11n_320.espdl"])
+def test_shipped_zoo_models_run_through_the_oracle(name):
+    """The model-zoo files as shipped parse with the own FlatBuffers reader (ESP32-P4 filter layout, per-channel exponents) and
+    run through the graph oracle with half-to-even rounding: outputs of the declared shapes, not saturated, and - the
+    network has no cross-image step - independent of what else is in the batch."""
+    import os
+    parsed = espdl_file.read(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "espdl", name))
+    inp = parsed["inputs"][0]
+    x = np.random.default_rng(3).integers(-128, 128, size=inp["shape"], dtype=np.int8)
+    want = graph_oracle.run_graph(parsed, {inp["name"]: x}, round_mode=abi.ROUND_HALF_EVEN, target="esp32p4")
+    for out in parsed["outputs"]:
+        y = want[out["name"]]
+        assert list(y.shape) == list(out["shape"])
+        assert y.astype(np.float32).std() > 1 and (np.abs(y.astype(np.int32)) == 127).mean() < 0.5
