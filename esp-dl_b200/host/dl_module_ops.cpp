@@ -567,6 +567,16 @@ size_t MatMul::workspace_bytes(ModelContext *context)
     return espdl_b200_conv2d_workspace_bytes(&d, &bytes) == ESPDL_OK ? bytes : 0;
 }
 
+esp_err_t MatMul::prepare(ModelContext *context)
+{
+    for (int idx : m_inputs_index) {
+        TensorBase *t = context->get_tensor(idx);
+        if (t && t->data && !t->device && t->to_device() != ESP_OK) // host data and no device copy: a parameter
+            return ESP_FAIL;
+    }
+    return espdl_b200_stream_sync(nullptr) == ESPDL_OK ? ESP_OK : ESP_FAIL;
+}
+
 void MatMul::forward(ModelContext *context, runtime_mode_t mode)
 {
     (void)mode;
@@ -1566,6 +1576,59 @@ Module *DepthToSpace::deserialize(fbs::FbsModel *m, std::string node)
     return new DepthToSpace(blocksize, mode.empty() ? "DCR" : mode, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
 }
 
+std::vector<std::vector<int>> InsertZeros::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    // dl_module_insert_zeros.hpp:33-58
+    std::vector<int> in = input_shapes[0], out = in;
+    if (in.size() != 3 && in.size() != 4) {
+        ESP_LOGE("InsertZeros", "%s: one or two spatial axes expected", name ? name : "?");
+        return {{}};
+    }
+    const int spatial = (int)in.size() - 2;
+    if (m_stride.size() == 1 && spatial > 1)
+        m_stride.assign(spatial, m_stride[0]);
+    if (m_output_padding.size() == 1 && spatial > 1)
+        m_output_padding.assign(spatial, m_output_padding[0]);
+    if ((int)m_stride.size() != spatial || (int)m_output_padding.size() != spatial)
+        return {{}};
+    for (int i = 0; i < spatial; i++) out[1 + i] = in[1 + i] + (m_stride[i] - 1) * (in[1 + i] - 1) + m_output_padding[i];
+    return {out};
+}
+
+void InsertZeros::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!in || !out || !in->device || !out->device || in->shape.size() != out->shape.size() ||
+              in->shape.size() != m_stride.size() + 2) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st)
+        st = espdl_b200_memset(out->device, 0, (size_t)out->get_size() * dtype_sizeof(out->dtype), context->stream);
+    if (!st) {
+        std::vector<long long> ds = dense_strides(out->shape);
+        for (size_t i = 0; i < m_stride.size(); i++) ds[1 + i] *= m_stride[i];
+        st = enqueue_copy(context, in->device, out->device, (int)dtype_sizeof(in->dtype), in->shape, dense_strides(in->shape), ds);
+    }
+    if (st)
+        ESP_LOGE("InsertZeros", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *InsertZeros::deserialize(fbs::FbsModel *m, std::string node)
+{
+    std::vector<int> stride, output_padding;
+    m->get_operation_attribute(node, "stride", stride);
+    m->get_operation_attribute(node, "output_padding", output_padding);
+    if (stride.empty())
+        stride = {1};
+    if (output_padding.empty())
+        output_padding = {0};
+    for (int v : stride)
+        if (v < 1)
+            return nullptr;
+    return new InsertZeros(node.c_str(), stride, output_padding, node_quant(m, node));
+}
+
 Gather::~Gather()
 {
     delete m_indices;
@@ -1939,6 +2002,7 @@ void ModuleCreator::register_dl_modules()
     register_module("SpaceToDepth", SpaceToDepth::deserialize);
     register_module("DepthToSpace", DepthToSpace::deserialize);
     register_module("Gather", Gather::deserialize);
+    register_module("InsertZeros", InsertZeros::deserialize);
     register_module("RMSNormalization", RMSNormalization::deserialize);
     register_module("LayerNormalization", LayerNormalization::deserialize);
     register_module("Reshape", Reshape::deserialize_reshape);

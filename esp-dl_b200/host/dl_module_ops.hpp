@@ -94,6 +94,7 @@ public:
     MatMul(activation_type_t activation = Linear, const char *name = nullptr, quant_type_t quant_type = QUANT_TYPE_NONE)
         : Module(name, MODULE_NON_INPLACE, quant_type), m_activation(activation) {}
     std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    esp_err_t prepare(ModelContext *context) override; ///< uploads an operand that is a parameter (a constant weight matrix)
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
     size_t workspace_bytes(ModelContext *context) override;
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
@@ -372,6 +373,23 @@ public:
 protected:
     int m_blocksize;
     std::string m_mode;
+};
+
+/// InsertZeros (dl_module_insert_zeros.hpp; the first half of a transposed convolution): the output is cleared and the
+/// input pixels are scattered `stride` apart along the one or two spatial axes of an NWC / NHWC tensor.
+class InsertZeros : public Module {
+public:
+    InsertZeros(const char *name = nullptr, const std::vector<int> &stride = {1}, const std::vector<int> &output_padding = {0},
+                quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, MODULE_NON_INPLACE, quant_type), m_stride(stride), m_output_padding(output_padding)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    std::vector<int> m_stride, m_output_padding;
 };
 
 /// Gather along one axis with constant indices (dl_module_gather.hpp): the module owns `indices` (int32 or int64, any

@@ -34,6 +34,7 @@
 #include "dl_module_less_or_equal.hpp"
 #include "dl_module_gather.hpp"
 #include "dl_module_gemm.hpp"
+#include "dl_module_insert_zeros.hpp"
 #include "dl_module_layer_normalization.hpp"
 #include "dl_module_global_average_pool.hpp"
 #include "dl_module_lut.hpp"
@@ -411,6 +412,18 @@ int ref_norm(const espdl_norm_desc *d)
         outs.push_back(mk({rows, 1}, d->inv_std_dev, d->inv_std_dev_exponent, d->dtype));
     }
     m->run(ins, outs, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* InsertZeros through the reference's own module: NWC / NHWC input of `ndim` axes, one stride and padding per spatial axis. */
+int ref_insert_zeros(const void *input, void *output, int dtype, const int *shape, int ndim, const int *stride, const int *output_padding)
+{
+    std::vector<int> sh(shape, shape + ndim), st(stride, stride + ndim - 2), op(output_padding, output_padding + ndim - 2);
+    module::InsertZeros m("iz", st, op, to_quant(dtype));
+    std::vector<std::vector<int>> in_shapes = {sh};
+    std::vector<int> so = m.get_output_shape(in_shapes)[0];
+    std::unique_ptr<TensorBase> ti(view(sh, input, 0, dtype)), to(view(so, output, 0, dtype));
+    m.run(ti.get(), to.get(), RUNTIME_MODE_SINGLE_CORE);
     return 0;
 }
 

@@ -147,15 +147,16 @@ def pool_case(op, seed=0, dtype=abi.DTYPE_INT8, n=2, h=9, w=10, c=24, kh=3, kw=3
     rng = np.random.default_rng(seed)
     info = np.iinfo(NP[dtype])
     x = rng.integers(info.min, info.max + 1, size=(n, h, w, c), dtype=NP[dtype])
+    sh, sw = (stride, stride) if isinstance(stride, int) else stride
     if op == abi.POOL_GLOBAL_AVG:
         oh = ow = 1
-        kh, kw, stride, pad = h, w, 1, (0, 0, 0, 0)
+        kh, kw, sh, sw, pad = h, w, 1, 1, (0, 0, 0, 0)
     else:
-        oh = (h + pad[0] + pad[1] - kh) // stride + 1
-        ow = (w + pad[2] + pad[3] - kw) // stride + 1
+        oh = (h + pad[0] + pad[1] - kh) // sh + 1
+        ow = (w + pad[2] + pad[3] - kw) // sw + 1
     out = np.zeros((n, oh, ow, c), dtype=NP[dtype])
     return dict(x=x, out=out, op=op, dtype=dtype, n=n, in_h=h, in_w=w, c=c, out_h=oh, out_w=ow, kh=kh, kw=kw,
-                stride_h=stride, stride_w=stride, pad_top=pad[0], pad_bottom=pad[1], pad_left=pad[2], pad_right=pad[3],
+                stride_h=sh, stride_w=sw, pad_top=pad[0], pad_bottom=pad[1], pad_left=pad[2], pad_right=pad[3],
                 in_exponent=e_in, out_exponent=e_out)
 
 

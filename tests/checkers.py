@@ -67,6 +67,8 @@ def ref():
         lib.ref_gather.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int]
         lib.ref_norm.restype = C.c_int
         lib.ref_norm.argtypes = [C.POINTER(abi.NormDesc)]
+        lib.ref_insert_zeros.restype = C.c_int
+        lib.ref_insert_zeros.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
         lib.ref_depth_space.restype = C.c_int
         lib.ref_depth_space.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 7
         _ref = lib

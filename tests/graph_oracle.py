@@ -99,21 +99,28 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
                 out_shape = x.shape[:-1] + (n_out,)
             else:
                 group = at.get("group", 1)
-                kh, kw, cin, cout = wt["dims"]
+                conv1d = len(wt["dims"]) == 3  # [N, W, C] with filter [K, Cin, Cout]: one row (esp-dl/dl/base/dl_base.hpp:150-182)
+                wdims = [1] + list(wt["dims"]) if conv1d else wt["dims"]
+                if conv1d:
+                    x = x.reshape(x.shape[0], 1, x.shape[1], x.shape[2])
+                kh, kw, cin, cout = wdims
                 depthwise = group != 1
                 if depthwise:
-                    w = espdl_file.depthwise_filter_to_hwc(wt["data"], wt["dims"], target)
+                    w = espdl_file.depthwise_filter_to_hwc(wt["data"], wdims, target)
                     cout = cin
                 else:
-                    w = espdl_file.filter_to_ohwi(wt["data"], wt["dims"], target)
+                    w = espdl_file.filter_to_ohwi(wt["data"], wdims, target)
                 pads = at.get("pads", [0, 0, 0, 0])  # ONNX [t, l, b, r]
                 strides = at.get("strides", [1, 1])
                 dil = at.get("dilations", [1, 1])
+                if conv1d:
+                    pads = [0, pads[0], 0, pads[1]] if len(pads) == 2 else pads
+                    strides, dil = [1, strides[0]], [1, dil[0]]
                 n, h, wd, c = x.shape
                 case = cases.conv_case(dtype=dt, n=n, h=h, w=wd, cin=c, cout=cout, kh=kh, kw=kw, stride=tuple(strides), dil=tuple(dil),
                                        pad=(pads[0], pads[2], pads[1], pads[3]), depthwise=depthwise)
                 case["x"] = np.ascontiguousarray(x)
-                out_shape = (n, case["out_h"], case["out_w"], cout)
+                out_shape = (n, case["out_w"], cout) if conv1d else (n, case["out_h"], case["out_w"], cout)
             case.update(w=np.ascontiguousarray(w), b=bias, lut=None, per_channel=int(per_channel),
                         ew=np.asarray(wt["exponents"], dtype=np.int32) if per_channel else None,
                         filter_exponent=0 if per_channel else wt["exponents"][0], in_exponent=exps[ins[0]], out_exponent=exps[outs[0]],
@@ -122,11 +129,12 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             st = o.oracle_conv2d(cases.conv_desc(case))
             assert st == 0, (node["name"], st)
             t[outs[0]] = case["out"].reshape(out_shape)
-        elif op in ("Add", "Sub", "Mul"):
+        elif op in ("Add", "Sub", "Mul", "Div", "Max", "Min", "Mod"):
             a, b = t[ins[0]], t.get(ins[1], None)
             if b is None:
                 b = init[ins[1]]["data"]
-            eop = {"Add": abi.ELT_ADD, "Sub": abi.ELT_SUB, "Mul": abi.ELT_MUL}[op]
+            eop = {"Add": abi.ELT_ADD, "Sub": abi.ELT_SUB, "Mul": abi.ELT_MUL, "Div": abi.ELT_DIV, "Max": abi.ELT_MAX, "Min": abi.ELT_MIN,
+                   "Mod": abi.ELT_MOD}[op]
             out_shape = np.broadcast_shapes(a.shape, b.shape)
             nd = len(out_shape)
             case = cases.eltwise_case(eop, dtype=QDT[at["quant_type"]], out_shape=out_shape, in0_shape=(1,) * (nd - a.ndim) + a.shape,
@@ -147,20 +155,31 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             t[outs[0]] = case["out"].reshape(x.shape)
         elif "lut" in at:
             table = init[at["lut"]]["data"]
-            case = cases.eltwise_case(abi.ELT_LUT, out_shape=(x.size,))
+            if x.dtype == np.int16:  # 65536 / step + 1 entries (dl_module_lut.hpp:33-36)
+                step = (65536 // (table.size - 1)) if table.size > 1 else 1
+                case = cases.eltwise_case(abi.ELT_LUT, dtype=abi.DTYPE_INT16, out_shape=(x.size,), lut_shift=int(step).bit_length() - 1,
+                                          round_mode=round_mode)
+            else:
+                case = cases.eltwise_case(abi.ELT_LUT, out_shape=(x.size,))
             case["a"], case["b"] = np.ascontiguousarray(x.reshape(-1)), np.ascontiguousarray(table)
             assert o.oracle_eltwise(cases.eltwise_desc(case)) == 0
             t[outs[0]] = case["out"].reshape(x.shape)
         elif op in ("GlobalAveragePool", "MaxPool", "AveragePool"):
             pop = {"GlobalAveragePool": abi.POOL_GLOBAL_AVG, "MaxPool": abi.POOL_MAX, "AveragePool": abi.POOL_AVG}[op]
-            n, h, wd, c = x.shape
+            pool1d = x.ndim == 3  # [N, W, C]: one row (dl_module_average_pool.hpp / dl_module_max_pool.hpp, 1-D form)
+            x4 = x.reshape(x.shape[0], 1, x.shape[1], x.shape[2]) if pool1d else x
+            n, h, wd, c = x4.shape
             ks = at.get("kernel_shape", [h, wd])
             pads = at.get("pads", [0, 0, 0, 0])
             st = at.get("strides", [1, 1])
-            case = cases.pool_case(pop, dtype=QDT[at["quant_type"]], n=n, h=h, w=wd, c=c, kh=ks[0], kw=ks[1], stride=st[0],
+            if pool1d and op != "GlobalAveragePool":
+                ks, st, pads = [1, ks[0]], [1, st[0]], [0, pads[0], 0, pads[1]]
+            case = cases.pool_case(pop, dtype=QDT[at["quant_type"]], n=n, h=h, w=wd, c=c, kh=ks[0], kw=ks[1], stride=(st[0], st[1]),
                                    pad=(pads[0], pads[2], pads[1], pads[3]), e_in=exps[ins[0]], e_out=exps[outs[0]])
-            case["x"] = np.ascontiguousarray(x)
+            case["x"] = np.ascontiguousarray(x4)
             assert o.oracle_pool(cases.pool_desc(case)) == 0
+            if pool1d:
+                case["out"] = case["out"].reshape(n, case["out"].shape[2], c)
             t[outs[0]] = case["out"]
         elif op == "Transpose":
             t[outs[0]] = np.ascontiguousarray(x.transpose(at["perm"]))
@@ -202,7 +221,9 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             assert o.oracle_softmax(cases.softmax_desc(xs.ctypes.data, y.ctypes.data, table.ctypes.data, xs.shape[0], xs.shape[1], abi.DTYPE_FLOAT, 0)) == 0
             t[outs[0]] = y.reshape(x.shape)
         elif op == "MatMul":
-            t[outs[0]] = matmul(o, x, t[ins[1]], exps[ins[0]], exps[ins[1]], exps[outs[0]], QDT[at["quant_type"]],
+            b_op = t[ins[1]] if ins[1] in t else init[ins[1]]["data"].reshape(init[ins[1]]["dims"])
+            e_b = exps[ins[1]] if ins[1] in exps else init[ins[1]]["exponents"][0]
+            t[outs[0]] = matmul(o, x, b_op, exps[ins[0]], e_b, exps[outs[0]], QDT[at["quant_type"]],
                                 ACT[at.get("activation", "Linear")], round_mode)
         elif op in ("ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin"):
             axes = [int(a) % x.ndim for a in init[ins[1]]["data"]] if len(ins) > 1 and ins[1] in init else list(range(x.ndim))
@@ -227,6 +248,30 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             for s0, e0, a, st in zip(starts, ends, axes, steps):
                 idx[a % x.ndim] = slice(s0, min(e0, x.shape[a % x.ndim]) if e0 >= 0 else e0, st)   # ONNX Slice = numpy slicing for st > 0
             t[outs[0]] = np.ascontiguousarray(x[tuple(idx)])
+        elif op == "InsertZeros":  # esp-dl/dl/module/include/dl_module_insert_zeros.hpp:33-58,76-128
+            sp = x.ndim - 2
+            stride = list(at.get("stride", [1]))
+            opad = list(at.get("output_padding", [0]))
+            stride = stride * sp if len(stride) == 1 else stride
+            opad = opad * sp if len(opad) == 1 else opad
+            shape = list(x.shape)
+            for i in range(sp):
+                shape[1 + i] = x.shape[1 + i] + (stride[i] - 1) * (x.shape[1 + i] - 1) + opad[i]
+            y = np.zeros(shape, dtype=x.dtype)
+            idx = (slice(None),) + tuple(slice(0, (x.shape[1 + i] - 1) * stride[i] + 1, stride[i]) for i in range(sp)) + (slice(None),)
+            y[idx] = x
+            t[outs[0]] = y
+        elif op in ("Squeeze", "Unsqueeze", "Identity"):
+            shape = m["value_info"][outs[0]]["shape"] if op != "Identity" else list(x.shape)
+            t[outs[0]] = np.ascontiguousarray(x).reshape([x.shape[0]] + list(shape[1:]) if len(shape) and shape[0] == 1 and x.size != int(np.prod(shape)) else shape)
+        elif op == "PRelu":  # without a `lut` attribute: slopes per channel (esp-dl/dl/base/dl_base_prelu.cpp:5-19)
+            alpha = init[ins[1]]
+            case = cases.eltwise_case(abi.ELT_PRELU, dtype=QDT[at["quant_type"]], out_shape=(x.size // x.shape[-1], x.shape[-1]),
+                                      e0=exps[ins[0]], e1=alpha["exponents"][0], eo=exps[outs[0]], round_mode=round_mode)
+            case["a"], case["b"] = np.ascontiguousarray(x.reshape(-1, x.shape[-1])), np.ascontiguousarray(alpha["data"].reshape(-1))
+            assert case["b"].size == x.shape[-1], "per-channel slopes expected"
+            assert o.oracle_eltwise(cases.eltwise_desc(case)) == 0
+            t[outs[0]] = case["out"].reshape(x.shape)
         else:
             raise NotImplementedError(op)
     return t

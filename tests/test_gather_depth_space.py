@@ -1,5 +1,5 @@
-"""Gather, SpaceToDepth and DepthToSpace ("DCR" / "CRD"): the oracle against the reference's own modules compiled for the
-host, the gather kernel against the oracle through the C ABI, and all three modules through one-node .espdl graphs."""
+"""Gather, SpaceToDepth, DepthToSpace ("DCR" / "CRD") and InsertZeros: the oracle against the reference's own modules compiled
+for the host, the gather kernel against the oracle through the C ABI, and the modules through one-node .espdl graphs."""
 import ctypes as C
 
 import numpy as np
@@ -129,6 +129,59 @@ def test_depth_space_modules(tmp_path, mode, n, h, w, c, bs, dt, qt):
     g.add_output("y", x.dtype.type, list(oshape), -5)
     path = str(tmp_path / "ds.espdl")
     g.save(path)
+    m = model.Model(path)
+    m.inputs[0].array[...] = x
+    m.run()
+    np.testing.assert_array_equal(np.asarray(m.outputs[0].array).reshape(oshape), want)
+    m.close()
+
+
+# (input shape, stride per spatial axis, output padding per spatial axis)
+INSERT_ZEROS = [((2, 5, 6, 8), (2, 2), (1, 1)), ((1, 7, 3, 16), (3, 2), (0, 1)), ((2, 9, 12), (2,), (1,)), ((1, 4, 4, 5), (1, 1), (0, 0))]
+
+
+def insert_zeros_graph(shape, stride, opad, dt):
+    """One-node graph as the exporter writes it, for the graph oracle and for dl::Model."""
+    from espdl_b200 import espdl_file
+    g = espdl_file.GraphBuilder("iz", metadata={"target": "c"})
+    g.add_input("x", NP[dt], list(shape), -5)
+    oshape = list(shape)
+    for i, (s, p) in enumerate(zip(stride, opad)):
+        oshape[1 + i] = shape[1 + i] + (s - 1) * (shape[1 + i] - 1) + p
+    g.add_node("InsertZeros", "iz", ["x"], ["y"], quant_type="S8" if dt == abi.DTYPE_INT8 else "S16", stride=list(stride), output_padding=list(opad))
+    g.add_output("y", NP[dt], oshape, -5)
+    return g, oshape
+
+
+@pytest.mark.parametrize("dt", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("shape,stride,opad", INSERT_ZEROS)
+def test_insert_zeros_graph_oracle_matches_reference(tmp_path, shape, stride, opad, dt):
+    import graph_oracle
+    from espdl_b200 import espdl_file
+    g, oshape = insert_zeros_graph(shape, stride, opad, dt)
+    path = str(tmp_path / "iz.espdl")
+    g.save(path)
+    info = np.iinfo(NP[dt])
+    x = np.random.default_rng(13).integers(info.min, info.max + 1, size=shape, dtype=NP[dt])
+    got = graph_oracle.run_graph(espdl_file.read(path), {"x": x})["y"]
+    ref = np.full(oshape, 0x55, dtype=NP[dt])
+    ci = lambda v: (C.c_int * len(v))(*v)
+    assert checkers.ref().ref_insert_zeros(x.ctypes.data, ref.ctypes.data, dt, ci(shape), len(shape), ci(stride), ci(opad)) == 0
+    np.testing.assert_array_equal(got, ref)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dt", [abi.DTYPE_INT8, abi.DTYPE_INT16])
+@pytest.mark.parametrize("shape,stride,opad", INSERT_ZEROS + [((4, 40, 40, 64), (2, 2), (1, 1))])
+def test_insert_zeros_module(tmp_path, shape, stride, opad, dt):
+    import graph_oracle
+    from espdl_b200 import espdl_file, model
+    g, oshape = insert_zeros_graph(shape, stride, opad, dt)
+    path = str(tmp_path / "iz.espdl")
+    g.save(path)
+    info = np.iinfo(NP[dt])
+    x = np.random.default_rng(17).integers(info.min, info.max + 1, size=shape, dtype=NP[dt])
+    want = graph_oracle.run_graph(espdl_file.read(path), {"x": x})["y"]
     m = model.Model(path)
     m.inputs[0].array[...] = x
     m.run()
