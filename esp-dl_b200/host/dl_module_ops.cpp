@@ -1629,6 +1629,85 @@ Module *InsertZeros::deserialize(fbs::FbsModel *m, std::string node)
     return new InsertZeros(node.c_str(), stride, output_padding, node_quant(m, node));
 }
 
+StreamingCache::~StreamingCache()
+{
+    if (m_cache)
+        espdl_b200_arena_free(m_cache);
+}
+
+std::vector<std::vector<int>> StreamingCache::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    std::vector<int> out = input_shapes[0];
+    if (m_frame_axis < 0)
+        m_frame_axis += (int)out.size();
+    if (m_frame_axis < 0 || m_frame_axis >= (int)out.size() || m_window_size < 1) {
+        ESP_LOGE("StreamingCache", "%s: frame_axis outside the tensor", name ? name : "?");
+        return {{}};
+    }
+    out[m_frame_axis] += m_window_size - 1;
+    return {out};
+}
+
+esp_err_t StreamingCache::prepare(ModelContext *context)
+{
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    if (!out || m_frame_axis < 0 || m_frame_axis >= (int)out->shape.size())
+        return ESP_FAIL;
+    size_t n = dtype_sizeof(out->dtype) * (size_t)(m_window_size - 1);
+    for (int i = 0; i < (int)out->shape.size(); i++)
+        if (i != m_frame_axis)
+            n *= (size_t)out->shape[i];
+    if (m_cache)
+        espdl_b200_arena_free(m_cache);
+    m_cache = nullptr, m_cache_bytes = n;
+    if (n == 0)
+        return ESP_OK;
+    if (espdl_b200_arena_alloc(n, &m_cache) != ESPDL_OK || espdl_b200_memset(m_cache, 0, n, nullptr) != ESPDL_OK ||
+        espdl_b200_stream_sync(nullptr) != ESPDL_OK)
+        return ESP_FAIL;
+    return ESP_OK;
+}
+
+void StreamingCache::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *in = context->get_tensor(m_inputs_index[0]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!in || !out || !in->device || !out->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    const size_t in_bytes = in ? (size_t)in->get_size() * dtype_sizeof(in->dtype) : 0;
+    if (!st && (size_t)out->get_size() * dtype_sizeof(out->dtype) != in_bytes + m_cache_bytes)
+        st = ESPDL_ERR_INVALID_ARG;
+    auto copy_bytes = [&](const void *src, void *dst, size_t n) {
+        return n ? enqueue_copy(context, src, dst, 1, {(int)n}, {1}, {1}) : ESPDL_OK;
+    };
+    // dl_module_streaming_cache.hpp:56-70
+    if (!st && m_cache_bytes)
+        st = copy_bytes(m_cache, out->device, m_cache_bytes);
+    if (!st)
+        st = copy_bytes(in->device, (char *)out->device + m_cache_bytes, in_bytes);
+    if (!st && m_cache_bytes)
+        st = copy_bytes((char *)out->device + in_bytes, m_cache, m_cache_bytes);
+    if (st)
+        ESP_LOGE("StreamingCache", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+void StreamingCache::reset()
+{
+    if (m_cache && m_cache_bytes) {
+        espdl_b200_memset(m_cache, 0, m_cache_bytes, nullptr);
+        espdl_b200_stream_sync(nullptr);
+    }
+}
+
+Module *StreamingCache::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int window_size = 1, frame_axis = 1;
+    m->get_operation_attribute(node, "window_size", window_size);
+    m->get_operation_attribute(node, "frame_axis", frame_axis);
+    return new StreamingCache(node.c_str(), window_size, frame_axis, MODULE_NON_INPLACE, node_quant(m, node));
+}
+
 Gather::~Gather()
 {
     delete m_indices;
@@ -2003,6 +2082,7 @@ void ModuleCreator::register_dl_modules()
     register_module("DepthToSpace", DepthToSpace::deserialize);
     register_module("Gather", Gather::deserialize);
     register_module("InsertZeros", InsertZeros::deserialize);
+    register_module("StreamingCache", StreamingCache::deserialize);
     register_module("RMSNormalization", RMSNormalization::deserialize);
     register_module("LayerNormalization", LayerNormalization::deserialize);
     register_module("Reshape", Reshape::deserialize_reshape);

@@ -392,6 +392,30 @@ protected:
     std::vector<int> m_stride, m_output_padding;
 };
 
+/// StreamingCache (dl_module_streaming_cache.hpp): keeps the last `window_size - 1` frames of its input between runs and puts
+/// them in front of the new frames: output = [cache | input], then cache = the output's last cache-size bytes (byte
+/// ranges of the flat tensors, as the reference copies them).  The cache lives in device memory and starts as zeros;
+/// reset() clears it.
+class StreamingCache : public Module {
+public:
+    StreamingCache(const char *name = nullptr, int window_size = 1, int frame_axis = 1, module_inplace_t inplace = MODULE_NON_INPLACE,
+                   quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, inplace, quant_type), m_window_size(window_size), m_frame_axis(frame_axis), m_cache(nullptr), m_cache_bytes(0)
+    {
+    }
+    ~StreamingCache();
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    esp_err_t prepare(ModelContext *context) override;
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    void reset() override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int m_window_size, m_frame_axis;
+    void *m_cache;
+    size_t m_cache_bytes;
+};
+
 /// Gather along one axis with constant indices (dl_module_gather.hpp): the module owns `indices` (int32 or int64, any
 /// shape); prepare() checks them against the axis length and uploads them as int32.
 class Gather : public Module {

@@ -118,6 +118,9 @@ int espdl_model_wait(void *handle)
     return h->model->wait() == ESP_OK ? 0 : (h->model->m_status ? h->model->m_status : -1);
 }
 
+/// dl::Model::reset(): clears the state modules keep between runs (the StreamingCache frames).
+void espdl_model_reset(void *handle) { ((Handle *)handle)->model->reset(); }
+
 int espdl_model_test(void *handle) { return ((Handle *)handle)->model->test(); }
 
 void *espdl_model_stream(void *handle) { return ((Handle *)handle)->model->stream(); }

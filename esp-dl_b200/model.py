@@ -82,6 +82,12 @@ class Model:
         """Host buffers -> device, execute, device -> host buffers (the call a user of dl::Model makes)."""
         abi.check(self.lib.espdl_model_run(self.h), "Model::run")
 
+    def reset(self):
+        """dl::Model::reset(): clears what modules keep between runs (streaming caches)."""
+        self.lib.espdl_model_reset.restype = None
+        self.lib.espdl_model_reset.argtypes = [C.c_void_p]
+        self.lib.espdl_model_reset(self.h)
+
     def submit(self):
         """Pipelined run(): uploads the input arrays (they may be refilled when this returns) and enqueues the pass."""
         abi.check(self.lib.espdl_model_submit(self.h), "Model::submit")

@@ -29,6 +29,8 @@ for chip, target in (("p4", "esp32p4"), ("s3", "esp32s3")):
 for target in ("esp32p4", "esp32s3"):
     SOURCES.append((os.path.join(REF, "examples/tutorial/how_to_deploy_streaming_model/test_streaming_model/main/models",
                                  target, "model.espdl"), f"{target}__streaming_tcn.espdl"))
+    SOURCES.append((os.path.join(REF, "examples/tutorial/how_to_deploy_streaming_model/test_streaming_model/main/models",
+                                 target, "streaming_model.espdl"), f"{target}__streaming_tcn_chunked.espdl"))
 
 SOURCES.append((os.path.join(REF, "models/imagenet_cls/models/p4/imagenet_cls_mobilenetv2_s8_v1.espdl"), "esp32p4__zoo_mobilenetv2.espdl"))
 SOURCES.append((os.path.join(REF, "models/coco_detect/models/p4/coco_detect_yolo11n_320_s8_v1.espdl"), "esp32p4__zoo_yolo11n_320.espdl"))

@@ -298,3 +298,27 @@ def test_block_fusion_pass(tmp_path, monkeypatch):
     m.run()
     np.testing.assert_array_equal(m.outputs[0].array, first)
     m.close()
+
+
+@pytest.mark.parametrize("target", ["esp32p4", "esp32s3"])
+def test_streaming_model_equals_the_whole_sequence_model(target, monkeypatch):
+    """The reference's own check of its streaming tutorial (examples/tutorial/how_to_deploy_streaming_model/
+    test_streaming_model/main/app_main.cpp:8-72): the model with StreamingCache nodes, fed the sequence three frames at a
+    time, ends on the output the whole-sequence model gives; after reset() it does so again."""
+    monkeypatch.setenv("ESPDL_B200_TARGET", target)
+    whole = model.Model(os.path.join(GOLDEN, f"{target}__streaming_tcn.espdl"))
+    chunked = model.Model(os.path.join(GOLDEN, f"{target}__streaming_tcn_chunked.espdl"))
+    frames, step = whole.inputs[0].shape[1], chunked.inputs[0].shape[1]
+    assert frames % step == 0 and chunked.inputs[0].shape[2:] == whole.inputs[0].shape[2:]
+    for seed in (1, 2):
+        x = np.random.default_rng(seed).integers(-128, 128, size=whole.inputs[0].shape, dtype=np.int8)
+        whole.inputs[0].array[...] = x
+        whole.run()
+        for k in range(frames // step):
+            chunked.inputs[0].array[...] = x[:, k * step:(k + 1) * step]
+            chunked.run()
+        np.testing.assert_array_equal(np.asarray(chunked.outputs[0].array), np.asarray(whole.outputs[0].array))
+        assert np.asarray(whole.outputs[0].array).astype(np.float32).std() > 0
+        chunked.reset()
+    whole.close()
+    chunked.close()
