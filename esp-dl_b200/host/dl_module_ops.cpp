@@ -563,6 +563,19 @@ size_t MatMul::workspace_bytes(ModelContext *context)
     memset(&d, 0, sizeof(d));
     d.dtype = ESPDL_DTYPE_INT16, d.n = 1, d.in_h = d.out_h = 1, d.in_w = d.out_w = M, d.in_c = K, d.out_c = N, d.kh = d.kw = 1;
     d.stride_h = d.stride_w = d.dilation_h = d.dilation_w = 1, d.group = 1;
+    // the query validates the descriptor like a launch does, so it needs the operands' addresses too
+    TensorBase *in0 = context->get_tensor(m_inputs_index[0]), *in1 = context->get_tensor(m_inputs_index[1]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    if (!in0 || !in1 || !out || !in0->device || !in1->device || !out->device)
+        return 0;
+    d.input = in0->device, d.filter = in1->device, d.output = out->device;
+    // the batched form (one launch over all slices) splits all rows at once
+    long long count = 1;
+    for (size_t i = 0; i < b0.size(); i++) count *= std::max(b0[i], b1[i]);
+    bool shared = true;
+    for (int v : b1) shared = shared && v == 1;
+    if (shared && count > 1 && count <= 0x7fffffffll)
+        d.n = (int)count;
     size_t bytes = 0;
     return espdl_b200_conv2d_workspace_bytes(&d, &bytes) == ESPDL_OK ? bytes : 0;
 }

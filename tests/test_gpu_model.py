@@ -322,3 +322,31 @@ def test_streaming_model_equals_the_whole_sequence_model(target, monkeypatch):
         chunked.reset()
     whole.close()
     chunked.close()
+
+
+@pytest.mark.parametrize("dt,qt,sa,sb", [(np.int16, "S16", (1, 40, 80), (80, 520)), (np.int16, "S16", (3, 24, 64), (64, 48)),
+                                         (np.int8, "S8", (1, 40, 160), (160, 80))])
+def test_matmul_with_a_constant_operand(tmp_path, dt, qt, sa, sb):
+    """MatMul whose second operand is a parameter of the file (the recognition head of a text model): the module uploads
+    it and, for int16, sizes the tile kernel's byte-plane scratch from its own shapes."""
+    e_a, e_b, e_out = (-12, -14, -9) if dt == np.int16 else (-5, -6, -3)
+    rng = np.random.default_rng(12)
+    info = np.iinfo(dt)
+    w = rng.integers(info.min // 8, info.max // 8, size=sb, dtype=dt)
+    g = espdl_file.GraphBuilder("matmul_const", metadata={"target": "c"})
+    g.add_input("a", dt, list(sa), e_a)
+    g.add_initializer("w", w, [e_b])
+    g.add_node("MatMul", "mm", ["a", "w"], ["y"], quant_type=qt, activation="Linear")
+    so = list(sa[:-1]) + [sb[-1]]
+    g.add_output("y", dt, so, e_out)
+    path = str(tmp_path / "mmc.espdl")
+    g.save(path)
+    m = model.Model(path)
+    a = rng.integers(info.min // 8, info.max // 8, size=sa, dtype=dt)
+    m.inputs[0].array[...] = a
+    m.run()
+    dtype = abi.DTYPE_INT16 if dt == np.int16 else abi.DTYPE_INT8
+    want = graph_oracle.matmul(__import__("checkers").oracle(), a, w, e_a, e_b, e_out, dtype, abi.ACT_LINEAR, abi.ROUND_HALF_UP)
+    np.testing.assert_array_equal(np.asarray(m.outputs[0].array).reshape(so), want.reshape(so))
+    assert want.std() > 0
+    m.close()
