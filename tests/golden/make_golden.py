@@ -35,6 +35,17 @@ for target in ("esp32p4", "esp32s3"):
 SOURCES.append((os.path.join(REF, "models/imagenet_cls/models/p4/imagenet_cls_mobilenetv2_s8_v1.espdl"), "esp32p4__zoo_mobilenetv2.espdl"))
 SOURCES.append((os.path.join(REF, "models/coco_detect/models/p4/coco_detect_yolo11n_320_s8_v1.espdl"), "esp32p4__zoo_yolo11n_320.espdl"))
 
+# smaller model-zoo files that bring operators and layouts the two above do not have: an ESP32-S3 layout (half-up rounding),
+# PRelu with per-channel slopes, InsertZeros (transposed-convolution halves) with rectangular pool strides, and the
+# detector / re-identification topologies
+for src, name in (("models/human_face_detect/models/p4/human_face_detect_msr_s8_v1.espdl", "esp32p4__zoo_face_msr.espdl"),
+                  ("models/human_face_detect/models/s3/human_face_detect_msr_s8_v1.espdl", "esp32s3__zoo_face_msr.espdl"),
+                  ("models/human_face_detect/models/p4/human_face_detect_mnp_s8_v1.espdl", "esp32p4__zoo_face_mnp.espdl"),
+                  ("models/pedestrian_detect/models/p4/pedestrian_detect_pico_s8_v1.espdl", "esp32p4__zoo_pedestrian_pico.espdl"),
+                  ("models/person_reid/models/p4/person_reid_feat_osn_s8_v1.espdl", "esp32p4__zoo_person_reid.espdl"),
+                  ("models/pp_ocr_v6/models/p4/pp_ocr_v6_det_s8.espdl", "esp32p4__zoo_ocr_det.espdl")):
+    SOURCES.append((os.path.join(REF, src), name))
+
 if __name__ == "__main__":
     os.makedirs(OUT, exist_ok=True)
     for src, name in SOURCES:

@@ -52,7 +52,7 @@ def test_cpp_reader_matches_python_reader_on_shipped_models(host, path):
         assert int(f[2]) == t["data_type"]
         assert f[3] == "[" + ", ".join(str(d) for d in (t["dims"] or [1])) + "]"
         assert int(f[4]) == max(1, len(t["exponents"]))
-        assert int(f[5]) == int(t["data"].view(np.uint8).astype(np.int64).sum())
+        assert int(f[5]) == int(np.ascontiguousarray(t["data"]).reshape(-1).view(np.uint8).astype(np.int64).sum())
 
 
 def test_cpp_reader_reads_generated_network(host, tmp_path):
@@ -69,7 +69,7 @@ def test_cpp_reader_reads_generated_network(host, tmp_path):
     assert first[4].startswith("features.0_out,[1, 112, 112, 32],")
     for name, f in params.items():
         t = m["initializers"][name]
-        assert int(f[5]) == int(t["data"].view(np.uint8).astype(np.int64).sum())
+        assert int(f[5]) == int(np.ascontiguousarray(t["data"]).reshape(-1).view(np.uint8).astype(np.int64).sum())
     assert int(params["features.0.weight"][4]) == 32   # per-channel exponents
 
 
