@@ -160,8 +160,19 @@ template <int OP>
 __global__ void __launch_bounds__(256) elt_s8_vec16_kernel(EltParams p, long long nvec)
 {
     __shared__ int8_t table[256];
+    // One-operand int8 -> int8 operators are functions of the input byte: every block tabulates the operator once with
+    // the scalar code (so the rounding is the reference's) and then runs as a table lookup like LUT itself.
+    constexpr bool TABULATED = OP == ESPDL_ELT_REQUANTIZE || OP == ESPDL_ELT_CLIP || OP == ESPDL_ELT_RELU;
     if (OP == ESPDL_ELT_LUT) {
         for (int i = threadIdx.x; i < 256; i += blockDim.x) table[i] = ((const int8_t *)p.b)[i];
+        __syncthreads();
+    } else if (TABULATED) {
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+            EltParams q2 = p;
+            q2.op = OP;
+            const int a = (int)(int8_t)(uint8_t)(i ^ 0x80);
+            table[i] = (int8_t)sat8((int)max(-1000000ll, min(1000000ll, elt_int(q2, a, 0))));
+        }
         __syncthreads();
     }
     for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
@@ -180,7 +191,7 @@ __global__ void __launch_bounds__(256) elt_s8_vec16_kernel(EltParams p, long lon
                 const int a = (int)(int8_t)(aw[q] >> (8 * j));
                 const int b = (int)(int8_t)(bw[q] >> (8 * j));
                 int r;
-                if (OP == ESPDL_ELT_LUT) {
+                if (OP == ESPDL_ELT_LUT || TABULATED) {
                     r = table[(uint8_t)a ^ 0x80u];
                 } else if (OP == ESPDL_ELT_ADD) {
                     r = sat8(a + b);

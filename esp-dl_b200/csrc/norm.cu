@@ -44,14 +44,142 @@ __device__ __forceinline__ void store_q(T *p, long long i, int q)
     p[i] = (T)(sizeof(T) == 1 ? sat8(q) : sat16(q));
 }
 
+// V consecutive elements of a row as one 32-bit word: 4 int8 or 2 int16.
+template <typename T>
+struct Word {
+    static constexpr int V = 4 / (int)sizeof(T);
+    uint32_t w;
+    __device__ __forceinline__ int get(int i) const
+    {
+        return sizeof(T) == 1 ? (int)(int8_t)(w >> (8 * i)) : (int)(int16_t)(w >> (16 * i));
+    }
+    __device__ __forceinline__ void set(int i, int q)
+    {
+        if (sizeof(T) == 1)
+            w |= ((uint32_t)sat8(q) & 0xffu) << (8 * i);
+        else
+            w |= ((uint32_t)sat16(q) & 0xffffu) << (16 * i);
+    }
+};
+
+// Rows whose length is a multiple of V and whose pointers are word aligned: every lane moves whole words.  The
+// variance terms of 32 * V consecutive elements go through shared memory (one float4 / float2 per lane) and every lane
+// then adds them in element order from broadcast reads, which costs a quarter of the shuffles of the scalar form.
+template <typename T>
+__device__ __forceinline__ void norm_row_words(const NormParams &p, const T *x, T *y, long long row, int lane, float *stage)
+{
+    constexpr int V = Word<T>::V;
+    const int words = p.len / V;
+    const uint32_t *xw = (const uint32_t *)x;
+    uint32_t *yw = (uint32_t *)y;
+    if (p.op == ESPDL_NORM_RMS) {
+        long long ss = 0;
+        for (int j = lane; j < words; j += 32) {
+            Word<T> a{xw[j]};
+#pragma unroll
+            for (int i = 0; i < V; i++) ss += (long long)(a.get(i) * a.get(i));
+        }
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float fsum = sizeof(T) == 1 ? __int2float_rn((int)ss) : __ll2float_rn(ss);
+        const float mean_sq = __fdiv_rn(__fmul_rn(fsum, __fmul_rn(p.in_scale, p.in_scale)), __int2float_rn(p.len));
+        float rms = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean_sq, p.epsilon)));
+        rms = __fmul_rn(rms, __fmul_rn(p.in_scale, p.out_rescale));
+        const float *sc = (const float *)p.scale;
+        const bool sc_vec = ((uintptr_t)sc % (4 * V)) == 0;
+        for (int j = lane; j < words; j += 32) {
+            Word<T> a{xw[j]}, r{0u};
+            float s4[V];
+            if (sc_vec && V == 4) {
+                const float4 t = *(const float4 *)(sc + j * V);
+                s4[0] = t.x, s4[1] = t.y, s4[V - 2] = t.z, s4[V - 1] = t.w;
+            } else if (sc_vec) {
+                const float2 t = *(const float2 *)(sc + j * V);
+                s4[0] = t.x, s4[1] = t.y;
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; i++) s4[i] = sc[j * V + i];
+            }
+#pragma unroll
+            for (int i = 0; i < V; i++) r.set(i, fround(__fmul_rn(__fmul_rn(__int2float_rn(a.get(i)), rms), s4[i]), p.half_even));
+            yw[j] = r.w;
+        }
+        return;
+    }
+    int sum = 0;
+    for (int j = lane; j < words; j += 32) {
+        Word<T> a{xw[j]};
+#pragma unroll
+        for (int i = 0; i < V; i++) sum += a.get(i);
+    }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    float mean = (float)((double)sum * 1.0 / (double)p.len);
+    if (p.mean && lane == 0)
+        store_q((T *)p.mean, row, fround(__fmul_rn(__fmul_rn(mean, p.mean_rescale), p.in_scale), p.half_even));
+    float var = 0.f;
+    for (int base = 0; base < words; base += 32) {
+        const int j = base + lane;
+        float d2[V];
+#pragma unroll
+        for (int i = 0; i < V; i++) d2[i] = 0.f;
+        if (j < words) {
+            Word<T> a{xw[j]};
+#pragma unroll
+            for (int i = 0; i < V; i++) {
+                const float d = __fsub_rn(__int2float_rn(a.get(i)), mean);
+                d2[i] = __fmul_rn(d, d);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < V; i++) stage[lane * V + i] = d2[i];
+        __syncwarp();
+        const int n = min(32, words - base) * V;
+        for (int k = 0; k < n; k += V) { // one broadcast read of V terms, added in element order
+            if (V == 4) {
+                const float4 t = *(const float4 *)(stage + k);
+                var = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(var, t.x), t.y), t.z), t.w);
+            } else {
+                const float2 t = *(const float2 *)(stage + k);
+                var = __fadd_rn(__fadd_rn(var, t.x), t.y);
+            }
+        }
+    }
+    mean = __fmul_rn(mean, p.in_scale);
+    var = __fmul_rn(var, __fmul_rn(p.in_scale, p.in_scale));
+    var = __fdiv_rn(var, __int2float_rn(p.len));
+    const float inv_std = __fdiv_rn(1.0f, sqrt_newton_dev(__fadd_rn(var, p.epsilon)));
+    if (p.inv_std && lane == 0)
+        store_q((T *)p.inv_std, row, fround(__fmul_rn(inv_std, p.inv_std_rescale), p.half_even));
+    const T *sc = (const T *)p.scale, *bi = (const T *)p.bias;
+    for (int j = lane; j < words; j += 32) {
+        Word<T> a{xw[j]}, r{0u};
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            const int e = j * V + i;
+            const float xv = __fmul_rn(__int2float_rn(a.get(i)), p.in_scale);
+            const float normalized = __fmul_rn(__fsub_rn(xv, mean), inv_std);
+            const float sv = sc ? __fmul_rn(__int2float_rn((int)sc[e]), p.scale_scale) : 1.0f;
+            const float bv = bi ? __fmul_rn(__int2float_rn((int)bi[e]), p.bias_scale) : 0.0f;
+            r.set(i, fround(__fmul_rn(__fadd_rn(__fmul_rn(normalized, sv), bv), p.out_rescale), p.half_even));
+        }
+        yw[j] = r.w;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) norm_kernel(NormParams p)
 {
+    __shared__ __align__(16) float stage_all[8][128];
+    const bool words_ok = p.len % Word<T>::V == 0 && ((uintptr_t)p.in % 4) == 0 && ((uintptr_t)p.out % 4) == 0;
     const int lane = threadIdx.x & 31;
     const long long warp = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5, warps = ((long long)gridDim.x * blockDim.x) >> 5;
     for (long long row = warp; row < p.rows; row += warps) {
         const T *x = (const T *)p.in + row * p.len;
         T *y = (T *)p.out + row * p.len;
+        if (words_ok) {
+            norm_row_words<T>(p, x, y, row, lane, stage_all[threadIdx.x >> 5]);
+            continue;
+        }
         if (p.op == ESPDL_NORM_RMS) {
             // int8: int32 sum of squares (as dl::base::reduce_l2 returns it), int16: int64
             long long ss = 0;

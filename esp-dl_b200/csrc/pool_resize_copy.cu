@@ -186,6 +186,109 @@ __global__ void __launch_bounds__(256) copy_kernel(CopyParams p)
     }
 }
 
+// Transposing copies (the destination's innermost axis is strided in the source while another axis - `ya` - is the
+// source's contiguous one): a 64 x 64 tile goes through shared memory so that both the reads (along ya) and the
+// writes (along the innermost axis) touch consecutive addresses.  The row pitch of 64 * sizeof(T) + 4 bytes keeps the
+// column reads of the store phase on distinct banks.
+template <typename T>
+__global__ void __launch_bounds__(256) copy_transpose_kernel(CopyParams p, int ya, long long tiles)
+{
+    constexpr int TILE = 64, PITCH = TILE * (int)sizeof(T) + 4;
+    __shared__ __align__(16) unsigned char tile[TILE * PITCH];
+    const int nx = p.shape[5], ny = p.shape[ya];
+    const int tx_count = (nx + TILE - 1) / TILE, ty_count = (ny + TILE - 1) / TILE;
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+        long long r = t;
+        const int x0 = (int)(r % tx_count) * TILE;
+        r /= tx_count;
+        const int y0 = (int)(r % ty_count) * TILE;
+        r /= ty_count;
+        long long si = 0, di = 0;
+#pragma unroll
+        for (int k = 4; k >= 0; k--) {
+            if (k == ya)
+                continue;
+            const int idx = (int)(r % p.shape[k]);
+            r /= p.shape[k];
+            si += idx * p.ss[k];
+            di += idx * p.ds[k];
+        }
+        const T *src = (const T *)p.src + si;
+        T *dst = (T *)p.dst + di;
+        __syncthreads(); // the previous tile has been stored
+        {
+            const int yy = threadIdx.x % TILE, xx0 = threadIdx.x / TILE;
+            const T *sp = src + (long long)(x0 + xx0) * p.ss[5] + (long long)(y0 + yy) * p.ss[ya];
+            const long long step = (256 / TILE) * p.ss[5];
+            if (y0 + yy < ny)
+                for (int xx = xx0; xx < TILE && x0 + xx < nx; xx += 256 / TILE, sp += step)
+                    *(T *)(tile + xx * PITCH + yy * (int)sizeof(T)) = *sp;
+        }
+        __syncthreads();
+        {
+            const int xx = threadIdx.x % TILE, yy0 = threadIdx.x / TILE;
+            T *dp = dst + (long long)(x0 + xx) * p.ds[5] + (long long)(y0 + yy0) * p.ds[ya];
+            const long long step = (256 / TILE) * p.ds[ya];
+            if (x0 + xx < nx)
+                for (int yy = yy0; yy < TILE && y0 + yy < ny; yy += 256 / TILE, dp += step)
+                    *dp = *(const T *)(tile + xx * PITCH + yy * (int)sizeof(T));
+        }
+    }
+}
+
+// The same tile with 32-bit global accesses: V = 4 / sizeof(T) elements per access on both sides.  The caller has checked
+// that both extents, every stride that is not 1, and both pointers are multiples of V elements.
+template <typename T>
+__global__ void __launch_bounds__(256) copy_transpose_words_kernel(CopyParams p, int ya, long long tiles)
+{
+    constexpr int TILE = 64, PITCH = TILE * (int)sizeof(T) + 4, V = 4 / (int)sizeof(T), WPR = TILE / V; // words per tile row
+    __shared__ __align__(16) unsigned char tile[TILE * PITCH];
+    const int nx = p.shape[5], ny = p.shape[ya];
+    const int tx_count = (nx + TILE - 1) / TILE, ty_count = (ny + TILE - 1) / TILE;
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+        long long r = t;
+        const int x0 = (int)(r % tx_count) * TILE;
+        r /= tx_count;
+        const int y0 = (int)(r % ty_count) * TILE;
+        r /= ty_count;
+        long long si = 0, di = 0;
+#pragma unroll
+        for (int k = 4; k >= 0; k--) {
+            if (k == ya)
+                continue;
+            const int idx = (int)(r % p.shape[k]);
+            r /= p.shape[k];
+            si += idx * p.ss[k];
+            di += idx * p.ds[k];
+        }
+        const T *src = (const T *)p.src + si;
+        T *dst = (T *)p.dst + di;
+        __syncthreads();
+        {
+            const int yy = (threadIdx.x % WPR) * V, xx0 = threadIdx.x / WPR;
+            const T *sp = src + (long long)(x0 + xx0) * p.ss[5] + (y0 + yy);
+            const long long step = (256 / WPR) * p.ss[5];
+            if (y0 + yy < ny)
+                for (int xx = xx0; xx < TILE && x0 + xx < nx; xx += 256 / WPR, sp += step)
+                    *(uint32_t *)(tile + xx * PITCH + yy * (int)sizeof(T)) = *(const uint32_t *)sp;
+        }
+        __syncthreads();
+        {
+            const int xx = (threadIdx.x % WPR) * V, yy0 = threadIdx.x / WPR;
+            T *dp = dst + (x0 + xx) + (long long)(y0 + yy0) * p.ds[ya];
+            const long long step = (256 / WPR) * p.ds[ya];
+            if (x0 + xx < nx)
+                for (int yy = yy0; yy < TILE && y0 + yy < ny; yy += 256 / WPR, dp += step) {
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int i = 0; i < V; i++)
+                        w |= (uint32_t)(*(const T *)(tile + (xx + i) * PITCH + yy * (int)sizeof(T))) << (8 * (int)sizeof(T) * i);
+                    *(uint32_t *)dp = w;
+                }
+        }
+    }
+}
+
 } // namespace espdl
 
 using namespace espdl;
@@ -424,8 +527,39 @@ extern "C" int espdl_b200_copy(const espdl_copy_desc *d, void *stream)
         p.total /= f;
         es *= f;
     }
-    long long blocks = min((p.total + 255) / 256, (long long)num_sms() * 32);
     cudaStream_t s = (cudaStream_t)stream;
+    if (es <= 2 && p.ds[5] == 1 && p.ss[5] != 1 && p.shape[5] >= 16) {
+        int ya = -1;
+        for (int k = 4; k >= 0; k--)
+            if (p.ss[k] == 1 && p.shape[k] >= 16)
+                ya = k;
+        if (ya >= 0) {
+            long long tiles = (long long)((p.shape[5] + 63) / 64) * ((p.shape[ya] + 63) / 64);
+            for (int k = 0; k < 5; k++)
+                if (k != ya)
+                    tiles *= p.shape[k];
+            const unsigned grid = (unsigned)min(tiles, (long long)num_sms() * 16);
+            const int V = 4 / es;
+            bool words = p.shape[5] % V == 0 && p.shape[ya] % V == 0 && ((uintptr_t)p.src % 4) == 0 && ((uintptr_t)p.dst % 4) == 0;
+            for (int k = 0; k < 6 && words; k++) {
+                if (k != ya && p.shape[k] > 1 && p.ss[k] % V != 0)
+                    words = false; // source rows start on word boundaries
+                if (k != 5 && p.shape[k] > 1 && p.ds[k] % V != 0)
+                    words = false;
+            }
+            if (words && es == 1)
+                copy_transpose_words_kernel<uint8_t><<<grid, 256, 0, s>>>(p, ya, tiles);
+            else if (words)
+                copy_transpose_words_kernel<uint16_t><<<grid, 256, 0, s>>>(p, ya, tiles);
+            else if (es == 1)
+                copy_transpose_kernel<uint8_t><<<grid, 256, 0, s>>>(p, ya, tiles);
+            else
+                copy_transpose_kernel<uint16_t><<<grid, 256, 0, s>>>(p, ya, tiles);
+            count_launch();
+            return check_launch("copy");
+        }
+    }
+    long long blocks = min((p.total + 255) / 256, (long long)num_sms() * 32);
     switch (es) {
     case 1: copy_kernel<uint8_t><<<(unsigned)blocks, 256, 0, s>>>(p); break;
     case 2: copy_kernel<uint16_t><<<(unsigned)blocks, 256, 0, s>>>(p); break;

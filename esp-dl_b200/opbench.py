@@ -4,6 +4,7 @@
     python esp-dl_b200/opbench.py --case pw32_192 [--iters 10] [--kernel auto|simt|tc]
     python esp-dl_b200/opbench.py --conv n,h,w,cin,cout,k,stride,depthwise(0/1),bits(8/16)
     python esp-dl_b200/opbench.py --block n,h,w,cin,hidden,cout,stride      (or a name from BLOCKS)
+    python esp-dl_b200/opbench.py --mem add|lut|requant|clip|mul|maxpool|resize2|rmsnorm|layernorm|gather|transpose   (or all)
     python esp-dl_b200/opbench.py --list
 
 Device memory, streams and events come from the library itself; between timed launches a buffer larger than the
@@ -215,11 +216,86 @@ def run_block(dev, spec, iters, warm):
     return ms_f, ms_s, 2 * macs / ms_f / 1e9, algo / ms_f / 1e6, algo
 
 
+MEM_CASES = ("add", "lut", "requant", "clip", "mul", "maxpool", "resize2", "rmsnorm", "layernorm", "gather", "transpose")
+
+
+def run_mem(dev, name, iters, warm):
+    """One bandwidth-bound kernel on an int8 tensor of 256x56x56x96 (77 MB, below L2 only after the flush): median ms and
+    GB/s over the algorithmic bytes (every input and output once)."""
+    L = dev.L
+    rng = np.random.default_rng(5)
+    n, h, w, c = 256, 56, 56, 96
+    x = rng.integers(-128, 128, size=(n, h, w, c), dtype=np.int8)
+    px = dev.put(x)
+    algo = 2 * x.nbytes
+    if name in ("add", "mul", "lut", "requant", "clip"):
+        d = abi.EltwiseDesc()
+        d.op = {"add": abi.ELT_ADD, "mul": abi.ELT_MUL, "lut": abi.ELT_LUT, "requant": abi.ELT_REQUANTIZE, "clip": abi.ELT_CLIP}[name]
+        d.input0, d.output = px, dev.empty(x.nbytes)
+        if name in ("add", "mul"):
+            d.input1 = dev.put(rng.integers(-128, 128, size=x.shape, dtype=np.int8))
+            algo = 3 * x.nbytes
+        elif name == "lut":
+            d.input1 = dev.put(rng.integers(-128, 128, size=256, dtype=np.int8))
+        d.in_dtype = d.out_dtype = abi.DTYPE_INT8
+        d.ndim = 1
+        d.out_shape[0] = d.in0_shape[0] = x.size
+        d.in1_shape[0] = x.size if name in ("add", "mul") else 1
+        d.in0_exponent, d.in1_exponent, d.out_exponent = (-5, -5, -5) if name == "add" else (-5, -6, -7)
+        d.clip_lo, d.clip_hi = 0, 96
+        fn = lambda: abi.check(L.espdl_b200_eltwise(C.byref(d), None), name)
+    elif name in ("maxpool", "resize2"):
+        if name == "maxpool":
+            d = abi.PoolDesc()
+            d.op, d.dtype = abi.POOL_MAX, abi.DTYPE_INT8
+            d.n, d.in_h, d.in_w, d.c, d.out_h, d.out_w = n, h, w, c, h, w
+            d.kh = d.kw = 5
+            d.stride_h = d.stride_w = 1
+            d.pad_top = d.pad_bottom = d.pad_left = d.pad_right = 2
+            d.in_exponent = d.out_exponent = -5
+            d.input, d.output = px, dev.empty(x.nbytes)
+            fn = lambda: abi.check(L.espdl_b200_pool(C.byref(d), None), name)
+        else:
+            d = abi.ResizeDesc()
+            d.dtype = abi.DTYPE_INT8
+            d.n, d.in_h, d.in_w, d.c, d.out_h, d.out_w = n, h, w, c, 2 * h, 2 * w
+            d.scale_h = d.scale_w = 2.0
+            d.in_exponent = d.out_exponent = -5
+            d.input, d.output = px, dev.empty(4 * x.nbytes)
+            algo = 5 * x.nbytes
+            fn = lambda: abi.check(L.espdl_b200_resize(C.byref(d), None), name)
+    elif name in ("rmsnorm", "layernorm"):
+        d = abi.NormDesc()
+        d.op, d.dtype = (abi.NORM_RMS if name == "rmsnorm" else abi.NORM_LAYER), abi.DTYPE_INT8
+        d.rows, d.len = x.size // 768, 768
+        d.input, d.output = px, dev.empty(x.nbytes)
+        d.scale = dev.put(np.ones(768, dtype=np.float32)) if name == "rmsnorm" else dev.put(np.full(768, 64, dtype=np.int8))
+        d.in_exponent, d.out_exponent, d.scale_exponent, d.epsilon = -5, -5, -6, 1e-5
+        fn = lambda: abi.check(L.espdl_b200_norm(C.byref(d), None), name)
+    elif name == "gather":
+        d = abi.GatherDesc()
+        idx = rng.permutation(h * w).astype(np.int32)
+        d.input, d.output, d.indices = px, dev.empty(x.nbytes), dev.put(idx)
+        d.elem_size, d.num_indices, d.outer, d.axis_size, d.inner = 1, idx.size, n, h * w, c
+        fn = lambda: abi.check(L.espdl_b200_gather(C.byref(d), None), name)
+    else:  # NHWC -> NCHW transpose of every image
+        d = abi.CopyDesc()
+        d.src, d.dst, d.elem_size, d.ndim = px, dev.empty(x.nbytes), 1, 3
+        for i, (sz, ss, ds) in enumerate([(n, h * w * c, h * w * c), (c, 1, h * w), (h * w, c, 1)]):
+            d.shape[i], d.src_stride[i], d.dst_stride[i] = sz, ss, ds
+        fn = lambda: abi.check(L.espdl_b200_copy(C.byref(d), None), name)
+    flush = dev.empty(FLUSH_BYTES)
+    ms = _time(L, flush, fn, iters, warm)
+    dev.close()
+    return ms, algo / ms / 1e6, algo
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", action="append", default=[])
     ap.add_argument("--conv", action="append", default=[])
     ap.add_argument("--block", action="append", default=[])
+    ap.add_argument("--mem", action="append", default=[])
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -232,7 +308,7 @@ def main():
         for name, spec in BLOCKS.items():
             print(name, spec)
         return
-    todo = [(name, CASES[name]) for name in (a.case or ([] if (a.conv or a.block) else list(CASES)))]
+    todo = [(name, CASES[name]) for name in (a.case or ([] if (a.conv or a.block or a.mem) else list(CASES)))]
     todo += [(c, tuple(int(v) for v in c.split(","))) for c in a.conv]
     dev = Dev(a.device)
     for name, spec in todo:
@@ -240,6 +316,9 @@ def main():
         print(f"{name:16s} {ms:9.4f} ms {tops:9.2f} TOPS {gbs:9.1f} GB/s  algorithmic_bytes={algo}", flush=True)
 
 
+    for name in (MEM_CASES if a.mem == ["all"] else a.mem):
+        ms, gbs, algo = run_mem(dev, name, a.iters, a.warmup)
+        print(f"{name:16s} {ms:9.4f} ms {gbs:9.1f} GB/s  algorithmic_bytes={algo}", flush=True)
     for name in a.block:
         spec = BLOCKS[name] if name in BLOCKS else tuple(int(v) for v in name.split(","))
         ms_f, ms_s, tops, gbs, algo = run_block(dev, spec, a.iters, a.warmup)

@@ -312,6 +312,24 @@ def test_copy_concat_and_transpose(es, dtype):
         np.testing.assert_array_equal(dev.download(pt, t), a.transpose(0, 3, 1, 2))
 
 
+@pytest.mark.parametrize("dtype", [np.int8, np.int16])
+@pytest.mark.parametrize("shape,perm", [((2, 70, 75, 96), (0, 3, 1, 2)), ((3, 130, 17), (0, 2, 1)), ((2, 2, 100, 33), (0, 1, 3, 2)), ((200, 300), (1, 0)),
+                                        ((2, 64, 64, 128), (0, 3, 1, 2)), ((4, 19, 64, 16), (2, 0, 3, 1))])
+def test_copy_tiled_transposes(shape, perm, dtype):
+    """Transposes whose destination runs along an axis that is strided in the source take the shared-memory tile kernel:
+    ragged extents, several outer axes, 1- and 2-byte elements."""
+    a = np.random.default_rng(29).integers(-30000, 30000, size=shape).astype(dtype)
+    want = np.ascontiguousarray(a.transpose(perm))
+    es = a.dtype.itemsize
+    src_strides = [a.strides[p] // es for p in perm]
+    dst_strides = [st // es for st in want.strides]
+    with gpu_util.DeviceBuffers() as dev:
+        pt = dev.upload(np.full_like(want, 0x55))
+        d = cases.copy_desc(dev.upload(a), pt, es, want.shape, src_strides, dst_strides)
+        abi.check(dev.lib.espdl_b200_copy(C.byref(d), None), "copy")
+        np.testing.assert_array_equal(dev.download(pt, want), want)
+
+
 @pytest.mark.parametrize("odt,eo", [(abi.DTYPE_FLOAT, 0), (abi.DTYPE_INT8, -7), (abi.DTYPE_INT16, -15)])
 @pytest.mark.parametrize("e_in,rows,length", [(-4, 64, 400), (-3, 3, 37), (-6, 5, 64)])
 def test_softmax(e_in, rows, length, odt, eo):
