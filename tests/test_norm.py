@@ -81,7 +81,7 @@ def test_oracle_matches_reference(op, kw, rows, n, dt):
 @pytest.mark.parametrize("round_mode", [abi.ROUND_HALF_UP, abi.ROUND_HALF_EVEN])
 @pytest.mark.parametrize("dt", [abi.DTYPE_INT8, abi.DTYPE_INT16])
 @pytest.mark.parametrize("op,kw", VARIANTS)
-@pytest.mark.parametrize("rows,n", SHAPES + [(1024, 384), (3, 5000)])
+@pytest.mark.parametrize("rows,n", SHAPES + [(1024, 384), (3, 5000), (70, 96), (33, 36), (64, 260), (32, 4)])
 def test_gpu_matches_oracle(op, kw, rows, n, dt, round_mode):
     import gpu_util
     a = make(op, dt, rows, n, seed=rows + n, round_mode=round_mode, **kw)
