@@ -118,6 +118,15 @@ int espdl_model_wait(void *handle)
     return h->model->wait() == ESP_OK ? 0 : (h->model->m_status ? h->model->m_status : -1);
 }
 
+/// Operator types with a registered creator (dl::module::ModuleCreator), one per line; needs no GPU.
+const char *espdl_registered_ops(void)
+{
+    static std::string text;
+    text.clear();
+    for (const std::string &op : dl::module::ModuleCreator::get_instance()->registered_ops()) text += op + "\n";
+    return text.c_str();
+}
+
 /// dl::Model::reset(): clears the state modules keep between runs (the StreamingCache frames).
 void espdl_model_reset(void *handle) { ((Handle *)handle)->model->reset(); }
 
