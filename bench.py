@@ -227,11 +227,15 @@ def main():
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local_rank)
+    stdout_fd = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL writes its version banner and debug lines to stdout when NCCL_DEBUG is set in the environment; stdout
-        # carries the one JSON line, so send them to stderr
+        # NCCL prints its version banner (and, with NCCL_DEBUG set, more) on the process's stdout when the communicator is
+        # created; stdout carries the one JSON line, so file descriptor 1 points at stderr until that line is written
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        sys.stdout.flush()
+        stdout_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     entry._package()
@@ -402,6 +406,11 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
+        if stdout_fd is not None:
+            sys.stdout.flush()
+            C.CDLL(None).fflush(None)  # what C libraries still hold for fd 1 goes to stderr too
+            os.dup2(stdout_fd, 1)
+            os.close(stdout_fd)
         print(json.dumps(result), flush=True)
 
 
