@@ -163,6 +163,7 @@ SYMBOLS = {
     "espdl_b200_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
     "espdl_b200_host_free": (C.c_int, [C.c_void_p]),
     "espdl_b200_launch_count": (C.c_uint64, []),
+    "espdl_b200_mem_info": (C.c_int, [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "espdl_b200_stream_create": (C.c_int, [C.POINTER(C.c_void_p)]),
     "espdl_b200_stream_destroy": (C.c_int, [C.c_void_p]),
     "espdl_b200_event_create": (C.c_int, [C.POINTER(C.c_void_p)]),

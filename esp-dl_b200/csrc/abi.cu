@@ -60,6 +60,10 @@ int espdl_b200_init(int device)
     }
     if (device < 0 || device >= count)
         return ESPDL_ERR_INVALID_ARG;
+    if (g_device >= 0 && g_device != device)
+        // one device per process: the cached scratch and the SM count belong to the device of the first call
+        return set_error_text(ESPDL_ERR_INVALID_ARG, "espdl_b200_init(%d): this process is bound to device %d; call espdl_b200_shutdown first",
+                              device, g_device);
     ESPDL_CUDA_TRY(cudaSetDevice(device));
     cudaDeviceProp prop;
     ESPDL_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
@@ -150,12 +154,11 @@ int espdl_b200_stream_sync(void *stream)
     ESPDL_CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
     // a tile kernel whose bounded wait expired leaves its status in a device word
     int dev = read_and_clear_device_error();
-    const int dev_dw = read_and_clear_device_error_dw();
     const int dev_stem = read_and_clear_device_error_stem();
     const int dev_conv = read_and_clear_device_error_conv();
     const int dev_block = read_and_clear_device_error_block();
     if (!dev)
-        dev = dev_dw ? dev_dw : (dev_stem ? dev_stem : (dev_conv ? dev_conv : dev_block));
+        dev = dev_stem ? dev_stem : (dev_conv ? dev_conv : dev_block);
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -179,6 +182,17 @@ int espdl_b200_host_free(void *hptr)
 }
 
 uint64_t espdl_b200_launch_count(void) { return g_launches.load(); }
+
+int espdl_b200_mem_info(size_t *free_bytes, size_t *total_bytes)
+{
+    size_t f = 0, t = 0;
+    ESPDL_CUDA_TRY(cudaMemGetInfo(&f, &t));
+    if (free_bytes)
+        *free_bytes = f;
+    if (total_bytes)
+        *total_bytes = t;
+    return ESPDL_OK;
+}
 
 int espdl_b200_stream_create(void **stream)
 {
@@ -293,8 +307,12 @@ int espdl_b200_graph_destroy(void *graph)
     return ESPDL_OK;
 }
 
+} // extern "C"
+
 // ------------------------------------------------------------------ conv2d
-static int conv_validate(const espdl_conv_desc *d)
+// Checks every conv entry point makes before anything is planned or launched: pointers, extents, the output size
+// the reference derives, exponent pointers that the kernels will dereference, and the supported enumerators.
+int espdl::conv_validate(const espdl_conv_desc *d)
 {
     if (!d || !d->input || !d->filter || !d->output)
         return ESPDL_ERR_INVALID_ARG;
@@ -337,6 +355,8 @@ static int conv_validate(const espdl_conv_desc *d)
     return ESPDL_OK;
 }
 
+extern "C" {
+
 int espdl_b200_conv2d_workspace_bytes(const espdl_conv_desc *desc, size_t *bytes)
 {
     if (!bytes)
@@ -361,14 +381,10 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
         return ESPDL_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (desc->group != 1) {
-        const bool dw_tc_ok = conv2d_dw_tc_supported(*desc);
-        if (desc->kernel == ESPDL_KERNEL_TCGEN05 && !dw_tc_ok)
+        // Depthwise convs run on the CUDA cores (dp4a): a tcgen05 MMA of M=128 takes ~143 cycles however small N is,
+        // which caps any diagonal-filter formulation on the tensor cores far below the dp4a walk.
+        if (desc->kernel == ESPDL_KERNEL_TCGEN05)
             return ESPDL_ERR_UNSUPPORTED;
-        // the dp4a kernel on the CUDA cores is the faster one for every shape measured (a tcgen05 MMA of M=128
-        // takes ~143 cycles however small N is, which caps the diagonal-filter formulation), so the tensor-core
-        // depthwise kernel runs only on request
-        if (dw_tc_ok && desc->kernel == ESPDL_KERNEL_TCGEN05)
-            return conv2d_dw_tc(*desc, s);
         return conv2d_depthwise(*desc, s);
     }
     if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_stem_tc_supported(*desc))
@@ -443,10 +459,17 @@ int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream)
 
 int espdl_b200_gemm_scatter(const espdl_conv_desc *desc, void *const *peer_outputs, int n_peers, void *stream)
 {
-    if (!desc || !desc->input || !desc->filter || !desc->output || n_peers < 0 || n_peers > 7 || (n_peers > 0 && !peer_outputs))
+    if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && !peer_outputs))
         return ESPDL_ERR_INVALID_ARG;
-    if (desc->dtype != ESPDL_DTYPE_INT8 || !conv2d_tc_supported(*desc))
+    const int st = conv_validate(desc);
+    if (st)
+        return st;
+    if (g_device < 0)
+        return ESPDL_ERR_NO_DEVICE;
+    if (desc->dtype != ESPDL_DTYPE_INT8 || desc->lut || desc->residual || desc->filter_image_stride != 0 || !conv2d_tc_supported(*desc))
         return ESPDL_ERR_UNSUPPORTED;
+    if (desc->n == 0)
+        return ESPDL_OK;
     long long delta[7] = {0, 0, 0, 0, 0, 0, 0};
     for (int i = 0; i < n_peers; i++) {
         if (!peer_outputs[i] || ((uintptr_t)peer_outputs[i] % 16) != ((uintptr_t)desc->output % 16))

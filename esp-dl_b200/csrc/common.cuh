@@ -24,6 +24,9 @@ int check_launch(const char *what);
             return ::espdl::set_cuda_error(e__, #call);     \
     } while (0)
 
+// Descriptor checks shared by every conv entry point (abi.cu); ESPDL_OK or the status to return.
+int conv_validate(const espdl_conv_desc *d);
+
 // kernels behind the C ABI (one translation unit each)
 int conv2d_simt(const espdl_conv_desc &d, cudaStream_t s);
 int conv2d_depthwise(const espdl_conv_desc &d, cudaStream_t s);
@@ -32,7 +35,6 @@ size_t conv2d_tc_workspace_bytes(const espdl_conv_desc &d);
 int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes, cudaStream_t s, const long long *peer_delta = nullptr,
               int n_peer = 0); // peer_delta: byte distances to copies of the output on other GPUs that receive every row as well
 int read_and_clear_device_error(); // status word written by device-side bounded waits (0 = none)
-int read_and_clear_device_error_dw();
 int read_and_clear_device_error_stem();
 int read_and_clear_device_error_conv();
 int read_and_clear_device_error_block();
@@ -46,8 +48,6 @@ bool conv2d_conv_tc_supported(const espdl_conv_desc &d);
 int conv2d_conv_tc(const espdl_conv_desc &d, cudaStream_t s);
 bool conv2d_stem_tc_supported(const espdl_conv_desc &d);
 int conv2d_stem_tc(const espdl_conv_desc &d, cudaStream_t s);
-bool conv2d_dw_tc_supported(const espdl_conv_desc &d);
-int conv2d_dw_tc(const espdl_conv_desc &d, cudaStream_t s);
 
 // ------------------------------------------------------------- device math
 // dl::tool::shift_and_round on a 32-bit accumulator (int8 operators).

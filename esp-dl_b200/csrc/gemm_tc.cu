@@ -958,10 +958,14 @@ static __device__ __align__(256) unsigned char g_static_limb_scratch[ESPDL_B200_
 extern "C" int espdl_b200_gemm_s16_static(const espdl_conv_desc *desc, void *stream)
 {
     using namespace espdl;
-    if (!desc || !desc->input || !desc->filter || !desc->output)
-        return ESPDL_ERR_INVALID_ARG;
-    if (desc->dtype != ESPDL_DTYPE_INT16 || !conv2d_tc_supported(*desc))
+    // the same descriptor checks as espdl_b200_conv2d, before anything is planned or launched
+    const int st = conv_validate(desc);
+    if (st)
+        return st;
+    if (desc->dtype != ESPDL_DTYPE_INT16 || desc->lut || desc->residual || desc->filter_image_stride != 0 || !conv2d_tc_supported(*desc))
         return ESPDL_ERR_UNSUPPORTED;
+    if (desc->n == 0)
+        return ESPDL_OK;
     const size_t need = conv2d_tc_workspace_bytes(*desc);
     if (need > (size_t)ESPDL_B200_STATIC_SCRATCH_BYTES)
         return set_error_text(ESPDL_ERR_TOO_LARGE,
@@ -988,7 +992,5 @@ extern "C" int espdl_b200_gemm_s16_static(const espdl_conv_desc *desc, void *str
         }
         scratch = addr_of_device[dev];
     }
-    if (desc->n == 0)
-        return ESPDL_OK;
     return conv2d_tc(*desc, scratch, (size_t)ESPDL_B200_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
 }

@@ -305,13 +305,15 @@ void Model::fuse_blocks()
             if (!m_module_inputs[k].empty() && m_module_inputs[k][0] == y2)
                 P = (int)k;
         module::Conv *proj = P >= 0 && m_module_types[P] == "Conv" ? dynamic_cast<module::Conv *>(m_execution_plan[P]) : nullptr;
-        if (!proj || !proj->is_pointwise() || m_module_outputs[P].size() != 1)
+        if (!proj || !proj->is_pointwise() || m_module_outputs[P].size() != 1 || m_module_inputs[P].size() < 2 ||
+            !module::Conv::filter_is_1x1(ctx->get_tensor(m_module_inputs[P][1])))
             continue;
         int E = producer(y1);
         module::Conv *expand = nullptr;
         if (E >= 0 && E < (int)s && m_module_types[E] == "Conv" && private_tensor(y1) && m_module_outputs[E].size() == 1) {
             expand = dynamic_cast<module::Conv *>(m_execution_plan[E]);
-            if (expand && !expand->is_pointwise())
+            if (expand && (!expand->is_pointwise() || m_module_inputs[E].size() < 2 ||
+                           !module::Conv::filter_is_1x1(ctx->get_tensor(m_module_inputs[E][1]))))
                 expand = nullptr;
         }
         if (!expand)
@@ -412,8 +414,9 @@ void Model::fold_residual_adds()
             if (producer < 0 || producer >= (int)s || readers != 1 || m_module_types[producer] != "Conv" || x_producer >= producer)
                 continue;
             module::Conv *conv = dynamic_cast<module::Conv *>(m_execution_plan[producer]);
-            if (!conv || !conv->can_fold_add() || m_module_outputs[producer].size() != 1)
-                continue;
+            if (!conv || !conv->can_fold_add() || m_module_outputs[producer].size() != 1 || m_module_inputs[producer].size() < 2 ||
+                !module::Conv::filter_is_1x1(m_model_context->get_tensor(m_module_inputs[producer][1])))
+                continue; // only a [1,1,Cin,Cout] filter: the kernels that add a residual are the pointwise ones
             if (m_fbs_model->get_value_info_dtype(x) != DATA_TYPE_INT8 || m_fbs_model->get_value_info_dtype(y) != DATA_TYPE_INT8 ||
                 m_fbs_model->get_value_info_dtype(out) != DATA_TYPE_INT8)
                 continue;

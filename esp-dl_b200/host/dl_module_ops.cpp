@@ -172,7 +172,7 @@ esp_err_t Conv::prepare(ModelContext *context)
     // unit moves rows of 16-64 bytes at a fraction of HBM speed, rows of 128 bytes at full speed.  The widest
     // grouping whose block-diagonal filter stays small is used (ESPDL_B200_GROUP_K overrides the target width).
     TensorBase *input = context->get_tensor(m_inputs_index[0]);
-    TensorBase *bias = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
+    TensorBase *bias = has_bias() ? context->get_tensor(m_inputs_index[2]) : nullptr;
     if (!m_no_grouping && !m_gemm && !dw && input && input->shape.size() == 4 && quant_type == QUANT_TYPE_SYMM_8BIT && fs[0] == 1 && fs[1] == 1 &&
         m_strides[0] == 1 && m_strides[1] == 1 && m_pads[0] + m_pads[1] + m_pads[2] + m_pads[3] == 0 && filter->data &&
         !getenv("ESPDL_B200_NO_PIXEL_GROUPING")) {
@@ -231,7 +231,7 @@ int Conv::fill_desc(ModelContext *context, void *desc)
     memset(&d, 0, sizeof(d));
     TensorBase *input = context->get_tensor(m_inputs_index[0]);
     TensorBase *filter = context->get_tensor(m_inputs_index[1]);
-    TensorBase *bias = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
+    TensorBase *bias = has_bias() ? context->get_tensor(m_inputs_index[2]) : nullptr;
     TensorBase *output = context->get_tensor(m_outputs_index[0]);
     if (!input || !filter || !output || !input->device || !filter->device || !output->device)
         return ESPDL_ERR_INVALID_ARG;
@@ -297,6 +297,9 @@ bool Conv::can_fold_add() const
             return false;
     for (int v : m_pads)
         if (v != 0)
+            return false;
+    for (int v : m_dilations)
+        if (v != 1)
             return false;
     return activation == Linear || activation == ReLU;
 }
@@ -376,7 +379,7 @@ void FusedBlock::forward(ModelContext *context, runtime_mode_t mode)
     } else {
         auto stage = [&](Conv *c, const void *&filter, const void *&bias, const int32_t *&exps, int32_t &e_scalar, int32_t &act, int bit) {
             TensorBase *f = context->get_tensor(c->m_inputs_index[1]);
-            TensorBase *b = c->m_inputs_index.size() > 2 ? context->get_tensor(c->m_inputs_index[2]) : nullptr;
+            TensorBase *b = c->has_bias() ? context->get_tensor(c->m_inputs_index[2]) : nullptr;
             filter = f->device, bias = b ? b->device : nullptr, exps = (const int32_t *)c->m_dev_exponents;
             e_scalar = f->exponent;
             if (f->exponent.is_per_channel())

@@ -27,10 +27,16 @@ public:
     bool can_fold_add() const;
     /// Fold a following Add into the epilogue: the module's LAST input is then the residual tensor.
     void set_residual() { m_residual = true; }
+    /// A conv has a bias when it has a third input that is not the residual of a folded Add (a reference Conv may
+    /// come without one: dl_module_conv.hpp:137-140).
+    bool has_bias() const { return m_inputs_index.size() > (m_residual ? 3u : 2u); }
 
     /// Geometry the block-fusion pass of dl::Model looks at.
     bool is_depthwise() const { return m_group != 1; }
-    bool is_pointwise() const;   ///< 1x1, stride 1, no padding, group 1, not a Gemm view, no fused table
+    bool is_pointwise() const;   ///< stride 1, dilation 1, no padding, group 1, not a Gemm view, no fused table; the
+                                 ///< caller checks that the filter is [1,1,Cin,Cout] (filter_is_1x1)
+    /// True when the filter tensor's declared shape is [1, 1, Cin, Cout].
+    static bool filter_is_1x1(const TensorBase *filter) { return filter && filter->shape.size() == 4 && filter->shape[0] == 1 && filter->shape[1] == 1; }
     bool is_dw3x3() const;       ///< depthwise, stride 1 or 2 (both axes), dilation 1, pads of at most 1
     void skip_pixel_grouping() { m_no_grouping = true; }
     int stride() const { return m_strides[0]; }

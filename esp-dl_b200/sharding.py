@@ -94,7 +94,13 @@ class NShardedGemm:
         """mode "gather": every rank computes its block, one all-gather and an interleaving copy assemble [M][N].
         mode "peer" (int8, one machine): every rank's kernel stores its columns straight into the [M][N] result of
         all ranks through peer-mapped pointers (espdl_b200_gemm_scatter); a one-element all-reduce on the stream then
-        orders every rank's reads behind every rank's kernel.  No gather, no copy."""
+        orders every rank's reads behind every rank's kernel.  No gather, no copy.
+
+        Peer mode returns a view of a library-owned buffer that OTHER GPUs write.  Two buffers per M are used in turn:
+        the result of call i stays valid until call i+2 is enqueued, provided it is read on the stream forward() was
+        called on (a rank's kernel of call i+2 starts only after the exchange of call i+1 has completed, which every
+        rank enqueues behind its own readers of result i).  A caller that reads a result on another stream, or keeps
+        it beyond the next call, has to copy it first."""
         import numpy as np
         from . import abi
         self.abi, self.lib, self.group = abi, abi.load(), group
@@ -118,7 +124,8 @@ class NShardedGemm:
         if mode not in ("gather", "peer") or (mode == "peer" and self.dtype != abi.DTYPE_INT8):
             raise ValueError("mode is 'gather' or 'peer'; 'peer' takes int8 only")
         self.mode = mode
-        self._peer = {}   # M -> (own buffer, peers' mapped buffers, tensor view)
+        self._peer = {}   # M -> two sets of (own buffer, peers' mapped buffers, tensor view), used in turn
+        self._turn = {}   # M -> which set the next call writes
         self._flag = None
 
     def forward(self, x):
@@ -158,7 +165,14 @@ class NShardedGemm:
     def _peer_buffers(self, m):
         import ctypes as C
         if m in self._peer:
-            return self._peer[m]
+            self._turn[m] ^= 1
+            return self._peer[m][self._turn[m]]
+        self._peer[m] = [self._new_peer_set(m), self._new_peer_set(m)]
+        self._turn[m] = 0
+        return self._peer[m][0]
+
+    def _new_peer_set(self, m):
+        import ctypes as C
         own = C.c_void_p()
         self.abi.check(self.lib.espdl_b200_arena_alloc(m * self.n, C.byref(own)), "arena_alloc")
         handle = (C.c_ubyte * 64)()
@@ -174,8 +188,7 @@ class NShardedGemm:
             self.abi.check(self.lib.espdl_b200_ipc_open(buf, C.byref(mapped)), "ipc_open")
             peers.append(mapped)
         view = torch.as_tensor(self._DeviceArray(own.value, (m, self.n), "|i1"), device=self.device)
-        self._peer[m] = (own, peers, view)
-        return self._peer[m]
+        return (own, peers, view)
 
     def _forward_peer(self, x):
         import ctypes as C
@@ -209,11 +222,12 @@ class NShardedGemm:
         torch.cuda.synchronize(self.device)
         if self.world > 1:
             dist.barrier(group=self.group)
-        for own, peers, _ in self._peer.values():
+        sets = [s for pair in self._peer.values() for s in pair]
+        for own, peers, _ in sets:
             for p in peers:
                 self.lib.espdl_b200_ipc_close(p)
         if self.world > 1:
             dist.barrier(group=self.group)
-        for own, _, _ in self._peer.values():
+        for own, _, _ in sets:
             self.lib.espdl_b200_arena_free(own)
-        self._peer = {}
+        self._peer, self._turn = {}, {}

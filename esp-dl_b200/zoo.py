@@ -387,3 +387,127 @@ def yolo11n_style(seed=6, input_hw=640, num_classes=80, e_act=(-8, -4), e_w=(-9,
             g.outputs.append((t, np.int8, net.shape[t], [net.exp[t]]))
             g.value_info = [v for v in g.value_info if v[0] != t]
     return g
+
+
+# ------------------------------------------------------------------------------------------------ topology files
+_NP_OF_ELEM = {1: np.float32, 3: np.int8, 5: np.int16, 6: np.int32, 7: np.int64, 9: np.bool_}
+
+
+def from_topology(topo, seed=6, target_rms=28.0):
+    """Builds a network from a topology description: the node list, tensor shapes, element types and activation exponents
+    of an exported graph, without its weights (a dict as written by tests/golden/make_golden.py::write_topology, e.g. the
+    249-node YOLO11n detector at 640x640).  Every Conv gets seeded random int8 weights with per-channel power-of-two
+    exponents drawn from about four neighbouring values, amplitudes chosen so that the requantised output uses the int8
+    range at the output exponent the graph prescribes, and an int32 bias at exponent e_in + e_w[c]; every Swish node gets
+    the 256-entry table of the reference's formula for its input / output exponents (dl_module_swish.hpp:62-76); the
+    small structural constants (Reshape / Split / Resize operands, the Mul scalar) are taken from the description.
+    Filters are stored in the order of target "c".  Returns the GraphBuilder."""
+    rng = np.random.default_rng(seed)
+    g = espdl_file.GraphBuilder("from_topology", {"target": "c"})
+    info = {v["name"]: v for v in topo["value_info"] + topo["inputs"] + topo["outputs"]}
+    params = topo["parameters"]
+    exp = {n: (v["exponents"][0] if v["exponents"] else 0) for n, v in info.items()}
+    ms = {}      # tensor name -> estimated mean square of the codes
+    for v in topo["inputs"]:
+        g.add_input(v["name"], _NP_OF_ELEM[v["elem_type"]], v["shape"], exp[v["name"]])
+        ms[v["name"]] = 74.0 ** 2
+    for v in topo["value_info"]:
+        if v["shape"] is None or v["name"] in params:
+            continue
+        g.add_value_info(v["name"], _NP_OF_ELEM[v["elem_type"]], v["shape"], exp[v["name"]] if v["exponents"] else None)
+    for v in topo["outputs"]:
+        g.add_output(v["name"], _NP_OF_ELEM[v["elem_type"]], v["shape"], exp[v["name"]])
+    done = set()
+
+    def constant(name):
+        if name in done or name not in params:
+            return
+        p = params[name]
+        if "values" not in p:
+            raise ValueError(f"parameter {name} has no values in the topology description")
+        arr = np.array(p["values"], dtype=_NP_OF_ELEM[p["data_type"]]).reshape(p["dims"] if p["dims"] else ())
+        g.add_initializer(name, arr, p.get("exponents") or None)
+        done.add(name)
+
+    for node in topo["nodes"]:
+        op, ins, outs, attrs = node["op_type"], [i for i in node["inputs"]], node["outputs"], dict(node["attrs"])
+        x = ins[0]
+        if op == "Conv":
+            wname = ins[1]
+            kh, kw, cin_g, cout_decl = params[wname]["dims"]
+            group = int(attrs.get("group", 1))
+            depthwise = group != 1
+            cout = info[outs[0]]["shape"][-1]
+            taps = kh * kw * (1 if depthwise else cin_g)
+            e_in, e_out = exp[x], exp[outs[0]]
+            need = target_rms * np.sqrt(3.0) / (np.sqrt(ms[x]) * np.sqrt(taps))   # weight amplitude wanted at shift 0
+            good = [s for s in range(1, 25) if 3 <= need * 2.0 ** s <= 127] or [max(1, int(np.round(np.log2(20.0 / need))))]
+            base = good[len(good) // 2 - (1 if len(good) > 3 else 0)] if len(good) > 1 else good[0]
+            choices = [s for s in good if base - 1 <= s <= base + 2] or good
+            shift = rng.choice(choices, size=cout)
+            ew = e_out - e_in - shift
+            wmax = np.clip(np.round(need * 2.0 ** shift), 1, 127).astype(np.int64)
+            if depthwise:
+                wt = np.stack([rng.integers(-wmax[c], wmax[c] + 1, size=(kh, kw)) for c in range(cout)], axis=-1).astype(np.int8)
+            else:
+                wt = np.stack([rng.integers(-wmax[c], wmax[c] + 1, size=(kh, kw, cin_g)) for c in range(cout)]).astype(np.int8)
+            g.add_initializer(wname, wt.reshape(params[wname]["dims"]), [int(e) for e in ew])
+            acc_rms = np.sqrt(ms[x]) * (wmax / np.sqrt(3.0)) * np.sqrt(taps)
+            if len(ins) > 2 and ins[2]:
+                b = np.round(rng.uniform(-0.5, 0.5, size=cout) * acc_rms).astype(np.int32)
+                g.add_initializer(ins[2], b, [int(e) for e in ew + e_in])
+            out_rms = np.minimum(acc_rms / 2.0 ** shift, 70.0).mean()
+            ms[outs[0]] = float(out_rms ** 2) * (0.5 if attrs.get("activation") == "Relu" else 1.0)
+        elif op == "Swish":
+            e_in, e_out = exp[x], exp[outs[0]]
+            q = np.arange(-128, 128, dtype=np.float32)
+            v = q * np.float32(2.0 ** e_in)
+            with np.errstate(over="ignore"):   # exp overflows to inf for very negative inputs: x / inf = -0, as in C
+                y = (v / (np.float32(1.0) + np.exp(-v, dtype=np.float32))) * np.float32(2.0 ** -e_out)
+            table = np.clip(np.floor(y.astype(np.float64) + 0.5), -128, 127).astype(np.int8)
+            g.add_initializer(attrs["lut"], table, [e_out])
+            sample = np.clip(np.round(rng.standard_normal(4096) * np.sqrt(ms[x])), -128, 127).astype(np.int64)
+            ms[outs[0]] = float(np.mean(table[sample + 128].astype(np.float64) ** 2)) + 1.0
+        elif "lut" in attrs:
+            raise ValueError(f"{op}: only Swish tables can be regenerated")
+        else:
+            for name in ins[1:]:
+                if name:
+                    constant(name)
+            if op in ("Add", "Sub"):
+                ms[outs[0]] = min(ms[ins[0]] + ms[ins[1]], 100.0 ** 2)
+            elif op == "Concat":
+                ms[outs[0]] = float(np.mean([ms[i] for i in ins]))
+            elif op in ("RequantizeLinear",):
+                ms[outs[0]] = min(ms[x] * 4.0 ** (exp[x] - exp[outs[0]]), 100.0 ** 2)
+            elif op == "MaxPool":
+                ms[outs[0]] = ms[x] * 1.7
+            elif op == "MatMul":
+                k = info[x]["shape"][-1]
+                shift = exp[outs[0]] - exp[ins[0]] - exp[ins[1]]
+                ms[outs[0]] = float(np.clip(ms[ins[0]] * ms[ins[1]] * k / 4.0 ** shift, 1.0, 100.0 ** 2))
+            elif op == "Mul":
+                c = params[ins[1]]
+                scale = c["values"][0] * 2.0 ** (c["exponents"][0] if c.get("exponents") else 0)
+                ms[outs[0]] = float(np.clip(ms[x] * (scale * 2.0 ** (exp[x] - exp[outs[0]])) ** 2, 1.0, 100.0 ** 2))
+            elif op == "Softmax":
+                ms[outs[0]] = 1.0
+            elif op == "QuantizeLinear":
+                n_tok = info[x]["shape"][-1]
+                ms[outs[0]] = float(np.clip((2.0 ** -exp[outs[0]] / n_tok) ** 2 * 4.0, 1.0, 100.0 ** 2))
+            else:   # Split, Reshape, Transpose, Resize, Slice, ...: the values move, their statistics stay
+                for o in outs:
+                    ms[o] = ms[x]
+        for o in outs:
+            ms.setdefault(o, ms.get(x, 400.0))
+        g.add_node(op, node["name"], ins, outs, **attrs)
+    return g
+
+
+def yolo11n_640(topology_path, seed=6):
+    """The YOLO11n detector at 640x640 as the reference ships it (249 nodes: 87 Conv, 77 Swish tables, 19 RequantizeLinear,
+    17 Concat, 14 Add, 10 Split, 8 Transpose, 7 Reshape, 3 MaxPool, 2 MatMul, 2 Resize, Mul, Softmax, QuantizeLinear) with
+    seeded random weights; `topology_path` is the JSON description of that graph."""
+    import json
+    with open(topology_path) as f:
+        return from_topology(json.load(f), seed=seed)

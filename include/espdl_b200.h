@@ -86,6 +86,9 @@ int espdl_b200_host_alloc(size_t bytes, void **hptr);
 int espdl_b200_host_free(void *hptr);
 /* Number of kernels this library has launched since init (all entry points). */
 uint64_t espdl_b200_launch_count(void);
+/* Free and total bytes of the current device's memory (cudaMemGetInfo): lets a caller check that a region of its
+ * program allocated nothing.  Either pointer may be NULL. */
+int espdl_b200_mem_info(size_t *free_bytes, size_t *total_bytes);
 
 /* Streams, events and CUDA-graph capture for the layer above (dl::Model runs its plan as one
  * captured graph; dl::Model::profile() times modules with events).  Handles are opaque. */
@@ -182,8 +185,15 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
  *  - scratch needed is what espdl_b200_conv2d_workspace_bytes reports, 2*(M*K + N*K) bytes rounded up; a larger
  *    problem is rejected with ESPDL_ERR_TOO_LARGE, shapes the tensor-core int16 path does not take (K % 16 != 0,
  *    filters other than 1x1, K > 16384) with ESPDL_ERR_UNSUPPORTED;
- *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress) and keeps it;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress) and keeps it; that
+ *    first call also makes the CUDA runtime load the kernels and materialise the array on the device, which the
+ *    driver may account as device memory: make one warm-up call per device OUTSIDE the allocation-fenced region and
+ *    before any stream capture; from the second call on, free device memory does not change
+ *    (tests/test_zz_no_alloc.py reads espdl_b200_mem_info around the calls);
  *  - the call itself runs no cudaMalloc, cudaFree or allocating library routine;
+ *  - the descriptor is checked like espdl_b200_conv2d's before anything is launched (ESPDL_ERR_INVALID_ARG for a
+ *    per-channel flag without an exponent array, output extents that do not follow from the input's, negative sizes);
+ *    a fused table, a residual and per-image filters are not offered here (ESPDL_ERR_UNSUPPORTED);
  *  - all calls share the one array and it keeps the previous call's bytes: every call rewrites the part it reads,
  *    so nothing has to be cleared, but two calls that overlap on the GPU (different streams, no ordering) race.
  */

@@ -9,10 +9,12 @@ import pytest
 
 import cases
 import checkers
+import graph_oracle
 from espdl_b200 import abi, espdl_file
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "espdl")
 GEMM_FILES = sorted(glob.glob(os.path.join(GOLDEN, "*__linear_*.espdl"))) + sorted(glob.glob(os.path.join(GOLDEN, "*__sin_mlp.espdl")))
+TCN_FILES = sorted(glob.glob(os.path.join(GOLDEN, "*__streaming_tcn.espdl")))
 ACT = {"Linear": abi.ACT_LINEAR, "Relu": abi.ACT_RELU}
 
 
@@ -69,3 +71,28 @@ def test_reference_build_reproduces_golden_gemm(path):
     m, tensors = replay_gemm_chain(path, ref_conv, abi.ROUND_HALF_UP)
     for name, t in m["test_outputs"].items():
         np.testing.assert_array_equal(tensors[name].reshape(-1), t["data"].reshape(-1))
+
+
+def test_streaming_tcn_files_present():
+    assert [os.path.basename(p).split("__")[0] for p in TCN_FILES] == ["esp32p4", "esp32s3"]
+
+
+@pytest.mark.parametrize("path", TCN_FILES, ids=os.path.basename)
+def test_oracle_reproduces_the_streaming_tcn_vector(path):
+    """The streaming tutorial model (examples/tutorial/how_to_deploy_streaming_model) embeds a test input and the
+    output the exporter computed for it: the only shipped vector that runs through Conv1d, dilated depthwise conv,
+    LUT-Sigmoid, Mul, Add, AveragePool, Slice and Gemm, with ESP32-P4 half-to-even / ESP32-S3 half-up rounding and the
+    16-wide filter layout.  The graph oracle has to reproduce it exactly (the check of the reference's Model::test(),
+    esp-dl/dl/model/src/dl_model_base.cpp:442-519)."""
+    target = os.path.basename(path).split("__")[0]
+    mode = abi.ROUND_HALF_EVEN if target == "esp32p4" else abi.ROUND_HALF_UP
+    m = espdl_file.read(path)
+    assert m["test_inputs"] and m["test_outputs"]
+    ops = {n["op_type"] for n in m["nodes"]}
+    assert {"Conv", "Gemm", "Mul", "Add"} <= ops
+    shapes = {v["name"]: v["shape"] for v in m["inputs"]}
+    inputs = {k: t["data"].reshape(shapes[k]) for k, t in m["test_inputs"].items()}
+    got = graph_oracle.run_graph(m, inputs, round_mode=mode, target=target)
+    for name, t in m["test_outputs"].items():
+        np.testing.assert_array_equal(np.asarray(got[name]).reshape(-1), t["data"].reshape(-1))
+        assert t["data"].astype(np.float32).std() > 0

@@ -12,12 +12,15 @@ from espdl_b200 import abi, espdl_file, model, zoo
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "espdl")
-GEMM_MODELS = sorted(glob.glob(os.path.join(GOLDEN, "*__linear_*.espdl"))) + sorted(glob.glob(os.path.join(GOLDEN, "*__sin_mlp.espdl")))
+GEMM_MODELS = (sorted(glob.glob(os.path.join(GOLDEN, "*__linear_*.espdl"))) + sorted(glob.glob(os.path.join(GOLDEN, "*__sin_mlp.espdl"))) +
+               sorted(glob.glob(os.path.join(GOLDEN, "*__streaming_tcn.espdl"))))
 
 
 @pytest.mark.parametrize("path", GEMM_MODELS, ids=os.path.basename)
 def test_model_test_passes_on_shipped_golden_models(path, monkeypatch):
-    """dl::Model::test(): embedded test inputs in, every embedded expected output compared - on the GPU."""
+    """dl::Model::test(): embedded test inputs in, every embedded expected output compared - on the GPU.  The Gemm and
+    sin-MLP files pin the Gemm path in all three filter layouts; the streaming-TCN files pin Conv1d, dilated depthwise
+    conv, LUT-Sigmoid, Mul, Add, AveragePool and Slice under ESP32-P4 (half-to-even) and ESP32-S3 (half-up) rules."""
     monkeypatch.setenv("ESPDL_B200_TARGET", os.path.basename(path).split("__")[0])  # the tutorial models carry no target tag
     m = model.Model(path)
     assert m.test() == 0
@@ -353,3 +356,100 @@ def test_matmul_with_a_constant_operand(tmp_path, dt, qt, sa, sb):
     np.testing.assert_array_equal(np.asarray(m.outputs[0].array).reshape(so), want.reshape(so))
     assert want.std() > 0
     m.close()
+
+
+def _conv_node(g, rng, name, x, out, cin, cout, k, e_in, e_out, bias):
+    """A Conv node with stride 1 and no padding, random per-channel weights; returns the output's (h, w) shrink."""
+    ew = rng.integers(-8, -5, size=cout)
+    w = rng.integers(-20, 21, size=(cout, k, k, cin)).astype(np.int8)      # payload order of target "c"
+    g.add_initializer(name + ".weight", w.reshape(k, k, cin, cout), list(ew))
+    inputs = [x, name + ".weight"]
+    if bias:
+        g.add_initializer(name + ".bias", rng.integers(-2000, 2000, size=cout).astype(np.int32), list(ew + e_in))
+        inputs.append(name + ".bias")
+    g.add_node("Conv", name, inputs, [out], activation="Linear", dilations=[1, 1], group=1, kernel_shape=[k, k], pads=[0, 0, 0, 0],
+               quant_type="S8", strides=[1, 1])
+
+
+@pytest.mark.parametrize("fold", ["1", "0"])
+@pytest.mark.parametrize("kind", ["pointwise_without_bias", "valid_3x3"])
+def test_add_behind_a_conv_that_cannot_or_need_not_take_it(tmp_path, monkeypatch, kind, fold):
+    """The Add-folding pass may only touch pointwise convs, and a conv without a bias (which the reference allows,
+    dl_module_conv.hpp:137-140) must not mistake the appended residual for its bias.  With the pass on and off the
+    output equals the oracle's."""
+    monkeypatch.setenv("ESPDL_B200_FOLD_ADD", fold)
+    rng = np.random.default_rng(17)
+    g = espdl_file.GraphBuilder("fold", metadata={"target": "c"})
+    e = -5
+    if kind == "pointwise_without_bias":
+        g.add_input("x", np.int8, [1, 12, 12, 32], e)
+        _conv_node(g, rng, "pw", "x", "y", 32, 32, 1, e, e, bias=False)
+        g.add_value_info("y", np.int8, [1, 12, 12, 32], e)
+        g.add_node("Add", "add", ["y", "x"], ["out"], quant_type="S8")
+        g.add_output("out", np.int8, [1, 12, 12, 32], e)
+    else:
+        g.add_input("x", np.int8, [1, 12, 12, 16], e)
+        _conv_node(g, rng, "c0", "x", "z", 16, 16, 3, e, e, bias=True)
+        g.add_value_info("z", np.int8, [1, 10, 10, 16], e)
+        _conv_node(g, rng, "c1", "x", "y", 16, 16, 3, e, e, bias=True)
+        g.add_value_info("y", np.int8, [1, 10, 10, 16], e)
+        g.add_node("Add", "add", ["y", "z"], ["out"], quant_type="S8")
+        g.add_output("out", np.int8, [1, 10, 10, 16], e)
+    m, want = run_and_compare(tmp_path, g, batch=3, seed=18, check_intermediates=False)
+    kinds = [r[1] for r in m.profile()]
+    if kind == "pointwise_without_bias" and fold == "1":
+        assert kinds == ["Conv"], kinds                  # folded, and still right
+    else:
+        assert kinds.count("Add") == 1, kinds            # a 3x3 conv keeps its Add
+    assert want[m.outputs[0].name].std() > 3
+    m.close()
+
+
+def _full_size_parity(path, batch, picks, small_batch, windows, seed):
+    """A model at its benchmarked batch: the oracle runs on the picked images, and every row of the windows must equal
+    the row a small-batch model gives for the same image (images are independent units)."""
+    parsed = espdl_file.read(path)
+    m = model.Model(path, batch=batch)
+    rng = np.random.default_rng(seed)
+    x = rng.integers(-128, 128, size=m.inputs[0].shape, dtype=np.int8)
+    x[picks[1]] = x[picks[-2]]                     # two equal images far apart must give equal rows
+    m.inputs[0].array[...] = x
+    m.run()
+    got = {o.name: np.array(o.array, copy=True) for o in m.outputs}
+    m.run()                                        # a second pass over the planned arena gives the same bytes
+    for o in m.outputs:
+        np.testing.assert_array_equal(o.array, got[o.name])
+    m.close()
+    want = graph_oracle.run_graph(parsed, {parsed["inputs"][0]["name"]: np.ascontiguousarray(x[picks])})
+    for name, g in got.items():
+        np.testing.assert_array_equal(g[picks].reshape(want[name].shape), want[name])
+        np.testing.assert_array_equal(g[picks[1]], g[picks[-2]])
+        assert want[name].astype(np.float32).std() > 3
+    ms = model.Model(path, batch=small_batch)
+    for start in windows:
+        ms.inputs[0].array[...] = x[start:start + small_batch]
+        ms.run()
+        for o in ms.outputs:
+            np.testing.assert_array_equal(o.array, got[o.name][start:start + small_batch])
+    ms.close()
+
+
+def test_mobilenet_v2_at_the_benchmarked_batch(tmp_path):
+    """MobileNetV2-1.0 at batch 1024, the size bench.py times: different tile counts, persistent-loop trip counts and
+    arena offsets than the batch-2 comparison.  Eight images from all over the batch (first, last, both sides of the
+    128-row tile boundaries of the late 7x7 layers) are checked against the graph oracle, windows of eight against a
+    batch-8 model."""
+    path = str(tmp_path / "mbv2.espdl")
+    zoo.mobilenet_v2(seed=5).save(path)
+    _full_size_parity(path, batch=1024, picks=[0, 1, 2, 3, 511, 512, 1022, 1023], small_batch=8, windows=(8, 504, 1016), seed=51)
+
+
+TOPOLOGY_640 = os.path.join(os.path.dirname(GOLDEN), "yolo11n_640_topology.json")
+
+
+def test_yolo11n_640_at_the_benchmarked_batch(tmp_path):
+    """The 249-node YOLO11n graph the reference ships for 640x640 (topology from its model file, seeded random weights) at
+    batch 512: four images through the graph oracle, windows of two against a batch-2 model, all six heads."""
+    path = str(tmp_path / "yolo640.espdl")
+    zoo.yolo11n_640(TOPOLOGY_640, seed=6).save(path)
+    _full_size_parity(path, batch=512, picks=[0, 255, 510, 511], small_batch=2, windows=(2, 300), seed=62)

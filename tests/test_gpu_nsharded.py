@@ -54,6 +54,15 @@ def _worker(rank, world, port, dtype_name, mode, ret):
         out2 = gemm.forward(x)              # buffers are reused from the second call on
         torch.cuda.synchronize()
         assert np.array_equal(out2.cpu().numpy(), first)
+        # consecutive calls on different inputs with no host synchronisation in between: each result is consumed on
+        # the stream (a clone) while the next call's kernels - on this and on the other GPUs - are already enqueued
+        xs = [x, torch.flip(x, dims=[0]), torch.roll(x, shifts=7, dims=0)]
+        results = [gemm.forward(xi).clone() for xi in xs for _ in range(2)]
+        torch.cuda.synchronize()
+        first_rows = first
+        for i, r in enumerate(results):
+            want_rows = [first_rows, first_rows[::-1], np.roll(first_rows, 7, axis=0)][i // 2]
+            assert np.array_equal(r.cpu().numpy(), want_rows), f"call {i} differs"
         ret.put((rank, first))
         gemm.close()
     finally:

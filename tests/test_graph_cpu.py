@@ -79,3 +79,25 @@ def test_shipped_zoo_models_run_through_the_oracle(name):
         y = want[out["name"]]
         assert list(y.shape) == list(out["shape"])
         assert y.astype(np.float32).std() > 0 and (np.abs(y.astype(np.int32)) == 127).mean() < 0.5
+
+
+def test_yolo11n_640_topology_graph_is_well_formed():
+    """The 640x640 detector built from the shipped graph's topology: 249 nodes with the shipped operator mix, and the graph
+    oracle's activations use the int8 range in every node (not all zero, not all saturated)."""
+    import collections
+    import os
+    from espdl_b200 import espdl_file, zoo
+    import graph_oracle
+    topo = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "yolo11n_640_topology.json")
+    blob = zoo.yolo11n_640(topo, seed=6).serialize()
+    m = espdl_file.read(blob)
+    kinds = collections.Counter(n["op_type"] for n in m["nodes"])
+    assert len(m["nodes"]) == 249 and kinds["Conv"] == 87 and kinds["Swish"] == 77 and kinds["Concat"] == 17 and kinds["MatMul"] == 2
+    assert m["inputs"][0]["shape"] == [1, 640, 640, 3] and len(m["outputs"]) == 6
+    x = np.random.default_rng(1).integers(-128, 128, size=(1, 640, 640, 3), dtype=np.int8)
+    out = graph_oracle.run_graph(m, {"images": x})
+    for n in m["nodes"]:
+        for o in n["outputs"]:
+            a = out[o]
+            if a.dtype == np.int8:
+                assert a.astype(np.float32).std() >= 2 and (np.abs(a.astype(int)) >= 127).mean() <= 0.5, (n["name"], o)
