@@ -49,6 +49,20 @@ int read_and_clear_device_error()
     return v;
 }
 
+// Role cycle counters of the tile kernel, compiled in only with -DESPDL_TC_TIMING (a measurement build; the product
+// build carries none of it): per CTA, cycles the producer waited for a free stage, the MMA issuer waited for an
+// accumulator / for a stage / spent issuing, and epilogue group 0 waited for an accumulator / spent working.
+#ifdef ESPDL_TC_TIMING
+__device__ long long g_tc_timing[256 * 8];
+#define TC_LAP_INIT long long t_ = clock64()
+#define TC_LAP(var) do { const long long n_ = clock64(); (var) += n_ - t_; t_ = n_; } while (0)
+#define TC_REC(slot, var) g_tc_timing[blockIdx.x * 8 + (slot)] = (var)
+#else
+#define TC_LAP_INIT
+#define TC_LAP(var)
+#define TC_REC(slot, var)
+#endif
+
 namespace {
 
 using namespace tc;
@@ -161,7 +175,7 @@ template <bool I16>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
-               const __grid_constant__ CUtensorMap map_out, const TcParams p)
+               const __grid_constant__ CUtensorMap map_out, const __grid_constant__ TcParams p)
 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -181,9 +195,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int *slow_flag = (int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_per_matrix = p.m_tiles * p.n_tiles;
-    const int total_tiles = p.batch * tiles_per_matrix;
+    const int total_tiles = p.batch * p.m_tiles * p.n_tiles;
     const int parts = 4 / p.acc_stages; // epilogue groups that share one tile (they split its columns)
+    // Tiles are numbered n-fastest: tile = row_tile * n_tiles + n_tile with row_tile running over batch x m_tiles.  Each
+    // role walks its tiles (blockIdx.x, + gridDim.x, ...) with two counters instead of a division per tile.
+    const int step_rows = (int)gridDim.x / p.n_tiles, step_n = (int)gridDim.x % p.n_tiles;
+    const int first_rows = (int)blockIdx.x / p.n_tiles, first_n = (int)blockIdx.x % p.n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
@@ -204,99 +221,151 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Per-channel constants for every output channel, once per kernel, by all threads: {bias_half, shift} pairs.
+    bool fast = false;
+    if (!I16) {
+        stage_fast_params(p.epi, fast_s, p.N, n_pad, (int)threadIdx.x, NUM_THREADS, slow_flag);
+        __syncthreads();
+        fast = !*slow_flag && !p.epi.half_even && !p.epi.lut && p.K <= 32768;
+    }
+
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int bi = tile / tiles_per_matrix, tm = tile % tiles_per_matrix;
-                const int m0 = (tm / p.n_tiles) * BLOCK_M;
-                const int n0 = (tm % p.n_tiles) * p.block_n;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t bar = smem_u32(&full_bar[stage]);
-                    uint8_t *st = smem + (size_t)stage * stage_bytes;
+        // The whole warp walks the tiles and waits (uniform control flow keeps addresses and counters in uniform
+        // registers); lane 0 alone issues the copies.
+        const bool issuer = lane == 0;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int rows = first_rows, nt = first_n;
+        long long w_empty = 0, w_load = 0;
+        (void)w_empty, (void)w_load;
+        TC_LAP_INIT;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int bi = p.batch == 1 ? 0 : rows / p.m_tiles;
+            const int m0 = (p.batch == 1 ? rows : rows % p.m_tiles) * BLOCK_M;
+            const int n0 = nt * p.block_n;
+            rows += step_rows, nt += step_n;
+            if (nt >= p.n_tiles)
+                nt -= p.n_tiles, rows++;
+            for (int kb = 0; kb < p.k_blocks; kb++) {
+                TC_LAP(w_load);
+                if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
+                    ok = false;
+                    break;
+                }
+                TC_LAP(w_empty);
+                const uint32_t bar = smem_u32(&full_bar[stage]);
+                const uint32_t st = smem_u32(smem) + (uint32_t)(stage * stage_bytes);
+                if (issuer) {
                     mbar_arrive_expect_tx(bar, (uint32_t)stage_bytes);
-                    tma_load_3d(smem_u32(st), &map_a, kb * p.swz, m0, bi, bar);
-                    tma_load_3d(smem_u32(st + NPLANE * a_bytes), &map_b, kb * p.swz, n0, bi, bar);
+                    tma_load_3d(st, &map_a, kb * p.swz, m0, bi, bar);
+                    tma_load_3d(st + NPLANE * a_bytes, &map_b, kb * p.swz, n0, bi, bar);
                     if (I16) {
-                        tma_load_3d(smem_u32(st + a_bytes), &map_a_lo, kb * p.swz, m0, bi, bar);
-                        tma_load_3d(smem_u32(st + 2 * a_bytes + b_bytes), &map_b_lo, kb * p.swz, n0, bi, bar);
-                    }
-                    if (++stage == p.stages) {
-                        stage = 0;
-                        phase ^= 1;
+                        tma_load_3d(st + a_bytes, &map_a_lo, kb * p.swz, m0, bi, bar);
+                        tma_load_3d(st + 2 * a_bytes + b_bytes, &map_b_lo, kb * p.swz, n0, bi, bar);
                     }
                 }
+                if (++stage == p.stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
             }
+        }
+        if (issuer) {
             if (!ok)
                 atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+            TC_REC(0, w_empty);
+            TC_REC(1, w_load);
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            int acc = 0;
-            uint32_t acc_phase = 0;
-            bool ok = true;
-            const uint32_t idesc_ss = idesc_i8(1, 1, BLOCK_M, p.block_n);
-            const uint32_t idesc_su = idesc_i8(1, 0, BLOCK_M, p.block_n);
-            const uint32_t idesc_us = idesc_i8(0, 1, BLOCK_M, p.block_n);
-            const uint32_t idesc_uu = idesc_i8(0, 0, BLOCK_M, p.block_n);
-            const int ksteps = p.swz / 32;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1)) {
+        // As above: the warp runs the loop, lane 0 issues.  A tcgen05.mma takes its descriptors from uniform registers;
+        // computed by one lane of a diverged warp they have to be moved there one by one, which made each issue cost
+        // a few hundred cycles - more than the MMA itself for the short reductions of the network's layers.
+        const bool issuer = lane == 0;
+        int stage = 0;
+        uint32_t phase = 0;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        long long w_tempty = 0, w_full = 0, w_issue = 0;
+        (void)w_tempty, (void)w_full, (void)w_issue;
+        TC_LAP_INIT;
+        const uint32_t idesc_ss = idesc_i8(1, 1, BLOCK_M, p.block_n);
+        const uint32_t idesc_su = idesc_i8(1, 0, BLOCK_M, p.block_n);
+        const uint32_t idesc_us = idesc_i8(0, 1, BLOCK_M, p.block_n);
+        const uint32_t idesc_uu = idesc_i8(0, 0, BLOCK_M, p.block_n);
+        const int ksteps = p.swz / 32;
+        const uint32_t smem_base = smem_u32(smem);
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            TC_LAP(w_issue);
+            if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1)) {
+                ok = false;
+                break;
+            }
+            TC_LAP(w_tempty);
+            fence_after();
+            const uint32_t d0 = tmem_base + (uint32_t)(acc * NACC * p.block_n);
+            for (int kb = 0; kb < p.k_blocks; kb++) {
+                TC_LAP(w_issue);
+                if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
                     ok = false;
                     break;
                 }
+                TC_LAP(w_full);
                 fence_after();
-                const uint32_t d0 = tmem_base + (uint32_t)(acc * NACC * p.block_n);
-                for (int kb = 0; kb < p.k_blocks; kb++) {
-                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
-                        ok = false;
-                        break;
+                const uint32_t st = smem_base + (uint32_t)(stage * stage_bytes);
+                const uint64_t da = smem_desc_swizzled(st, p.swz);
+                const uint64_t db = smem_desc_swizzled(st + NPLANE * a_bytes, p.swz);
+                if (!I16) {
+                    const uint32_t first = kb != 0 ? 1u : 0u;
+                    if (issuer) {
+                        mma_i8(d0, da, db, idesc_ss, first);
+                        if (ksteps > 1)
+                            mma_i8(d0, da + 2, db + 2, idesc_ss, 1u);
+                        if (ksteps > 2) {
+                            mma_i8(d0, da + 4, db + 4, idesc_ss, 1u);
+                            mma_i8(d0, da + 6, db + 6, idesc_ss, 1u);
+                        }
+                        commit(smem_u32(&empty_bar[stage]));
                     }
-                    fence_after();
-                    const uint32_t st = smem_u32(smem + (size_t)stage * stage_bytes);
-                    const uint64_t da = smem_desc_swizzled(st, p.swz);
-                    const uint64_t db = smem_desc_swizzled(st + NPLANE * a_bytes, p.swz);
-                    for (int k = 0; k < ksteps; k++) {
-                        const uint32_t accum = (kb | k) != 0;
-                        const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K, in 16-byte units
-                        if (!I16) {
-                            mma_i8(d0, da + koff, db + koff, idesc_ss, accum);
-                        } else {
-                            const uint64_t da_lo = smem_desc_swizzled(st + a_bytes, p.swz);
-                            const uint64_t db_lo = smem_desc_swizzled(st + 2 * a_bytes + b_bytes, p.swz);
+                } else {
+                    const uint64_t da_lo = smem_desc_swizzled(st + a_bytes, p.swz);
+                    const uint64_t db_lo = smem_desc_swizzled(st + 2 * a_bytes + b_bytes, p.swz);
+                    if (issuer) {
+                        for (int k = 0; k < ksteps; k++) {
+                            const uint32_t accum = (kb | k) != 0;
+                            const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K, in 16-byte units
                             mma_i8(d0, da + koff, db + koff, idesc_ss, accum);                      // hi * hi
                             mma_i8(d0 + p.block_n, da + koff, db_lo + koff, idesc_su, accum);       // hi * lo
                             mma_i8(d0 + p.block_n, da_lo + koff, db + koff, idesc_us, 1u);          // lo * hi
                             mma_i8(d0 + 2 * p.block_n, da_lo + koff, db_lo + koff, idesc_uu, accum); // lo * lo
                         }
-                    }
-                    commit(smem_u32(&empty_bar[stage]));
-                    if (++stage == p.stages) {
-                        stage = 0;
-                        phase ^= 1;
+                        commit(smem_u32(&empty_bar[stage]));
                     }
                 }
-                if (!ok)
-                    break;
-                commit(smem_u32(&tfull_bar[acc]));
-                if (++acc == p.acc_stages) {
-                    acc = 0;
-                    acc_phase ^= 1;
+                if (++stage == p.stages) {
+                    stage = 0;
+                    phase ^= 1;
                 }
             }
             if (!ok)
+                break;
+            if (issuer)
+                commit(smem_u32(&tfull_bar[acc]));
+            if (++acc == p.acc_stages) {
+                acc = 0;
+                acc_phase ^= 1;
+            }
+        }
+        if (issuer) {
+            if (!ok)
                 atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+            TC_REC(2, w_tempty);
+            TC_REC(3, w_full);
+            TC_REC(4, w_issue);
         }
         __syncwarp();
     } else {
@@ -307,29 +376,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int part = group / p.acc_stages;   // which share of the tile's columns
         const int lane_group = warp & 3;         // TMEM lanes this warp may read: 32*lane_group .. +31
         const int row_in_tile = lane_group * 32 + lane;
-        const int et = threadIdx.x - 64;
 
-        // per-channel constants for every output channel, once per kernel
-        bool fast = false;
-        if (!I16) {
-            stage_fast_params(p.epi, fast_s, p.N, n_pad, et, EPI_WARPS * 32, slow_flag);
-            asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
-            fast = !*slow_flag && !p.epi.half_even && !p.epi.lut && p.K <= 32768;
-        }
         const uint32_t fp_base = epi_param_base(fast_s);
         uint32_t acc_phase = 0;
         bool ok = true;
         int local = 0;
+        int rows = first_rows, nt = first_n;
+        long long w_tfull = 0, w_work = 0, w_store = 0;
+        (void)w_tfull, (void)w_work, (void)w_store;
+        TC_LAP_INIT;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
-            if (local % p.acc_stages != acc)
+            const int bi = p.batch == 1 ? 0 : rows / p.m_tiles;
+            const int m0 = (p.batch == 1 ? rows : rows % p.m_tiles) * BLOCK_M;
+            const int n0 = nt * p.block_n;
+            rows += step_rows, nt += step_n;
+            if (nt >= p.n_tiles)
+                nt -= p.n_tiles, rows++;
+            if ((local & (p.acc_stages - 1)) != acc) // acc_stages is 1, 2 or 4
                 continue;
-            const int bi = tile / tiles_per_matrix, tm = tile % tiles_per_matrix;
-            const int m0 = (tm / p.n_tiles) * BLOCK_M;
-            const int n0 = (tm % p.n_tiles) * p.block_n;
+            TC_LAP(w_work);
             if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase)) {
                 ok = false;
                 break;
             }
+            TC_LAP(w_tfull);
             acc_phase ^= 1;
             fence_after();
             const bool row_ok = m0 + row_in_tile < p.M;
@@ -343,6 +413,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (leader)
                         bulk_wait_read_all(); // the previous store out of this tile has been read
                     named_bar(2 + group, 128);
+                    TC_LAP(w_store);
                     const int col0 = part * p.out_pw;
                     const uint32_t fpp = fp_base + (uint32_t)(n0 + col0) * 8u;
                     const int floor_q = p.epi.relu ? 0 : INT_MIN;
@@ -404,6 +475,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!ok && lane == 0)
             atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+        if (ew == 0 && lane == 0) {
+            TC_LAP(w_work);
+            TC_REC(5, w_tfull);
+            TC_REC(6, w_work);
+            TC_REC(7, w_store);
+        }
         if (!I16 && p.out_pw && (ew & 3) == 0 && lane == 0)
             bulk_wait_all(); // shared memory stays allocated until the last store has left it
     }
@@ -733,7 +810,9 @@ bool plan(const espdl_conv_desc &d, TcParams &p, bool force_direct = false)
         return false;
     p.M = (int)M, p.N = d.out_c, p.K = d.in_c;
     p.batch = batched ? d.n : 1;
-    const int max_bn = i16 ? 128 : 256;
+    int max_bn = i16 ? 128 : 256;
+    if (const char *cap = getenv("ESPDL_B200_MAX_BLOCK_N")) // tile width cap (a multiple of 16), for experiments
+        max_bn = max(16, min(max_bn, atoi(cap) / 16 * 16));
     p.n_tiles = (p.N + max_bn - 1) / max_bn;
     p.block_n = (((p.N + p.n_tiles - 1) / p.n_tiles) + 15) / 16 * 16;
     if (!i16 && p.block_n > 128)
@@ -994,3 +1073,11 @@ extern "C" int espdl_b200_gemm_s16_static(const espdl_conv_desc *desc, void *str
     }
     return conv2d_tc(*desc, scratch, (size_t)ESPDL_B200_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
 }
+
+#ifdef ESPDL_TC_TIMING
+// Measurement builds only: copies the role cycle counters of the last gemm_tc_kernel launch (8 values per CTA).
+extern "C" int espdl_b200_debug_gemm_timing(long long *out, int ctas)
+{
+    return cudaMemcpyFromSymbol(out, espdl::g_tc_timing, sizeof(long long) * 8 * (size_t)(ctas > 256 ? 256 : ctas)) == cudaSuccess ? 0 : -3;
+}
+#endif
