@@ -155,10 +155,11 @@ int espdl_b200_stream_sync(void *stream)
     // a tile kernel whose bounded wait expired leaves its status in a device word
     int dev = read_and_clear_device_error();
     const int dev_stem = read_and_clear_device_error_stem();
+    const int dev_dw = read_and_clear_device_error_dw();
     const int dev_conv = read_and_clear_device_error_conv();
     const int dev_block = read_and_clear_device_error_block();
     if (!dev)
-        dev = dev_stem ? dev_stem : (dev_conv ? dev_conv : dev_block);
+        dev = dev_stem ? dev_stem : (dev_conv ? dev_conv : (dev_block ? dev_block : dev_dw));
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -385,6 +386,10 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
         // which caps any diagonal-filter formulation on the tensor cores far below the dp4a walk.
         if (desc->kernel == ESPDL_KERNEL_TCGEN05)
             return ESPDL_ERR_UNSUPPORTED;
+        // 3x3 int8 with 16-byte channel runs: the TMA-fed kernel; ESPDL_KERNEL_SIMT asks for the kernels that read global
+        // memory directly
+        if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_dw_tma_supported(*desc))
+            return conv2d_dw_tma(*desc, s);
         return conv2d_depthwise(*desc, s);
     }
     if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_stem_tc_supported(*desc))
@@ -398,6 +403,10 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
             return conv2d_tc(*desc, workspace, workspace_bytes, s);
         if (desc->kernel == ESPDL_KERNEL_TCGEN05)
             return ESPDL_ERR_UNSUPPORTED;
+        // 3x3 int8 with 16-byte channel runs: the TMA-fed kernel; ESPDL_KERNEL_SIMT asks for the kernels that read global
+        // memory directly
+        if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_dw_tma_supported(*desc))
+            return conv2d_dw_tma(*desc, s);
         // shapes the tile kernel does not take: one call per image
         const size_t es = desc->dtype == ESPDL_DTYPE_INT16 ? 2 : 1;
         const long long ips = desc->in_pixel_stride ? desc->in_pixel_stride : desc->in_c;

@@ -36,6 +36,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
               int n_peer = 0); // peer_delta: byte distances to copies of the output on other GPUs that receive every row as well
 int read_and_clear_device_error(); // status word written by device-side bounded waits (0 = none)
 int read_and_clear_device_error_stem();
+int read_and_clear_device_error_dw();
 int read_and_clear_device_error_conv();
 int read_and_clear_device_error_block();
 int image_preprocess(const espdl_image_desc &d, cudaStream_t s);
@@ -46,6 +47,8 @@ bool fused_block_supported(const espdl_block_desc &d);
 int fused_block_tc(const espdl_block_desc &d, cudaStream_t s);
 bool conv2d_conv_tc_supported(const espdl_conv_desc &d);
 int conv2d_conv_tc(const espdl_conv_desc &d, cudaStream_t s);
+bool conv2d_dw_tma_supported(const espdl_conv_desc &d);
+int conv2d_dw_tma(const espdl_conv_desc &d, cudaStream_t s);
 bool conv2d_stem_tc_supported(const espdl_conv_desc &d);
 int conv2d_stem_tc(const espdl_conv_desc &d, cudaStream_t s);
 

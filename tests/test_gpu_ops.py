@@ -85,10 +85,17 @@ DW_SHAPES = [
 ]
 
 
+@pytest.mark.parametrize("narrow", [False, True], ids=["auto", "tma-narrow"])
 @pytest.mark.parametrize("kw", DW_SHAPES, ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items() if a != "pad"))
-def test_depthwise_3x3_shapes(kw):
-    """The 3x3 depthwise kernel on the network's layer shapes, ragged extents and unusual paddings, against the oracle;
-    a depthwise conv has no tensor-core form, so asking for one is refused."""
+def test_depthwise_3x3_shapes(kw, narrow, monkeypatch):
+    """The 3x3 depthwise kernels on the network's layer shapes, ragged extents and unusual paddings, against the oracle:
+    the TMA-fed kernel (the default from 64 channels on; with ESPDL_B200_DW_TMA_NARROW=1 also below) and the kernel that
+    reads global memory directly (ESPDL_KERNEL_SIMT).  A depthwise conv has no tensor-core form, so asking for one is
+    refused."""
+    if narrow:
+        if kw["cin"] >= 64:
+            pytest.skip("already on the TMA-fed kernel")
+        monkeypatch.setenv("ESPDL_B200_DW_TMA_NARROW", "1")
     case = cases.conv_case(seed=61, depthwise=True, kh=3, kw=3, per_channel=True, e_in=-5, e_out=-5, e_w=(-9, -5), **kw)
     want = gpu_util.run_conv_oracle(case)
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), want)
