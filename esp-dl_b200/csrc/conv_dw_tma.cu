@@ -108,7 +108,7 @@ __device__ __forceinline__ void dwt_load_consts(DwtConsts<S> &k, const DwtParams
         const int s = max(-31, min(31, p.e_shift_base - e));
         // (acc + bias + 2^(s-1)) >> s is exact while nothing can overflow: |acc| <= 9 * 2^14, |bias| < 2^30, 1 <= s <= 24
         k.fast = k.fast && s >= 1 && s <= 24 && b < (1 << 30) && b > -(1 << 30);
-        k.shift[i] = s;
+        k.shift[i] = s - (p.relu ? 1 : 0); // what the walk shifts by (see dwt_emit); the general form recomputes its own
         k.init[i] = b + (s >= 1 ? (1 << (s - 1)) : 0);
     }
 }
@@ -165,14 +165,27 @@ __device__ __forceinline__ void dwt_emit(const DwtConsts<S> &k, const DwtCol<S> 
             }
         }
     }
+    if (floor_q == 0) {
+        // ReLU: the staged shifts are one less than the real ones; packing with saturation to [0, 255] clamps below at
+        // zero, halving every byte completes the shift and turns the upper clamp into 127 - a shift and a mask per
+        // word instead of a max per output
 #pragma unroll
-    for (int ro = 0; ro < ROWS_OUT; ro++) {
-        const int q0 = max(acc[ro][0] >> k.shift[0], floor_q), q1 = max(acc[ro][1] >> k.shift[1], floor_q);
-        const int q2 = max(acc[ro][2] >> k.shift[2], floor_q), q3 = max(acc[ro][3] >> k.shift[3], floor_q);
-        uint32_t hi, wd;
-        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
-        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
-        op[ro * out_row_words] = wd;
+        for (int ro = 0; ro < ROWS_OUT; ro++) {
+            const int q0 = acc[ro][0] >> k.shift[0], q1 = acc[ro][1] >> k.shift[1], q2 = acc[ro][2] >> k.shift[2], q3 = acc[ro][3] >> k.shift[3];
+            uint32_t hi, wd;
+            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
+            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
+            op[ro * out_row_words] = (wd >> 1) & 0x7f7f7f7fu;
+        }
+    } else {
+#pragma unroll
+        for (int ro = 0; ro < ROWS_OUT; ro++) {
+            const int q0 = acc[ro][0] >> k.shift[0], q1 = acc[ro][1] >> k.shift[1], q2 = acc[ro][2] >> k.shift[2], q3 = acc[ro][3] >> k.shift[3];
+            uint32_t hi, wd;
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
+            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
+            op[ro * out_row_words] = wd;
+        }
     }
 }
 

@@ -82,6 +82,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t *full_bar = bars, *empty_bar = bars + CV_MAX_STAGES, *tfull_bar = bars + 2 * CV_MAX_STAGES, *tempty_bar = tfull_bar + CV_MAX_ACC;
     uint32_t *tmem_slot = (uint32_t *)(tempty_bar + CV_MAX_ACC);
     int *slow_flag = (int *)(tmem_slot + 1);
+    uint8_t *lut_s = (uint8_t *)(slow_flag + 3); // the fused 8-bit table, 256 bytes, 16-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_image = p.ytiles * p.xtiles * p.n_tiles;
@@ -200,8 +201,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int row_in_tile = lane_group * 32 + lane;
         const int et = threadIdx.x - 64;
         stage_fast_params(p.epi, fast_s, p.cout, n_pad, et, 16 * 32, slow_flag);
+        if (p.epi.lut)
+            stage_lut(p.epi.lut, lut_s, et, 16 * 32);
         asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
-        const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut && (long long)p.cin * p.kh * p.kw <= 32768;
+        // a fused table rides on the staged form; the direct-store form applies it in its general path
+        const bool fast = !*slow_flag && !p.epi.half_even && (long long)p.cin * p.kh * p.kw <= 32768;
         const uint32_t fp_base = epi_param_base(fast_s);
         const int floor_q = p.epi.relu ? 0 : INT_MIN;
         const int ry = row_in_tile / p.P, rx = row_in_tile % p.P;
@@ -231,7 +235,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 named_bar(2 + group, 128);
                 const int col0 = part * p.out_pw;
                 const uint32_t fpp = fp_base + (uint32_t)(n0 + col0) * 8u;
-                if (p.out_pw == 128)
+                if (p.epi.lut) {
+                    const uint32_t tbl = smem_u32(lut_s);
+                    if (p.out_pw == 128)
+                        epilogue_stage<128, true>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q, tbl);
+                    else if (p.out_pw == 64)
+                        epilogue_stage<64, true>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q, tbl);
+                    else
+                        epilogue_stage<0, true>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q, tbl);
+                } else if (p.out_pw == 128)
                     epilogue_stage<128>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q);
                 else if (p.out_pw == 64)
                     epilogue_stage<64>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q);
@@ -259,7 +271,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ld16(t0 + c0, v);
                     ld_wait16(v);
                     uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    if (fast) {
+                    if (fast && !p.epi.lut) {
                         if (p.epi.relu)
                             requant16_fast<true>(v, fast_s + n0 + c0, pk);
                         else
@@ -314,7 +326,7 @@ CUtensorMapSwizzle swizzle_of(int bytes)
         : (bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : (bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE));
 }
 
-size_t conv_aux_bytes(const ConvTcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * CV_MAX_STAGES + 2 * CV_MAX_ACC) * 8 + 32; }
+size_t conv_aux_bytes(const ConvTcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * CV_MAX_STAGES + 2 * CV_MAX_ACC) * 8 + 32 + 256; }
 
 bool conv_plan(const espdl_conv_desc &d, ConvTcParams &p)
 {

@@ -193,6 +193,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t *full_bar = bars, *empty_bar = bars + MAX_STAGES, *tfull_bar = bars + 2 * MAX_STAGES, *tempty_bar = tfull_bar + MAX_ACC;
     uint32_t *tmem_slot = (uint32_t *)(tempty_bar + MAX_ACC);
     int *slow_flag = (int *)(tmem_slot + 1);
+    uint8_t *lut_s = (uint8_t *)(slow_flag + 3); // the fused 8-bit table, 256 bytes, 16-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.batch * p.m_tiles * p.n_tiles;
@@ -225,8 +226,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bool fast = false;
     if (!I16) {
         stage_fast_params(p.epi, fast_s, p.N, n_pad, (int)threadIdx.x, NUM_THREADS, slow_flag);
+        if (p.epi.lut)
+            stage_lut(p.epi.lut, lut_s, (int)threadIdx.x, NUM_THREADS);
         __syncthreads();
-        fast = !*slow_flag && !p.epi.half_even && !p.epi.lut && p.K <= 32768;
+        fast = !*slow_flag && !p.epi.half_even && p.K <= 32768; // a fused table rides on the staged form; the direct-store forms apply it in their general path
     }
 
     if (warp == 0) {
@@ -417,7 +420,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const int col0 = part * p.out_pw;
                     const uint32_t fpp = fp_base + (uint32_t)(n0 + col0) * 8u;
                     const int floor_q = p.epi.relu ? 0 : INT_MIN;
-                    if (p.res)
+                    if (p.epi.lut) {
+                        const uint32_t tbl = smem_u32(lut_s);
+                        if (p.out_pw == 128)
+                            epilogue_stage<128, true>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q, tbl);
+                        else if (p.out_pw == 64)
+                            epilogue_stage<64, true>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q, tbl);
+                        else
+                            epilogue_stage<0, true>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q, tbl);
+                    } else if (p.res)
                         epilogue_stage_residual(t0 + col0, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q,
                                                 p.res + m * p.rps + n0 + col0, row_ok, p.N - (n0 + col0));
                     else if (p.out_pw == 128)
@@ -439,7 +450,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         mbar_arrive(smem_u32(&tempty_bar[acc]));
                     continue;
                 }
-                epilogue_direct_tile(p, fast_s, fp_base, t0, m, n0, row_ok, fast, parts, part);
+                epilogue_direct_tile(p, fast_s, fp_base, t0, m, n0, row_ok, fast && !p.epi.lut, parts, part);
             } else {
                 int chunk = 0;
                 for (int c0 = 0; c0 < p.block_n; c0 += 16, chunk++) {
@@ -796,7 +807,7 @@ constexpr size_t SMEM_BUDGET = 200 * 1024;      // stages + staging tiles of the
 constexpr size_t SMEM_BUDGET_DEEP = 225 * 1024; // long reductions with direct row stores: one more stage in flight (1.79 -> 1.97 POPS
                                                 // at 65536x1024x1024); for the staged layers the larger budget measured 5 % slower
 
-size_t aux_bytes(const TcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * MAX_STAGES + 2 * MAX_ACC) * 8 + 32; }
+size_t aux_bytes(const TcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * MAX_STAGES + 2 * MAX_ACC) * 8 + 32 + 256; }
 
 bool plan(const espdl_conv_desc &d, TcParams &p, bool force_direct = false)
 {

@@ -390,6 +390,27 @@ __device__ __forceinline__ uint32_t requant4_floor(const int32_t *v, uint32_t fp
     return w;
 }
 
+// Fused 8-bit table (ESP-DL's LUT activations, e.g. Swish: out = table[(uint8)q ^ 0x80], esp-dl/dl/base/dl_base_lut.cpp:10-15)
+// for the staged epilogue: the 256 entries sit in shared memory, re-ordered so that the raw output byte is the index
+// (entry b holds table[b ^ 0x80]).  Staged once per CTA by `nthreads` cooperating threads.
+__device__ __forceinline__ void stage_lut(const int8_t *lut, uint8_t *lut_s, int tid, int nthreads)
+{
+    for (int i = tid; i < 256; i += nthreads) lut_s[i] = (uint8_t)lut[i ^ 0x80];
+}
+
+// Four saturated int8 in a word -> the four table entries: a byte extraction, a one-byte shared-memory load and a
+// share of three merges per output.
+__device__ __forceinline__ uint32_t lut4(uint32_t w, uint32_t tbl)
+{
+    const uint32_t i0 = w & 0xffu, i1 = __byte_perm(w, 0u, 0x4441), i2 = __byte_perm(w, 0u, 0x4442), i3 = w >> 24;
+    uint32_t b0, b1, b2, b3;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(b0) : "r"(tbl + i0));
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(b1) : "r"(tbl + i1));
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(b2) : "r"(tbl + i2));
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(b3) : "r"(tbl + i3));
+    return __byte_perm(__byte_perm(b0, b1, 0x3340), __byte_perm(b2, b3, 0x3340), 0x5410);
+}
+
 // Staged epilogue: this thread's accumulator row, PW columns (multiple of 16, at most 128) starting at TMEM address
 // t0, requantised and written as row `row` of a [128][PW] byte tile in shared memory, from where one TMA store moves
 // the whole tile to global memory in full lines (a thread storing its own row 32 bytes at a time reaches less than
@@ -397,8 +418,8 @@ __device__ __forceinline__ uint32_t requant4_floor(const int32_t *v, uint32_t fp
 // other widths): 16-byte chunk index XOR bits 7.. of the byte offset, which for these widths is a function of the
 // row alone.  PW is a template parameter so that the walk over the columns is straight-line code; PW = 0 is the
 // generic form for any width (`pw`).  TMEM is read 16 columns at a time into two register sets in turn.
-template <int PW>
-__device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, int floor_q)
+template <int PW, bool LUT = false>
+__device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, int floor_q, uint32_t tbl = 0)
 {
     const int width = PW ? PW : pw;
     uint32_t rx = 0; // what the chunk offset of this row is XORed with
@@ -422,6 +443,10 @@ __device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_
             ld16(t0 + c + 16, vb);
 #pragma unroll
         for (int q = 0; q < 4; q++) pk[q] = requant4_floor(va + 4 * q, fp + (uint32_t)(c + 4 * q) * 8u, floor_q);
+        if (LUT) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) pk[q] = lut4(pk[q], tbl);
+        }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)c ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                      : "memory");
         if (!second)
@@ -432,6 +457,10 @@ __device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_
             ld16(t0 + c + 32, va);
 #pragma unroll
         for (int q = 0; q < 4; q++) pk[q] = requant4_floor(vb + 4 * q, fp + (uint32_t)(c + 16 + 4 * q) * 8u, floor_q);
+        if (LUT) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) pk[q] = lut4(pk[q], tbl);
+        }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)(c + 16) ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
                      "r"(pk[3])
                      : "memory");

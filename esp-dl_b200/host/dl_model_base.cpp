@@ -388,6 +388,56 @@ void Model::fuse_blocks()
     }
 }
 
+// A LUT-type node (LUT, Swish, Sigmoid, Tanh, ... exported with a 256-entry int8 table: esp-dl/dl/module/include/
+// dl_module_swish.hpp:84-103, dl_module_lut.hpp:50-76) whose input comes from a dense int8 Conv and is read by nothing
+// else: the conv applies the table in its epilogue (espdl_conv_desc::lut, held in shared memory by the tile kernels)
+// and writes the LUT node's output; the node and the tensor between the two leave the plan.  Exactly the reference's
+// arithmetic: requantise and saturate to the intermediate exponent, then table[(uint8)q ^ 0x80]
+// (esp-dl/dl/base/dl_base_lut.cpp:10-15).  Only convs the tensor-core tile kernels take (input channels a multiple of
+// 16) are folded; ESPDL_B200_FOLD_LUT=0 keeps the nodes.
+void Model::fold_luts()
+{
+    if (!env_flag("ESPDL_B200_FOLD_LUT", true) || !m_reuse_memory)
+        return;
+    ModelContext *ctx = m_model_context;
+    std::vector<std::string> graph_outputs = m_fbs_model->get_graph_outputs();
+    auto is_graph_output = [&](const std::string &n) { return std::find(graph_outputs.begin(), graph_outputs.end(), n) != graph_outputs.end(); };
+    for (size_t s = 0; s < m_execution_plan.size(); s++) {
+        module::LUT *lut = dynamic_cast<module::LUT *>(m_execution_plan[s]);
+        if (!lut || lut->quant_type != QUANT_TYPE_SYMM_8BIT || m_module_inputs[s].empty() || m_module_outputs[s].size() != 1)
+            continue;
+        TensorBase *table = lut->get_table();
+        if (!table || table->dtype != DATA_TYPE_INT8 || table->get_size() != 256)
+            continue;
+        const std::string x = m_module_inputs[s][0], y = m_module_outputs[s][0];
+        if (is_graph_output(x) || m_fbs_model->is_parameter(x) || m_fbs_model->get_value_info_dtype(x) != DATA_TYPE_INT8 ||
+            m_fbs_model->get_value_info_dtype(y) != DATA_TYPE_INT8)
+            continue;
+        int producer = -1, readers = 0;
+        for (size_t k = 0; k < m_execution_plan.size(); k++) {
+            for (const std::string &o : m_module_outputs[k])
+                if (o == x) producer = (int)k;
+            for (const std::string &i : m_module_inputs[k])
+                if (i == x) readers++;
+        }
+        if (producer < 0 || producer >= (int)s || readers != 1 || m_module_types[producer] != "Conv" || m_module_outputs[producer].size() != 1 ||
+            m_module_inputs[producer].size() < 2)
+            continue;
+        module::Conv *conv = dynamic_cast<module::Conv *>(m_execution_plan[producer]);
+        TensorBase *filter = ctx->get_tensor(m_module_inputs[producer][1]);
+        if (!conv || !conv->can_fuse_lut() || !filter || filter->shape.size() != 4 || filter->shape[2] % 16 != 0)
+            continue;
+        conv->set_fused_lut(lut->release_table(), m_fbs_model->get_value_info_exponent(x));
+        m_module_outputs[producer][0] = y;
+        delete m_execution_plan[s];
+        m_execution_plan.erase(m_execution_plan.begin() + s);
+        m_module_types.erase(m_module_types.begin() + s);
+        m_module_inputs.erase(m_module_inputs.begin() + s);
+        m_module_outputs.erase(m_module_outputs.begin() + s);
+        s--;
+    }
+}
+
 void Model::fold_residual_adds()
 {
     if (!env_flag("ESPDL_B200_FOLD_ADD", true) || !m_reuse_memory)
@@ -447,6 +497,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
     if (!m_fbs_model || !m_model_context || m_built)
         return;
     fuse_blocks();
+    fold_luts();
     fold_residual_adds();
     ModelContext *ctx = m_model_context;
     std::vector<TensorInfo> &infos = m_tensor_infos;

@@ -135,6 +135,7 @@ protected:
     long long m_submitted = 0, m_collected = 0;
     void release_pipeline();
     void fold_residual_adds();
+    void fold_luts();
     void fuse_blocks();
     bool m_built = false;
     std::vector<TensorInfo> m_tensor_infos;

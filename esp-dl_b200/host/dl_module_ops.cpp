@@ -85,6 +85,7 @@ Conv::~Conv()
     for (void *p : {m_dev_exponents, m_grp_filter, m_grp_bias, m_grp_exponents})
         if (p)
             espdl_b200_arena_free(p);
+    delete m_lut;
 }
 
 std::vector<std::vector<int>> Conv::get_output_shape(std::vector<std::vector<int>> &input_shapes)
@@ -264,7 +265,7 @@ int Conv::fill_desc(ModelContext *context, void *desc)
     } else {
         return ESPDL_ERR_UNSUPPORTED;
     }
-    d.in_exponent = input->exponent, d.out_exponent = output->exponent;
+    d.in_exponent = input->exponent, d.out_exponent = m_lut ? m_pre_lut_exponent : (int)output->exponent;
     d.per_channel = filter->exponent.is_per_channel();
     d.filter_exponent = filter->exponent;
     if (m_group_px > 1) { // same bytes, g pixels per row: [N, 1, H*W/g, g*Cin] x block-diagonal filter -> [N, 1, H*W/g, g*Cout]

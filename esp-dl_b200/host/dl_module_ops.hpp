@@ -20,8 +20,16 @@ public:
     size_t workspace_bytes(ModelContext *context) override;
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
     void print() override;
-    /// Fuse a following 8-bit LUT node into the epilogue (the table must already be on the device).
-    void set_fused_lut(TensorBase *table) { m_lut = table; }
+    /// Fuse a following 8-bit LUT node (Swish, Sigmoid, ... exported as tables) into the epilogue.  The conv takes
+    /// ownership of the table and keeps requantising to `pre_lut_exponent`, the exponent of the tensor that stood
+    /// between the two nodes; its output tensor is then the LUT node's.
+    void set_fused_lut(TensorBase *table, int pre_lut_exponent)
+    {
+        m_lut = table;
+        m_pre_lut_exponent = pre_lut_exponent;
+    }
+    /// True for the convs whose kernels apply a table in their staged epilogue: dense int8, no residual, no table yet.
+    bool can_fuse_lut() const { return m_group == 1 && quant_type == QUANT_TYPE_SYMM_8BIT && !m_lut && !m_residual && (activation == Linear || activation == ReLU); }
     /// True for a pointwise int8 conv (1x1, stride 1, no padding, group 1) without a fused table: the shapes whose
     /// kernels can add a residual to their result.
     bool can_fold_add() const;
@@ -59,7 +67,8 @@ protected:
     // and the filter becomes block diagonal, [g*Cout][g*Cin].  NHWC memory is unchanged on both sides.
     int m_group_px = 1;
     void *m_grp_filter = nullptr, *m_grp_bias = nullptr, *m_grp_exponents = nullptr;
-    TensorBase *m_lut = nullptr;
+    TensorBase *m_lut = nullptr;     ///< fused 8-bit table (owned)
+    int m_pre_lut_exponent = 0;      ///< what the accumulator is requantised to before the table is applied
     bool m_prepared = false;
 };
 
@@ -170,6 +179,13 @@ public:
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
     esp_err_t prepare(ModelContext *context) override;
     TensorBase *get_table() { return m_param; }
+    /// Hands the table (or PReLU slopes) to the caller, who owns it from then on.
+    TensorBase *release_table()
+    {
+        TensorBase *t = m_param;
+        m_param = nullptr;
+        return t;
+    }
     int op() const { return m_op; }
 
 protected:

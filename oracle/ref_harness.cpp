@@ -20,6 +20,8 @@
  */
 #include "../include/espdl_b200.h"
 
+#include "dl_detect_yolo11_postprocessor.hpp"
+#include "dl_image_norm_quant.hpp"
 #include "dl_module_add.hpp"
 #include "dl_module_average_pool.hpp"
 #include "dl_module_clip.hpp"
@@ -444,6 +446,69 @@ int ref_pad(const espdl_pad_desc *d)
     std::vector<int> so = m.get_output_shape(in_shapes)[0];
     std::unique_ptr<TensorBase> ti(view(shape, d->input, 0, dtype)), to(view(so, d->output, 0, dtype));
     m.run({ti.get()}, {to.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* The reference's own YOLO11 post-processor (esp-dl/vision/detect/dl_detect_yolo11_postprocessor.cpp:8-96 over
+ * dl_detect_postprocessor.cpp:5-50), unmodified, on host tensors: three (or fewer) heads named score<i> / box<i>.
+ * Same arguments and result layout as oracle_yolo11_postprocess: boxes[5*i] = category, then the clipped box; returns
+ * the number of results. */
+struct ref_det_stage {
+    const int8_t *score, *box;
+    int h, w, classes, score_exponent, box_exponent, stride_y, stride_x, offset_y, offset_x;
+};
+
+int ref_yolo11_postprocess(const ref_det_stage *stages, int n_stages, float score_thr, float nms_thr, int top_k, float inv_scale_x,
+                           float inv_scale_y, int border_left, int border_top, int width, int height, int round_mode, int max_results,
+                           int *boxes, float *scores)
+{
+    (void)round_mode; /* the host build rounds half up, as every generic-C build of the reference does */
+    if (n_stages != 3)
+        return -1; /* postprocess() reads exactly score0..2 / box0..2 */
+    dl::Model model;
+    dl::image::ImagePreprocessor pre;
+    pre.inv_scale_x = inv_scale_x, pre.inv_scale_y = inv_scale_y, pre.border_left = border_left, pre.border_top = border_top;
+    std::vector<dl::TensorBase *> owned;
+    std::vector<dl::detect::anchor_point_stage_t> geo;
+    for (int i = 0; i < n_stages; i++) {
+        const ref_det_stage &st = stages[i];
+        dl::TensorBase *sc = new dl::TensorBase({1, st.h, st.w, st.classes}, st.score, st.score_exponent, dl::DATA_TYPE_INT8, false);
+        dl::TensorBase *bx = new dl::TensorBase({1, st.h, st.w, 64}, st.box, st.box_exponent, dl::DATA_TYPE_INT8, false);
+        owned.push_back(sc), owned.push_back(bx);
+        model.outputs["score" + std::to_string(i)] = sc;
+        model.outputs["box" + std::to_string(i)] = bx;
+        geo.push_back({st.stride_y, st.stride_x, st.offset_y, st.offset_x});
+    }
+    dl::detect::yolo11PostProcessor post(&model, &pre, score_thr, nms_thr, top_k, geo);
+    post.postprocess();
+    std::list<dl::detect::result_t> &res = post.get_result(width, height);
+    int n = 0;
+    for (const dl::detect::result_t &r : res) {
+        if (n >= max_results)
+            break;
+        boxes[5 * n] = r.category;
+        for (int j = 0; j < 4; j++) boxes[5 * n + 1 + j] = r.box[j];
+        scores[n] = r.score;
+        n++;
+    }
+    for (dl::TensorBase *t : owned) delete t;
+    return n;
+}
+
+/* The reference's NormQuant tables (esp-dl/vision/image/dl_image_norm_quant.hpp:13-31), three channels, int8 or int16:
+ * `table` receives 3 * 256 entries. */
+int ref_norm_quant_table(void *table, const float *mean, const float *std, int exponent, int bits)
+{
+    const std::array<float, 3> m = {mean[0], mean[1], mean[2]}, s = {std[0], std[1], std[2]};
+    if (bits == 8) {
+        dl::image::NormQuant<int8_t, 3> nq(m, s, exponent);
+        memcpy(table, nq.m_lut1, 3 * 256);
+    } else if (bits == 16) {
+        dl::image::NormQuant<int16_t, 3> nq(m, s, exponent);
+        memcpy(table, nq.m_lut1, 3 * 256 * 2);
+    } else {
+        return -1;
+    }
     return 0;
 }
 

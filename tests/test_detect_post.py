@@ -1,6 +1,8 @@
 """Detection post-processing: the device candidate scan plus the host decode / sort / NMS of dl::detect::yolo11PostProcessor
 against the oracle's sequential restatement of the reference, on the three heads of the generated detector and on
-synthetic head tensors.  The reference ships no vectors for this step (parity pinned by the restatement only)."""
+synthetic head tensors.  The reference ships no vectors for this step; the restatement is pinned against the
+reference's own post-processor classes compiled for the host (oracle/_ref: dl_detect_postprocessor.cpp and
+dl_detect_yolo11_postprocessor.cpp, unmodified, behind stand-ins for dl::Model and dl::image::ImagePreprocessor)."""
 import ctypes as C
 
 import numpy as np
@@ -31,6 +33,47 @@ def oracle_detect(heads, score_thr, nms_thr, top_k, width, height, max_results=3
     boxes, scores = (C.c_int * (5 * max_results))(), (C.c_float * max_results)()
     n = L.oracle_yolo11_postprocess(st, len(heads), score_thr, nms_thr, top_k, 1.0, 1.0, 0, 0, width, height, 0, max_results, boxes, scores)
     return [(boxes[5 * i], scores[i], tuple(boxes[5 * i + 1:5 * i + 5])) for i in range(n)]
+
+
+def reference_detect(heads, score_thr, nms_thr, top_k, width, height, inv_scale=(1.0, 1.0), border=(0, 0), max_results=300):
+    """The same call on the reference's own yolo11PostProcessor (oracle/_ref)."""
+    R = checkers.ref()
+    R.ref_yolo11_postprocess.restype = C.c_int
+    R.ref_yolo11_postprocess.argtypes = [C.POINTER(Stage), C.c_int, C.c_float, C.c_float, C.c_int, C.c_float, C.c_float, C.c_int, C.c_int,
+                                         C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_float)]
+    st = (Stage * len(heads))()
+    keep = []
+    for i, (s, b, es, eb, stride) in enumerate(heads):
+        s, b = np.ascontiguousarray(s), np.ascontiguousarray(b)
+        keep += [s, b]
+        st[i] = Stage(s.ctypes.data, b.ctypes.data, s.shape[0], s.shape[1], s.shape[2], es, eb, stride, stride, stride // 2, stride // 2)
+    boxes, scores = (C.c_int * (5 * max_results))(), (C.c_float * max_results)()
+    n = R.ref_yolo11_postprocess(st, len(heads), score_thr, nms_thr, top_k, inv_scale[0], inv_scale[1], border[0], border[1], width, height,
+                                 0, max_results, boxes, scores)
+    assert n >= 0
+    return [(boxes[5 * i], scores[i], tuple(boxes[5 * i + 1:5 * i + 5])) for i in range(n)]
+
+
+@pytest.mark.skipif(not checkers.have_ref(), reason="oracle/_ref/libespdl_ref.so not built")
+@pytest.mark.parametrize("seed,score_thr,nms_thr,top_k,hot", [(1, 0.5, 0.5, 100, 60), (2, 0.25, 0.7, 20, 200), (3, 0.6, 0.3, 5, 40), (4, 0.9, 0.45, 300, 400)])
+def test_oracle_post_processor_equals_the_reference(seed, score_thr, nms_thr, top_k, hot):
+    """Random heads of three strides with a few hundred scores above the threshold, overlapping boxes, equal scores
+    (the stable order of the sorted list matters) and boxes that leave the image: the restatement returns the
+    reference's list - categories, float scores bit for bit, boxes - for several thresholds and top-k limits."""
+    rng = np.random.default_rng(seed)
+    heads = []
+    for stride, hw in ((8, 20), (16, 10), (32, 5)):
+        score = rng.integers(-128, -40, size=(hw, hw, 7), dtype=np.int8)
+        idx = rng.integers(0, score.size, size=hot // 3)
+        score.reshape(-1)[idx] = rng.integers(-10, 90, size=idx.size).astype(np.int8) // 8 * 8      # many ties
+        box = rng.integers(-30, 100, size=(hw, hw, 64), dtype=np.int8)
+        heads.append((score, box, -4, -3, stride))
+    got = oracle_detect(heads, score_thr, nms_thr, top_k, 150, 140)
+    want = reference_detect(heads, score_thr, nms_thr, top_k, 150, 140)
+    assert len(want) > 3
+    assert [g[0] for g in got] == [w[0] for w in want]
+    assert [np.float32(g[1]).tobytes() for g in got] == [np.float32(w[1]).tobytes() for w in want]
+    assert [g[2] for g in got] == [w[2] for w in want]
 
 
 def test_oracle_keeps_the_best_box_of_a_cluster():

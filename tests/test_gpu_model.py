@@ -453,3 +453,21 @@ def test_yolo11n_640_at_the_benchmarked_batch(tmp_path):
     path = str(tmp_path / "yolo640.espdl")
     zoo.yolo11n_640(TOPOLOGY_640, seed=6).save(path)
     _full_size_parity(path, batch=512, picks=[0, 255, 510, 511], small_batch=2, windows=(2, 300), seed=62)
+
+
+def test_lut_folding_pass(tmp_path, monkeypatch):
+    """Swish tables behind dense convs whose input channels are a multiple of 16 are applied in the conv's epilogue (table
+    in shared memory): the nodes leave the plan, the outputs stay the oracle's, with the pass on and off."""
+    g = zoo.yolo11n_style(seed=6, input_hw=96)
+    m, want = run_and_compare(tmp_path, g, batch=2, seed=63, check_intermediates=False)
+    folded = [r[1] for r in m.profile()]
+    first = {o.name: np.array(o.array, copy=True) for o in m.outputs}
+    m.close()
+    monkeypatch.setenv("ESPDL_B200_FOLD_LUT", "0")
+    m, _ = run_and_compare(tmp_path, g, batch=2, seed=63, check_intermediates=False)
+    plain = [r[1] for r in m.profile()]
+    for o in m.outputs:
+        np.testing.assert_array_equal(o.array, first[o.name])
+    m.close()
+    assert plain.count("Swish") >= 50 and folded.count("Swish") <= plain.count("Swish") - 45, (plain.count("Swish"), folded.count("Swish"))
+    assert len(folded) == len(plain) - (plain.count("Swish") - folded.count("Swish"))

@@ -22,6 +22,22 @@ def table(channels, exponent, bits=8, mean=MEAN, std=STD):
     return t
 
 
+@pytest.mark.skipif(not checkers.have_ref(), reason="oracle/_ref/libespdl_ref.so not built")
+@pytest.mark.parametrize("bits", [8, 16])
+@pytest.mark.parametrize("exponent", [-7, -5, -4, 0, 2])
+@pytest.mark.parametrize("mean,std", [(MEAN, STD), ((0.0, 0.0, 0.0), (1.0, 1.0, 1.0)), ((127.5, 127.5, 127.5), (128.0, 64.0, 255.0))])
+def test_oracle_norm_quant_table_equals_the_reference(bits, exponent, mean, std):
+    """The normalise + quantise table against the reference's own NormQuant (vision/image/dl_image_norm_quant.hpp,
+    compiled into oracle/_ref): all 3 x 256 entries, int8 and int16, exponents on both sides of zero."""
+    R = checkers.ref()
+    R.ref_norm_quant_table.restype = C.c_int
+    R.ref_norm_quant_table.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_int, C.c_int]
+    want = np.zeros((3, 256), dtype=np.int8 if bits == 8 else np.int16)
+    assert R.ref_norm_quant_table(want.ctypes.data, (C.c_float * 3)(*mean), (C.c_float * 3)(*std), exponent, bits) == 0
+    np.testing.assert_array_equal(table(3, exponent, bits, mean, std), want)
+    assert exponent > 0 or want.std() > 0
+
+
 def letterbox(src_w, src_h, dst_w, dst_h):
     """dl_image_preprocessor.cpp:108-131"""
     sx, sy = np.float32(dst_w) / np.float32(src_w), np.float32(dst_h) / np.float32(src_h)
