@@ -236,13 +236,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int col0 = part * p.out_pw;
                 const uint32_t fpp = fp_base + (uint32_t)(n0 + col0) * 8u;
                 if (p.epi.lut) {
-                    const uint32_t tbl = smem_u32(lut_s);
-                    if (p.out_pw == 128)
-                        epilogue_stage<128, true>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q, tbl);
-                    else if (p.out_pw == 64)
-                        epilogue_stage<64, true>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q, tbl);
-                    else
-                        epilogue_stage<0, true>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q, tbl);
+                    epilogue_stage_lut(t0 + col0, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q, smem_u32(lut_s));
                 } else if (p.out_pw == 128)
                     epilogue_stage<128>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q);
                 else if (p.out_pw == 64)

@@ -234,9 +234,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        // The whole warp walks the tiles and waits (uniform control flow keeps addresses and counters in uniform
-        // registers); lane 0 alone issues the copies.
+        // One lane runs the loop and issues the copies.  (Letting the whole warp walk the tiles and wait, with lane 0
+        // issuing, measured the same on the network's short reductions and 25-35 % slower on the long reductions of a
+        // large Gemm, where the issue rate of this loop and of the MMA loop below is what bounds the kernel.)
         const bool issuer = lane == 0;
+        if (issuer) {
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -275,19 +277,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
             }
         }
-        if (issuer) {
-            if (!ok)
-                atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
-            TC_REC(0, w_empty);
-            TC_REC(1, w_load);
+        if (!ok)
+            atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+        TC_REC(0, w_empty);
+        TC_REC(1, w_load);
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        // As above: the warp runs the loop, lane 0 issues.  A tcgen05.mma takes its descriptors from uniform registers;
-        // computed by one lane of a diverged warp they have to be moved there one by one, which made each issue cost
-        // a few hundred cycles - more than the MMA itself for the short reductions of the network's layers.
+        // One lane runs the loop and issues (see the producer).  Each tcgen05.mma of M = 128 costs this thread about 250
+        // cycles whatever N is (measured with the role cycle counters: 4 MMAs per tile of K = 128 take ~1000 cycles), so
+        // tiles are made as wide as TMEM allows and carry as few K steps as the layer has.
         const bool issuer = lane == 0;
+        if (issuer) {
         int stage = 0;
         uint32_t phase = 0;
         int acc = 0;
@@ -363,12 +365,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 acc_phase ^= 1;
             }
         }
-        if (issuer) {
-            if (!ok)
-                atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
-            TC_REC(2, w_tempty);
-            TC_REC(3, w_full);
-            TC_REC(4, w_issue);
+        if (!ok)
+            atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
+        TC_REC(2, w_tempty);
+        TC_REC(3, w_full);
+        TC_REC(4, w_issue);
         }
         __syncwarp();
     } else {
@@ -421,13 +422,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t fpp = fp_base + (uint32_t)(n0 + col0) * 8u;
                     const int floor_q = p.epi.relu ? 0 : INT_MIN;
                     if (p.epi.lut) {
-                        const uint32_t tbl = smem_u32(lut_s);
-                        if (p.out_pw == 128)
-                            epilogue_stage<128, true>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q, tbl);
-                        else if (p.out_pw == 64)
-                            epilogue_stage<64, true>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q, tbl);
-                        else
-                            epilogue_stage<0, true>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q, tbl);
+                        epilogue_stage_lut(t0 + col0, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q, smem_u32(lut_s));
                     } else if (p.res)
                         epilogue_stage_residual(t0 + col0, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q,
                                                 p.res + m * p.rps + n0 + col0, row_ok, p.N - (n0 + col0));

@@ -418,8 +418,8 @@ __device__ __forceinline__ uint32_t lut4(uint32_t w, uint32_t tbl)
 // other widths): 16-byte chunk index XOR bits 7.. of the byte offset, which for these widths is a function of the
 // row alone.  PW is a template parameter so that the walk over the columns is straight-line code; PW = 0 is the
 // generic form for any width (`pw`).  TMEM is read 16 columns at a time into two register sets in turn.
-template <int PW, bool LUT = false>
-__device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, int floor_q, uint32_t tbl = 0)
+template <int PW>
+__device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, int floor_q)
 {
     const int width = PW ? PW : pw;
     uint32_t rx = 0; // what the chunk offset of this row is XORed with
@@ -443,10 +443,6 @@ __device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_
             ld16(t0 + c + 16, vb);
 #pragma unroll
         for (int q = 0; q < 4; q++) pk[q] = requant4_floor(va + 4 * q, fp + (uint32_t)(c + 4 * q) * 8u, floor_q);
-        if (LUT) {
-#pragma unroll
-            for (int q = 0; q < 4; q++) pk[q] = lut4(pk[q], tbl);
-        }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)c ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                      : "memory");
         if (!second)
@@ -457,12 +453,28 @@ __device__ __forceinline__ void epilogue_stage(uint32_t t0, uint32_t fp, uint32_
             ld16(t0 + c + 32, va);
 #pragma unroll
         for (int q = 0; q < 4; q++) pk[q] = requant4_floor(vb + 4 * q, fp + (uint32_t)(c + 16 + 4 * q) * 8u, floor_q);
-        if (LUT) {
-#pragma unroll
-            for (int q = 0; q < 4; q++) pk[q] = lut4(pk[q], tbl);
-        }
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)(c + 16) ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]),
                      "r"(pk[3])
+                     : "memory");
+    }
+}
+
+// Staged epilogue with a fused table: as epilogue_stage, any piece width (a multiple of 16, at most 128; `mask` = 7 / 3 / 0
+// is the swizzle of 128- / 64-byte / other rows), every packed word goes through lut4 before it is stored.  A compact
+// loop kept out of line: the kernels that call it carry none of its registers in their other epilogues.
+static __device__ __noinline__ void epilogue_stage_lut(uint32_t t0, uint32_t fp, uint32_t buf, int row, int pw, uint32_t mask, int floor_q, uint32_t tbl)
+{
+    const uint32_t rx = ((((uint32_t)(row * pw)) >> 7) & mask) << 4;
+    const uint32_t rb = buf + (uint32_t)(row * pw);
+#pragma unroll 1
+    for (int c = 0; c < pw; c += 16) {
+        int32_t v[16];
+        uint32_t pk[4];
+        ld16(t0 + c, v);
+        ld_wait16(v);
+#pragma unroll
+        for (int q = 0; q < 4; q++) pk[q] = lut4(requant4_floor(v + 4 * q, fp + (uint32_t)(c + 4 * q) * 8u, floor_q), tbl);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)c ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                      : "memory");
     }
 }
