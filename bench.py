@@ -384,6 +384,18 @@ def roofline_of(m, parsed, batch):
             for prod in parsed["nodes"]:
                 if prod["name"] in executed and prod["op_type"] == "Conv" and prod["outputs"][0] in node["inputs"]:
                     traffic[prod["name"]]["bytes"] += int(np.prod(shapes[node["outputs"][0]])) * batch
+    # a depthwise conv that the model fused into the pointwise conv behind it (one launch, named after the pointwise conv)
+    # has no launch of its own either: that launch reads the depthwise conv's input and filter instead of the tensor between
+    # the two, which never exists
+    for node in parsed["nodes"]:
+        if node["op_type"] == "Conv" and node["name"] not in executed and node["attrs"].get("group", 1) != 1:
+            for cons in parsed["nodes"]:
+                if cons["name"] in executed and cons["op_type"] == "Conv" and cons["inputs"][0] == node["outputs"][0]:
+                    hidden = int(np.prod(shapes[node["outputs"][0]])) * batch
+                    t = traffic[cons["name"]]
+                    t["bytes"] += traffic[node["name"]]["bytes"] - 2 * hidden
+                    t["macs"] += traffic[node["name"]]["macs"]
+                    t["kind"] = "depthwise_pointwise_fused"
     by_kind = {}
     for (idx, typ, us, name) in prof:
         tr = traffic[name]
@@ -398,7 +410,8 @@ def roofline_of(m, parsed, batch):
     peaks = measured_peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = dom["bytes"] / (dom["us"] * 1e-6) / 1e9
-    kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw3x3_tma_kernel", "conv_simt": "stem_tc_kernel"}
+    kernel_names = {"pointwise_tc": "gemm_tc_kernel", "depthwise": "dw3x3_tma_kernel", "conv_simt": "stem_tc_kernel",
+                    "depthwise_pointwise_fused": "dwpw_kernel"}
     # DRAM bytes moved per algorithmic byte, from one profiler capture of each kernel on a layer larger than L2
     # (profiles/): the launches of a step differ in shape, so the per-launch traffic is that ratio applied to
     # the average algorithmic bytes of a launch.

@@ -158,8 +158,9 @@ int espdl_b200_stream_sync(void *stream)
     const int dev_dw = read_and_clear_device_error_dw();
     const int dev_conv = read_and_clear_device_error_conv();
     const int dev_block = read_and_clear_device_error_block();
+    const int dev_dwpw = read_and_clear_device_error_dwpw();
     if (!dev)
-        dev = dev_stem ? dev_stem : (dev_conv ? dev_conv : (dev_block ? dev_block : dev_dw));
+        dev = dev_stem ? dev_stem : (dev_conv ? dev_conv : (dev_block ? dev_block : (dev_dw ? dev_dw : dev_dwpw)));
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -518,6 +519,13 @@ int espdl_b200_fused_block(const espdl_block_desc *desc, void *stream)
 {
     if (!desc)
         return ESPDL_ERR_INVALID_ARG;
+    if (!desc->input || !desc->output || !desc->dw_filter || !desc->project_filter || desc->n < 0)
+        return ESPDL_ERR_INVALID_ARG;
+    if (desc->n == 0)
+        return ESPDL_OK;
+    // a depthwise -> pointwise pair (no expand conv) has a kernel of its own
+    if (!desc->expand_filter && fused_dwpw_supported(*desc, false))
+        return fused_dwpw(*desc, (cudaStream_t)stream);
     return fused_block_tc(*desc, (cudaStream_t)stream);
 }
 
@@ -553,6 +561,8 @@ int espdl_b200_fused_block_supported(const espdl_block_desc *desc)
 {
     if (!desc)
         return ESPDL_ERR_INVALID_ARG;
+    if (desc->reserved[0] == 0 && fused_dwpw_supported(*desc, false))
+        return ESPDL_OK;
     return fused_block_supported(*desc) ? ESPDL_OK : ESPDL_ERR_UNSUPPORTED;
 }
 

@@ -39,12 +39,15 @@ int read_and_clear_device_error_stem();
 int read_and_clear_device_error_dw();
 int read_and_clear_device_error_conv();
 int read_and_clear_device_error_block();
+int read_and_clear_device_error_dwpw();
 int image_preprocess(const espdl_image_desc &d, cudaStream_t s);
 int detect_candidates(const espdl_detect_desc &d, cudaStream_t s);
 int reduce_op(const espdl_reduce_desc &d, cudaStream_t s);
 int pad_op(const espdl_pad_desc &d, cudaStream_t s);
 bool fused_block_supported(const espdl_block_desc &d);
 int fused_block_tc(const espdl_block_desc &d, cudaStream_t s);
+bool fused_dwpw_supported(const espdl_block_desc &d, bool has_expand); // depthwise -> pointwise pair without an expand conv
+int fused_dwpw(const espdl_block_desc &d, cudaStream_t s);
 bool conv2d_conv_tc_supported(const espdl_conv_desc &d);
 int conv2d_conv_tc(const espdl_conv_desc &d, cudaStream_t s);
 bool conv2d_dw_tma_supported(const espdl_conv_desc &d);

@@ -18,6 +18,7 @@
 //               memory (clipped at the image border, so ragged tiles need no code either).
 // Every mbarrier wait is bounded; a wait that expires records ESPDL_ERR_TIMEOUT, raises a CTA-wide flag that every role
 // reads at a point all of them pass, and the CTA leaves with its barriers matched.
+#include "dw_walk.cuh"
 #include "tc_common.cuh"
 
 #include <cmath>
@@ -44,6 +45,7 @@ int read_and_clear_device_error_dw()
 namespace {
 
 using namespace tc;
+using namespace dwt;
 
 constexpr int DWT_CONSUMER_WARPS = 16;
 constexpr int DWT_CONSUMERS = DWT_CONSUMER_WARPS * 32;
@@ -54,12 +56,9 @@ constexpr size_t DWT_SMEM_BUDGET = 200 * 1024;
 struct DwtParams {
     int S, CB, NB, TH, TW, IH, IW, L, nseg, nbands, items;
     int cblocks, nblocks, ytiles, xtiles, tiles_per_cb, total_tiles;
-    int C, pt, pl;
+    int pt, pl;
     int stage_bytes, out_bytes, tx_bytes; // patch stride in the ring, output tile size, bytes one patch load delivers
-    const int8_t *w;
-    const int32_t *bias, *ew;
-    const int8_t *lut;
-    int e_shift_base, ew_scalar, per_channel, relu, half_even;
+    DwtSource src;
 };
 
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3)
@@ -69,198 +68,11 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t sr
                  : "memory");
 }
 
-// Per-thread constants of the four channels a thread owns: the filter columns as dp4a operands, the accumulator start
-// values and the shifts.
-template <int S>
-struct DwtConsts {
-    uint32_t wv[3][4];   // (w[0][kx], w[1][kx], w[2][kx], 0) of channel i
-    uint32_t wv1[3][4];  // the same shifted to the band's next output row
-    uint32_t wsel[3][4]; // stride 2: w[2][kx] in the byte of its channel
-    int init[4], shift[4];
-    bool fast;
-};
-
-template <int S>
-__device__ __forceinline__ void dwt_load_consts(DwtConsts<S> &k, const DwtParams &p, int c0)
-{
-#pragma unroll
-    for (int kx = 0; kx < 3; kx++) {
-        uint32_t f[3];
-#pragma unroll
-        for (int ky = 0; ky < 3; ky++) f[ky] = __ldg((const uint32_t *)(p.w + (long long)(ky * 3 + kx) * p.C + c0));
-        const uint32_t lo0 = __byte_perm(f[0], f[1], 0x5140), hi0 = __byte_perm(f[0], f[1], 0x7362);
-        const uint32_t lo1 = __byte_perm(f[2], 0u, 0x5140), hi1 = __byte_perm(f[2], 0u, 0x7362);
-        k.wv[kx][0] = __byte_perm(lo0, lo1, 0x5410);
-        k.wv[kx][1] = __byte_perm(lo0, lo1, 0x7632);
-        k.wv[kx][2] = __byte_perm(hi0, hi1, 0x5410);
-        k.wv[kx][3] = __byte_perm(hi0, hi1, 0x7632);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            k.wv1[kx][i] = k.wv[kx][i] << (S == 1 ? 8 : 16);
-            k.wsel[kx][i] = S == 2 ? (f[2] & (0xffu << (8 * i))) : 0u;
-        }
-    }
-    k.fast = !p.half_even && !p.lut;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const int b = p.bias ? __ldg(p.bias + c0 + i) : 0;
-        const int e = p.per_channel ? __ldg(p.ew + c0 + i) : p.ew_scalar;
-        const int s = max(-31, min(31, p.e_shift_base - e));
-        // (acc + bias + 2^(s-1)) >> s is exact while nothing can overflow: |acc| <= 9 * 2^14, |bias| < 2^30, 1 <= s <= 24
-        k.fast = k.fast && s >= 1 && s <= 24 && b < (1 << 30) && b > -(1 << 30);
-        k.shift[i] = s - (p.relu ? 1 : 0); // what the walk shifts by (see dwt_emit); the general form recomputes its own
-        k.init[i] = b + (s >= 1 ? (1 << (s - 1)) : 0);
-    }
-}
-
-// Four (stride 1) or two (stride 2) vertically adjacent pixels per channel in one word, from the raw rows of a column.
-template <int S>
-struct DwtCol {
-    uint32_t t[S == 1 ? 2 : 1][4];
-    uint32_t extra; // stride 2: the fifth input row, untransposed
-};
-
-template <int S>
-__device__ __forceinline__ void dwt_transpose(DwtCol<S> &col, const uint32_t (&raw)[S == 1 ? 6 : 5])
-{
-    constexpr int PAIRS = S == 1 ? 3 : 2;
-    uint32_t lo[PAIRS], hi[PAIRS];
-#pragma unroll
-    for (int j = 0; j < PAIRS; j++) {
-        lo[j] = __byte_perm(raw[2 * j], raw[2 * j + 1], 0x5140);
-        hi[j] = __byte_perm(raw[2 * j], raw[2 * j + 1], 0x7362);
-    }
-#pragma unroll
-    for (int g = 0; g < (S == 1 ? 2 : 1); g++) {
-        col.t[g][0] = __byte_perm(lo[g], lo[g + 1], 0x5410);
-        col.t[g][1] = __byte_perm(lo[g], lo[g + 1], 0x7632);
-        col.t[g][2] = __byte_perm(hi[g], hi[g + 1], 0x5410);
-        col.t[g][3] = __byte_perm(hi[g], hi[g + 1], 0x7632);
-    }
-    col.extra = S == 2 ? raw[S == 2 ? 4 : 0] : 0u;
-}
-
-// One output column of a band (ROWS_OUT pixels x four channels) from three transposed input columns.
-template <int S>
-__device__ __forceinline__ void dwt_emit(const DwtConsts<S> &k, const DwtCol<S> &k0, const DwtCol<S> &k1, const DwtCol<S> &k2, uint32_t *op, int out_row_words,
-                                         int floor_q)
-{
-    constexpr int ROWS_OUT = S == 1 ? 4 : 2;
-    int acc[ROWS_OUT][4];
-#pragma unroll
-    for (int kx = 0; kx < 3; kx++) {
-        const DwtCol<S> &c = kx == 0 ? k0 : (kx == 1 ? k1 : k2);
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const uint32_t w = k.wv[kx][i], w1 = k.wv1[kx][i];
-            if constexpr (S == 1) {
-                acc[0][i] = __dp4a((int)c.t[0][i], (int)w, kx == 0 ? k.init[i] : acc[0][i]);
-                acc[1][i] = __dp4a((int)c.t[0][i], (int)w1, kx == 0 ? k.init[i] : acc[1][i]);
-                acc[2][i] = __dp4a((int)c.t[1][i], (int)w, kx == 0 ? k.init[i] : acc[2][i]);
-                acc[3][i] = __dp4a((int)c.t[1][i], (int)w1, kx == 0 ? k.init[i] : acc[3][i]);
-            } else {
-                acc[0][i] = __dp4a((int)c.t[0][i], (int)w, kx == 0 ? k.init[i] : acc[0][i]);
-                acc[1][i] = __dp4a((int)c.t[0][i], (int)w1, kx == 0 ? k.init[i] : acc[1][i]);
-                acc[1][i] = __dp4a((int)c.extra, (int)k.wsel[kx][i], acc[1][i]);
-            }
-        }
-    }
-    if (floor_q == 0) {
-        // ReLU: the staged shifts are one less than the real ones; packing with saturation to [0, 255] clamps below at
-        // zero, halving every byte completes the shift and turns the upper clamp into 127 - a shift and a mask per
-        // word instead of a max per output
-#pragma unroll
-        for (int ro = 0; ro < ROWS_OUT; ro++) {
-            const int q0 = acc[ro][0] >> k.shift[0], q1 = acc[ro][1] >> k.shift[1], q2 = acc[ro][2] >> k.shift[2], q3 = acc[ro][3] >> k.shift[3];
-            uint32_t hi, wd;
-            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
-            asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
-            op[ro * out_row_words] = (wd >> 1) & 0x7f7f7f7fu;
-        }
-    } else {
-#pragma unroll
-        for (int ro = 0; ro < ROWS_OUT; ro++) {
-            const int q0 = acc[ro][0] >> k.shift[0], q1 = acc[ro][1] >> k.shift[1], q2 = acc[ro][2] >> k.shift[2], q3 = acc[ro][3] >> k.shift[3];
-            uint32_t hi, wd;
-            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(q3), "r"(q2));
-            asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(wd) : "r"(q1), "r"(q0), "r"(hi));
-            op[ro * out_row_words] = wd;
-        }
-    }
-}
-
-// The run of one thread: L output columns of its band, four channels.  `ip` points at the thread's word in the
-// patch's first row and column of the run, `op` at its word in the output tile.  CB4 = channel-block width in words:
-// a template argument where the launch has one (column steps become immediate offsets), else `cb4`.
-template <int S, int CB4T>
-__device__ __forceinline__ void dwt_walk(const DwtConsts<S> &k, const uint32_t *ip, uint32_t *op, int in_row_words, int out_row_words, int cb4, int L, int floor_q)
-{
-    constexpr int ROWS_IN = S == 1 ? 6 : 5;
-    const int CB4 = CB4T ? CB4T : cb4;
-    const uint32_t *rp[ROWS_IN];
-#pragma unroll
-    for (int r = 0; r < ROWS_IN; r++) rp[r] = ip + r * in_row_words;
-    uint32_t raw[ROWS_IN];
-    auto load_col = [&](int j) {
-#pragma unroll
-        for (int r = 0; r < ROWS_IN; r++) raw[r] = rp[r][j * CB4];
-    };
-    auto advance = [&](int cols) {
-#pragma unroll
-        for (int r = 0; r < ROWS_IN; r++) rp[r] += cols * CB4;
-    };
-    DwtCol<S> ca, cb, cc;
-    if constexpr (S == 1) {
-        // output x reads input columns x + {0,1,2}: two columns prime the window, every step brings one in
-        load_col(0);
-        dwt_transpose<S>(ca, raw);
-        load_col(1);
-        dwt_transpose<S>(cb, raw);
-        load_col(2);
-        for (int x = 0; x < L; x += 3) {
-            dwt_transpose<S>(cc, raw);
-            load_col(3);
-            dwt_emit<S>(k, ca, cb, cc, op, out_row_words, floor_q);
-            if (x + 1 >= L)
-                break;
-            dwt_transpose<S>(ca, raw);
-            load_col(4);
-            dwt_emit<S>(k, cb, cc, ca, op + CB4, out_row_words, floor_q);
-            if (x + 2 >= L)
-                break;
-            dwt_transpose<S>(cb, raw);
-            load_col(5);
-            dwt_emit<S>(k, cc, ca, cb, op + 2 * CB4, out_row_words, floor_q);
-            advance(3);
-            op += 3 * CB4;
-        }
-    } else {
-        // output x reads input columns 2x + {0,1,2}; the last of them is the first of the next output
-        load_col(0);
-        dwt_transpose<S>(ca, raw);
-        for (int x = 0; x < L; x += 2) {
-            load_col(1);
-            dwt_transpose<S>(cb, raw);
-            load_col(2);
-            dwt_transpose<S>(cc, raw);
-            dwt_emit<S>(k, ca, cb, cc, op, out_row_words, floor_q);
-            if (x + 1 >= L)
-                break;
-            load_col(3);
-            dwt_transpose<S>(cb, raw);
-            load_col(4);
-            dwt_transpose<S>(ca, raw);
-            dwt_emit<S>(k, cc, cb, ca, op + CB4, out_row_words, floor_q);
-            advance(4);
-            op += 2 * CB4;
-        }
-    }
-}
-
 // The same run for channels outside the one-add-one-shift form (a shift outside 1..24, a huge bias, half-even rounding
 // or a fused table): plain loops over the patch with the general requantisation.
-__device__ __noinline__ void dwt_walk_general(const DwtParams &p, int S, const int8_t *ip, int8_t *op, int in_row_bytes, int out_row_bytes, int c0, int L)
+__device__ __noinline__ void dwt_walk_general(const DwtParams &pp, int S, const int8_t *ip, int8_t *op, int in_row_bytes, int out_row_bytes, int c0, int L)
 {
+    const DwtSource &p = pp.src;
     const int rows_out = S == 1 ? 4 : 2;
     for (int ro = 0; ro < rows_out; ro++)
         for (int x = 0; x < L; x++)
@@ -268,13 +80,13 @@ __device__ __noinline__ void dwt_walk_general(const DwtParams &p, int S, const i
                 int32_t acc = 0;
                 for (int ky = 0; ky < 3; ky++)
                     for (int kx = 0; kx < 3; kx++)
-                        acc += (int)ip[(ro * S + ky) * in_row_bytes + (x * S + kx) * p.CB + i] * (int)p.w[(ky * 3 + kx) * p.C + c0 + i];
+                        acc += (int)ip[(ro * S + ky) * in_row_bytes + (x * S + kx) * pp.CB + i] * (int)p.w[(ky * 3 + kx) * p.C + c0 + i];
                 const int e = p.per_channel ? p.ew[c0 + i] : p.ew_scalar;
                 const int shift = max(-31, min(31, p.e_shift_base - e));
                 int32_t v = requant8(acc, p.bias ? p.bias[c0 + i] : 0, shift, p.relu, p.half_even);
                 if (p.lut)
                     v = p.lut[(uint8_t)v ^ 0x80u];
-                op[ro * out_row_bytes + x * p.CB + i] = (int8_t)v;
+                op[ro * out_row_bytes + x * pp.CB + i] = (int8_t)v;
             }
 }
 
@@ -346,7 +158,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
     const int in_row_words = p.IW * W4, out_row_words = p.TW * W4;
     const int in_off = ((nb * p.IH + band * RB * S) * p.IW + seg * p.L * S) * W4 + cw;   // words from the patch
     const int out_off = ((nb * p.TH + band * RB) * p.TW + seg * p.L) * W4 + cw;          // words from the output tile
-    const int floor_q = p.relu ? 0 : INT_MIN;
+    const int floor_q = p.src.relu ? 0 : INT_MIN;
 
     DwtConsts<S> k;
     int have_cb = -1;
@@ -356,7 +168,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
     for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, local++) {
         while (t_in_cb >= p.tiles_per_cb) t_in_cb -= p.tiles_per_cb, cb++;
         if (cb != have_cb && active) {
-            dwt_load_consts<S>(k, p, cb * CB + cw * 4);
+            dwt_load_consts<S>(k, p.src, cb * CB + cw * 4);
             have_cb = cb;
         }
         if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
@@ -369,8 +181,12 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
         const uint32_t *patch = (const uint32_t *)(patch0 + (size_t)stage * p.stage_bytes);
         uint32_t *obuf = (uint32_t *)(out0 + (size_t)(local & 1) * p.out_bytes);
         if (active) {
-            if (k.fast)
-                dwt_walk<S, CBT / 4>(k, patch + in_off, obuf + out_off, in_row_words, out_row_words, W4, p.L, floor_q);
+            if (k.fast) {
+                uint32_t *op = obuf + out_off;
+                const int cb4 = CBT ? CBT / 4 : W4;
+                auto store = [=](int ro, int x, uint32_t word) { op[ro * out_row_words + x * cb4] = word; };
+                dwt_walk<S, CBT / 4>(k, patch + in_off, store, in_row_words, W4, p.L, floor_q);
+            }
             else
                 dwt_walk_general(p, S, (const int8_t *)(patch + in_off), (int8_t *)(obuf + out_off), in_row_words * 4, out_row_words * 4,
                                  cb * CB + cw * 4, p.L);
@@ -550,11 +366,12 @@ int conv2d_dw_tma(const espdl_conv_desc &d, cudaStream_t s)
     if (!enc)
         return set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c, ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
-    p.C = d.in_c, p.pt = d.pad_top, p.pl = d.pad_left;
-    p.w = (const int8_t *)d.filter, p.bias = (const int32_t *)d.bias, p.ew = d.filter_exponents, p.lut = d.lut;
-    p.e_shift_base = d.out_exponent - d.in_exponent;
-    p.ew_scalar = d.filter_exponent, p.per_channel = d.per_channel;
-    p.relu = d.activation == ESPDL_ACT_RELU, p.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
+    p.pt = d.pad_top, p.pl = d.pad_left;
+    p.src.C = d.in_c;
+    p.src.w = (const int8_t *)d.filter, p.src.bias = (const int32_t *)d.bias, p.src.ew = d.filter_exponents, p.src.lut = d.lut;
+    p.src.e_shift_base = d.out_exponent - d.in_exponent;
+    p.src.ew_scalar = d.filter_exponent, p.src.per_channel = d.per_channel;
+    p.src.relu = d.activation == ESPDL_ACT_RELU, p.src.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
     CUtensorMap mi, mo;
     {
         cuuint64_t dims[4] = {(cuuint64_t)d.in_c, (cuuint64_t)d.in_w, (cuuint64_t)d.in_h, (cuuint64_t)d.n};

@@ -434,15 +434,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         epilogue_stage<64>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q);
                     else
                         epilogue_stage<0>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q);
+                    // the accumulator is free as soon as this warp's TMEM loads are done: hand it back before the
+                    // shared-memory tile is completed and stored, so that the MMAs of the tile after next start earlier
                     fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(smem_u32(&tempty_bar[acc]));
                     fence_async_smem();
                     named_bar(2 + group, 128);
                     if (leader) {
                         tma_store_3d(&map_out, buf, n0 + col0, m0, bi); // rows >= M and columns >= N are clipped
                         bulk_commit();
                     }
-                    if (lane == 0)
-                        mbar_arrive(smem_u32(&tempty_bar[acc]));
                     continue;
                 }
                 epilogue_direct_tile(p, fast_s, fp_base, t0, m, n0, row_ok, fast && !p.epi.lut, parts, part);

@@ -27,15 +27,21 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// One probe of an mbarrier phase.  The suspend-time hint lets the hardware park the thread until the phase completes
+// (or the hint, in nanoseconds, runs out) instead of returning after the short system default: a waiting warp then
+// issues a handful of instructions per hand-over instead of spinning through the issue slots the working warps of its
+// scheduler need (a quarter of all instructions of the tile kernels were such spins).
+constexpr uint32_t WAIT_HINT_NS = 1000000u;
+
 __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
 {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(WAIT_HINT_NS)
         : "memory");
     return done;
 }

@@ -266,11 +266,14 @@ esp_err_t Model::load(fbs::FbsModel *fbs_model)
 // Block fusion: a depthwise 3x3 conv whose input comes from a pointwise conv (optional) and whose output feeds a
 // pointwise conv, optionally followed by a residual Add, becomes ONE FusedBlock module (espdl_b200_fused_block);
 // the tensors between the stages then never exist in the arena.  Only tensors with a single reader that are not
-// graph outputs may disappear.  Off unless ESPDL_B200_FUSE_BLOCKS=1: on the networks measured so far the separate
-// kernels are as fast, because all of them are bound by integer instruction issue rather than by memory.
+// graph outputs may disappear.  By default the depthwise -> pointwise pair (and a residual Add behind it) is fused - the
+// tensor between them, as large as the depthwise input, never reaches HBM - and the expand conv stays a launch of its
+// own (ESPDL_B200_FUSE_DWPW=0 keeps the pair apart); ESPDL_B200_FUSE_BLOCKS=1 also takes the expand conv into the
+// launch, which the measurements so far do not reward.
 void Model::fuse_blocks()
 {
-    if (!env_flag("ESPDL_B200_FUSE_BLOCKS", false) || !m_reuse_memory)
+    const bool whole_blocks = env_flag("ESPDL_B200_FUSE_BLOCKS", false);
+    if ((!whole_blocks && !env_flag("ESPDL_B200_FUSE_DWPW", false)) || !m_reuse_memory)
         return;
     ModelContext *ctx = m_model_context;
     std::vector<std::string> graph_outputs = m_fbs_model->get_graph_outputs();
@@ -310,7 +313,7 @@ void Model::fuse_blocks()
             continue;
         int E = producer(y1);
         module::Conv *expand = nullptr;
-        if (E >= 0 && E < (int)s && m_module_types[E] == "Conv" && private_tensor(y1) && m_module_outputs[E].size() == 1) {
+        if (whole_blocks && E >= 0 && E < (int)s && m_module_types[E] == "Conv" && private_tensor(y1) && m_module_outputs[E].size() == 1) {
             expand = dynamic_cast<module::Conv *>(m_execution_plan[E]);
             if (expand && (!expand->is_pointwise() || m_module_inputs[E].size() < 2 ||
                            !module::Conv::filter_is_1x1(ctx->get_tensor(m_module_inputs[E][1]))))

@@ -58,3 +58,44 @@ def test_block_general_requantisation(round_mode):
 def test_block_rejects_what_it_cannot_run():
     case = cases.block_case(seed=8, n=1, h=8, w=8, cin=24, chid=144, cout=24)  # Cin not a multiple of 16
     gpu_util.run_block_gpu(case, expect=abi.ERR_UNSUPPORTED)
+
+
+# depthwise -> pointwise pairs (no expand conv): (h, w, hidden, cout, stride)
+PAIRS = [
+    (112, 112, 96, 24, 2),      # the network's largest pair: stride 2, 24 output channels (rows of 24 bytes)
+    (56, 56, 144, 24, 1),       # residual, channel block 48 (64-byte operand rows, 16 of them padding)
+    (56, 56, 144, 32, 2),
+    (28, 28, 192, 32, 1),       # residual
+    (28, 28, 192, 64, 2),
+    (14, 14, 384, 64, 1),
+    (14, 14, 384, 96, 1),
+    (14, 14, 576, 96, 1),
+    (14, 14, 576, 160, 2),      # 14 -> 7
+    (7, 7, 960, 160, 1),        # several images per tile
+    (112, 112, 32, 16, 1),      # 32-byte operand rows
+    (33, 45, 64, 40, 1),        # ragged tiles, output channels that are no multiple of 16
+    (15, 17, 16, 8, 2),
+    (9, 9, 128, 250, 1),        # a wide pointwise conv
+]
+
+
+@pytest.mark.parametrize("shape", PAIRS, ids=lambda s: "x".join(str(v) for v in s))
+def test_depthwise_pointwise_pair_matches_node_chain(shape):
+    """The fused depthwise -> pointwise kernel (the depthwise result goes from registers into the tensor cores' operand in
+    shared memory) against the oracle's two nodes (+ Add where the block has a residual), bit for bit."""
+    h, w, chid, cout, stride = shape
+    case = cases.block_case(seed=11, n=3, h=h, w=w, cin=chid, chid=chid, cout=cout, stride=stride, expand=False)
+    got = gpu_util.run_block_gpu(case)
+    want = gpu_util.run_block_oracle(case)
+    assert want.std() > 2
+    np.testing.assert_array_equal(got, want)
+
+
+def test_depthwise_pointwise_pair_many_tiles_and_general_requantisation():
+    case = cases.block_case(seed=12, n=70, h=28, w=28, cin=192, chid=192, cout=32, expand=False)   # more tiles than CTAs
+    np.testing.assert_array_equal(gpu_util.run_block_gpu(case), gpu_util.run_block_oracle(case))
+    # per-tensor exponents, and depthwise shifts outside 1..24 (the plain-loop form of the depthwise warps)
+    case = cases.block_case(seed=13, n=2, h=14, w=14, cin=96, chid=96, cout=24, expand=False, per_channel=False)
+    np.testing.assert_array_equal(gpu_util.run_block_gpu(case), gpu_util.run_block_oracle(case))
+    case = cases.block_case(seed=14, n=2, h=10, w=10, cin=32, chid=32, cout=16, expand=False, e=(-5, -5, -14, -5))
+    np.testing.assert_array_equal(gpu_util.run_block_gpu(case), gpu_util.run_block_oracle(case))

@@ -266,8 +266,8 @@ def test_profile_lists_every_module(tmp_path):
     zoo.inverted_residual_block(seed=4, hw=28).save(path)
     m = model.Model(path, batch=2)
     rows = m.profile()
-    # the residual Add is folded into the project conv when buffers are planned for reuse
-    assert [r[1] for r in rows] == ["Conv", "Conv", "Conv"] and all(r[2] > 0 for r in rows)
+    # with buffers planned for reuse the depthwise conv, the project conv and the residual Add are one launch
+    assert [r[1] for r in rows] == ["Conv", "FusedBlock"] and all(r[2] > 0 for r in rows)
     m.close()
     m = model.Model(path, batch=2, reuse=False)
     assert [r[1] for r in m.profile()] == ["Conv", "Conv", "Conv", "Add"]
