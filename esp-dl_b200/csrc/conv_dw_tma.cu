@@ -58,6 +58,8 @@ struct DwtParams {
     int cblocks, nblocks, ytiles, xtiles, tiles_per_cb, total_tiles;
     int pt, pl;
     int stage_bytes, out_bytes, tx_bytes; // patch stride in the ring, output tile size, bytes one patch load delivers
+    long long wait_limit;                 // cycles a wait may take (WAIT_LIMIT_CYCLES; shorter only in the expiry test)
+    int withhold_arrive;                  // expiry test: consumer warp 0 never reports a patch as read, so the producer's wait runs out
     DwtSource src;
 };
 
@@ -124,7 +126,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
             while (t_in_cb >= p.tiles_per_cb) t_in_cb -= p.tiles_per_cb, cb++;
             if (*abort_flag)
                 break;
-            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
+            if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, p.wait_limit)) {
                 *abort_flag = 1;
                 if (lane == 0)
                     atomicExch(&g_dwt_error, ESPDL_ERR_TIMEOUT);
@@ -171,7 +173,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
             dwt_load_consts<S>(k, p.src, cb * CB + cw * 4);
             have_cb = cb;
         }
-        if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+        if (!mbar_wait(smem_u32(&full_bar[stage]), phase, p.wait_limit)) {
             // the patch never came: note it and carry on with whatever the buffer holds, so that every thread still
             // reaches the barrier below, where all of them see the flag and leave together
             *abort_flag = 1;
@@ -192,7 +194,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
                                  cb * CB + cw * 4, p.L);
         }
         __syncwarp();
-        if (lane == 0)
+        if (lane == 0 && !(p.withhold_arrive && warp == 0))
             mbar_arrive(smem_u32(&empty_bar[stage])); // this warp has read the patch
         fence_async_smem();                           // the output words are visible to the TMA unit
         if (tid == 0)
@@ -367,6 +369,12 @@ int conv2d_dw_tma(const espdl_conv_desc &d, cudaStream_t s)
         return set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c, ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
     p.pt = d.pad_top, p.pl = d.pad_left;
+    // ESPDL_B200_DEBUG_WAIT_EXPIRY=<milliseconds>: the test of the bounded waits.  One arrival is withheld and the limit is
+    // that short, so the producer's wait runs out, the CTA raises its flag and every role leaves; espdl_b200_stream_sync
+    // then reports ESPDL_ERR_TIMEOUT.  Nothing traps, nothing waits without a limit.
+    const char *expiry = getenv("ESPDL_B200_DEBUG_WAIT_EXPIRY");
+    p.withhold_arrive = expiry && atoi(expiry) > 0 ? 1 : 0;
+    p.wait_limit = p.withhold_arrive ? (long long)atoi(expiry) * 2000000ll : WAIT_LIMIT_CYCLES;
     p.src.C = d.in_c;
     p.src.w = (const int8_t *)d.filter, p.src.bias = (const int32_t *)d.bias, p.src.ew = d.filter_exponents, p.src.lut = d.lut;
     p.src.e_shift_base = d.out_exponent - d.in_exponent;

@@ -243,13 +243,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     epilogue_stage<64>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q);
                 else
                     epilogue_stage<0>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q);
+                // the accumulator is free once this warp's TMEM loads are done: hand it back before the tile is stored
                 fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(smem_u32(&tempty_bar[acc]));
                 fence_async_smem();
                 named_bar(2 + group, 128);
                 if (leader) {
                     tma_store_4d(&map_out, buf, n0 + col0, xt * p.P, yt * p.R, img); // clipped at the image border and at Cout
                     bulk_commit();
                 }
+                continue;
             } else {
                 // direct rows: any rounding mode, any shift, optional LUT, any alignment
                 const int oy = yt * p.R + ry, ox = xt * p.P + rx;

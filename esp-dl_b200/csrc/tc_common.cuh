@@ -51,17 +51,20 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
 // every hand-over of the pipeline); WAIT_LIMIT_CYCLES is about two seconds at the lowest clocks the part runs at.
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit_cycles = WAIT_LIMIT_CYCLES)
 {
     if (mbar_try(bar, parity))
         return true;
     const long long t0 = clock64();
     while (true) {
 #pragma unroll 1
-        for (int spin = 0; spin < 256; spin++)
+        for (int spin = 0; spin < 256; spin++) {
             if (mbar_try(bar, parity))
                 return true;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES)
+            if (limit_cycles < WAIT_LIMIT_CYCLES && clock64() - t0 > limit_cycles) // a short, test-only limit: check every probe
+                return false;
+        }
+        if (clock64() - t0 > limit_cycles)
             return false;
     }
 }

@@ -951,6 +951,23 @@ void Model::profile_memory()
            m_model_context->workspace_bytes / 1048576.0);
 }
 
+void Model::minimize()
+{
+    if (!m_model_context)
+        return;
+    for (TensorBase *t : m_model_context->m_variables) {
+        // parameters that live on the device: the kernels read that copy; operands of a few bytes (Clip bounds, Resize
+        // scales, Mul scalars) are read on the host at every forward and stay
+        if (t && t->device && t->device_owned && t->data && t->auto_free && t->get_aligned_bytes() > 256) {
+            free(t->data);
+            t->data = nullptr;
+        }
+    }
+    if (m_fbs_model)
+        m_fbs_model->clear_map();
+    module::ModuleCreator::get_instance()->clear();
+}
+
 void Model::profile(bool sort_module_by_latency)
 {
     profile_memory();

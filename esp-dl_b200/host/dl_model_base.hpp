@@ -100,7 +100,10 @@ public:
     std::string get_metadata_prop(const std::string &key);
     virtual void print();
     virtual void reset();
-    void minimize() {}
+    /// Releases what inference does not need (reference: dl_model_base.cpp:431-440): the host copies of parameters that
+    /// are resident on the device (filters, biases, tables; small operands that modules read on the host are kept), the
+    /// FlatBuffers name maps and the module registry.  Model::test() and graph inspection no longer work afterwards.
+    void minimize();
     virtual fbs::FbsModel *get_fbs_model() { return m_fbs_model; }
 
     // backend knobs (set before build / the constructor reads the environment for defaults)

@@ -130,6 +130,9 @@ const char *espdl_registered_ops(void)
 /// dl::Model::reset(): clears the state modules keep between runs (the StreamingCache frames).
 void espdl_model_reset(void *handle) { ((Handle *)handle)->model->reset(); }
 
+/// dl::Model::minimize(): frees the host copies of device-resident parameters, the name maps and the module registry.
+void espdl_model_minimize(void *handle) { ((Handle *)handle)->model->minimize(); }
+
 int espdl_model_test(void *handle) { return ((Handle *)handle)->model->test(); }
 
 void *espdl_model_stream(void *handle) { return ((Handle *)handle)->model->stream(); }

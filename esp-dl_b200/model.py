@@ -88,6 +88,13 @@ class Model:
         self.lib.espdl_model_reset.argtypes = [C.c_void_p]
         self.lib.espdl_model_reset(self.h)
 
+    def minimize(self):
+        """dl::Model::minimize(): releases what inference does not need (host copies of the parameters that are resident
+        on the device, name maps, module registry).  test() is no longer possible afterwards."""
+        self.lib.espdl_model_minimize.restype = None
+        self.lib.espdl_model_minimize.argtypes = [C.c_void_p]
+        self.lib.espdl_model_minimize(self.h)
+
     def submit(self):
         """Pipelined run(): uploads the input arrays (they may be refilled when this returns) and enqueues the pass."""
         abi.check(self.lib.espdl_model_submit(self.h), "Model::submit")

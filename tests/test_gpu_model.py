@@ -266,12 +266,34 @@ def test_profile_lists_every_module(tmp_path):
     zoo.inverted_residual_block(seed=4, hw=28).save(path)
     m = model.Model(path, batch=2)
     rows = m.profile()
-    # with buffers planned for reuse the depthwise conv, the project conv and the residual Add are one launch
-    assert [r[1] for r in rows] == ["Conv", "FusedBlock"] and all(r[2] > 0 for r in rows)
+    # with buffers planned for reuse the residual Add is folded into the project conv's epilogue
+    assert [r[1] for r in rows] == ["Conv", "Conv", "Conv"] and all(r[2] > 0 for r in rows)
     m.close()
     m = model.Model(path, batch=2, reuse=False)
     assert [r[1] for r in m.profile()] == ["Conv", "Conv", "Conv", "Add"]
     m.close()
+
+
+def test_minimize_keeps_inference_working(tmp_path):
+    """dl::Model::minimize() (dl_model_base.cpp:431-440 of the reference): the host copies of the device-resident
+    parameters go, results stay the same, and a model created afterwards finds the operator registry again."""
+    path = str(tmp_path / "net.espdl")
+    zoo.mobilenet_v2(seed=9, input_hw=64, num_classes=16).save(path)
+    m = model.Model(path, batch=3)
+    rng = np.random.default_rng(5)
+    m.inputs[0].array[...] = rng.integers(-128, 128, m.inputs[0].array.shape, dtype=np.int8)
+    m.run()
+    before = m.outputs[0].array.copy()
+    m.minimize()
+    m.outputs[0].array[...] = 0
+    m.run()
+    np.testing.assert_array_equal(m.outputs[0].array, before)
+    m2 = model.Model(path, batch=3)
+    m2.inputs[0].array[...] = m.inputs[0].array
+    m2.run()
+    np.testing.assert_array_equal(m2.outputs[0].array, before)
+    m.close()
+    m2.close()
 
 
 def test_unsupported_operator_fails_to_load(tmp_path):

@@ -372,3 +372,26 @@ def test_invalid_arguments_are_rejected():
         empty = cases.conv_desc(dict(case, n=0), ptrs)
         assert L.espdl_b200_conv2d(C.byref(empty), None) == abi.OK  # empty batch: nothing to do
     assert b"invalid" in L.espdl_b200_strerror(abi.ERR_INVALID_ARG)
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_works(monkeypatch):
+    """Every mbarrier wait of the persistent kernels has a limit.  With ESPDL_B200_DEBUG_WAIT_EXPIRY the TMA-fed depthwise
+    kernel withholds one arrival and shortens the limit to a few milliseconds: the wait runs out, the CTA raises its flag,
+    every role leaves (nothing traps, nothing spins on), espdl_b200_stream_sync reports ESPDL_ERR_TIMEOUT - and the same
+    launch without the switch gives the oracle's result on the same context."""
+    import ctypes as C
+    case = cases.conv_case(seed=71, n=96, h=56, w=56, cin=64, kh=3, kw=3, depthwise=True, per_channel=True, e_in=-5, e_out=-5, e_w=(-9, -5))
+    want = gpu_util.run_conv_oracle(case)
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input=dev.upload(case["x"]), filter=dev.upload(case["w"]), bias=dev.upload(case["b"]),
+                    filter_exponents=dev.upload(case["ew"]), lut=None, residual=None, output=dev.upload(np.full_like(case["out"], 0x55)))
+        d = cases.conv_desc(case, ptrs)
+        monkeypatch.setenv("ESPDL_B200_DEBUG_WAIT_EXPIRY", "5")
+        assert dev.lib.espdl_b200_conv2d(C.byref(d), None) == abi.OK          # the launch itself succeeds
+        assert dev.lib.espdl_b200_stream_sync(None) == abi.ERR_TIMEOUT        # ... and reports that a wait expired
+        assert b"wait expired" in dev.lib.espdl_b200_last_error()
+        assert dev.lib.espdl_b200_stream_sync(None) == abi.OK                 # the status word was cleared by the read
+        monkeypatch.delenv("ESPDL_B200_DEBUG_WAIT_EXPIRY")
+        assert dev.lib.espdl_b200_conv2d(C.byref(d), None) == abi.OK
+        got = dev.download(ptrs["output"], case["out"])
+    np.testing.assert_array_equal(got, want)
