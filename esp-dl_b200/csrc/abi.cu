@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 namespace espdl {
 
@@ -35,6 +36,45 @@ int set_error_text(int status, const char *fmt, ...)
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
 int num_sms() { return g_num_sms > 0 ? g_num_sms : 148; }
+
+namespace {
+constexpr int SCHED_PAIRS = 2048;
+__device__ unsigned g_sched_words[2 * SCHED_PAIRS]; // zero at load; every kernel leaves its pair zero
+}
+
+unsigned *sched_counters(cudaStream_t s)
+{
+    static std::mutex mu;
+    static std::unordered_map<unsigned long long, int> pair_of; // stream handle / capture id -> pair
+    static unsigned *base = nullptr;
+    static const bool off = getenv("ESPDL_B200_STATIC_TILES") != nullptr;
+    if (off)
+        return nullptr;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    unsigned long long id = 0;
+    if (cudaStreamGetCaptureInfo(s, &cs, &id) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    // keys: capture ids count up from 1 and stay far below 2^48; stream handles are pointers (or the small legacy values)
+    const unsigned long long key = cs == cudaStreamCaptureStatusActive ? (id | (1ull << 63)) : (unsigned long long)(uintptr_t)s;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!base) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_sched_words) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        base = (unsigned *)p;
+    }
+    auto it = pair_of.find(key);
+    if (it == pair_of.end()) {
+        if ((int)pair_of.size() >= SCHED_PAIRS)
+            return nullptr;
+        it = pair_of.emplace(key, (int)pair_of.size()).first;
+    }
+    return base + 2 * it->second;
+}
 
 int check_launch(const char *what)
 {

@@ -14,6 +14,12 @@ int set_cuda_error(cudaError_t e, const char *what); // records text, returns ES
 int set_error_text(int status, const char *fmt, ...); // records text for espdl_b200_last_error, returns status
 void count_launch(int n = 1);
 int num_sms();
+// Work counters of a persistent kernel that hands out its tiles dynamically: two zero-initialised words {next tile,
+// CTAs done} in device memory that no other launch in flight uses - one pair per stream, or per capture sequence while
+// `s` is being captured into a graph (launches of one stream, and the nodes of one graph, run one after the other; two
+// graphs may run side by side).  The kernel's last CTA writes both words back to zero.  Null when no pair is left: the
+// kernel then walks its tiles in the fixed order.
+unsigned *sched_counters(cudaStream_t s);
 // Records the most recent failed launch (cudaGetLastError) if any.
 int check_launch(const char *what);
 

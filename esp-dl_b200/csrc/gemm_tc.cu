@@ -57,7 +57,11 @@ __device__ long long g_tc_timing[256 * 8];
 #define TC_LAP_INIT long long t_ = clock64()
 #define TC_LAP(var) do { const long long n_ = clock64(); (var) += n_ - t_; t_ = n_; } while (0)
 #define TC_REC(slot, var) g_tc_timing[blockIdx.x * 8 + (slot)] = (var)
+__device__ long long g_tc_clock[256 * 4]; // per CTA: clock64 and globaltimer at entry and at exit
+#define TC_STAMP(i) do { if (threadIdx.x == 0) { unsigned long long g_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_)); \
+    g_tc_clock[blockIdx.x * 4 + 2 * (i)] = clock64(); g_tc_clock[blockIdx.x * 4 + 2 * (i) + 1] = (long long)g_; } } while (0)
 #else
+#define TC_STAMP(i)
 #define TC_LAP_INIT
 #define TC_LAP(var)
 #define TC_REC(slot, var)
@@ -90,8 +94,12 @@ struct TcParams {
     long long rps;     // residual row stride in elements
     long long peer_delta[7]; // byte distance from `out` to the same buffer on other GPUs: every result row is stored there too
     int n_peer;
+    unsigned *sched; // {next tile, CTAs done}: the tiles from static_tiles on are handed out by this counter; null = fixed walk
+    int static_tiles; // tiles walked in the fixed order (a multiple of the grid size; all of them without a counter)
     EpiConfig epi;
 };
+
+constexpr int TILE_RING = 32; // tile numbers on their way from the producer to the MMA issuer (more than stages + accumulators)
 
 // Epilogue of one int8 tile for outputs that cannot go through the staged path (piece widths that are not whole
 // 16-byte groups, unaligned rows, channels outside the fast form): rows are stored directly from registers.  Out of
@@ -194,14 +202,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint32_t *tmem_slot = (uint32_t *)(tempty_bar + MAX_ACC);
     int *slow_flag = (int *)(tmem_slot + 1);
     uint8_t *lut_s = (uint8_t *)(slow_flag + 3); // the fused 8-bit table, 256 bytes, 16-byte aligned
+    volatile int *tile_ring = (volatile int *)(lut_s + 256); // TILE_RING tile numbers, producer -> MMA issuer
+    volatile int *epi_tile = tile_ring + TILE_RING;          // MAX_ACC tile numbers, MMA issuer -> the accumulator's epilogue groups
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    TC_STAMP(0);
     const int total_tiles = p.batch * p.m_tiles * p.n_tiles;
     const int parts = 4 / p.acc_stages; // epilogue groups that share one tile (they split its columns)
-    // Tiles are numbered n-fastest: tile = row_tile * n_tiles + n_tile with row_tile running over batch x m_tiles.  Each
-    // role walks its tiles (blockIdx.x, + gridDim.x, ...) with two counters instead of a division per tile.
-    const int step_rows = (int)gridDim.x / p.n_tiles, step_n = (int)gridDim.x % p.n_tiles;
-    const int first_rows = (int)blockIdx.x / p.n_tiles, first_n = (int)blockIdx.x % p.n_tiles;
+    // Tiles are numbered n-fastest: tile = row_tile * n_tiles + n_tile with row_tile running over batch x m_tiles.  A CTA
+    // starts with tile blockIdx.x; every further tile comes from a global counter (p.sched), so that an SM that runs
+    // slower than the others (measured: one in ten takes 15-25 % longer per tile) gets fewer tiles instead of setting
+    // the kernel's duration.  The producer fetches the numbers and passes them on through shared memory: to the MMA
+    // issuer in a ring (published by the arrive on the first stage's "full" barrier), from there to the epilogue groups
+    // (published by a plain arrive on the accumulator's "full" barrier, which therefore counts two arrivals: that one
+    // and the tensor cores' commit).  A negative number ends the walk.
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
@@ -209,7 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (int a = 0; a < MAX_ACC; a++) {
-            mbar_init(smem_u32(&tfull_bar[a]), 1);
+            mbar_init(smem_u32(&tfull_bar[a]), 2);
             mbar_init(smem_u32(&tempty_bar[a]), 4 * parts);
         }
         *slow_flag = 0;
@@ -242,17 +256,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        int rows = first_rows, nt = first_n;
         long long w_empty = 0, w_load = 0;
         (void)w_empty, (void)w_load;
         TC_LAP_INIT;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        // Tiles below p.static_tiles are walked in the fixed order (blockIdx.x, + gridDim.x, ...); the rest is handed out
+        // by the counter, one number per tile and asked for one tile ahead (an atomic on a word that every SM hammers
+        // takes ~1000 cycles to answer: with every tile handed out that way the producer no longer ran ahead)
+        int tile = blockIdx.x; // the grid never has more CTAs than there are tiles
+        bool handed = false;
+        auto after = [&](int cur) {
+            if (!handed && cur + (int)gridDim.x < p.static_tiles)
+                return cur + (int)gridDim.x;
+            if (!p.sched)
+                return handed || cur + (int)gridDim.x >= total_tiles ? total_tiles : cur + (int)gridDim.x;
+            handed = true;
+            return p.static_tiles + (int)atomicAdd(p.sched, 1u);
+        };
+        int next = after(tile);
+        int local = 0;
+        for (; tile < total_tiles && ok; local++) {
+            tile_ring[local & (TILE_RING - 1)] = tile;
+            const int rows = tile / p.n_tiles, nt = tile - rows * p.n_tiles;
             const int bi = p.batch == 1 ? 0 : rows / p.m_tiles;
             const int m0 = (p.batch == 1 ? rows : rows % p.m_tiles) * BLOCK_M;
             const int n0 = nt * p.block_n;
-            rows += step_rows, nt += step_n;
-            if (nt >= p.n_tiles)
-                nt -= p.n_tiles, rows++;
             for (int kb = 0; kb < p.k_blocks; kb++) {
                 TC_LAP(w_load);
                 if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
@@ -262,20 +289,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 TC_LAP(w_empty);
                 const uint32_t bar = smem_u32(&full_bar[stage]);
                 const uint32_t st = smem_u32(smem) + (uint32_t)(stage * stage_bytes);
-                if (issuer) {
-                    mbar_arrive_expect_tx(bar, (uint32_t)stage_bytes);
-                    tma_load_3d(st, &map_a, kb * p.swz, m0, bi, bar);
-                    tma_load_3d(st + NPLANE * a_bytes, &map_b, kb * p.swz, n0, bi, bar);
-                    if (I16) {
-                        tma_load_3d(st + a_bytes, &map_a_lo, kb * p.swz, m0, bi, bar);
-                        tma_load_3d(st + 2 * a_bytes + b_bytes, &map_b_lo, kb * p.swz, n0, bi, bar);
-                    }
+                mbar_arrive_expect_tx(bar, (uint32_t)stage_bytes);
+                tma_load_3d(st, &map_a, kb * p.swz, m0, bi, bar);
+                tma_load_3d(st + NPLANE * a_bytes, &map_b, kb * p.swz, n0, bi, bar);
+                if (I16) {
+                    tma_load_3d(st + a_bytes, &map_a_lo, kb * p.swz, m0, bi, bar);
+                    tma_load_3d(st + 2 * a_bytes + b_bytes, &map_b_lo, kb * p.swz, n0, bi, bar);
                 }
                 if (++stage == p.stages) {
                     stage = 0;
                     phase ^= 1;
                 }
             }
+            // the number after next is asked for one tile ahead of its use: the answer is back long before it is needed
+            tile = next;
+            if (tile < total_tiles)
+                next = after(tile);
+        }
+        if (ok) {
+            // end of the walk: one stage without data whose ring entry is negative
+            tile_ring[local & (TILE_RING - 1)] = -1;
+            if (mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1))
+                mbar_arrive(smem_u32(&full_bar[stage]));
+            else
+                ok = false;
         }
         if (!ok)
             atomicExch(&g_tc_error, ESPDL_ERR_TIMEOUT);
@@ -304,18 +341,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t idesc_uu = idesc_i8(0, 0, BLOCK_M, p.block_n);
         const int ksteps = p.swz / 32;
         const uint32_t smem_base = smem_u32(smem);
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int local = 0; ok; local++) {
             TC_LAP(w_issue);
+            // the tile's first stage: its arrival publishes the tile number
+            if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+                ok = false;
+                break;
+            }
+            TC_LAP(w_full);
+            const int tile = tile_ring[local & (TILE_RING - 1)];
+            if (tile < 0) {
+                // end of the walk: every accumulator's epilogue groups are told, in the order they wait
+                for (int a = 0; a < p.acc_stages && ok; a++) {
+                    if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1)) {
+                        ok = false;
+                        break;
+                    }
+                    epi_tile[acc] = -1;
+                    mbar_arrive(smem_u32(&tfull_bar[acc]));
+                    mbar_arrive(smem_u32(&tfull_bar[acc]));
+                    if (++acc == p.acc_stages) {
+                        acc = 0;
+                        acc_phase ^= 1;
+                    }
+                }
+                break;
+            }
             if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1)) {
                 ok = false;
                 break;
             }
             TC_LAP(w_tempty);
             fence_after();
+            epi_tile[acc] = tile;
             const uint32_t d0 = tmem_base + (uint32_t)(acc * NACC * p.block_n);
             for (int kb = 0; kb < p.k_blocks; kb++) {
                 TC_LAP(w_issue);
-                if (!mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+                if (kb != 0 && !mbar_wait(smem_u32(&full_bar[stage]), phase)) {
                     ok = false;
                     break;
                 }
@@ -326,30 +388,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint64_t db = smem_desc_swizzled(st + NPLANE * a_bytes, p.swz);
                 if (!I16) {
                     const uint32_t first = kb != 0 ? 1u : 0u;
-                    if (issuer) {
-                        mma_i8(d0, da, db, idesc_ss, first);
-                        if (ksteps > 1)
-                            mma_i8(d0, da + 2, db + 2, idesc_ss, 1u);
-                        if (ksteps > 2) {
-                            mma_i8(d0, da + 4, db + 4, idesc_ss, 1u);
-                            mma_i8(d0, da + 6, db + 6, idesc_ss, 1u);
-                        }
-                        commit(smem_u32(&empty_bar[stage]));
+                    mma_i8(d0, da, db, idesc_ss, first);
+                    if (ksteps > 1)
+                        mma_i8(d0, da + 2, db + 2, idesc_ss, 1u);
+                    if (ksteps > 2) {
+                        mma_i8(d0, da + 4, db + 4, idesc_ss, 1u);
+                        mma_i8(d0, da + 6, db + 6, idesc_ss, 1u);
                     }
+                    commit(smem_u32(&empty_bar[stage]));
                 } else {
                     const uint64_t da_lo = smem_desc_swizzled(st + a_bytes, p.swz);
                     const uint64_t db_lo = smem_desc_swizzled(st + 2 * a_bytes + b_bytes, p.swz);
-                    if (issuer) {
-                        for (int k = 0; k < ksteps; k++) {
-                            const uint32_t accum = (kb | k) != 0;
-                            const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K, in 16-byte units
-                            mma_i8(d0, da + koff, db + koff, idesc_ss, accum);                      // hi * hi
-                            mma_i8(d0 + p.block_n, da + koff, db_lo + koff, idesc_su, accum);       // hi * lo
-                            mma_i8(d0 + p.block_n, da_lo + koff, db + koff, idesc_us, 1u);          // lo * hi
-                            mma_i8(d0 + 2 * p.block_n, da_lo + koff, db_lo + koff, idesc_uu, accum); // lo * lo
-                        }
-                        commit(smem_u32(&empty_bar[stage]));
+                    for (int k = 0; k < ksteps; k++) {
+                        const uint32_t accum = (kb | k) != 0;
+                        const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K, in 16-byte units
+                        mma_i8(d0, da + koff, db + koff, idesc_ss, accum);                      // hi * hi
+                        mma_i8(d0 + p.block_n, da + koff, db_lo + koff, idesc_su, accum);       // hi * lo
+                        mma_i8(d0 + p.block_n, da_lo + koff, db + koff, idesc_us, 1u);          // lo * hi
+                        mma_i8(d0 + 2 * p.block_n, da_lo + koff, db_lo + koff, idesc_uu, accum); // lo * lo
                     }
+                    commit(smem_u32(&empty_bar[stage]));
                 }
                 if (++stage == p.stages) {
                     stage = 0;
@@ -358,8 +416,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             if (!ok)
                 break;
-            if (issuer)
-                commit(smem_u32(&tfull_bar[acc]));
+            commit(smem_u32(&tfull_bar[acc]));
+            mbar_arrive(smem_u32(&tfull_bar[acc])); // publishes epi_tile[acc]
             if (++acc == p.acc_stages) {
                 acc = 0;
                 acc_phase ^= 1;
@@ -384,26 +442,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t fp_base = epi_param_base(fast_s);
         uint32_t acc_phase = 0;
         bool ok = true;
-        int local = 0;
-        int rows = first_rows, nt = first_n;
         long long w_tfull = 0, w_work = 0, w_store = 0;
         (void)w_tfull, (void)w_work, (void)w_store;
         TC_LAP_INIT;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
-            const int bi = p.batch == 1 ? 0 : rows / p.m_tiles;
-            const int m0 = (p.batch == 1 ? rows : rows % p.m_tiles) * BLOCK_M;
-            const int n0 = nt * p.block_n;
-            rows += step_rows, nt += step_n;
-            if (nt >= p.n_tiles)
-                nt -= p.n_tiles, rows++;
-            if ((local & (p.acc_stages - 1)) != acc) // acc_stages is 1, 2 or 4
-                continue;
+        while (ok) {
             TC_LAP(w_work);
             if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase)) {
                 ok = false;
                 break;
             }
             TC_LAP(w_tfull);
+            const int tile = epi_tile[acc];
+            if (tile < 0)
+                break;
+            const int rows = tile / p.n_tiles, nt = tile - rows * p.n_tiles;
+            const int bi = p.batch == 1 ? 0 : rows / p.m_tiles;
+            const int m0 = (p.batch == 1 ? rows : rows % p.m_tiles) * BLOCK_M;
+            const int n0 = nt * p.block_n;
             acc_phase ^= 1;
             fence_after();
             const bool row_ok = m0 + row_in_tile < p.M;
@@ -496,9 +551,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     fence_before();
     __syncthreads();
+    TC_STAMP(1);
     if (warp == 1) {
         fence_after();
         tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+    // the last CTA to get here leaves the counters as it found them (thread 0 is also the one that asked for tiles)
+    if (p.sched && threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+            p.sched[0] = 0;
+            p.sched[1] = 0;
+        }
     }
 }
 
@@ -805,7 +869,10 @@ constexpr size_t SMEM_BUDGET = 200 * 1024;      // stages + staging tiles of the
 constexpr size_t SMEM_BUDGET_DEEP = 225 * 1024; // long reductions with direct row stores: one more stage in flight (1.79 -> 1.97 POPS
                                                 // at 65536x1024x1024); for the staged layers the larger budget measured 5 % slower
 
-size_t aux_bytes(const TcParams &p) { return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * MAX_STAGES + 2 * MAX_ACC) * 8 + 32 + 256; }
+size_t aux_bytes(const TcParams &p)
+{
+    return sizeof(FastParam) * (size_t)p.n_tiles * p.block_n + (2 * MAX_STAGES + 2 * MAX_ACC) * 8 + 32 + 256 + (TILE_RING + MAX_ACC) * 4;
+}
 
 bool plan(const espdl_conv_desc &d, TcParams &p, bool force_direct = false)
 {
@@ -953,6 +1020,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     if (!plan(d, p, n_peer > 0))
         return ESPDL_ERR_UNSUPPORTED;
     p.n_peer = n_peer;
+    p.sched = nullptr, p.static_tiles = 0;
     for (int i = 0; i < 7; i++) p.peer_delta[i] = i < n_peer ? peer_delta[i] : 0;
     const bool i16 = d.dtype == ESPDL_DTYPE_INT16;
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
@@ -1016,6 +1084,9 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     if (all_tiles > 0x7fffffffll)
         return ESPDL_ERR_TOO_LARGE;
     const int grid = (int)min(all_tiles, (long long)num_sms());
+    // three quarters of the tiles in the fixed order, the last quarter to whichever SM is free
+    p.sched = all_tiles >= 4ll * grid && all_tiles < (1ll << 30) ? sched_counters(s) : nullptr;
+    p.static_tiles = p.sched ? (int)(all_tiles * 3 / 4 / grid) * grid : (int)all_tiles;
     static std::once_flag attr_once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once, [] {
@@ -1088,5 +1159,9 @@ extern "C" int espdl_b200_gemm_s16_static(const espdl_conv_desc *desc, void *str
 extern "C" int espdl_b200_debug_gemm_timing(long long *out, int ctas)
 {
     return cudaMemcpyFromSymbol(out, espdl::g_tc_timing, sizeof(long long) * 8 * (size_t)(ctas > 256 ? 256 : ctas)) == cudaSuccess ? 0 : -3;
+}
+extern "C" int espdl_b200_debug_gemm_clock(long long *out, int ctas)
+{
+    return cudaMemcpyFromSymbol(out, espdl::g_tc_clock, sizeof(long long) * 4 * (size_t)(ctas > 256 ? 256 : ctas)) == cudaSuccess ? 0 : -3;
 }
 #endif
