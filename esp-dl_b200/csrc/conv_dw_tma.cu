@@ -51,6 +51,7 @@ constexpr int DWT_CONSUMER_WARPS = 16;
 constexpr int DWT_CONSUMERS = DWT_CONSUMER_WARPS * 32;
 constexpr int DWT_THREADS = DWT_CONSUMERS + 32;
 constexpr int DWT_STAGES = 2;
+constexpr int DWT_RING = 8; // tile numbers on their way from the producer to the consumers (more than DWT_STAGES)
 constexpr size_t DWT_SMEM_BUDGET = 200 * 1024;
 
 struct DwtParams {
@@ -60,6 +61,8 @@ struct DwtParams {
     int stage_bytes, out_bytes, tx_bytes; // patch stride in the ring, output tile size, bytes one patch load delivers
     long long wait_limit;                 // cycles a wait may take (WAIT_LIMIT_CYCLES; shorter only in the expiry test)
     int withhold_arrive;                  // expiry test: consumer warp 0 never reports a patch as read, so the producer's wait runs out
+    unsigned *sched;                      // {next tile, CTAs done}: the tiles from static_tiles on are handed out by this counter; null = fixed walk
+    int static_tiles;                     // tiles walked in the fixed order (a multiple of the grid size)
     DwtSource src;
 };
 
@@ -104,6 +107,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
     uint64_t *bars = (uint64_t *)(out0 + 2 * (size_t)p.out_bytes);
     uint64_t *full_bar = bars, *empty_bar = bars + DWT_STAGES;
     volatile int *abort_flag = (volatile int *)(bars + 2 * DWT_STAGES);
+    volatile int *tile_ring = abort_flag + 1; // DWT_RING tile numbers, producer -> consumers (published by the "full" arrive)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -112,6 +116,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
             mbar_init(smem_u32(&empty_bar[s]), DWT_CONSUMER_WARPS);
         }
         *abort_flag = 0;
+        for (int i = 0; i < DWT_RING; i++) tile_ring[i] = 0; // never negative before the producer says so
         fence_barrier_init();
     }
     __syncthreads();
@@ -119,29 +124,66 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
 
     if (warp == DWT_CONSUMER_WARPS) {
         // ------------------------------------------------------------ producer: the warp walks the tiles, lane 0 issues
-        int stage = 0;
+        // Tiles below p.static_tiles go round the CTAs in the fixed order; the rest is handed out by a global counter, one
+        // number per tile and asked for one tile ahead, so that an SM that runs slower than the others ends with fewer tiles.
+        int stage = 0, local = 0;
         uint32_t phase = 0;
-        int cb = 0, t_in_cb = (int)blockIdx.x;
-        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x) {
-            while (t_in_cb >= p.tiles_per_cb) t_in_cb -= p.tiles_per_cb, cb++;
-            if (*abort_flag)
+        bool handed = false, ok = true;
+        auto after = [&](int cur) {
+            if (!handed && cur + (int)gridDim.x < p.static_tiles)
+                return cur + (int)gridDim.x;
+            if (!p.sched)
+                return handed || cur + (int)gridDim.x >= p.total_tiles ? p.total_tiles : cur + (int)gridDim.x;
+            handed = true;
+            int v = 0;
+            if (lane == 0)
+                v = p.static_tiles + (int)atomicAdd(p.sched, 1u);
+            return __shfl_sync(0xffffffffu, v, 0);
+        };
+        int t = blockIdx.x;
+        int next = after(t);
+        for (; t < p.total_tiles; local++) {
+            if (*abort_flag) {
+                ok = false;
                 break;
+            }
             if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, p.wait_limit)) {
                 *abort_flag = 1;
                 if (lane == 0)
                     atomicExch(&g_dwt_error, ESPDL_ERR_TIMEOUT);
+                ok = false;
                 break;
             }
+            const int cb = t / p.tiles_per_cb, t_in_cb = t - cb * p.tiles_per_cb;
             const int xt = t_in_cb % p.xtiles, r = t_in_cb / p.xtiles;
             const int yt = r % p.ytiles, nblk = r / p.ytiles;
             if (lane == 0) {
+                tile_ring[local & (DWT_RING - 1)] = t;
                 const uint32_t bar = smem_u32(&full_bar[stage]);
                 mbar_arrive_expect_tx(bar, (uint32_t)p.tx_bytes);
                 tma_load_4d(smem_u32(patch0 + (size_t)stage * p.stage_bytes), &map_in, cb * CB, xt * p.TW * S - p.pl, yt * p.TH * S - p.pt, nblk * p.NB, bar);
             }
-            t_in_cb += gridDim.x;
             if (++stage == DWT_STAGES)
                 stage = 0, phase ^= 1;
+            t = next;
+            if (t < p.total_tiles)
+                next = after(t);
+        }
+        // end of the walk: one stage without data whose ring entry is negative
+        if (ok && mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, p.wait_limit)) {
+            if (lane == 0) {
+                tile_ring[local & (DWT_RING - 1)] = -1;
+                mbar_arrive(smem_u32(&full_bar[stage]));
+            }
+        }
+        __syncwarp();
+        if (p.sched && lane == 0) {
+            // the last CTA's producer leaves the counters as it found them (it is also the thread that asked for tiles)
+            __threadfence();
+            if (atomicAdd(p.sched + 1, 1u) == gridDim.x - 1) {
+                p.sched[0] = 0;
+                p.sched[1] = 0;
+            }
         }
         __syncwarp();
         return;
@@ -164,21 +206,22 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
 
     DwtConsts<S> k;
     int have_cb = -1;
-    int stage = 0, local = 0;
+    int stage = 0;
     uint32_t phase = 0;
-    int cb = 0, t_in_cb = (int)blockIdx.x;
-    for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, local++) {
-        while (t_in_cb >= p.tiles_per_cb) t_in_cb -= p.tiles_per_cb, cb++;
-        if (cb != have_cb && active) {
-            dwt_load_consts<S>(k, p.src, cb * CB + cw * 4);
-            have_cb = cb;
-        }
+    for (int local = 0;; local++) {
         if (!mbar_wait(smem_u32(&full_bar[stage]), phase, p.wait_limit)) {
-            // the patch never came: note it and carry on with whatever the buffer holds, so that every thread still
-            // reaches the barrier below, where all of them see the flag and leave together
+            // the patch never came: note it and leave at the barrier below, where all threads see the flag together
             *abort_flag = 1;
             if (lane == 0)
                 atomicExch(&g_dwt_error, ESPDL_ERR_TIMEOUT);
+        }
+        const int t = *abort_flag ? 0 : tile_ring[local & (DWT_RING - 1)];
+        if (t < 0)
+            break;
+        const int cb = t / p.tiles_per_cb, t_in_cb = t - cb * p.tiles_per_cb;
+        if (cb != have_cb && active) {
+            dwt_load_consts<S>(k, p.src, cb * CB + cw * 4);
+            have_cb = cb;
         }
         const uint32_t *patch = (const uint32_t *)(patch0 + (size_t)stage * p.stage_bytes);
         uint32_t *obuf = (uint32_t *)(out0 + (size_t)(local & 1) * p.out_bytes);
@@ -207,7 +250,6 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
             tma_store_4d(&map_out, smem_u32(obuf), cb * CB, xt * p.TW, (rr % p.ytiles) * p.TH, (rr / p.ytiles) * p.NB);
             bulk_commit();
         }
-        t_in_cb += gridDim.x;
         if (++stage == DWT_STAGES)
             stage = 0, phase ^= 1;
     }
@@ -232,7 +274,7 @@ EncodeTiledFn dwt_encode()
     return fn;
 }
 
-size_t dwt_smem_bytes(const DwtParams &p) { return 1024 + (size_t)DWT_STAGES * p.stage_bytes + 2 * (size_t)p.out_bytes + 2 * DWT_STAGES * 8 + 64; }
+size_t dwt_smem_bytes(const DwtParams &p) { return 1024 + (size_t)DWT_STAGES * p.stage_bytes + 2 * (size_t)p.out_bytes + 2 * DWT_STAGES * 8 + 64 + DWT_RING * 4; }
 
 // Tile shape: channel block CB, NB images, nbands bands of rows, nseg runs of L columns - the combination that keeps the
 // most consumer threads at useful work (one run per thread) within the shared-memory budget.
@@ -401,6 +443,9 @@ int conv2d_dw_tma(const espdl_conv_desc &d, cudaStream_t s)
     }
     const size_t smem = dwt_smem_bytes(p);
     const int grid = min(p.total_tiles, num_sms());
+    // three quarters of the tiles in the fixed order, the last quarter to whichever SM is free
+    p.sched = p.total_tiles >= 4 * grid ? sched_counters(s) : nullptr;
+    p.static_tiles = p.sched ? (int)((long long)p.total_tiles * 3 / 4 / grid) * grid : p.total_tiles;
     return d.stride_h == 1 ? dwt_dispatch<1>(mi, mo, p, smem, grid, s) : dwt_dispatch<2>(mi, mo, p, smem, grid, s);
 }
 
