@@ -16,7 +16,7 @@ ACT_LINEAR, ACT_RELU = 0, 1
 ROUND_HALF_UP, ROUND_HALF_EVEN = 0, 1
 KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05 = 0, 1, 2
 ELT_ADD, ELT_MUL, ELT_REQUANTIZE, ELT_LUT, ELT_CLIP, ELT_RELU, ELT_PRELU, ELT_SUB = range(8)
-ELT_MAX, ELT_MIN, ELT_DIV, ELT_MOD, ELT_GREATER, ELT_GREATER_EQUAL, ELT_EQUAL, ELT_LESS, ELT_LESS_EQUAL = range(8, 17)
+ELT_MAX, ELT_MIN, ELT_DIV, ELT_MOD, ELT_GREATER, ELT_GREATER_EQUAL, ELT_EQUAL, ELT_LESS, ELT_LESS_EQUAL, ELT_POW = range(8, 18)
 POOL_MAX, POOL_AVG, POOL_GLOBAL_AVG = 0, 1, 2
 
 i32 = C.c_int32
@@ -43,7 +43,7 @@ class EltwiseDesc(C.Structure):
         ("op", i32), ("in_dtype", i32), ("out_dtype", i32), ("ndim", i32),
         ("out_shape", i32 * 4), ("in0_shape", i32 * 4), ("in1_shape", i32 * 4),
         ("in0_exponent", i32), ("in1_exponent", i32), ("out_exponent", i32),
-        ("clip_lo", i32), ("clip_hi", i32), ("round_mode", i32), ("lut_shift", i32),
+        ("clip_lo", i32), ("clip_hi", i32), ("round_mode", i32), ("lut_shift", i32), ("table", C.c_void_p),
     ]
 
 
@@ -76,7 +76,7 @@ class CopyDesc(C.Structure):
 class SoftmaxDesc(C.Structure):
     _fields_ = [
         ("input", C.c_void_p), ("output", C.c_void_p), ("exp_table", C.c_void_p),
-        ("rows", i32), ("len", i32), ("out_dtype", i32), ("out_exponent", i32),
+        ("rows", i32), ("len", i32), ("out_dtype", i32), ("out_exponent", i32), ("inner", i32), ("log", i32), ("in_exponent", i32),
     ]
 
 
@@ -119,10 +119,11 @@ class DetectDesc(C.Structure):
 
 class ReduceDesc(C.Structure):
     _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("op", i32), ("dtype", i32), ("ndim", i32), ("shape", i32 * 6),
-                ("reduce", i32 * 6), ("in_exponent", i32), ("out_exponent", i32), ("round_mode", i32)]
+                ("reduce", i32 * 6), ("in_exponent", i32), ("out_exponent", i32), ("round_mode", i32), ("exp_table", C.c_void_p)]
 
 
-REDUCE_MEAN, REDUCE_SUM, REDUCE_MAX, REDUCE_MIN, REDUCE_L1, REDUCE_SUM_SQUARE, REDUCE_L2 = range(7)
+(REDUCE_MEAN, REDUCE_SUM, REDUCE_MAX, REDUCE_MIN, REDUCE_L1, REDUCE_SUM_SQUARE, REDUCE_L2, REDUCE_PROD, REDUCE_LOG_SUM,
+ REDUCE_LOG_SUM_EXP) = range(10)
 
 
 class PadDesc(C.Structure):
@@ -137,10 +138,24 @@ class NormDesc(C.Structure):
     _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("scale", C.c_void_p), ("bias", C.c_void_p), ("mean", C.c_void_p),
                 ("inv_std_dev", C.c_void_p), ("op", i32), ("dtype", i32), ("rows", C.c_int64), ("len", i32), ("in_exponent", i32),
                 ("out_exponent", i32), ("scale_exponent", i32), ("bias_exponent", i32), ("mean_exponent", i32),
-                ("inv_std_dev_exponent", i32), ("epsilon", C.c_float), ("round_mode", i32)]
+                ("inv_std_dev_exponent", i32), ("epsilon", C.c_float), ("round_mode", i32), ("p", i32), ("inner", C.c_int64)]
 
 
-NORM_RMS, NORM_LAYER = range(2)
+NORM_RMS, NORM_LAYER, NORM_LP = range(3)
+
+
+class ReverseSequenceDesc(C.Structure):
+    _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("seq_lens", C.c_void_p), ("elem_size", i32), ("batch_axis", i32),
+                ("dim0", i32), ("dim1", i32), ("feature", C.c_int64)]
+
+
+class ScatterNDDesc(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("indices", C.c_void_p), ("updates", C.c_void_p), ("output", C.c_void_p), ("dtype", i32),
+                ("reduction", i32), ("index_depth", i32), ("n_slices", i32), ("slice_size", C.c_int64), ("data_size", C.c_int64),
+                ("axis_offset", C.c_int64 * 6)]
+
+
+SCATTER_NONE, SCATTER_ADD, SCATTER_MUL, SCATTER_MAX, SCATTER_MIN = range(5)
 
 
 class GatherDesc(C.Structure):
@@ -198,6 +213,8 @@ SYMBOLS = {
     "espdl_b200_pad": (C.c_int, [C.POINTER(PadDesc), C.c_void_p]),
     "espdl_b200_gather": (C.c_int, [C.POINTER(GatherDesc), C.c_void_p]),
     "espdl_b200_norm": (C.c_int, [C.POINTER(NormDesc), C.c_void_p]),
+    "espdl_b200_reverse_sequence": (C.c_int, [C.POINTER(ReverseSequenceDesc), C.c_void_p]),
+    "espdl_b200_scatter_nd": (C.c_int, [C.POINTER(ScatterNDDesc), C.c_void_p]),
 }
 
 _lib = None

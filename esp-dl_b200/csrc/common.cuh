@@ -20,6 +20,7 @@ int num_sms();
 // graphs may run side by side).  The kernel's last CTA writes both words back to zero.  Null when no pair is left: the
 // kernel then walks its tiles in the fixed order.
 unsigned *sched_counters(cudaStream_t s);
+int lp_norm_op(const espdl_norm_desc &d, cudaStream_t s); // sequence_ops.cu
 // Records the most recent failed launch (cudaGetLastError) if any.
 int check_launch(const char *what);
 

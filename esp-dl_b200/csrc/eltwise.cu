@@ -13,6 +13,8 @@
 //   Mod      esp-dl/dl/base/dl_base_mod.cpp:9-62                 comparisons esp-dl/dl/base/dl_base_greater.cpp:9-44 (and siblings)
 #include "common.cuh"
 
+#include <climits>
+
 namespace espdl {
 
 struct EltParams {
@@ -24,6 +26,7 @@ struct EltParams {
     int e0, e1, eo, lo, hi, half_even;
     float mul_scale, clip_rescale, in_scale, in1_scale, out_rescale, inv_scale;
     int prelu_shift, lut_shift;
+    const int8_t *pow_table; // Pow on int8: the host's 256 x 256 answers, or null
     int div_n1, div_table0; // Div: divisor broadcast along the innermost axis; int8 dividend of one element (table form)
     float div_scale;
     long long total;
@@ -31,7 +34,7 @@ struct EltParams {
 
 __host__ __device__ __forceinline__ bool elt_two_operands(int op)
 {
-    return op == ESPDL_ELT_ADD || op == ESPDL_ELT_SUB || op == ESPDL_ELT_MUL || (op >= ESPDL_ELT_MAX && op <= ESPDL_ELT_LESS_EQUAL);
+    return op == ESPDL_ELT_ADD || op == ESPDL_ELT_SUB || op == ESPDL_ELT_MUL || (op >= ESPDL_ELT_MAX && op <= ESPDL_ELT_POW);
 }
 
 __device__ __forceinline__ long long ld_int(const void *p, int dt, long long i)
@@ -104,6 +107,16 @@ __device__ __forceinline__ long long elt_int(const EltParams &p, long long a, lo
         const float av = __fmul_rn(__int2float_rn((int)a), p.in_scale), bv = __fmul_rn(__int2float_rn((int)b), p.in1_scale);
         const float r = bv != 0.f ? fmodf(av, bv) : 0.f;
         return fround(__fmul_rn(r, p.out_rescale), p.half_even);
+    }
+    case ESPDL_ELT_POW: {
+        if (p.pow_table)
+            return p.pow_table[(((unsigned)a & 0xffu) ^ 0x80u) * 256u + (((unsigned)b & 0xffu) ^ 0x80u)];
+        const float av = __fmul_rn(__int2float_rn((int)a), p.in_scale), bv = __fmul_rn(__int2float_rn((int)b), p.in1_scale);
+        const float r = __fmul_rn(powf(av, bv), p.out_rescale);
+        // a float that is no int32 (NaN, infinity, too large) converts to the minimum on x86, where the reference runs
+        if (!(fabsf(r) < 2147483520.f))
+            return (long long)INT_MIN;
+        return fround(r, p.half_even);
     }
     case ESPDL_ELT_GREATER: return a > b;
     case ESPDL_ELT_GREATER_EQUAL: return a >= b;
@@ -230,7 +243,7 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     const bool compare = d->op >= ESPDL_ELT_GREATER && d->op <= ESPDL_ELT_LESS_EQUAL;
     if ((binary || d->op == ESPDL_ELT_LUT || d->op == ESPDL_ELT_PRELU) && !d->input1)
         return ESPDL_ERR_INVALID_ARG;
-    if (d->op < ESPDL_ELT_ADD || d->op > ESPDL_ELT_LESS_EQUAL)
+    if (d->op < ESPDL_ELT_ADD || d->op > ESPDL_ELT_POW)
         return ESPDL_ERR_INVALID_ARG;
     auto is_int = [](int t) { return t == ESPDL_DTYPE_INT8 || t == ESPDL_DTYPE_INT16; };
     if (d->op == ESPDL_ELT_REQUANTIZE) {
@@ -274,6 +287,7 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     p.e0 = d->in0_exponent, p.e1 = d->in1_exponent, p.eo = d->out_exponent;
     p.lo = d->clip_lo, p.hi = d->clip_hi, p.half_even = d->round_mode == ESPDL_ROUND_HALF_EVEN;
     p.lut_shift = d->lut_shift;
+    p.pow_table = d->op == ESPDL_ELT_POW && d->in_dtype == ESPDL_DTYPE_INT8 ? (const int8_t *)d->table : nullptr;
     for (int e : {p.e0, p.e1, p.eo})
         if (e > 30 || e < -30)
             return ESPDL_ERR_INVALID_ARG;
@@ -298,7 +312,7 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = same && d->in_dtype == ESPDL_DTYPE_INT8 && (d->out_dtype == ESPDL_DTYPE_INT8 || compare) && total % 16 == 0 &&
         ((uintptr_t)d->input0 % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && (!binary || ((uintptr_t)d->input1 % 16) == 0) &&
-        d->op != ESPDL_ELT_PRELU;
+        d->op != ESPDL_ELT_PRELU && d->op != ESPDL_ELT_POW;
     if (vec) {
         const long long nvec = total / 16;
         switch (d->op) {

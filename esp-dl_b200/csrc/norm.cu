@@ -239,7 +239,7 @@ extern "C" int espdl_b200_norm(const espdl_norm_desc *d, void *stream)
 {
     if (!d || !d->input || !d->output || d->rows < 0 || d->len <= 0)
         return ESPDL_ERR_INVALID_ARG;
-    if (d->op != ESPDL_NORM_RMS && d->op != ESPDL_NORM_LAYER)
+    if (d->op != ESPDL_NORM_RMS && d->op != ESPDL_NORM_LAYER && d->op != ESPDL_NORM_LP)
         return ESPDL_ERR_INVALID_ARG;
     if (d->op == ESPDL_NORM_RMS && !d->scale)
         return ESPDL_ERR_INVALID_ARG;
@@ -250,6 +250,8 @@ extern "C" int espdl_b200_norm(const espdl_norm_desc *d, void *stream)
             return ESPDL_ERR_INVALID_ARG;
     if (d->rows == 0)
         return ESPDL_OK;
+    if (d->op == ESPDL_NORM_LP)
+        return lp_norm_op(*d, (cudaStream_t)stream);
     NormParams p;
     p.in = d->input, p.out = d->output, p.scale = d->scale, p.bias = d->bias, p.mean = d->mean, p.inv_std = d->inv_std_dev;
     p.op = d->op, p.half_even = d->round_mode == ESPDL_ROUND_HALF_EVEN, p.len = d->len, p.rows = d->rows;

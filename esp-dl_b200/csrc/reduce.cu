@@ -1,11 +1,16 @@
 // Reductions over any set of axes of an int8 / int16 tensor: ReduceMean, ReduceSum, ReduceMax, ReduceMin, ReduceL1,
-// ReduceSumSquare, ReduceL2 (dl_module_reduce_l1.hpp, dl_module_reduce_sum_square.hpp, dl_module_reduce_l2.hpp).
+// ReduceSumSquare, ReduceL2 (dl_module_reduce_l1.hpp, dl_module_reduce_sum_square.hpp, dl_module_reduce_l2.hpp), ReduceProd,
+// ReduceLogSum, ReduceLogSumExp (dl_module_reduce_prod.hpp, dl_module_reduce_log_sum.hpp, dl_module_reduce_log_sum_exp.hpp).
 // Replaces dl::module::ReduceBase::forward_template and the reduce functions of the modules built on it
 // (esp-dl/dl/module/include/dl_module_reduce_base.hpp:121-262, dl_module_reduce_mean.hpp:17-45, dl_module_reduce_sum.hpp:
 // 17-42).  A thread owns one output element and walks the reduced axes; with channels innermost and kept (the usual
 // spatial mean of an NHWC map) neighbouring threads read neighbouring bytes.  Integer sums are exact, so the order
-// of the walk does not matter; the mean's fp32 expression is evaluated in the reference's order.
+// of the walk does not matter; the mean's fp32 expression is evaluated in the reference's order.  The floating-point
+// accumulations (the product, the sum of exponentials) are not associative: the walk visits the reduced elements in
+// the reference's order (row-major over the reduced axes), one thread per output.
 #include "common.cuh"
+
+#include <climits>
 
 namespace espdl {
 
@@ -19,7 +24,16 @@ struct ReduceParams {
     int ksize[6], rsize[6];
     long long kstride[6], rstride[6];
     long long outputs, count;
+    const float *exp_table;
 };
+
+// tool::round of a float that may be no int32 (NaN, infinity): such a value converts to the minimum on x86
+__device__ __forceinline__ long long fround_x86(float v, int half_even)
+{
+    if (!(fabsf(v) < 2147483520.f))
+        return (long long)INT_MIN;
+    return fround(v, half_even);
+}
 
 template <typename T, typename ACC>
 __global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
@@ -36,9 +50,20 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
         int idx[6] = {0, 0, 0, 0, 0, 0};
         long long off = base;
         ACC acc = p.op == ESPDL_REDUCE_MAX ? (ACC)lo : (p.op == ESPDL_REDUCE_MIN ? (ACC)hi : (ACC)0);
+        float facc = p.op == ESPDL_REDUCE_PROD ? 1.f : 0.f; // int8 product, both sums of exponentials
+        double dacc = 1.0;                                   // int16 product
+        const float in_scale = dl_scale(p.e_in);
         for (long long i = 0; i < p.count; i++) {
             const ACC v = (ACC)in[off];
-            if (p.op == ESPDL_REDUCE_MAX)
+            if (p.op == ESPDL_REDUCE_PROD) {
+                const float t = __fmul_rn((float)(int)v, in_scale);
+                if (sizeof(T) == 1)
+                    facc = __fmul_rn(facc, t);
+                else
+                    dacc = __dmul_rn(dacc, (double)t);
+            } else if (p.op == ESPDL_REDUCE_LOG_SUM_EXP) {
+                facc = __fadd_rn(facc, sizeof(T) == 1 ? p.exp_table[(int)v + 128] : expf(__fmul_rn((float)(int)v, in_scale)));
+            } else if (p.op == ESPDL_REDUCE_MAX)
                 acc = acc > v ? acc : v;
             else if (p.op == ESPDL_REDUCE_MIN)
                 acc = acc < v ? acc : v;
@@ -76,6 +101,20 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
                 }
             }
             q = fround(__fmul_rn(r, dl_rescale(p.e_out)), p.half_even);
+        } else if (p.op == ESPDL_REDUCE_PROD) {
+            if (sizeof(T) == 1) {
+                q = fround_x86(__fmul_rn(facc, dl_rescale(p.e_out)), p.half_even);
+            } else {
+                // the fp64 product times the fp32 scale, rounded as a double (floor(v + 0.5), or to nearest even)
+                const double v = __dmul_rn(dacc, (double)dl_rescale(p.e_out));
+                q = !(fabs(v) < 2147483647.0) ? (long long)INT_MIN : (p.half_even ? (long long)__double2ll_rn(v) : (long long)floor(__dadd_rn(v, 0.5)));
+            }
+        } else if (p.op == ESPDL_REDUCE_LOG_SUM) {
+            // static_cast<float>(sum * input_scale): the integer sum becomes a float before the multiplication
+            const float sumf = sizeof(ACC) == 4 ? __int2float_rn((int)acc) : __ll2float_rn((long long)acc);
+            q = fround_x86(__fmul_rn(logf(__fmul_rn(sumf, in_scale)), dl_rescale(p.e_out)), p.half_even);
+        } else if (p.op == ESPDL_REDUCE_LOG_SUM_EXP) {
+            q = fround_x86(__fmul_rn(logf(facc), dl_rescale(p.e_out)), p.half_even);
         } else if (p.op == ESPDL_REDUCE_SUM || p.op == ESPDL_REDUCE_L1 || p.op == ESPDL_REDUCE_SUM_SQUARE) {
             const int shift = max(-62, min(62, p.e_out - (p.op == ESPDL_REDUCE_SUM_SQUARE ? 2 * p.e_in : p.e_in)));
             q = sizeof(ACC) == 4 ? (long long)shift_round32((int32_t)acc, max(-31, min(31, shift)), p.half_even)
@@ -91,13 +130,16 @@ __global__ void __launch_bounds__(256) reduce_kernel(ReduceParams p)
 
 int reduce_op(const espdl_reduce_desc &d, cudaStream_t s)
 {
-    if (!d.input || !d.output || d.ndim < 1 || d.ndim > 6 || d.op < 0 || d.op > ESPDL_REDUCE_L2)
+    if (!d.input || !d.output || d.ndim < 1 || d.ndim > 6 || d.op < 0 || d.op > ESPDL_REDUCE_LOG_SUM_EXP)
+        return ESPDL_ERR_INVALID_ARG;
+    if (d.op == ESPDL_REDUCE_LOG_SUM_EXP && d.dtype == ESPDL_DTYPE_INT8 && !d.exp_table)
         return ESPDL_ERR_INVALID_ARG;
     if (d.dtype != ESPDL_DTYPE_INT8 && d.dtype != ESPDL_DTYPE_INT16)
         return ESPDL_ERR_UNSUPPORTED;
     ReduceParams p;
     p.in = d.input, p.out = d.output, p.op = d.op, p.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
     p.e_in = d.in_exponent, p.e_out = d.out_exponent;
+    p.exp_table = d.exp_table;
     p.nk = p.nr = 0, p.outputs = 1, p.count = 1;
     long long stride = 1;
     long long strides[6];

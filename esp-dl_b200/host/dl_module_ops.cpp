@@ -1268,6 +1268,29 @@ std::vector<std::vector<int>> Reduce::get_output_shape(std::vector<std::vector<i
     return {out};
 }
 
+// tool::gen_lut_8bit(expf) (esp-dl/dl/tool/src/dl_tool.cpp:258-268) on the device; rebuilt when the exponent changes
+static int upload_exp_table(void *&dev, int &have_exponent, int exponent)
+{
+    if (dev && have_exponent == exponent)
+        return ESPDL_OK;
+    float table[256];
+    const float scale = DL_SCALE(exponent);
+    for (int i = 0; i < 256; i++) table[i] = expf(scale * (float)(i - 128));
+    if (!dev && espdl_b200_arena_alloc(sizeof(table), &dev) != ESPDL_OK)
+        return ESPDL_ERR_NO_MEM;
+    int st = espdl_b200_upload(dev, table, sizeof(table), nullptr);
+    if (!st)
+        st = espdl_b200_stream_sync(nullptr);
+    have_exponent = exponent;
+    return st;
+}
+
+Reduce::~Reduce()
+{
+    if (m_dev_table)
+        espdl_b200_arena_free(m_dev_table);
+}
+
 void Reduce::forward(ModelContext *context, runtime_mode_t mode)
 {
     (void)mode;
@@ -1278,7 +1301,10 @@ void Reduce::forward(ModelContext *context, runtime_mode_t mode)
     memset(&d, 0, sizeof(d));
     if (!in || !out || !in->device || !out->device || in->shape.size() > 6 || in->shape.empty()) {
         st = ESPDL_ERR_INVALID_ARG;
+    } else if (m_op == ESPDL_REDUCE_LOG_SUM_EXP && quant_type != QUANT_TYPE_SYMM_16BIT &&
+               (st = upload_exp_table(m_dev_table, m_table_exponent, (int)in->exponent)) != ESPDL_OK) {
     } else {
+        d.exp_table = (const float *)m_dev_table;
         d.input = in->device, d.output = out->device, d.op = m_op, d.dtype = quant_dtype(quant_type), d.ndim = (int)in->shape.size();
         for (size_t i = 0; i < in->shape.size(); i++) d.shape[i] = in->shape[i], d.reduce[i] = i < m_axes_reduce_flag.size() && m_axes_reduce_flag[i];
         d.in_exponent = in->exponent, d.out_exponent = out->exponent, d.round_mode = context->round_mode;
@@ -1296,7 +1322,9 @@ Module *Reduce::deserialize(fbs::FbsModel *m, std::string node)
     int op = ESPDL_REDUCE_MIN;
     for (auto &kv : std::initializer_list<std::pair<const char *, int>>{{"ReduceMean", ESPDL_REDUCE_MEAN}, {"ReduceSum", ESPDL_REDUCE_SUM},
                                                                        {"ReduceMax", ESPDL_REDUCE_MAX}, {"ReduceL1", ESPDL_REDUCE_L1},
-                                                                       {"ReduceSumSquare", ESPDL_REDUCE_SUM_SQUARE}, {"ReduceL2", ESPDL_REDUCE_L2}})
+                                                                       {"ReduceSumSquare", ESPDL_REDUCE_SUM_SQUARE}, {"ReduceL2", ESPDL_REDUCE_L2},
+                                                                       {"ReduceProd", ESPDL_REDUCE_PROD}, {"ReduceLogSum", ESPDL_REDUCE_LOG_SUM},
+                                                                       {"ReduceLogSumExp", ESPDL_REDUCE_LOG_SUM_EXP}})
         if (type == kv.first)
             op = kv.second;
     int keepdims = 1, noop = 0;
@@ -2019,28 +2047,20 @@ void Softmax::forward(ModelContext *context, runtime_mode_t mode)
     int st = (!in || !out || !in->device || !out->device) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
     const int nd = in ? (int)in->shape.size() : 0;
     const int ax = axis < 0 ? axis + nd : axis;
-    if (!st && (in->dtype != DATA_TYPE_INT8 || ax != nd - 1))
+    if (!st && (in->dtype != DATA_TYPE_INT8 || ax < 0 || ax >= nd))
         st = ESPDL_ERR_UNSUPPORTED;
-    if (!st && (!m_dev_table || m_table_exponent != (int)in->exponent)) {
-        // dl::tool::gen_lut_8bit(expf): esp-dl/dl/tool/src/dl_tool.cpp:258-268, built once on the host
-        float table[256];
-        const float scale = DL_SCALE((int)in->exponent);
-        for (int i = 0; i < 256; i++) table[i] = expf(scale * (float)(i - 128));
-        if (!m_dev_table && espdl_b200_arena_alloc(sizeof(table), &m_dev_table) != ESPDL_OK)
-            st = ESPDL_ERR_NO_MEM;
-        if (!st)
-            st = espdl_b200_upload(m_dev_table, table, sizeof(table), nullptr);
-        if (!st)
-            st = espdl_b200_stream_sync(nullptr);
-        m_table_exponent = in->exponent;
-    }
+    if (!st)
+        st = upload_exp_table(m_dev_table, m_table_exponent, (int)in->exponent);
     if (!st) {
         espdl_softmax_desc d;
         memset(&d, 0, sizeof(d));
+        long long inner = 1;
+        for (int i = ax + 1; i < nd; i++) inner *= in->shape[i];
         d.input = (const int8_t *)in->device, d.output = out->device, d.exp_table = (const float *)m_dev_table;
-        d.len = in->shape.back(), d.rows = in->get_size() / d.len;
+        d.len = in->shape[ax], d.rows = in->get_size() / d.len;
+        d.inner = (int)inner, d.log = m_log ? 1 : 0, d.in_exponent = in->exponent;
         d.out_dtype = espdl_dtype(out), d.out_exponent = out->exponent;
-        st = espdl_b200_softmax(&d, context->stream);
+        st = inner > INT_MAX ? ESPDL_ERR_TOO_LARGE : espdl_b200_softmax(&d, context->stream);
     }
     if (st)
         ESP_LOGE("Softmax", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
@@ -2052,6 +2072,215 @@ Module *Softmax::deserialize(fbs::FbsModel *m, std::string node)
     int axis = -1;
     m->get_operation_attribute(node, "axis", axis);
     return new Softmax(node.c_str(), axis, MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+// --------------------------------------------------------------------------------- Pow
+Pow::Pow(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Elementwise(ESPDL_ELT_POW, name, inplace, quant_type) {}
+Pow::~Pow()
+{
+    if (m_dev_table)
+        espdl_b200_arena_free(m_dev_table);
+}
+Module *Pow::deserialize(fbs::FbsModel *m, std::string node) { return new Pow(node.c_str(), MODULE_NON_INPLACE, node_quant(m, node)); }
+
+void Pow::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *a = context->get_tensor(m_inputs_index[0]), *b = context->get_tensor(m_inputs_index[1]);
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    espdl_eltwise_desc d;
+    memset(&d, 0, sizeof(d));
+    int st = ESPDL_OK;
+    if (!a || !b || !out || !a->device || !b->device || !out->device)
+        st = ESPDL_ERR_INVALID_ARG;
+    if (!st && !pack_shapes(out->shape, a->shape, b->shape, d))
+        st = ESPDL_ERR_UNSUPPORTED;
+    if (!st && a->dtype == DATA_TYPE_INT8) {
+        const int key[4] = {(int)a->exponent, (int)b->exponent, (int)out->exponent, (int)context->round_mode};
+        if (!m_dev_table || memcmp(key, m_table_key, sizeof(key)) != 0) {
+            // every (base, power) pair once, with the host's powf: c_impl_pow_n_n of esp-dl/dl/base/dl_base_pow.cpp:49-63
+            std::vector<int8_t> table(65536);
+            const float s0 = DL_SCALE(key[0]), s1 = DL_SCALE(key[1]), rescale = DL_RESCALE(key[2]);
+            for (int ua = 0; ua < 256; ua++)
+                for (int ub = 0; ub < 256; ub++) {
+                    const float base_val = (float)(int8_t)(ua ^ 0x80) * s0, exp_val = (float)(int8_t)(ub ^ 0x80) * s1;
+                    const float r = powf(base_val, exp_val) * rescale;
+                    long long q;
+                    if (!(fabsf(r) < 2147483520.f))
+                        q = INT_MIN; // what the float -> int conversion of a NaN or an infinity gives where the reference runs
+                    else
+                        q = key[3] == ESPDL_ROUND_HALF_EVEN ? (long long)rintf(r) : (long long)floorf((float)((double)r + 0.5));
+                    table[ua * 256 + ub] = (int8_t)std::max(-128ll, std::min(127ll, q));
+                }
+            if (!m_dev_table && espdl_b200_arena_alloc(table.size(), &m_dev_table) != ESPDL_OK)
+                st = ESPDL_ERR_NO_MEM;
+            if (!st)
+                st = espdl_b200_upload(m_dev_table, table.data(), table.size(), nullptr);
+            if (!st)
+                st = espdl_b200_stream_sync(nullptr);
+            memcpy(m_table_key, key, sizeof(key));
+        }
+        d.table = m_dev_table;
+    }
+    if (!st) {
+        d.input0 = a->device, d.input1 = b->device, d.output = out->device;
+        d.op = m_op, d.in_dtype = espdl_dtype(a), d.out_dtype = espdl_dtype(out);
+        d.in0_exponent = a->exponent, d.in1_exponent = b->exponent, d.out_exponent = out->exponent;
+        d.round_mode = context->round_mode;
+        st = espdl_b200_eltwise(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("Pow", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+// --------------------------------------------------------------------------------- LogSoftmax, LpNormalization
+Module *LogSoftmax::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int axis = -1;
+    m->get_operation_attribute(node, "axis", axis);
+    return new LogSoftmax(node.c_str(), axis, MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+void LpNormalization::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *x = context->get_tensor(m_inputs_index[0]);
+    TensorBase *y = context->get_tensor(m_outputs_index[0]);
+    int st = (!x || !y || !x->device || !y->device || x->shape.empty()) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st) {
+        const int nd = (int)x->shape.size(), axis = m_axis < 0 ? nd + m_axis : m_axis;
+        espdl_norm_desc d;
+        memset(&d, 0, sizeof(d));
+        if (axis < 0 || axis >= nd) {
+            st = ESPDL_ERR_INVALID_ARG;
+        } else {
+            long long inner = 1;
+            for (int i = axis + 1; i < nd; i++) inner *= x->shape[i];
+            d.input = x->device, d.output = y->device, d.op = ESPDL_NORM_LP, d.dtype = quant_dtype(quant_type);
+            d.len = x->shape[axis], d.rows = x->get_size() / d.len, d.inner = inner, d.p = m_p;
+            d.in_exponent = x->exponent, d.out_exponent = y->exponent, d.round_mode = context->round_mode;
+            st = espdl_b200_norm(&d, context->stream);
+        }
+    }
+    if (st)
+        ESP_LOGE("LpNormalization", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *LpNormalization::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int axis = -1, p = 2;
+    m->get_operation_attribute(node, "axis", axis);
+    m->get_operation_attribute(node, "p", p);
+    return new LpNormalization(axis, p, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+// --------------------------------------------------------------------------------- ReverseSequence, ScatterND
+static esp_err_t upload_parameters(ModelContext *context, const std::vector<int> &inputs)
+{
+    for (int idx : inputs) {
+        TensorBase *t = context->get_tensor(idx);
+        if (t && t->data && !t->device && t->to_device() != ESP_OK) // host data and no device copy: a parameter
+            return ESP_FAIL;
+    }
+    return espdl_b200_stream_sync(nullptr) == ESPDL_OK ? ESP_OK : ESP_FAIL;
+}
+
+esp_err_t ReverseSequence::prepare(ModelContext *context) { return upload_parameters(context, m_inputs_index); }
+
+void ReverseSequence::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *x = context->get_tensor(m_inputs_index[0]);
+    TensorBase *lens = m_inputs_index.size() > 1 ? context->get_tensor(m_inputs_index[1]) : nullptr;
+    TensorBase *y = context->get_tensor(m_outputs_index[0]);
+    int st = (!x || !y || !lens || !x->device || !y->device || !lens->device || x->shape.size() < 2) ? ESPDL_ERR_INVALID_ARG : ESPDL_OK;
+    if (!st && (lens->dtype != DATA_TYPE_INT64 || m_batch_axis + m_time_axis != 1 || x->device == y->device ||
+                lens->get_size() < x->shape[m_batch_axis]))
+        st = ESPDL_ERR_UNSUPPORTED;
+    if (!st) {
+        espdl_reverse_sequence_desc d;
+        memset(&d, 0, sizeof(d));
+        d.input = x->device, d.output = y->device, d.seq_lens = (const int64_t *)lens->device;
+        d.elem_size = (int)dtype_sizeof(x->dtype), d.batch_axis = m_batch_axis, d.dim0 = x->shape[0], d.dim1 = x->shape[1];
+        d.feature = 1;
+        for (size_t i = 2; i < x->shape.size(); i++) d.feature *= x->shape[i];
+        st = espdl_b200_reverse_sequence(&d, context->stream);
+    }
+    if (st)
+        ESP_LOGE("ReverseSequence", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *ReverseSequence::deserialize(fbs::FbsModel *m, std::string node)
+{
+    int batch_axis = 1, time_axis = 0;
+    m->get_operation_attribute(node, "batch_axis", batch_axis);
+    m->get_operation_attribute(node, "time_axis", time_axis);
+    // the reference swaps in place after a copy; here the kernel reads one buffer and writes another
+    return new ReverseSequence(batch_axis, time_axis, node.c_str(), MODULE_NON_INPLACE, node_quant(m, node));
+}
+
+ScatterND::ScatterND(const std::string &reduction, const char *name, module_inplace_t inplace, quant_type_t quant_type) :
+    Module(name, inplace, quant_type), m_reduction(ESPDL_SCATTER_NONE)
+{
+    // unknown strings fall back to "none", as apply_reduction does (dl_module_scatter_nd.hpp:34-47)
+    for (auto &kv : std::initializer_list<std::pair<const char *, int>>{
+             {"add", ESPDL_SCATTER_ADD}, {"mul", ESPDL_SCATTER_MUL}, {"max", ESPDL_SCATTER_MAX}, {"min", ESPDL_SCATTER_MIN}})
+        if (reduction == kv.first)
+            m_reduction = kv.second;
+}
+
+esp_err_t ScatterND::prepare(ModelContext *context) { return upload_parameters(context, m_inputs_index); }
+
+void ScatterND::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    TensorBase *data = context->get_tensor(m_inputs_index[0]);
+    TensorBase *indices = m_inputs_index.size() > 1 ? context->get_tensor(m_inputs_index[1]) : nullptr;
+    TensorBase *updates = m_inputs_index.size() > 2 ? context->get_tensor(m_inputs_index[2]) : nullptr;
+    TensorBase *out = context->get_tensor(m_outputs_index[0]);
+    int st = (!data || !indices || !updates || !out || !data->device || !indices->device || !updates->device || !out->device ||
+              indices->shape.empty() || data->shape.empty())
+        ? ESPDL_ERR_INVALID_ARG
+        : ESPDL_OK;
+    if (!st && indices->dtype != DATA_TYPE_INT64)
+        st = ESPDL_ERR_UNSUPPORTED;
+    if (!st) {
+        espdl_scatter_nd_desc d;
+        memset(&d, 0, sizeof(d));
+        const int depth = indices->shape.back(), rank = (int)data->shape.size();
+        if (depth < 1 || depth > rank || depth > 6) {
+            st = ESPDL_ERR_INVALID_ARG;
+        } else {
+            d.data = data->device, d.indices = (const int64_t *)indices->device, d.updates = updates->device, d.output = out->device;
+            d.dtype = espdl_dtype(data), d.reduction = m_reduction, d.index_depth = depth;
+            d.n_slices = (int)(indices->get_size() / depth);
+            d.slice_size = 1;
+            for (int i = depth; i < rank; i++) d.slice_size *= data->shape[i];
+            d.data_size = data->get_size();
+            long long stride = d.data_size;
+            for (int k = 0; k < depth; k++) {
+                stride /= data->shape[k];
+                d.axis_offset[k] = stride;
+            }
+            if (updates->get_size() < (long long)d.n_slices * d.slice_size)
+                st = ESPDL_ERR_INVALID_ARG;
+            else
+                st = espdl_b200_scatter_nd(&d, context->stream);
+        }
+    }
+    if (st)
+        ESP_LOGE("ScatterND", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+Module *ScatterND::deserialize(fbs::FbsModel *m, std::string node)
+{
+    std::string reduction = "none";
+    m->get_operation_attribute(node, "reduction", reduction);
+    return new ScatterND(reduction, node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node));
 }
 
 // --------------------------------------------------------------------------------- registry
@@ -2082,7 +2311,14 @@ void ModuleCreator::register_dl_modules()
     for (const char *op : {"LUT", "Swish", "Sigmoid", "Tanh", "HardSwish", "HardSigmoid", "Gelu", "Elu", "LeakyRelu", "Exp", "Log", "Sqrt",
                            "Neg", "Abs"})
         register_module(op, LUT::deserialize);
-    for (const char *op : {"ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin", "ReduceL1", "ReduceSumSquare", "ReduceL2"}) register_module(op, Reduce::deserialize);
+    for (const char *op : {"ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin", "ReduceL1", "ReduceSumSquare", "ReduceL2", "ReduceProd",
+                           "ReduceLogSum", "ReduceLogSumExp"})
+        register_module(op, Reduce::deserialize);
+    register_module("Pow", Pow::deserialize);
+    register_module("LogSoftmax", LogSoftmax::deserialize);
+    register_module("LpNormalization", LpNormalization::deserialize);
+    register_module("ReverseSequence", ReverseSequence::deserialize);
+    register_module("ScatterND", ScatterND::deserialize);
     register_module("Slice", Slice::deserialize);
     register_module("Pad", Pad::deserialize);
     register_module("Clip", Clip::deserialize);

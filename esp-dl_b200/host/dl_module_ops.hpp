@@ -165,6 +165,21 @@ ESPDL_B200_TWO_OPERAND_MODULE(Less)
 ESPDL_B200_TWO_OPERAND_MODULE(LessOrEqual)
 #undef ESPDL_B200_TWO_OPERAND_MODULE
 
+/// Pow (reference: dl_module_pow.hpp:17-110, dl_base_pow.cpp:9-63): round(powf(a * 2^ea, b * 2^eb) * 2^-eo) with numpy
+/// broadcasting.  For int8 the 256 x 256 possible answers are computed once on the host with its own powf and the kernel
+/// looks them up, which makes the result the reference's bit for bit; int16 calls powf on the device.
+class Pow : public Elementwise {
+public:
+    Pow(const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE);
+    ~Pow();
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    void *m_dev_table = nullptr;
+    int m_table_key[4] = {0x7fffffff, 0, 0, 0}; ///< exponents and rounding mode the table was built for
+};
+
 /// One-input elementwise modules: RequantizeLinear / QuantizeLinear / DequantizeLinear
 /// (dl_module_requantize_linear.hpp:8-60), LUT and every activation exported with a `lut` attribute
 /// (dl_module_lut.hpp:15-104), Clip (dl_module_clip.hpp), Relu (dl_module_relu.hpp), PRelu (dl_module_prelu.hpp).
@@ -309,9 +324,13 @@ public:
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
 
+    ~Reduce();
+
 protected:
     int m_op, m_keepdims;
     std::vector<bool> m_axes_reduce_flag;
+    void *m_dev_table = nullptr; ///< ReduceLogSumExp on int8: the exp table (tool::gen_lut_8bit(expf)) on the device
+    int m_table_exponent = 0x7fffffff;
 };
 
 /// Slice with positive steps (reference: dl_module_slice.hpp:10-128, TensorBase::slice); a strided device copy.
@@ -527,8 +546,70 @@ public:
 
 protected:
     int axis;
+    bool m_log = false; ///< LogSoftmax
     void *m_dev_table = nullptr;
     int m_table_exponent = 0x7fffffff;
+};
+
+/// LogSoftmax on int8 (reference: dl_module_log_softmax.hpp:150-215): the same exp table and sequential sum as Softmax,
+/// y = 2^e_in * x - logf(sum); float output, or int8 / int16 when the following QuantizeLinear is folded in.
+class LogSoftmax : public Softmax {
+public:
+    LogSoftmax(const char *name = nullptr, int axis = -1, module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Softmax(name, axis, inplace, quant_type)
+    {
+        m_log = true;
+    }
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+
+/// LpNormalization along one axis, p = 1 or 2 (reference: dl_module_lp_normalization.hpp:20-360).
+class LpNormalization : public Module {
+public:
+    LpNormalization(int axis = -1, int p = 2, const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+                    quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, inplace, quant_type), m_axis(axis), m_p(p)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override { return {input_shapes[0]}; }
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int m_axis, m_p;
+};
+
+/// ReverseSequence (reference: dl_module_reverse_sequence.hpp:10-126): inputs x and sequence_lens (int64); batch and time are
+/// the first two axes in either order.
+class ReverseSequence : public Module {
+public:
+    ReverseSequence(int batch_axis = 1, int time_axis = 0, const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+                    quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Module(name, inplace, quant_type), m_batch_axis(batch_axis), m_time_axis(time_axis)
+    {
+    }
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override { return {input_shapes[0]}; }
+    esp_err_t prepare(ModelContext *context) override; ///< uploads sequence_lens when it is a parameter
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int m_batch_axis, m_time_axis;
+};
+
+/// ScatterND (reference: dl_module_scatter_nd.hpp:20-264): inputs data, indices (int64), updates; reduction none / add / mul /
+/// max / min applied slice by slice in the order of the index tuples.
+class ScatterND : public Module {
+public:
+    ScatterND(const std::string &reduction = "none", const char *name = nullptr, module_inplace_t inplace = MODULE_NON_INPLACE,
+              quant_type_t quant_type = QUANT_TYPE_NONE);
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override { return {input_shapes[0]}; }
+    esp_err_t prepare(ModelContext *context) override; ///< uploads indices / updates when they are parameters
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+
+protected:
+    int m_reduction;
 };
 
 } // namespace module

@@ -224,7 +224,12 @@ typedef enum {
     ESPDL_ELT_GREATER_EQUAL = 13,
     ESPDL_ELT_EQUAL = 14,
     ESPDL_ELT_LESS = 15,
-    ESPDL_ELT_LESS_EQUAL = 16
+    ESPDL_ELT_LESS_EQUAL = 16,
+    ESPDL_ELT_POW = 17        /* sat(round(powf(a*2^ea, b*2^eb) * 2^-eo)); a result that is not a finite int32 (NaN, inf)
+                                 becomes the minimum, as the reference's float -> int conversion gives on x86.  int8 with `table`
+                                 set reads the 256 x 256 answers the host computed with its own powf (bit-exact); without it,
+                                 and for int16, powf runs on the device (within 1 of the reference where powf's last bit decides)
+                                 esp-dl/dl/base/dl_base_pow.cpp:9-63 */
 } espdl_eltwise_op_t;
 
 typedef struct espdl_eltwise_desc {
@@ -245,6 +250,7 @@ typedef struct espdl_eltwise_desc {
     int32_t lut_shift;        /* int16 LUT: log2 of the table step (5 for the usual 2049 entries): index = ((uint16)x ^ 0x8000)
                                  >> lut_shift, rounded to nearest (ties up, or to even with ROUND_HALF_EVEN), esp-dl/dl/base/
                                  dl_base_lut.cpp:50-107; 0 = a full 65536-entry table                             */
+    const void *table;        /* POW, int8: int8[256][256], entry [(uint8)a ^ 0x80][(uint8)b ^ 0x80]; else NULL */
 } espdl_eltwise_desc;
 
 int espdl_b200_eltwise(const espdl_eltwise_desc *desc, void *stream);
@@ -331,9 +337,13 @@ typedef struct espdl_softmax_desc {
     const int8_t *input;
     void *output;
     const float *exp_table; /* device float[256], entry k = expf(2^in_exponent * (k - 128)) */
-    int32_t rows, len;
+    int32_t rows, len;       /* rows = outer * inner */
     int32_t out_dtype;
     int32_t out_exponent;
+    int32_t inner;           /* elements between neighbours along the softmax axis (0 or 1: the last axis) */
+    int32_t log;             /* 1: LogSoftmax, y = 2^in_exponent * x - logf(sum)
+                                esp-dl/dl/module/include/dl_module_log_softmax.hpp:150-215 (logf on the device) */
+    int32_t in_exponent;     /* LogSoftmax only */
 } espdl_softmax_desc;
 
 int espdl_b200_softmax(const espdl_softmax_desc *desc, void *stream);
@@ -462,9 +472,16 @@ typedef enum {
     ESPDL_REDUCE_MIN = 3,
     ESPDL_REDUCE_L1 = 4,         /* shift_and_round(sum |x|, e_out - e_in)      esp-dl/dl/module/include/dl_module_reduce_l1.hpp:18-50 */
     ESPDL_REDUCE_SUM_SQUARE = 5, /* shift_and_round(sum x*x, e_out - 2*e_in)    esp-dl/dl/module/include/dl_module_reduce_sum_square.hpp:18-45 */
-    ESPDL_REDUCE_L2 = 6          /* round(sqrt_newton(sum x*x * 2^(2*e_in)) * 2^-e_out), the Newton iteration of
+    ESPDL_REDUCE_L2 = 6,         /* round(sqrt_newton(sum x*x * 2^(2*e_in)) * 2^-e_out), the Newton iteration of
                                     esp-dl/dl/math/include/dl_math.hpp:83-97 in fp32 (at most 100 steps here)
                                     esp-dl/dl/module/include/dl_module_reduce_l2.hpp:17-48 */
+    ESPDL_REDUCE_PROD = 7,       /* round(prod(x * 2^e_in) * 2^-e_out): the product runs in element order in fp32 (int8) or
+                                    fp64 (int16)      esp-dl/dl/module/include/dl_module_reduce_prod.hpp:18-52 */
+    ESPDL_REDUCE_LOG_SUM = 8,    /* round(logf((float)(sum x * 2^e_in)) * 2^-e_out), integer sum
+                                    esp-dl/dl/module/include/dl_module_reduce_log_sum.hpp:19-48 */
+    ESPDL_REDUCE_LOG_SUM_EXP = 9 /* round(logf(sum exp) * 2^-e_out): fp32 sum in element order of exp_table[x + 128] (int8) or
+                                    expf(x * 2^e_in) (int16)   esp-dl/dl/module/include/dl_module_reduce_log_sum_exp.hpp:27-107.
+                                    logf / expf run on the device: within 1 of the reference where their last bit decides */
 } espdl_reduce_op_t;
 
 typedef struct espdl_reduce_desc {
@@ -474,6 +491,7 @@ typedef struct espdl_reduce_desc {
     int32_t shape[6];
     int32_t reduce[6];       /* 1 = this axis is reduced                                                  */
     int32_t in_exponent, out_exponent, round_mode;
+    const float *exp_table;  /* LOG_SUM_EXP on int8: device float[256], entry k = expf(2^in_exponent * (k - 128)) */
 } espdl_reduce_desc;
 
 int espdl_b200_reduce(const espdl_reduce_desc *desc, void *stream);
@@ -487,7 +505,7 @@ int espdl_b200_reduce(const espdl_reduce_desc *desc, void *stream);
  * order, 1 / sqrt_newton(var + epsilon), y = sat(round((((x*2^e_in - mean) * inv_std) * scale + bias) * 2^-e_out)) with
  * scale / bias of the tensor's integer type (either may be NULL); the optional mean / inv_std_dev outputs hold one
  * value per row.  Rows are the leading axes, len the product of the normalised trailing axes; output may alias input. */
-typedef enum { ESPDL_NORM_RMS = 0, ESPDL_NORM_LAYER = 1 } espdl_norm_op_t;
+typedef enum { ESPDL_NORM_RMS = 0, ESPDL_NORM_LAYER = 1, ESPDL_NORM_LP = 2 } espdl_norm_op_t;
 
 typedef struct espdl_norm_desc {
     const void *input;
@@ -502,6 +520,11 @@ typedef struct espdl_norm_desc {
     int32_t in_exponent, out_exponent, scale_exponent, bias_exponent, mean_exponent, inv_std_dev_exponent;
     float epsilon;
     int32_t round_mode;
+    int32_t p;          /* LP: 1 or 2.  y = sat(round(x / ||x||_p * 2^-e_out)) along an axis of `len` elements that are `inner`
+                           apart (rows = outer * inner); 0 where the norm is 0.  The order of the fp32 operations differs
+                           between the last axis and any other, as in the reference
+                           esp-dl/dl/module/include/dl_module_lp_normalization.hpp:122-262, 300-356 */
+    int64_t inner;      /* LP: 1 = the last axis */
 } espdl_norm_desc;
 
 int espdl_b200_norm(const espdl_norm_desc *desc, void *stream);
@@ -521,6 +544,41 @@ typedef struct espdl_pad_desc {
 } espdl_pad_desc;
 
 int espdl_b200_pad(const espdl_pad_desc *desc, void *stream);
+
+/* ---------------------------------------------------------- ReverseSequence, ScatterND */
+/* dl::module::ReverseSequence (esp-dl/dl/module/include/dl_module_reverse_sequence.hpp:14-58): the first two axes are
+ * batch and time in either order; for batch b the first seq_lens[b] time steps are reversed, the rest copied. */
+typedef struct espdl_reverse_sequence_desc {
+    const void *input;
+    void *output;            /* not the input buffer */
+    const int64_t *seq_lens; /* device int64[batch] */
+    int32_t elem_size;       /* 1, 2 or 4 */
+    int32_t batch_axis;      /* 0 or 1; the time axis is the other one */
+    int32_t dim0, dim1;
+    int64_t feature;         /* product of the remaining extents */
+} espdl_reverse_sequence_desc;
+
+int espdl_b200_reverse_sequence(const espdl_reverse_sequence_desc *desc, void *stream);
+
+/* dl::module::ScatterND (esp-dl/dl/module/include/dl_module_scatter_nd.hpp:20-228): output = data, then for each of the
+ * n_slices index tuples IN ORDER, output[slice] = reduction(output[slice], updates[slice]); add and mul saturate after
+ * every step.  Slices addressed twice therefore see the earlier update, as in the reference. */
+typedef enum { ESPDL_SCATTER_NONE = 0, ESPDL_SCATTER_ADD = 1, ESPDL_SCATTER_MUL = 2, ESPDL_SCATTER_MAX = 3, ESPDL_SCATTER_MIN = 4 } espdl_scatter_reduction_t;
+
+typedef struct espdl_scatter_nd_desc {
+    const void *data;
+    const int64_t *indices; /* device int64[n_slices][index_depth] */
+    const void *updates;    /* [n_slices][slice_size] */
+    void *output;           /* may be the data buffer */
+    int32_t dtype;          /* ESPDL_DTYPE_INT8 / INT16 / FLOAT */
+    int32_t reduction;      /* espdl_scatter_reduction_t */
+    int32_t index_depth;    /* <= 6 */
+    int32_t n_slices;
+    int64_t slice_size, data_size;
+    int64_t axis_offset[6]; /* elements per step of each indexed axis of data */
+} espdl_scatter_nd_desc;
+
+int espdl_b200_scatter_nd(const espdl_scatter_nd_desc *desc, void *stream);
 
 #ifdef __cplusplus
 }

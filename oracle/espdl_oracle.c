@@ -230,7 +230,7 @@ int oracle_eltwise(const espdl_eltwise_desc *d)
         s1[4 - d->ndim + i] = d->in1_shape[i];
     }
     const int binary = d->op == ESPDL_ELT_ADD || d->op == ESPDL_ELT_MUL || d->op == ESPDL_ELT_SUB ||
-        (d->op >= ESPDL_ELT_MAX && d->op <= ESPDL_ELT_LESS_EQUAL);
+        (d->op >= ESPDL_ELT_MAX && d->op <= ESPDL_ELT_POW);
     if ((binary || d->op == ESPDL_ELT_LUT || d->op == ESPDL_ELT_PRELU) && !d->input1)
         return ESPDL_ERR_INVALID_ARG;
     int64_t st0[4], st1[4];
@@ -383,6 +383,15 @@ int oracle_eltwise(const espdl_eltwise_desc *d)
                         const float b_val = (float)load_int(d->input1, idt, b_i) * dl_scale(d->in1_exponent);
                         const float r = b_val != 0.0f ? fmodf(a_val, b_val) : 0.0f;
                         store_sat(d->output, odt, oi, fround(r * dl_rescale(d->out_exponent), mode));
+                        break;
+                    }
+                    case ESPDL_ELT_POW: { /* esp-dl/dl/base/dl_base_pow.cpp:9-63 (the three loops differ only in what is hoisted) */
+                        const float base_val = (float)load_int(d->input0, idt, a_i) * dl_scale(d->in0_exponent);
+                        const float exp_val = (float)load_int(d->input1, idt, b_i) * dl_scale(d->in1_exponent);
+                        const float r = powf(base_val, exp_val) * dl_rescale(d->out_exponent);
+                        /* (int)floorf(r + 0.5) of a NaN, an infinity or a value past int32 is INT32_MIN on x86 (cvttss2si);
+                         * written out so that the restatement does not rest on undefined behaviour */
+                        store_sat(d->output, odt, oi, !(fabsf(r) < 2147483520.f) ? INT32_MIN : fround(r, mode));
                         break;
                     }
                     case ESPDL_ELT_GREATER: /* esp-dl/dl/base/dl_base_greater.cpp:9-44 and its siblings: raw integers */
@@ -593,13 +602,19 @@ int oracle_softmax(const espdl_softmax_desc *d)
     if (!d || !d->input || !d->output || !d->exp_table)
         return ESPDL_ERR_INVALID_ARG;
     const float inv_scale = dl_rescale(d->out_exponent);
+    const int inner = d->inner > 1 ? d->inner : 1;
+    const float scale = dl_scale(d->in_exponent);
     for (int r = 0; r < d->rows; r++) {
-        const int8_t *x = d->input + (int64_t)r * d->len;
+        /* a row: len elements that lie `inner` apart (any axis, dl_module_log_softmax.hpp:185-215) */
+        const int64_t base = (int64_t)(r / inner) * d->len * inner + r % inner;
+        const int8_t *x = d->input + base;
         float sum = 0.f;
-        for (int i = 0; i < d->len; i++) sum += d->exp_table[x[i] + 128];
+        for (int i = 0; i < d->len; i++) sum += d->exp_table[x[(int64_t)i * inner] + 128];
+        const float log_sum = d->log ? logf(sum) : 0.f; /* esp-dl/dl/module/include/dl_module_log_softmax.hpp:168-175 */
         for (int i = 0; i < d->len; i++) {
-            float y = d->exp_table[x[i] + 128] / sum;
-            int64_t oi = (int64_t)r * d->len + i;
+            const int xi = x[(int64_t)i * inner];
+            float y = d->log ? scale * xi - log_sum : d->exp_table[xi + 128] / sum;
+            int64_t oi = base + (int64_t)i * inner;
             if (d->out_dtype == ESPDL_DTYPE_FLOAT)
                 ((float *)d->output)[oi] = y;
             else
@@ -820,6 +835,8 @@ int oracle_reduce(const espdl_reduce_desc *d)
                 rem /= d->shape[i];
             }
         int64_t acc = d->op == ESPDL_REDUCE_MAX ? lo : (d->op == ESPDL_REDUCE_MIN ? hi : 0);
+        float facc = d->op == ESPDL_REDUCE_PROD ? 1.f : 0.f; /* V_T = float: int8 product, sums of exponentials */
+        double dacc = 1.0;                                    /* V_T = double: int16 product */
         for (int64_t r = 0; r < count; r++) {
             int64_t off = base, rr = r;
             for (int i = d->ndim - 1; i >= 0; i--)
@@ -828,7 +845,22 @@ int oracle_reduce(const espdl_reduce_desc *d)
                     rr /= d->shape[i];
                 }
             const int64_t v = load_int(d->input, d->dtype, off);
-            if (d->op == ESPDL_REDUCE_MAX)
+            if (d->op == ESPDL_REDUCE_PROD) {
+                /* ReduceBase::reduce with an exponent, dl_module_reduce_base.hpp:100-118: float tmp = x * input_scale;
+                 * sum = sum * tmp in V_T (dl_module_reduce_prod.hpp:18-21, 54-60) */
+                const float tmp = (float)v * dl_scale(d->in_exponent);
+                if (is8)
+                    facc = facc * tmp;
+                else
+                    dacc = dacc * tmp;
+            } else if (d->op == ESPDL_REDUCE_LOG_SUM_EXP) {
+                /* dl_module_reduce_log_sum_exp.hpp:27-44: int8 adds exp_table[x + 128] (tool::gen_lut_8bit(expf)), int16 adds
+                 * expf(x * input_scale); V_T = float for both (:112-123) */
+                if (is8)
+                    facc = facc + expf(dl_scale(d->in_exponent) * (float)((int)v + 128 - 128));
+                else
+                    facc = facc + expf((float)v * dl_scale(d->in_exponent));
+            } else if (d->op == ESPDL_REDUCE_MAX)
                 acc = acc > v ? acc : v;
             else if (d->op == ESPDL_REDUCE_MIN)
                 acc = acc < v ? acc : v;
@@ -849,6 +881,18 @@ int oracle_reduce(const espdl_reduce_desc *d)
             f = f / (float)(size_t)count;
             f = f * dl_rescale(d->out_exponent);
             q = fround(f, d->round_mode);
+        } else if (d->op == ESPDL_REDUCE_PROD) { /* dl_module_reduce_prod.hpp:39-47 */
+            if (is8) {
+                q = fround(facc * dl_rescale(d->out_exponent), d->round_mode);
+            } else {
+                const double t = dacc * dl_rescale(d->out_exponent); /* tool::round(double), dl_tool.cpp:51-80 */
+                q = d->round_mode == ESPDL_ROUND_HALF_EVEN ? (int)rint(t) : (int)floor(t + 0.5);
+            }
+        } else if (d->op == ESPDL_REDUCE_LOG_SUM) { /* dl_module_reduce_log_sum.hpp:36-45 */
+            const float tmp = is8 ? (float)((int32_t)acc * dl_scale(d->in_exponent)) : (float)(acc * dl_scale(d->in_exponent));
+            q = fround(logf(tmp) * dl_rescale(d->out_exponent), d->round_mode);
+        } else if (d->op == ESPDL_REDUCE_LOG_SUM_EXP) { /* dl_module_reduce_log_sum_exp.hpp:62-68, 98-103 */
+            q = fround(logf(facc) * dl_rescale(d->out_exponent), d->round_mode);
         } else if (d->op == ESPDL_REDUCE_SUM || d->op == ESPDL_REDUCE_L1) {
             q = shift_and_round(acc, d->out_exponent - d->in_exponent, d->round_mode, is8 ? 32 : 64);
         } else if (d->op == ESPDL_REDUCE_SUM_SQUARE) { /* esp-dl/dl/module/include/dl_module_reduce_sum_square.hpp:36-39 */
@@ -999,6 +1043,42 @@ int oracle_norm(const espdl_norm_desc *d)
         return ESPDL_ERR_INVALID_ARG;
     const int is8 = d->dtype == ESPDL_DTYPE_INT8, mode = d->round_mode;
     const float input_scale = dl_scale(d->in_exponent), output_scale = dl_rescale(d->out_exponent);
+    if (d->op == ESPDL_NORM_LP) {
+        /* dl::module::LpNormalization::forward_int8 / forward_int16 with compute_quant_inv_norm(_strided)
+         * (esp-dl/dl/module/include/dl_module_lp_normalization.hpp:122-262, 328-356); math::fast_inv_sqrt is
+         * 1.0f / sqrtf(x) because DL_FAST_MATH is 0 (esp-dl/dl/dl_define_private.hpp:21, dl_math.hpp:60-72) */
+        const int64_t inner = d->inner > 1 ? d->inner : 1;
+        for (int64_t r = 0; r < d->rows; r++) {
+            const int64_t base = (r / inner) * d->len * inner + r % inner;
+            float inv_norm;
+            if (d->p == 1) {
+                float sum_abs = 0.0f;
+                for (int j = 0; j < d->len; j++) sum_abs += fabsf((float)load_int(d->input, d->dtype, base + j * inner));
+                inv_norm = sum_abs > 0.0f ? 1.0f / sum_abs : 0.0f;
+            } else {
+                int64_t sq = 0;
+                for (int j = 0; j < d->len; j++) {
+                    const int64_t v = load_int(d->input, d->dtype, base + j * inner);
+                    sq += v * v;
+                }
+                const float sum_sq = is8 ? (float)(int32_t)sq : (float)sq;
+                inv_norm = sum_sq > 0.0f ? 1.0f / sqrtf(sum_sq) : 0.0f;
+            }
+            if (inner == 1) { /* last axis: the scale is folded into the factor first (:153-160) */
+                inv_norm *= output_scale;
+                for (int j = 0; j < d->len; j++) {
+                    const float result = (float)load_int(d->input, d->dtype, base + j) * inv_norm;
+                    store_sat(d->output, d->dtype, base + j, inv_norm > 0.0f ? fround(result, mode) : 0);
+                }
+            } else { /* any other axis: two multiplications (:175-181) */
+                for (int j = 0; j < d->len; j++) {
+                    const float result = (float)load_int(d->input, d->dtype, base + j * inner) * inv_norm;
+                    store_sat(d->output, d->dtype, base + j * inner, inv_norm > 0.0f ? fround(result * output_scale, mode) : 0);
+                }
+            }
+        }
+        return ESPDL_OK;
+    }
     for (int64_t i = 0; i < d->rows; i++) {
         const int64_t base = i * d->len;
         if (d->op == ESPDL_NORM_RMS) { /* esp-dl/dl/module/include/dl_module_rms_normalization.hpp:57-84, dl_base_norm.cpp:16-20 */
@@ -1043,6 +1123,67 @@ int oracle_norm(const espdl_norm_desc *d)
                 const float bias_val = d->bias ? (float)load_int(d->bias, d->dtype, j) * bias_scale : 0.0f;
                 const float result = normalized * scale_val + bias_val;
                 store_sat(d->output, d->dtype, base + j, fround(result * output_scale, mode));
+            }
+        }
+    }
+    return ESPDL_OK;
+}
+
+/* ---------------------------------------------------------------- ReverseSequence, ScatterND */
+/* dl::module::ReverseSequence::reverse_sequence_impl (esp-dl/dl/module/include/dl_module_reverse_sequence.hpp:14-58):
+ * copy, then for every batch swap time steps t and len-1-t for t < len/2. */
+int oracle_reverse_sequence(const espdl_reverse_sequence_desc *d, const int64_t *seq_lens_host)
+{
+    if (!d || !d->input || !d->output || !seq_lens_host)
+        return ESPDL_ERR_INVALID_ARG;
+    const int64_t es = d->elem_size, total = (int64_t)d->dim0 * d->dim1 * d->feature;
+    memcpy(d->output, d->input, (size_t)(total * es));
+    const int batch = d->batch_axis == 0 ? d->dim0 : d->dim1, time = d->batch_axis == 0 ? d->dim1 : d->dim0;
+    const int64_t batch_stride = d->batch_axis == 0 ? d->dim1 * d->feature : d->feature;
+    const int64_t time_stride = d->batch_axis == 0 ? d->feature : d->dim1 * d->feature;
+    uint8_t *out = (uint8_t *)d->output;
+    for (int b = 0; b < batch; b++) {
+        const int len = (int)seq_lens_host[b];
+        if (len <= 1 || len > time)
+            continue;
+        for (int t = 0; t < len / 2; t++) {
+            uint8_t *p1 = out + (b * batch_stride + t * time_stride) * es, *p2 = out + (b * batch_stride + (len - 1 - t) * time_stride) * es;
+            for (int64_t i = 0; i < d->feature * es; i++) {
+                const uint8_t tmp = p1[i];
+                p1[i] = p2[i];
+                p2[i] = tmp;
+            }
+        }
+    }
+    return ESPDL_OK;
+}
+
+/* dl::module::ScatterND::forward_template with apply_reduction (esp-dl/dl/module/include/dl_module_scatter_nd.hpp:34-103,
+ * 160-228): slices in order, add / mul saturate after every update. */
+int oracle_scatter_nd(const espdl_scatter_nd_desc *d)
+{
+    if (!d || !d->data || !d->output)
+        return ESPDL_ERR_INVALID_ARG;
+    const int64_t es = d->dtype == ESPDL_DTYPE_INT8 ? 1 : (d->dtype == ESPDL_DTYPE_INT16 ? 2 : 4);
+    if (d->data != d->output)
+        memcpy(d->output, d->data, (size_t)(d->data_size * es));
+    for (int s = 0; s < d->n_slices; s++) {
+        int64_t flat = 0;
+        for (int k = 0; k < d->index_depth; k++) flat += d->indices[(int64_t)s * d->index_depth + k] * d->axis_offset[k];
+        if (flat < 0 || flat + d->slice_size > d->data_size)
+            continue;
+        for (int64_t i = 0; i < d->slice_size; i++) {
+            const int64_t o = flat + i, u = (int64_t)s * d->slice_size + i;
+            if (d->dtype == ESPDL_DTYPE_FLOAT) {
+                float *out = (float *)d->output;
+                const float cur = out[o], upd = ((const float *)d->updates)[u];
+                out[o] = d->reduction == ESPDL_SCATTER_ADD ? cur + upd : d->reduction == ESPDL_SCATTER_MUL ? cur * upd
+                    : d->reduction == ESPDL_SCATTER_MAX ? (cur > upd ? cur : upd) : d->reduction == ESPDL_SCATTER_MIN ? (cur < upd ? cur : upd) : upd;
+            } else {
+                const int64_t cur = load_int(d->output, d->dtype, o), upd = load_int(d->updates, d->dtype, u);
+                const int64_t v = d->reduction == ESPDL_SCATTER_ADD ? cur + upd : d->reduction == ESPDL_SCATTER_MUL ? cur * upd
+                    : d->reduction == ESPDL_SCATTER_MAX ? (cur > upd ? cur : upd) : d->reduction == ESPDL_SCATTER_MIN ? (cur < upd ? cur : upd) : upd;
+                store_sat(d->output, d->dtype, o, v);
             }
         }
     }

@@ -38,6 +38,8 @@
 #include "dl_module_gemm.hpp"
 #include "dl_module_insert_zeros.hpp"
 #include "dl_module_layer_normalization.hpp"
+#include "dl_module_log_softmax.hpp"
+#include "dl_module_lp_normalization.hpp"
 #include "dl_module_global_average_pool.hpp"
 #include "dl_module_lut.hpp"
 #include "dl_module_matmul.hpp"
@@ -47,18 +49,24 @@
 #include "dl_module_mod.hpp"
 #include "dl_module_mul.hpp"
 #include "dl_module_pad.hpp"
+#include "dl_module_pow.hpp"
 #include "dl_module_prelu.hpp"
 #include "dl_module_reduce_l1.hpp"
 #include "dl_module_reduce_l2.hpp"
+#include "dl_module_reduce_log_sum.hpp"
+#include "dl_module_reduce_log_sum_exp.hpp"
 #include "dl_module_reduce_max.hpp"
 #include "dl_module_reduce_mean.hpp"
 #include "dl_module_reduce_min.hpp"
+#include "dl_module_reduce_prod.hpp"
 #include "dl_module_reduce_sum.hpp"
 #include "dl_module_reduce_sum_square.hpp"
 #include "dl_module_relu.hpp"
 #include "dl_module_requantize_linear.hpp"
 #include "dl_module_resize.hpp"
+#include "dl_module_reverse_sequence.hpp"
 #include "dl_module_rms_normalization.hpp"
+#include "dl_module_scatter_nd.hpp"
 #include "dl_module_softmax.hpp"
 #include "dl_module_space_to_depth.hpp"
 #include "dl_module_sub.hpp"
@@ -166,7 +174,8 @@ int ref_eltwise(const espdl_eltwise_desc *d)
     case ESPDL_ELT_GREATER_EQUAL:
     case ESPDL_ELT_EQUAL:
     case ESPDL_ELT_LESS:
-    case ESPDL_ELT_LESS_EQUAL: {
+    case ESPDL_ELT_LESS_EQUAL:
+    case ESPDL_ELT_POW: {
         std::unique_ptr<TensorBase> in1(view(s1, d->input1, d->in1_exponent, d->in_dtype));
         std::unique_ptr<module::Module> m;
         if (d->op == ESPDL_ELT_ADD)
@@ -191,6 +200,8 @@ int ref_eltwise(const espdl_eltwise_desc *d)
             m.reset(new module::Less(nullptr, MODULE_NON_INPLACE, qt));
         else if (d->op == ESPDL_ELT_LESS_EQUAL)
             m.reset(new module::LessOrEqual(nullptr, MODULE_NON_INPLACE, qt));
+        else if (d->op == ESPDL_ELT_POW)
+            m.reset(new module::Pow(nullptr, MODULE_NON_INPLACE, qt));
         else
             m.reset(new module::Mul(nullptr, MODULE_NON_INPLACE, qt));
         m->run({in0.get(), in1.get()}, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
@@ -295,6 +306,17 @@ int ref_softmax(const espdl_softmax_desc *d, int in_exponent)
 {
     if (!d || d->out_dtype != ESPDL_DTYPE_FLOAT)
         return ESPDL_ERR_UNSUPPORTED;
+    if (d->log) { /* LogSoftmax along axis 1 of [outer, len, inner] */
+        const int inner = d->inner > 1 ? d->inner : 1;
+        std::vector<int> shape = {d->rows / inner, d->len, inner};
+        if (inner == 1)
+            shape.pop_back();
+        std::unique_ptr<TensorBase> in(view(shape, d->input, in_exponent, ESPDL_DTYPE_INT8));
+        std::unique_ptr<TensorBase> out(view(shape, d->output, 0, ESPDL_DTYPE_FLOAT));
+        module::LogSoftmax m(nullptr, 1, MODULE_NON_INPLACE, QUANT_TYPE_SYMM_8BIT);
+        m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+        return ESPDL_OK;
+    }
     std::unique_ptr<TensorBase> in(view({d->rows, d->len}, d->input, in_exponent, ESPDL_DTYPE_INT8));
     std::unique_ptr<TensorBase> out(view({d->rows, d->len}, d->output, 0, ESPDL_DTYPE_FLOAT));
     module::Softmax m(nullptr, -1, MODULE_NON_INPLACE, QUANT_TYPE_SYMM_8BIT);
@@ -350,6 +372,12 @@ int ref_reduce(const espdl_reduce_desc *d)
         m.reset(new module::ReduceSumSquare(1, flags, "ReduceSumSquare", "reduce", MODULE_NON_INPLACE, q));
     else if (d->op == ESPDL_REDUCE_L2)
         m.reset(new module::ReduceL2(1, flags, "ReduceL2", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_PROD)
+        m.reset(new module::ReduceProd(1, flags, "ReduceProd", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_LOG_SUM)
+        m.reset(new module::ReduceLogSum(1, flags, "ReduceLogSum", "reduce", MODULE_NON_INPLACE, q));
+    else if (d->op == ESPDL_REDUCE_LOG_SUM_EXP)
+        m.reset(new module::ReduceLogSumExp(1, flags, "ReduceLogSumExp", "reduce", MODULE_NON_INPLACE, q));
     else
         m.reset(new module::ReduceMin(1, flags, "ReduceMin", "reduce", MODULE_NON_INPLACE, q));
     std::vector<std::vector<int>> in_shapes = {shape};
@@ -512,4 +540,43 @@ int ref_norm_quant_table(void *table, const float *mean, const float *std, int e
     return 0;
 }
 
+
+/* LpNormalization along axis 1 of [outer, len, inner] (inner == 1: the last axis of [outer, len]). */
+int ref_lp_norm(const espdl_norm_desc *d)
+{
+    const int inner = d->inner > 1 ? (int)d->inner : 1;
+    std::vector<int> shape = {(int)(d->rows / inner), d->len, inner};
+    if (inner == 1)
+        shape.pop_back();
+    std::unique_ptr<TensorBase> in(view(shape, d->input, d->in_exponent, d->dtype)), out(view(shape, d->output, d->out_exponent, d->dtype));
+    module::LpNormalization m(1, d->p, nullptr, MODULE_NON_INPLACE, to_quant(d->dtype));
+    m.run(in.get(), out.get(), RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* ReverseSequence: input [dim0, dim1, feature], seq_lens int64[batch] on the host. */
+int ref_reverse_sequence(const espdl_reverse_sequence_desc *d, const int64_t *seq_lens)
+{
+    const int batch = d->batch_axis == 0 ? d->dim0 : d->dim1;
+    std::vector<int> shape = {d->dim0, d->dim1, (int)d->feature};
+    const int dt = d->elem_size == 1 ? ESPDL_DTYPE_INT8 : (d->elem_size == 2 ? ESPDL_DTYPE_INT16 : ESPDL_DTYPE_FLOAT);
+    std::unique_ptr<TensorBase> in(view(shape, d->input, 0, dt)), out(view(shape, d->output, 0, dt));
+    std::unique_ptr<TensorBase> lens(view({batch}, seq_lens, 0, ESPDL_DTYPE_INT64));
+    module::ReverseSequence m(d->batch_axis, 1 - d->batch_axis, nullptr, MODULE_NON_INPLACE, to_quant(dt));
+    m.run({in.get(), lens.get()}, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* ScatterND: data of shape `shape`, indices [n_slices, index_depth] int64, updates [n_slices, slice dims...]. */
+int ref_scatter_nd(const espdl_scatter_nd_desc *d, const int *shape, int ndim)
+{
+    static const char *names[] = {"none", "add", "mul", "max", "min"};
+    std::vector<int> ds(shape, shape + ndim), is = {d->n_slices, d->index_depth}, us = {d->n_slices};
+    for (int i = d->index_depth; i < ndim; i++) us.push_back(shape[i]);
+    std::unique_ptr<TensorBase> data(view(ds, d->data, 0, d->dtype)), out(view(ds, d->output, 0, d->dtype));
+    std::unique_ptr<TensorBase> idx(view(is, d->indices, 0, ESPDL_DTYPE_INT64)), upd(view(us, d->updates, 0, d->dtype));
+    module::ScatterND m(names[d->reduction], nullptr, MODULE_NON_INPLACE, to_quant(d->dtype));
+    m.run({data.get(), idx.get(), upd.get()}, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
 } /* extern "C" */

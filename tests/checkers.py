@@ -33,6 +33,10 @@ def oracle():
         lib.oracle_num_threads.restype = C.c_int
         lib.oracle_depth_space.restype = C.c_int
         lib.oracle_depth_space.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 7
+        lib.oracle_reverse_sequence.restype = C.c_int
+        lib.oracle_reverse_sequence.argtypes = [C.POINTER(abi.ReverseSequenceDesc), C.c_void_p]
+        lib.oracle_scatter_nd.restype = C.c_int
+        lib.oracle_scatter_nd.argtypes = [C.POINTER(abi.ScatterNDDesc)]
         _oracle = lib
     return _oracle
 
@@ -71,6 +75,12 @@ def ref():
         lib.ref_insert_zeros.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]
         lib.ref_depth_space.restype = C.c_int
         lib.ref_depth_space.argtypes = [C.c_void_p, C.c_void_p] + [C.c_int] * 7
+        lib.ref_lp_norm.restype = C.c_int
+        lib.ref_lp_norm.argtypes = [C.POINTER(abi.NormDesc)]
+        lib.ref_reverse_sequence.restype = C.c_int
+        lib.ref_reverse_sequence.argtypes = [C.POINTER(abi.ReverseSequenceDesc), C.c_void_p]
+        lib.ref_scatter_nd.restype = C.c_int
+        lib.ref_scatter_nd.argtypes = [C.POINTER(abi.ScatterNDDesc), C.POINTER(C.c_int), C.c_int]
         _ref = lib
     return _ref
 

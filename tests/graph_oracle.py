@@ -129,12 +129,12 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             st = o.oracle_conv2d(cases.conv_desc(case))
             assert st == 0, (node["name"], st)
             t[outs[0]] = case["out"].reshape(out_shape)
-        elif op in ("Add", "Sub", "Mul", "Div", "Max", "Min", "Mod"):
+        elif op in ("Add", "Sub", "Mul", "Div", "Max", "Min", "Mod", "Pow"):
             a, b = t[ins[0]], t.get(ins[1], None)
             if b is None:
                 b = init[ins[1]]["data"]
             eop = {"Add": abi.ELT_ADD, "Sub": abi.ELT_SUB, "Mul": abi.ELT_MUL, "Div": abi.ELT_DIV, "Max": abi.ELT_MAX, "Min": abi.ELT_MIN,
-                   "Mod": abi.ELT_MOD}[op]
+                   "Mod": abi.ELT_MOD, "Pow": abi.ELT_POW}[op]
             out_shape = np.broadcast_shapes(a.shape, b.shape)
             nd = len(out_shape)
             case = cases.eltwise_case(eop, dtype=QDT[at["quant_type"]], out_shape=out_shape, in0_shape=(1,) * (nd - a.ndim) + a.shape,
@@ -211,6 +211,51 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             for name, sz in zip(outs, sizes):
                 t[name] = np.ascontiguousarray(np.take(x, range(pos, pos + sz), axis=ax))
                 pos += sz
+        elif op == "LpNormalization":
+            ax = at.get("axis", -1) % x.ndim
+            d = abi.NormDesc()
+            d.op, d.dtype, d.len, d.p = abi.NORM_LP, QDT[at["quant_type"]], x.shape[ax], at.get("p", 2)
+            d.inner = int(np.prod(x.shape[ax + 1:], dtype=np.int64))
+            d.rows = x.size // x.shape[ax]
+            d.in_exponent, d.out_exponent, d.round_mode = exps[ins[0]], exps[outs[0]], round_mode
+            xc, y = np.ascontiguousarray(x), np.zeros_like(x)
+            d.input, d.output = xc.ctypes.data, y.ctypes.data
+            assert o.oracle_norm(C.byref(d)) == 0
+            t[outs[0]] = y
+        elif op == "ReverseSequence":
+            lens = np.ascontiguousarray(t[ins[1]] if ins[1] in t else init[ins[1]]["data"]).astype(np.int64)
+            d = abi.ReverseSequenceDesc()
+            d.elem_size, d.batch_axis, d.dim0, d.dim1 = x.dtype.itemsize, at.get("batch_axis", 1), x.shape[0], x.shape[1]
+            d.feature = int(np.prod(x.shape[2:], dtype=np.int64))
+            xc, y = np.ascontiguousarray(x), np.zeros_like(x)
+            d.input, d.output = xc.ctypes.data, y.ctypes.data
+            assert o.oracle_reverse_sequence(C.byref(d), lens.ctypes.data) == 0
+            t[outs[0]] = y
+        elif op == "ScatterND":
+            idx = np.ascontiguousarray(t[ins[1]] if ins[1] in t else init[ins[1]]["data"].reshape(init[ins[1]]["dims"])).astype(np.int64)
+            upd = np.ascontiguousarray(t[ins[2]] if ins[2] in t else init[ins[2]]["data"].reshape(init[ins[2]]["dims"]))
+            d = abi.ScatterNDDesc()
+            depth = idx.shape[-1]
+            d.dtype, d.index_depth, d.n_slices = QDT[at["quant_type"]], depth, idx.size // depth
+            d.reduction = {"none": 0, "add": 1, "mul": 2, "max": 3, "min": 4}.get(at.get("reduction", "none"), 0)
+            d.slice_size, d.data_size = int(np.prod(x.shape[depth:], dtype=np.int64)), x.size
+            for k in range(depth):
+                d.axis_offset[k] = int(np.prod(x.shape[k + 1:], dtype=np.int64))
+            xc, y = np.ascontiguousarray(x), np.zeros_like(x)
+            d.data, d.indices, d.updates, d.output = xc.ctypes.data, idx.ctypes.data, upd.ctypes.data, y.ctypes.data
+            assert o.oracle_scatter_nd(C.byref(d)) == 0
+            t[outs[0]] = y
+        elif op == "LogSoftmax":
+            ax = at.get("axis", -1) % x.ndim
+            table = np.zeros(256, dtype=np.float32)
+            o.oracle_softmax_table(table.ctypes.data, exps[ins[0]])
+            d = abi.SoftmaxDesc()
+            d.len, d.inner, d.log, d.in_exponent = x.shape[ax], int(np.prod(x.shape[ax + 1:], dtype=np.int64)), 1, exps[ins[0]]
+            d.rows, d.out_dtype = x.size // x.shape[ax], abi.DTYPE_FLOAT
+            xc, y = np.ascontiguousarray(x), np.zeros(x.shape, dtype=np.float32)
+            d.input, d.output, d.exp_table = xc.ctypes.data, y.ctypes.data, table.ctypes.data
+            assert o.oracle_softmax(C.byref(d)) == 0
+            t[outs[0]] = y
         elif op == "Softmax":
             ax = at.get("axis", -1) % x.ndim
             assert ax == x.ndim - 1
@@ -225,10 +270,11 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             e_b = exps[ins[1]] if ins[1] in exps else init[ins[1]]["exponents"][0]
             t[outs[0]] = matmul(o, x, b_op, exps[ins[0]], e_b, exps[outs[0]], QDT[at["quant_type"]],
                                 ACT[at.get("activation", "Linear")], round_mode)
-        elif op in ("ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin"):
+        elif op in ("ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin", "ReduceProd", "ReduceLogSum", "ReduceLogSumExp"):
             axes = [int(a) % x.ndim for a in init[ins[1]]["data"]] if len(ins) > 1 and ins[1] in init else list(range(x.ndim))
             d = abi.ReduceDesc()
-            d.op = {"ReduceMean": abi.REDUCE_MEAN, "ReduceSum": abi.REDUCE_SUM, "ReduceMax": abi.REDUCE_MAX, "ReduceMin": abi.REDUCE_MIN}[op]
+            d.op = {"ReduceMean": abi.REDUCE_MEAN, "ReduceSum": abi.REDUCE_SUM, "ReduceMax": abi.REDUCE_MAX, "ReduceMin": abi.REDUCE_MIN,
+                    "ReduceProd": abi.REDUCE_PROD, "ReduceLogSum": abi.REDUCE_LOG_SUM, "ReduceLogSumExp": abi.REDUCE_LOG_SUM_EXP}[op]
             d.dtype, d.ndim = QDT[at["quant_type"]], x.ndim
             for i, sz in enumerate(x.shape):
                 d.shape[i], d.reduce[i] = sz, int(i in axes)

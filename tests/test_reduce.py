@@ -1,5 +1,7 @@
-"""ReduceMean / ReduceSum / ReduceMax / ReduceMin / ReduceL1 / ReduceSumSquare / ReduceL2: the oracle against the reference's own modules compiled for the
-host (pin), the CUDA kernel against the oracle."""
+"""ReduceMean / ReduceSum / ReduceMax / ReduceMin / ReduceL1 / ReduceSumSquare / ReduceL2 / ReduceProd / ReduceLogSum /
+ReduceLogSumExp: the oracle against the reference's own modules compiled for the host (pin), the CUDA kernel against the
+oracle.  The two logarithm reductions call logf / expf on the device: their results may differ from the host's by one
+code where the last bit of logf decides a rounding; everything else is bit-exact."""
 import ctypes as C
 
 import numpy as np
@@ -13,11 +15,15 @@ SHAPES = [((2, 7, 7, 40), (1, 2)), ((3, 5, 6, 8), (3,)), ((4, 9, 16), (0, 2)), (
           ((2, 3, 4, 5), (0, 3)), ((17,), (0,))]
 
 
-def make(op, dtype, shape, axes, e_in, e_out, seed, inp=None, out=None):
+def make(op, dtype, shape, axes, e_in, e_out, seed, inp=None, out=None, keep=None):
     rng = np.random.default_rng(seed)
     t = np.int8 if dtype == abi.DTYPE_INT8 else np.int16
     info = np.iinfo(t)
     x = rng.integers(info.min, info.max + 1, size=shape, dtype=t)
+    if op == abi.REDUCE_LOG_SUM:      # a sum that has a logarithm
+        x = np.abs(x.astype(np.int32)).clip(0, info.max).astype(t)
+    if op == abi.REDUCE_PROD:         # factors around one, so that products of a few dozen of them stay in range
+        x = (x.astype(np.int32) // 3 + (info.max + 1) // 2).clip(info.min, info.max).astype(t)
     kept = [s for i, s in enumerate(shape) if i not in axes] or [1]
     y = np.zeros(kept, dtype=t)
     d = abi.ReduceDesc()
@@ -27,10 +33,19 @@ def make(op, dtype, shape, axes, e_in, e_out, seed, inp=None, out=None):
     d.in_exponent, d.out_exponent, d.round_mode = e_in, e_out, abi.ROUND_HALF_UP
     d.input = x.ctypes.data if inp is None else inp
     d.output = y.ctypes.data if out is None else out
+    if op == abi.REDUCE_LOG_SUM_EXP and dtype == abi.DTYPE_INT8:
+        # tool::gen_lut_8bit(expf) as the host module builds it
+        table = np.zeros(256, dtype=np.float32)
+        checkers.oracle().oracle_softmax_table(table.ctypes.data, e_in)
+        if keep is not None:
+            keep.append(table)
+        d.exp_table = table.ctypes.data
+        d._table = table
     return d, x, y
 
 
-CASES = [(op, dt, sh, ax) for op in range(7) for dt in (abi.DTYPE_INT8, abi.DTYPE_INT16) for sh, ax in SHAPES]
+CASES = [(op, dt, sh, ax) for op in range(10) for dt in (abi.DTYPE_INT8, abi.DTYPE_INT16) for sh, ax in SHAPES]
+LOG_OPS = (abi.REDUCE_LOG_SUM, abi.REDUCE_LOG_SUM_EXP)
 
 
 def exps(op, dt):
@@ -44,6 +59,12 @@ def exps(op, dt):
         return (-6, 0) if dt == abi.DTYPE_INT8 else (-14, -7)
     if op == abi.REDUCE_L2:
         return (-6, -3) if dt == abi.DTYPE_INT8 else (-14, -11)
+    if op == abi.REDUCE_PROD:
+        return (-6, -5) if dt == abi.DTYPE_INT8 else (-14, -12)
+    if op == abi.REDUCE_LOG_SUM:
+        return (-5, -4) if dt == abi.DTYPE_INT8 else (-12, -11)
+    if op == abi.REDUCE_LOG_SUM_EXP:
+        return (-5, -4) if dt == abi.DTYPE_INT8 else (-13, -11)
     return (-5, -5)
 
 
@@ -69,9 +90,14 @@ def test_gpu_matches_oracle(op, dt, shape, axes):
     with gpu_util.DeviceBuffers() as dev:
         out = dev.upload(np.full_like(want, 0x55))
         dg, _, _ = make(op, dt, shape, axes, e_in, e_out, seed=7, inp=dev.upload(x), out=out)
+        if dg.exp_table:
+            dg.exp_table = dev.upload(dg._table)
         abi.check(dev.lib.espdl_b200_reduce(C.byref(dg), None), "reduce")
         got = dev.download(out, want)
-    np.testing.assert_array_equal(got, want)
+    if op in LOG_OPS:  # logf / expf on the device: one code where their last bit decides the rounding
+        assert np.abs(got.astype(np.int32) - want.astype(np.int32)).max() <= 1
+    else:
+        np.testing.assert_array_equal(got, want)
 
 
 @pytest.mark.gpu
