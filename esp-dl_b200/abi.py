@@ -158,6 +158,18 @@ class ScatterNDDesc(C.Structure):
 SCATTER_NONE, SCATTER_ADD, SCATTER_MUL, SCATTER_MAX, SCATTER_MIN = range(5)
 
 
+class RnnDesc(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("w", C.c_void_p), ("r", C.c_void_p), ("b", C.c_void_p), ("initial_h", C.c_void_p),
+                ("initial_c", C.c_void_p), ("y", C.c_void_p), ("y_h", C.c_void_p), ("y_c", C.c_void_p), ("sigmoid_table", C.c_void_p),
+                ("tanh_table", C.c_void_p), ("sigmoid_max", i32), ("tanh_max", i32), ("op", i32), ("dtype", i32), ("seq_length", i32),
+                ("input_size", i32), ("hidden_size", i32), ("directions", i32), ("x_exponent", i32), ("w_exponent", i32),
+                ("r_exponent", i32), ("h_exponent", i32), ("y_exponent", i32), ("c_exponent", i32), ("gate_exponent", i32),
+                ("round_mode", i32)]
+
+
+RNN_GRU, RNN_LSTM = range(2)
+
+
 class GatherDesc(C.Structure):
     _fields_ = [("input", C.c_void_p), ("output", C.c_void_p), ("indices", C.c_void_p), ("elem_size", i32), ("num_indices", i32),
                 ("outer", C.c_int64), ("axis_size", C.c_int64), ("inner", C.c_int64)]
@@ -215,6 +227,7 @@ SYMBOLS = {
     "espdl_b200_norm": (C.c_int, [C.POINTER(NormDesc), C.c_void_p]),
     "espdl_b200_reverse_sequence": (C.c_int, [C.POINTER(ReverseSequenceDesc), C.c_void_p]),
     "espdl_b200_scatter_nd": (C.c_int, [C.POINTER(ScatterNDDesc), C.c_void_p]),
+    "espdl_b200_rnn": (C.c_int, [C.POINTER(RnnDesc), C.c_void_p]),
 }
 
 _lib = None

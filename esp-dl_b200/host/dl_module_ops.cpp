@@ -2283,6 +2283,124 @@ Module *ScatterND::deserialize(fbs::FbsModel *m, std::string node)
     return new ScatterND(reduction, node.c_str(), MODULE_INPLACE_CHANGED_BUFFER, node_quant(m, node));
 }
 
+// --------------------------------------------------------------------------------- GRU, LSTM
+Rnn::~Rnn()
+{
+    if (m_dev_sigmoid)
+        espdl_b200_arena_free(m_dev_sigmoid);
+    if (m_dev_tanh)
+        espdl_b200_arena_free(m_dev_tanh);
+}
+
+std::vector<std::vector<int>> Rnn::get_output_shape(std::vector<std::vector<int>> &input_shapes)
+{
+    // dl_module_gru.hpp:80-101, dl_module_lstm.hpp:86-112
+    std::vector<std::vector<int>> out;
+    if (input_shapes.size() < 3 || input_shapes[0].size() < 3)
+        return out;
+    const std::vector<int> &x = input_shapes[0];
+    const int seq = m_layout == 0 ? x[0] : x[1], batch = m_layout == 0 ? x[1] : x[0];
+    out.push_back({seq, m_direction_num, batch, m_hidden_size});
+    out.push_back({m_direction_num, batch, m_hidden_size});
+    if (m_op == ESPDL_RNN_LSTM)
+        out.push_back({m_direction_num, batch, m_hidden_size});
+    return out;
+}
+
+// math::sigmoid / math::tanh and the two tables of esp-dl/dl/math/include/dl_math.hpp:168-176, 324-429
+static float rnn_sigmoid(float x) { return (float)(1.0 / (1.0 + expf(-x))); }
+static float rnn_tanh(float x) { return 2 * rnn_sigmoid(2 * x) - 1; }
+static int rnn_table(int gate_exponent, bool tanh_table, std::vector<float> &table)
+{
+    const float bound = tanh_table ? (float)3.5 : (float)6.3, input_scale = DL_SCALE(gate_exponent);
+    int quant_min = (int)(-bound / input_scale) - 1, quant_max = (int)(bound / input_scale) + 1;
+    if (-quant_min > quant_max)
+        quant_max = -quant_min;
+    table.resize((size_t)quant_max + 1);
+    for (int i = 0; i <= quant_max; i++) table[i] = tanh_table ? rnn_tanh(i * input_scale) : rnn_sigmoid(i * input_scale);
+    return quant_max;
+}
+
+esp_err_t Rnn::prepare(ModelContext *context)
+{
+    if (m_gate_exponent > 0 || m_gate_exponent < -14) // the tables would be empty or hold millions of entries
+        return ESP_FAIL;
+    for (int which = 0; which < 2; which++) {
+        std::vector<float> table;
+        const int mx = rnn_table(m_gate_exponent, which == 1, table);
+        void *&dev = which ? m_dev_tanh : m_dev_sigmoid;
+        (which ? m_tanh_max : m_sigmoid_max) = mx;
+        if (!dev && espdl_b200_arena_alloc(table.size() * sizeof(float), &dev) != ESPDL_OK)
+            return ESP_FAIL;
+        if (espdl_b200_upload(dev, table.data(), table.size() * sizeof(float), nullptr) != ESPDL_OK)
+            return ESP_FAIL;
+    }
+    return upload_parameters(context, m_inputs_index);
+}
+
+void Rnn::forward(ModelContext *context, runtime_mode_t mode)
+{
+    (void)mode;
+    auto in = [&](size_t i) { return m_inputs_index.size() > i ? context->get_tensor(m_inputs_index[i]) : nullptr; };
+    auto out = [&](size_t i) { return m_outputs_index.size() > i ? context->get_tensor(m_outputs_index[i]) : nullptr; };
+    TensorBase *x = in(0), *w = in(1), *r = in(2), *b = in(3), *h0 = in(5), *c0 = m_op == ESPDL_RNN_LSTM ? in(6) : nullptr;
+    TensorBase *y = out(0), *yh = out(1), *yc = m_op == ESPDL_RNN_LSTM ? out(2) : nullptr;
+    int st = (!x || !w || !r || !y || !yh || !x->device || !w->device || !r->device || !y->device || !yh->device || x->shape.size() != 3)
+        ? ESPDL_ERR_INVALID_ARG
+        : ESPDL_OK;
+    if (!st && ((b && !b->device) || (h0 && !h0->device) || (c0 && !c0->device) || (yc && !yc->device)))
+        st = ESPDL_ERR_INVALID_ARG;
+    if (!st) {
+        const int G = m_op == ESPDL_RNN_GRU ? 3 : 4, H = m_hidden_size;
+        const int seq = m_layout == 0 ? x->shape[0] : x->shape[1], batch = m_layout == 0 ? x->shape[1] : x->shape[0], isz = x->shape[2];
+        // what the reference supports (dl_module_gru.hpp:161, dl_module_lstm.hpp:179): one sequence at a time; the weights'
+        // shapes as its first step checks them; an int16 bias at the gates' exponent; an int16 cell state at that exponent
+        const bool shapes_ok = batch == 1 && w->shape == std::vector<int>({m_direction_num, G * H, isz}) &&
+            r->shape == std::vector<int>({m_direction_num, G * H, H}) && (!b || (b->dtype == DATA_TYPE_INT16 && b->get_size() >= m_direction_num * 2 * G * H)) &&
+            (!h0 || h0->get_size() >= m_direction_num * H) && (!c0 || (c0->dtype == DATA_TYPE_INT16 && c0->get_size() >= m_direction_num * H)) &&
+            (!yc || (yc->dtype == DATA_TYPE_INT16 && (int)yc->exponent == m_gate_exponent));
+        if (!shapes_ok || x->dtype != w->dtype || x->dtype != r->dtype || y->dtype != x->dtype || yh->dtype != x->dtype || (h0 && h0->dtype != x->dtype)) {
+            st = ESPDL_ERR_UNSUPPORTED;
+        } else {
+            espdl_rnn_desc d;
+            memset(&d, 0, sizeof(d));
+            d.x = x->device, d.w = w->device, d.r = r->device, d.b = b ? (const int16_t *)b->device : nullptr;
+            d.initial_h = h0 ? h0->device : nullptr, d.initial_c = c0 ? (const int16_t *)c0->device : nullptr;
+            d.y = y->device, d.y_h = yh->device, d.y_c = yc ? (int16_t *)yc->device : nullptr;
+            d.sigmoid_table = (const float *)m_dev_sigmoid, d.tanh_table = (const float *)m_dev_tanh;
+            d.sigmoid_max = m_sigmoid_max, d.tanh_max = m_tanh_max;
+            d.op = m_op, d.dtype = quant_dtype(quant_type), d.seq_length = seq, d.input_size = isz, d.hidden_size = H, d.directions = m_direction_num;
+            d.x_exponent = x->exponent, d.w_exponent = w->exponent, d.r_exponent = r->exponent, d.h_exponent = yh->exponent;
+            d.y_exponent = y->exponent, d.c_exponent = yc ? (int)yc->exponent : m_gate_exponent, d.gate_exponent = m_gate_exponent;
+            d.round_mode = context->round_mode;
+            st = espdl_b200_rnn(&d, context->stream);
+        }
+    }
+    if (st)
+        ESP_LOGE("Rnn", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+    context->note(st);
+}
+
+static Module *deserialize_rnn(fbs::FbsModel *m, const std::string &node, bool lstm)
+{
+    int hidden_size = 0, layout = 0, gate_exponent = -8, flag = lstm ? 0 : 0;
+    std::string direction = "forward";
+    m->get_operation_attribute(node, "hidden_size", hidden_size);
+    m->get_operation_attribute(node, "direction", direction);
+    m->get_operation_attribute(node, "layout", layout);
+    m->get_operation_attribute(node, "gate_exponent", gate_exponent);
+    m->get_operation_attribute(node, lstm ? "input_forget" : "linear_before_reset", flag);
+    // dl_module_gru.hpp:409-412: only the PyTorch form (linear_before_reset = 1); dl_module_lstm.hpp:480-483: no coupled gates
+    if ((!lstm && flag == 0) || (lstm && flag == 1) || hidden_size <= 0)
+        return nullptr;
+    const int dirs = direction == "bidirectional" ? 2 : 1;
+    if (lstm)
+        return new LSTM(node.c_str(), hidden_size, dirs, layout, gate_exponent, MODULE_NON_INPLACE, node_quant(m, node));
+    return new GRU(node.c_str(), hidden_size, dirs, layout, gate_exponent, MODULE_NON_INPLACE, node_quant(m, node));
+}
+Module *GRU::deserialize(fbs::FbsModel *m, std::string node) { return deserialize_rnn(m, node, false); }
+Module *LSTM::deserialize(fbs::FbsModel *m, std::string node) { return deserialize_rnn(m, node, true); }
+
 // --------------------------------------------------------------------------------- registry
 void ModuleCreator::register_dl_modules()
 {
@@ -2319,6 +2437,8 @@ void ModuleCreator::register_dl_modules()
     register_module("LpNormalization", LpNormalization::deserialize);
     register_module("ReverseSequence", ReverseSequence::deserialize);
     register_module("ScatterND", ScatterND::deserialize);
+    register_module("GRU", GRU::deserialize);
+    register_module("LSTM", LSTM::deserialize);
     register_module("Slice", Slice::deserialize);
     register_module("Pad", Pad::deserialize);
     register_module("Clip", Clip::deserialize);

@@ -597,6 +597,46 @@ protected:
     int m_batch_axis, m_time_axis;
 };
 
+/// GRU / LSTM, quantized, batch 1 (reference: dl_module_gru.hpp:12-449, dl_module_lstm.hpp:12-522): inputs X, W, R [, B,
+/// sequence_lens, initial_h [, initial_c]], outputs Y, Y_h [, Y_c].  The whole sequence is one kernel launch; the sigmoid and
+/// tanh tables (math::SigmoidLUT(-6.3, 6.3), math::TanhLUT(-3.5, 3.5) at gate_exponent) are built on the host.
+class Rnn : public Module {
+public:
+    Rnn(int op, const char *name, int hidden_size, int direction_num, int layout, int gate_exponent, module_inplace_t inplace,
+        quant_type_t quant_type) :
+        Module(name, inplace, quant_type), m_op(op), m_hidden_size(hidden_size), m_direction_num(direction_num), m_layout(layout),
+        m_gate_exponent(gate_exponent)
+    {
+    }
+    ~Rnn();
+    std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
+    esp_err_t prepare(ModelContext *context) override; ///< uploads W, R, B and the two tables
+    void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+
+protected:
+    int m_op, m_hidden_size, m_direction_num, m_layout, m_gate_exponent;
+    void *m_dev_sigmoid = nullptr, *m_dev_tanh = nullptr;
+    int m_sigmoid_max = 0, m_tanh_max = 0;
+};
+class GRU : public Rnn {
+public:
+    GRU(const char *name = nullptr, int hidden_size = 0, int direction_num = 1, int layout = 0, int gate_exponent = -8,
+        module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Rnn(0, name, hidden_size, direction_num, layout, gate_exponent, inplace, quant_type)
+    {
+    }
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+class LSTM : public Rnn {
+public:
+    LSTM(const char *name = nullptr, int hidden_size = 0, int direction_num = 1, int layout = 0, int gate_exponent = -8,
+         module_inplace_t inplace = MODULE_NON_INPLACE, quant_type_t quant_type = QUANT_TYPE_NONE) :
+        Rnn(1, name, hidden_size, direction_num, layout, gate_exponent, inplace, quant_type)
+    {
+    }
+    static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+};
+
 /// ScatterND (reference: dl_module_scatter_nd.hpp:20-264): inputs data, indices (int64), updates; reduction none / add / mul /
 /// max / min applied slice by slice in the order of the index tuples.
 class ScatterND : public Module {

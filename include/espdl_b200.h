@@ -580,6 +580,30 @@ typedef struct espdl_scatter_nd_desc {
 
 int espdl_b200_scatter_nd(const espdl_scatter_nd_desc *desc, void *stream);
 
+/* ---------------------------------------------------------- GRU, LSTM */
+/* dl::module::GRU / dl::module::LSTM, quantized (esp-dl/dl/module/include/dl_module_gru.hpp:114-256, dl_module_lstm.hpp:125-300):
+ * batch 1, sequence-major X [seq][1][input], W [dir][G*H][input], R [dir][G*H][H], B int16 [dir][2*G*H] at gate_exponent or
+ * NULL, initial_h [dir][1][H] or NULL; Y [seq][dir][1][H], Y_h [dir][1][H]; LSTM: initial_c / Y_c int16 [dir][1][H] at
+ * gate_exponent.  G = 3 (GRU: z, r, n; linear_before_reset = 1) or 4 (LSTM: i, o, f, c).  The tables are the host's
+ * math::SigmoidLUT / math::TanhLUT for gate_exponent: entries 0 .. max (esp-dl/dl/math/include/dl_math.hpp:324-429). */
+typedef enum { ESPDL_RNN_GRU = 0, ESPDL_RNN_LSTM = 1 } espdl_rnn_op_t;
+
+typedef struct espdl_rnn_desc {
+    const void *x, *w, *r;
+    const int16_t *b;
+    const void *initial_h;
+    const int16_t *initial_c;
+    void *y, *y_h;
+    int16_t *y_c;
+    const float *sigmoid_table, *tanh_table; /* device float[max + 1] */
+    int32_t sigmoid_max, tanh_max;
+    int32_t op, dtype;                       /* espdl_rnn_op_t; ESPDL_DTYPE_INT8 or ESPDL_DTYPE_INT16 */
+    int32_t seq_length, input_size, hidden_size, directions;
+    int32_t x_exponent, w_exponent, r_exponent, h_exponent, y_exponent, c_exponent, gate_exponent, round_mode;
+} espdl_rnn_desc;
+
+int espdl_b200_rnn(const espdl_rnn_desc *desc, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

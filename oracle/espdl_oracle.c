@@ -1189,3 +1189,119 @@ int oracle_scatter_nd(const espdl_scatter_nd_desc *d)
     }
     return ESPDL_OK;
 }
+
+/* ---------------------------------------------------------------- GRU, LSTM */
+/* math::sigmoid / math::tanh (esp-dl/dl/math/include/dl_math.hpp:168-176): 1.0 / (1.0 + expf(-x)) in double, narrowed to
+ * float; tanh = 2 * sigmoid(2 * x) - 1 in float. */
+static float math_sigmoid(float x) { return (float)(1.0 / (1.0 + expf(-x))); }
+static float math_tanh(float x) { return 2 * math_sigmoid(2 * x) - 1; }
+
+/* Entry count - 1 of math::SigmoidLUT(e, -6.3, 6.3) (which = 0) or math::TanhLUT(e, -3.5, 3.5) (which = 1), and the table
+ * itself when `table` is not NULL (esp-dl/dl/math/include/dl_math.hpp:331-352, 385-405; the bounds as the modules pass them,
+ * dl_module_gru.hpp:49-50). */
+int oracle_rnn_table(int gate_exponent, int which, float *table)
+{
+    const float bound = which == 0 ? (float)6.3 : (float)3.5; /* a double literal passed to a float parameter */
+    const float input_scale = dl_scale(gate_exponent);
+    int quant_min = (int)(-bound / input_scale) - 1, quant_max = (int)(bound / input_scale) + 1;
+    if (-quant_min > quant_max)
+        quant_max = -quant_min;
+    if (table)
+        for (int i = 0; i <= quant_max; i++) table[i] = which == 0 ? math_sigmoid(i * input_scale) : math_tanh(i * input_scale);
+    return quant_max;
+}
+
+typedef struct {
+    const float *t;
+    int max;
+} rnn_lut;
+
+static float sigmoid_get(const rnn_lut *l, int index) /* SigmoidLUT::get, dl_math.hpp:360-375 */
+{
+    if (index >= 0)
+        return index < l->max ? l->t[index] : l->t[l->max];
+    return index > -l->max ? 1 - l->t[-index] : 1 - l->t[l->max];
+}
+
+static float tanh_get(const rnn_lut *l, int index) /* TanhLUT::get, dl_math.hpp:413-428 */
+{
+    if (index >= 0)
+        return index < l->max ? l->t[index] : l->t[l->max];
+    return index > -l->max ? -l->t[-index] : -l->t[l->max];
+}
+
+/* base::mat_vec_dotprod with dotprod_c (esp-dl/dl/base/dl_base_dotprod.hpp:36-43, dl_base_dotprod.cpp:8-42) */
+static void rnn_mat_vec(const void *matrix, int dtype, const int32_t *vector, int16_t *result, int rows, int cols, int shift, int mode)
+{
+    const float scale = dl_rescale(shift);
+    for (int i = 0; i < rows; i++) {
+        int64_t acc = 0;
+        for (int j = 0; j < cols; j++) acc += (int32_t)load_int(matrix, dtype, (int64_t)i * cols + j) * vector[j];
+        const float f = dtype == ESPDL_DTYPE_INT8 ? (float)(int32_t)acc * scale : (float)acc * scale;
+        result[i] = (int16_t)clamp64(fround(f, mode), -32768, 32767);
+    }
+}
+
+int oracle_rnn(const espdl_rnn_desc *d)
+{
+    if (!d || !d->x || !d->w || !d->r || !d->y || !d->y_h || !d->sigmoid_table || !d->tanh_table)
+        return ESPDL_ERR_INVALID_ARG;
+    const int H = d->hidden_size, G = d->op == ESPDL_RNN_GRU ? 3 : 4, GH = G * H, mode = d->round_mode, dt = d->dtype;
+    const rnn_lut sig = {d->sigmoid_table, d->sigmoid_max}, tnh = {d->tanh_table, d->tanh_max};
+    int32_t *h_prev = (int32_t *)calloc((size_t)H, 4), *xv = (int32_t *)calloc((size_t)d->input_size, 4);
+    int16_t *c_prev = (int16_t *)calloc((size_t)H, 2), *ic = (int16_t *)calloc((size_t)GH, 2), *hc = (int16_t *)calloc((size_t)GH, 2);
+    float *gates = (float *)calloc((size_t)GH, 4);
+    const float rescale_y = dl_rescale(d->y_exponent), rescale_c = dl_rescale(d->c_exponent);
+    const int w_shift = d->gate_exponent - (d->x_exponent + d->w_exponent), r_shift = d->gate_exponent - (d->h_exponent + d->r_exponent);
+    const int64_t lo = dt == ESPDL_DTYPE_INT8 ? -128 : -32768, hi = dt == ESPDL_DTYPE_INT8 ? 127 : 32767;
+    const int es = dt == ESPDL_DTYPE_INT8 ? 1 : 2;
+    for (int di = 0; di < d->directions; di++) {
+        const uint8_t *w = (const uint8_t *)d->w + (int64_t)di * GH * d->input_size * es, *r = (const uint8_t *)d->r + (int64_t)di * GH * H * es;
+        const int16_t *wb = d->b ? d->b + (int64_t)di * 2 * GH : NULL, *rb = wb ? wb + GH : NULL;
+        for (int i = 0; i < H; i++) {
+            h_prev[i] = d->initial_h ? (int32_t)load_int(d->initial_h, dt, di * H + i) : 0;
+            c_prev[i] = d->initial_c ? d->initial_c[di * H + i] : 0;
+        }
+        for (int step = 0; step < d->seq_length; step++) {
+            const int t = di == 0 ? step : d->seq_length - 1 - step; /* the reverse pass walks the pointers backwards */
+            for (int i = 0; i < d->input_size; i++) xv[i] = (int32_t)load_int(d->x, dt, (int64_t)t * d->input_size + i);
+            rnn_mat_vec(w, dt, xv, ic, GH, d->input_size, w_shift, mode);
+            rnn_mat_vec(r, dt, h_prev, hc, GH, H, r_shift, mode);
+            if (d->op == ESPDL_RNN_GRU) { /* dl_module_gru.hpp:216-242 */
+                if (wb)
+                    for (int i = 0; i < GH; i++) {
+                        ic[i] = (int16_t)(ic[i] + wb[i]);
+                        hc[i] = (int16_t)(hc[i] + rb[i]);
+                    }
+                for (int i = 0; i < 2 * H; i++) gates[i] = sigmoid_get(&sig, ic[i] + hc[i]);
+                for (int i = 0; i < H; i++) {
+                    const int index = fround(ic[i + 2 * H] + gates[H + i] * hc[i + 2 * H], mode);
+                    gates[2 * H + i] = tanh_get(&tnh, index);
+                }
+                for (int i = 0; i < H; i++) {
+                    float temp = (1 - gates[i]) * gates[2 * H + i] * rescale_y;
+                    temp += gates[i] * h_prev[i];
+                    h_prev[i] = (int32_t)clamp64(fround(temp, mode), lo, hi);
+                }
+            } else { /* dl_module_lstm.hpp:257-283 */
+                for (int i = 0; i < GH; i++) ic[i] = (int16_t)(ic[i] + (wb ? wb[i] + hc[i] + rb[i] : hc[i]));
+                for (int i = 0; i < H; i++) {
+                    const float ig = sigmoid_get(&sig, ic[i]), og = sigmoid_get(&sig, ic[H + i]);
+                    const float fg = sigmoid_get(&sig, ic[2 * H + i]), gg = tanh_get(&tnh, ic[3 * H + i]);
+                    float temp = fg * c_prev[i] + ig * gg * rescale_c;
+                    c_prev[i] = (int16_t)fround(temp, mode);
+                    temp = og * tanh_get(&tnh, c_prev[i]) * rescale_y;
+                    h_prev[i] = (int32_t)clamp64(fround(temp, mode), lo, hi);
+                }
+            }
+            for (int i = 0; i < H; i++) store_sat(d->y, dt, ((int64_t)t * d->directions + di) * H + i, h_prev[i]);
+        }
+        for (int i = 0; i < H; i++) {
+            store_sat(d->y_h, dt, di * H + i, h_prev[i]);
+            if (d->op == ESPDL_RNN_LSTM && d->y_c)
+                d->y_c[di * H + i] = c_prev[i];
+        }
+    }
+    free(h_prev), free(xv), free(c_prev), free(ic), free(hc), free(gates);
+    return ESPDL_OK;
+}

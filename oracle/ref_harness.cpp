@@ -32,6 +32,7 @@
 #include "dl_module_equal.hpp"
 #include "dl_module_greater.hpp"
 #include "dl_module_greater_or_equal.hpp"
+#include "dl_module_gru.hpp"
 #include "dl_module_less.hpp"
 #include "dl_module_less_or_equal.hpp"
 #include "dl_module_gather.hpp"
@@ -40,6 +41,7 @@
 #include "dl_module_layer_normalization.hpp"
 #include "dl_module_log_softmax.hpp"
 #include "dl_module_lp_normalization.hpp"
+#include "dl_module_lstm.hpp"
 #include "dl_module_global_average_pool.hpp"
 #include "dl_module_lut.hpp"
 #include "dl_module_matmul.hpp"
@@ -577,6 +579,47 @@ int ref_scatter_nd(const espdl_scatter_nd_desc *d, const int *shape, int ndim)
     std::unique_ptr<TensorBase> idx(view(is, d->indices, 0, ESPDL_DTYPE_INT64)), upd(view(us, d->updates, 0, d->dtype));
     module::ScatterND m(names[d->reduction], nullptr, MODULE_NON_INPLACE, to_quant(d->dtype));
     m.run({data.get(), idx.get(), upd.get()}, {out.get()}, RUNTIME_MODE_SINGLE_CORE);
+    return 0;
+}
+
+/* GRU / LSTM through the reference's own modules: inputs X, W, R, B, (sequence_lens, unused), initial_h, initial_c in the
+ * operator's input order; absent optional inputs end the list (an absent B with a present initial_h cannot be expressed
+ * by position and is not pinned). */
+int ref_rnn(const espdl_rnn_desc *d)
+{
+    const int H = d->hidden_size, G = d->op == ESPDL_RNN_GRU ? 3 : 4, D = d->directions;
+    std::unique_ptr<TensorBase> x(view({d->seq_length, 1, d->input_size}, d->x, d->x_exponent, d->dtype));
+    std::unique_ptr<TensorBase> w(view({D, G * H, d->input_size}, d->w, d->w_exponent, d->dtype));
+    std::unique_ptr<TensorBase> r(view({D, G * H, H}, d->r, d->r_exponent, d->dtype));
+    std::unique_ptr<TensorBase> b, lens, h0, c0;
+    int64_t seq_lens[1] = {d->seq_length};
+    std::vector<TensorBase *> ins = {x.get(), w.get(), r.get()};
+    if (d->b) {
+        b.reset(view({D, 2 * G * H}, d->b, d->gate_exponent, ESPDL_DTYPE_INT16));
+        ins.push_back(b.get());
+        if (d->initial_h) {
+            lens.reset(view({1}, seq_lens, 0, ESPDL_DTYPE_INT64));
+            h0.reset(view({D, 1, H}, d->initial_h, d->h_exponent, d->dtype));
+            ins.push_back(lens.get());
+            ins.push_back(h0.get());
+            if (d->op == ESPDL_RNN_LSTM && d->initial_c) {
+                c0.reset(view({D, 1, H}, d->initial_c, d->gate_exponent, ESPDL_DTYPE_INT16));
+                ins.push_back(c0.get());
+            }
+        }
+    } else if (d->initial_h) {
+        return ESPDL_ERR_UNSUPPORTED;
+    }
+    std::unique_ptr<TensorBase> y(view({d->seq_length, D, 1, H}, d->y, d->y_exponent, d->dtype));
+    std::unique_ptr<TensorBase> yh(view({D, 1, H}, d->y_h, d->h_exponent, d->dtype));
+    if (d->op == ESPDL_RNN_GRU) {
+        module::GRU m(nullptr, H, D, 0, d->gate_exponent, MODULE_NON_INPLACE, to_quant(d->dtype));
+        m.run(ins, {y.get(), yh.get()}, RUNTIME_MODE_SINGLE_CORE);
+    } else {
+        std::unique_ptr<TensorBase> yc(view({D, 1, H}, d->y_c, d->c_exponent, ESPDL_DTYPE_INT16));
+        module::LSTM m(nullptr, H, D, 0, d->gate_exponent, MODULE_NON_INPLACE, to_quant(d->dtype));
+        m.run(ins, {y.get(), yh.get(), yc.get()}, RUNTIME_MODE_SINGLE_CORE);
+    }
     return 0;
 }
 } /* extern "C" */

@@ -37,6 +37,10 @@ def oracle():
         lib.oracle_reverse_sequence.argtypes = [C.POINTER(abi.ReverseSequenceDesc), C.c_void_p]
         lib.oracle_scatter_nd.restype = C.c_int
         lib.oracle_scatter_nd.argtypes = [C.POINTER(abi.ScatterNDDesc)]
+        lib.oracle_rnn.restype = C.c_int
+        lib.oracle_rnn.argtypes = [C.POINTER(abi.RnnDesc)]
+        lib.oracle_rnn_table.restype = C.c_int
+        lib.oracle_rnn_table.argtypes = [C.c_int, C.c_int, C.c_void_p]
         _oracle = lib
     return _oracle
 
@@ -81,6 +85,8 @@ def ref():
         lib.ref_reverse_sequence.argtypes = [C.POINTER(abi.ReverseSequenceDesc), C.c_void_p]
         lib.ref_scatter_nd.restype = C.c_int
         lib.ref_scatter_nd.argtypes = [C.POINTER(abi.ScatterNDDesc), C.POINTER(C.c_int), C.c_int]
+        lib.ref_rnn.restype = C.c_int
+        lib.ref_rnn.argtypes = [C.POINTER(abi.RnnDesc)]
         _ref = lib
     return _ref
 

@@ -211,6 +211,41 @@ def run_graph(m, inputs, round_mode=abi.ROUND_HALF_UP, target=None, backend="por
             for name, sz in zip(outs, sizes):
                 t[name] = np.ascontiguousarray(np.take(x, range(pos, pos + sz), axis=ax))
                 pos += sz
+        elif op in ("GRU", "LSTM"):
+            def operand(i):
+                if i >= len(ins) or not ins[i]:
+                    return None, 0
+                if ins[i] in t:
+                    return np.ascontiguousarray(t[ins[i]]), exps[ins[i]]
+                return np.ascontiguousarray(init[ins[i]]["data"].reshape(init[ins[i]]["dims"])), (init[ins[i]]["exponents"] or [0])[0]
+            d = abi.RnnDesc()
+            hid, dirs = at["hidden_size"], 2 if at.get("direction", "forward") == "bidirectional" else 1
+            d.op, d.dtype = (abi.RNN_GRU if op == "GRU" else abi.RNN_LSTM), QDT[at["quant_type"]]
+            d.seq_length, d.input_size, d.hidden_size, d.directions = x.shape[0], x.shape[2], hid, dirs
+            (w, ew), (r, er), (b, _), (h0, _), (c0, _) = operand(1), operand(2), operand(3), operand(5), operand(6)
+            d.x_exponent, d.w_exponent, d.r_exponent = exps[ins[0]], ew, er
+            d.y_exponent, d.h_exponent = exps[outs[0]], exps[outs[1]]
+            d.c_exponent = d.gate_exponent = at.get("gate_exponent", -8)
+            d.round_mode = round_mode
+            tabs = []
+            for which in (0, 1):
+                n = o.oracle_rnn_table(d.gate_exponent, which, None)
+                tb = np.zeros(n + 1, dtype=np.float32)
+                o.oracle_rnn_table(d.gate_exponent, which, tb.ctypes.data)
+                tabs.append((tb, n))
+            xc = np.ascontiguousarray(x)
+            y = np.zeros((x.shape[0], dirs, 1, hid), dtype=x.dtype)
+            yh, yc = np.zeros((dirs, 1, hid), dtype=x.dtype), np.zeros((dirs, 1, hid), dtype=np.int16)
+            d.x, d.w, d.r = xc.ctypes.data, w.ctypes.data, r.ctypes.data
+            d.b = b.ctypes.data if b is not None else None
+            d.initial_h = h0.ctypes.data if h0 is not None else None
+            d.initial_c = c0.ctypes.data if c0 is not None else None
+            d.y, d.y_h, d.y_c = y.ctypes.data, yh.ctypes.data, yc.ctypes.data
+            d.sigmoid_table, d.tanh_table, d.sigmoid_max, d.tanh_max = tabs[0][0].ctypes.data, tabs[1][0].ctypes.data, tabs[0][1], tabs[1][1]
+            assert o.oracle_rnn(C.byref(d)) == 0
+            t[outs[0]], t[outs[1]] = y, yh
+            if op == "LSTM" and len(outs) > 2:
+                t[outs[2]] = yc
         elif op == "LpNormalization":
             ax = at.get("axis", -1) % x.ndim
             d = abi.NormDesc()
