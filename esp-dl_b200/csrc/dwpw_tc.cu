@@ -560,10 +560,6 @@ int fused_dwpw(const espdl_block_desc &d, cudaStream_t s)
     }
     const size_t smem = dp_smem_bytes(p);
     const int grid = min(p.total_tiles, num_sms());
-    if (getenv("ESPDL_B200_DWPW_VERBOSE"))
-        fprintf(stderr, "dwpw C=%d %dx%d n=%d S=%d cout=%d: CB=%d pitch=%d ksteps=%d NB=%d TH=%d TW=%d L=%d nseg=%d nbands=%d items=%d MB=%d m_valid=%d tiles=%d cblocks=%d smem=%zu\n",
-                d.hidden_c, d.out_h, d.out_w, d.n, d.stride, d.out_c, p.CB, p.pitch, p.ksteps, p.NB, p.TH, p.TW, p.L, p.nseg, p.nbands, p.items, p.MB,
-                p.m_valid, p.total_tiles, p.cblocks, smem);
     return d.stride == 1 ? dp_dispatch<1>(mi, mw, p, smem, grid, s) : dp_dispatch<2>(mi, mw, p, smem, grid, s);
 }
 

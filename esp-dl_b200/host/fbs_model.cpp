@@ -100,6 +100,195 @@ std::vector<int> read_i64_vec(const Table &t, int fid)
     return v;
 }
 
+// Walks everything the accessors below can touch, once, with every offset and length checked against the buffer: a
+// truncated or damaged file is refused when it is loaded instead of being read out of bounds later.
+struct Verifier {
+    const uint8_t *lo;
+    size_t size;
+    bool ok = true;
+    bool in(const uint8_t *q, size_t n)
+    {
+        if (!ok || q < lo || n > size || (size_t)(q - lo) > size - n) {
+            ok = false;
+        }
+        return ok;
+    }
+    // a table: its vtable lies inside the buffer, and so does the table's inline part
+    bool table(const uint8_t *t)
+    {
+        if (!in(t, 4))
+            return false;
+        const int64_t vt_off = (int64_t)(t - lo) - (int64_t)Table::rd<int32_t>(t);
+        if (vt_off < 0 || (uint64_t)vt_off + 4 > size)
+            return ok = false;
+        const uint8_t *vt = lo + vt_off;
+        const uint16_t vt_size = Table::rd<uint16_t>(vt), t_size = Table::rd<uint16_t>(vt + 2);
+        return vt_size >= 4 && vt_size % 2 == 0 && in(vt, vt_size) && in(t, t_size < 4 ? 4 : t_size);
+    }
+    // offset of field `fid` inside a verified table (0 = absent); `width` bytes at that place are inside the table
+    uint16_t field(const uint8_t *t, int fid, size_t width)
+    {
+        const uint8_t *vt = t - Table::rd<int32_t>(t);
+        const uint16_t vt_size = Table::rd<uint16_t>(vt), t_size = Table::rd<uint16_t>(vt + 2);
+        const int o = 4 + 2 * fid;
+        if (o + 2 > vt_size)
+            return 0;
+        const uint16_t f = Table::rd<uint16_t>(vt + o);
+        if (f && (size_t)f + width > (size_t)(t_size < 4 ? 4 : t_size)) {
+            ok = false;
+        }
+        return ok ? f : 0;
+    }
+    const uint8_t *indirect(const uint8_t *t, int fid)
+    {
+        const uint16_t f = field(t, fid, 4);
+        if (!f)
+            return nullptr;
+        const uint8_t *q = t + f;
+        const uint32_t rel = Table::rd<uint32_t>(q);
+        const uint8_t *r = q + rel;
+        return in(r, 4) ? r : nullptr;
+    }
+    // a vector of `elem`-byte scalars (a string with elem = 1); returns the element count
+    uint32_t vec(const uint8_t *t, int fid, size_t elem)
+    {
+        const uint8_t *r = indirect(t, fid);
+        if (!r)
+            return 0;
+        const uint32_t n = Table::rd<uint32_t>(r);
+        return in(r + 4, (size_t)n * elem) ? n : 0;
+    }
+    // a vector of offsets to tables / strings: calls `each` on every target that lies inside the buffer
+    template <typename F> void vec_of(const uint8_t *t, int fid, F each)
+    {
+        const uint8_t *r = indirect(t, fid);
+        if (!r)
+            return;
+        const uint32_t n = Table::rd<uint32_t>(r);
+        if (!in(r + 4, (size_t)n * 4))
+            return;
+        for (uint32_t i = 0; i < n && ok; i++) {
+            const uint8_t *q = r + 4 + 4 * (size_t)i;
+            const uint8_t *target = q + Table::rd<uint32_t>(q);
+            if (in(target, 4))
+                each(target);
+        }
+    }
+    void string_at(const uint8_t *sp) { in(sp + 4, Table::rd<uint32_t>(sp)); }
+    void sub_table(const uint8_t *t, int fid, void (Verifier::*walk)(const uint8_t *))
+    {
+        const uint8_t *r = indirect(t, fid);
+        if (r && table(r))
+            (this->*walk)(r);
+    }
+    void tensor(const uint8_t *t)
+    {
+        vec(t, TENSOR_NAME, 1);
+        const uint32_t nd = vec(t, TENSOR_DIMS, 8);
+        const uint16_t dtf = field(t, TENSOR_DATA_TYPE, 4);
+        const size_t raw = 16 * (size_t)vec(t, TENSOR_RAW_DATA, 16); // a vector of 16-byte AlignedBytes structs (espdl.fbs)
+        const size_t f32 = vec(t, TENSOR_FLOAT_DATA, 4), i32 = vec(t, TENSOR_INT32_DATA, 4), i64 = vec(t, TENSOR_INT64_DATA, 8);
+        vec(t, TENSOR_EXPONENTS, 8);
+        if (!ok)
+            return;
+        // the payload holds what the dims promise (a tensor object is built over it and read to its end)
+        const uint8_t *dims = nd ? indirect(t, TENSOR_DIMS) + 4 : nullptr;
+        uint64_t count = 1;
+        for (uint32_t i = 0; i < nd; i++) {
+            const int64_t d = Table::rd<int64_t>(dims + 8 * (size_t)i);
+            if (d < 0 || d > 0x7fffffff || (count *= (uint64_t)d) > 0x7fffffffull)
+                ok = false;
+        }
+        const size_t have = raw ? raw : (f32 ? 4 * f32 : (i32 ? 4 * i32 : 8 * i64));
+        const size_t es = dl::dtype_sizeof((dl::dtype_t)(dtf ? Table::rd<int32_t>(t + dtf) : 0));
+        if (ok && have && es && count * es > have) {
+            ok = false;
+        }
+    }
+    void dimension_value(const uint8_t *t) { field(t, 1, 8); }
+    void dimension(const uint8_t *t) { sub_table(t, 0, &Verifier::dimension_value); }
+    void shape(const uint8_t *t)
+    {
+        vec_of(t, 0, [&](const uint8_t *d) {
+            if (table(d))
+                dimension(d);
+        });
+    }
+    void tensor_type(const uint8_t *t)
+    {
+        field(t, TT_ELEM_TYPE, 4);
+        sub_table(t, TT_SHAPE, &Verifier::shape);
+    }
+    void type_info(const uint8_t *t)
+    {
+        field(t, TI_VALUE_TYPE, 1);
+        sub_table(t, TI_VALUE, &Verifier::tensor_type);
+    }
+    void value_info(const uint8_t *t)
+    {
+        vec(t, VI_NAME, 1);
+        sub_table(t, VI_TYPE, &Verifier::type_info);
+        vec(t, VI_EXPONENTS, 8);
+    }
+    void attribute(const uint8_t *t)
+    {
+        vec(t, ATTR_NAME, 1);
+        field(t, ATTR_TYPE, 4);
+        field(t, ATTR_F, 4);
+        field(t, ATTR_I, 8);
+        vec(t, ATTR_S, 1);
+        sub_table(t, ATTR_T, &Verifier::tensor);
+        vec(t, ATTR_FLOATS, 4);
+        vec(t, ATTR_INTS, 8);
+    }
+    void node(const uint8_t *t)
+    {
+        vec(t, NODE_NAME, 1);
+        vec(t, NODE_OP_TYPE, 1);
+        for (int fid : {NODE_INPUT, NODE_OUTPUT}) vec_of(t, fid, [&](const uint8_t *sp) { string_at(sp); });
+        vec_of(t, NODE_ATTRIBUTE, [&](const uint8_t *a) {
+            if (table(a))
+                attribute(a);
+        });
+    }
+    void graph(const uint8_t *g)
+    {
+        vec(g, GRAPH_NAME, 1);
+        vec_of(g, GRAPH_NODE, [&](const uint8_t *n) {
+            if (table(n))
+                node(n);
+        });
+        for (int fid : {GRAPH_INITIALIZER, GRAPH_TEST_INPUTS, GRAPH_TEST_OUTPUTS})
+            vec_of(g, fid, [&](const uint8_t *t) {
+                if (table(t))
+                    tensor(t);
+            });
+        for (int fid : {GRAPH_INPUT, GRAPH_OUTPUT, GRAPH_VALUE_INFO})
+            vec_of(g, fid, [&](const uint8_t *v) {
+                if (table(v))
+                    value_info(v);
+            });
+    }
+    bool model()
+    {
+        if (size < 8 || !in(lo, 4))
+            return false;
+        const uint8_t *root = lo + Table::rd<uint32_t>(lo);
+        if (!table(root))
+            return false;
+        field(root, MODEL_MODEL_VERSION, 8);
+        vec(root, MODEL_DOC_STRING, 1);
+        vec_of(root, MODEL_METADATA, [&](const uint8_t *kv) {
+            if (table(kv)) {
+                vec(kv, 0, 1);
+                vec(kv, 1, 1);
+            }
+        });
+        sub_table(root, MODEL_GRAPH, &Verifier::graph);
+        return ok;
+    }
+};
+
 } // namespace
 
 FbsModel::FbsModel(const void *data, size_t size, model_location_type_t location, bool encrypt, bool rodata_move, bool auto_free,
@@ -108,7 +297,12 @@ FbsModel::FbsModel(const void *data, size_t size, model_location_type_t location
 {
     (void)encrypt;
     (void)rodata_move;
-    load_map();
+    Verifier v{m_data, m_size};
+    m_valid = m_data && m_size && v.model();
+    if (m_valid)
+        load_map();
+    else
+        ESP_LOGE("FbsModel", "the model's FlatBuffer is truncated or damaged: an offset or a length points outside its %zu bytes", m_size);
 }
 
 FbsModel::~FbsModel()
@@ -494,20 +688,35 @@ FbsLoader::FbsLoader(const char *name, model_location_type_t location) : m_locat
     } else {
         m_buf = (const uint8_t *)name;
     }
-    if (!m_buf || (m_buf_size && m_buf_size < 16))
+    if (!m_buf || (m_buf_size && m_buf_size < 16)) {
+        m_buf = nullptr;
         return;
+    }
+    // a buffer in memory comes without its length (as in the reference); a file's length bounds every header field
+    auto inside = [&](uint64_t o, uint64_t n) { return !m_buf_size || (n <= m_buf_size && o <= m_buf_size - n); };
     auto u32 = [&](size_t o) { return Table::rd<uint32_t>(m_buf + o); };
     const std::string magic((const char *)m_buf, 4);
+    // 12-byte model headers in the EDL1 / PDL1 containers, 16-byte ones in the others (fbs_loader.cpp:297-301)
+    m_header_bytes = (magic == "EDL1" || magic == "PDL1") ? 12 : 16;
     if (magic == "EDL1" || magic == "EDL2") {
         m_models.push_back({"", 0});
     } else if (magic == "PDL1" || magic == "PDL2" || magic == "PDL3") {
         m_pdl3 = magic == "PDL3";
         size_t o = m_pdl3 ? 4 + 16 + 4 + 32 : 4;
-        const uint32_t n = u32(o);
+        bool good = inside(o, 4);
+        const uint32_t n = good ? u32(o) : 0;
         o += 4;
-        for (uint32_t i = 0; i < n; i++, o += 12) {
+        good = good && inside(o, (uint64_t)n * 12);
+        for (uint32_t i = 0; i < n && good; i++, o += 12) {
             const uint32_t data_off = u32(o), name_off = u32(o + 4), name_len = u32(o + 8);
-            m_models.push_back({std::string((const char *)m_buf + name_off, name_len), data_off});
+            good = inside(name_off, name_len) && inside(data_off, 16) && name_len < 4096;
+            if (good)
+                m_models.push_back({std::string((const char *)m_buf + name_off, name_len), data_off});
+        }
+        if (!good) {
+            ESP_LOGE("FbsLoader", "the package's model table points outside the file");
+            m_models.clear();
+            m_buf = nullptr;
         }
     } else {
         ESP_LOGE("FbsLoader", "unknown model container magic");
@@ -576,8 +785,12 @@ FbsModel *FbsLoader::make(size_t offset, const uint8_t *key, bool param_copy)
 {
     if (!m_buf)
         return nullptr;
+    if (m_buf_size && (offset > m_buf_size || m_buf_size - offset < 16)) {
+        ESP_LOGE("FbsLoader", "model header is truncated");
+        return nullptr;
+    }
     const uint8_t *h = m_buf + offset;
-    const bool v1 = h[3] == '1';
+    const bool v1 = m_header_bytes == 12;
     const uint32_t mode = Table::rd<uint32_t>(h + 4), size = Table::rd<uint32_t>(h + 8);
     if (mode != 0 && !key) {
         ESP_LOGE("FbsLoader", "This is a cryptographic model, please enter the secret key!"); // fbs_loader.cpp:311-315
@@ -586,7 +799,7 @@ FbsModel *FbsLoader::make(size_t offset, const uint8_t *key, bool param_copy)
     if (mode == 0 && key)
         ESP_LOGW("FbsLoader", "This is not a cryptographic model, the secret key is ignored.");
     const uint8_t *payload = h + (v1 ? 12 : 16);
-    if (m_buf_size && offset + (v1 ? 12 : 16) + size > m_buf_size) {
+    if (m_buf_size && (uint64_t)offset + (v1 ? 12 : 16) + size > m_buf_size) {
         ESP_LOGE("FbsLoader", "model payload is truncated");
         return nullptr;
     }
@@ -621,7 +834,12 @@ FbsModel *FbsLoader::make(size_t offset, const uint8_t *key, bool param_copy)
         free(copy);
         return nullptr;
     }
-    return new FbsModel(copy, size, m_location, mode != 0, false, true, param_copy);
+    FbsModel *model = new FbsModel(copy, size, m_location, mode != 0, false, true, param_copy);
+    if (!model->valid()) { // the constructor has said why
+        delete model;
+        return nullptr;
+    }
+    return model;
 }
 
 FbsModel *FbsLoader::load(const int model_index, const uint8_t *key, bool param_copy)

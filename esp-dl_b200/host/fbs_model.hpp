@@ -66,6 +66,8 @@ public:
     std::string get_model_doc_string();
     std::string get_model_metadata_prop(const std::string &key);
     size_t get_size() const { return m_size; }
+    /// false when an offset or a length of the FlatBuffer points outside it (checked once, when the model is constructed)
+    bool valid() const { return m_valid; }
     void print();
 
     bool m_param_copy;
@@ -76,6 +78,7 @@ private:
     model_location_type_t m_location;
     bool m_auto_free;
     size_t m_size;
+    bool m_valid = false;
     const uint8_t *m_data;
     std::map<std::string, const void *> m_name_to_node_map;
     std::map<std::string, const void *> m_name_to_initial_tensor_map;
@@ -109,6 +112,7 @@ public:
 private:
     FbsModel *make(size_t offset, const uint8_t *key, bool param_copy);
     bool m_pdl3 = false;
+    int m_header_bytes = 16; ///< per-model header: 12 bytes in EDL1 / PDL1 containers, 16 in the others
     std::vector<uint8_t> m_file; ///< file contents when loaded from a path
     const uint8_t *m_buf = nullptr;
     size_t m_buf_size = 0; ///< 0 = unknown (in-memory model)

@@ -213,3 +213,84 @@ def test_registry_covers_the_reference_creator_list(host):
         RMSNormalization""".split()
     missing = set()
     assert set(reference) - registered_ops(host) == missing
+
+
+def test_truncated_and_damaged_files_are_refused_not_read_out_of_bounds(host, tmp_path):
+    """Every offset and length of the FlatBuffer is checked when a model is loaded: a file cut short at any point either
+    fails to load or (when the cut lies past everything the reader uses) loads like the whole file; a file with flipped
+    bytes either fails to load or describes without touching memory outside its buffer.  The child process would die on
+    an out-of-bounds read of the freed tail (the loader's copy is exactly as long as the payload)."""
+    import subprocess
+    import sys
+    good = open(_golden_model(), "rb").read()
+    want = host.espdl_fbs_describe(os.fsencode(_golden_model()))
+    assert want
+    want = bytes(want)
+    cuts = sorted(set([0, 3, 4, 15, 16, 17, 40, 100, 500] + [len(good) * k // 23 for k in range(1, 23)] + [len(good) - 1]))
+    refused = 0
+    for n in cuts:
+        path = tmp_path / f"cut_{n}.espdl"
+        path.write_bytes(good[:n])
+        got = host.espdl_fbs_describe(os.fsencode(path))
+        if got is None:
+            refused += 1
+        else:
+            assert bytes(got) == want
+    assert refused == len(cuts)  # the header's size field no longer fits the file: every cut is refused
+    # the same cuts with the header's size field patched to the shortened payload: now the FlatBuffer itself is short
+    refused = 0
+    for n in [c for c in cuts if c > 64]:
+        blob = bytearray(good[:n])
+        blob[8:12] = (n - 16).to_bytes(4, "little")
+        path = tmp_path / f"short_{n}.espdl"
+        path.write_bytes(bytes(blob))
+        got = host.espdl_fbs_describe(os.fsencode(path))
+        refused += got is None
+        if got is not None:
+            assert bytes(got) == want
+    assert refused >= 10
+    # flipped bytes, in a child process per batch so that a crash would be seen as a failure of this test
+    rng = np.random.default_rng(7)
+    files = []
+    for k in range(60):
+        blob = bytearray(good)
+        for _ in range(1 + k % 4):
+            pos = int(rng.integers(16, len(blob)))
+            blob[pos] ^= int(rng.integers(1, 256))
+        path = tmp_path / f"flip_{k}.espdl"
+        path.write_bytes(bytes(blob))
+        files.append(str(path))
+    code = ("import ctypes as C, os, sys\n"
+            f"L = C.CDLL({model.HOST_LIB_PATH!r})\n"
+            "L.espdl_fbs_describe.restype = C.c_char_p\nL.espdl_fbs_describe.argtypes = [C.c_char_p]\n"
+            "n = sum(L.espdl_fbs_describe(os.fsencode(p)) is not None for p in sys.argv[1:])\nprint(n)\n")
+    r = subprocess.run([sys.executable, "-c", code] + files, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert 0 <= int(r.stdout.strip().splitlines()[-1]) <= len(files)
+
+
+def test_pdl_package_table_is_checked_against_the_file(host, tmp_path):
+    """A PDL package whose model table points outside the file is refused (names and data offsets are checked)."""
+    good = open(_golden_model(), "rb").read()
+    name = b"m0"
+    header = b"PDL2" + (1).to_bytes(4, "little")
+    table_at = len(header)
+    data_off = table_at + 12 + len(name)
+    data_off += (-data_off) % 16
+    entry = data_off.to_bytes(4, "little") + (table_at + 12).to_bytes(4, "little") + len(name).to_bytes(4, "little")
+    blob = header + entry + name
+    blob += b"\0" * (data_off - len(blob)) + good
+    ok = tmp_path / "ok.espdl"
+    ok.write_bytes(blob)
+    assert host.espdl_fbs_describe(os.fsencode(ok)) is not None
+    for field, value in ((0, len(blob) + 100), (4, len(blob) - 1), (8, 1 << 20)):
+        bad = bytearray(blob)
+        bad[table_at + field:table_at + field + 4] = value.to_bytes(4, "little")
+        path = tmp_path / f"bad_{field}.espdl"
+        path.write_bytes(bytes(bad))
+        assert host.espdl_fbs_describe(os.fsencode(path)) is None
+    count = bytearray(blob)
+    count[4:8] = (1 << 28).to_bytes(4, "little")
+    path = tmp_path / "bad_count.espdl"
+    path.write_bytes(bytes(count))
+    assert host.espdl_fbs_describe(os.fsencode(path)) is None
