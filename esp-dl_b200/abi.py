@@ -76,7 +76,7 @@ class CopyDesc(C.Structure):
 class SoftmaxDesc(C.Structure):
     _fields_ = [
         ("input", C.c_void_p), ("output", C.c_void_p), ("exp_table", C.c_void_p),
-        ("rows", i32), ("len", i32), ("out_dtype", i32), ("out_exponent", i32), ("inner", i32), ("log", i32), ("in_exponent", i32),
+        ("rows", i32), ("len", i32), ("out_dtype", i32), ("out_exponent", i32), ("inner", i32), ("log", i32), ("in_exponent", i32), ("round_mode", i32),
     ]
 
 

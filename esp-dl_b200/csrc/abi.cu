@@ -199,8 +199,9 @@ int espdl_b200_stream_sync(void *stream)
     const int dev_conv = read_and_clear_device_error_conv();
     const int dev_block = read_and_clear_device_error_block();
     const int dev_dwpw = read_and_clear_device_error_dwpw();
+    const int dev_band = read_and_clear_device_error_band();
     if (!dev)
-        dev = dev_stem ? dev_stem : (dev_conv ? dev_conv : (dev_block ? dev_block : (dev_dw ? dev_dw : dev_dwpw)));
+        dev = dev_stem ? dev_stem : (dev_conv ? dev_conv : (dev_block ? dev_block : (dev_dw ? dev_dw : (dev_dwpw ? dev_dwpw : dev_band))));
     if (dev) {
         snprintf(g_last_error, sizeof(g_last_error), "a device-side bounded wait expired in the tensor-core tile kernel");
         return dev;
@@ -464,6 +465,8 @@ int espdl_b200_conv2d_ws(const espdl_conv_desc *desc, void *workspace, size_t wo
         }
         return ESPDL_OK;
     }
+    if (desc->kernel != ESPDL_KERNEL_SIMT && conv2d_band_tc_supported(*desc))
+        return conv2d_band_tc(*desc, s); // 3x3 with 8 or 16 input channels: banded filter over 128-byte row windows
     const bool conv_tc_ok = conv2d_conv_tc_supported(*desc);
     if (conv_tc_ok && desc->kernel != ESPDL_KERNEL_SIMT)
         return conv2d_conv_tc(*desc, s); // filters larger than 1x1 (or strided): implicit GEMM over the taps

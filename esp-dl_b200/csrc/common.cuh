@@ -43,6 +43,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
               int n_peer = 0); // peer_delta: byte distances to copies of the output on other GPUs that receive every row as well
 int read_and_clear_device_error(); // status word written by device-side bounded waits (0 = none)
 int read_and_clear_device_error_stem();
+int read_and_clear_device_error_band();
 int read_and_clear_device_error_dw();
 int read_and_clear_device_error_conv();
 int read_and_clear_device_error_block();
@@ -61,6 +62,9 @@ bool conv2d_dw_tma_supported(const espdl_conv_desc &d);
 int conv2d_dw_tma(const espdl_conv_desc &d, cudaStream_t s);
 bool conv2d_stem_tc_supported(const espdl_conv_desc &d);
 int conv2d_stem_tc(const espdl_conv_desc &d, cudaStream_t s);
+// 3x3 conv with 8 or 16 input channels: banded-filter tensor-core kernel over 128-byte row windows (conv_band_tc.cu)
+bool conv2d_band_tc_supported(const espdl_conv_desc &d);
+int conv2d_band_tc(const espdl_conv_desc &d, cudaStream_t s);
 
 // ------------------------------------------------------------- device math
 // dl::tool::shift_and_round on a 32-bit accumulator (int8 operators).

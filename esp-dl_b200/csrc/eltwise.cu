@@ -223,6 +223,33 @@ __global__ void __launch_bounds__(256) elt_s8_vec16_kernel(EltParams p, long lon
     }
 }
 
+// int8 (op) one-element int8 -> int8 (Mul by a scalar factor, Add of a constant, ...): with the second operand fixed the
+// operator is a function of the input byte, so every block tabulates it once with the scalar code (the reference's
+// rounding, whatever the operator) and then runs as a table lookup at the speed of LUT.
+__global__ void __launch_bounds__(256) elt_s8_scalar_b_kernel(EltParams p, long long nvec)
+{
+    __shared__ int8_t table[256];
+    const int b = (int)((const int8_t *)p.b)[0];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        const int a = (int)(int8_t)(uint8_t)(i ^ 0x80);
+        table[i] = (int8_t)sat8((int)max(-1000000ll, min(1000000ll, elt_int(p, a, b))));
+    }
+    __syncthreads();
+    for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+        const uint4 a4 = ((const uint4 *)p.a)[v];
+        const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            uint32_t wd = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) wd |= ((uint32_t)(uint8_t)table[(uint8_t)(aw[q] >> (8 * j)) ^ 0x80u]) << (8 * j);
+            ow[q] = wd;
+        }
+        ((uint4 *)p.out)[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 template <int OP>
 static void launch_vec(const EltParams &p, long long nvec, cudaStream_t s)
 {
@@ -313,7 +340,16 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     const bool vec = same && d->in_dtype == ESPDL_DTYPE_INT8 && (d->out_dtype == ESPDL_DTYPE_INT8 || compare) && total % 16 == 0 &&
         ((uintptr_t)d->input0 % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && (!binary || ((uintptr_t)d->input1 % 16) == 0) &&
         d->op != ESPDL_ELT_PRELU && d->op != ESPDL_ELT_POW;
-    if (vec) {
+    // second operand of one element, first operand of the output's shape
+    bool a_full = true;
+    for (int i = 0; i < 4; i++) a_full = a_full && s0[i] == os[i];
+    const bool scalar_b = binary && !compare && !same && a_full && b == 1 && d->in_dtype == ESPDL_DTYPE_INT8 && d->out_dtype == ESPDL_DTYPE_INT8 &&
+        total % 16 == 0 && ((uintptr_t)d->input0 % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && d->op != ESPDL_ELT_POW;
+    if (scalar_b) {
+        const long long nvec = total / 16;
+        const long long blocks = min((nvec + 255) / 256, (long long)num_sms() * 16);
+        elt_s8_scalar_b_kernel<<<(unsigned)max(blocks, 1ll), 256, 0, s>>>(p, nvec);
+    } else if (vec) {
         const long long nvec = total / 16;
         switch (d->op) {
         case ESPDL_ELT_ADD: launch_vec<ESPDL_ELT_ADD>(p, nvec, s); break;

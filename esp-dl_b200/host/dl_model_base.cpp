@@ -441,6 +441,39 @@ void Model::fold_luts()
     }
 }
 
+void Model::fold_quantize_after_softmax()
+{
+    if (!env_flag("ESPDL_B200_FOLD_QUANT", true) || !m_reuse_memory)
+        return;
+    std::vector<std::string> graph_outputs = m_fbs_model->get_graph_outputs();
+    auto is_graph_output = [&](const std::string &n) { return std::find(graph_outputs.begin(), graph_outputs.end(), n) != graph_outputs.end(); };
+    for (size_t s = 0; s < m_execution_plan.size(); s++) {
+        if (m_module_types[s] != "QuantizeLinear" || m_module_inputs[s].empty() || m_module_outputs[s].size() != 1)
+            continue;
+        const std::string x = m_module_inputs[s][0], y = m_module_outputs[s][0];
+        const dtype_t yt = m_fbs_model->get_value_info_dtype(y);
+        if (is_graph_output(x) || m_fbs_model->get_value_info_dtype(x) != DATA_TYPE_FLOAT || (yt != DATA_TYPE_INT8 && yt != DATA_TYPE_INT16))
+            continue;
+        int producer = -1, readers = 0;
+        for (size_t k = 0; k < m_execution_plan.size(); k++) {
+            for (const std::string &o : m_module_outputs[k])
+                if (o == x) producer = (int)k;
+            for (const std::string &i : m_module_inputs[k])
+                if (i == x) readers++;
+        }
+        if (producer < 0 || producer >= (int)s || readers != 1 || m_module_outputs[producer].size() != 1 ||
+            (m_module_types[producer] != "Softmax" && m_module_types[producer] != "LogSoftmax"))
+            continue;
+        m_module_outputs[producer][0] = y;
+        delete m_execution_plan[s];
+        m_execution_plan.erase(m_execution_plan.begin() + s);
+        m_module_types.erase(m_module_types.begin() + s);
+        m_module_inputs.erase(m_module_inputs.begin() + s);
+        m_module_outputs.erase(m_module_outputs.begin() + s);
+        s--;
+    }
+}
+
 void Model::fold_residual_adds()
 {
     if (!env_flag("ESPDL_B200_FOLD_ADD", true) || !m_reuse_memory)
@@ -501,6 +534,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
         return;
     fuse_blocks();
     fold_luts();
+    fold_quantize_after_softmax();
     fold_residual_adds();
     ModelContext *ctx = m_model_context;
     std::vector<TensorInfo> &infos = m_tensor_infos;

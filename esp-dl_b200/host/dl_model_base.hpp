@@ -139,6 +139,9 @@ protected:
     void release_pipeline();
     void fold_residual_adds();
     void fold_luts();
+    /// A QuantizeLinear whose only input is the float output of a Softmax / LogSoftmax with no other reader disappears: the softmax
+    /// kernel writes the quantized tensor itself (the same `round(y * 2^-e)` on the same float).  ESPDL_B200_FOLD_QUANT=0 keeps it.
+    void fold_quantize_after_softmax();
     void fuse_blocks();
     bool m_built = false;
     std::vector<TensorInfo> m_tensor_infos;

@@ -2059,7 +2059,7 @@ void Softmax::forward(ModelContext *context, runtime_mode_t mode)
         d.input = (const int8_t *)in->device, d.output = out->device, d.exp_table = (const float *)m_dev_table;
         d.len = in->shape[ax], d.rows = in->get_size() / d.len;
         d.inner = (int)inner, d.log = m_log ? 1 : 0, d.in_exponent = in->exponent;
-        d.out_dtype = espdl_dtype(out), d.out_exponent = out->exponent;
+        d.out_dtype = espdl_dtype(out), d.out_exponent = out->exponent, d.round_mode = context->round_mode;
         st = inner > INT_MAX ? ESPDL_ERR_TOO_LARGE : espdl_b200_softmax(&d, context->stream);
     }
     if (st)

@@ -344,6 +344,7 @@ typedef struct espdl_softmax_desc {
     int32_t log;             /* 1: LogSoftmax, y = 2^in_exponent * x - logf(sum)
                                 esp-dl/dl/module/include/dl_module_log_softmax.hpp:150-215 (logf on the device) */
     int32_t in_exponent;     /* LogSoftmax only */
+    int32_t round_mode;      /* rounding of the INT8 / INT16 output (the QuantizeLinear that follows, folded in) */
 } espdl_softmax_desc;
 
 int espdl_b200_softmax(const espdl_softmax_desc *desc, void *stream);

@@ -618,7 +618,7 @@ int oracle_softmax(const espdl_softmax_desc *d)
             if (d->out_dtype == ESPDL_DTYPE_FLOAT)
                 ((float *)d->output)[oi] = y;
             else
-                store_sat(d->output, d->out_dtype, oi, fround_half_up(y * inv_scale));
+                store_sat(d->output, d->out_dtype, oi, fround(y * inv_scale, d->round_mode));
         }
     }
     return ESPDL_OK;

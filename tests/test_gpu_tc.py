@@ -238,3 +238,29 @@ def test_gemm_s8_same_shape_without_cta_pairs(monkeypatch):
     monkeypatch.delenv("ESPDL_B200_CTA_PAIRS", raising=False)
     case = cases.gemm_case(seed=77, m=2304, k=512, n_out=256, per_channel=True, e_in=-7, e_out=-5, e_w=(-9, -6))
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), gpu_util.run_conv_oracle(case))
+
+
+# 3x3 convs with 8 or 16 input channels: the banded-filter kernel over 128-byte row windows (conv_band_tc.cu).
+# (cin, cout, stride, pad (t, b, l, r), n, h, w)
+BAND = [(16, 8, 1, (1, 1, 1, 1), 3, 20, 24), (8, 16, 1, (1, 1, 1, 1), 2, 17, 26), (16, 32, 2, (0, 1, 0, 1), 5, 32, 32),
+        (16, 32, 2, (1, 1, 1, 1), 2, 21, 40), (16, 32, 1, (1, 1, 1, 1), 9, 16, 16), (16, 16, 1, (0, 0, 0, 0), 1, 9, 11),
+        (8, 32, 2, (1, 0, 1, 0), 4, 30, 36), (8, 8, 1, (1, 1, 1, 1), 1, 12, 100), (16, 64, 1, (1, 1, 1, 1), 2, 10, 7),
+        (16, 8, 1, (1, 1, 1, 1), 16, 160, 160)]
+
+
+@pytest.mark.parametrize("cin,cout,stride,pad,n,h,w", BAND)
+@pytest.mark.parametrize("act,per_channel,lut", [(abi.ACT_RELU, True, False), (abi.ACT_LINEAR, False, False), (abi.ACT_LINEAR, True, True)])
+def test_small_channel_conv_banded_kernel(cin, cout, stride, pad, n, h, w, act, per_channel, lut):
+    case = cases.conv_case(seed=cin + cout + h, n=n, h=h, w=w, cin=cin, cout=cout, kh=3, kw=3, stride=stride, pad=pad, act=act,
+                           per_channel=per_channel, e_in=-6, e_out=-5, e_w=(-9, -7), lut=lut)
+    want = gpu_util.run_conv_oracle(case)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), want)
+    # the CUDA-core kernels give the same bytes
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_SIMT), want)
+
+
+@pytest.mark.parametrize("round_mode,lut", [(abi.ROUND_HALF_EVEN, False), (abi.ROUND_HALF_UP, True), (abi.ROUND_HALF_EVEN, True)])
+def test_small_channel_conv_general_epilogue(round_mode, lut):
+    """Half-even rounding takes the banded kernel's general epilogue; a fused table is applied in the staged epilogue."""
+    case = cases.conv_case(seed=3, n=2, h=18, w=22, cin=16, cout=16, kh=3, kw=3, per_channel=True, round_mode=round_mode, lut=lut)
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), gpu_util.run_conv_oracle(case))

@@ -93,7 +93,7 @@ def softmax_desc(rows, length, inner, e_in, log, out_dtype=abi.DTYPE_FLOAT, e_ou
     return d
 
 
-LSM = [(6, 33, 1), (4, 10, 7), (1, 1000, 1), (3, 5, 16)]  # outer, len, inner
+LSM = [(6, 33, 1), (4, 10, 7), (1, 1000, 1), (3, 5, 16), (100, 33, 1), (5, 40, 20), (300, 400, 1), (70, 1000, 1)]  # outer, len, inner
 
 
 @pytest.mark.parametrize("outer,length,inner", LSM)
