@@ -73,6 +73,11 @@ class CopyDesc(C.Structure):
     ]
 
 
+class PartsDesc(C.Structure):
+    _fields_ = [("wide", C.c_void_p), ("parts", C.c_void_p * 8), ("part_bytes", C.c_int64 * 8), ("n_parts", i32), ("split", i32),
+                ("rows", C.c_int64)]
+
+
 class SoftmaxDesc(C.Structure):
     _fields_ = [
         ("input", C.c_void_p), ("output", C.c_void_p), ("exp_table", C.c_void_p),
@@ -212,6 +217,7 @@ SYMBOLS = {
     "espdl_b200_pool": (C.c_int, [C.POINTER(PoolDesc), C.c_void_p]),
     "espdl_b200_resize": (C.c_int, [C.POINTER(ResizeDesc), C.c_void_p]),
     "espdl_b200_copy": (C.c_int, [C.POINTER(CopyDesc), C.c_void_p]),
+    "espdl_b200_concat_split": (C.c_int, [C.POINTER(PartsDesc), C.c_void_p]),
     "espdl_b200_softmax": (C.c_int, [C.POINTER(SoftmaxDesc), C.c_void_p]),
     "espdl_b200_gemm_scatter": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_void_p), C.c_int, C.c_void_p]),
     "espdl_b200_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -494,6 +494,68 @@ extern "C" int espdl_b200_gather(const espdl_gather_desc *d, void *stream)
     return check_launch("gather");
 }
 
+// Concat / Split in one launch: a thread moves one 16-byte unit of a row of the wide tensor; which part the unit
+// belongs to comes from a table of at most eight unit offsets.
+namespace espdl {
+namespace {
+struct PartsParams {
+    uint4 *wide;
+    uint4 *parts[8];
+    int start[9]; // first unit of part i inside a row of the wide tensor; start[n_parts] = units per row
+    int n_parts, split;
+    long long total; // rows x units per row
+};
+
+__global__ void __launch_bounds__(256) concat_split_kernel(PartsParams p)
+{
+    const int upr = p.start[p.n_parts];
+    for (long long u = blockIdx.x * (long long)blockDim.x + threadIdx.x; u < p.total; u += (long long)gridDim.x * blockDim.x) {
+        const long long row = u / upr;
+        const int col = (int)(u - row * upr);
+        int i = 0;
+#pragma unroll
+        for (int k = 1; k < 8; k++)
+            if (k < p.n_parts && col >= p.start[k])
+                i = k;
+        uint4 *part = p.parts[i] + row * (p.start[i + 1] - p.start[i]) + (col - p.start[i]);
+        if (p.split)
+            *part = p.wide[u];
+        else
+            p.wide[u] = *part;
+    }
+}
+} // namespace
+} // namespace espdl
+
+extern "C" int espdl_b200_concat_split(const espdl_parts_desc *d, void *stream)
+{
+    if (!d || !d->wide || d->n_parts < 1 || d->n_parts > 8 || d->rows < 0 || ((uintptr_t)d->wide % 16))
+        return ESPDL_ERR_INVALID_ARG;
+    PartsParams p;
+    p.wide = (uint4 *)d->wide, p.n_parts = d->n_parts, p.split = d->split ? 1 : 0;
+    long long units = 0;
+    for (int i = 0; i < 8; i++) {
+        p.parts[i] = nullptr;
+        p.start[i] = (int)units;
+        if (i < d->n_parts) {
+            if (!d->parts[i] || d->part_bytes[i] <= 0 || d->part_bytes[i] % 16 || ((uintptr_t)d->parts[i] % 16))
+                return ESPDL_ERR_INVALID_ARG;
+            p.parts[i] = (uint4 *)d->parts[i];
+            units += d->part_bytes[i] / 16;
+            if (units > 0x7fffffffll)
+                return ESPDL_ERR_TOO_LARGE;
+        }
+    }
+    for (int i = d->n_parts; i <= 8; i++) p.start[i] = (int)units;
+    p.total = d->rows * units;
+    if (p.total == 0)
+        return ESPDL_OK;
+    const long long blocks = (p.total + 255) / 256;
+    concat_split_kernel<<<(unsigned)min(blocks, (long long)num_sms() * 32), 256, 0, (cudaStream_t)stream>>>(p);
+    count_launch();
+    return check_launch("concat_split");
+}
+
 extern "C" int espdl_b200_copy(const espdl_copy_desc *d, void *stream)
 {
     if (!d || !d->src || !d->dst || d->ndim < 1 || d->ndim > 6)

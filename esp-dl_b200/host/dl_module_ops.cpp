@@ -1159,6 +1159,32 @@ std::vector<std::vector<int>> Concat::get_output_shape(std::vector<std::vector<i
     return {out};
 }
 
+// Concat / Split as one launch when every part is whole, aligned 16-byte units per row (rows = the extents before the axis);
+// returns false when the shapes call for the strided copies instead.
+static bool parts_in_one_launch(ModelContext *context, TensorBase *wide, const std::vector<TensorBase *> &parts, int axis, bool split, int &st)
+{
+    if (parts.empty() || parts.size() > 8 || !wide || !wide->device || ((uintptr_t)wide->device % 16))
+        return false;
+    const long long es = (long long)dtype_sizeof(wide->dtype);
+    long long rows = 1, inner = es;
+    for (int i = 0; i < axis; i++) rows *= wide->shape[i];
+    for (size_t i = axis + 1; i < wide->shape.size(); i++) inner *= wide->shape[i];
+    espdl_parts_desc d;
+    memset(&d, 0, sizeof(d));
+    d.wide = wide->device, d.n_parts = (int)parts.size(), d.split = split ? 1 : 0, d.rows = rows;
+    for (size_t i = 0; i < parts.size(); i++) {
+        TensorBase *t = parts[i];
+        if (!t || !t->device || ((uintptr_t)t->device % 16) || t->dtype != wide->dtype || (int)t->shape.size() != (int)wide->shape.size())
+            return false;
+        d.parts[i] = t->device;
+        d.part_bytes[i] = (long long)t->shape[axis] * inner;
+        if (d.part_bytes[i] % 16 != 0)
+            return false;
+    }
+    st = espdl_b200_concat_split(&d, context->stream);
+    return true;
+}
+
 void Concat::forward(ModelContext *context, runtime_mode_t mode)
 {
     (void)mode;
@@ -1167,6 +1193,17 @@ void Concat::forward(ModelContext *context, runtime_mode_t mode)
     const std::vector<long long> os = dense_strides(out->shape);
     long long offset = 0;
     int st = ESPDL_OK;
+    {
+        std::vector<TensorBase *> parts;
+        for (int idx : m_inputs_index) parts.push_back(context->get_tensor(idx));
+        const int ax = axis < 0 ? axis + (int)out->shape.size() : axis;
+        if (parts_in_one_launch(context, out, parts, ax, false, st)) {
+            if (st)
+                ESP_LOGE("Concat", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+            context->note(st);
+            return;
+        }
+    }
     for (size_t i = 0; i < m_inputs_index.size() && !st; i++) {
         TensorBase *in = context->get_tensor(m_inputs_index[i]);
         if (!in || !in->device || !out->device) {
@@ -1225,6 +1262,16 @@ void Split::forward(ModelContext *context, runtime_mode_t mode)
     const std::vector<long long> is = dense_strides(in->shape);
     long long offset = 0;
     int st = ESPDL_OK;
+    {
+        std::vector<TensorBase *> parts;
+        for (int idx : m_outputs_index) parts.push_back(context->get_tensor(idx));
+        if (parts_in_one_launch(context, in, parts, m_axis, true, st)) {
+            if (st)
+                ESP_LOGE("Split", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
+            context->note(st);
+            return;
+        }
+    }
     for (size_t i = 0; i < m_outputs_index.size() && !st; i++) {
         TensorBase *out = context->get_tensor(m_outputs_index[i]);
         if (!out || !out->device || !in->device) {

@@ -311,6 +311,22 @@ typedef struct espdl_copy_desc {
 
 int espdl_b200_copy(const espdl_copy_desc *desc, void *stream);
 
+/* Concat / Split along one axis in ONE launch (esp-dl/dl/module/include/dl_module_concat.hpp:38-107, dl_module_split.hpp):
+ * the "wide" tensor is [rows][sum of part_bytes], part i is a dense [rows][part_bytes[i]]; split = 0 gathers the parts
+ * into the wide tensor (Concat), split = 1 scatters the wide tensor into the parts (Split).  Every part_bytes[i] and every
+ * base address is a multiple of 16: threads move 16-byte units of the wide tensor's rows, so both sides of the copy are
+ * whole sectors.  Other shapes go through espdl_b200_copy, one launch per part. */
+typedef struct espdl_parts_desc {
+    void *wide;
+    void *parts[8];
+    int64_t part_bytes[8];
+    int32_t n_parts; /* 1..8 */
+    int32_t split;
+    int64_t rows;
+} espdl_parts_desc;
+
+int espdl_b200_concat_split(const espdl_parts_desc *desc, void *stream);
+
 /* ----------------------------------------------------------------- gather */
 /* dl::module::Gather (esp-dl/dl/module/include/dl_module_gather.hpp:66-96): out[o][i][:] = in[o][indices[i]][:] for
  * o < outer, i < num_indices, rows of `inner` elements.  Indices are int32 in device memory and must lie in
