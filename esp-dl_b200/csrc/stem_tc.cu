@@ -81,6 +81,7 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
     uint64_t *full_bar = bars, *empty_bar = bars + ST_STAGES, *tfull_bar = bars + 2 * ST_STAGES, *tempty_bar = tfull_bar + ST_ACC;
     uint32_t *tmem_slot = (uint32_t *)(tempty_bar + ST_ACC);
     int *slow_flag = (int *)(tmem_slot + 1);
+    uint8_t *lut_s = (uint8_t *)(slow_flag + 3); // a fused 8-bit table, 256 bytes, 16-byte aligned
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.ngroups * p.yblocks * p.segs;
@@ -116,6 +117,8 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
         const uint32_t off = (uint32_t)(row * ST_K + k0);
         *(uint32_t *)(b_s + (size_t)ky * 256 * ST_K + (off ^ (((off >> 7) & 3u) << 4))) = word;
     }
+    if (p.epi.lut)
+        stage_lut(p.epi.lut, lut_s, (int)threadIdx.x, ST_THREADS);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 1)
         tmem_alloc(smem_u32(tmem_slot), 512);
@@ -223,7 +226,7 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
                 atomicOr(slow_flag, 1);
         }
         asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
-        const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut;
+        const bool fast = !*slow_flag && !p.epi.half_even; // a fused table rides on the staged form
         const uint32_t fp = epi_param_base(fast_s);
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -256,7 +259,9 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
                 named_bar(2 + group, 128);
                 const int col0 = part * out_pw;
                 const int floor_q = p.epi.relu ? 0 : INT_MIN;
-                if (out_pw == 128)
+                if (p.epi.lut)
+                    epilogue_stage_lut(t0 + col0, fp + (uint32_t)col0 * 8u, buf, row_in_tile, out_pw, out_pw == 128 ? 7u : 3u, floor_q, smem_u32(lut_s));
+                else if (out_pw == 128)
                     epilogue_stage<128>(t0 + col0, fp + (uint32_t)col0 * 8u, buf, row_in_tile, 128, floor_q);
                 else
                     epilogue_stage<64>(t0 + col0, fp + (uint32_t)col0 * 8u, buf, row_in_tile, 64, floor_q);
@@ -401,7 +406,7 @@ int conv2d_stem_tc(const espdl_conv_desc &d, cudaStream_t s)
             return set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(stem output)");
     }
     const size_t smem = 1024 + 3 * 256 * ST_K + (size_t)ST_STAGES * 3 * ST_A_BYTES + 4 * 128 * 128 + sizeof(FastParam) * 256 +
-        (2 * ST_STAGES + 2 * ST_ACC) * 8 + 32;
+        (2 * ST_STAGES + 2 * ST_ACC) * 8 + 32 + 256 + 16;
     static std::once_flag attr_once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute(stem_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024); });

@@ -428,7 +428,12 @@ void Model::fold_luts()
             continue;
         module::Conv *conv = dynamic_cast<module::Conv *>(m_execution_plan[producer]);
         TensorBase *filter = ctx->get_tensor(m_module_inputs[producer][1]);
-        if (!conv || !conv->can_fuse_lut() || !filter || filter->shape.size() != 4 || filter->shape[2] % 16 != 0)
+        // the kernels that apply a table in their staged epilogue: the tile kernels (Cin a multiple of 16) and the two
+        // banded-filter kernels (3x3 with 3 or 8 input channels)
+        if (!conv || !conv->can_fuse_lut() || !filter || filter->shape.size() != 4)
+            continue;
+        const bool banded = filter->shape[0] == 3 && filter->shape[1] == 3 && (filter->shape[2] == 3 || filter->shape[2] == 8);
+        if (filter->shape[2] % 16 != 0 && !banded)
             continue;
         conv->set_fused_lut(lut->release_table(), m_fbs_model->get_value_info_exponent(x));
         m_module_outputs[producer][0] = y;
