@@ -302,6 +302,283 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------------------------ stride-1 windows from ONE patch
+// The kernel above fetches every input byte once per filter tap (nine boxes of 128 pixels for a 3x3 window), and with
+// 32-128 byte rows that traffic, not the MMAs, bounds it (64 -> 64 channels at 80x80: 1.8 GB through the TMA unit for a
+// 0.4 GB tensor).  For stride 1, dilation 1 and one channel block the taps are shifted views of the same pixels: here a
+// tile's input arrives as ONE 4-D box {Cin, PW pixels, RT + KH - 1 rows, 1 image} whose dense shared-memory image is
+// a run of "flat positions" row * PW + x, and tap (ky, kx) is the same run started (ky * PW + kx) rows later - a
+// descriptor start address, no data movement (the swizzle is a function of the absolute shared-memory address, so a
+// start moved by whole rows stays consistent with what the TMA unit wrote).  The 128 rows of an MMA are 128 consecutive
+// flat positions = RT = 128 / PW image rows of PW positions, of which the last KW - 1 of every row are not outputs (their
+// windows run into the next row); they are computed and dropped.  The whole filter stays in shared memory for the life of
+// the CTA.  Borders are TMA zero fill.  Epilogue and roles as above; a tile leaves through one TMA store per image row.
+struct PatchParams {
+    int n, oh, ow, cin, cout;
+    int kh, kw, pt, pl;
+    int PW, RT, PV;               // positions per patch row (32, 64 or 128), image rows per tile, outputs per row = PW - (KW - 1)
+    int xtiles, ytiles;
+    int block_n, swz;
+    int stages, acc_stages, tmem_cols;
+    int patch_bytes, patch_tx;    // shared-memory stride of a stage (with slack for the last taps' overrun), bytes one box delivers
+    int out_pw, out_mask;
+    int stack, ncols;             // the KW taps of a filter row side by side along N (ncols = KW * block_n accumulator columns per tile)
+    void *out;
+    long long ops;                // output pixel stride in bytes
+    EpiConfig epi;
+};
+
+// Stacked taps: accumulator column block kx of TMEM lane m holds tap column kx's share of the output at position m - kx,
+// so an output is the sum over kx of block kx read kx lanes further on.  With 32 positions per patch row a warp's 32
+// lanes are exactly one image row and the last KW - 1 of them are dropped, so the shuffles never leave the warp.
+__device__ __forceinline__ void ld16_sum(uint32_t t, int kw, int stride, int32_t *v)
+{
+    ld16(t, v);
+    ld_wait16(v);
+    for (int kx = 1; kx < kw; kx++) {
+        int32_t u[16];
+        ld16(t + (uint32_t)(kx * stride), u);
+        ld_wait16(u);
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] += __shfl_down_sync(0xffffffffu, u[i], kx);
+    }
+}
+
+static __device__ __noinline__ void epilogue_stage_stacked(uint32_t t0, int kw, int stride, uint32_t fp, uint32_t buf, int row, int pw, uint32_t mask,
+                                                           int floor_q, uint32_t tbl)
+{
+    const uint32_t rx = ((((uint32_t)(row * pw)) >> 7) & mask) << 4;
+    const uint32_t rb = buf + (uint32_t)(row * pw);
+#pragma unroll 1
+    for (int c = 0; c < pw; c += 16) {
+        int32_t v[16];
+        uint32_t pk[4];
+        ld16_sum(t0 + c, kw, stride, v);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            pk[q] = requant4_floor(v + 4 * q, fp + (uint32_t)(c + 4 * q) * 8u, floor_q);
+            if (tbl)
+                pk[q] = lut4(pk[q], tbl);
+        }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)c ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                     : "memory");
+    }
+}
+
+__global__ void __launch_bounds__(CV_THREADS, 1)
+conv_patch_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_out,
+                  const __grid_constant__ PatchParams p)
+{
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int taps = p.kh * p.kw;
+    const int b_tap = p.block_n * p.swz;                       // one tap's filter rows: whole swizzle patterns (block_n % 16 == 0)
+    uint8_t *filt_s = smem;                                    // taps x [block_n][swz]
+    uint8_t *patch_s = smem + (size_t)taps * b_tap;            // stages x patch
+    uint8_t *out_stage = patch_s + (size_t)p.stages * p.patch_bytes;
+    const int out_tile_bytes = (128 * p.out_pw + 1023) & ~1023;
+    uint8_t *aux = out_stage + 4 * (size_t)out_tile_bytes;
+    FastParam *fast_s = (FastParam *)aux;
+    uint64_t *bars = (uint64_t *)(aux + sizeof(FastParam) * (size_t)p.block_n);
+    uint64_t *full_bar = bars, *empty_bar = bars + CV_MAX_STAGES, *tfull_bar = bars + 2 * CV_MAX_STAGES, *tempty_bar = tfull_bar + CV_MAX_ACC;
+    uint64_t *filt_bar = tempty_bar + CV_MAX_ACC;
+    uint32_t *tmem_slot = (uint32_t *)(filt_bar + 1);
+    int *slow_flag = (int *)(tmem_slot + 1);
+    uint8_t *lut_s = (uint8_t *)(slow_flag + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_per_image = p.ytiles * p.xtiles;
+    const int total_tiles = p.n * tiles_per_image;
+    const int parts = 4 / p.acc_stages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < CV_MAX_ACC; a++) {
+            mbar_init(smem_u32(&tfull_bar[a]), 1);
+            mbar_init(smem_u32(&tempty_bar[a]), 4 * parts);
+        }
+        mbar_init(smem_u32(filt_bar), 1);
+        *slow_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1)
+        tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            // the filter, once: one box per tap
+            mbar_arrive_expect_tx(smem_u32(filt_bar), (uint32_t)(taps * b_tap));
+            for (int tap = 0; tap < taps; tap++) tma_load_2d(smem_u32(filt_s + (size_t)tap * b_tap), &map_b, tap * p.cin, 0, smem_u32(filt_bar));
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int xt = tile % p.xtiles;
+                const int yt = (tile / p.xtiles) % p.ytiles;
+                const int img = tile / tiles_per_image;
+                if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t bar = smem_u32(&full_bar[stage]);
+                mbar_arrive_expect_tx(bar, (uint32_t)p.patch_tx);
+                tma_load_4d(smem_u32(patch_s + (size_t)stage * p.patch_bytes), &map_a, 0, xt * p.PV - p.pl, yt * p.RT - p.pt, img, bar);
+                if (++stage == p.stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok)
+                atomicExch(&g_conv_tc_error, ESPDL_ERR_TIMEOUT);
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = mbar_wait(smem_u32(filt_bar), 0);
+            const uint32_t idesc = idesc_i8(1, 1, 128, p.ncols);
+            const int ksteps = p.swz / 32;
+            const uint32_t f0 = smem_u32(filt_s);
+            const int kx_count = p.stack ? 1 : p.kw;   // stacked: one MMA covers the KW taps of a filter row
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1) || !mbar_wait(smem_u32(&full_bar[stage]), phase)) {
+                    ok = false;
+                    break;
+                }
+                fence_after();
+                const uint32_t d0 = tmem_base + (uint32_t)(acc * p.ncols);
+                const uint32_t st = smem_u32(patch_s + (size_t)stage * p.patch_bytes);
+                int first = 1;
+                for (int ky = 0; ky < p.kh; ky++)
+                    for (int kx = 0; kx < kx_count; kx++) {
+                        const uint64_t da = smem_desc_swizzled(st + (uint32_t)((ky * p.PW + kx) * p.swz), p.swz);
+                        const uint64_t db = smem_desc_swizzled(f0 + (uint32_t)((ky * p.kw + kx) * b_tap), p.swz);
+                        for (int k = 0; k < ksteps; k++, first = 0) mma_i8(d0, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, !first);
+                    }
+                commit(smem_u32(&empty_bar[stage]));
+                commit(smem_u32(&tfull_bar[acc]));
+                if (++stage == p.stages) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+                if (++acc == p.acc_stages) {
+                    acc = 0;
+                    acc_phase ^= 1;
+                }
+            }
+            if (!ok)
+                atomicExch(&g_conv_tc_error, ESPDL_ERR_TIMEOUT);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..17)
+        const int ew = warp - 2;
+        const int group = ew >> 2;
+        const int acc = group % p.acc_stages;
+        const int part = group / p.acc_stages;
+        const int lane_group = warp & 3;
+        const int row_in_tile = lane_group * 32 + lane;
+        const int et = threadIdx.x - 64;
+        stage_fast_params(p.epi, fast_s, p.cout, p.block_n, et, 16 * 32, slow_flag);
+        if (p.epi.lut)
+            stage_lut(p.epi.lut, lut_s, et, 16 * 32);
+        asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
+        const bool fast = !*slow_flag && !p.epi.half_even && (long long)p.cin * p.kh * p.kw <= 32768;
+        const uint32_t fp_base = epi_param_base(fast_s);
+        const int floor_q = p.epi.relu ? 0 : INT_MIN;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+            if (local % p.acc_stages != acc)
+                continue;
+            const int xt = tile % p.xtiles;
+            const int yt = (tile / p.xtiles) % p.ytiles;
+            const int img = tile / tiles_per_image;
+            if (!mbar_wait(smem_u32(&tfull_bar[acc]), acc_phase)) {
+                ok = false;
+                break;
+            }
+            acc_phase ^= 1;
+            fence_after();
+            const uint32_t t0 = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * p.ncols);
+            if (!fast) {
+                // direct rows: any rounding mode, any shift, optional table
+                const int r = row_in_tile / p.PW, xx = row_in_tile % p.PW;
+                const int oy = yt * p.RT + r, ox = xt * p.PV + xx;
+                const bool row_ok = xx < p.PV && oy < p.oh && ox < p.ow;
+                int8_t *orow = (int8_t *)p.out + (((long long)img * p.oh + oy) * p.ow + ox) * p.ops;
+                const uintptr_t amix = (uintptr_t)p.ops | ((uintptr_t)p.out) | 16u;
+                const int out_align = (int)(amix & (~amix + 1));
+                for (int c0 = part * p.out_pw; c0 < (part + 1) * p.out_pw; c0 += 16) {
+                    int32_t v[16];
+                    ld16_sum(t0 + c0, p.stack ? p.kw : 1, p.block_n, v);
+                    uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                    requant16_general(v, p.epi, c0, p.cout, pk);
+                    const int count = min(16, p.cout - c0);
+                    if (row_ok && count > 0)
+                        store_bytes(orow + c0, pk, count, out_align);
+                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(smem_u32(&tempty_bar[acc]));
+                continue;
+            }
+            const bool leader = (ew & 3) == 0 && lane == 0;
+            const uint32_t buf = smem_u32(out_stage + (size_t)group * out_tile_bytes);
+            if (leader)
+                bulk_wait_read_all();
+            named_bar(2 + group, 128);
+            const int col0 = part * p.out_pw;
+            const uint32_t fpp = fp_base + (uint32_t)col0 * 8u;
+            if (p.stack)
+                epilogue_stage_stacked(t0 + col0, p.kw, p.block_n, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q,
+                                       p.epi.lut ? smem_u32(lut_s) : 0u);
+            else if (p.epi.lut)
+                epilogue_stage_lut(t0 + col0, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q, smem_u32(lut_s));
+            else if (p.out_pw == 128)
+                epilogue_stage<128>(t0 + col0, fpp, buf, row_in_tile, 128, floor_q);
+            else if (p.out_pw == 64)
+                epilogue_stage<64>(t0 + col0, fpp, buf, row_in_tile, 64, floor_q);
+            else
+                epilogue_stage<0>(t0 + col0, fpp, buf, row_in_tile, p.out_pw, floor_q);
+            fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(smem_u32(&tempty_bar[acc]));
+            fence_async_smem();
+            named_bar(2 + group, 128);
+            if (leader) {
+                // one store per image row of the tile: PV outputs of out_pw channels; rows and columns outside the image are clipped
+                for (int r = 0; r < p.RT; r++) tma_store_4d(&map_out, buf + (uint32_t)(r * p.PW * p.out_pw), col0, xt * p.PV, yt * p.RT + r, img);
+                bulk_commit();
+            }
+        }
+        if (!ok && lane == 0)
+            atomicExch(&g_conv_tc_error, ESPDL_ERR_TIMEOUT);
+        if ((ew & 3) == 0 && lane == 0)
+            bulk_wait_all();
+    }
+
+    fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after();
+        tmem_dealloc(tmem_base, p.tmem_cols);
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -380,6 +657,130 @@ bool conv_plan(const espdl_conv_desc &d, ConvTcParams &p)
     return true;
 }
 
+size_t patch_aux_bytes(const PatchParams &p) { return sizeof(FastParam) * (size_t)p.block_n + (2 * CV_MAX_STAGES + 2 * CV_MAX_ACC + 1) * 8 + 32 + 256; }
+
+// The one-patch form: stride 1, dilation 1, Cin = 64 or 128 (one swizzle row per pixel), Cout <= 256 in one tile, the
+// filter small enough to stay in shared memory next to two or more patches, and the staged epilogue's alignment.
+bool patch_plan(const espdl_conv_desc &d, PatchParams &p)
+{
+    if (getenv("ESPDL_B200_NO_CONV_PATCH"))
+        return false;
+    if (d.stride_h != 1 || d.stride_w != 1 || d.dilation_h != 1 || d.dilation_w != 1 || (d.in_c != 32 && d.in_c != 64 && d.in_c != 128))
+        return false;
+    if (d.out_c > 256 || d.out_c % 16 != 0 || d.kw > 8 || d.kh > 8 || d.kh * d.kw < 2)
+        return false;
+    const long long ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
+    if (ops % 16 != 0 || ((uintptr_t)d.output % 16) != 0)
+        return false;
+    p.n = d.n, p.oh = d.out_h, p.ow = d.out_w, p.cin = d.in_c, p.cout = d.out_c;
+    p.kh = d.kh, p.kw = d.kw, p.pt = d.pad_top, p.pl = d.pad_left;
+    p.swz = d.in_c, p.block_n = d.out_c;
+    // An MMA of 128 rows costs the tensor pipe about the same time for any N up to 256, so the KW taps of a filter row
+    // go side by side along N whenever KW * Cout fits and the epilogue's channel split stays a multiple of 16.
+    p.stack = 0, p.ncols = p.block_n;
+    if (d.kw >= 2 && d.kw <= 4 && d.kw * p.block_n <= 256 && !getenv("ESPDL_B200_NO_TAP_STACK")) {
+        const int acc = 4 * d.kw * p.block_n <= 512 ? 4 : 2;
+        if (p.block_n % (16 * (4 / acc)) == 0)
+            p.stack = 1, p.ncols = d.kw * p.block_n;
+    }
+    p.acc_stages = 4 * p.ncols <= 512 ? 4 : 2;
+    int pow2 = 32;
+    while (pow2 < p.acc_stages * p.ncols) pow2 *= 2;
+    p.tmem_cols = pow2;
+    const int parts = 4 / p.acc_stages;
+    if (p.block_n % (16 * parts) != 0 || p.block_n / parts > 128)
+        return false;
+    p.out_pw = p.block_n / parts;
+    p.out_mask = p.out_pw == 128 ? 7 : (p.out_pw == 64 ? 3 : 0);
+    // positions per patch row: the width that wastes the fewest of an MMA's 128 rows on this image (stacked taps: 32,
+    // one warp of the epilogue per image row)
+    double best = -1;
+    p.PW = 0;
+    for (int PW : {32, 64, 128}) {
+        const int PV = PW - (d.kw - 1), RT = 128 / PW;
+        if (PV < 8 || (p.stack && PW != 32))
+            continue;
+        const int xt = (d.out_w + PV - 1) / PV, yt = (d.out_h + RT - 1) / RT;
+        const double eff = (double)d.out_w * d.out_h / ((double)xt * PW * yt * RT);
+        if (eff > best + 1e-9)
+            best = eff, p.PW = PW;
+    }
+    if (!p.PW)
+        return false;
+    p.RT = 128 / p.PW, p.PV = p.PW - (d.kw - 1);
+    p.xtiles = (d.out_w + p.PV - 1) / p.PV, p.ytiles = (d.out_h + p.RT - 1) / p.RT;
+    const int rows = (p.RT + d.kh - 1) * p.PW;
+    p.patch_tx = rows * p.swz;
+    p.patch_bytes = ((rows + d.kw) * p.swz + 1023) & ~1023; // the last taps of the last (dropped) positions read a few rows further
+    const size_t filt = (size_t)d.kh * d.kw * p.block_n * p.swz;
+    const size_t out_bytes = 4 * (size_t)((128 * p.out_pw + 1023) & ~1023);
+    const long long room = (long long)CV_SMEM_BUDGET - (long long)filt - (long long)out_bytes - (long long)patch_aux_bytes(p) - 1024;
+    const long long stages = room / p.patch_bytes;
+    if (stages < 2)
+        return false;
+    p.stages = stages > 4 ? 4 : (int)stages;
+    return true;
+}
+
+int launch_patch(const espdl_conv_desc &d, PatchParams &p, cudaStream_t s)
+{
+    EncodeTiledFn enc = conv_encode();
+    if (!enc)
+        return set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");
+    const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
+    p.out = d.output;
+    p.ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
+    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut;
+    p.epi.e_shift_base = d.out_exponent - d.in_exponent;
+    p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;
+    p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
+    CUtensorMap ma, mb, mo;
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)d.in_c, (cuuint64_t)d.in_w, (cuuint64_t)d.in_h, (cuuint64_t)d.n};
+        cuuint64_t strides[3] = {(cuuint64_t)ips, (cuuint64_t)ips * d.in_w, (cuuint64_t)ips * d.in_w * d.in_h};
+        cuuint32_t box[4] = {(cuuint32_t)p.swz, (cuuint32_t)p.PW, (cuuint32_t)(p.RT + d.kh - 1), 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (enc(&ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(d.input), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                swizzle_of(p.swz), CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(conv patch input)");
+    }
+    {
+        const cuuint64_t krow = (cuuint64_t)d.kh * d.kw * d.in_c;
+        cuuint64_t dims[2] = {krow, (cuuint64_t)d.out_c};
+        cuuint64_t strides[1] = {krow};
+        cuuint32_t box[2] = {(cuuint32_t)p.swz, (cuuint32_t)p.block_n};
+        cuuint32_t estr[2] = {1, 1};
+        if (enc(&mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(d.filter), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                swizzle_of(p.swz), CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(conv patch filter)");
+    }
+    {
+        cuuint64_t dims[4] = {(cuuint64_t)d.out_c, (cuuint64_t)d.out_w, (cuuint64_t)d.out_h, (cuuint64_t)d.n};
+        cuuint64_t strides[3] = {(cuuint64_t)p.ops, (cuuint64_t)p.ops * d.out_w, (cuuint64_t)p.ops * d.out_w * d.out_h};
+        cuuint32_t box[4] = {(cuuint32_t)p.out_pw, (cuuint32_t)p.PV, 1, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (enc(&mo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, d.output, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                swizzle_of(p.out_pw == 128 ? 128 : (p.out_pw == 64 ? 64 : 0)), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(conv patch output)");
+    }
+    size_t smem = 1024 + (size_t)d.kh * d.kw * p.block_n * p.swz + (size_t)p.stages * p.patch_bytes + 4 * (size_t)((128 * p.out_pw + 1023) & ~1023) +
+        patch_aux_bytes(p);
+    if (smem < 120 * 1024)
+        smem = 120 * 1024;
+    static std::once_flag attr_once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute(conv_patch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(CV_SMEM_BUDGET + 2048)); });
+    if (attr_err != cudaSuccess)
+        return set_cuda_error(attr_err, "cudaFuncSetAttribute(conv_patch_kernel)");
+    const long long total = (long long)p.n * p.ytiles * p.xtiles;
+    if (total > 0x7fffffffll)
+        return ESPDL_ERR_TOO_LARGE;
+    conv_patch_kernel<<<(int)min(total, (long long)num_sms()), CV_THREADS, smem, s>>>(ma, mb, mo, p);
+    count_launch();
+    return check_launch("conv_patch");
+}
+
 } // namespace
 
 bool conv2d_conv_tc_supported(const espdl_conv_desc &d)
@@ -404,6 +805,12 @@ int conv2d_conv_tc(const espdl_conv_desc &d, cudaStream_t s)
     ConvTcParams p;
     if (!conv2d_conv_tc_supported(d) || !conv_plan(d, p))
         return ESPDL_ERR_UNSUPPORTED;
+    {
+        PatchParams pp;
+        memset(&pp, 0, sizeof(pp));
+        if (patch_plan(d, pp))
+            return launch_patch(d, pp, s);
+    }
     EncodeTiledFn enc = conv_encode();
     if (!enc)
         return set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");

@@ -264,3 +264,39 @@ def test_small_channel_conv_general_epilogue(round_mode, lut):
     """Half-even rounding takes the banded kernel's general epilogue; a fused table is applied in the staged epilogue."""
     case = cases.conv_case(seed=3, n=2, h=18, w=22, cin=16, cout=16, kh=3, kw=3, per_channel=True, round_mode=round_mode, lut=lut)
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), gpu_util.run_conv_oracle(case))
+
+
+# Stride-1 windows over 32, 64 or 128 input channels: one input patch per tile, taps as shifted descriptor starts, the
+# filter resident in shared memory (conv_patch_kernel in conv_tc.cu).
+PATCH = [
+    dict(n=2, h=80, w=80, cin=64, cout=64),                                   # the detector's 3x3 at its largest map
+    dict(n=3, h=20, w=17, cin=128, cout=48),                                  # ragged in both directions, one 32-position row per image row
+    dict(n=2, h=40, w=40, cin=128, cout=64),
+    dict(n=1, h=33, w=70, cin=64, cout=128),
+    dict(n=1, h=9, w=124, cin=64, cout=32),                                   # 128 positions per row
+    dict(n=2, h=24, w=24, cin=64, cout=32, kh=5, kw=5, pad=(2, 2, 2, 2)),     # 25 resident taps
+    dict(n=2, h=12, w=40, cin=64, cout=256, kh=1, kw=3, pad=(0, 0, 1, 1)),    # 256 columns: two epilogue parts per tile
+    dict(n=2, h=15, w=15, cin=64, cout=192, pad=(0, 0, 0, 0)),                # no padding, 96-column parts (unswizzled staging)
+    dict(n=5, h=7, w=7, cin=128, cout=16, pad=(1, 0, 0, 1)),                  # uneven pads, the smallest tile
+    dict(n=2, h=80, w=80, cin=32, cout=16),                                   # 32-byte rows, three taps side by side in 48 columns
+    dict(n=3, h=21, w=35, cin=32, cout=32, kh=2, kw=2, pad=(0, 1, 0, 1)),     # two taps side by side
+    dict(n=2, h=13, w=31, cin=32, cout=96),                                   # 32-byte rows, taps one by one
+    dict(n=2, h=11, w=45, cin=64, cout=48, kh=3, kw=4, pad=(1, 1, 1, 2)),     # four taps side by side
+]
+
+
+@pytest.mark.parametrize("kw", PATCH, ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items() if a != "pad"))
+@pytest.mark.parametrize("act,per_channel,lut,round_mode", [(abi.ACT_RELU, True, False, abi.ROUND_HALF_UP), (abi.ACT_LINEAR, False, True, abi.ROUND_HALF_UP),
+                                                            (abi.ACT_LINEAR, True, False, abi.ROUND_HALF_EVEN)])
+def test_conv_one_patch_per_tile(kw, act, per_channel, lut, round_mode, monkeypatch):
+    kw = dict(kw)
+    kw.setdefault("kh", 3)
+    kw.setdefault("kw", 3)
+    case = cases.conv_case(seed=91, per_channel=per_channel, e_in=-7, e_out=-6, e_w=(-9, -7), act=act, lut=lut, round_mode=round_mode, **kw)
+    want = gpu_util.run_conv_oracle(case)
+    assert want.std() > 0
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+    monkeypatch.setenv("ESPDL_B200_NO_TAP_STACK", "1")    # one MMA per tap instead of one per filter row
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+    monkeypatch.setenv("ESPDL_B200_NO_CONV_PATCH", "1")   # the tap-per-box kernel gives the same bytes
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
