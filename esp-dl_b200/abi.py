@@ -44,6 +44,7 @@ class EltwiseDesc(C.Structure):
         ("out_shape", i32 * 4), ("in0_shape", i32 * 4), ("in1_shape", i32 * 4),
         ("in0_exponent", i32), ("in1_exponent", i32), ("out_exponent", i32),
         ("clip_lo", i32), ("clip_hi", i32), ("round_mode", i32), ("lut_shift", i32), ("table", C.c_void_p),
+        ("in0_row_stride", C.c_int64), ("in1_row_stride", C.c_int64), ("out_row_stride", C.c_int64),
     ]
 
 
@@ -75,7 +76,7 @@ class CopyDesc(C.Structure):
 
 class PartsDesc(C.Structure):
     _fields_ = [("wide", C.c_void_p), ("parts", C.c_void_p * 8), ("part_bytes", C.c_int64 * 8), ("n_parts", i32), ("split", i32),
-                ("rows", C.c_int64)]
+                ("rows", C.c_int64), ("part_stride", C.c_int64 * 8), ("skip", i32 * 8)]
 
 
 class SoftmaxDesc(C.Structure):
@@ -190,6 +191,7 @@ SYMBOLS = {
     "espdl_b200_arena_free": (C.c_int, [C.c_void_p]),
     "espdl_b200_upload": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "espdl_b200_download": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "espdl_b200_download_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_void_p]),
     "espdl_b200_memset": (C.c_int, [C.c_void_p, C.c_int, C.c_size_t, C.c_void_p]),
     "espdl_b200_stream_sync": (C.c_int, [C.c_void_p]),
     "espdl_b200_host_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),

@@ -183,6 +183,18 @@ int espdl_b200_download(void *dst_host, const void *src_dev, size_t bytes, void 
     return ESPDL_OK;
 }
 
+int espdl_b200_download_rows(void *dst_host, const void *src_dev, size_t row_bytes, size_t src_stride_bytes, size_t rows, void *stream)
+{
+    if ((!dst_host || !src_dev) && row_bytes && rows)
+        return ESPDL_ERR_INVALID_ARG;
+    if (src_stride_bytes < row_bytes)
+        return ESPDL_ERR_INVALID_ARG;
+    if (!row_bytes || !rows)
+        return ESPDL_OK;
+    ESPDL_CUDA_TRY(cudaMemcpy2DAsync(dst_host, row_bytes, src_dev, src_stride_bytes, row_bytes, rows, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return ESPDL_OK;
+}
+
 int espdl_b200_memset(void *dst_dev, int value, size_t bytes, void *stream)
 {
     ESPDL_CUDA_TRY(cudaMemsetAsync(dst_dev, value, bytes, (cudaStream_t)stream));

@@ -349,6 +349,38 @@ static __device__ __noinline__ void epilogue_stage_stacked(uint32_t t0, int kw, 
 {
     const uint32_t rx = ((((uint32_t)(row * pw)) >> 7) & mask) << 4;
     const uint32_t rb = buf + (uint32_t)(row * pw);
+    if (kw == 3) {
+        // three column blocks per chunk, the next chunk's loads in flight while this one is requantised
+        int32_t a0[16], a1[16], a2[16];
+        ld16(t0, a0);
+        ld16(t0 + (uint32_t)stride, a1);
+        ld16(t0 + (uint32_t)(2 * stride), a2);
+#pragma unroll 1
+        for (int c = 0; c < pw; c += 16) {
+            int32_t v[16];
+            uint32_t pk[4];
+            ld_wait16(a0);
+            tie16(a1);
+            tie16(a2);
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = a0[i] + __shfl_down_sync(0xffffffffu, a1[i] + __shfl_down_sync(0xffffffffu, a2[i], 1), 1);
+            tie16(v);
+            if (c + 16 < pw) {
+                ld16(t0 + (uint32_t)(c + 16), a0);
+                ld16(t0 + (uint32_t)(c + 16 + stride), a1);
+                ld16(t0 + (uint32_t)(c + 16 + 2 * stride), a2);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                pk[q] = requant4_floor(v + 4 * q, fp + (uint32_t)(c + 4 * q) * 8u, floor_q);
+                if (tbl)
+                    pk[q] = lut4(pk[q], tbl);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rb + ((uint32_t)c ^ rx)), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                         : "memory");
+        }
+        return;
+    }
 #pragma unroll 1
     for (int c = 0; c < pw; c += 16) {
         int32_t v[16];

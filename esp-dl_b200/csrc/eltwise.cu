@@ -30,7 +30,23 @@ struct EltParams {
     int div_n1, div_table0; // Div: divisor broadcast along the innermost axis; int8 dividend of one element (table form)
     float div_scale;
     long long total;
+    // rows of the innermost axis that do not follow one another in memory (channel slices of a wider tensor): element
+    // strides between rows of the output / the operands; 0 = dense.  Vector kernels: the same in 16-byte units.
+    long long ro, ra, rb;
+    int vpr; // 16-byte units per row (vector kernels, strided rows only; 0 = flat)
 };
+
+// Vector index -> unit offsets of the output and the two operands.
+__device__ __forceinline__ void vec_offsets(const EltParams &p, long long v, long long &io, long long &ia, long long &ib)
+{
+    if (p.vpr) {
+        const long long row = v / p.vpr;
+        const long long col = v - row * p.vpr;
+        io = row * p.ro + col, ia = row * p.ra + col, ib = row * p.rb + col;
+    } else {
+        io = ia = ib = v;
+    }
+}
 
 __host__ __device__ __forceinline__ bool elt_two_operands(int op)
 {
@@ -139,6 +155,7 @@ __global__ void __launch_bounds__(256) elt_generic_kernel(EltParams p)
         const int i3 = (int)(r / p.os[1]);
         const long long ai = i3 * p.sa[0] + i2 * p.sa[1] + i1 * p.sa[2] + i0 * p.sa[3];
         const long long bi = i3 * p.sb[0] + i2 * p.sb[1] + i1 * p.sb[2] + i0 * p.sb[3];
+        const long long oi = p.ro ? (i / p.os[3]) * p.ro + i0 : i;
         if (p.op == ESPDL_ELT_LUT && p.idt == ESPDL_DTYPE_INT16) {
             // nearest table entry: index = ((uint16)x ^ 0x8000) >> shift, rounded (dl_base_lut.cpp:50-69)
             const uint32_t value = (uint32_t)(uint16_t)((const int16_t *)p.a)[ai] ^ 0x8000u;
@@ -149,13 +166,13 @@ __global__ void __launch_bounds__(256) elt_generic_kernel(EltParams p)
                 if (p.half_even ? (rem > half || (rem == half && (index & 1u))) : rem >= half)
                     index++;
             }
-            ((int16_t *)p.out)[i] = ((const int16_t *)p.b)[index];
+            ((int16_t *)p.out)[oi] = ((const int16_t *)p.b)[index];
         } else if (p.op == ESPDL_ELT_LUT) {
-            ((int8_t *)p.out)[i] = ((const int8_t *)p.b)[(uint8_t)((const int8_t *)p.a)[ai] ^ 0x80u];
+            ((int8_t *)p.out)[oi] = ((const int8_t *)p.b)[(uint8_t)((const int8_t *)p.a)[ai] ^ 0x80u];
         } else if (p.op == ESPDL_ELT_REQUANTIZE && p.idt == ESPDL_DTYPE_FLOAT) {
-            st_sat(p.out, p.odt, i, fround(__fmul_rn(((const float *)p.a)[ai], p.out_rescale), p.half_even));
+            st_sat(p.out, p.odt, oi, fround(__fmul_rn(((const float *)p.a)[ai], p.out_rescale), p.half_even));
         } else if (p.op == ESPDL_ELT_REQUANTIZE && p.odt == ESPDL_DTYPE_FLOAT) {
-            ((float *)p.out)[i] = __fmul_rn(__int2float_rn((int)ld_int(p.a, p.idt, ai)), p.in_scale);
+            ((float *)p.out)[oi] = __fmul_rn(__int2float_rn((int)ld_int(p.a, p.idt, ai)), p.in_scale);
         } else {
             const long long a = ld_int(p.a, p.idt, ai);
             long long b = 0;
@@ -163,7 +180,7 @@ __global__ void __launch_bounds__(256) elt_generic_kernel(EltParams p)
                 b = ld_int(p.b, p.idt, bi);
             else if (p.op == ESPDL_ELT_PRELU)
                 b = ld_int(p.b, p.idt, i0);
-            st_sat(p.out, p.odt, i, elt_int(p, a, b));
+            st_sat(p.out, p.odt, oi, elt_int(p, a, b));
         }
     }
 }
@@ -189,10 +206,12 @@ __global__ void __launch_bounds__(256) elt_s8_vec16_kernel(EltParams p, long lon
         __syncthreads();
     }
     for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-        const uint4 a4 = ((const uint4 *)p.a)[v];
+        long long io, ia, ib;
+        vec_offsets(p, v, io, ia, ib);
+        const uint4 a4 = ((const uint4 *)p.a)[ia];
         uint4 b4 = make_uint4(0, 0, 0, 0);
         if (elt_two_operands(OP))
-            b4 = ((const uint4 *)p.b)[v];
+            b4 = ((const uint4 *)p.b)[ib];
         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
         const uint32_t bw[4] = {b4.x, b4.y, b4.z, b4.w};
         uint32_t ow[4];
@@ -219,7 +238,7 @@ __global__ void __launch_bounds__(256) elt_s8_vec16_kernel(EltParams p, long lon
             }
             ow[q] = wd;
         }
-        ((uint4 *)p.out)[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        ((uint4 *)p.out)[io] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
@@ -236,7 +255,9 @@ __global__ void __launch_bounds__(256) elt_s8_scalar_b_kernel(EltParams p, long 
     }
     __syncthreads();
     for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
-        const uint4 a4 = ((const uint4 *)p.a)[v];
+        long long io, ia, ib;
+        vec_offsets(p, v, io, ia, ib);
+        const uint4 a4 = ((const uint4 *)p.a)[ia];
         const uint32_t aw[4] = {a4.x, a4.y, a4.z, a4.w};
         uint32_t ow[4];
 #pragma unroll
@@ -246,7 +267,7 @@ __global__ void __launch_bounds__(256) elt_s8_scalar_b_kernel(EltParams p, long 
             for (int j = 0; j < 4; j++) wd |= ((uint32_t)(uint8_t)table[(uint8_t)(aw[q] >> (8 * j)) ^ 0x80u]) << (8 * j);
             ow[q] = wd;
         }
-        ((uint4 *)p.out)[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        ((uint4 *)p.out)[io] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 }
 
@@ -297,18 +318,31 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     }
     long long a = 1, b = 1, total = 1;
     bool same = true;
+    // strided rows: a stride is given for a tensor whose innermost extent is the output's (no broadcast along it)
+    const long long rs0 = d->in0_row_stride, rs1 = binary ? d->in1_row_stride : 0, rso = d->out_row_stride;
+    if (rs0 < 0 || rs1 < 0 || rso < 0 || (rs0 && (rs0 < s0[3] || s0[3] != os[3])) || (rs1 && (rs1 < s1[3] || s1[3] != os[3])) || (rso && rso < os[3]))
+        return ESPDL_ERR_INVALID_ARG;
     for (int i = 3; i >= 0; i--) {
         if (os[i] < 0 || (s0[i] != os[i] && s0[i] != 1) || (s1[i] != os[i] && s1[i] != 1))
             return ESPDL_ERR_INVALID_ARG;
         p.os[i] = os[i];
         p.sa[i] = s0[i] == 1 ? 0 : a;
         p.sb[i] = s1[i] == 1 ? 0 : b;
-        a *= s0[i], b *= s1[i], total *= os[i];
+        a *= i == 3 && rs0 ? rs0 : s0[i], b *= i == 3 && rs1 ? rs1 : s1[i], total *= os[i];
         if (s0[i] != os[i] || (binary && s1[i] != os[i]))
             same = false;
     }
     if (total == 0)
         return ESPDL_OK;
+    const bool strided = rs0 || rs1 || rso;
+    if (strided && d->op == ESPDL_ELT_DIV)
+        return ESPDL_ERR_UNSUPPORTED; // Div reads the operands' element counts
+    p.ro = rso;
+    const bool rows16 = !strided || (os[3] % 16 == 0 && rs0 % 16 == 0 && rs1 % 16 == 0 && rso % 16 == 0);
+    if (strided && rows16) {
+        p.vpr = os[3] / 16;
+        p.ra = (rs0 ? rs0 : os[3]) / 16, p.rb = (rs1 ? rs1 : os[3]) / 16;
+    }
     p.a = d->input0, p.b = d->input1, p.out = d->output;
     p.op = d->op, p.idt = d->in_dtype, p.odt = d->out_dtype;
     p.e0 = d->in0_exponent, p.e1 = d->in1_exponent, p.eo = d->out_exponent;
@@ -337,14 +371,16 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     p.prelu_shift = p.eo - p.e0 - p.e1;
     p.total = total;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = same && d->in_dtype == ESPDL_DTYPE_INT8 && (d->out_dtype == ESPDL_DTYPE_INT8 || compare) && total % 16 == 0 &&
+    const bool vec = same && rows16 && d->in_dtype == ESPDL_DTYPE_INT8 && (d->out_dtype == ESPDL_DTYPE_INT8 || compare) && total % 16 == 0 &&
         ((uintptr_t)d->input0 % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && (!binary || ((uintptr_t)d->input1 % 16) == 0) &&
         d->op != ESPDL_ELT_PRELU && d->op != ESPDL_ELT_POW;
     // second operand of one element, first operand of the output's shape
     bool a_full = true;
     for (int i = 0; i < 4; i++) a_full = a_full && s0[i] == os[i];
-    const bool scalar_b = binary && !compare && !same && a_full && b == 1 && d->in_dtype == ESPDL_DTYPE_INT8 && d->out_dtype == ESPDL_DTYPE_INT8 &&
+    const bool scalar_b = binary && !compare && !same && a_full && b == 1 && rows16 && d->in_dtype == ESPDL_DTYPE_INT8 && d->out_dtype == ESPDL_DTYPE_INT8 &&
         total % 16 == 0 && ((uintptr_t)d->input0 % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && d->op != ESPDL_ELT_POW;
+    if ((scalar_b || vec) && p.vpr)
+        p.ro = (rso ? rso : os[3]) / 16;
     if (scalar_b) {
         const long long nvec = total / 16;
         const long long blocks = min((nvec + 255) / 256, (long long)num_sms() * 16);

@@ -502,6 +502,7 @@ struct PartsParams {
     uint4 *wide;
     uint4 *parts[8];
     int start[9]; // first unit of part i inside a row of the wide tensor; start[n_parts] = units per row
+    long long pitch[8]; // units between rows of part i; a null part is left alone
     int n_parts, split;
     long long total; // rows x units per row
 };
@@ -517,7 +518,9 @@ __global__ void __launch_bounds__(256) concat_split_kernel(PartsParams p)
         for (int k = 1; k < 8; k++)
             if (k < p.n_parts && col >= p.start[k])
                 i = k;
-        uint4 *part = p.parts[i] + row * (p.start[i + 1] - p.start[i]) + (col - p.start[i]);
+        if (!p.parts[i])
+            continue;
+        uint4 *part = p.parts[i] + row * p.pitch[i] + (col - p.start[i]);
         if (p.split)
             *part = p.wide[u];
         else
@@ -537,10 +540,16 @@ extern "C" int espdl_b200_concat_split(const espdl_parts_desc *d, void *stream)
     for (int i = 0; i < 8; i++) {
         p.parts[i] = nullptr;
         p.start[i] = (int)units;
+        p.pitch[i] = 0;
         if (i < d->n_parts) {
-            if (!d->parts[i] || d->part_bytes[i] <= 0 || d->part_bytes[i] % 16 || ((uintptr_t)d->parts[i] % 16))
+            if (d->part_bytes[i] <= 0 || d->part_bytes[i] % 16)
                 return ESPDL_ERR_INVALID_ARG;
-            p.parts[i] = (uint4 *)d->parts[i];
+            if (!d->skip[i]) {
+                if (!d->parts[i] || ((uintptr_t)d->parts[i] % 16) || d->part_stride[i] % 16 || (d->part_stride[i] && d->part_stride[i] < d->part_bytes[i]))
+                    return ESPDL_ERR_INVALID_ARG;
+                p.parts[i] = (uint4 *)d->parts[i];
+                p.pitch[i] = (d->part_stride[i] ? d->part_stride[i] : d->part_bytes[i]) / 16;
+            }
             units += d->part_bytes[i] / 16;
             if (units > 0x7fffffffll)
                 return ESPDL_ERR_TOO_LARGE;

@@ -20,12 +20,14 @@ size_t MemoryManagerGreedy::plan(std::vector<TensorInfo> &tensors, bool reuse)
         while (tensors[r].alias_of >= 0) r = tensors[r].alias_of;
         root[i] = r;
     }
-    std::vector<int> last(tensors.size());
+    std::vector<int> last(tensors.size()), first(tensors.size());
     std::vector<size_t> bytes(tensors.size());
-    for (size_t i = 0; i < tensors.size(); i++) last[i] = tensors[i].last, bytes[i] = round_up(tensors[i].bytes);
+    for (size_t i = 0; i < tensors.size(); i++) last[i] = tensors[i].last, first[i] = tensors[i].first, bytes[i] = round_up(tensors[i].bytes);
     for (size_t i = 0; i < tensors.size(); i++) {
         last[root[i]] = std::max(last[root[i]], tensors[i].last);
-        bytes[root[i]] = std::max(bytes[root[i]], round_up(tensors[i].bytes));
+        first[root[i]] = std::min(first[root[i]], tensors[i].first); // a slice may be written before the tensor it lives in
+        if (!tensors[i].row_stride) // a slice lies inside its root
+            bytes[root[i]] = std::max(bytes[root[i]], round_up(tensors[i].bytes));
     }
     struct Chunk {
         size_t offset, size;
@@ -37,12 +39,12 @@ size_t MemoryManagerGreedy::plan(std::vector<TensorInfo> &tensors, bool reuse)
     for (size_t i = 0; i < tensors.size(); i++)
         if (root[i] == (int)i)
             order.push_back((int)i);
-    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return tensors[a].first < tensors[b].first; });
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return first[a] < first[b]; });
     std::vector<int> live;
     for (int t : order) {
         if (reuse) {
             for (size_t k = 0; k < live.size();) {
-                if (last[live[k]] < tensors[t].first) {
+                if (last[live[k]] < first[t]) {
                     Chunk c{tensors[live[k]].offset, bytes[live[k]]};
                     // coalesce with neighbours
                     for (size_t f = 0; f < free_list.size();) {
@@ -93,10 +95,25 @@ size_t MemoryManagerGreedy::plan(std::vector<TensorInfo> &tensors, bool reuse)
         }
         live.push_back(t);
     }
-    for (size_t i = 0; i < tensors.size(); i++)
-        if (root[i] != (int)i)
-            tensors[i].offset = tensors[root[i]].offset;
+    for (size_t i = 0; i < tensors.size(); i++) {
+        if (root[i] == (int)i)
+            continue;
+        size_t off = tensors[root[i]].offset;
+        for (int r = (int)i; tensors[r].alias_of >= 0; r = tensors[r].alias_of) off += tensors[r].view_offset;
+        tensors[i].offset = off;
+    }
     return arena;
+}
+
+// A tensor's device copy into a dense host buffer, also when it is a channel slice of a wider tensor.
+static void download_dense(void *host, TensorBase *t, void *stream)
+{
+    if (!t->row_stride) {
+        espdl_b200_download(host, t->device, t->get_bytes(), stream);
+        return;
+    }
+    const size_t es = dtype_sizeof(t->dtype), row = (size_t)t->shape.back() * es;
+    espdl_b200_download_rows(host, t->device, row, (size_t)t->row_stride * es, row ? t->get_bytes() / row : 0, stream);
 }
 
 // ----------------------------------------------------------------------------- model
@@ -530,6 +547,98 @@ void Model::fold_residual_adds()
     }
 }
 
+// Concat and Split along the last axis without the copy: an input of a Concat whose producer can write rows a stride
+// apart is placed inside the Concat's output (the producer writes its channels of every row directly), and an output
+// of a Split whose consumers can read such rows is a window into the Split's input.  Both need every other consumer of
+// the slice to read strided rows too; offsets, widths and strides are whole 16-byte units.  A tensor is a slice of one
+// wider tensor at most, and a tensor that holds slices is not itself a slice.  Returns how many tensors became slices.
+int Model::alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::string, int> &info_index,
+                                const std::vector<std::vector<std::vector<int>>> &step_in_shapes, std::vector<bool> &is_root)
+{
+    const int steps = (int)m_execution_plan.size();
+    std::vector<std::vector<std::pair<int, int>>> consumers(infos.size()); // (step, input position)
+    for (int step = 0; step < steps; step++)
+        for (size_t i = 0; i < m_module_inputs[step].size(); i++) {
+            auto it = info_index.find(m_module_inputs[step][i]);
+            if (it != info_index.end())
+                consumers[it->second].push_back({step, (int)i});
+        }
+    std::vector<bool> is_view(infos.size(), false);
+    auto readers_ok = [&](int t, int but_step) {
+        for (const auto &c : consumers[t])
+            if (c.first != but_step && !m_execution_plan[c.first]->strided_input_ok(c.second, step_in_shapes[c.first]))
+                return false;
+        return true;
+    };
+    int made = 0;
+    for (int step = 0; step < steps; step++) {
+        module::Module *mod = m_execution_plan[step];
+        if (module::Concat *cat = dynamic_cast<module::Concat *>(mod)) {
+            auto oit = info_index.find(m_module_outputs[step][0]);
+            if (oit == info_index.end())
+                continue;
+            const int out = oit->second;
+            const int nd = (int)infos[out].shape.size();
+            const int ax = cat->get_axis() < 0 ? cat->get_axis() + nd : cat->get_axis();
+            const long long es = (long long)dtype_sizeof(infos[out].dtype);
+            if (nd < 2 || ax != nd - 1 || is_view[out] || infos[out].alias_of >= 0 || (infos[out].shape[ax] * es) % 16 != 0)
+                continue;
+            long long off = 0;
+            for (size_t i = 0; i < m_module_inputs[step].size(); i++) {
+                const std::string &in_name = m_module_inputs[step][i];
+                const long long ci = step_in_shapes[step][i].empty() ? 0 : step_in_shapes[step][i].back();
+                auto it = info_index.find(in_name);
+                const long long at = off;
+                off += ci;
+                if (it == info_index.end())
+                    continue;
+                const int t = it->second;
+                TensorInfo &ti = infos[t];
+                if (ti.is_graph_io || ti.first < 0 || is_view[t] || is_root[t] || ti.alias_of >= 0 || ti.dtype != infos[out].dtype ||
+                    (at * es) % 16 != 0 || (ci * es) % 16 != 0 || (int)ti.shape.size() != nd)
+                    continue;
+                if (std::count(m_module_inputs[step].begin(), m_module_inputs[step].end(), in_name) != 1)
+                    continue;
+                const std::vector<std::string> &pouts = m_module_outputs[ti.first];
+                const int o_pos = (int)(std::find(pouts.begin(), pouts.end(), in_name) - pouts.begin());
+                if (!m_execution_plan[ti.first]->strided_output_ok(o_pos, step_in_shapes[ti.first]) || !readers_ok(t, step))
+                    continue;
+                ti.alias_of = out, ti.view_offset = (size_t)(at * es), ti.row_stride = infos[out].shape[ax];
+                is_view[t] = true, is_root[out] = true;
+                made++;
+            }
+        } else if (module::Split *sp = dynamic_cast<module::Split *>(mod)) {
+            auto xit = info_index.find(m_module_inputs[step][0]);
+            if (xit == info_index.end())
+                continue;
+            const int x = xit->second;
+            const int nd = (int)infos[x].shape.size();
+            const int ax = sp->get_axis() < 0 ? sp->get_axis() + nd : sp->get_axis();
+            const long long es = (long long)dtype_sizeof(infos[x].dtype);
+            if (nd < 2 || ax != nd - 1 || is_view[x] || infos[x].alias_of >= 0 || (infos[x].shape[ax] * es) % 16 != 0)
+                continue;
+            long long off = 0;
+            for (size_t o = 0; o < m_module_outputs[step].size(); o++) {
+                auto it = info_index.find(m_module_outputs[step][o]);
+                if (it == info_index.end())
+                    break;
+                const int t = it->second;
+                TensorInfo &ti = infos[t];
+                const long long co = ti.shape.empty() ? 0 : ti.shape.back();
+                const long long at = off;
+                off += co;
+                if (ti.is_graph_io || ti.last == INT_MAX || is_view[t] || is_root[t] || ti.alias_of >= 0 || (at * es) % 16 != 0 || (co * es) % 16 != 0 ||
+                    consumers[t].empty() || !mod->strided_output_ok((int)o, step_in_shapes[step]) || !readers_ok(t, -1))
+                    continue;
+                ti.alias_of = x, ti.view_offset = (size_t)(at * es), ti.row_stride = infos[x].shape[ax];
+                is_view[t] = true, is_root[x] = true;
+                made++;
+            }
+        }
+    }
+    return made;
+}
+
 void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool preload, const std::map<std::string, std::vector<int>> &input_shapes)
 {
     (void)max_internal_size;
@@ -570,6 +679,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
         ti.last = INT_MAX;
     }
     // shape inference, lifetimes and in-place links along the plan
+    std::vector<std::vector<std::vector<int>>> step_in_shapes;
     for (size_t step = 0; step < m_execution_plan.size(); step++) {
         module::Module *mod = m_execution_plan[step];
         std::vector<std::vector<int>> in_shapes;
@@ -599,6 +709,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
         std::vector<std::vector<int>> out_shapes = mod->get_output_shape(in_shapes);
         for (size_t o = 0; o < m_module_outputs[step].size() && o < out_shapes.size(); o++)
             add_info(m_module_outputs[step][o], out_shapes[o], (int)step);
+        step_in_shapes.push_back(in_shapes);
     }
     for (const std::string &name : m_fbs_model->get_graph_outputs()) {
         auto it = info_index.find(name);
@@ -610,13 +721,18 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
     // In-place: a view (Reshape / Flatten / ...) always shares its input's buffer; a module that may overwrite an
     // input (Add, LUT, RequantizeLinear, ...) takes the buffer of an input that dies at this step, is no graph
     // input/output, is not shared through a view, and is large enough (dl_memory_manager_greedy.cpp:147-212).
+    std::vector<bool> slice_root(infos.size(), false);
+    if (env_flag("ESPDL_B200_SLICE_VIEWS", true))
+        m_slice_views = alias_channel_slices(infos, info_index, step_in_shapes, slice_root);
     if (m_reuse_memory) {
-        std::vector<bool> has_view(infos.size(), false);
+        std::vector<bool> has_view = slice_root; // nothing is overwritten in a buffer that holds slices
         for (size_t step = 0; step < m_execution_plan.size(); step++) {
             module::Module *mod = m_execution_plan[step];
             if (mod->inplace == MODULE_NON_INPLACE || m_module_outputs[step].size() != 1)
                 continue;
             const int out = info_index[m_module_outputs[step][0]];
+            if (infos[out].row_stride)
+                continue; // the output is a slice of a Concat output: it has its place already
             for (const std::string &in_name : m_module_inputs[step]) {
                 auto it = info_index.find(in_name);
                 if (it == info_index.end())
@@ -662,6 +778,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
     for (TensorInfo &ti : infos) {
         TensorBase *t = new TensorBase(ti.shape, nullptr, ti.exponent, ti.dtype, false);
         t->device = (char *)m_arena + ti.offset;
+        t->row_stride = ti.row_stride;
         if (ti.is_graph_io) { // pinned host buffer the user reads / writes
             void *h = nullptr;
             if (espdl_b200_host_alloc(t->get_aligned_bytes(), &h) == ESPDL_OK) {
@@ -856,7 +973,10 @@ void Model::run(std::map<std::string, TensorBase *> &user_inputs, runtime_mode_t
     for (auto &kv : user_outputs) {
         TensorBase *t = get_intermediate(kv.first);
         if (t && kv.second && kv.second->data && t->device) {
-            espdl_b200_download(kv.second->data, t->device, std::min(kv.second->get_bytes(), t->get_bytes()), m_model_context->stream);
+            if (t->row_stride && kv.second->get_bytes() >= t->get_bytes())
+                download_dense(kv.second->data, t, m_model_context->stream);
+            else if (!t->row_stride)
+                espdl_b200_download(kv.second->data, t->device, std::min(kv.second->get_bytes(), t->get_bytes()), m_model_context->stream);
             espdl_b200_stream_sync(m_model_context->stream);
         }
     }
@@ -917,7 +1037,7 @@ esp_err_t Model::test()
                 continue;
             TensorBase *got_dev = ctx->get_tensor(out_name);
             TensorBase got(got_dev->shape, nullptr, (int)got_dev->exponent, got_dev->dtype, true);
-            espdl_b200_download(got.data, got_dev->device, got.get_bytes(), ctx->stream);
+            download_dense(got.data, got_dev, ctx->stream);
             espdl_b200_stream_sync(ctx->stream);
             if (!got.equal(expect, 2e-5f, true)) {
                 ESP_LOGE("dl::Model", "Test failed for output %s of %s", out_name.c_str(), m_module_types[step].c_str());

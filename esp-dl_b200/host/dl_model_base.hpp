@@ -30,6 +30,8 @@ struct TensorInfo {
     size_t bytes = 0;
     size_t offset = 0;
     int alias_of = -1;      ///< index of the tensor whose buffer this one shares (in-place / view), or -1
+    size_t view_offset = 0; ///< bytes from the start of `alias_of`'s buffer (a channel slice of a Concat output / Split input)
+    int row_stride = 0;     ///< elements between rows of the last axis when this tensor is such a slice, else 0
     bool is_graph_io = false;
 };
 
@@ -108,10 +110,13 @@ public:
 
     // backend knobs (set before build / the constructor reads the environment for defaults)
     bool m_use_graph = true;     ///< replay the plan as a captured CUDA graph
+    int m_slice_views = 0;       ///< tensors placed as channel slices of a Concat output / Split input (no copy)
     bool m_reuse_memory = true;  ///< false: every tensor keeps its own buffer (lets tests read intermediates)
     int m_status = 0;            ///< first failing C-ABI status, 0 if none
     size_t arena_bytes() const { return m_arena_bytes; }
     size_t num_modules() const { return m_execution_plan.size(); }
+    /// Tensors that live as channel slices inside a Concat output / Split input (ESPDL_B200_SLICE_VIEWS=0 switches them off).
+    int num_slice_views() const { return m_slice_views; }
     void *stream() { return m_model_context ? m_model_context->stream : nullptr; }
     int round_mode() const { return m_model_context ? (int)m_model_context->round_mode : 0; }
 
@@ -138,6 +143,8 @@ protected:
     long long m_submitted = 0, m_collected = 0;
     void release_pipeline();
     void fold_residual_adds();
+    int alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::string, int> &info_index,
+                             const std::vector<std::vector<std::vector<int>>> &step_in_shapes, std::vector<bool> &is_root);
     void fold_luts();
     /// A QuantizeLinear whose only input is the float output of a Softmax / LogSoftmax with no other reader disappears: the softmax
     /// kernel writes the quantized tensor itself (the same `round(y * 2^-e)` on the same float).  ESPDL_B200_FOLD_QUANT=0 keeps it.

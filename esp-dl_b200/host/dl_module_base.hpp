@@ -66,6 +66,18 @@ public:
     virtual void forward_args(void *args) { (void)args; }
     /// Called once after the tensor table is complete and parameters are on the device.
     virtual esp_err_t prepare(ModelContext *context) { (void)context; return ESP_OK; }
+    /// May input `i` / output `o` be a channel slice of a wider tensor (TensorBase::row_stride != 0)?  The planner asks
+    /// with the shapes of all inputs, parameters included; slices start and stride on 16-byte boundaries.
+    virtual bool strided_input_ok(int i, const std::vector<std::vector<int>> &input_shapes) const
+    {
+        (void)i, (void)input_shapes;
+        return false;
+    }
+    virtual bool strided_output_ok(int o, const std::vector<std::vector<int>> &input_shapes) const
+    {
+        (void)o, (void)input_shapes;
+        return false;
+    }
     /// Bytes of shared scratch forward() needs (0 for most modules).
     virtual size_t workspace_bytes(ModelContext *context) { (void)context; return 0; }
     virtual void print() {}

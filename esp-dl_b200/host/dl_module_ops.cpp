@@ -179,25 +179,9 @@ esp_err_t Conv::prepare(ModelContext *context)
         !getenv("ESPDL_B200_NO_PIXEL_GROUPING")) {
         const int cin = fs[2], cout = fs[3];
         const long long pixels = (long long)input->shape[1] * input->shape[2];
-        // Score of a grouping g: input row width towards 128 bytes, output rows made of whole 16-byte groups and at
-        // least 32 bytes wide, minus the extra L2 traffic of the g*g times larger filter (bytes per pixel relative to
-        // the activations).  ESPDL_B200_GROUP_K, when set, caps g * Cin.
-        const int cap = getenv("ESPDL_B200_GROUP_K") ? atoi(getenv("ESPDL_B200_GROUP_K")) : 1 << 20;
-        int best = 1;
-        double best_score = -1.0;
-        for (int g : {1, 2, 4, 8, 16}) {
-            if ((g * cin) % 16 != 0 || pixels % g != 0 || g * cout > 1024 || (g > 1 && g * cin > cap))
-                continue;
-            const double in_score = std::min(g * cin, 128) / 128.0;
-            const double out_score = ((g * cout) % 16 == 0 ? 1.0 : 0.0) + 0.5 * std::min(g * cout, 32) / 32.0;
-            const double filter_cost = g == 1 ? 0.0 : 0.5 * ((double)g * cin * cout / 128.0) / (cin + cout);
-            const double score = in_score + out_score - filter_cost;
-            if (score > best_score + 1e-9) {
-                best_score = score;
-                best = g;
-            }
-        }
-        m_group_px = best;
+        TensorBase *output = context->get_tensor(m_outputs_index[0]);
+        const bool sliced = input->row_stride || (output && output->row_stride); // a slice has no runs of whole pixels
+        m_group_px = sliced ? 1 : choose_pixel_group(cin, cout, pixels);
         if (m_group_px > 1) {
             const int g = m_group_px;
             std::vector<int8_t> wf((size_t)g * cout * g * cin, 0);
@@ -224,6 +208,48 @@ esp_err_t Conv::prepare(ModelContext *context)
         }
     }
     return espdl_b200_stream_sync(nullptr) == ESPDL_OK ? ESP_OK : ESP_FAIL;
+}
+
+int Conv::choose_pixel_group(int cin, int cout, long long pixels)
+{
+    // Score of a grouping g: input row width towards 128 bytes, output rows made of whole 16-byte groups and at
+    // least 32 bytes wide, minus the extra L2 traffic of the g*g times larger filter (bytes per pixel relative to
+    // the activations).  ESPDL_B200_GROUP_K, when set, caps g * Cin.
+    const int cap = getenv("ESPDL_B200_GROUP_K") ? atoi(getenv("ESPDL_B200_GROUP_K")) : 1 << 20;
+    int best = 1;
+    double best_score = -1.0;
+    for (int g : {1, 2, 4, 8, 16}) {
+        if ((g * cin) % 16 != 0 || pixels % g != 0 || g * cout > 1024 || (g > 1 && g * cin > cap))
+            continue;
+        const double in_score = std::min(g * cin, 128) / 128.0;
+        const double out_score = ((g * cout) % 16 == 0 ? 1.0 : 0.0) + 0.5 * std::min(g * cout, 32) / 32.0;
+        const double filter_cost = g == 1 ? 0.0 : 0.5 * ((double)g * cin * cout / 128.0) / (cin + cout);
+        const double score = in_score + out_score - filter_cost;
+        if (score > best_score + 1e-9) {
+            best_score = score;
+            best = g;
+        }
+    }
+    return best;
+}
+
+bool Conv::strided_ok(const std::vector<std::vector<int>> &in) const
+{
+    if (m_gemm || quant_type != QUANT_TYPE_SYMM_8BIT || in.size() < 2 || in[0].size() != 4 || in[1].size() != 4)
+        return false;
+    const std::vector<int> &x = in[0], &f = in[1];
+    const int cin = x[3];
+    if (m_group != 1)
+        return cin % 16 == 0; // depthwise: both kernels take pixel strides
+    const int cout = f[3];
+    if (cin % 16 != 0 || cout % 16 != 0)
+        return false;
+    if (f[0] == 3 && f[1] == 3 && cin == 16)
+        return false; // the banded kernel reads 128-byte runs of whole pixels
+    const bool plain_1x1 = f[0] == 1 && f[1] == 1 && m_strides[0] == 1 && m_strides[1] == 1 && m_pads[0] + m_pads[1] + m_pads[2] + m_pads[3] == 0;
+    if (plain_1x1 && !m_no_grouping && !getenv("ESPDL_B200_NO_PIXEL_GROUPING") && choose_pixel_group(cin, cout, (long long)x[1] * x[2]) != 1)
+        return false;
+    return true;
 }
 
 int Conv::fill_desc(ModelContext *context, void *desc)
@@ -266,6 +292,7 @@ int Conv::fill_desc(ModelContext *context, void *desc)
         return ESPDL_ERR_UNSUPPORTED;
     }
     d.in_exponent = input->exponent, d.out_exponent = m_lut ? m_pre_lut_exponent : (int)output->exponent;
+    d.in_pixel_stride = input->row_stride, d.out_pixel_stride = output->row_stride; // channel slices (0 = dense)
     d.per_channel = filter->exponent.is_per_channel();
     d.filter_exponent = filter->exponent;
     if (m_group_px > 1) { // same bytes, g pixels per row: [N, 1, H*W/g, g*Cin] x block-diagonal filter -> [N, 1, H*W/g, g*Cout]
@@ -742,8 +769,20 @@ void Elementwise::forward(ModelContext *context, runtime_mode_t mode)
     int st = ESPDL_OK;
     if (!a || !b || !out || !a->device || !b->device || !out->device)
         st = ESPDL_ERR_INVALID_ARG;
-    if (!st && !pack_shapes(out->shape, a->shape, b->shape, d))
+    const bool sliced = !st && (a->row_stride || b->row_stride || out->row_stride);
+    if (sliced) { // operands of one shape: rows of the last axis, each tensor with its own row stride
+        if (a->shape != out->shape || b->shape != out->shape) {
+            st = ESPDL_ERR_UNSUPPORTED;
+        } else {
+            const int c = out->shape.back();
+            d.ndim = 2;
+            d.out_shape[0] = d.in0_shape[0] = d.in1_shape[0] = out->get_size() / c;
+            d.out_shape[1] = d.in0_shape[1] = d.in1_shape[1] = c;
+            d.in0_row_stride = a->row_stride, d.in1_row_stride = b->row_stride, d.out_row_stride = out->row_stride;
+        }
+    } else if (!st && !pack_shapes(out->shape, a->shape, b->shape, d)) {
         st = ESPDL_ERR_UNSUPPORTED;
+    }
     if (!st) {
         d.input0 = a->device, d.input1 = b->device, d.output = out->device;
         d.op = m_op, d.in_dtype = espdl_dtype(a), d.out_dtype = espdl_dtype(out);
@@ -754,6 +793,11 @@ void Elementwise::forward(ModelContext *context, runtime_mode_t mode)
     if (st)
         ESP_LOGE("Elementwise", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
     context->note(st);
+}
+
+bool Elementwise::same_shapes(const std::vector<std::vector<int>> &in) const
+{
+    return m_op != ESPDL_ELT_DIV && in.size() == 2 && !in[0].empty() && in[0] == in[1];
 }
 
 Add::Add(const char *name, module_inplace_t inplace, quant_type_t quant_type) : Elementwise(ESPDL_ELT_ADD, name, inplace, quant_type) {}
@@ -818,7 +862,15 @@ void Unary::forward(ModelContext *context, runtime_mode_t mode)
             int step = 65536 / (m_param->get_size() - 1);
             while (step > 1) d.lut_shift++, step >>= 1;
         }
-        if (m_op == ESPDL_ELT_PRELU && in->shape.size() <= 4) {
+        if (in->row_stride || out->row_stride) { // a channel slice on either side: rows of the last axis
+            const int c = in->shape.back();
+            d.ndim = 2;
+            d.out_shape[0] = d.in0_shape[0] = in->get_size() / c, d.out_shape[1] = d.in0_shape[1] = c;
+            d.in1_shape[0] = d.in1_shape[1] = 1;
+            d.in0_row_stride = in->row_stride, d.out_row_stride = out->row_stride;
+            if (m_op == ESPDL_ELT_PRELU)
+                st = ESPDL_ERR_UNSUPPORTED;
+        } else if (m_op == ESPDL_ELT_PRELU && in->shape.size() <= 4) {
             d.ndim = (int)in->shape.size();
             for (int i = 0; i < d.ndim; i++) d.out_shape[i] = d.in0_shape[i] = in->shape[i], d.in1_shape[i] = 1;
         } else {
@@ -826,11 +878,17 @@ void Unary::forward(ModelContext *context, runtime_mode_t mode)
             d.out_shape[0] = d.in0_shape[0] = in->get_size();
             d.in1_shape[0] = 1;
         }
-        st = espdl_b200_eltwise(&d, context->stream);
+        if (!st)
+            st = espdl_b200_eltwise(&d, context->stream);
     }
     if (st)
         ESP_LOGE("Unary", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
     context->note(st);
+}
+
+bool Unary::strided_input_ok(int i, const std::vector<std::vector<int>> &in) const
+{
+    return i == 0 && m_op != ESPDL_ELT_PRELU && !in.empty() && !in[0].empty();
 }
 
 RequantizeLinear::RequantizeLinear(const char *name, module_inplace_t inplace, quant_type_t quant_type) :
@@ -1084,6 +1142,7 @@ void Resize::forward(ModelContext *context, runtime_mode_t mode)
             d.scale_h = 1, d.scale_w = m_scales[2];
         }
         d.in_exponent = in->exponent, d.out_exponent = out->exponent;
+        d.out_pixel_stride = out->row_stride;
         d.mode = m_resize_mode == RESIZE_NEAREST ? 0 : (m_align_corners ? 2 : 1);
         st = espdl_b200_resize(&d, context->stream);
     }
@@ -1148,6 +1207,18 @@ static std::vector<long long> dense_strides(const std::vector<int> &shape)
     return st;
 }
 
+// Element strides of a tensor's device copy: dense, or with the rows of the last axis `row_stride` apart (a channel slice).
+static std::vector<long long> device_strides(const TensorBase *t)
+{
+    std::vector<long long> st = dense_strides(t->shape);
+    if (t->row_stride && t->shape.size() >= 2) {
+        const int nd = (int)t->shape.size();
+        st[nd - 2] = t->row_stride;
+        for (int i = nd - 3; i >= 0; i--) st[i] = st[i + 1] * t->shape[i + 1];
+    }
+    return st;
+}
+
 std::vector<std::vector<int>> Concat::get_output_shape(std::vector<std::vector<int>> &input_shapes)
 {
     const int nd = (int)input_shapes[0].size();
@@ -1172,6 +1243,11 @@ static bool parts_in_one_launch(ModelContext *context, TensorBase *wide, const s
     espdl_parts_desc d;
     memset(&d, 0, sizeof(d));
     d.wide = wide->device, d.n_parts = (int)parts.size(), d.split = split ? 1 : 0, d.rows = rows;
+    long long at = 0, wide_row = 0;
+    for (TensorBase *t : parts)
+        if (t && (int)t->shape.size() == (int)wide->shape.size())
+            wide_row += (long long)t->shape[axis] * inner;
+    int to_move = 0;
     for (size_t i = 0; i < parts.size(); i++) {
         TensorBase *t = parts[i];
         if (!t || !t->device || ((uintptr_t)t->device % 16) || t->dtype != wide->dtype || (int)t->shape.size() != (int)wide->shape.size())
@@ -1180,9 +1256,47 @@ static bool parts_in_one_launch(ModelContext *context, TensorBase *wide, const s
         d.part_bytes[i] = (long long)t->shape[axis] * inner;
         if (d.part_bytes[i] % 16 != 0)
             return false;
+        if (t->row_stride) { // a channel slice: already inside the wide tensor (nothing to move), or rows apart elsewhere
+            d.part_stride[i] = (long long)t->row_stride * es;
+            if ((char *)t->device == (char *)wide->device + at && d.part_stride[i] == wide_row)
+                d.skip[i] = 1;
+        }
+        to_move += d.skip[i] ? 0 : 1;
+        at += d.part_bytes[i];
     }
-    st = espdl_b200_concat_split(&d, context->stream);
+    st = to_move ? espdl_b200_concat_split(&d, context->stream) : ESPDL_OK;
     return true;
+}
+
+// Last axis, at most eight parts, every part whole 16-byte units per row: the one-launch form, which also moves slices.
+static bool parts_are_units(const std::vector<std::vector<int>> &shapes, int axis, int es)
+{
+    if (shapes.empty() || shapes.size() > 8 || shapes[0].size() < 2)
+        return false;
+    const int nd = (int)shapes[0].size();
+    if ((axis < 0 ? axis + nd : axis) != nd - 1)
+        return false;
+    for (const std::vector<int> &s : shapes)
+        if ((int)s.size() != nd || ((long long)s.back() * es) % 16 != 0)
+            return false;
+    return true;
+}
+
+static int quant_elem_size(quant_type_t q) { return q == QUANT_TYPE_SYMM_16BIT ? 2 : 1; }
+
+bool Concat::strided_input_ok(int i, const std::vector<std::vector<int>> &in) const
+{
+    return i >= 0 && i < (int)in.size() && quant_type != QUANT_TYPE_NONE && parts_are_units(in, axis, quant_elem_size(quant_type));
+}
+
+bool Split::strided_output_ok(int o, const std::vector<std::vector<int>> &in) const
+{
+    if (o < 0 || in.empty() || quant_type == QUANT_TYPE_NONE)
+        return false;
+    std::vector<std::vector<int>> shapes = in;
+    shapes.resize(1);
+    std::vector<std::vector<int>> outs = const_cast<Split *>(this)->get_output_shape(shapes);
+    return o < (int)outs.size() && parts_are_units(outs, m_axis, quant_elem_size(quant_type));
 }
 
 void Concat::forward(ModelContext *context, runtime_mode_t mode)
@@ -1210,8 +1324,11 @@ void Concat::forward(ModelContext *context, runtime_mode_t mode)
             st = ESPDL_ERR_INVALID_ARG;
             break;
         }
-        st = enqueue_copy(context, in->device, (char *)out->device + offset * os[axis] * es, es, in->shape, dense_strides(in->shape), os);
+        char *place = (char *)out->device + offset * os[axis] * es;
         offset += in->shape[axis];
+        if (in->row_stride && (char *)in->device == place && in->row_stride == out->shape.back())
+            continue; // a slice of this very output: its producer wrote it in place
+        st = enqueue_copy(context, in->device, place, es, in->shape, device_strides(in), os);
     }
     if (st)
         ESP_LOGE("Concat", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));
@@ -1278,8 +1395,11 @@ void Split::forward(ModelContext *context, runtime_mode_t mode)
             st = ESPDL_ERR_INVALID_ARG;
             break;
         }
-        st = enqueue_copy(context, (char *)in->device + offset * is[m_axis] * es, out->device, es, out->shape, is, dense_strides(out->shape));
+        char *place = (char *)in->device + offset * is[m_axis] * es;
         offset += out->shape[m_axis];
+        if (out->row_stride && (char *)out->device == place && out->row_stride == in->shape.back())
+            continue; // a window into this very input
+        st = enqueue_copy(context, place, out->device, es, out->shape, is, device_strides(out));
     }
     if (st)
         ESP_LOGE("Split", "%s failed: %s", name ? name : "?", espdl_b200_strerror(st));

@@ -47,12 +47,19 @@ public:
     static bool filter_is_1x1(const TensorBase *filter) { return filter && filter->shape.size() == 4 && filter->shape[0] == 1 && filter->shape[1] == 1; }
     bool is_dw3x3() const;       ///< depthwise, stride 1 or 2 (both axes), dilation 1, pads of at most 1
     void skip_pixel_grouping() { m_no_grouping = true; }
+    /// Pixels a pointwise int8 conv treats as one row (1 = none) for these channel counts and this many pixels per image.
+    static int choose_pixel_group(int cin, int cout, long long pixels);
+    /// Channel slices on either side: the int8 kernels that take a pixel stride (not the pixel-grouped pointwise form, the
+    /// banded 8/16-channel 3x3 kernel or the 3-channel first layer, which read or write runs of whole pixels).
+    bool strided_input_ok(int i, const std::vector<std::vector<int>> &input_shapes) const override { return i == 0 && strided_ok(input_shapes); }
+    bool strided_output_ok(int o, const std::vector<std::vector<int>> &input_shapes) const override { return o == 0 && strided_ok(input_shapes); }
     int stride() const { return m_strides[0]; }
     const std::vector<int> &pads() const { return m_pads; }
     friend class FusedBlock;
 
 protected:
     int fill_desc(ModelContext *context, void *desc);
+    bool strided_ok(const std::vector<std::vector<int>> &input_shapes) const;
     bool m_no_grouping = false;
     std::vector<int> m_dilations, m_strides;
     const int m_group;
@@ -126,8 +133,12 @@ public:
     esp_err_t prepare(ModelContext *context) override; ///< uploads an operand that is a parameter (e.g. a scalar factor)
     std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
+    /// Channel slices: operands of the output's shape (no broadcast), not Div.
+    bool strided_input_ok(int i, const std::vector<std::vector<int>> &input_shapes) const override { return i < 2 && same_shapes(input_shapes); }
+    bool strided_output_ok(int o, const std::vector<std::vector<int>> &input_shapes) const override { return o == 0 && same_shapes(input_shapes); }
 
 protected:
+    bool same_shapes(const std::vector<std::vector<int>> &input_shapes) const;
     int m_op;
 };
 class Add : public Elementwise {
@@ -202,6 +213,9 @@ public:
         return t;
     }
     int op() const { return m_op; }
+    /// Channel slices: every one-operand operator but PRelu (its slopes broadcast over the leading axes).
+    bool strided_input_ok(int i, const std::vector<std::vector<int>> &input_shapes) const override;
+    bool strided_output_ok(int o, const std::vector<std::vector<int>> &input_shapes) const override { return strided_input_ok(o, input_shapes); }
 
 protected:
     int m_op;
@@ -279,6 +293,10 @@ public:
     std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+    bool strided_output_ok(int o, const std::vector<std::vector<int>> &input_shapes) const override
+    {
+        return o == 0 && quant_type == QUANT_TYPE_SYMM_8BIT && !input_shapes.empty() && input_shapes[0].size() >= 3;
+    }
 
 protected:
     resize_mode_t m_resize_mode;
@@ -297,6 +315,9 @@ public:
     std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+    int get_axis() const { return axis; }
+    /// A part may be a channel slice when the parts move as 16-byte units in one launch (last axis, whole units).
+    bool strided_input_ok(int i, const std::vector<std::vector<int>> &input_shapes) const override;
 
 protected:
     int axis;
@@ -308,6 +329,8 @@ public:
     std::vector<std::vector<int>> get_output_shape(std::vector<std::vector<int>> &input_shapes) override;
     void forward(ModelContext *context, runtime_mode_t mode = RUNTIME_MODE_AUTO) override;
     static Module *deserialize(fbs::FbsModel *fbs_model, std::string node_name);
+    int get_axis() const { return m_axis; }
+    bool strided_output_ok(int o, const std::vector<std::vector<int>> &input_shapes) const override;
 
 protected:
     std::vector<int> m_split;

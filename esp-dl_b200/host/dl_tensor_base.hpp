@@ -66,6 +66,8 @@ public:
     void *data;             ///< host copy (may be null for arena intermediates)
     void *device;           ///< device copy (null until the tensor is placed / uploaded)
     bool device_owned;      ///< `device` was allocated by this object (parameters)
+    int row_stride = 0;     ///< device copy only: elements between consecutive rows of the last axis when this tensor
+                            ///< is a channel slice of a wider one (the arena planner's Concat / Split views); 0 = dense
     uint32_t caps;
 
     TensorBase(std::vector<int> shape, const void *element, int exponent = 0, dtype_t dtype = DATA_TYPE_FLOAT, bool deep = true,

@@ -140,6 +140,8 @@ void *espdl_model_stream(void *handle) { return ((Handle *)handle)->model->strea
 size_t espdl_model_arena_bytes(void *handle) { return ((Handle *)handle)->model->arena_bytes(); }
 
 int espdl_model_num_modules(void *handle) { return (int)((Handle *)handle)->model->num_modules(); }
+/// Tensors the planner placed as channel slices inside a Concat output / Split input (no copy).
+int espdl_model_num_slice_views(void *handle) { return ((Handle *)handle)->model->num_slice_views(); }
 
 /// Copies the named tensor (any graph tensor; meaningful for intermediates only when built without buffer reuse)
 /// to `dst`.  Returns the tensor's byte size, or a negative status.
@@ -152,7 +154,13 @@ long long espdl_model_read_tensor(void *handle, const char *name, void *dst, siz
     if (dst) {
         if (dst_bytes < t->get_bytes())
             return ESPDL_ERR_INVALID_ARG;
-        int st = espdl_b200_download(dst, t->device, t->get_bytes(), h->model->stream());
+        int st;
+        if (t->row_stride) { // a channel slice of a wider tensor: gather its rows
+            const size_t es = dtype_sizeof(t->dtype), row = (size_t)t->shape.back() * es;
+            st = espdl_b200_download_rows(dst, t->device, row, (size_t)t->row_stride * es, row ? t->get_bytes() / row : 0, h->model->stream());
+        } else {
+            st = espdl_b200_download(dst, t->device, t->get_bytes(), h->model->stream());
+        }
         if (!st)
             st = espdl_b200_stream_sync(h->model->stream());
         if (st)

@@ -34,6 +34,7 @@ def host_lib():
         L.espdl_model_arena_bytes.restype = C.c_size_t
         L.espdl_model_arena_bytes.argtypes = [C.c_void_p]
         L.espdl_model_num_modules.argtypes = [C.c_void_p]
+        L.espdl_model_num_slice_views.argtypes = [C.c_void_p]
         L.espdl_model_read_tensor.restype = C.c_longlong
         L.espdl_model_read_tensor.argtypes = [C.c_void_p, C.c_char_p, C.c_void_p, C.c_size_t]
         L.espdl_model_preprocess.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float),
@@ -153,6 +154,10 @@ class Model:
     @property
     def num_modules(self):
         return self.lib.espdl_model_num_modules(self.h)
+
+    def num_slice_views(self):
+        """Tensors that live as channel slices inside a Concat output / Split input (ESPDL_B200_SLICE_VIEWS=0: none)."""
+        return self.lib.espdl_model_num_slice_views(self.h)
 
     def read_tensor(self, name, dtype, shape):
         out = np.empty(shape, dtype=dtype)

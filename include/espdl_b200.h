@@ -79,6 +79,9 @@ int espdl_b200_arena_alloc(size_t bytes, void **dptr);
 int espdl_b200_arena_free(void *dptr);
 int espdl_b200_upload(void *dst_dev, const void *src_host, size_t bytes, void *stream);
 int espdl_b200_download(void *dst_host, const void *src_dev, size_t bytes, void *stream);
+/* `rows` rows of `row_bytes`, `src_stride_bytes` apart on the device, into a dense host buffer (a tensor that is a
+ * channel slice of a wider one). */
+int espdl_b200_download_rows(void *dst_host, const void *src_dev, size_t row_bytes, size_t src_stride_bytes, size_t rows, void *stream);
 int espdl_b200_memset(void *dst_dev, int value, size_t bytes, void *stream);
 int espdl_b200_stream_sync(void *stream);
 /* Pinned host staging memory (for the end-to-end path with host buffers). */
@@ -251,6 +254,9 @@ typedef struct espdl_eltwise_desc {
                                  >> lut_shift, rounded to nearest (ties up, or to even with ROUND_HALF_EVEN), esp-dl/dl/base/
                                  dl_base_lut.cpp:50-107; 0 = a full 65536-entry table                             */
     const void *table;        /* POW, int8: int8[256][256], entry [(uint8)a ^ 0x80][(uint8)b ^ 0x80]; else NULL */
+    int64_t in0_row_stride;   /* elements between consecutive rows of the innermost axis (a channel slice of a wider     */
+    int64_t in1_row_stride;   /* tensor); 0 = dense.  Only for a tensor whose innermost extent equals the output's;     */
+    int64_t out_row_stride;   /* not with DIV.  Rows and strides that are multiples of 16 keep the 16-byte kernels.     */
 } espdl_eltwise_desc;
 
 int espdl_b200_eltwise(const espdl_eltwise_desc *desc, void *stream);
@@ -323,6 +329,9 @@ typedef struct espdl_parts_desc {
     int32_t n_parts; /* 1..8 */
     int32_t split;
     int64_t rows;
+    int64_t part_stride[8]; /* bytes between consecutive rows of part i (a multiple of 16); 0 = dense (part_bytes[i]) */
+    int32_t skip[8];        /* non-zero: part i is already where it belongs (it lives inside the wide tensor): its
+                               columns are left alone and parts[i] is not read                                       */
 } espdl_parts_desc;
 
 int espdl_b200_concat_split(const espdl_parts_desc *desc, void *stream);

@@ -493,3 +493,26 @@ def test_lut_folding_pass(tmp_path, monkeypatch):
     m.close()
     assert plain.count("Swish") >= 50 and folded.count("Swish") <= plain.count("Swish") - 45, (plain.count("Swish"), folded.count("Swish"))
     assert len(folded) == len(plain) - (plain.count("Swish") - folded.count("Swish"))
+
+
+def test_concat_and_split_as_channel_slices(tmp_path, monkeypatch):
+    """The planner places Concat inputs inside the Concat's output and makes Split outputs windows into the Split's input
+    wherever the producers / readers take a row stride: fewer bytes move, every tensor still equals the oracle's, and the
+    outputs equal those of the plan with the pass switched off."""
+    g = zoo.yolo11n_style(seed=6, input_hw=96)
+    m, want = run_and_compare(tmp_path, g, batch=2, seed=64, check_intermediates=True)
+    assert m.num_slice_views() >= 8, m.num_slice_views()
+    m.close()
+    m, _ = run_and_compare(tmp_path, g, batch=2, seed=64, check_intermediates=False)   # planned arena + CUDA graph
+    views = m.num_slice_views()
+    first = {o.name: np.array(o.array, copy=True) for o in m.outputs}
+    m.run()
+    for o in m.outputs:
+        np.testing.assert_array_equal(o.array, first[o.name])
+    m.close()
+    monkeypatch.setenv("ESPDL_B200_SLICE_VIEWS", "0")
+    m, _ = run_and_compare(tmp_path, g, batch=2, seed=64, check_intermediates=False)
+    assert m.num_slice_views() == 0 and views >= 8
+    for o in m.outputs:
+        np.testing.assert_array_equal(o.array, first[o.name])
+    m.close()

@@ -395,3 +395,105 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_works(monk
         assert dev.lib.espdl_b200_conv2d(C.byref(d), None) == abi.OK
         got = dev.download(ptrs["output"], case["out"])
     np.testing.assert_array_equal(got, want)
+
+
+# Channel slices: rows of the innermost axis that sit `stride` elements apart inside wider tensors (what the model's
+# planner makes of Concat inputs and Split outputs).  The oracle computes the dense case; the device sees slices.
+SLICED = [
+    (abi.ELT_ADD, abi.DTYPE_INT8, 32, (96, 64, 48), {}),                    # 16-byte kernels, all three strided
+    (abi.ELT_REQUANTIZE, abi.DTYPE_INT8, 16, (48, 0, 48), dict(e0=-5, eo=-4)),
+    (abi.ELT_REQUANTIZE, abi.DTYPE_INT8, 64, (0, 0, 192), dict(e0=-4, eo=-6)),
+    (abi.ELT_LUT, abi.DTYPE_INT8, 48, (64, 0, 0), {}),
+    (abi.ELT_MUL, abi.DTYPE_INT8, 16, (32, 48, 0), {}),
+    (abi.ELT_ADD, abi.DTYPE_INT8, 24, (40, 24, 56), {}),                    # rows that are no 16-byte units: the scalar kernel
+    (abi.ELT_ADD, abi.DTYPE_INT16, 16, (48, 32, 16), {}),
+    (abi.ELT_MAX, abi.DTYPE_INT8, 32, (0, 64, 64), {}),
+]
+
+
+@pytest.mark.parametrize("op,dtype,c,strides,kw", SLICED)
+def test_eltwise_on_channel_slices(op, dtype, c, strides, kw):
+    shape = (3, 5, 7, c)
+    rows = 3 * 5 * 7
+    case = cases.eltwise_case(op, seed=41, dtype=dtype, out_shape=shape, **kw)
+    want = case["out"].copy()
+    assert checkers.oracle().oracle_eltwise(cases.eltwise_desc(dict(case, out=want))) == 0
+    rng = np.random.default_rng(8)
+    es = case["out"].dtype.itemsize
+
+    def widen(arr, stride, lead):
+        """The dense rows of `arr` placed `lead` elements into rows of `stride` elements; the rest is random filler."""
+        if not stride:
+            return np.ascontiguousarray(arr), 0
+        wide = rng.integers(-100, 100, size=(rows, stride)).astype(arr.dtype)
+        wide[:, lead:lead + c] = arr.reshape(rows, c)
+        return wide, lead
+
+    two = case["b"] is not None and case["b"].shape == case["a"].shape
+    wa, la = widen(case["a"], strides[0], 16 if strides[0] >= c + 16 else 0)
+    wb, lb = widen(case["b"], strides[1], 0) if two else (case["b"], 0)
+    wo, lo = widen(case["out"], strides[2], 16 if strides[2] >= c + 16 else 0)
+    before = wo.copy()
+    with gpu_util.DeviceBuffers() as dev:
+        pa, pb, po = dev.upload(wa), dev.upload(wb), dev.upload(wo)
+        d = cases.eltwise_desc(case, dict(input0=pa + la * es, input1=(pb + lb * es) if pb else None, output=po + lo * es))
+        d.in0_row_stride, d.in1_row_stride, d.out_row_stride = strides[0], strides[1] if two else 0, strides[2]
+        d.ndim = 2
+        for name in ("out_shape", "in0_shape", "in1_shape"):
+            getattr(d, name)[0], getattr(d, name)[1] = rows, c
+        if not two:
+            d.in1_shape[0] = d.in1_shape[1] = 1
+        abi.check(dev.lib.espdl_b200_eltwise(C.byref(d), None), "eltwise")
+        got = dev.download(po, wo)
+    if strides[2]:
+        np.testing.assert_array_equal(got[:, lo:lo + c], want.reshape(rows, c))
+        before[:, lo:lo + c] = want.reshape(rows, c)
+        np.testing.assert_array_equal(got, before)          # nothing outside the slice was written
+    else:
+        np.testing.assert_array_equal(got, want)
+    assert want.astype(np.float32).std() > 0
+
+
+def test_eltwise_rejects_bad_row_strides():
+    case = cases.eltwise_case(abi.ELT_ADD, seed=1, out_shape=(4, 16))
+    with gpu_util.DeviceBuffers() as dev:
+        ptrs = dict(input0=dev.upload(case["a"]), input1=dev.upload(case["b"]), output=dev.upload(case["out"]))
+        d = cases.eltwise_desc(case, ptrs)
+        d.out_row_stride = 8                                 # shorter than a row
+        assert dev.lib.espdl_b200_eltwise(C.byref(d), None) == abi.ERR_INVALID_ARG
+        d = cases.eltwise_desc(dict(case, op=abi.ELT_DIV), ptrs)
+        d.in0_row_stride = 32
+        assert dev.lib.espdl_b200_eltwise(C.byref(d), None) == abi.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("split", [0, 1])
+def test_concat_split_with_slices_and_parts_in_place(split):
+    """Parts whose rows sit a stride apart, and a part that already lives inside the wide tensor (left alone)."""
+    rng = np.random.default_rng(12)
+    rows, widths = 37, [32, 16, 48]
+    wide = rng.integers(-128, 128, size=(rows, sum(widths)), dtype=np.int8)
+    holder = rng.integers(-128, 128, size=(rows, 80), dtype=np.int8)      # part 1 lives at columns 32..48 of 80-byte rows
+    dense2 = rng.integers(-128, 128, size=(rows, widths[2]), dtype=np.int8)
+    with gpu_util.DeviceBuffers() as dev:
+        pw, ph, p2 = dev.upload(wide), dev.upload(holder), dev.upload(dense2)
+        d = abi.PartsDesc()
+        d.wide, d.n_parts, d.split, d.rows = pw, 3, split, rows
+        for i, w in enumerate(widths):
+            d.part_bytes[i] = w
+        d.parts[0], d.skip[0] = None, 1
+        d.parts[1], d.part_stride[1] = ph + 32, 80
+        d.parts[2] = p2
+        abi.check(dev.lib.espdl_b200_concat_split(C.byref(d), None), "concat_split")
+        got_w, got_h, got_2 = dev.download(pw, wide), dev.download(ph, holder), dev.download(p2, dense2)
+    if split:
+        np.testing.assert_array_equal(got_w, wide)
+        want_h = holder.copy()
+        want_h[:, 32:48] = wide[:, 32:48]
+        np.testing.assert_array_equal(got_h, want_h)
+        np.testing.assert_array_equal(got_2, wide[:, 48:])
+    else:
+        want_w = wide.copy()
+        want_w[:, 32:48] = holder[:, 32:48]
+        want_w[:, 48:] = dense2
+        np.testing.assert_array_equal(got_w, want_w)
+        np.testing.assert_array_equal(got_h, holder)
