@@ -303,6 +303,20 @@ size_t espdl_plan_arena(int n, const int *first, const int *last, const size_t *
     return arena;
 }
 
+/// The same with channel slices: tensor i with row_stride[i] != 0 lives view_offset[i] bytes into the buffer of alias_of[i].
+size_t espdl_plan_arena_slices(int n, const int *first, const int *last, const size_t *bytes, const int *alias_of, const size_t *view_offset,
+                               const int *row_stride, size_t *offsets, int reuse)
+{
+    std::vector<TensorInfo> infos(n);
+    for (int i = 0; i < n; i++) {
+        infos[i].first = first[i], infos[i].last = last[i], infos[i].bytes = bytes[i], infos[i].alias_of = alias_of[i];
+        infos[i].view_offset = view_offset[i], infos[i].row_stride = row_stride[i];
+    }
+    const size_t arena = MemoryManagerGreedy::plan(infos, reuse != 0);
+    for (int i = 0; i < n; i++) offsets[i] = infos[i].offset;
+    return arena;
+}
+
 /// Per-module latency table as text: one "index<TAB>type<TAB>microseconds<TAB>name" line per module.
 const char *espdl_model_profile(void *handle)
 {

@@ -181,6 +181,30 @@ def test_arena_planner_aliases_share_the_root_buffer(host):
     assert arena == 1024 + 512
 
 
+def test_arena_planner_places_channel_slices_inside_their_wide_tensor(host):
+    """Three slices of a Concat output (tensor 0, produced at step 6) are written at steps 1, 3 and 5: the wide buffer is
+    alive from step 1 on, the slices sit at their channel offsets inside it and add nothing to its size, and a tensor that
+    lives meanwhile does not share its bytes; a tensor that is dead before step 1 may."""
+    host.espdl_plan_arena_slices.restype = C.c_size_t
+    host.espdl_plan_arena_slices.argtypes = [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_size_t), C.POINTER(C.c_int),
+                                             C.POINTER(C.c_size_t), C.POINTER(C.c_int), C.POINTER(C.c_size_t), C.c_int]
+    first = [6, 1, 3, 5, 2, -1, 0]
+    last = [8, 6, 6, 6, 4, 0, 0]
+    nbytes = [4800, 1600, 1600, 1600, 7000, 3000, 512]
+    alias = [-1, 0, 0, 0, -1, -1, -1]
+    view = [0, 0, 16, 32, 0, 0, 0]
+    stride = [0, 48, 48, 48, 0, 0, 0]
+    n = len(first)
+    off = (C.c_size_t * n)()
+    arena = host.espdl_plan_arena_slices(n, (C.c_int * n)(*first), (C.c_int * n)(*last), (C.c_size_t * n)(*nbytes), (C.c_int * n)(*alias),
+                                         (C.c_size_t * n)(*view), (C.c_int * n)(*stride), off, 1)
+    off = list(off)
+    assert [off[1] - off[0], off[2] - off[0], off[3] - off[0]] == [0, 16, 32]
+    wide = (off[0], off[0] + 4800)
+    assert off[4] >= wide[1] or off[4] + 7000 <= wide[0]           # alive during steps 2..4, while the slices are written
+    assert off[5] + 3000 <= arena and arena <= 4864 + 7168 + 3072 + 512
+
+
 def test_python_writer_round_trip():
     g = zoo.inverted_residual_block(seed=4, hw=16)
     m = espdl_file.read(g.serialize())
