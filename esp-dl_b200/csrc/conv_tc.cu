@@ -322,7 +322,8 @@ struct PatchParams {
     int stages, acc_stages, tmem_cols;
     int patch_bytes, patch_tx;    // shared-memory stride of a stage (with slack for the last taps' overrun), bytes one box delivers
     int out_pw, out_mask;
-    int stack, ncols;             // the KW taps of a filter row side by side along N (ncols = KW * block_n accumulator columns per tile)
+    int stack, ncols;             // the first `stack` taps of a filter row side by side along N (0: none); ncols = accumulator columns per tile
+    int staged;                   // the tile leaves through shared memory and TMA stores (else rows go out of registers)
     void *out;
     long long ops;                // output pixel stride in bytes
     EpiConfig epi;
@@ -408,7 +409,7 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     uint8_t *filt_s = smem;                                    // taps x [block_n][swz]
     uint8_t *patch_s = smem + (size_t)taps * b_tap;            // stages x patch
     uint8_t *out_stage = patch_s + (size_t)p.stages * p.patch_bytes;
-    const int out_tile_bytes = (128 * p.out_pw + 1023) & ~1023;
+    const int out_tile_bytes = p.staged ? (128 * p.out_pw + 1023) & ~1023 : 0;
     uint8_t *aux = out_stage + 4 * (size_t)out_tile_bytes;
     FastParam *fast_s = (FastParam *)aux;
     uint64_t *bars = (uint64_t *)(aux + sizeof(FastParam) * (size_t)p.block_n);
@@ -478,10 +479,10 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = mbar_wait(smem_u32(filt_bar), 0);
-            const uint32_t idesc = idesc_i8(1, 1, 128, p.ncols);
+            const uint32_t idesc = idesc_i8(1, 1, 128, p.ncols), idesc_one = idesc_i8(1, 1, 128, p.block_n);
             const int ksteps = p.swz / 32;
             const uint32_t f0 = smem_u32(filt_s);
-            const int kx_count = p.stack ? 1 : p.kw;   // stacked: one MMA covers the KW taps of a filter row
+            const int wide = p.stack ? p.stack : 1;    // taps the first MMA of a filter row covers; the others follow one by one
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!mbar_wait(smem_u32(&tempty_bar[acc]), acc_phase ^ 1) || !mbar_wait(smem_u32(&full_bar[stage]), phase)) {
                     ok = false;
@@ -492,10 +493,12 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint32_t st = smem_u32(patch_s + (size_t)stage * p.patch_bytes);
                 int first = 1;
                 for (int ky = 0; ky < p.kh; ky++)
-                    for (int kx = 0; kx < kx_count; kx++) {
+                    for (int kx = 0; kx < p.kw; kx += (kx == 0 ? wide : 1)) {
+                        // a single tap behind the stacked ones adds to column block 0 from rows kx further on
                         const uint64_t da = smem_desc_swizzled(st + (uint32_t)((ky * p.PW + kx) * p.swz), p.swz);
                         const uint64_t db = smem_desc_swizzled(f0 + (uint32_t)((ky * p.kw + kx) * b_tap), p.swz);
-                        for (int k = 0; k < ksteps; k++, first = 0) mma_i8(d0, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, !first);
+                        const uint32_t id = kx == 0 ? idesc : idesc_one;
+                        for (int k = 0; k < ksteps; k++, first = 0) mma_i8(d0, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), id, !first);
                     }
                 commit(smem_u32(&empty_bar[stage]));
                 commit(smem_u32(&tfull_bar[acc]));
@@ -554,7 +557,7 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const int out_align = (int)(amix & (~amix + 1));
                 for (int c0 = part * p.out_pw; c0 < (part + 1) * p.out_pw; c0 += 16) {
                     int32_t v[16];
-                    ld16_sum(t0 + c0, p.stack ? p.kw : 1, p.block_n, v);
+                    ld16_sum(t0 + c0, p.stack ? p.stack : 1, p.block_n, v);
                     uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                     requant16_general(v, p.epi, c0, p.cout, pk);
                     const int count = min(16, p.cout - c0);
@@ -567,15 +570,41 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                     mbar_arrive(smem_u32(&tempty_bar[acc]));
                 continue;
             }
+            const int col0 = part * p.out_pw;
+            const uint32_t fpp = fp_base + (uint32_t)col0 * 8u;
+            if (!p.staged) {
+                // no room for staging tiles next to a large resident filter: 16 bytes of the thread's own row per store
+                const int r = row_in_tile / p.PW, xx = row_in_tile % p.PW;
+                const int oy = yt * p.RT + r, ox = xt * p.PV + xx;
+                const bool row_ok = xx < p.PV && oy < p.oh && ox < p.ow;
+                int8_t *orow = (int8_t *)p.out + (((long long)img * p.oh + oy) * p.ow + ox) * p.ops + col0;
+                const uint32_t tbl = p.epi.lut ? smem_u32(lut_s) : 0u;
+                for (int c = 0; c < p.out_pw; c += 16) {
+                    int32_t v[16];
+                    uint32_t pk[4];
+                    ld16_sum(t0 + col0 + c, p.stack ? p.stack : 1, p.block_n, v);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        pk[q] = requant4_floor(v + 4 * q, fpp + (uint32_t)(c + 4 * q) * 8u, floor_q);
+                        if (tbl)
+                            pk[q] = lut4(pk[q], tbl);
+                    }
+                    if (row_ok)
+                        *(uint4 *)(orow + c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+                fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(smem_u32(&tempty_bar[acc]));
+                continue;
+            }
             const bool leader = (ew & 3) == 0 && lane == 0;
             const uint32_t buf = smem_u32(out_stage + (size_t)group * out_tile_bytes);
             if (leader)
                 bulk_wait_read_all();
             named_bar(2 + group, 128);
-            const int col0 = part * p.out_pw;
-            const uint32_t fpp = fp_base + (uint32_t)col0 * 8u;
             if (p.stack)
-                epilogue_stage_stacked(t0 + col0, p.kw, p.block_n, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q,
+                epilogue_stage_stacked(t0 + col0, p.stack, p.block_n, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q,
                                        p.epi.lut ? smem_u32(lut_s) : 0u);
             else if (p.epi.lut)
                 epilogue_stage_lut(t0 + col0, fpp, buf, row_in_tile, p.out_pw, (uint32_t)p.out_mask, floor_q, smem_u32(lut_s));
@@ -689,6 +718,10 @@ bool conv_plan(const espdl_conv_desc &d, ConvTcParams &p)
     return true;
 }
 
+// The one-patch kernel may use all of an SM's shared memory (227 KB per CTA): a resident 3x3 filter over 128 -> 128
+// channels is 144 KB, and what is left decides between two and three patches in flight.
+constexpr size_t PATCH_SMEM_BUDGET = 226 * 1024;
+
 size_t patch_aux_bytes(const PatchParams &p) { return sizeof(FastParam) * (size_t)p.block_n + (2 * CV_MAX_STAGES + 2 * CV_MAX_ACC + 1) * 8 + 32 + 256; }
 
 // The one-patch form: stride 1, dilation 1, Cin = 64 or 128 (one swizzle row per pixel), Cout <= 256 in one tile, the
@@ -707,13 +740,15 @@ bool patch_plan(const espdl_conv_desc &d, PatchParams &p)
     p.n = d.n, p.oh = d.out_h, p.ow = d.out_w, p.cin = d.in_c, p.cout = d.out_c;
     p.kh = d.kh, p.kw = d.kw, p.pt = d.pad_top, p.pl = d.pad_left;
     p.swz = d.in_c, p.block_n = d.out_c;
-    // An MMA of 128 rows costs the tensor pipe about the same time for any N up to 256, so the KW taps of a filter row
-    // go side by side along N whenever KW * Cout fits and the epilogue's channel split stays a multiple of 16.
+    // An MMA of 128 rows costs the tensor pipe about the same time for any N up to 256, so as many taps of a filter row
+    // as fit into 256 columns (at most four) go side by side along N, if the epilogue's channel split stays a multiple of 16.
+    // Filter rows wider than that keep their first taps stacked and issue the others one by one into column block 0.
     p.stack = 0, p.ncols = p.block_n;
-    if (d.kw >= 2 && d.kw <= 4 && d.kw * p.block_n <= 256 && !getenv("ESPDL_B200_NO_TAP_STACK")) {
-        const int acc = 4 * d.kw * p.block_n <= 512 ? 4 : 2;
+    const int fit = std::min(std::min(d.kw, 256 / p.block_n), 4);
+    if (fit >= 2 && !getenv("ESPDL_B200_NO_TAP_STACK")) {
+        const int acc = 4 * fit * p.block_n <= 512 ? 4 : 2;
         if (p.block_n % (16 * (4 / acc)) == 0)
-            p.stack = 1, p.ncols = d.kw * p.block_n;
+            p.stack = fit, p.ncols = fit * p.block_n;
     }
     p.acc_stages = 4 * p.ncols <= 512 ? 4 : 2;
     int pow2 = 32;
@@ -746,8 +781,13 @@ bool patch_plan(const espdl_conv_desc &d, PatchParams &p)
     p.patch_bytes = ((rows + d.kw) * p.swz + 1023) & ~1023; // the last taps of the last (dropped) positions read a few rows further
     const size_t filt = (size_t)d.kh * d.kw * p.block_n * p.swz;
     const size_t out_bytes = 4 * (size_t)((128 * p.out_pw + 1023) & ~1023);
-    const long long room = (long long)CV_SMEM_BUDGET - (long long)filt - (long long)out_bytes - (long long)patch_aux_bytes(p) - 1024;
-    const long long stages = room / p.patch_bytes;
+    const long long room = (long long)PATCH_SMEM_BUDGET - (long long)filt - (long long)patch_aux_bytes(p) - 1024;
+    p.staged = 1;
+    long long stages = (room - (long long)out_bytes) / p.patch_bytes;
+    if (stages < 2) { // a filter that leaves no room for the staging tiles: rows go out of registers (long reductions, the epilogue is a small part)
+        p.staged = 0;
+        stages = room / p.patch_bytes;
+    }
     if (stages < 2)
         return false;
     p.stages = stages > 4 ? 4 : (int)stages;
@@ -796,13 +836,13 @@ int launch_patch(const espdl_conv_desc &d, PatchParams &p, cudaStream_t s)
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return set_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled(conv patch output)");
     }
-    size_t smem = 1024 + (size_t)d.kh * d.kw * p.block_n * p.swz + (size_t)p.stages * p.patch_bytes + 4 * (size_t)((128 * p.out_pw + 1023) & ~1023) +
-        patch_aux_bytes(p);
+    size_t smem = 1024 + (size_t)d.kh * d.kw * p.block_n * p.swz + (size_t)p.stages * p.patch_bytes +
+        (p.staged ? 4 * (size_t)((128 * p.out_pw + 1023) & ~1023) : 0) + patch_aux_bytes(p);
     if (smem < 120 * 1024)
         smem = 120 * 1024;
     static std::once_flag attr_once;
     static cudaError_t attr_err = cudaSuccess;
-    std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute(conv_patch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(CV_SMEM_BUDGET + 2048)); });
+    std::call_once(attr_once, [] { attr_err = cudaFuncSetAttribute(conv_patch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(PATCH_SMEM_BUDGET + 1024)); });
     if (attr_err != cudaSuccess)
         return set_cuda_error(attr_err, "cudaFuncSetAttribute(conv_patch_kernel)");
     const long long total = (long long)p.n * p.ytiles * p.xtiles;

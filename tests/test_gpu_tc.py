@@ -282,6 +282,10 @@ PATCH = [
     dict(n=3, h=21, w=35, cin=32, cout=32, kh=2, kw=2, pad=(0, 1, 0, 1)),     # two taps side by side
     dict(n=2, h=13, w=31, cin=32, cout=96),                                   # 32-byte rows, taps one by one
     dict(n=2, h=11, w=45, cin=64, cout=48, kh=3, kw=4, pad=(1, 1, 1, 2)),     # four taps side by side
+    dict(n=2, h=40, w=40, cin=128, cout=128),                                 # two taps in an N = 256 MMA, the third alone; 144 KB filter, rows out of registers
+    dict(n=2, h=17, w=33, cin=64, cout=96),                                   # two taps side by side (192 columns), 48-column epilogue parts
+    dict(n=1, h=20, w=31, cin=64, cout=64, kh=5, kw=5, pad=(2, 2, 2, 2)),     # four of five taps side by side
+    dict(n=2, h=9, w=61, cin=32, cout=128),                                   # 32-byte rows, two taps side by side
 ]
 
 
