@@ -270,11 +270,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ld16(t0 + c0, v);
                     ld_wait16(v);
                     uint32_t pk[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-                    if (fast && !p.epi.lut) {
+                    if (fast) {
                         if (p.epi.relu)
                             requant16_fast<true>(v, fast_s + n0 + c0, pk);
                         else
                             requant16_fast<false>(v, fast_s + n0 + c0, pk);
+                        if (p.epi.lut) { // a fused table on rows that leave unstaged: same lookups on the packed words
+#pragma unroll
+                            for (int q = 0; q < 4; q++) pk[q] = lut4(pk[q], smem_u32(lut_s));
+                        }
                     } else {
                         requant16_general(v, p.epi, n0 + c0, p.cout, pk);
                     }

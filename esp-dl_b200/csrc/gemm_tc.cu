@@ -105,14 +105,14 @@ constexpr int TILE_RING = 32; // tile numbers on their way from the producer to 
 // 16-byte groups, unaligned rows, channels outside the fast form): rows are stored directly from registers.  Out of
 // line on purpose: the staged path in the kernel then carries none of this code's registers.
 __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastParam *fast_s, uint32_t fp_base, uint32_t t0, long long m, int n0,
-                                                  bool row_ok, bool fast, int parts, int part, bool allow_wide = true)
+                                                  bool row_ok, bool fast, int parts, int part, bool allow_wide = true, uint32_t tbl = 0u)
 {
     int8_t *orow = (int8_t *)p.out + m * p.ops + n0;
     const bool vec_ok = (p.ops % 16 == 0) && ((((uintptr_t)p.out) + n0) % 16 == 0);
     // what every row start (and every 16-column step from it) is aligned to
     const uintptr_t amix = (uintptr_t)p.ops | (((uintptr_t)p.out) + (uintptr_t)n0) | 16u;
     const int out_align = (int)(amix & (~amix + 1));
-    if (fast && vec_ok && p.N % 16 == 0 && !p.res && p.n_peer == 0) {
+    if (fast && !tbl && vec_ok && p.N % 16 == 0 && !p.res && p.n_peer == 0) {
         // whole 16-column groups, aligned rows, one-add-one-shift constants
         const bool wide = allow_wide && (p.ops % 32 == 0) && ((((uintptr_t)p.out) + n0) % 32 == 0);
         const uint32_t fp = fp_base + (uint32_t)n0 * 8u;
@@ -144,6 +144,10 @@ __device__ __noinline__ void epilogue_direct_tile(const TcParams &p, const FastP
                 requant16_fast<false>(v, fast_s + n0 + c0, pk);
                 if (two)
                     requant16_fast<false>(v + 16, fast_s + n0 + c0 + 16, pk + 4);
+            }
+            if (tbl) { // a fused table on rows that leave unstaged (`tbl`: its shared-memory copy): same lookups on the packed words
+#pragma unroll
+                for (int q = 0; q < 8; q++) pk[q] = lut4(pk[q], tbl);
             }
         } else {
             requant16_general(v, p.epi, n0 + c0, p.N, pk);
@@ -503,7 +507,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     }
                     continue;
                 }
-                epilogue_direct_tile(p, fast_s, fp_base, t0, m, n0, row_ok, fast && !p.epi.lut, parts, part);
+                epilogue_direct_tile(p, fast_s, fp_base, t0, m, n0, row_ok, fast, parts, part, true, p.epi.lut ? smem_u32(lut_s) : 0u);
             } else {
                 int chunk = 0;
                 for (int c0 = 0; c0 < p.block_n; c0 += 16, chunk++) {

@@ -304,3 +304,28 @@ def test_conv_one_patch_per_tile(kw, act, per_channel, lut, round_mode, monkeypa
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
     monkeypatch.setenv("ESPDL_B200_NO_CONV_PATCH", "1")   # the tap-per-box kernel gives the same bytes
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+
+
+@pytest.mark.parametrize("m,k,n,act,direct", [(1000, 512, 256, abi.ACT_LINEAR, False), (700, 384, 256, abi.ACT_RELU, False), (300, 64, 48, abi.ACT_LINEAR, True),
+                                              (260, 96, 200, abi.ACT_RELU, True)])
+def test_fused_table_on_rows_that_leave_unstaged(m, k, n, act, direct, monkeypatch):
+    """Long reductions with 256 columns keep their shared memory for load stages, so their rows leave out of registers;
+    a fused table is then applied to the packed words of the one-add-one-shift form (ragged N in the last case)."""
+    if direct:
+        monkeypatch.setenv("ESPDL_B200_DIRECT_STORES", "1")
+    case = cases.gemm_case(seed=m + k, m=m, k=k, n_out=n, per_channel=True, act=act, lut=True, e_in=-7, e_out=-5 + (k > 256), e_w=(-9, -7))
+    want = gpu_util.run_conv_oracle(case)
+    assert want.std() > 5
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+
+
+@pytest.mark.parametrize("direct", [False, True])
+def test_strided_conv_with_fused_table_and_256_columns(direct, monkeypatch):
+    """3x3 stride 2 over 128 -> 256 channels with a fused table (the detector's downsampling conv): conv_tc_kernel without staging tiles."""
+    if direct:
+        monkeypatch.setenv("ESPDL_B200_DIRECT_STORES", "1")
+    case = cases.conv_case(seed=15, n=2, h=20, w=22, cin=128, cout=256, kh=3, kw=3, stride=2, per_channel=True, lut=True, act=abi.ACT_LINEAR,
+                           e_in=-7, e_out=-5, e_w=(-9, -7))
+    want = gpu_util.run_conv_oracle(case)
+    assert want.std() > 5
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
