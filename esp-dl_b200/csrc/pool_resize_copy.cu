@@ -84,6 +84,95 @@ __global__ void __launch_bounds__(256) maxpool_s8_vec16_kernel(PoolParams p)
     }
 }
 
+// Stride-1 K x K max pool (the detector's 5x5 pools), int8, C % 16 == 0: a thread owns 16 channels of one output COLUMN and
+// walks down the image.  Per input row it takes the maximum over the K columns of the window once (K loads), keeps
+// the last K of these row maxima in registers and emits one output per row as their maximum: K loads and 2(K - 1)
+// maxima per output instead of K*K of each.  Bytes are compared as the high bytes of 16-bit lanes (even and odd
+// bytes of a word apart), where the packed 16-bit maximum is one instruction.  The row loop is unrolled by K so that
+// the ring of row maxima is indexed statically.  Taps outside the image are left out, as in pool_kernel.
+struct Lanes16 {
+    uint32_t e[4], o[4]; // even / odd bytes of four words, each in the high byte of a 16-bit lane
+};
+
+__device__ __forceinline__ void split_bytes(const uint4 v, Lanes16 &l)
+{
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) l.e[i] = (w[i] << 8) & 0xff00ff00u, l.o[i] = w[i] & 0xff00ff00u;
+}
+
+// max.s16x2 is one instruction on this architecture (the __vmaxs2 intrinsic expands to several)
+__device__ __forceinline__ uint32_t max_s16x2(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("max.s16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+__device__ __forceinline__ void max_lanes(Lanes16 &a, const Lanes16 &b)
+{
+#pragma unroll
+    for (int i = 0; i < 4; i++) a.e[i] = max_s16x2(a.e[i], b.e[i]), a.o[i] = max_s16x2(a.o[i], b.o[i]);
+}
+
+template <int K>
+__global__ void __launch_bounds__(256) maxpool_s8_walk_kernel(PoolParams p, int segments)
+{
+    const int chunks = p.c >> 4;
+    const int seg_rows = (p.oh + segments - 1) / segments; // a column is cut into `segments` runs of output rows when there are few columns
+    const long long total = (long long)p.n * segments * p.ow * chunks;
+    for (long long item = blockIdx.x * (long long)blockDim.x + threadIdx.x; item < total; item += (long long)gridDim.x * blockDim.x) {
+        const int ch = (int)(item % chunks) * 16;
+        const int ox = (int)((item / chunks) % p.ow);
+        const int seg = (int)((item / ((long long)chunks * p.ow)) % segments);
+        const long long n = item / ((long long)chunks * p.ow * segments);
+        const int oy0 = seg * seg_rows, oy1 = min(p.oh, oy0 + seg_rows);
+        const int8_t *in = (const int8_t *)p.in + n * p.ih * (long long)p.iw * p.c + ch;
+        int8_t *out = (int8_t *)p.out + (n * p.oh * (long long)p.ow + ox) * p.c + ch;
+        // taps outside the image count as -128, the identity of the maximum (every window holds at least one real tap)
+        Lanes16 ring[K];
+#pragma unroll
+        for (int j = 0; j < K; j++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) ring[j].e[i] = ring[j].o[i] = 0x80008000u;
+        const int last_iy = oy1 - 1 + K - 1 - p.pt; // the input row (possibly below the image) that completes the run's last output row
+        const int first_iy = max(oy0 - p.pt, 0);
+#pragma unroll 1
+        for (int base = first_iy / K * K; base <= last_iy; base += K) {
+#pragma unroll
+            for (int j = 0; j < K; j++) {
+                const int iy = base + j;
+                const bool row_in = iy >= first_iy && iy < p.ih;
+                const int8_t *row = in + (long long)min(iy, p.ih - 1) * p.iw * p.c;
+                uint4 v[K]; // all K loads of the row are issued before the first is used
+#pragma unroll
+                for (int kx = 0; kx < K; kx++) {
+                    const int x = ox - p.pl + kx;
+                    v[kx] = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+                    if (row_in && x >= 0 && x < p.iw)
+                        v[kx] = __ldg((const uint4 *)(row + (long long)x * p.c));
+                }
+                split_bytes(v[0], ring[j]);
+#pragma unroll
+                for (int kx = 1; kx < K; kx++) {
+                    Lanes16 t;
+                    split_bytes(v[kx], t);
+                    max_lanes(ring[j], t);
+                }
+                const int oy = iy - (K - 1) + p.pt; // its window is input rows iy - K + 1 .. iy
+                if (oy >= oy0 && oy < oy1) {
+                    Lanes16 m = ring[0];
+#pragma unroll
+                    for (int d = 1; d < K; d++) max_lanes(m, ring[d]);
+                    uint4 o;
+                    o.x = (m.e[0] >> 8) | m.o[0], o.y = (m.e[1] >> 8) | m.o[1], o.z = (m.e[2] >> 8) | m.o[2], o.w = (m.e[3] >> 8) | m.o[3];
+                    *(uint4 *)(out + (long long)oy * p.ow * p.c) = o;
+                }
+            }
+        }
+    }
+}
+
 // Global average pool, int8, C % 4 == 0: a thread owns four channels (one word of each pixel) of one image and sums
 // the whole plane; lanes are consecutive words, so every load of a warp is one contiguous run.  The four byte sums
 // come from dp4a against one-hot byte selectors.  Same arithmetic as pool_kernel (int32 sum, one fp32 multiply).
@@ -327,6 +416,21 @@ extern "C" int espdl_b200_pool(const espdl_pool_desc *d, void *stream)
         gap_s8_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p);
         count_launch();
         return check_launch("global average pool");
+    }
+    if (d->op == ESPDL_POOL_MAX && !p.is16 && p.c % 16 == 0 && ((uintptr_t)d->input % 16) == 0 && ((uintptr_t)d->output % 16) == 0 && p.sh == 1 &&
+        p.sw == 1 && p.kh == p.kw && (p.kh == 3 || p.kh == 5) && p.oh >= 4 * p.kh && !getenv("ESPDL_B200_NO_POOL_WALK")) {
+        // stride-1 windows on maps tall enough for the walk down a column to pay
+        const long long columns = (long long)p.n * p.ow * (p.c / 16);
+        int segments = 1; // enough threads to fill the SMs, runs of at least 2K rows
+        while (columns * segments < (long long)num_sms() * 2048 && p.oh / (segments * 2) >= 2 * p.kh) segments *= 2;
+        const long long items = columns * segments;
+        const unsigned grid = (unsigned)min((items + 255) / 256, (long long)num_sms() * 32);
+        if (p.kh == 3)
+            maxpool_s8_walk_kernel<3><<<grid, 256, 0, (cudaStream_t)stream>>>(p, segments);
+        else
+            maxpool_s8_walk_kernel<5><<<grid, 256, 0, (cudaStream_t)stream>>>(p, segments);
+        count_launch();
+        return check_launch("max pool walk");
     }
     if (d->op == ESPDL_POOL_MAX && !p.is16 && p.c % 16 == 0 && ((uintptr_t)d->input % 16) == 0 && ((uintptr_t)d->output % 16) == 0) {
         const long long items = p.total / 16;

@@ -245,6 +245,10 @@ def test_lut_all_codes():
     (abi.POOL_MAX, dict(kh=3, kw=3, stride=2, pad=(1, 1, 1, 1))),
     (abi.POOL_MAX, dict(h=20, w=20, c=128, kh=5, kw=5, stride=1, pad=(2, 2, 2, 2))),
     (abi.POOL_MAX, dict(kh=2, kw=2, stride=2, pad=(0, 0, 0, 0))),
+    (abi.POOL_MAX, dict(n=3, h=24, w=9, c=32, kh=5, kw=5, stride=1, pad=(0, 0, 0, 0))),     # the column walk, no padding
+    (abi.POOL_MAX, dict(n=2, h=43, w=11, c=16, kh=5, kw=5, stride=1, pad=(2, 1, 0, 3))),    # uneven pads, columns cut into runs of rows
+    (abi.POOL_MAX, dict(n=2, h=13, w=21, c=48, kh=3, kw=3, stride=1, pad=(1, 1, 1, 1))),
+    (abi.POOL_MAX, dict(n=1, h=80, w=5, c=16, kh=3, kw=3, stride=1, pad=(0, 2, 2, 0))),
     (abi.POOL_AVG, dict(kh=2, kw=2, stride=2, pad=(0, 0, 0, 0))),
     (abi.POOL_AVG, dict(kh=3, kw=3, stride=2, pad=(1, 1, 1, 1), e_out=-4)),
     (abi.POOL_GLOBAL_AVG, dict(h=7, w=7, c=40, e_in=-4, e_out=-5)),
