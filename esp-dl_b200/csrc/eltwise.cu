@@ -34,13 +34,15 @@ struct EltParams {
     // strides between rows of the output / the operands; 0 = dense.  Vector kernels: the same in 16-byte units.
     long long ro, ra, rb;
     int vpr; // 16-byte units per row (vector kernels, strided rows only; 0 = flat)
+    int vpr_shift; // log2(vpr) when it is a power of two, else -1
 };
 
 // Vector index -> unit offsets of the output and the two operands.
 __device__ __forceinline__ void vec_offsets(const EltParams &p, long long v, long long &io, long long &ia, long long &ib)
 {
     if (p.vpr) {
-        const long long row = v / p.vpr;
+        // no 64-bit division on the common widths (1, 2, 4, 8 units per row)
+        const long long row = p.vpr_shift >= 0 ? (v >> p.vpr_shift) : (v < 0x7fffffffll ? (long long)((unsigned)v / (unsigned)p.vpr) : v / p.vpr);
         const long long col = v - row * p.vpr;
         io = row * p.ro + col, ia = row * p.ra + col, ib = row * p.rb + col;
     } else {
@@ -341,6 +343,10 @@ extern "C" int espdl_b200_eltwise(const espdl_eltwise_desc *d, void *stream)
     const bool rows16 = !strided || (os[3] % 16 == 0 && rs0 % 16 == 0 && rs1 % 16 == 0 && rso % 16 == 0);
     if (strided && rows16) {
         p.vpr = os[3] / 16;
+        p.vpr_shift = -1;
+        for (int sft = 0; sft < 16; sft++)
+            if ((1 << sft) == p.vpr)
+                p.vpr_shift = sft;
         p.ra = (rs0 ? rs0 : os[3]) / 16, p.rb = (rs1 ? rs1 : os[3]) / 16;
     }
     p.a = d->input0, p.b = d->input1, p.out = d->output;

@@ -555,6 +555,9 @@ void Model::fold_residual_adds()
 int Model::alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::string, int> &info_index,
                                 const std::vector<std::vector<std::vector<int>>> &step_in_shapes, std::vector<bool> &is_root)
 {
+    // Slices start, end and stride on 32-byte boundaries: a 16-byte slice of a 48-byte row would be read and written as half
+    // sectors, which costs its elementwise producers more than the copy it saves (measured on the detector's first C3k2 block).
+    constexpr long long SLICE_UNIT = 32;
     const int steps = (int)m_execution_plan.size();
     std::vector<std::vector<std::pair<int, int>>> consumers(infos.size()); // (step, input position)
     for (int step = 0; step < steps; step++)
@@ -581,7 +584,7 @@ int Model::alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::st
             const int nd = (int)infos[out].shape.size();
             const int ax = cat->get_axis() < 0 ? cat->get_axis() + nd : cat->get_axis();
             const long long es = (long long)dtype_sizeof(infos[out].dtype);
-            if (nd < 2 || ax != nd - 1 || is_view[out] || infos[out].alias_of >= 0 || (infos[out].shape[ax] * es) % 16 != 0)
+            if (nd < 2 || ax != nd - 1 || is_view[out] || infos[out].alias_of >= 0 || (infos[out].shape[ax] * es) % SLICE_UNIT != 0)
                 continue;
             long long off = 0;
             for (size_t i = 0; i < m_module_inputs[step].size(); i++) {
@@ -595,7 +598,7 @@ int Model::alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::st
                 const int t = it->second;
                 TensorInfo &ti = infos[t];
                 if (ti.is_graph_io || ti.first < 0 || is_view[t] || is_root[t] || ti.alias_of >= 0 || ti.dtype != infos[out].dtype ||
-                    (at * es) % 16 != 0 || (ci * es) % 16 != 0 || (int)ti.shape.size() != nd)
+                    (at * es) % SLICE_UNIT != 0 || (ci * es) % SLICE_UNIT != 0 || (int)ti.shape.size() != nd)
                     continue;
                 if (std::count(m_module_inputs[step].begin(), m_module_inputs[step].end(), in_name) != 1)
                     continue;
@@ -615,7 +618,7 @@ int Model::alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::st
             const int nd = (int)infos[x].shape.size();
             const int ax = sp->get_axis() < 0 ? sp->get_axis() + nd : sp->get_axis();
             const long long es = (long long)dtype_sizeof(infos[x].dtype);
-            if (nd < 2 || ax != nd - 1 || is_view[x] || infos[x].alias_of >= 0 || (infos[x].shape[ax] * es) % 16 != 0)
+            if (nd < 2 || ax != nd - 1 || is_view[x] || infos[x].alias_of >= 0 || (infos[x].shape[ax] * es) % SLICE_UNIT != 0)
                 continue;
             long long off = 0;
             for (size_t o = 0; o < m_module_outputs[step].size(); o++) {
@@ -627,7 +630,7 @@ int Model::alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::st
                 const long long co = ti.shape.empty() ? 0 : ti.shape.back();
                 const long long at = off;
                 off += co;
-                if (ti.is_graph_io || ti.last == INT_MAX || is_view[t] || is_root[t] || ti.alias_of >= 0 || (at * es) % 16 != 0 || (co * es) % 16 != 0 ||
+                if (ti.is_graph_io || ti.last == INT_MAX || is_view[t] || is_root[t] || ti.alias_of >= 0 || (at * es) % SLICE_UNIT != 0 || (co * es) % SLICE_UNIT != 0 ||
                     consumers[t].empty() || !mod->strided_output_ok((int)o, step_in_shapes[step]) || !readers_ok(t, -1))
                     continue;
                 ti.alias_of = x, ti.view_offset = (size_t)(at * es), ti.row_stride = infos[x].shape[ax];
