@@ -183,6 +183,16 @@ int espdl_b200_download(void *dst_host, const void *src_dev, size_t bytes, void 
     return ESPDL_OK;
 }
 
+} // extern "C"
+namespace espdl {
+bool pdl_enabled()
+{
+    static const bool on = !getenv("ESPDL_B200_NO_PDL");
+    return on;
+}
+} // namespace espdl
+extern "C" {
+
 int espdl_b200_download_rows(void *dst_host, const void *src_dev, size_t row_bytes, size_t src_stride_bytes, size_t rows, void *stream)
 {
     if ((!dst_host || !src_dev) && row_bytes && rows)

@@ -23,6 +23,30 @@ unsigned *sched_counters(cudaStream_t s);
 int lp_norm_op(const espdl_norm_desc &d, cudaStream_t s); // sequence_ops.cu
 // Records the most recent failed launch (cudaGetLastError) if any.
 int check_launch(const char *what);
+// Programmatic dependent launch: the kernel may become resident while the previous kernel of the stream is still
+// draining (its CTAs take an SM as soon as one is free and run their prologue: barriers, TMEM, per-channel constants).
+// Such a kernel calls grid_dep_wait() before it reads or writes anything a previous kernel touches, and
+// grid_dep_launch() once its own CTA is set up.  ESPDL_B200_NO_PDL=1 launches them the plain way.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args &&...args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#ifdef __CUDACC__
+// Blocks until every kernel this one depends on has finished and its writes are visible to this grid.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// This CTA no longer minds the next kernel's CTAs becoming resident.
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 #define ESPDL_CUDA_TRY(call)                                \
     do {                                                    \

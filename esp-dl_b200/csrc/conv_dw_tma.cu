@@ -121,8 +121,11 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
     }
     __syncthreads();
     const int CB = CBT ? CBT : p.CB;
+    if (threadIdx.x == 0)
+        grid_dep_launch(); // set up: the next kernel's CTAs may take SMs as they become free
 
     if (warp == DWT_CONSUMER_WARPS) {
+        grid_dep_wait(); // the previous kernel's output (and its use of the tile counter) before the first load
         // ------------------------------------------------------------ producer: the warp walks the tiles, lane 0 issues
         // Tiles below p.static_tiles go round the CTAs in the fixed order; the rest is handed out by a global counter, one
         // number per tile and asked for one tile ahead, so that an SM that runs slower than the others ends with fewer tiles.
@@ -361,7 +364,7 @@ int dwt_launch(const CUtensorMap &mi, const CUtensorMap &mo, const DwtParams &p,
     std::call_once(once, [] { attr_err = cudaFuncSetAttribute(dw3x3_tma_kernel<S, CBT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(DWT_SMEM_BUDGET + 2048)); });
     if (attr_err != cudaSuccess)
         return set_cuda_error(attr_err, "cudaFuncSetAttribute(dw3x3_tma_kernel)");
-    dw3x3_tma_kernel<S, CBT><<<grid, DWT_THREADS, smem, s>>>(mi, mo, p);
+    launch_overlapped(dw3x3_tma_kernel<S, CBT>, dim3(grid), dim3(DWT_THREADS), smem, s, mi, mo, p);
     count_launch();
     return check_launch("dw3x3_tma");
 }

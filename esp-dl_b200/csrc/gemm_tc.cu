@@ -249,6 +249,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncthreads();
         fast = !*slow_flag && !p.epi.half_even && p.K <= 32768; // a fused table rides on the staged form; the direct-store forms apply it in their general path
     }
+    // This CTA is set up (everything above reads launch parameters and model constants only): the next kernel's CTAs may
+    // take SMs as they become free.  The producer below waits for the previous kernel before its first load, and every
+    // other role only ever acts on what the producer brought in.
+    if (threadIdx.x == 0)
+        grid_dep_launch();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -257,6 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // large Gemm, where the issue rate of this loop and of the MMA loop below is what bounds the kernel.)
         const bool issuer = lane == 0;
         if (issuer) {
+        grid_dep_wait(); // the previous kernel's output, and its use of the tile counter, before the first load
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -1103,7 +1109,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     if (i16)
         gemm_tc_kernel<true><<<grid, NUM_THREADS, smem, s>>>(ma, mb, ma_lo, mb_lo, mo, p);
     else
-        gemm_tc_kernel<false><<<grid, NUM_THREADS, smem, s>>>(ma, mb, ma_lo, mb_lo, mo, p);
+        launch_overlapped(gemm_tc_kernel<false>, dim3(grid), dim3(NUM_THREADS), smem, s, ma, mb, ma_lo, mb_lo, mo, p);
     count_launch();
     return check_launch("gemm_tc");
 }
