@@ -119,6 +119,10 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap map_in, const __grid_consta
         for (int i = 0; i < DWT_RING; i++) tile_ring[i] = 0; // never negative before the producer says so
         fence_barrier_init();
     }
+    if (threadIdx.x == 32) {
+        prefetch_tensormap(&map_in);
+        prefetch_tensormap(&map_out);
+    }
     __syncthreads();
     const int CB = CBT ? CBT : p.CB;
     if (threadIdx.x == 0)

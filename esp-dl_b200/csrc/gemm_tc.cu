@@ -233,6 +233,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         *slow_flag = 0;
         fence_barrier_init();
     }
+    if (threadIdx.x == 32 * 2) { // an epilogue thread: the descriptors are in the cache when the first copies are issued
+        prefetch_tensormap(&map_a);
+        prefetch_tensormap(&map_b);
+        if (I16) {
+            prefetch_tensormap(&map_a_lo);
+            prefetch_tensormap(&map_b_lo);
+        } else if (p.out_pw) {
+            prefetch_tensormap(&map_out);
+        }
+    }
     if (warp == 1)
         tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
     fence_before();

@@ -137,6 +137,12 @@ __device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_
         : "memory");
 }
 
+// Brings a tensor map (a __grid_constant__ kernel parameter) into the descriptor cache ahead of the first copy that uses it.
+__device__ __forceinline__ void prefetch_tensormap(const void *map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols)
 {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
