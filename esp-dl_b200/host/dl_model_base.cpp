@@ -771,6 +771,8 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
         }
     }
     m_arena_bytes = MemoryManagerGreedy::plan(infos, m_reuse_memory);
+    if (m_plan_only)
+        return;
     if (espdl_b200_arena_alloc(m_arena_bytes + 256, &m_arena) != ESPDL_OK) {
         ESP_LOGE("dl::Model", "Failed to allocate a %.1f MB device arena", m_arena_bytes / 1048576.0);
         m_status = ESPDL_ERR_NO_MEM;

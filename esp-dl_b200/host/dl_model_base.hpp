@@ -111,6 +111,8 @@ public:
     // backend knobs (set before build / the constructor reads the environment for defaults)
     bool m_use_graph = true;     ///< replay the plan as a captured CUDA graph
     int m_slice_views = 0;       ///< tensors placed as channel slices of a Concat output / Split input (no copy)
+    bool m_plan_only = false;    ///< build() stops after the arena plan: no device is touched (planner tests on CPU)
+    const std::vector<TensorInfo> &tensor_infos() const { return m_tensor_infos; }
     bool m_reuse_memory = true;  ///< false: every tensor keeps its own buffer (lets tests read intermediates)
     int m_status = 0;            ///< first failing C-ABI status, 0 if none
     size_t arena_bytes() const { return m_arena_bytes; }

@@ -62,6 +62,48 @@ void *espdl_model_create(const char *path, int batch, int flags)
     return h;
 }
 
+/// Loads a model and plans its arena without touching a device.  Returns the number of planned tensors (negative on
+/// error); *arena_bytes and *slices receive the arena size and the number of channel slices, and `text` (capacity `cap`)
+/// one line per slice: "name<TAB>name of the tensor it lives in<TAB>byte offset inside it<TAB>row stride in elements".
+int espdl_model_plan(const char *path, int batch, int reuse, size_t *arena_bytes, int *slices, char *text, size_t cap)
+{
+    Model m;
+    m.m_plan_only = true;
+    m.m_reuse_memory = reuse != 0;
+    if (m.load(path, fbs::MODEL_LOCATION_IN_SDCARD, 0, nullptr, true) != ESP_OK)
+        return -1;
+    std::map<std::string, std::vector<int>> shapes;
+    if (batch > 0) {
+        for (const std::string &name : m.get_fbs_model()->get_graph_inputs()) {
+            std::vector<int> s = m.get_fbs_model()->get_value_info_shape(name);
+            if (!s.empty())
+                s[0] = batch;
+            shapes[name] = s;
+        }
+    }
+    m.build(0, MEMORY_MANAGER_GREEDY, false, shapes);
+    if (m.m_status)
+        return -2;
+    const std::vector<TensorInfo> &infos = m.tensor_infos();
+    std::string lines;
+    int n_slices = 0;
+    for (const TensorInfo &ti : infos)
+        if (ti.row_stride) {
+            n_slices++;
+            lines += ti.name + "\t" + infos[ti.alias_of].name + "\t" + std::to_string(ti.view_offset) + "\t" + std::to_string(ti.row_stride) + "\n";
+        }
+    if (arena_bytes)
+        *arena_bytes = m.arena_bytes();
+    if (slices)
+        *slices = n_slices;
+    if (text && cap) {
+        const size_t n = std::min(cap - 1, lines.size());
+        memcpy(text, lines.data(), n);
+        text[n] = 0;
+    }
+    return (int)infos.size();
+}
+
 void espdl_model_destroy(void *handle)
 {
     Handle *h = (Handle *)handle;

@@ -318,3 +318,52 @@ def test_pdl_package_table_is_checked_against_the_file(host, tmp_path):
     path = tmp_path / "bad_count.espdl"
     path.write_bytes(bytes(count))
     assert host.espdl_fbs_describe(os.fsencode(path)) is None
+
+
+def _plan(host, path, batch=0, reuse=1):
+    host.espdl_model_plan.restype = C.c_int
+    host.espdl_model_plan.argtypes = [C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_int), C.c_char_p, C.c_size_t]
+    arena, slices = C.c_size_t(), C.c_int()
+    text = C.create_string_buffer(1 << 16)
+    n = host.espdl_model_plan(os.fsencode(path), batch, reuse, C.byref(arena), C.byref(slices), text, len(text))
+    assert n > 0, n
+    rows = [line.split("\t") for line in text.value.decode().splitlines()]
+    return n, arena.value, slices.value, {r[0]: (r[1], int(r[2]), int(r[3])) for r in rows}
+
+
+def test_planner_places_concat_inputs_and_split_outputs_as_channel_slices(host, tmp_path, monkeypatch):
+    """The arena plan of the detector-shaped graph, made without a device: tensors that feed a Concat along the channel axis
+    from a producer that can write strided rows live inside the Concat's output, Split outputs whose readers can read such
+    rows are windows into the Split's input; slices start and stride on 32-byte boundaries; the plan with the pass switched
+    off has none and needs more memory."""
+    g = zoo.yolo11n_style(seed=6, input_hw=96)
+    path = str(tmp_path / "det.espdl")
+    g.save(path)
+    parsed = espdl_file.read(path)
+    n, arena, slices, views = _plan(host, path, batch=2)
+    assert slices == len(views) >= 8
+    producer = {o: nd for nd in parsed["nodes"] for o in nd["outputs"]}
+    consumers = {}
+    for nd in parsed["nodes"]:
+        for i in nd["inputs"]:
+            consumers.setdefault(i, []).append(nd)
+    for name, (wide, offset, stride) in views.items():
+        assert offset % 32 == 0 and stride % 32 == 0
+        into_concat = producer.get(wide, {}).get("op_type") == "Concat" and name in producer[wide]["inputs"]
+        from_split = producer.get(name, {}).get("op_type") == "Split" and producer[name]["inputs"][0] == wide
+        assert into_concat or from_split, (name, wide)
+        # the table lookups that were folded into their convs are gone from the plan: what reads or writes a slice takes a row stride
+        for c in consumers.get(name, []):
+            assert c["op_type"] in ("Conv", "Concat", "Add", "RequantizeLinear", "Swish", "Mul"), (name, c["op_type"])
+    monkeypatch.setenv("ESPDL_B200_SLICE_VIEWS", "0")
+    n0, arena0, slices0, _ = _plan(host, path, batch=2)
+    assert n0 == n and slices0 == 0 and arena0 > arena
+
+
+def test_planner_leaves_ragged_concats_alone(host):
+    """The face detector concatenates 48 + 24 + 24 channels: 24-byte parts are no whole 32-byte units, nothing becomes a slice."""
+    path = os.path.join(GOLDEN, "esp32p4__zoo_face_msr.espdl")
+    if not os.path.exists(path):
+        pytest.skip("fixture not present")
+    n, arena, slices, views = _plan(host, path)
+    assert n > 40 and slices == 0 and arena > 0
