@@ -360,6 +360,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const uint32_t idesc_us = idesc_i8(0, 1, BLOCK_M, p.block_n);
         const uint32_t idesc_uu = idesc_i8(0, 0, BLOCK_M, p.block_n);
         const int ksteps = p.swz / 32;
+        const int last_ksteps = (p.K - (p.k_blocks - 1) * p.swz + 31) / 32; // 32-byte K steps of the last block that hold data
         const uint32_t smem_base = smem_u32(smem);
         for (int local = 0; ok; local++) {
             TC_LAP(w_issue);
@@ -406,20 +407,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const uint32_t st = smem_base + (uint32_t)(stage * stage_bytes);
                 const uint64_t da = smem_desc_swizzled(st, p.swz);
                 const uint64_t db = smem_desc_swizzled(st + NPLANE * a_bytes, p.swz);
+                // the reduction's last block may end early: its K steps past the end would multiply the TMA unit's zero fill
+                const int ks = kb == p.k_blocks - 1 ? last_ksteps : ksteps;
                 if (!I16) {
                     const uint32_t first = kb != 0 ? 1u : 0u;
                     mma_i8(d0, da, db, idesc_ss, first);
-                    if (ksteps > 1)
+                    if (ks > 1)
                         mma_i8(d0, da + 2, db + 2, idesc_ss, 1u);
-                    if (ksteps > 2) {
+                    if (ks > 2)
                         mma_i8(d0, da + 4, db + 4, idesc_ss, 1u);
+                    if (ks > 3)
                         mma_i8(d0, da + 6, db + 6, idesc_ss, 1u);
-                    }
                     commit(smem_u32(&empty_bar[stage]));
                 } else {
                     const uint64_t da_lo = smem_desc_swizzled(st + a_bytes, p.swz);
                     const uint64_t db_lo = smem_desc_swizzled(st + 2 * a_bytes + b_bytes, p.swz);
-                    for (int k = 0; k < ksteps; k++) {
+                    for (int k = 0; k < ks; k++) {
                         const uint32_t accum = (kb | k) != 0;
                         const uint64_t koff = (uint64_t)(k * 2); // 32 bytes of K, in 16-byte units
                         mma_i8(d0, da + koff, db + koff, idesc_ss, accum);                      // hi * hi
