@@ -33,7 +33,7 @@ class ConvDesc(C.Structure):
         ("group", i32), ("in_pixel_stride", i32), ("out_pixel_stride", i32),
         ("in_exponent", i32), ("out_exponent", i32), ("filter_exponent", i32), ("per_channel", i32),
         ("activation", i32), ("round_mode", i32), ("kernel", i32), ("filter_image_stride", i32),
-        ("residual", C.c_void_p), ("residual_pixel_stride", i32), ("reserved", i32),
+        ("residual", C.c_void_p), ("residual_pixel_stride", i32), ("lut_channel_stride", i32),
     ]
 
 

@@ -399,6 +399,8 @@ int espdl::conv_validate(const espdl_conv_desc *d)
         return ESPDL_ERR_INVALID_ARG;
     if (d->lut && d->dtype != ESPDL_DTYPE_INT8)
         return ESPDL_ERR_UNSUPPORTED;
+    if (d->lut_channel_stride != 0 && (!d->lut || d->lut_channel_stride < 256))
+        return ESPDL_ERR_INVALID_ARG;
     if ((d->in_pixel_stride && d->in_pixel_stride < d->in_c) || (d->out_pixel_stride && d->out_pixel_stride < d->out_c))
         return ESPDL_ERR_INVALID_ARG;
     if (d->filter_image_stride != 0 && d->group != 1)

@@ -15,6 +15,7 @@ struct DwParams {
     void *out;
     const int32_t *ew;
     const int8_t *lut;
+    int lut_stride; // 0: one table, else entries between the tables of consecutive channels
     int n, ih, iw, c, oh, ow, kh, kw, sh, sw, dh, dw, pt, pl, ips, ops;
     int e_shift_base, ew_scalar, per_channel, relu, half_even;
     long long total;
@@ -68,7 +69,7 @@ __global__ void __launch_bounds__(256) dw_s8_vec16_kernel(DwParams p)
                 const int shift = max(-31, min(31, p.e_shift_base - e));
                 int32_t v = requant8(acc[q * 4 + i], bias ? __ldg(bias + c) : 0, shift, p.relu, p.half_even);
                 if (p.lut)
-                    v = p.lut[(uint8_t)v ^ 0x80u];
+                    v = p.lut[(long long)c * p.lut_stride + ((uint8_t)v ^ 0x80u)];
                 wd |= ((uint32_t)v & 0xffu) << (8 * i);
             }
             packed[q] = wd;
@@ -142,7 +143,7 @@ __device__ __noinline__ void dw3x3_band_general(const DwParams &p, int S, int n,
                 const int shift = max(-31, min(31, p.e_shift_base - e));
                 int32_t v = requant8(acc, p.bias ? ((const int32_t *)p.bias)[c] : 0, shift, p.relu, p.half_even);
                 if (p.lut)
-                    v = p.lut[(uint8_t)v ^ 0x80u];
+                    v = p.lut[(long long)c * p.lut_stride + ((uint8_t)v ^ 0x80u)];
                 out[((long long)oy * p.ow + ox) * p.ops + c] = (int8_t)v;
             }
 }
@@ -352,7 +353,7 @@ __global__ void __launch_bounds__(256) dw_generic_kernel(DwParams p)
             const int shift = max(-31, min(31, p.e_shift_base - e));
             int32_t v = requant8((int32_t)acc, bias ? (int32_t)bias[c] : 0, shift, p.relu, p.half_even);
             if (p.lut)
-                v = p.lut[(uint8_t)v ^ 0x80u];
+                v = p.lut[(long long)c * p.lut_stride + ((uint8_t)v ^ 0x80u)];
             out[pix * p.ops + c] = (T)v;
         } else {
             const int shift = max(-62, min(62, p.e_shift_base - e));
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(256) dw_generic_kernel(DwParams p)
 int conv2d_depthwise(const espdl_conv_desc &d, cudaStream_t s)
 {
     DwParams p;
-    p.in = d.input, p.w = d.filter, p.bias = d.bias, p.out = d.output, p.ew = d.filter_exponents, p.lut = d.lut;
+    p.in = d.input, p.w = d.filter, p.bias = d.bias, p.out = d.output, p.ew = d.filter_exponents, p.lut = d.lut, p.lut_stride = d.lut_channel_stride;
     p.n = d.n, p.ih = d.in_h, p.iw = d.in_w, p.c = d.in_c, p.oh = d.out_h, p.ow = d.out_w;
     p.kh = d.kh, p.kw = d.kw, p.sh = d.stride_h, p.sw = d.stride_w, p.dh = d.dilation_h, p.dw = d.dilation_w;
     p.pt = d.pad_top, p.pl = d.pad_left;

@@ -90,7 +90,7 @@ __device__ __noinline__ void dwt_walk_general(const DwtParams &pp, int S, const 
                 const int shift = max(-31, min(31, p.e_shift_base - e));
                 int32_t v = requant8(acc, p.bias ? p.bias[c0 + i] : 0, shift, p.relu, p.half_even);
                 if (p.lut)
-                    v = p.lut[(uint8_t)v ^ 0x80u];
+                    v = p.lut[(long long)(c0 + i) * p.lut_stride + ((uint8_t)v ^ 0x80u)];
                 op[ro * out_row_bytes + x * pp.CB + i] = (int8_t)v;
             }
 }
@@ -425,7 +425,7 @@ int conv2d_dw_tma(const espdl_conv_desc &d, cudaStream_t s)
     p.withhold_arrive = expiry && atoi(expiry) > 0 ? 1 : 0;
     p.wait_limit = p.withhold_arrive ? (long long)atoi(expiry) * 2000000ll : WAIT_LIMIT_CYCLES;
     p.src.C = d.in_c;
-    p.src.w = (const int8_t *)d.filter, p.src.bias = (const int32_t *)d.bias, p.src.ew = d.filter_exponents, p.src.lut = d.lut;
+    p.src.w = (const int8_t *)d.filter, p.src.bias = (const int32_t *)d.bias, p.src.ew = d.filter_exponents, p.src.lut = d.lut, p.src.lut_stride = d.lut_channel_stride;
     p.src.e_shift_base = d.out_exponent - d.in_exponent;
     p.src.ew_scalar = d.filter_exponent, p.src.per_channel = d.per_channel;
     p.src.relu = d.activation == ESPDL_ACT_RELU, p.src.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;

@@ -16,6 +16,7 @@ struct ConvParams {
     void *out;
     const int32_t *ew;
     const int8_t *lut;
+    int lut_stride; // 0: one table, else entries between the tables of consecutive channels
     const int8_t *res; // optional residual added to the result (a folded Add), or null
     int rps;           // residual pixel stride
     int n, ih, iw, ic, oh, ow, oc, kh, kw, sh, sw, dh, dw, pt, pl, ips, ops;
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(256) conv_s8_kernel(ConvParams p)
                 const int shift = max(-31, min(31, p.e_shift_base - e));
                 int32_t q = requant8(acc[j], bias ? bias[oc] : 0, shift, p.relu, p.half_even);
                 if (p.lut)
-                    q = p.lut[(uint8_t)q ^ 0x80u];
+                    q = p.lut[(long long)oc * p.lut_stride + ((uint8_t)q ^ 0x80u)];
                 if (p.res)
                     q = sat8(q + (int)p.res[pix * p.rps + oc]);
                 op[j] = (int8_t)q;
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(256) conv_s8_small_k_kernel(ConvParams p)
                     for (int i = 0; i < words; i++) acc = __dp4a(a[i], wr[i], acc);
                     int q = requant8(acc, bias_s[oc], shift_s[oc], p.relu, p.half_even);
                     if (p.lut)
-                        q = p.lut[(uint8_t)q ^ 0x80u];
+                        q = p.lut[(long long)oc * p.lut_stride + ((uint8_t)q ^ 0x80u)];
                     pk[j >> 2] |= ((uint32_t)q & 0xffu) << (8 * (j & 3));
                 }
             }
@@ -238,7 +239,7 @@ int conv2d_simt(const espdl_conv_desc &d, cudaStream_t s)
 {
     ConvParams p;
     p.res = (const int8_t *)d.residual, p.rps = d.residual_pixel_stride ? d.residual_pixel_stride : d.out_c;
-    p.in = d.input, p.w = d.filter, p.bias = d.bias, p.out = d.output, p.ew = d.filter_exponents, p.lut = d.lut;
+    p.in = d.input, p.w = d.filter, p.bias = d.bias, p.out = d.output, p.ew = d.filter_exponents, p.lut = d.lut, p.lut_stride = d.lut_channel_stride;
     p.n = d.n, p.ih = d.in_h, p.iw = d.in_w, p.ic = d.in_c, p.oh = d.out_h, p.ow = d.out_w, p.oc = d.out_c;
     p.kh = d.kh, p.kw = d.kw, p.sh = d.stride_h, p.sw = d.stride_w, p.dh = d.dilation_h, p.dw = d.dilation_w;
     p.pt = d.pad_top, p.pl = d.pad_left;

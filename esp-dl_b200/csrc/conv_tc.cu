@@ -205,7 +205,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             stage_lut(p.epi.lut, lut_s, et, 16 * 32);
         asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
         // a fused table rides on the staged form; the direct-store form applies it in its general path
-        const bool fast = !*slow_flag && !p.epi.half_even && (long long)p.cin * p.kh * p.kw <= 32768;
+        const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut_stride && (long long)p.cin * p.kh * p.kw <= 32768;
         const uint32_t fp_base = epi_param_base(fast_s);
         const int floor_q = p.epi.relu ? 0 : INT_MIN;
         const int ry = row_in_tile / p.P, rx = row_in_tile % p.P;
@@ -532,7 +532,7 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         if (p.epi.lut)
             stage_lut(p.epi.lut, lut_s, et, 16 * 32);
         asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
-        const bool fast = !*slow_flag && !p.epi.half_even && (long long)p.cin * p.kh * p.kw <= 32768;
+        const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut_stride && (long long)p.cin * p.kh * p.kw <= 32768;
         const uint32_t fp_base = epi_param_base(fast_s);
         const int floor_q = p.epi.relu ? 0 : INT_MIN;
         uint32_t acc_phase = 0;
@@ -806,7 +806,7 @@ int launch_patch(const espdl_conv_desc &d, PatchParams &p, cudaStream_t s)
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
     p.out = d.output;
     p.ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
-    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut;
+    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut, p.epi.lut_stride = d.lut_channel_stride;
     p.epi.e_shift_base = d.out_exponent - d.in_exponent;
     p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;
     p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;
@@ -893,7 +893,7 @@ int conv2d_conv_tc(const espdl_conv_desc &d, cudaStream_t s)
     const int ips = d.in_pixel_stride ? d.in_pixel_stride : d.in_c;
     p.out = d.output;
     p.ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
-    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut;
+    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut, p.epi.lut_stride = d.lut_channel_stride;
     p.epi.e_shift_base = d.out_exponent - d.in_exponent;
     p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;
     p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;

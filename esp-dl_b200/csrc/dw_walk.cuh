@@ -23,6 +23,7 @@ struct DwtSource {
     const int8_t *w;          // [3][3][C]
     const int32_t *bias, *ew; // int32[C] or null
     const int8_t *lut;
+    int lut_stride; // 0: one table, else entries between the tables of consecutive channels
     int C, e_shift_base, ew_scalar, per_channel, relu, half_even;
 };
 

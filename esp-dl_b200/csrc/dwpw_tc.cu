@@ -529,7 +529,7 @@ int fused_dwpw(const espdl_block_desc &d, cudaStream_t s)
         return set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");
     p.N = d.n, p.OH = d.out_h, p.OW = d.out_w, p.cout = d.out_c, p.K = d.hidden_c;
     p.pt = d.pad_top, p.pl = d.pad_left;
-    p.dw.C = d.hidden_c, p.dw.w = (const int8_t *)d.dw_filter, p.dw.bias = (const int32_t *)d.dw_bias, p.dw.ew = d.dw_filter_exponents, p.dw.lut = nullptr;
+    p.dw.C = d.hidden_c, p.dw.w = (const int8_t *)d.dw_filter, p.dw.bias = (const int32_t *)d.dw_bias, p.dw.ew = d.dw_filter_exponents, p.dw.lut = nullptr, p.dw.lut_stride = 0;
     p.dw.e_shift_base = d.dw_exponent - d.in_exponent, p.dw.ew_scalar = d.dw_filter_exponent, p.dw.per_channel = (d.per_channel >> 1) & 1;
     p.dw.relu = d.dw_activation == ESPDL_ACT_RELU, p.dw.half_even = 0;
     p.e2 = EpiConfig{d.project_bias, d.project_filter_exponents, nullptr, d.out_exponent - d.dw_exponent, d.project_filter_exponent, (d.per_channel >> 2) & 1,

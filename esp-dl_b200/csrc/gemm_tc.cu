@@ -257,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (p.epi.lut)
             stage_lut(p.epi.lut, lut_s, (int)threadIdx.x, NUM_THREADS);
         __syncthreads();
-        fast = !*slow_flag && !p.epi.half_even && p.K <= 32768; // a fused table rides on the staged form; the direct-store forms apply it in their general path
+        fast = !*slow_flag && !p.epi.half_even && !p.epi.lut_stride && p.K <= 32768; // one table rides on the staged form and on the packed words of unstaged rows; per-channel tables take the general path
     }
     // This CTA is set up (everything above reads launch parameters and model constants only): the next kernel's CTAs may
     // take SMs as they become free.  The producer below waits for the previous kernel before its first load, and every
@@ -1051,7 +1051,7 @@ int conv2d_tc(const espdl_conv_desc &d, void *workspace, size_t workspace_bytes,
     p.ops = d.out_pixel_stride ? d.out_pixel_stride : d.out_c;
     p.res = (const int8_t *)d.residual;
     p.rps = d.residual_pixel_stride ? d.residual_pixel_stride : d.out_c;
-    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut;
+    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut, p.epi.lut_stride = d.lut_channel_stride;
     p.epi.e_shift_base = d.out_exponent - d.in_exponent;
     p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;
     p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;

@@ -226,7 +226,7 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
                 atomicOr(slow_flag, 1);
         }
         asm volatile("bar.sync 1, %0;" ::"n"(16 * 32) : "memory");
-        const bool fast = !*slow_flag && !p.epi.half_even; // a fused table rides on the staged form
+        const bool fast = !*slow_flag && !p.epi.half_even && !p.epi.lut_stride; // one fused table rides on the staged form, per-channel tables take the general path
         const uint32_t fp = epi_param_base(fast_s);
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -288,7 +288,7 @@ stem_tc_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__
                         const int shift = max(-31, min(31, p.epi.e_shift_base - e));
                         int32_t r = requant8(v[i], p.epi.bias ? __ldg((const int32_t *)p.epi.bias + c) : 0, shift, p.epi.relu, p.epi.half_even);
                         if (p.epi.lut)
-                            r = p.epi.lut[(uint8_t)r ^ 0x80u];
+                            r = p.epi.lut[(long long)c * p.epi.lut_stride + ((uint8_t)r ^ 0x80u)];
                         pk[i >> 2] |= ((uint32_t)r & 0xffu) << (8 * (i & 3));
                     }
                     if (row_ok)
@@ -369,7 +369,7 @@ int conv2d_stem_tc(const espdl_conv_desc &d, cudaStream_t s)
     p.x_shift = d.pad_left ? 16 : 0;
     p.k_base = d.pad_left ? 16 - 3 * d.pad_left : 0;
     p.w = (const int8_t *)d.filter, p.out = d.output;
-    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut;
+    p.epi.bias = d.bias, p.epi.ew = d.filter_exponents, p.epi.lut = d.lut, p.epi.lut_stride = d.lut_channel_stride;
     p.epi.e_shift_base = d.out_exponent - d.in_exponent;
     p.epi.ew_scalar = d.filter_exponent, p.epi.per_channel = d.per_channel;
     p.epi.relu = d.activation == ESPDL_ACT_RELU, p.epi.half_even = d.round_mode == ESPDL_ROUND_HALF_EVEN;

@@ -243,6 +243,7 @@ struct EpiConfig {
     const int32_t *ew;  // per-channel filter exponents or null
     const int8_t *lut;  // optional fused 256-entry table
     int e_shift_base, ew_scalar, per_channel, relu, half_even;
+    int lut_stride;     // 0: one table; else entries between the tables of consecutive channels (general epilogue only)
 };
 
 // Fills fast[j] for channels [0, n_pad) with `nthreads` cooperating threads (tid in [0, nthreads)).
@@ -549,7 +550,7 @@ __device__ __forceinline__ void requant16_general(const int32_t *v, const EpiCon
             const int b = c.bias ? __ldg((const int32_t *)c.bias + n) : 0;
             int32_t r = requant8(v[q * 4 + i], b, shift, c.relu, c.half_even);
             if (c.lut)
-                r = c.lut[(uint8_t)r ^ 0x80u];
+                r = c.lut[(long long)n * c.lut_stride + ((uint8_t)r ^ 0x80u)];
             wd |= ((uint32_t)r & 0xffu) << (8 * i);
         }
         pk[q] = wd;

@@ -463,6 +463,69 @@ void Model::fold_luts()
     }
 }
 
+void Model::fold_prelus()
+{
+    if (!env_flag("ESPDL_B200_FOLD_PRELU", true) || !m_reuse_memory)
+        return;
+    ModelContext *ctx = m_model_context;
+    std::vector<std::string> graph_outputs = m_fbs_model->get_graph_outputs();
+    auto is_graph_output = [&](const std::string &n) { return std::find(graph_outputs.begin(), graph_outputs.end(), n) != graph_outputs.end(); };
+    for (size_t s = 0; s < m_execution_plan.size(); s++) {
+        module::PRelu *act = dynamic_cast<module::PRelu *>(m_execution_plan[s]);
+        if (!act || act->quant_type != QUANT_TYPE_SYMM_8BIT || m_module_inputs[s].empty() || m_module_outputs[s].size() != 1)
+            continue;
+        TensorBase *alpha = act->get_table();
+        const std::string x = m_module_inputs[s][0], y = m_module_outputs[s][0];
+        if (!alpha || alpha->dtype != DATA_TYPE_INT8 || !alpha->data || is_graph_output(x) || m_fbs_model->is_parameter(x) ||
+            m_fbs_model->get_value_info_dtype(x) != DATA_TYPE_INT8 || m_fbs_model->get_value_info_dtype(y) != DATA_TYPE_INT8)
+            continue;
+        int producer = -1, readers = 0;
+        for (size_t k = 0; k < m_execution_plan.size(); k++) {
+            for (const std::string &o : m_module_outputs[k])
+                if (o == x) producer = (int)k;
+            for (const std::string &i : m_module_inputs[k])
+                if (i == x) readers++;
+        }
+        if (producer < 0 || producer >= (int)s || readers != 1 || m_module_types[producer] != "Conv" || m_module_outputs[producer].size() != 1 ||
+            m_module_inputs[producer].size() < 2)
+            continue;
+        module::Conv *conv = dynamic_cast<module::Conv *>(m_execution_plan[producer]);
+        TensorBase *filter = ctx->get_tensor(m_module_inputs[producer][1]);
+        if (!conv || !conv->can_fuse_channel_tables() || !filter || filter->shape.size() != 4)
+            continue;
+        const int channels = conv->is_depthwise() ? filter->shape[2] * filter->shape[3] : filter->shape[3];
+        if (alpha->get_size() != channels)
+            continue;
+        // dl::base::prelu (esp-dl/dl/base/dl_base_prelu.cpp:7-21): a value below zero becomes (value * slope) >> shift with a
+        // plain arithmetic shift, shift = e_out - e_in - e_slope (a left shift when negative); the rest passes unchanged
+        const int shift = m_fbs_model->get_value_info_exponent(y) - m_fbs_model->get_value_info_exponent(x) - (int)alpha->exponent;
+        if (shift > 30 || shift < -16)
+            continue;
+        std::vector<int8_t> tables((size_t)channels * 256);
+        const int8_t *slope = (const int8_t *)alpha->data;
+        for (int c = 0; c < channels; c++)
+            for (int i = 0; i < 256; i++) {
+                const int q = (int)(int8_t)(uint8_t)(i ^ 0x80);
+                int v = q;
+                if (q < 0) {
+                    const int prod = q * (int)slope[c];
+                    v = shift > 0 ? (prod >> shift) : (int)((unsigned)prod << (-shift));
+                    v = std::max(-128, std::min(127, v));
+                }
+                tables[(size_t)c * 256 + i] = (int8_t)v;
+            }
+        TensorBase *t = new TensorBase({channels * 256}, tables.data(), 0, DATA_TYPE_INT8, true);
+        conv->set_fused_channel_tables(t, m_fbs_model->get_value_info_exponent(x));
+        m_module_outputs[producer][0] = y;
+        delete m_execution_plan[s];
+        m_execution_plan.erase(m_execution_plan.begin() + s);
+        m_module_types.erase(m_module_types.begin() + s);
+        m_module_inputs.erase(m_module_inputs.begin() + s);
+        m_module_outputs.erase(m_module_outputs.begin() + s);
+        s--;
+    }
+}
+
 void Model::fold_quantize_after_softmax()
 {
     if (!env_flag("ESPDL_B200_FOLD_QUANT", true) || !m_reuse_memory)
@@ -651,6 +714,7 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
         return;
     fuse_blocks();
     fold_luts();
+    fold_prelus();
     fold_quantize_after_softmax();
     fold_residual_adds();
     ModelContext *ctx = m_model_context;

@@ -148,6 +148,9 @@ protected:
     int alias_channel_slices(std::vector<TensorInfo> &infos, std::map<std::string, int> &info_index,
                              const std::vector<std::vector<std::vector<int>>> &step_in_shapes, std::vector<bool> &is_root);
     void fold_luts();
+    /// A PRelu that is the only reader of an int8 conv's output becomes that conv's per-channel tables (one launch less; the
+    /// conv's kernels apply them in their general epilogue).  ESPDL_B200_FOLD_PRELU=0 switches the pass off.
+    void fold_prelus();
     /// A QuantizeLinear whose only input is the float output of a Softmax / LogSoftmax with no other reader disappears: the softmax
     /// kernel writes the quantized tensor itself (the same `round(y * 2^-e)` on the same float).  ESPDL_B200_FOLD_QUANT=0 keeps it.
     void fold_quantize_after_softmax();

@@ -181,7 +181,7 @@ esp_err_t Conv::prepare(ModelContext *context)
         const long long pixels = (long long)input->shape[1] * input->shape[2];
         TensorBase *output = context->get_tensor(m_outputs_index[0]);
         const bool sliced = input->row_stride || (output && output->row_stride); // a slice has no runs of whole pixels
-        m_group_px = sliced ? 1 : choose_pixel_group(cin, cout, pixels);
+        m_group_px = sliced || m_lut_stride ? 1 : choose_pixel_group(cin, cout, pixels); // per-channel tables are indexed by the real channel
         if (m_group_px > 1) {
             const int g = m_group_px;
             std::vector<int8_t> wf((size_t)g * cout * g * cin, 0);
@@ -265,6 +265,7 @@ int Conv::fill_desc(ModelContext *context, void *desc)
     d.input = input->device, d.filter = filter->device, d.bias = bias ? bias->device : nullptr, d.output = output->device;
     d.filter_exponents = (const int32_t *)m_dev_exponents;
     d.lut = m_lut ? (const int8_t *)m_lut->device : nullptr;
+    d.lut_channel_stride = m_lut ? m_lut_stride : 0;
     d.dtype = quant_dtype(quant_type);
     std::vector<int> fs = filter->shape;
     if (m_gemm) {

@@ -28,6 +28,18 @@ public:
         m_lut = table;
         m_pre_lut_exponent = pre_lut_exponent;
     }
+    /// Fuse a following per-channel activation (PRelu) as one 256-entry table per output channel, `tables` = int8[Cout * 256]
+    /// (entry [c][(uint8)q ^ 0x80]); every conv kernel applies such tables in its general epilogue.
+    void set_fused_channel_tables(TensorBase *tables, int pre_lut_exponent)
+    {
+        m_lut = tables;
+        m_lut_stride = 256;
+        m_pre_lut_exponent = pre_lut_exponent;
+    }
+    bool can_fuse_channel_tables() const
+    {
+        return !m_gemm && quant_type == QUANT_TYPE_SYMM_8BIT && !m_lut && !m_residual && (activation == Linear || activation == ReLU);
+    }
     /// True for the convs whose kernels apply a table in their staged epilogue: dense int8, no residual, no table yet.
     bool can_fuse_lut() const { return m_group == 1 && quant_type == QUANT_TYPE_SYMM_8BIT && !m_lut && !m_residual && (activation == Linear || activation == ReLU); }
     /// True for a pointwise int8 conv (1x1, stride 1, no padding, group 1) without a fused table: the shapes whose
@@ -75,6 +87,7 @@ protected:
     int m_group_px = 1;
     void *m_grp_filter = nullptr, *m_grp_bias = nullptr, *m_grp_exponents = nullptr;
     TensorBase *m_lut = nullptr;     ///< fused 8-bit table (owned)
+    int m_lut_stride = 0;            ///< 0: one table; 256: one table per output channel
     int m_pre_lut_exponent = 0;      ///< what the accumulator is requantised to before the table is applied
     bool m_prepared = false;
 };

@@ -133,7 +133,9 @@ typedef struct espdl_conv_desc {
     void *output;                     /* NHWC, dtype                                                   */
     const int32_t *filter_exponents;  /* device int32[out_c] if per_channel, else ignored              */
     const int8_t *lut;                /* optional device int8[256]: out = lut[(uint8)q ^ 0x80] after
-                                         the epilogue (a fused dl::module::LUT node); int8 only        */
+                                         the epilogue (a fused dl::module::LUT node); int8 only.  With
+                                         lut_channel_stride != 0 one table per output channel:
+                                         out = lut[c * lut_channel_stride + ((uint8)q ^ 0x80)]            */
     int32_t dtype;                    /* ESPDL_DTYPE_INT8 or ESPDL_DTYPE_INT16                         */
     int32_t n, in_h, in_w, in_c;
     int32_t out_h, out_w, out_c;
@@ -161,7 +163,9 @@ typedef struct espdl_conv_desc {
                                          exponents (esp-dl/dl/base/dl_base_add.cpp:8-44) folded into the conv.
                                          int8, group 1, filters without a window only; NULL = none          */
     int32_t residual_pixel_stride;    /* elements between consecutive residual pixels; 0 = out_c (dense)  */
-    int32_t reserved;
+    int32_t lut_channel_stride;       /* 0: `lut` is one table.  Else (>= 256) entries between the tables of consecutive
+                                         output channels - a per-channel activation folded into the conv, e.g. a following
+                                         dl::module::PRelu (esp-dl/dl/base/dl_base_prelu.cpp:7-21) tabulated per channel  */
 } espdl_conv_desc;
 
 int espdl_b200_conv2d(const espdl_conv_desc *desc, void *stream);

@@ -185,7 +185,7 @@ int oracle_conv2d(const espdl_conv_desc *d)
                     o16[oi] = (int16_t)q;
                 } else {
                     /* fused dl::module::LUT node: esp-dl/dl/base/dl_base_lut.cpp:10-15 */
-                    int32_t r8 = d->lut ? d->lut[(uint8_t)(int8_t)q ^ 0x80u] : (int8_t)q;
+                    int32_t r8 = d->lut ? d->lut[(int64_t)oc * d->lut_channel_stride + ((uint8_t)(int8_t)q ^ 0x80u)] : (int8_t)q;
                     if (d->residual) { /* a following Add with equal exponents: saturating sum, dl_base_add.cpp:8-44 */
                         const int rps = d->residual_pixel_stride ? d->residual_pixel_stride : d->out_c;
                         r8 += ((const int8_t *)d->residual)[(((int64_t)n * d->out_h + oy) * d->out_w + ox) * rps + oc];

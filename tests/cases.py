@@ -48,7 +48,8 @@ def conv_case(seed=0, dtype=abi.DTYPE_INT8, n=1, h=8, w=8, cin=16, cout=16, kh=3
     else:
         ew = None
         ew_scalar = int(rng.integers(e_w[0], e_w[1] + 1))
-    table = rng.integers(-128, 128, size=(256,), dtype=np.int8) if lut else None
+    # lut=True: one 256-entry table; lut="channels": one table per output channel (lut_channel_stride = 256)
+    table = rng.integers(-128, 128, size=((cout if not depthwise else cin) * 256 if lut == "channels" else 256,), dtype=np.int8) if lut else None
     out = np.zeros((n, oh, ow, ops), dtype=t)
     return dict(x=x, w=wt, b=b, ew=ew, lut=table, out=out, dtype=dtype, n=n, in_h=h, in_w=w, in_c=cin, out_h=oh, out_w=ow,
                 out_c=cout, kh=kh, kw=kw, stride_h=sh, stride_w=sw, dilation_h=dh, dilation_w=dw, pad_top=pt,
@@ -64,7 +65,7 @@ def gemm_case(seed=0, dtype=abi.DTYPE_INT8, m=64, k=64, n_out=32, **kw):
     return conv_case(seed=seed, dtype=dtype, n=1, h=1, w=m, cin=k, cout=n_out, kh=1, kw=1, pad=(0, 0, 0, 0), **kw)
 
 
-_SCALARS = [f for f, t in abi.ConvDesc._fields_ if t is abi.i32 and f != "reserved"]
+_SCALARS = [f for f, t in abi.ConvDesc._fields_ if t is abi.i32 and f != "lut_channel_stride"]
 
 
 def conv_desc(case, ptrs=None):
@@ -79,6 +80,7 @@ def conv_desc(case, ptrs=None):
             setattr(d, k, None if a is None else a.ctypes.data)
     for f in _SCALARS:
         setattr(d, f, int(case.get(f, 0)))
+    d.lut_channel_stride = 256 if case["lut"] is not None and case["lut"].size > 256 else 0
     return d
 
 

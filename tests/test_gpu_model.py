@@ -516,3 +516,33 @@ def test_concat_and_split_as_channel_slices(tmp_path, monkeypatch):
     for o in m.outputs:
         np.testing.assert_array_equal(o.array, first[o.name])
     m.close()
+
+
+def test_prelu_folding_pass(monkeypatch):
+    """The MNP face detector: eight Conv -> PRelu pairs (first layer, pointwise and depthwise convs).  Every PRelu becomes
+    per-channel tables of its conv (espdl_conv_desc.lut_channel_stride): 15 launches instead of 23, same bytes as the graph
+    oracle and as the plan with the pass switched off."""
+    path = os.path.join(GOLDEN, "esp32p4__zoo_face_mnp.espdl")
+    if not os.path.exists(path):
+        pytest.skip("fixture not present")
+    monkeypatch.setenv("ESPDL_B200_TARGET", "esp32p4")
+    parsed = espdl_file.read(path)
+    x = None
+    outs = {}
+    for fold in ("1", "0"):
+        monkeypatch.setenv("ESPDL_B200_FOLD_PRELU", fold)
+        m = model.Model(path)
+        if x is None:
+            x = np.random.default_rng(4).integers(-128, 128, size=m.inputs[0].shape, dtype=np.int8)
+        m.inputs[0].array[...] = x
+        m.run()
+        kinds = [r[1] for r in m.profile()]
+        outs[fold] = ({o.name: np.array(o.array, copy=True) for o in m.outputs}, kinds)
+        m.close()
+    assert outs["0"][1].count("PRelu") == 8 and outs["1"][1].count("PRelu") == 0
+    assert len(outs["1"][1]) == len(outs["0"][1]) - 8
+    want = graph_oracle.run_graph(parsed, {parsed["inputs"][0]["name"]: x}, round_mode=abi.ROUND_HALF_EVEN, target="esp32p4")
+    for name, got in outs["1"][0].items():
+        np.testing.assert_array_equal(got.reshape(want[name].shape), want[name])
+        np.testing.assert_array_equal(got, outs["0"][0][name])
+        assert want[name].astype(np.float32).std() > 0

@@ -329,3 +329,31 @@ def test_strided_conv_with_fused_table_and_256_columns(direct, monkeypatch):
     want = gpu_util.run_conv_oracle(case)
     assert want.std() > 5
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+
+
+# One table per output channel (espdl_conv_desc.lut_channel_stride): what a folded PRelu becomes.  Every conv kernel takes it
+# in its general epilogue.
+CHANNEL_TABLES = [
+    dict(n=1, h=1, w=300, cin=64, cout=48, kh=1, kw=1, pad=(0, 0, 0, 0)),            # tile kernel
+    dict(n=2, h=18, w=22, cin=32, cout=48),                                          # implicit GEMM, one MMA per tap
+    dict(n=2, h=20, w=20, cin=64, cout=64),                                          # one patch per tile, stacked taps
+    dict(n=2, h=18, w=22, cin=16, cout=16),                                          # banded filter
+    dict(n=2, h=48, w=64, cin=3, cout=16, stride=2, pad=(0, 1, 0, 1)),               # first layer
+    dict(n=2, h=19, w=23, cin=80, cout=80, depthwise=True),                          # depthwise, TMA patches
+    dict(n=2, h=15, w=15, cin=24, cout=24, depthwise=True, stride=2, pad=(0, 1, 0, 1)),  # depthwise, narrow
+    dict(n=2, h=9, w=9, cin=20, cout=12),                                            # CUDA-core conv
+]
+
+
+@pytest.mark.parametrize("kw", CHANNEL_TABLES, ids=lambda k: "-".join(f"{a}{b}" for a, b in k.items() if a != "pad"))
+@pytest.mark.parametrize("act", [abi.ACT_LINEAR, abi.ACT_RELU])
+def test_conv_with_per_channel_tables(kw, act):
+    kw = dict(kw)
+    kw.setdefault("kh", 3)
+    kw.setdefault("kw", 3)
+    case = cases.conv_case(seed=17, per_channel=True, e_in=-7, e_out=-6, e_w=(-9, -7), act=act, lut="channels", **kw)
+    want = gpu_util.run_conv_oracle(case)
+    assert want.std() > 5
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), want)
+    one = dict(case, lut=np.ascontiguousarray(case["lut"][:256]))        # the same conv with the first channel's table for all
+    assert not np.array_equal(gpu_util.run_conv_oracle(one), want)
