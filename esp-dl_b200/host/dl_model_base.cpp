@@ -181,7 +181,11 @@ void Model::release()
     release_pipeline();
     if (m_graph)
         espdl_b200_graph_destroy(m_graph);
-    m_graph = nullptr;
+    if (m_graph_head)
+        espdl_b200_graph_destroy(m_graph_head);
+    if (m_graph_tail)
+        espdl_b200_graph_destroy(m_graph_tail);
+    m_graph = m_graph_head = m_graph_tail = nullptr;
     for (auto *m : m_execution_plan) delete m;
     m_execution_plan.clear();
     if (m_model_context) {
@@ -835,6 +839,18 @@ void Model::build(size_t max_internal_size, memory_manager_t mm_type, bool prelo
         }
     }
     m_arena_bytes = MemoryManagerGreedy::plan(infos, m_reuse_memory);
+    // the last step that reads a graph input's buffer (directly, or through a view / slice that lives in it)
+    m_input_steps = 0;
+    for (size_t i = 0; i < infos.size(); i++) {
+        int r = (int)i;
+        while (infos[r].alias_of >= 0) r = infos[r].alias_of;
+        if (infos[r].first >= 0)
+            continue;
+        for (size_t step = 0; step < m_execution_plan.size(); step++)
+            for (const std::string &in : m_module_inputs[step])
+                if (in == infos[i].name)
+                    m_input_steps = std::max(m_input_steps, (int)step + 1);
+    }
     if (m_plan_only)
         return;
     if (espdl_b200_arena_alloc(m_arena_bytes + 256, &m_arena) != ESPDL_OK) {
@@ -933,6 +949,34 @@ esp_err_t Model::run_device(bool sync)
     return st ? ESP_FAIL : ESP_OK;
 }
 
+// One of the two parts of a pipelined pass on the model's stream: steps [0, m_input_steps) or the rest, replayed as a
+// captured graph of its own when graphs are in use.
+esp_err_t Model::run_part(bool head)
+{
+    ModelContext *ctx = m_model_context;
+    const int first = head ? 0 : m_input_steps, last = head ? m_input_steps : (int)m_execution_plan.size();
+    if (first >= last)
+        return ESP_OK;
+    if (!m_use_graph)
+        return execute(first, last);
+    void *&graph = head ? m_graph_head : m_graph_tail;
+    int st = ESPDL_OK;
+    if (!graph) {
+        st = espdl_b200_graph_begin(ctx->stream);
+        if (!st) {
+            esp_err_t e = execute(first, last);
+            st = espdl_b200_graph_end(ctx->stream, &graph);
+            if (e != ESP_OK)
+                st = m_status ? m_status : ESPDL_ERR_CUDA;
+        }
+    }
+    if (!st)
+        st = espdl_b200_graph_launch(graph, ctx->stream);
+    if (st)
+        m_status = st;
+    return st ? ESP_FAIL : ESP_OK;
+}
+
 void Model::run(runtime_mode_t mode)
 {
     (void)mode;
@@ -958,14 +1002,16 @@ esp_err_t Model::submit()
         return ESP_FAIL;
     ModelContext *ctx = m_model_context;
     int st = ESPDL_OK;
+    // Upload straight into the input tensors when the plan has steps that never read them (see m_input_steps)
+    const bool direct = m_input_steps > 0 && m_input_steps < (int)m_execution_plan.size() && env_flag("ESPDL_B200_DIRECT_UPLOAD", true);
     if (!m_copy_stream) {
-        // first use: second stream, events, a device staging buffer per input, two pinned slots per output
+        // first use: second stream, events, a device staging buffer per input (unless uploads go direct), two pinned slots per output
         st = espdl_b200_stream_create(&m_copy_stream);
         if (!st) st = espdl_b200_event_create(&m_ev_uploaded);
         if (!st) st = espdl_b200_event_create(&m_ev_consumed);
         for (int s = 0; s < 2 && !st; s++) st = espdl_b200_event_create(&m_ev_done[s]);
         for (auto &kv : m_inputs)
-            if (!st)
+            if (!st && !direct)
                 st = espdl_b200_arena_alloc(kv.second->get_bytes(), &m_in_stage[kv.first]);
         for (int s = 0; s < 2; s++)
             for (auto &kv : m_outputs)
@@ -974,22 +1020,31 @@ esp_err_t Model::submit()
         if (!st && !m_graph && m_use_graph) // capture the plan before the first pipelined pass
             st = run_device(true) == ESP_OK ? ESPDL_OK : (m_status ? m_status : ESPDL_ERR_CUDA);
     }
-    // upload on the copy stream as soon as the previous submission has taken its inputs out of the staging buffers
+    // upload on the copy stream as soon as the previous submission no longer needs the destination: its staging buffers
+    // copied out, or (direct) its steps that read the input tensors finished
     if (!st && m_submitted > 0)
         st = espdl_b200_stream_wait_event(m_copy_stream, m_ev_consumed);
     for (auto &kv : m_inputs)
         if (!st && kv.second->data)
-            st = espdl_b200_upload(m_in_stage[kv.first], kv.second->data, kv.second->get_bytes(), m_copy_stream);
+            st = espdl_b200_upload(direct ? kv.second->device : m_in_stage[kv.first], kv.second->data, kv.second->get_bytes(), m_copy_stream);
     if (!st) st = espdl_b200_event_record(m_ev_uploaded, m_copy_stream);
     if (!st) st = espdl_b200_event_sync(m_ev_uploaded); // the host buffers are free again when submit() returns
-    // plan on the compute stream: staging -> input tensors, forward pass, outputs -> this submission's pinned slot
+    // plan on the compute stream: (staging -> input tensors,) forward pass, outputs -> this submission's pinned slot
     if (!st) st = espdl_b200_stream_wait_event(ctx->stream, m_ev_uploaded);
-    for (auto &kv : m_inputs)
-        if (!st)
-            st = espdl_b200_device_copy(kv.second->device, m_in_stage[kv.first], kv.second->get_bytes(), ctx->stream);
-    if (!st) st = espdl_b200_event_record(m_ev_consumed, ctx->stream);
-    if (!st && run_device(false) != ESP_OK)
-        st = m_status ? m_status : ESPDL_ERR_CUDA;
+    if (direct) {
+        if (!st && run_part(true) != ESP_OK)
+            st = m_status ? m_status : ESPDL_ERR_CUDA;
+        if (!st) st = espdl_b200_event_record(m_ev_consumed, ctx->stream);
+        if (!st && run_part(false) != ESP_OK)
+            st = m_status ? m_status : ESPDL_ERR_CUDA;
+    } else {
+        for (auto &kv : m_inputs)
+            if (!st)
+                st = espdl_b200_device_copy(kv.second->device, m_in_stage[kv.first], kv.second->get_bytes(), ctx->stream);
+        if (!st) st = espdl_b200_event_record(m_ev_consumed, ctx->stream);
+        if (!st && run_device(false) != ESP_OK)
+            st = m_status ? m_status : ESPDL_ERR_CUDA;
+    }
     const int slot = (int)(m_submitted & 1);
     for (auto &kv : m_outputs)
         if (!st)

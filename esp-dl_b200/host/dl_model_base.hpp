@@ -138,6 +138,12 @@ protected:
     void *m_arena = nullptr;
     size_t m_arena_bytes = 0;
     void *m_graph = nullptr;
+    // Pipelined passes (submit / wait) run the plan in two parts: the steps that read a graph input, then the rest.  Once the
+    // first part of a pass is done its input buffers are free again, so the next pass's upload goes straight into them while
+    // the second part runs - no staging copy.  m_input_steps = number of leading steps that belong to the first part.
+    void *m_graph_head = nullptr, *m_graph_tail = nullptr;
+    int m_input_steps = 0;
+    esp_err_t run_part(bool head);
     // submit()/wait() state
     void *m_copy_stream = nullptr, *m_ev_uploaded = nullptr, *m_ev_consumed = nullptr, *m_ev_done[2] = {nullptr, nullptr};
     std::map<std::string, void *> m_in_stage;                 ///< device staging buffer per graph input
