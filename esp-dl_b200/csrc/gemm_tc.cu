@@ -940,8 +940,20 @@ bool plan(const espdl_conv_desc &d, TcParams &p, bool force_direct = false)
         }
     }
     size_t out_bytes = 4 * (size_t)((BLOCK_M * p.out_pw + 1023) & ~1023);
-    const size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
+    size_t stage_bytes = (size_t)(i16 ? 2 : 1) * (BLOCK_M + p.block_n) * p.swz;
     int stages = (int)((SMEM_BUDGET - aux_bytes(p) - out_bytes - 1024) / stage_bytes);
+    // A wide tile with a reduction of two 128-byte blocks and room for only two or three stages has barely one tile's loads
+    // in flight, and every tile then waits a full load latency (192 -> 256 columns over 3.3 M rows: 0.39 ms).  Blocks of 64
+    // bytes make stages half as large: more of them, more tiles in flight (0.28 ms), although the TMA unit moves 64-byte
+    // rows more slowly - so only where the 128-byte form is starved.
+    if (!i16 && p.swz == 128 && p.k_blocks == 2 && stages < 3 * p.k_blocks / 2 + 1 && !getenv("ESPDL_B200_NO_NARROW_K")) {
+        const size_t stage64 = (size_t)(BLOCK_M + p.block_n) * 64;
+        const int kb64 = (p.K + 63) / 64;
+        const int stages64 = (int)std::min<size_t>((SMEM_BUDGET - aux_bytes(p) - out_bytes - 1024) / stage64, MAX_STAGES);
+        if (stages64 * p.k_blocks > stages * kb64) { // more tiles in flight
+            p.swz = 64, p.k_blocks = kb64, stage_bytes = stage64, stages = stages64;
+        }
+    }
     if (p.out_pw && p.k_blocks > 2 && stages < 4) {
         // a long reduction needs the deep load pipeline more than the output needs staging
         p.out_pw = 0, p.out_mask = 0, out_bytes = 0;

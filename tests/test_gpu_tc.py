@@ -357,3 +357,15 @@ def test_conv_with_per_channel_tables(kw, act):
     np.testing.assert_array_equal(gpu_util.run_conv_gpu(case), want)
     one = dict(case, lut=np.ascontiguousarray(case["lut"][:256]))        # the same conv with the first channel's table for all
     assert not np.array_equal(gpu_util.run_conv_oracle(one), want)
+
+
+@pytest.mark.parametrize("m,k,n", [(3000, 192, 256), (1000, 256, 256), (700, 160, 960), (900, 144, 250)])
+def test_wide_tiles_with_two_k_blocks_take_64_byte_stages(m, k, n, monkeypatch):
+    """Reductions of two 128-byte blocks under 256-column tiles leave room for two or three stages only; the plan then
+    halves the blocks (64-byte swizzle, more stages in flight).  Same bytes either way."""
+    case = cases.gemm_case(seed=k + n, m=m, k=k, n_out=n, per_channel=True, e_in=-7, e_out=-5, e_w=(-9, -7), act=abi.ACT_RELU)
+    want = gpu_util.run_conv_oracle(case)
+    assert want.std() > 5
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
+    monkeypatch.setenv("ESPDL_B200_NO_NARROW_K", "1")
+    np.testing.assert_array_equal(gpu_util.run_conv_gpu(case, kernel=abi.KERNEL_TCGEN05), want)
