@@ -378,6 +378,72 @@ __global__ void __launch_bounds__(256) copy_transpose_words_kernel(CopyParams p,
     }
 }
 
+// Byte transposes with 4 x 4 blocks turned in registers: a thread reads one word from each of four consecutive source rows,
+// eight byte permutes give the four words of the transposed block, which go into a shared-memory tile already in
+// destination order; the tile then leaves as whole words (16 bytes per thread where rows allow), 64 contiguous bytes per
+// destination row.  No byte-granular shared-memory traffic on either side.  Same preconditions as the word kernel above
+// (extents, strides and pointers multiples of 4).
+__global__ void __launch_bounds__(256) copy_transpose_bytes4_kernel(CopyParams p, int ya, long long tiles, int vec16)
+{
+    constexpr int TILE = 64, PITCH = TILE + 4; // 17 words per destination row: the block stores meet two-way conflicts at most
+    __shared__ __align__(16) unsigned char tile[TILE * PITCH];
+    const int nx = p.shape[5], ny = p.shape[ya];
+    const int tx_count = (nx + TILE - 1) / TILE, ty_count = (ny + TILE - 1) / TILE;
+    for (long long t = blockIdx.x; t < tiles; t += gridDim.x) {
+        long long r = t;
+        const int x0 = (int)(r % tx_count) * TILE;
+        r /= tx_count;
+        const int y0 = (int)(r % ty_count) * TILE;
+        r /= ty_count;
+        long long si = 0, di = 0;
+#pragma unroll
+        for (int k = 4; k >= 0; k--) {
+            if (k == ya)
+                continue;
+            const int idx = (int)(r % p.shape[k]);
+            r /= p.shape[k];
+            si += idx * p.ss[k];
+            di += idx * p.ds[k];
+        }
+        const unsigned char *src = (const unsigned char *)p.src + si;
+        unsigned char *dst = (unsigned char *)p.dst + di;
+        __syncthreads();
+        {
+            // source element (x, y) lies at src + x * ss[5] + y: rows of x, contiguous along y
+            const int cw = threadIdx.x & 15, g = threadIdx.x >> 4; // word of the row (4 bytes along y), group of four rows
+            const int y = y0 + 4 * cw, x = x0 + 4 * g;
+            if (y < ny && x < nx) {
+                const unsigned char *sp = src + (long long)x * p.ss[5] + y;
+                const uint32_t r0 = *(const uint32_t *)sp, r1 = *(const uint32_t *)(sp + p.ss[5]), r2 = *(const uint32_t *)(sp + 2 * p.ss[5]),
+                               r3 = *(const uint32_t *)(sp + 3 * p.ss[5]);
+                // bytes (r0.j, r1.j, r2.j, r3.j) -> word j
+                const uint32_t a = __byte_perm(r0, r1, 0x5140), b = __byte_perm(r2, r3, 0x5140); // (r0.0 r1.0 r0.1 r1.1), (r2.0 r3.0 r2.1 r3.1)
+                const uint32_t c = __byte_perm(r0, r1, 0x7362), e = __byte_perm(r2, r3, 0x7362); // (r0.2 r1.2 r0.3 r1.3), ...
+                uint32_t *tp = (uint32_t *)(tile + (4 * cw) * PITCH + 4 * g);
+                tp[0] = __byte_perm(a, b, 0x5410);
+                tp[PITCH / 4] = __byte_perm(a, b, 0x7632);
+                tp[2 * (PITCH / 4)] = __byte_perm(c, e, 0x5410);
+                tp[3 * (PITCH / 4)] = __byte_perm(c, e, 0x7632);
+            }
+        }
+        __syncthreads();
+        {
+            const int xq = threadIdx.x & 3, yy = threadIdx.x >> 2; // 16 bytes of one destination row
+            const int y = y0 + yy, x = x0 + 16 * xq;
+            if (y < ny && x < nx) {
+                const uint32_t *tp = (const uint32_t *)(tile + yy * PITCH + 16 * xq);
+                unsigned char *dp = dst + x + (long long)y * p.ds[ya];
+                const int words = min(4, (nx - x) >> 2);
+                if (vec16 && words == 4) {
+                    *(uint4 *)dp = make_uint4(tp[0], tp[1], tp[2], tp[3]);
+                } else {
+                    for (int i = 0; i < words; i++) ((uint32_t *)dp)[i] = tp[i];
+                }
+            }
+        }
+    }
+}
+
 } // namespace espdl
 
 using namespace espdl;
@@ -722,7 +788,14 @@ extern "C" int espdl_b200_copy(const espdl_copy_desc *d, void *stream)
                 if (k != 5 && p.shape[k] > 1 && p.ds[k] % V != 0)
                     words = false;
             }
-            if (words && es == 1)
+            if (words && es == 1 && !getenv("ESPDL_B200_NO_TRANSPOSE4")) {
+                // 16-byte stores when every destination row starts on a 16-byte boundary
+                bool vec16 = ((uintptr_t)p.dst % 16) == 0;
+                for (int k = 0; k < 5 && vec16; k++)
+                    if (p.shape[k] > 1 && p.ds[k] % 16 != 0)
+                        vec16 = false;
+                copy_transpose_bytes4_kernel<<<grid, 256, 0, s>>>(p, ya, tiles, vec16 ? 1 : 0);
+            } else if (words && es == 1)
                 copy_transpose_words_kernel<uint8_t><<<grid, 256, 0, s>>>(p, ya, tiles);
             else if (words)
                 copy_transpose_words_kernel<uint16_t><<<grid, 256, 0, s>>>(p, ya, tiles);
